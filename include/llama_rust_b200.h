@@ -1,0 +1,163 @@
+/* llama_rust_b200 — C ABI of the B200 (sm_100a) quantized matrix executor.
+ *
+ * Drop-in boundary for the matrix-executor seam of mingley/llama-rust: the
+ * entry points below are what the crate's FFI for this path binds in place of
+ * the `llama_native_cuda` crate (native-cuda/src/gpu.rs) and of
+ * `native_gpu::matmul` (langtax/src/native_gpu.rs:124).  Plain pointers and
+ * sizes only; every function returns an int status, 0 = ok.
+ *
+ * Conventions shared by all entry points (reference behaviour in brackets):
+ *  - dtype tags are the reference's `GemmKind as u8` [langtax/src/quant.rs:6645]:
+ *    F16=0 BF16=1 F32=2 Q5_0=6 Q5_1=7 Q4_0=12 Q8_0=13 Q4_K=17 Q6_K=19.  Any
+ *    other tag is LLR_ERR_DTYPE; there is no CPU fallback [README.md:29-31].
+ *  - activations and results are token-major f32: x[t*cols + c], y[t*rows + r]
+ *    [quant.rs:6264-6267].
+ *  - weights are GGUF packed blocks, rows contiguous without padding; they stay
+ *    packed in device memory and are never expanded to f32.
+ *  - all validation happens before any device work; a failing call leaves the
+ *    output buffer untouched and the executor usable
+ *    [langtax/tests/native_cuda_parity.rs:410-431, native-cuda/src/main.rs:48-66].
+ *  - an executor is not thread-safe: one per inference thread
+ *    [native_gpu.rs:114-116].  Host-pointer calls are synchronous: the output
+ *    is valid on return.
+ */
+#ifndef LLAMA_RUST_B200_H
+#define LLAMA_RUST_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LLR_DTYPE_F16 0
+#define LLR_DTYPE_BF16 1
+#define LLR_DTYPE_F32 2
+#define LLR_DTYPE_Q5_0 6
+#define LLR_DTYPE_Q5_1 7
+#define LLR_DTYPE_Q4_0 12
+#define LLR_DTYPE_Q8_0 13
+#define LLR_DTYPE_Q4_K 17
+#define LLR_DTYPE_Q6_K 19
+
+#define LLR_OK 0
+#define LLR_ERR_INVALID 1   /* bad shape / length / null pointer  [QuantError::Size, ::NativeCuda] */
+#define LLR_ERR_UNALIGNED 2 /* cols not a multiple of the block   [QuantError::UnalignedCols]      */
+#define LLR_ERR_DTYPE 3     /* unsupported dtype tag                                               */
+#define LLR_ERR_OVERFLOW 4  /* a size product overflows           ["... shape overflow"]           */
+#define LLR_ERR_FOREIGN 5   /* matrix belongs to another executor [gpu.rs:286-288]                 */
+#define LLR_ERR_CUDA 6      /* CUDA runtime failure; see llr_exec_last_error                       */
+#define LLR_ERR_OOM 7       /* device allocation failed after dropping cached weights              */
+#define LLR_ERR_CONFIG 8    /* malformed LLAMA_CUDA_CACHE_BYTES   [native_gpu.rs:20-32]            */
+
+typedef struct llr_exec llr_exec;     /* opaque executor: device, stream, scratch, residency */
+typedef struct llr_matrix llr_matrix; /* opaque resident packed matrix, tied to its executor  */
+
+typedef struct llr_counters {
+  uint64_t launches;       /* kernels launched by this executor                     */
+  uint64_t uploads;        /* packed matrices copied host -> device                 */
+  uint64_t upload_bytes;
+  uint64_t resident_bytes; /* packed bytes held by the residency cache              */
+  uint64_t cache_limit;    /* residency budget in bytes (0 = residency disabled)    */
+  uint64_t cache_hits;
+  uint64_t cache_misses;
+  uint64_t evictions;
+  uint64_t h2d_bytes;      /* activation bytes copied host -> device                */
+  uint64_t d2h_bytes;      /* result bytes copied device -> host                    */
+} llr_counters;
+
+/* Replaces CudaGemv::new(device_ordinal) [native-cuda/src/gpu.rs:148]. */
+int llr_exec_create(int device, llr_exec** out);
+int llr_exec_destroy(llr_exec* exec);
+
+/* Replaces CudaGemv::memory_info [gpu.rs:164]: free and total device bytes. */
+int llr_exec_mem_info(llr_exec* exec, size_t* free_bytes, size_t* total_bytes);
+
+/* Message of the last failing call on this executor ("" if none).  With a null
+ * executor: the last failure of llr_exec_create on the calling thread.
+ * Replaces the String of Result<_, String> [gpu.rs] / QuantError::NativeCuda
+ * [quant.rs:4157]. */
+const char* llr_exec_last_error(const llr_exec* exec);
+
+int llr_exec_counters(const llr_exec* exec, llr_counters* out);
+
+/* Diagnostic knob: which decode kernel serves 1..8 activation rows.  0 = pick
+ * automatically, 1 = the shape-agnostic byte-load kernel, 2 = the
+ * shared-memory staged kernel (falls back to 1 for shapes it cannot take).
+ * Also read once from the environment variable LLR_GEMV_PATH
+ * (generic|staged) when the executor is created. */
+int llr_exec_set_path(llr_exec* exec, int path);
+
+/* Packed bytes of one row of `cols` columns.  Replaces the <t>_row_bytes
+ * family [quant.rs:4210-4218 and siblings]. */
+int llr_row_bytes(uint8_t dtype, size_t cols, size_t* out);
+
+/* Copy a packed matrix to the device and keep it resident.  Replaces
+ * CudaGemv::upload [gpu.rs:264], which took F32-expanded weights; this one
+ * takes the GGUF bytes as they are.  rows and cols must be positive and
+ * packed_len == rows * row_bytes(dtype, cols). */
+int llr_matrix_upload(llr_exec* exec, uint8_t dtype, size_t rows, size_t cols,
+                      const void* packed, size_t packed_len, llr_matrix** out);
+/* Same, from packed bytes already in device memory (device-to-device copy). */
+int llr_matrix_upload_device(llr_exec* exec, uint8_t dtype, size_t rows, size_t cols,
+                             const void* packed_dev, size_t packed_len, llr_matrix** out);
+int llr_matrix_free(llr_matrix* matrix);
+int llr_matrix_info(const llr_matrix* matrix, uint8_t* dtype, size_t* rows, size_t* cols,
+                    size_t* packed_bytes);
+
+/* y[rows] = W x.  Replaces CudaGemv::gemv_resident [gpu.rs:280].  Host
+ * pointers; x_len must equal cols and y_len rows. */
+int llr_gemv_resident(llr_exec* exec, const llr_matrix* matrix, const float* x, size_t x_len,
+                      float* y, size_t y_len);
+
+/* y[t*rows + r] for `tokens` activation rows in one call.  Replaces
+ * CudaGemv::gemm_resident [gpu.rs:351].  tokens == 0 is an error. */
+int llr_gemm_resident(llr_exec* exec, const llr_matrix* matrix, size_t tokens, const float* x,
+                      size_t x_len, float* y, size_t y_len);
+
+/* The call the crate makes for every f32-activation matrix product.  Replaces
+ * native_gpu::matmul [langtax/src/native_gpu.rs:124-214] together with the
+ * validation of native_matmul [quant.rs:6683-6758]; the `expand` closure of
+ * the reference is never needed.  Weights are looked up in a device residency
+ * cache keyed by (dtype, rows, cols, length, 128-bit content hash), so the
+ * same bytes at another address hit and changed bytes at the same address miss
+ * [native_cuda_parity.rs:181-187].  The budget is LLAMA_CUDA_CACHE_BYTES
+ * ("auto" or unset: free - max(free/4, 512 MiB); a decimal byte count; 0
+ * disables residency but not execution) [native_gpu.rs:5-9, 34-40] and counts
+ * packed bytes only.  rows == 0 is a successful no-op [quant.rs:6743]. */
+int llr_matmul(llr_exec* exec, uint8_t dtype, size_t rows, size_t cols, size_t tokens,
+               const void* packed, size_t packed_len, const float* x, size_t x_len, float* y,
+               size_t y_len);
+
+/* Device-pointer form of llr_gemm_resident: x_dev and y_dev are device
+ * buffers of tokens*cols and tokens*rows floats; the work is enqueued on
+ * `stream` (a cudaStream_t; null = the executor's own stream) and the call
+ * returns without synchronizing.  An extension with no counterpart in the
+ * reference, whose executor copies through host memory on every call
+ * [gpu.rs:301-334]. */
+int llr_matmul_device(llr_exec* exec, const llr_matrix* matrix, size_t tokens, const float* x_dev,
+                      float* y_dev, void* stream);
+/* Block the calling thread until the executor's own stream is idle. */
+int llr_exec_synchronize(llr_exec* exec);
+
+/* Dequantize rows [row0, row0+n_rows) of a resident matrix to f32 on the
+ * device and copy them to out (n_rows*cols floats, host).  Bit-exact
+ * counterpart of dequant_<t>_row [quant.rs:7511, 7533, 7734, 7884, 7918, 8046,
+ * 8083, 8783]. */
+int llr_dequant_rows(llr_exec* exec, const llr_matrix* matrix, size_t row0, size_t n_rows,
+                     float* out, size_t out_len);
+
+/* Fill a resident matrix with seeded synthetic packed blocks on the device
+ * (uniform quant bits from SplitMix64 [langtax/src/sample.rs:306-312], binary16
+ * scales |n|*0.01 with n an exact-integer Irwin-Hall normal).  Benchmark
+ * input generator; bit-identical to llama_rust_b200.synth on the host. */
+int llr_matrix_synth(llr_exec* exec, uint8_t dtype, size_t rows, size_t cols, uint64_t seed,
+                     llr_matrix** out);
+/* Copy the packed bytes of a resident matrix back to the host. */
+int llr_matrix_download(llr_exec* exec, const llr_matrix* matrix, void* out, size_t out_len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,63 @@
+"""Loads libllama_rust_b200.so (the C ABI of include/llama_rust_b200.h) through ctypes.
+
+There is no fallback: if the shared library is missing or a symbol is absent,
+importing fails with instructions to build it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libllama_rust_b200.so")
+
+# every symbol include/llama_rust_b200.h declares
+SYMBOLS = [
+    "llr_exec_create", "llr_exec_destroy", "llr_exec_mem_info", "llr_exec_last_error",
+    "llr_exec_counters", "llr_exec_set_path", "llr_row_bytes", "llr_matrix_upload",
+    "llr_matrix_upload_device", "llr_matrix_free", "llr_matrix_info", "llr_gemv_resident",
+    "llr_gemm_resident", "llr_matmul", "llr_matmul_device", "llr_exec_synchronize",
+    "llr_dequant_rows", "llr_matrix_synth", "llr_matrix_download",
+]
+
+
+class Counters(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in (
+        "launches", "uploads", "upload_bytes", "resident_bytes", "cache_limit", "cache_hits",
+        "cache_misses", "evictions", "h2d_bytes", "d2h_bytes")]
+
+
+def load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m llama_rust_b200.build` "
+            "(needs nvcc; there is no CPU fallback)")
+    lib = C.CDLL(LIB_PATH)
+    missing = [s for s in SYMBOLS if not hasattr(lib, s)]
+    if missing:
+        raise ImportError(f"{LIB_PATH} lacks symbols {missing}; rebuild it")
+    vp, sz, u8 = C.c_void_p, C.c_size_t, C.c_uint8
+    lib.llr_exec_create.argtypes = [C.c_int, C.POINTER(vp)]
+    lib.llr_exec_destroy.argtypes = [vp]
+    lib.llr_exec_mem_info.argtypes = [vp, C.POINTER(sz), C.POINTER(sz)]
+    lib.llr_exec_last_error.argtypes = [vp]
+    lib.llr_exec_last_error.restype = C.c_char_p
+    lib.llr_exec_counters.argtypes = [vp, C.POINTER(Counters)]
+    lib.llr_exec_set_path.argtypes = [vp, C.c_int]
+    lib.llr_row_bytes.argtypes = [u8, sz, C.POINTER(sz)]
+    lib.llr_matrix_upload.argtypes = [vp, u8, sz, sz, vp, sz, C.POINTER(vp)]
+    lib.llr_matrix_upload_device.argtypes = [vp, u8, sz, sz, vp, sz, C.POINTER(vp)]
+    lib.llr_matrix_free.argtypes = [vp]
+    lib.llr_matrix_info.argtypes = [vp, C.POINTER(u8), C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]
+    lib.llr_gemv_resident.argtypes = [vp, vp, vp, sz, vp, sz]
+    lib.llr_gemm_resident.argtypes = [vp, vp, sz, vp, sz, vp, sz]
+    lib.llr_matmul.argtypes = [vp, u8, sz, sz, sz, vp, sz, vp, sz, vp, sz]
+    lib.llr_matmul_device.argtypes = [vp, vp, sz, vp, vp, vp]
+    lib.llr_exec_synchronize.argtypes = [vp]
+    lib.llr_dequant_rows.argtypes = [vp, vp, sz, sz, vp, sz]
+    lib.llr_matrix_synth.argtypes = [vp, u8, sz, sz, C.c_uint64, C.POINTER(vp)]
+    lib.llr_matrix_download.argtypes = [vp, vp, vp, sz]
+    for s in SYMBOLS:
+        if s != "llr_exec_last_error":
+            getattr(lib, s).restype = C.c_int
+    return lib

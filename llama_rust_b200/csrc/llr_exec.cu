@@ -1,0 +1,640 @@
+// C ABI of the matrix executor: validation, device residency of packed
+// weights, host<->device staging and kernel dispatch.
+//
+// Plays the role of two reference components at once: the `CudaGemv` executor
+// (native-cuda/src/gpu.rs:126-418: context, stream, scratch reuse, upload,
+// gemv/gemm_resident) and the crate-side dispatcher `native_gpu::matmul`
+// (langtax/src/native_gpu.rs:124-214: content-identity residency with a byte
+// budget).  Differences by design: weights stay packed on the device (the
+// reference expands to F32 on a miss), identity is a 128-bit content hash
+// instead of a retained host copy of every matrix, and the budget counts
+// packed bytes only.
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <list>
+#include <new>
+#include <string>
+#include <unordered_set>
+
+#include "../../include/llama_rust_b200.h"
+#include "llr_formats.cuh"
+#include "llr_kernels.cuh"
+
+using namespace llr;
+
+struct llr_matrix {
+  llr_exec* owner;   // null once the owning executor is gone
+  uint8_t* dev;
+  size_t bytes;      // packed bytes (allocation is padded beyond this)
+  int dtype;
+  int64_t rows, cols, row_bytes;
+};
+
+namespace {
+
+constexpr size_t PAD = 256;  // readable slack after the last row (16-byte copy windows)
+constexpr size_t MIN_HEADROOM = 512ull << 20;  // native_gpu.rs:16
+
+struct Hash128 {
+  uint64_t a, b;
+  bool operator==(const Hash128& o) const { return a == o.a && b == o.b; }
+};
+
+inline uint64_t rotl(uint64_t v, int s) { return (v << s) | (v >> (64 - s)); }
+inline uint64_t fmix(uint64_t k) {
+  k ^= k >> 33; k *= 0xff51afd7ed558ccdull; k ^= k >> 33; k *= 0xc4ceb9fe1a85ec53ull; k ^= k >> 33;
+  return k;
+}
+
+// 128-bit content fingerprint of the packed bytes: four independent
+// multiply-rotate lanes over 32-byte strides, folded with the length.
+Hash128 content_hash(const uint8_t* p, size_t n) {
+  uint64_t l0 = 0x9E3779B97F4A7C15ull, l1 = 0xC2B2AE3D27D4EB4Full, l2 = 0x165667B19E3779F9ull,
+           l3 = 0x27D4EB2F165667C5ull;
+  size_t i = 0;
+  for (; i + 32 <= n; i += 32) {
+    uint64_t w[4];
+    std::memcpy(w, p + i, 32);
+    l0 = rotl((l0 ^ w[0]) * 0x9FB21C651E98DF25ull, 29);
+    l1 = rotl((l1 ^ w[1]) * 0xD6E8FEB86659FD93ull, 31);
+    l2 = rotl((l2 ^ w[2]) * 0xA0761D6478BD642Full, 27);
+    l3 = rotl((l3 ^ w[3]) * 0xE7037ED1A0B428DBull, 33);
+  }
+  uint8_t tail[32] = {0};
+  if (i < n) {
+    std::memcpy(tail, p + i, n - i);
+    uint64_t w[4];
+    std::memcpy(w, tail, 32);
+    l0 = rotl((l0 ^ w[0]) * 0x9FB21C651E98DF25ull, 29);
+    l1 = rotl((l1 ^ w[1]) * 0xD6E8FEB86659FD93ull, 31);
+    l2 = rotl((l2 ^ w[2]) * 0xA0761D6478BD642Full, 27);
+    l3 = rotl((l3 ^ w[3]) * 0xE7037ED1A0B428DBull, 33);
+  }
+  Hash128 h;
+  h.a = fmix(l0 ^ rotl(l1, 17) ^ (uint64_t)n) + fmix(l2 + 0x52DCE729ull);
+  h.b = fmix(l3 ^ rotl(l2, 23) ^ ((uint64_t)n * 0x9E3779B97F4A7C15ull)) + fmix(l1 ^ l0);
+  return h;
+}
+
+struct CacheEntry {
+  int dtype;
+  int64_t rows, cols;
+  size_t len;
+  Hash128 hash;
+  llr_matrix* mat;
+};
+
+thread_local std::string g_create_error;
+
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+    else prev = -1;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+}  // namespace
+
+struct llr_exec {
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  llr_counters ctr{};
+  int path = PATH_AUTO;
+  // activation / result staging
+  float* pin_x = nullptr; size_t pin_x_cap = 0;
+  float* pin_y = nullptr; size_t pin_y_cap = 0;
+  float* dev_x = nullptr; size_t dev_x_cap = 0;
+  float* dev_y = nullptr; size_t dev_y_cap = 0;
+  // residency
+  std::list<CacheEntry> cache;  // front = least recently used
+  bool limit_resolved = false;
+  size_t limit = 0;
+  std::unordered_set<llr_matrix*> live;
+};
+
+namespace {
+
+int fail(llr_exec* e, int code, const std::string& msg) {
+  if (e) e->err = msg;
+  return code;
+}
+int fail_cuda(llr_exec* e, cudaError_t ce, const char* what) {
+  cudaGetLastError();  // clear the sticky-less error state
+  const int code = ce == cudaErrorMemoryAllocation ? LLR_ERR_OOM : LLR_ERR_CUDA;
+  return fail(e, code, std::string(what) + ": " + cudaGetErrorString(ce));
+}
+
+bool mul_ok(size_t a, size_t b, size_t* out) {
+  if (a != 0 && b > SIZE_MAX / a) return false;
+  *out = a * b;
+  return true;
+}
+
+int row_bytes_checked(int dtype, size_t cols, size_t* out, std::string* msg) {
+  const int be = block_elems(dtype);
+  if (be == 0) {
+    *msg = "unsupported dtype tag " + std::to_string(dtype) + " (no CPU fallback)";
+    return LLR_ERR_DTYPE;
+  }
+  if (cols % (size_t)be != 0) {
+    *msg = "n_cols " + std::to_string(cols) + " is not a multiple of the block width " +
+           std::to_string(be);
+    return LLR_ERR_UNALIGNED;
+  }
+  if (!mul_ok(cols / (size_t)be, (size_t)block_bytes(dtype), out)) {
+    *msg = "weight shape overflow";
+    return LLR_ERR_OVERFLOW;
+  }
+  return LLR_OK;
+}
+
+template <class T>
+cudaError_t grow_pinned(T** p, size_t* cap, size_t need) {
+  if (need <= *cap) return cudaSuccess;
+  size_t ncap = *cap ? *cap : 4096;
+  while (ncap < need) ncap *= 2;
+  T* np_ = nullptr;
+  cudaError_t ce = cudaMallocHost((void**)&np_, ncap * sizeof(T));
+  if (ce != cudaSuccess) return ce;
+  if (*p) cudaFreeHost(*p);
+  *p = np_;
+  *cap = ncap;
+  return cudaSuccess;
+}
+
+template <class T>
+cudaError_t grow_device(T** p, size_t* cap, size_t need) {
+  if (need <= *cap) return cudaSuccess;
+  size_t ncap = *cap ? *cap : 4096;
+  while (ncap < need) ncap *= 2;
+  T* np_ = nullptr;
+  cudaError_t ce = cudaMalloc((void**)&np_, ncap * sizeof(T));
+  if (ce != cudaSuccess) return ce;
+  if (*p) cudaFree(*p);
+  *p = np_;
+  *cap = ncap;
+  return cudaSuccess;
+}
+
+void drop_entry(llr_exec* e, std::list<CacheEntry>::iterator it) {
+  e->ctr.resident_bytes -= it->len;
+  ++e->ctr.evictions;
+  llr_matrix* m = it->mat;
+  e->cache.erase(it);
+  e->live.erase(m);
+  cudaFree(m->dev);
+  delete m;
+}
+
+void drop_all_cached(llr_exec* e) {
+  while (!e->cache.empty()) drop_entry(e, e->cache.begin());
+}
+
+// LLAMA_CUDA_CACHE_BYTES, native_gpu.rs:19-54
+int resolve_limit(llr_exec* e) {
+  if (e->limit_resolved) return LLR_OK;
+  const char* v = std::getenv("LLAMA_CUDA_CACHE_BYTES");
+  if (v && std::strcmp(v, "auto") != 0) {
+    const size_t n = std::strlen(v);
+    bool digits = n > 0;
+    for (size_t i = 0; i < n; ++i) digits = digits && v[i] >= '0' && v[i] <= '9';
+    if (!digits)
+      return fail(e, LLR_ERR_CONFIG,
+                  "LLAMA_CUDA_CACHE_BYTES must be auto or a nonnegative decimal byte count");
+    size_t acc = 0;
+    for (size_t i = 0; i < n; ++i) {
+      const size_t dg = (size_t)(v[i] - '0');
+      if (acc > (SIZE_MAX - dg) / 10)
+        return fail(e, LLR_ERR_CONFIG, "LLAMA_CUDA_CACHE_BYTES exceeds addressable memory");
+      acc = acc * 10 + dg;
+    }
+    e->limit = acc;
+  } else {
+    size_t fr = 0, tot = 0;
+    cudaError_t ce = cudaMemGetInfo(&fr, &tot);
+    if (ce != cudaSuccess) return fail_cuda(e, ce, "cudaMemGetInfo");
+    const size_t avail = fr < tot ? fr : tot;  // native_gpu.rs:34-40
+    const size_t reserve = avail / 4 > MIN_HEADROOM ? avail / 4 : MIN_HEADROOM;
+    e->limit = avail > reserve ? avail - reserve : 0;
+  }
+  e->limit_resolved = true;
+  e->ctr.cache_limit = e->limit;
+  return LLR_OK;
+}
+
+int alloc_matrix(llr_exec* e, int dtype, size_t rows, size_t cols, size_t rb, size_t bytes,
+                 llr_matrix** out) {
+  uint8_t* dev = nullptr;
+  cudaError_t ce = cudaMalloc((void**)&dev, bytes + PAD);
+  if (ce == cudaErrorMemoryAllocation) {
+    // cached weights must never keep an otherwise viable matrix from fitting (gpu.rs:198-210)
+    cudaGetLastError();
+    drop_all_cached(e);
+    ce = cudaMalloc((void**)&dev, bytes + PAD);
+  }
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "device allocation for packed weights");
+  ce = cudaMemsetAsync(dev + bytes, 0, PAD, e->stream);
+  if (ce != cudaSuccess) { cudaFree(dev); return fail_cuda(e, ce, "cudaMemsetAsync"); }
+  llr_matrix* m = new (std::nothrow) llr_matrix{e, dev, bytes, dtype, (int64_t)rows, (int64_t)cols,
+                                                (int64_t)rb};
+  if (!m) { cudaFree(dev); return fail(e, LLR_ERR_OOM, "host allocation failed"); }
+  e->live.insert(m);
+  *out = m;
+  return LLR_OK;
+}
+
+void release_matrix(llr_exec* e, llr_matrix* m) {
+  e->live.erase(m);
+  cudaFree(m->dev);
+  delete m;
+}
+
+int check_matrix(llr_exec* e, const llr_matrix* m) {
+  if (!m) return fail(e, LLR_ERR_INVALID, "null matrix");
+  if (m->owner != e) return fail(e, LLR_ERR_FOREIGN, "CUDA matrix belongs to a different executor");
+  return LLR_OK;
+}
+
+MatView view_of(const llr_matrix* m) {
+  return MatView{m->dev, m->dtype, m->rows, m->cols, m->row_bytes};
+}
+
+bool is_pinned_host(const void* p) {
+  cudaPointerAttributes a{};
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+  return a.type == cudaMemoryTypeHost;
+}
+
+// H2D of the activations, launch, D2H of the result, synchronize (gpu.rs:301-334,
+// 381-416).  `y` is written only after everything succeeded.
+int run_host(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, float* y) {
+  const size_t nx = tokens * (size_t)m->cols, ny = tokens * (size_t)m->rows;
+  cudaError_t ce;
+  if ((ce = grow_device(&e->dev_x, &e->dev_x_cap, nx)) != cudaSuccess) return fail_cuda(e, ce, "activation scratch");
+  if ((ce = grow_device(&e->dev_y, &e->dev_y_cap, ny)) != cudaSuccess) return fail_cuda(e, ce, "result scratch");
+  const float* src = x;
+  if (!is_pinned_host(x)) {
+    if ((ce = grow_pinned(&e->pin_x, &e->pin_x_cap, nx)) != cudaSuccess) return fail_cuda(e, ce, "pinned activation staging");
+    std::memcpy(e->pin_x, x, nx * sizeof(float));
+    src = e->pin_x;
+  }
+  const bool y_pinned = is_pinned_host(y);
+  float* dst = y;
+  if (!y_pinned) {
+    if ((ce = grow_pinned(&e->pin_y, &e->pin_y_cap, ny)) != cudaSuccess) return fail_cuda(e, ce, "pinned result staging");
+    dst = e->pin_y;
+  }
+  if ((ce = cudaMemcpyAsync(e->dev_x, src, nx * sizeof(float), cudaMemcpyHostToDevice, e->stream)) != cudaSuccess)
+    return fail_cuda(e, ce, "activation upload");
+  if ((ce = launch_matmul(view_of(m), e->dev_x, e->dev_y, (int64_t)tokens, e->stream, e->path,
+                          e->sm_count, &e->ctr.launches)) != cudaSuccess)
+    return fail_cuda(e, ce, "kernel launch");
+  if ((ce = cudaMemcpyAsync(dst, e->dev_y, ny * sizeof(float), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess)
+    return fail_cuda(e, ce, "result download");
+  if ((ce = cudaStreamSynchronize(e->stream)) != cudaSuccess) return fail_cuda(e, ce, "stream synchronize");
+  if (!y_pinned) std::memcpy(y, e->pin_y, ny * sizeof(float));
+  e->ctr.h2d_bytes += nx * sizeof(float);
+  e->ctr.d2h_bytes += ny * sizeof(float);
+  return LLR_OK;
+}
+
+}  // namespace
+
+namespace llr {
+
+cudaError_t launch_matmul(const MatView& m, const float* x, float* y, int64_t tokens,
+                          cudaStream_t stream, int path, int sm_count, uint64_t* launches) {
+  const bool x_aligned = ((uintptr_t)x & 15) == 0 && (m.cols % 4 == 0);
+  const bool staged_ok = gemv_staged_supported(m) && x_aligned;
+  if (path == PATH_GENERIC || !staged_ok) return launch_gemv_generic(m, x, y, tokens, stream, launches);
+  return launch_gemv_staged(m, x, y, tokens, stream, sm_count, launches);
+}
+
+}  // namespace llr
+
+extern "C" {
+
+int llr_exec_create(int device, llr_exec** out) {
+  if (!out) { g_create_error = "null output pointer"; return LLR_ERR_INVALID; }
+  *out = nullptr;
+  int n = 0;
+  cudaError_t ce = cudaGetDeviceCount(&n);
+  if (ce != cudaSuccess) {
+    cudaGetLastError();
+    g_create_error = std::string("no usable CUDA device: ") + cudaGetErrorString(ce);
+    return LLR_ERR_CUDA;
+  }
+  if (device < 0 || device >= n) {
+    g_create_error = "device ordinal " + std::to_string(device) + " out of range";
+    return LLR_ERR_INVALID;
+  }
+  DeviceGuard guard(device);
+  llr_exec* e = new (std::nothrow) llr_exec();
+  if (!e) { g_create_error = "host allocation failed"; return LLR_ERR_OOM; }
+  e->device = device;
+  cudaDeviceProp prop{};
+  if ((ce = cudaGetDeviceProperties(&prop, device)) != cudaSuccess ||
+      (ce = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking)) != cudaSuccess) {
+    cudaGetLastError();
+    g_create_error = std::string("CUDA initialisation failed: ") + cudaGetErrorString(ce);
+    delete e;
+    return LLR_ERR_CUDA;
+  }
+  if (prop.major < 10) {
+    g_create_error = std::string("device ") + prop.name + " is sm_" + std::to_string(prop.major) +
+                     std::to_string(prop.minor) + "; this library is built for sm_100a only";
+    cudaStreamDestroy(e->stream);
+    delete e;
+    return LLR_ERR_CUDA;
+  }
+  e->sm_count = prop.multiProcessorCount;
+  if (const char* p = std::getenv("LLR_GEMV_PATH")) {
+    if (!std::strcmp(p, "generic")) e->path = PATH_GENERIC;
+    else if (!std::strcmp(p, "staged")) e->path = PATH_STAGED;
+  }
+  *out = e;
+  return LLR_OK;
+}
+
+int llr_exec_destroy(llr_exec* e) {
+  if (!e) return LLR_OK;
+  DeviceGuard guard(e->device);
+  cudaStreamSynchronize(e->stream);
+  drop_all_cached(e);
+  for (llr_matrix* m : e->live) {  // handles the caller still holds: free the device side
+    cudaFree(m->dev);
+    m->dev = nullptr;
+    m->owner = nullptr;
+  }
+  if (e->pin_x) cudaFreeHost(e->pin_x);
+  if (e->pin_y) cudaFreeHost(e->pin_y);
+  if (e->dev_x) cudaFree(e->dev_x);
+  if (e->dev_y) cudaFree(e->dev_y);
+  cudaStreamDestroy(e->stream);
+  cudaGetLastError();
+  delete e;
+  return LLR_OK;
+}
+
+int llr_exec_mem_info(llr_exec* e, size_t* free_bytes, size_t* total_bytes) {
+  if (!e || !free_bytes || !total_bytes) return fail(e, LLR_ERR_INVALID, "null argument");
+  DeviceGuard guard(e->device);
+  cudaError_t ce = cudaMemGetInfo(free_bytes, total_bytes);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "cudaMemGetInfo");
+  return LLR_OK;
+}
+
+const char* llr_exec_last_error(const llr_exec* e) { return e ? e->err.c_str() : g_create_error.c_str(); }
+
+int llr_exec_counters(const llr_exec* e, llr_counters* out) {
+  if (!e || !out) return LLR_ERR_INVALID;
+  *out = e->ctr;
+  return LLR_OK;
+}
+
+int llr_exec_set_path(llr_exec* e, int path) {
+  if (!e || path < PATH_AUTO || path > PATH_STAGED) return LLR_ERR_INVALID;
+  e->path = path;
+  return LLR_OK;
+}
+
+int llr_row_bytes(uint8_t dtype, size_t cols, size_t* out) {
+  if (!out) return LLR_ERR_INVALID;
+  std::string msg;
+  return row_bytes_checked(dtype, cols, out, &msg);
+}
+
+static int upload_common(llr_exec* e, uint8_t dtype, size_t rows, size_t cols, const void* packed,
+                         size_t packed_len, bool from_device, llr_matrix** out) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!out) return fail(e, LLR_ERR_INVALID, "null output pointer");
+  *out = nullptr;
+  if (rows == 0 || cols == 0) return fail(e, LLR_ERR_INVALID, "GEMV dimensions must be positive");
+  size_t rb = 0, expect = 0;
+  std::string msg;
+  int rc = row_bytes_checked(dtype, cols, &rb, &msg);
+  if (rc) return fail(e, rc, msg);
+  if (!mul_ok(rb, rows, &expect)) return fail(e, LLR_ERR_OVERFLOW, "GEMV shape overflow");
+  if (packed_len != expect || !packed)
+    return fail(e, LLR_ERR_INVALID, "GEMV buffer lengths do not match shape");
+  DeviceGuard guard(e->device);
+  llr_matrix* m = nullptr;
+  if ((rc = alloc_matrix(e, dtype, rows, cols, rb, expect, &m)) != LLR_OK) return rc;
+  cudaError_t ce = cudaMemcpyAsync(m->dev, packed, expect,
+                                   from_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
+                                   e->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+  if (ce != cudaSuccess) { release_matrix(e, m); return fail_cuda(e, ce, "weight upload"); }
+  ++e->ctr.uploads;
+  e->ctr.upload_bytes += expect;
+  *out = m;
+  return LLR_OK;
+}
+
+int llr_matrix_upload(llr_exec* e, uint8_t dtype, size_t rows, size_t cols, const void* packed,
+                      size_t packed_len, llr_matrix** out) {
+  return upload_common(e, dtype, rows, cols, packed, packed_len, false, out);
+}
+
+int llr_matrix_upload_device(llr_exec* e, uint8_t dtype, size_t rows, size_t cols,
+                             const void* packed_dev, size_t packed_len, llr_matrix** out) {
+  return upload_common(e, dtype, rows, cols, packed_dev, packed_len, true, out);
+}
+
+int llr_matrix_free(llr_matrix* m) {
+  if (!m) return LLR_OK;
+  if (m->owner) {
+    DeviceGuard guard(m->owner->device);
+    cudaStreamSynchronize(m->owner->stream);
+    release_matrix(m->owner, m);
+  } else {
+    delete m;
+  }
+  return LLR_OK;
+}
+
+int llr_matrix_info(const llr_matrix* m, uint8_t* dtype, size_t* rows, size_t* cols,
+                    size_t* packed_bytes) {
+  if (!m) return LLR_ERR_INVALID;
+  if (dtype) *dtype = (uint8_t)m->dtype;
+  if (rows) *rows = (size_t)m->rows;
+  if (cols) *cols = (size_t)m->cols;
+  if (packed_bytes) *packed_bytes = m->bytes;
+  return LLR_OK;
+}
+
+int llr_gemm_resident(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, size_t x_len,
+                      float* y, size_t y_len) {
+  if (!e) return LLR_ERR_INVALID;
+  int rc = check_matrix(e, m);
+  if (rc) return rc;
+  size_t nx = 0, ny = 0;
+  if (!mul_ok(tokens, (size_t)m->cols, &nx)) return fail(e, LLR_ERR_OVERFLOW, "CUDA GEMM input shape overflow");
+  if (!mul_ok(tokens, (size_t)m->rows, &ny)) return fail(e, LLR_ERR_OVERFLOW, "CUDA GEMM output shape overflow");
+  if (tokens == 0 || x_len != nx || y_len != ny || !x || !y)
+    return fail(e, LLR_ERR_INVALID, "CUDA GEMM buffer lengths do not match shape");
+  DeviceGuard guard(e->device);
+  return run_host(e, m, tokens, x, y);
+}
+
+int llr_gemv_resident(llr_exec* e, const llr_matrix* m, const float* x, size_t x_len, float* y,
+                      size_t y_len) {
+  if (!e) return LLR_ERR_INVALID;
+  int rc = check_matrix(e, m);
+  if (rc) return rc;
+  if (x_len != (size_t)m->cols || y_len != (size_t)m->rows || !x || !y)
+    return fail(e, LLR_ERR_INVALID, "CUDA GEMV vector lengths do not match resident matrix");
+  DeviceGuard guard(e->device);
+  return run_host(e, m, 1, x, y);
+}
+
+int llr_matmul(llr_exec* e, uint8_t dtype, size_t rows, size_t cols, size_t tokens,
+               const void* packed, size_t packed_len, const float* x, size_t x_len, float* y,
+               size_t y_len) {
+  if (!e) return LLR_ERR_INVALID;
+  // native_matmul, quant.rs:6698-6745
+  if (tokens == 0 || cols == 0 || y_len % tokens != 0)
+    return fail(e, LLR_ERR_INVALID, "matrix dimensions must be positive and token-aligned");
+  size_t nx = 0;
+  if (!mul_ok(tokens, cols, &nx)) return fail(e, LLR_ERR_OVERFLOW, "input shape overflow");
+  if (x_len != nx)
+    return fail(e, LLR_ERR_INVALID, "X F32 elems: expected " + std::to_string(nx) + ", got " + std::to_string(x_len));
+  if (y_len / tokens != rows)
+    return fail(e, LLR_ERR_INVALID, "Y F32 elems do not match rows x tokens");
+  size_t rb = 0, expect = 0;
+  std::string msg;
+  int rc = row_bytes_checked(dtype, cols, &rb, &msg);
+  if (rc) return fail(e, rc, msg);
+  if (!mul_ok(rb, rows, &expect)) return fail(e, LLR_ERR_OVERFLOW, "weight shape overflow");
+  if (packed_len != expect)
+    return fail(e, LLR_ERR_INVALID, "W bytes: expected " + std::to_string(expect) + ", got " + std::to_string(packed_len));
+  if (rows == 0) return LLR_OK;
+  if (!packed || !x || !y) return fail(e, LLR_ERR_INVALID, "null buffer");
+
+  DeviceGuard guard(e->device);
+  if ((rc = resolve_limit(e)) != LLR_OK) return rc;
+
+  const Hash128 h = content_hash((const uint8_t*)packed, packed_len);
+  for (auto it = e->cache.begin(); it != e->cache.end(); ++it) {
+    if (it->dtype == dtype && it->rows == (int64_t)rows && it->cols == (int64_t)cols &&
+        it->len == packed_len && it->hash == h) {
+      e->cache.splice(e->cache.end(), e->cache, it);  // most recently used
+      ++e->ctr.cache_hits;
+      return run_host(e, it->mat, tokens, x, y);
+    }
+  }
+  ++e->ctr.cache_misses;
+  // native_gpu.rs:42-44, 178-185: evict oldest entries until the newcomer fits
+  while (!e->cache.empty() &&
+         (expect > e->limit || e->ctr.resident_bytes > e->limit - expect))
+    drop_entry(e, e->cache.begin());
+  llr_matrix* m = nullptr;
+  if ((rc = alloc_matrix(e, dtype, rows, cols, rb, expect, &m)) != LLR_OK) return rc;
+  cudaError_t ce = cudaMemcpyAsync(m->dev, packed, expect, cudaMemcpyHostToDevice, e->stream);
+  if (ce != cudaSuccess) { release_matrix(e, m); return fail_cuda(e, ce, "weight upload"); }
+  ++e->ctr.uploads;
+  e->ctr.upload_bytes += expect;
+  rc = run_host(e, m, tokens, x, y);
+  if (rc != LLR_OK) { cudaStreamSynchronize(e->stream); cudaGetLastError(); release_matrix(e, m); return rc; }
+  // oversized matrices run once and are released (native_gpu.rs:199-211)
+  if (expect <= e->limit) {
+    e->cache.push_back(CacheEntry{dtype, (int64_t)rows, (int64_t)cols, packed_len, h, m});
+    e->ctr.resident_bytes += expect;
+  } else {
+    release_matrix(e, m);
+  }
+  return LLR_OK;
+}
+
+int llr_matmul_device(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x_dev,
+                      float* y_dev, void* stream) {
+  if (!e) return LLR_ERR_INVALID;
+  int rc = check_matrix(e, m);
+  if (rc) return rc;
+  if (tokens == 0 || !x_dev || !y_dev)
+    return fail(e, LLR_ERR_INVALID, "CUDA GEMM buffer lengths do not match shape");
+  DeviceGuard guard(e->device);
+  cudaStream_t s = stream ? (cudaStream_t)stream : e->stream;
+  cudaError_t ce = launch_matmul(view_of(m), x_dev, y_dev, (int64_t)tokens, s, e->path, e->sm_count,
+                                 &e->ctr.launches);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
+  return LLR_OK;
+}
+
+int llr_exec_synchronize(llr_exec* e) {
+  if (!e) return LLR_ERR_INVALID;
+  DeviceGuard guard(e->device);
+  cudaError_t ce = cudaStreamSynchronize(e->stream);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "stream synchronize");
+  return LLR_OK;
+}
+
+int llr_dequant_rows(llr_exec* e, const llr_matrix* m, size_t row0, size_t n_rows, float* out,
+                     size_t out_len) {
+  if (!e) return LLR_ERR_INVALID;
+  int rc = check_matrix(e, m);
+  if (rc) return rc;
+  size_t n = 0;
+  if (row0 > (size_t)m->rows || n_rows > (size_t)m->rows - row0 ||
+      !mul_ok(n_rows, (size_t)m->cols, &n) || out_len != n || (!out && n))
+    return fail(e, LLR_ERR_INVALID, "dequant row range or output length does not match the matrix");
+  if (n == 0) return LLR_OK;
+  DeviceGuard guard(e->device);
+  cudaError_t ce;
+  if ((ce = grow_device(&e->dev_y, &e->dev_y_cap, n)) != cudaSuccess) return fail_cuda(e, ce, "result scratch");
+  if ((ce = launch_dequant(view_of(m), (int64_t)row0, (int64_t)n_rows, e->dev_y, e->stream,
+                           &e->ctr.launches)) != cudaSuccess)
+    return fail_cuda(e, ce, "kernel launch");
+  if ((ce = grow_pinned(&e->pin_y, &e->pin_y_cap, n)) != cudaSuccess) return fail_cuda(e, ce, "pinned result staging");
+  if ((ce = cudaMemcpyAsync(e->pin_y, e->dev_y, n * sizeof(float), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
+      (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)
+    return fail_cuda(e, ce, "result download");
+  std::memcpy(out, e->pin_y, n * sizeof(float));
+  e->ctr.d2h_bytes += n * sizeof(float);
+  return LLR_OK;
+}
+
+int llr_matrix_synth(llr_exec* e, uint8_t dtype, size_t rows, size_t cols, uint64_t seed,
+                     llr_matrix** out) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!out) return fail(e, LLR_ERR_INVALID, "null output pointer");
+  *out = nullptr;
+  if (rows == 0 || cols == 0) return fail(e, LLR_ERR_INVALID, "GEMV dimensions must be positive");
+  size_t rb = 0, expect = 0;
+  std::string msg;
+  int rc = row_bytes_checked(dtype, cols, &rb, &msg);
+  if (rc) return fail(e, rc, msg);
+  if (!mul_ok(rb, rows, &expect)) return fail(e, LLR_ERR_OVERFLOW, "GEMV shape overflow");
+  DeviceGuard guard(e->device);
+  llr_matrix* m = nullptr;
+  if ((rc = alloc_matrix(e, dtype, rows, cols, rb, expect, &m)) != LLR_OK) return rc;
+  cudaError_t ce = launch_synth(dtype, (int64_t)rows, (int64_t)cols, seed, m->dev, e->stream,
+                                &e->ctr.launches);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+  if (ce != cudaSuccess) { release_matrix(e, m); return fail_cuda(e, ce, "synthetic fill"); }
+  *out = m;
+  return LLR_OK;
+}
+
+int llr_matrix_download(llr_exec* e, const llr_matrix* m, void* out, size_t out_len) {
+  if (!e) return LLR_ERR_INVALID;
+  int rc = check_matrix(e, m);
+  if (rc) return rc;
+  if (!out || out_len != m->bytes) return fail(e, LLR_ERR_INVALID, "output length does not match the matrix");
+  DeviceGuard guard(e->device);
+  cudaError_t ce = cudaMemcpyAsync(out, m->dev, m->bytes, cudaMemcpyDeviceToHost, e->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "weight download");
+  return LLR_OK;
+}
+
+}  // extern "C"

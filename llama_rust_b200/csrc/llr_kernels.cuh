@@ -1,0 +1,42 @@
+// Internal launch interface between the executor (llr_exec.cu) and the kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace llr {
+
+// A resident packed matrix as the kernels see it.  `w` is 256-byte aligned and
+// the allocation is padded so that 16-byte windows around any row are readable.
+struct MatView {
+  const uint8_t* w;
+  int dtype;
+  int64_t rows, cols;
+  int64_t row_bytes;
+};
+
+enum GemvPath : int { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_STAGED = 2 };
+
+// y[t*rows + r] = sum_c W[r,c] * x[t*cols + c] for t < tokens.  Any shape the
+// entry points accept.  `launches` is incremented by the kernels launched.
+cudaError_t launch_matmul(const MatView& m, const float* x, float* y, int64_t tokens,
+                          cudaStream_t stream, int path, int sm_count, uint64_t* launches);
+
+// Always-available reference kernel: one warp per row, byte loads, any alignment.
+cudaError_t launch_gemv_generic(const MatView& m, const float* x, float* y, int64_t tokens,
+                                cudaStream_t stream, uint64_t* launches);
+
+// Shared-memory staged decode GEMV (tokens <= 8 per pass); see llr_gemv_staged.cu.
+bool gemv_staged_supported(const MatView& m);
+cudaError_t launch_gemv_staged(const MatView& m, const float* x, float* y, int64_t tokens,
+                               cudaStream_t stream, int sm_count, uint64_t* launches);
+
+// out[(r-row0)*cols + c] = dequantized W[r,c], bit-exact with the reference.
+cudaError_t launch_dequant(const MatView& m, int64_t row0, int64_t n_rows, float* out,
+                           cudaStream_t stream, uint64_t* launches);
+
+// Seeded synthetic packed blocks (see llama_rust_b200/synth.py for the recipe).
+cudaError_t launch_synth(int dtype, int64_t rows, int64_t cols, uint64_t seed, uint8_t* w,
+                         cudaStream_t stream, uint64_t* launches);
+
+}  // namespace llr

@@ -1,0 +1,171 @@
+"""Host-side mirror of the reference's executor types over the C ABI.
+
+``Executor`` stands where ``llama_native_cuda::CudaGemv`` stands in the
+reference (native-cuda/src/gpu.rs:139-418) and ``Matrix`` where ``CudaMatrix``
+does (gpu.rs:126-130); method names, argument meaning and error behaviour follow
+them, except that ``upload`` takes GGUF packed bytes and a dtype tag instead of
+F32-expanded weights.  Errors surface as ``NativeCudaError`` carrying the status
+code and the executor's message (the reference's ``Result<_, String>``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+
+F16, BF16, F32, Q5_0, Q5_1, Q4_0, Q8_0, Q4_K, Q6_K = 0, 1, 2, 6, 7, 12, 13, 17, 19
+DTYPES = {"F16": F16, "BF16": BF16, "F32": F32, "Q5_0": Q5_0, "Q5_1": Q5_1, "Q4_0": Q4_0,
+          "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K}
+OK, ERR_INVALID, ERR_UNALIGNED, ERR_DTYPE, ERR_OVERFLOW, ERR_FOREIGN, ERR_CUDA, ERR_OOM, ERR_CONFIG = range(9)
+PATH_AUTO, PATH_GENERIC, PATH_STAGED = 0, 1, 2
+
+_cdll = None
+
+
+def lib() -> C.CDLL:
+    global _cdll
+    if _cdll is None:
+        _cdll = _lib.load()
+    return _cdll
+
+
+class NativeCudaError(Exception):
+    """A failing executor call: ``code`` is the LLR_ERR_* status, ``args[0]`` the message."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(message)
+        self.code = code
+
+
+def row_bytes(dtype: int, cols: int) -> int:
+    out = C.c_size_t(0)
+    rc = lib().llr_row_bytes(dtype, cols, C.byref(out))
+    if rc:
+        raise NativeCudaError(rc, f"row_bytes(dtype={dtype}, cols={cols}) failed with status {rc}")
+    return out.value
+
+
+def _as_u8(a) -> np.ndarray:
+    if isinstance(a, (bytes, bytearray, memoryview)):
+        return np.frombuffer(a, dtype=np.uint8)
+    return np.ascontiguousarray(a).view(np.uint8).reshape(-1)
+
+
+def _as_f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32).reshape(-1)
+
+
+class Matrix:
+    """Immutable packed matrix resident on the device (CudaMatrix, gpu.rs:126)."""
+
+    def __init__(self, executor: "Executor", handle: int):
+        self._exec = executor
+        self._h = handle
+        dt, r, c, b = C.c_uint8(), C.c_size_t(), C.c_size_t(), C.c_size_t()
+        lib().llr_matrix_info(handle, C.byref(dt), C.byref(r), C.byref(c), C.byref(b))
+        self.dtype, self.rows, self.cols, self.packed_bytes = dt.value, r.value, c.value, b.value
+
+    def free(self) -> None:
+        if self._h:
+            lib().llr_matrix_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Executor:
+    """One device, one stream, scratch reuse and weight residency (CudaGemv, gpu.rs:139)."""
+
+    def __init__(self, device: int = 0):
+        h = C.c_void_p()
+        rc = lib().llr_exec_create(device, C.byref(h))
+        if rc:
+            raise NativeCudaError(rc, lib().llr_exec_last_error(None).decode())
+        self._h = h.value
+        self.device = device
+
+    # -- plumbing ---------------------------------------------------------
+    def _check(self, rc: int) -> None:
+        if rc:
+            raise NativeCudaError(rc, lib().llr_exec_last_error(self._h).decode())
+
+    def close(self) -> None:
+        if self._h:
+            lib().llr_exec_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # -- CudaGemv surface ---------------------------------------------------
+    def memory_info(self) -> tuple[int, int]:
+        fr, tot = C.c_size_t(), C.c_size_t()
+        self._check(lib().llr_exec_mem_info(self._h, C.byref(fr), C.byref(tot)))
+        return fr.value, tot.value
+
+    def upload(self, dtype: int, rows: int, cols: int, packed) -> Matrix:
+        w = _as_u8(packed)
+        h = C.c_void_p()
+        self._check(lib().llr_matrix_upload(self._h, dtype, rows, cols, w.ctypes.data, w.size, C.byref(h)))
+        return Matrix(self, h.value)
+
+    def synth(self, dtype: int, rows: int, cols: int, seed: int) -> Matrix:
+        h = C.c_void_p()
+        self._check(lib().llr_matrix_synth(self._h, dtype, rows, cols, seed & (2 ** 64 - 1), C.byref(h)))
+        return Matrix(self, h.value)
+
+    def download(self, m: Matrix) -> np.ndarray:
+        out = np.empty(m.packed_bytes, np.uint8)
+        self._check(lib().llr_matrix_download(self._h, m._h, out.ctypes.data, out.size))
+        return out
+
+    def gemv_resident(self, m: Matrix, x, y: np.ndarray) -> None:
+        xv = _as_f32(x)
+        self._check(lib().llr_gemv_resident(self._h, m._h, xv.ctypes.data, xv.size, y.ctypes.data, y.size))
+
+    def gemm_resident(self, m: Matrix, tokens: int, x, y: np.ndarray) -> None:
+        xv = _as_f32(x)
+        self._check(lib().llr_gemm_resident(self._h, m._h, tokens, xv.ctypes.data, xv.size,
+                                            y.ctypes.data, y.size))
+
+    def matmul(self, dtype: int, rows: int, cols: int, tokens: int, packed, x, y: np.ndarray) -> None:
+        """native_gpu::matmul (langtax/src/native_gpu.rs:124): content-identity residency."""
+        w, xv = _as_u8(packed), _as_f32(x)
+        assert y.dtype == np.float32 and y.flags.c_contiguous
+        self._check(lib().llr_matmul(self._h, dtype, rows, cols, tokens, w.ctypes.data, w.size,
+                                     xv.ctypes.data, xv.size, y.ctypes.data, y.size))
+
+    def matmul_device(self, m: Matrix, tokens: int, x_ptr: int, y_ptr: int, stream: int = 0) -> None:
+        self._check(lib().llr_matmul_device(self._h, m._h, tokens, x_ptr, y_ptr, stream))
+
+    def dequant_rows(self, m: Matrix, row0: int = 0, n_rows: int | None = None) -> np.ndarray:
+        n = m.rows - row0 if n_rows is None else n_rows
+        out = np.empty((n, m.cols), np.float32)
+        self._check(lib().llr_dequant_rows(self._h, m._h, row0, n, out.ctypes.data, out.size))
+        return out
+
+    def synchronize(self) -> None:
+        self._check(lib().llr_exec_synchronize(self._h))
+
+    def set_path(self, path: int) -> None:
+        self._check(lib().llr_exec_set_path(self._h, path))
+
+    def counters(self) -> dict:
+        c = _lib.Counters()
+        lib().llr_exec_counters(self._h, C.byref(c))
+        return {n: getattr(c, n) for n, _ in c._fields_}

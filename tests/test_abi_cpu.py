@@ -1,0 +1,89 @@
+"""CPU-only checks of the boundary: the shared library loads, exports exactly what
+include/llama_rust_b200.h declares, and its host-only entry points behave."""
+import ctypes as C
+import glob
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from llama_rust_b200 import build, executor
+    build.build()
+    return executor.lib()
+
+
+def declared_symbols():
+    names = set()
+    for h in glob.glob(os.path.join(ROOT, "include", "*.h")):
+        text = re.sub(r"/\*.*?\*/", "", open(h).read(), flags=re.S)
+        names |= set(re.findall(r"\b(llr_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
+
+
+def test_library_exports_every_declared_symbol(lib):
+    from llama_rust_b200 import _lib
+    declared = declared_symbols()
+    assert declared, "no declarations found"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+    assert sorted(_lib.SYMBOLS) == declared
+
+
+def test_row_bytes_matches_reference_table(lib, orc):
+    from llama_rust_b200 import executor as ex
+    for kind in (0, 1, 2, 6, 7, 12, 13, 17, 19):
+        for cols in (0, 256, 4096, 14336):
+            assert ex.row_bytes(kind, cols) == orc.row_bytes(kind, cols)
+    # BASELINE shapes (quant.rs:86-163)
+    assert ex.row_bytes(13, 4096) == 4352 and ex.row_bytes(17, 4096) == 2304
+    assert ex.row_bytes(17, 14336) == 8064 and ex.row_bytes(19, 4096) == 3360
+    assert ex.row_bytes(19, 14336) == 11760 and ex.row_bytes(6, 4096) == 2816 and ex.row_bytes(7, 4096) == 3072
+    with pytest.raises(ex.NativeCudaError) as e:
+        ex.row_bytes(13, 33)
+    assert e.value.code == ex.ERR_UNALIGNED
+    for bad in (3, 4, 5, 8, 14, 18, 20, 255):  # the other GemmKind tags are out of scope
+        with pytest.raises(ex.NativeCudaError) as e:
+            ex.row_bytes(bad, 256)
+        assert e.value.code == ex.ERR_DTYPE
+
+
+def test_executor_creation_fails_loudly_without_a_gpu(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from llama_rust_b200 import executor as ex
+    with pytest.raises(ex.NativeCudaError) as e:
+        ex.Executor(0)
+    assert e.value.code in (ex.ERR_CUDA, ex.ERR_INVALID)
+    assert str(e.value)
+
+
+def test_null_handles_are_rejected(lib):
+    assert lib.llr_exec_destroy(None) == 0
+    assert lib.llr_matrix_free(None) == 0
+    out = C.c_size_t()
+    assert lib.llr_exec_mem_info(None, C.byref(out), C.byref(out)) != 0
+    assert lib.llr_matmul(None, 13, 1, 32, 1, None, 34, None, 32, None, 1) != 0
+
+
+def test_host_synth_is_deterministic_and_well_formed(orc):
+    from llama_rust_b200 import synth
+    a = synth.packed_matrix(synth.Q4_K, 8, 512, 99)
+    b = synth.packed_matrix(synth.Q4_K, 8, 512, 99)
+    assert np.array_equal(a, b) and a.size == 8 * 2 * 144
+    assert not np.array_equal(a, synth.packed_matrix(synth.Q4_K, 8, 512, 100))
+    # a block is independent of where the chunk boundaries fall
+    assert np.array_equal(synth.packed_blocks(synth.Q6_K, 5, 3, 7), synth.packed_matrix(synth.Q6_K, 1, 2048, 7)[5 * 210:8 * 210])
+    q = synth.packed_matrix(synth.Q8_0, 4, 256, 1).reshape(-1, 34)[:, 2:].view(np.int8)
+    assert q.min() >= -127 and q.max() <= 127
+    w = orc.dequant_matrix(orc.Q4_K, 8, 512, a)
+    assert np.all(np.isfinite(w))
+    x = synth.activations(4096, 3)
+    assert abs(float(x.mean())) < 0.1 and 0.9 < float(x.std()) < 1.1
+    assert synth.tensor_seed(0, "blk.0.attn_q.weight") != synth.tensor_seed(0, "blk.1.attn_q.weight")
