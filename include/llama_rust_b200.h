@@ -82,11 +82,12 @@ const char* llr_exec_last_error(const llr_exec* exec);
 
 int llr_exec_counters(const llr_exec* exec, llr_counters* out);
 
-/* Diagnostic knob: which decode kernel serves 1..8 activation rows.  0 = pick
- * automatically, 1 = the shape-agnostic byte-load kernel, 2 = the
- * shared-memory staged kernel (falls back to 1 for shapes it cannot take).
- * Also read once from the environment variable LLR_GEMV_PATH
- * (generic|staged) when the executor is created. */
+/* Diagnostic knob: which decode kernel serves the call.  0 = pick automatically
+ * (integer tensor-core kernel where the format and shape allow, else the
+ * staged kernel, else the shape-agnostic one), 1 = the shape-agnostic byte-load
+ * kernel, 2 = the shared-memory staged FMA kernel (falls back to 1 for shapes
+ * it cannot take), 3 = same as 0.  Also read once from the environment
+ * variable LLR_GEMV_PATH (generic|staged|mma) when the executor is created. */
 int llr_exec_set_path(llr_exec* exec, int path);
 
 /* Packed bytes of one row of `cols` columns.  Replaces the <t>_row_bytes
@@ -138,7 +139,8 @@ int llr_matmul(llr_exec* exec, uint8_t dtype, size_t rows, size_t cols, size_t t
  * [gpu.rs:301-334]. */
 int llr_matmul_device(llr_exec* exec, const llr_matrix* matrix, size_t tokens, const float* x_dev,
                       float* y_dev, void* stream);
-/* Block the calling thread until the executor's own stream is idle. */
+/* Block the calling thread until the executor's own stream is idle; reports
+ * LLR_ERR_CUDA if a kernel's bounded device-side wait gave up since the last check. */
 int llr_exec_synchronize(llr_exec* exec);
 
 /* Dequantize rows [row0, row0+n_rows) of a resident matrix to f32 on the

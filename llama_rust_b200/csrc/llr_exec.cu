@@ -109,6 +109,8 @@ struct llr_exec {
   std::string err;
   llr_counters ctr{};
   int path = PATH_AUTO;
+  int* err_flag = nullptr;  // device word set by a kernel whose bounded wait ran out
+  int err_host = 0;
   // activation / result staging
   float* pin_x = nullptr; size_t pin_x_cap = 0;
   float* pin_y = nullptr; size_t pin_y_cap = 0;
@@ -296,11 +298,18 @@ int run_host(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, fl
   if ((ce = cudaMemcpyAsync(e->dev_x, src, nx * sizeof(float), cudaMemcpyHostToDevice, e->stream)) != cudaSuccess)
     return fail_cuda(e, ce, "activation upload");
   if ((ce = launch_matmul(view_of(m), e->dev_x, e->dev_y, (int64_t)tokens, e->stream, e->path,
-                          e->sm_count, &e->ctr.launches)) != cudaSuccess)
+                          e->sm_count, e->err_flag, &e->ctr.launches)) != cudaSuccess)
     return fail_cuda(e, ce, "kernel launch");
   if ((ce = cudaMemcpyAsync(dst, e->dev_y, ny * sizeof(float), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess)
     return fail_cuda(e, ce, "result download");
+  if ((ce = cudaMemcpyAsync(&e->err_host, e->err_flag, sizeof(int), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess)
+    return fail_cuda(e, ce, "status download");
   if ((ce = cudaStreamSynchronize(e->stream)) != cudaSuccess) return fail_cuda(e, ce, "stream synchronize");
+  if (e->err_host != 0) {
+    cudaMemsetAsync(e->err_flag, 0, sizeof(int), e->stream);
+    e->err_host = 0;
+    return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations (copy engine did not deliver a weight tile)");
+  }
   if (!y_pinned) std::memcpy(y, e->pin_y, ny * sizeof(float));
   e->ctr.h2d_bytes += nx * sizeof(float);
   e->ctr.d2h_bytes += ny * sizeof(float);
@@ -312,11 +321,14 @@ int run_host(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, fl
 namespace llr {
 
 cudaError_t launch_matmul(const MatView& m, const float* x, float* y, int64_t tokens,
-                          cudaStream_t stream, int path, int sm_count, uint64_t* launches) {
+                          cudaStream_t stream, int path, int sm_count, int* err_flag,
+                          uint64_t* launches) {
   const bool x_aligned = ((uintptr_t)x & 15) == 0 && (m.cols % 4 == 0);
-  const bool staged_ok = gemv_staged_supported(m) && x_aligned;
-  if (path == PATH_GENERIC || !staged_ok) return launch_gemv_generic(m, x, y, tokens, stream, launches);
-  return launch_gemv_staged(m, x, y, tokens, stream, sm_count, launches);
+  if ((path == PATH_AUTO || path == PATH_MMA) && x_aligned && err_flag && gemv_mma_supported(m))
+    return launch_gemv_mma(m, x, y, tokens, stream, sm_count, err_flag, launches);
+  if (path != PATH_GENERIC && x_aligned && gemv_staged_supported(m))
+    return launch_gemv_staged(m, x, y, tokens, stream, sm_count, launches);
+  return launch_gemv_generic(m, x, y, tokens, stream, launches);
 }
 
 }  // namespace llr
@@ -357,9 +369,18 @@ int llr_exec_create(int device, llr_exec** out) {
     return LLR_ERR_CUDA;
   }
   e->sm_count = prop.multiProcessorCount;
+  if ((ce = cudaMalloc((void**)&e->err_flag, sizeof(int))) != cudaSuccess ||
+      (ce = cudaMemset(e->err_flag, 0, sizeof(int))) != cudaSuccess) {
+    cudaGetLastError();
+    g_create_error = std::string("CUDA initialisation failed: ") + cudaGetErrorString(ce);
+    cudaStreamDestroy(e->stream);
+    delete e;
+    return LLR_ERR_CUDA;
+  }
   if (const char* p = std::getenv("LLR_GEMV_PATH")) {
     if (!std::strcmp(p, "generic")) e->path = PATH_GENERIC;
     else if (!std::strcmp(p, "staged")) e->path = PATH_STAGED;
+    else if (!std::strcmp(p, "mma")) e->path = PATH_MMA;
   }
   *out = e;
   return LLR_OK;
@@ -379,6 +400,7 @@ int llr_exec_destroy(llr_exec* e) {
   if (e->pin_y) cudaFreeHost(e->pin_y);
   if (e->dev_x) cudaFree(e->dev_x);
   if (e->dev_y) cudaFree(e->dev_y);
+  if (e->err_flag) cudaFree(e->err_flag);
   cudaStreamDestroy(e->stream);
   cudaGetLastError();
   delete e;
@@ -402,7 +424,7 @@ int llr_exec_counters(const llr_exec* e, llr_counters* out) {
 }
 
 int llr_exec_set_path(llr_exec* e, int path) {
-  if (!e || path < PATH_AUTO || path > PATH_STAGED) return LLR_ERR_INVALID;
+  if (!e || path < PATH_AUTO || path > PATH_MMA) return LLR_ERR_INVALID;
   e->path = path;
   return LLR_OK;
 }
@@ -565,7 +587,7 @@ int llr_matmul_device(llr_exec* e, const llr_matrix* m, size_t tokens, const flo
   DeviceGuard guard(e->device);
   cudaStream_t s = stream ? (cudaStream_t)stream : e->stream;
   cudaError_t ce = launch_matmul(view_of(m), x_dev, y_dev, (int64_t)tokens, s, e->path, e->sm_count,
-                                 &e->ctr.launches);
+                                 e->err_flag, &e->ctr.launches);
   if (ce != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
   return LLR_OK;
 }
@@ -573,8 +595,14 @@ int llr_matmul_device(llr_exec* e, const llr_matrix* m, size_t tokens, const flo
 int llr_exec_synchronize(llr_exec* e) {
   if (!e) return LLR_ERR_INVALID;
   DeviceGuard guard(e->device);
-  cudaError_t ce = cudaStreamSynchronize(e->stream);
+  cudaError_t ce = cudaMemcpyAsync(&e->err_host, e->err_flag, sizeof(int), cudaMemcpyDeviceToHost, e->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
   if (ce != cudaSuccess) return fail_cuda(e, ce, "stream synchronize");
+  if (e->err_host != 0) {
+    cudaMemsetAsync(e->err_flag, 0, sizeof(int), e->stream);
+    e->err_host = 0;
+    return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations (copy engine did not deliver a weight tile)");
+  }
   return LLR_OK;
 }
 

@@ -15,12 +15,14 @@ struct MatView {
   int64_t row_bytes;
 };
 
-enum GemvPath : int { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_STAGED = 2 };
+enum GemvPath : int { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_STAGED = 2, PATH_MMA = 3 };
 
 // y[t*rows + r] = sum_c W[r,c] * x[t*cols + c] for t < tokens.  Any shape the
 // entry points accept.  `launches` is incremented by the kernels launched.
+// `err_flag` is a device int that kernels with bounded waits set to non-zero when a wait ran out.
 cudaError_t launch_matmul(const MatView& m, const float* x, float* y, int64_t tokens,
-                          cudaStream_t stream, int path, int sm_count, uint64_t* launches);
+                          cudaStream_t stream, int path, int sm_count, int* err_flag,
+                          uint64_t* launches);
 
 // Always-available reference kernel: one warp per row, byte loads, any alignment.
 cudaError_t launch_gemv_generic(const MatView& m, const float* x, float* y, int64_t tokens,
@@ -30,6 +32,12 @@ cudaError_t launch_gemv_generic(const MatView& m, const float* x, float* y, int6
 bool gemv_staged_supported(const MatView& m);
 cudaError_t launch_gemv_staged(const MatView& m, const float* x, float* y, int64_t tokens,
                                cudaStream_t stream, int sm_count, uint64_t* launches);
+
+// Integer tensor-core decode GEMV for Q4_K / Q6_K / Q8_0 (tokens <= 8 per pass); see
+// llr_gemv_mma.cu.  Launched with programmatic stream serialization.
+bool gemv_mma_supported(const MatView& m);
+cudaError_t launch_gemv_mma(const MatView& m, const float* x, float* y, int64_t tokens,
+                            cudaStream_t stream, int sm_count, int* err_flag, uint64_t* launches);
 
 // out[(r-row0)*cols + c] = dequantized W[r,c], bit-exact with the reference.
 cudaError_t launch_dequant(const MatView& m, int64_t row0, int64_t n_rows, float* out,

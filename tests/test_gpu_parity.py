@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 
 from helpers import (ALL, BF16, F16, F32, Q4_0, Q4_K, Q5_0, Q5_1, Q6_K, Q8_0, check_boundary,
-                     check_kernel, formats, random_packed, values)
+                     check_gemv, check_kernel, formats, gemv_references, random_packed, values)
 
 pytestmark = pytest.mark.gpu
 
@@ -73,9 +73,6 @@ def test_multi_block_quantized_batches_match_cpu_oracle(q, orc, fmt):  # parity.
         cols = fmt.cols * blocks
         for rows in (1, 9):
             packed = np.concatenate([fmt.pack_row(r + b * 5) for r in range(rows) for b in range(blocks)])
-            if fmt.kind in (F32, F16, BF16):
-                # element formats: the row is the concatenation of the per-block value runs
-                pass
             for tokens in (1, 2, 7, 8, 9, 31, 32, 33):
                 x = np.concatenate([values(t * 3 + 1, cols) for t in range(tokens)])
                 expected = orc.gemm_f64(fmt.kind, cols, tokens, packed, x, rows)
@@ -197,48 +194,88 @@ def test_all_zero_bytes_dequantize_to_negative_zero(ex):  # simd/tests.rs:1481-1
 
 
 # ---- decode GEMV against the CPU row kernels --------------------------------------
-PATHS = {"generic": 1, "staged": 2}
+PATHS = {"generic": 1, "staged": 2, "auto": 0}
 
 
 @pytest.mark.parametrize("path", list(PATHS))
 @pytest.mark.parametrize("name", list(ALL))
 def test_gemv_matches_cpu_row_kernels(ex, orc, name, path):
-    """|gpu - cpu| <= 1e-5 (1 + |cpu|) against the AVX2 restatement, M = 1, 2, 3, 4, 8."""
+    """Every kernel family (shape-agnostic, staged FMA, integer tensor core) against the CPU
+    row kernels on seeded random blocks, M = 1, 2, 3, 4, 8 and 11 (two passes)."""
     kind = ALL[name]
     ex.set_path(PATHS[path])
     rng = np.random.default_rng(0xA0 + kind)
-    for rows, cols in ((64, 4096), (33, 2048 + 256), (5, 14336)):
+    for rows, cols in ((64, 4096), (33, 2048 + 256), (5, 14336), (17, 6144)):
         w = random_packed(rng, kind, rows, cols)
         m = ex.upload(kind, rows, cols, w)
-        for tokens in (1, 2, 3, 4, 8):
+        for tokens in (1, 2, 3, 4, 8, 11):
             x = rng.standard_normal(tokens * cols).astype(np.float32)
-            cpu = orc.gemm(kind, cols, tokens, w, x, rows, simd=True)
+            cpu, exact, abs_sum = gemv_references(kind, rows, cols, w, x, tokens)
             y = np.full(rows * tokens, np.nan, np.float32)
             ex.gemm_resident(m, tokens, x, y)
-            check_kernel(y, cpu, f"{name} {rows}x{cols} M={tokens} {path}")
+            check_gemv(y, cpu, exact, abs_sum, cols, f"{name} {rows}x{cols} M={tokens} {path}")
         m.free()
     ex.set_path(0)
+
+
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0"])
+def test_tensor_core_gemv_handles_awkward_activations(ex, orc, name):
+    """Outliers, tiny values, zero blocks and a non-finite activation through the digit split."""
+    kind = ALL[name]
+    rng = np.random.default_rng(0xB0 + kind)
+    rows, cols = 48, 4096
+    w = random_packed(rng, kind, rows, cols)
+    m = ex.upload(kind, rows, cols, w)
+    x = rng.standard_normal(cols).astype(np.float32)
+    x[7] = 3000.0          # a massive activation next to ordinary ones
+    x[300:556] = 0.0       # an all-zero 256-block
+    x[600:700] *= 1e-12    # values far below their block's maximum
+    x[1024:1280] *= 1e20   # a block with a huge common scale
+    x[2048:2304] *= 1e-30  # and a tiny one
+    cpu, exact, abs_sum = gemv_references(kind, rows, cols, w, x, 1)
+    y = np.empty(rows, np.float32)
+    ex.gemv_resident(m, x, y)
+    check_gemv(y, cpu, exact, abs_sum, cols, name + " awkward x")
+    x[5] = np.inf
+    ex.gemv_resident(m, x, y)
+    assert np.all(np.isnan(y)), "a non-finite activation must poison its output row"
+    m.free()
 
 
 def test_config1_q8_0_4096_gemv_seed0(ex, orc):
-    """BASELINE config 1: Q8_0 4096x4096, x ~ N(0,1), seed 0, M = 1; also vs f64 in units of u*sum|wx|."""
+    """BASELINE config 1: Q8_0 4096x4096, x ~ N(0,1), seed 0, M = 1, every kernel family."""
     from llama_rust_b200 import synth
     w = synth.packed_matrix(Q8_0, 4096, 4096, synth.tensor_seed(0, "config1.w"))
     x = synth.activations(4096, synth.tensor_seed(0, "config1.x"))
-    cpu = orc.gemv(Q8_0, 4096, w, x, 4096, simd=True)
-    for path in (1, 2):
+    cpu, exact, abs_sum = gemv_references(Q8_0, 4096, 4096, w, x, 1)
+    m = ex.upload(Q8_0, 4096, 4096, w)
+    for path in (1, 2, 0):
         ex.set_path(path)
-        m = ex.upload(Q8_0, 4096, 4096, w)
         y = np.empty(4096, np.float32)
         ex.gemv_resident(m, x, y)
-        check_kernel(y, cpu, "config1")
-        wf = orc.dequant_matrix(Q8_0, 4096, 4096, w).astype(np.float64)
-        exact = wf @ x.astype(np.float64)
-        abs_sum = np.abs(wf * x.astype(np.float64)).sum(axis=1)
-        err_u = np.abs(y - exact) / abs_sum / 2.0 ** -24
+        vs_cpu, vs_exact = check_gemv(y, cpu, exact, abs_sum, 4096, f"config1 path {path}")
+        err_u = np.abs(y - exact.ravel()) / abs_sum.ravel() / 2.0 ** -24
         assert err_u.max() < 64.0  # the reference's envelope for n = 4096 is 8*sqrt(n) = 512 u
-        m.free()
+    m.free()
     ex.set_path(0)
+
+
+@pytest.mark.parametrize("name,rows,cols", [("Q4_K", 4096, 4096), ("Q4_K", 1024, 4096), ("Q4_K", 2048, 14336),
+                                            ("Q6_K", 1024, 4096), ("Q6_K", 1024, 14336), ("Q6_K", 4008, 4096)])
+def test_config2_decode_shapes(ex, orc, name, rows, cols):
+    """BASELINE config 2 shapes (row counts trimmed where the CPU oracle would take long), M = 1, 2, 4, 8."""
+    from llama_rust_b200 import synth
+    kind = ALL[name]
+    seed = synth.tensor_seed(2, f"config2.{name}.{rows}x{cols}")
+    m = ex.synth(kind, rows, cols, seed)
+    w = ex.download(m)
+    for tokens in (1, 2, 4, 8):
+        x = synth.activations(tokens * cols, synth.tensor_seed(2, f"x.{tokens}"))
+        cpu, exact, abs_sum = gemv_references(kind, rows, cols, w, x, tokens)
+        y = np.empty(rows * tokens, np.float32)
+        ex.gemm_resident(m, tokens, x, y)
+        check_gemv(y, cpu, exact, abs_sum, cols, f"{name} {rows}x{cols} M={tokens}")
+    m.free()
 
 
 def test_gemv_is_linear_and_deterministic(ex):
