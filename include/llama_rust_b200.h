@@ -143,6 +143,32 @@ int llr_matmul_device(llr_exec* exec, const llr_matrix* matrix, size_t tokens, c
  * LLR_ERR_CUDA if a kernel's bounded device-side wait gave up since the last check. */
 int llr_exec_synchronize(llr_exec* exec);
 
+/* ---- programs: many decode products in one persistent launch -----------------
+ * An extension with no counterpart in the reference, which launches and
+ * synchronizes once per product [gpu.rs:301-334].  A program is a fixed list of
+ * products over resident matrices with device activation / result buffers.
+ * Entries with the same `phase` value are independent of each other; a phase
+ * starts only after every product of the previous phase has been written, so a
+ * later entry may read an earlier phase's y as its x.  `phase` must be
+ * non-decreasing along the list.  Supported: Q4_K, Q6_K (cols % 2048 == 0) and
+ * Q8_0 matrices with cols % 256 == 0, tokens 1..8, buffers 16-byte aligned.
+ * One launch (cooperative: the whole grid is resident) runs the list;
+ * llr_program_run returns without synchronizing.  A program owns a few bytes
+ * of device scratch (one counter per phase); two runs of the same program must
+ * not overlap on the device. */
+typedef struct llr_program llr_program;
+typedef struct llr_program_entry {
+  const llr_matrix* matrix;
+  const float* x_dev; /* tokens * cols floats */
+  float* y_dev;       /* tokens * rows floats */
+  uint32_t tokens;
+  uint32_t phase;
+} llr_program_entry;
+int llr_program_create(llr_exec* exec, const llr_program_entry* entries, size_t n_entries,
+                       llr_program** out);
+int llr_program_run(llr_exec* exec, llr_program* program, void* stream);
+int llr_program_free(llr_program* program);
+
 /* Dequantize rows [row0, row0+n_rows) of a resident matrix to f32 on the
  * device and copy them to out (n_rows*cols floats, host).  Bit-exact
  * counterpart of dequant_<t>_row [quant.rs:7511, 7533, 7734, 7884, 7918, 8046,

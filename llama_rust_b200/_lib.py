@@ -17,7 +17,8 @@ SYMBOLS = [
     "llr_exec_counters", "llr_exec_set_path", "llr_row_bytes", "llr_matrix_upload",
     "llr_matrix_upload_device", "llr_matrix_free", "llr_matrix_info", "llr_gemv_resident",
     "llr_gemm_resident", "llr_matmul", "llr_matmul_device", "llr_exec_synchronize",
-    "llr_dequant_rows", "llr_matrix_synth", "llr_matrix_download",
+    "llr_dequant_rows", "llr_matrix_synth", "llr_matrix_download", "llr_program_create",
+    "llr_program_run", "llr_program_free",
 ]
 
 
@@ -25,6 +26,11 @@ class Counters(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "launches", "uploads", "upload_bytes", "resident_bytes", "cache_limit", "cache_hits",
         "cache_misses", "evictions", "h2d_bytes", "d2h_bytes")]
+
+
+class ProgramEntry(C.Structure):
+    _fields_ = [("matrix", C.c_void_p), ("x_dev", C.c_void_p), ("y_dev", C.c_void_p),
+                ("tokens", C.c_uint32), ("phase", C.c_uint32)]
 
 
 def load() -> C.CDLL:
@@ -57,6 +63,9 @@ def load() -> C.CDLL:
     lib.llr_dequant_rows.argtypes = [vp, vp, sz, sz, vp, sz]
     lib.llr_matrix_synth.argtypes = [vp, u8, sz, sz, C.c_uint64, C.POINTER(vp)]
     lib.llr_matrix_download.argtypes = [vp, vp, vp, sz]
+    lib.llr_program_create.argtypes = [vp, C.POINTER(ProgramEntry), sz, C.POINTER(vp)]
+    lib.llr_program_run.argtypes = [vp, vp, vp]
+    lib.llr_program_free.argtypes = [vp]
     for s in SYMBOLS:
         if s != "llr_exec_last_error":
             getattr(lib, s).restype = C.c_int

@@ -17,6 +17,7 @@
 #include <new>
 #include <string>
 #include <unordered_set>
+#include <vector>
 
 #include "../../include/llama_rust_b200.h"
 #include "llr_formats.cuh"
@@ -603,6 +604,65 @@ int llr_exec_synchronize(llr_exec* e) {
     e->err_host = 0;
     return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations (copy engine did not deliver a weight tile)");
   }
+  return LLR_OK;
+}
+
+struct llr_program {
+  llr_exec* owner;
+  llr::Program* prog;
+};
+
+int llr_program_create(llr_exec* e, const llr_program_entry* entries, size_t n, llr_program** out) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!out) return fail(e, LLR_ERR_INVALID, "null output pointer");
+  *out = nullptr;
+  if (!entries || n == 0 || n > (1u << 20)) return fail(e, LLR_ERR_INVALID, "a program needs 1..2^20 entries");
+  std::vector<ProgEntry> pe(n);
+  std::vector<int> phase(n);
+  for (size_t i = 0; i < n; ++i) {
+    const llr_program_entry& in = entries[i];
+    int rc = check_matrix(e, in.matrix);
+    if (rc) return rc;
+    if (in.tokens == 0 || in.tokens > 8 || !in.x_dev || !in.y_dev || ((uintptr_t)in.x_dev & 15) != 0)
+      return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) + ": tokens must be 1..8 and buffers 16-byte aligned");
+    if (i > 0 && in.phase < entries[i - 1].phase)
+      return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) + ": phase must be non-decreasing");
+    const MatView v = view_of(in.matrix);
+    if (!prog_entry_supported(v))
+      return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) +
+                                          ": only Q4_K, Q6_K (cols % 2048 == 0) and Q8_0 with cols % 256 == 0 run in programs");
+    pe[i] = ProgEntry{v.w, in.x_dev, in.y_dev, v.row_bytes, (int)v.rows, (int)v.cols, v.dtype, (int)in.tokens, 0, 0};
+    phase[i] = (int)in.phase;
+  }
+  DeviceGuard guard(e->device);
+  llr::Program* prog = nullptr;
+  std::string msg;
+  cudaError_t ce = program_create(pe, phase, e->sm_count, &prog, &msg);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "program creation");
+  llr_program* p = new (std::nothrow) llr_program{e, prog};
+  if (!p) { program_destroy(prog); return fail(e, LLR_ERR_OOM, "host allocation failed"); }
+  *out = p;
+  return LLR_OK;
+}
+
+int llr_program_run(llr_exec* e, llr_program* p, void* stream) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!p || p->owner != e) return fail(e, LLR_ERR_FOREIGN, "program belongs to a different executor");
+  DeviceGuard guard(e->device);
+  cudaStream_t s = stream ? (cudaStream_t)stream : e->stream;
+  cudaError_t ce = program_run(p->prog, s, e->err_flag, &e->ctr.launches);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "program launch");
+  return LLR_OK;
+}
+
+int llr_program_free(llr_program* p) {
+  if (!p) return LLR_OK;
+  if (p->owner) {
+    DeviceGuard guard(p->owner->device);
+    cudaDeviceSynchronize();
+    program_destroy(p->prog);
+  }
+  delete p;
   return LLR_OK;
 }
 

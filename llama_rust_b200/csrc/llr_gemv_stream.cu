@@ -1,0 +1,511 @@
+// Decode matrix products (1..8 activation rows) for Q4_K, Q6_K and Q8_0 on the
+// integer tensor cores: the streaming kernel behind llr_matmul*/llr_gemm_resident
+// (one product per launch) and llr_program_run (a whole list per launch).
+//
+// What it computes: gemv_<t>_f32 / gemm_<t>_f32 of langtax/src/quant.rs (:6214,
+// :6891, :7199 and the gemm twins), y[t][r] = sum_c W[r,c] x[t][c] with W the
+// packed GGUF blocks, never expanded.  The arithmetic (activations split into
+// four int8 digits, exact mma.sync dot products, integer scale folding) is
+// described in llr_mma_common.cuh.
+//
+// Pipeline.  A CTA has ten warps with three roles and no CTA-wide barrier in
+// its steady state:
+//   * producer warp: walks the CTA's chunk list (16 rows x one column piece)
+//     and keeps NST TMA bulk copies in flight, one cp.async.bulk per row into a
+//     padded shared-memory stride; a stage is refilled as soon as the eight
+//     consumer warps have released it (mbarrier `empty`), not at a barrier;
+//   * eight consumer warps: wait for a stage (`full`), turn their share of its
+//     columns into A fragments and MMAs, release the stage, and at the end of a
+//     tile hand their partial sums to a reduction buffer (`rfull`);
+//   * reducer warp: adds the eight partials in warp order and writes y, so
+//     results are bit-reproducible; four buffers decouple it from the math.
+// Every wait is bounded; a wait that runs out sets the executor's error word
+// and the warp carries on so that the kernel always terminates.
+//
+// One product per launch: launched with programmatic stream serialization; the
+// producer prefetches before griddepcontrol.wait because weights never depend
+// on earlier kernels, everything that touches activations or results waits.
+//
+// Program: one cooperative launch runs a list of products grouped in phases
+// (independent products share a phase, e.g. attn_q|k|v; a phase starts when the
+// previous one is completely written).  The producer runs ahead across product
+// and phase boundaries, so the next weights stream in while the CTA waits for
+// the dependency, which is a per-phase counter in global memory: the reducer
+// adds one after its share of the phase is written and fenced, consumers poll
+// with acquire loads.  Activations written during the launch are read with
+// L2-coherent loads.
+#include <cuda_runtime.h>
+
+#include <new>
+#include <string>
+#include <vector>
+
+#include "llr_kernels.cuh"
+#include "llr_mma_common.cuh"
+
+namespace llr {
+namespace {
+using namespace mma;
+
+constexpr int CW = NWARP;                 // consumer warps
+constexpr int NTHREADS = (CW + 2) * 32;   // + producer + reducer
+constexpr int NRB = 4;                    // reduction buffers
+constexpr int MAX_CHUNK = Lay<DT_Q4_K, 1>::CHUNK;
+static_assert(Lay<DT_Q6_K, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q8_0, 1>::CHUNK <= MAX_CHUNK, "ring stage");
+constexpr int POLL_LIMIT = 1 << 20;
+
+template <int MT> struct SLay {
+  static constexpr int NT = (MT + 1) / 2;
+  static constexpr int RING = 0;
+  static constexpr int DIG = RING + NST * MAX_CHUNK;
+  static constexpr int SXF = DIG + NT * 8 * DS;
+  static constexpr int XSI = SXF + MT * (SPAN / 32) * 4;
+  static constexpr int RED = XSI + MT * (SPAN / 256) * 4;          // float [NRB][CW][16][MT]
+  static constexpr int BAR = RED + NRB * CW * 16 * MT * 4;          // full[NST] empty[NST] rfull[NRB] rempty[NRB]
+  static constexpr int TOTAL = BAR + (2 * NST + 2 * NRB) * 8 + 16;
+};
+
+struct Geom { int kseg, segb, rs; };
+__device__ __forceinline__ Geom geom_of(int dtype) {
+  if (dtype == DT_Q4_K) return {Fmt<DT_Q4_K>::KSEG, Lay<DT_Q4_K, 1>::SEGB, Lay<DT_Q4_K, 1>::RS};
+  if (dtype == DT_Q6_K) return {Fmt<DT_Q6_K>::KSEG, Lay<DT_Q6_K, 1>::SEGB, Lay<DT_Q6_K, 1>::RS};
+  return {Fmt<DT_Q8_0>::KSEG, Lay<DT_Q8_0, 1>::SEGB, Lay<DT_Q8_0, 1>::RS};
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+// bounded wait; false when it gave up
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity) {
+  int spins = 0;
+  while (!mbar_try_wait(b, parity))
+    if (++spins > SPIN_LIMIT) return false;
+  return true;
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory"); }
+
+// What a launch works on: a list of entries in global memory (program) or one entry
+// passed by value (single product).
+struct Work {
+  const ProgEntry* entries;
+  const ProgPhase* phases;
+  int n_phases;
+};
+
+// Tile range of this CTA inside a phase, and inside one entry of it.
+__device__ __forceinline__ void phase_range(const ProgPhase& P, int bid, int nb, int* lo, int* hi) {
+  *lo = (int)((int64_t)P.n_tiles * bid / nb);
+  *hi = (int)((int64_t)P.n_tiles * (bid + 1) / nb);
+}
+__device__ __forceinline__ bool entry_range(const ProgEntry& E, int lo, int hi, int* t0, int* t1) {
+  *t0 = max(lo, E.tile_begin) - E.tile_begin;
+  *t1 = min(hi, E.tile_begin + E.n_tiles) - E.tile_begin;
+  return *t0 < *t1;
+}
+
+template <int MT, bool PROGRAM>
+__device__ __forceinline__ void stream_body(const Work wk, unsigned long long* counters,
+                                            unsigned long long epoch, int* err) {
+  using L = SLay<MT>;
+  constexpr int NT = L::NT;
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* ring = smem + L::RING;
+  uint8_t* dig = smem + L::DIG;
+  float* sxf = (float*)(smem + L::SXF);
+  float* xsi = (float*)(smem + L::XSI);
+  float* red = (float*)(smem + L::RED);
+  uint64_t* full = (uint64_t*)(smem + L::BAR);
+  uint64_t* empty = full + NST;
+  uint64_t* rfull = empty + NST;
+  uint64_t* rempty = rfull + NRB;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bid = blockIdx.x, nb = gridDim.x;
+
+  if (!PROGRAM) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (tid == 0) {
+    for (int s = 0; s < NST; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CW); }
+    for (int s = 0; s < NRB; ++s) { mbar_init(&rfull[s], CW); mbar_init(&rempty[s], 1); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = tid; i < NT * 8 * DS / 16; i += NTHREADS) ((uint4*)dig)[i] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+
+  if (warp == CW) {
+    // ------------------------------------------------------------- producer
+    if (lane == 0) {
+      int c = 0;
+      bool ok = true;
+      for (int ph = 0; ph < wk.n_phases; ++ph) {
+        const ProgPhase P = wk.phases[ph];
+        int lo, hi;
+        phase_range(P, bid, nb, &lo, &hi);
+        for (int ei = 0; ei < P.n_entries && lo < hi; ++ei) {
+          const ProgEntry E = wk.entries[P.first_entry + ei];
+          int t0, t1;
+          if (!entry_range(E, lo, hi, &t0, &t1)) continue;
+          const Geom gm = geom_of(E.dtype);
+          const int n_span = (E.cols + SPAN - 1) / SPAN;
+          for (int span = 0; span < n_span; ++span) {
+            const int span_cols = min(SPAN, E.cols - span * SPAN);
+            const int nsub = (span_cols + gm.kseg - 1) / gm.kseg;
+            for (int tile = t0; tile < t1; ++tile) {
+              for (int sub = 0; sub < nsub; ++sub, ++c) {
+                const int stage = c % NST;
+                if (ok && !mbar_wait(&empty[stage], (uint32_t)(((c / NST) & 1) ^ 1))) { ok = false; atomicExch(err, 1); }
+                const int64_t seg_off = ((int64_t)span * (SPAN / gm.kseg) + sub) * gm.segb;
+                const int64_t left = E.row_bytes - seg_off;
+                const uint32_t bytes = (uint32_t)(left < gm.segb ? left : gm.segb);
+                mbar_expect_tx(&full[stage], 16 * bytes);
+                const uint8_t* src = E.w + (int64_t)(tile * 16) * E.row_bytes + seg_off;
+                uint8_t* dst = ring + stage * MAX_CHUNK;
+                const int last = E.rows - 1 - tile * 16;  // rows beyond the matrix refetch the last one
+#pragma unroll 4
+                for (int r = 0; r < 16; ++r)
+                  bulk_g2s(dst + r * gm.rs, src + (int64_t)min(r, last) * E.row_bytes, bytes, &full[stage]);
+              }
+            }
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  if (!PROGRAM) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  if (warp == CW + 1) {
+    // -------------------------------------------------------------- reducer
+    int j = 0;  // tiles reduced by this CTA
+    bool ok = true;
+    for (int ph = 0; ph < wk.n_phases; ++ph) {
+      const ProgPhase P = wk.phases[ph];
+      int lo, hi;
+      phase_range(P, bid, nb, &lo, &hi);
+      for (int ei = 0; ei < P.n_entries && lo < hi; ++ei) {
+        const ProgEntry E = wk.entries[P.first_entry + ei];
+        int t0, t1;
+        if (!entry_range(E, lo, hi, &t0, &t1)) continue;
+        const int n_span = (E.cols + SPAN - 1) / SPAN;
+        for (int span = 0; span < n_span; ++span) {
+          for (int tile = t0; tile < t1; ++tile, ++j) {
+            const int rb = j % NRB;
+            if (ok && !mbar_wait(&rfull[rb], (uint32_t)((j / NRB) & 1))) { ok = false; if (lane == 0) atomicExch(err, 1); }
+            const float* rp0 = red + rb * CW * 16 * MT;
+            for (int idx = lane; idx < 16 * MT; idx += 32) {
+              const int r = idx / MT, k = idx % MT, row = tile * 16 + r;
+              float v = 0.f;
+#pragma unroll
+              for (int w = 0; w < CW; ++w) v += rp0[w * 16 * MT + idx];
+              if (row < E.rows && k < E.tokens) {
+                float* yp = E.y + (int64_t)k * E.rows + row;
+                *yp = span == 0 ? v : *yp + v;
+              }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&rempty[rb]);
+          }
+        }
+      }
+      if (PROGRAM) {
+        // this CTA's share of the phase is written: publish it
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          atomicAdd(counters + ph, 1ull);
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------------------------------------------------------- consumers
+  const int g = lane >> 2, t = lane & 3;
+  int c = 0, j = 0;
+  bool ok = true;
+  const float* cur_x = nullptr;
+  int cur_cols = -1, cur_span = -1, cur_tokens = -1;
+  bool produced_here = false;
+  for (int ph = 0; ph < wk.n_phases; ++ph) {
+    const ProgPhase P = wk.phases[ph];
+    int lo, hi;
+    phase_range(P, bid, nb, &lo, &hi);
+    if (PROGRAM && P.wait_prev && ph > 0) {
+      if (tid == 0) {
+        const unsigned long long want = epoch * (unsigned long long)nb;
+        int polls = 0;
+        for (;;) {
+          unsigned long long v;
+          asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(counters + ph - 1) : "memory");
+          if (v >= want) break;
+          if (++polls > POLL_LIMIT) { atomicExch(err, 2); break; }
+          __nanosleep(polls < 8 ? 64 : 256);  // hundreds of CTAs poll one word: keep the L2 bank free for the adds
+        }
+      }
+      consumer_sync();
+      produced_here = true;
+      cur_x = nullptr;  // the same buffer may hold new values now
+    }
+    for (int ei = 0; ei < P.n_entries && lo < hi; ++ei) {
+      const ProgEntry E = wk.entries[P.first_entry + ei];
+      int t0, t1;
+      if (!entry_range(E, lo, hi, &t0, &t1)) continue;
+      const Geom gm = geom_of(E.dtype);
+      const int n_span = (E.cols + SPAN - 1) / SPAN;
+      for (int span = 0; span < n_span; ++span) {
+        const int span_cols = min(SPAN, E.cols - span * SPAN), nblk256 = span_cols >> 8;
+        if (cur_x != E.x || cur_cols != E.cols || cur_span != span || cur_tokens != E.tokens) {
+          consumer_sync();  // nobody still multiplies against the old planes
+          split_activations(E.x, E.cols, span * SPAN, nblk256, E.tokens, dig, sxf, xsi, warp, lane, produced_here);
+          consumer_sync();
+          cur_x = E.x; cur_cols = E.cols; cur_span = span; cur_tokens = E.tokens;
+        }
+        const int nsub = (span_cols + gm.kseg - 1) / gm.kseg;
+        for (int tile = t0; tile < t1; ++tile, ++j) {
+          AccT<MT> acc;
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc.y[nt][i] = 0.f;
+#pragma unroll
+          for (int k = 0; k < MT; ++k) acc.mn[0][k] = acc.mn[1][k] = 0.f;
+          for (int sub = 0; sub < nsub; ++sub, ++c) {
+            const int stage = c % NST;
+            if (ok && !mbar_wait(&full[stage], (uint32_t)((c / NST) & 1))) { ok = false; if (lane == 0) atomicExch(err, 1); }
+            const uint8_t* chunk = ring + stage * MAX_CHUNK;
+            const uint8_t* rowA = chunk + g * gm.rs;
+            const uint8_t* rowB = chunk + (g + 8) * gm.rs;
+            const int seg_cols = min(gm.kseg, span_cols - sub * gm.kseg);
+            if (E.dtype == DT_Q4_K) {
+              for (int b = warp; b < (seg_cols >> 8); b += CW)
+                block_q4k<MT>(rowA, rowB, b, sub * (gm.kseg / 256) + b, dig, sxf, xsi, g, t, acc);
+            } else if (E.dtype == DT_Q6_K) {
+              for (int b = warp; b < (seg_cols >> 8); b += CW)
+                block_q6k<MT>(rowA, rowB, b, sub * (gm.kseg / 256) + b, dig, xsi, g, t, acc);
+            } else {
+              for (int b = warp; b < (seg_cols >> 5); b += CW)
+                block_q80<MT>(rowA, rowB, b, sub * (gm.kseg / 32) + b, dig, xsi, g, t, acc);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[stage]);  // this warp no longer reads the stage
+          }
+          // ---- hand this warp's partial sums of the tile to the reducer ----
+          const int rb = j % NRB;
+          if (ok && !mbar_wait(&rempty[rb], (uint32_t)(((j / NRB) & 1) ^ 1))) { ok = false; if (lane == 0) atomicExch(err, 1); }
+          float* myred = red + (rb * CW + warp) * 16 * MT;
+          if (E.dtype == DT_Q4_K) {
+#pragma unroll
+            for (int k = 0; k < MT; ++k)
+#pragma unroll
+              for (int r = 0; r < 2; ++r) {
+                float v = acc.mn[r][k];
+                v += __shfl_xor_sync(~0u, v, 1);
+                v += __shfl_xor_sync(~0u, v, 2);
+                acc.mn[r][k] = v;
+              }
+          }
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            float vA = acc.y[nt][0] + acc.y[nt][1], vB = acc.y[nt][2] + acc.y[nt][3];
+            vA += __shfl_xor_sync(~0u, vA, 1);
+            vB += __shfl_xor_sync(~0u, vB, 1);
+            const int tok = 2 * nt + (t >> 1);
+            if ((t & 1) == 0 && tok < MT) {
+              float mA = 0.f, mB = 0.f;
+#pragma unroll
+              for (int k = 0; k < MT; ++k)
+                if (k == tok) { mA = acc.mn[0][k]; mB = acc.mn[1][k]; }
+              myred[g * MT + tok] = vA - mA;
+              myred[(g + 8) * MT + tok] = vB - mB;
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&rfull[rb]);
+        }
+      }
+    }
+  }
+}
+
+// two CTAs per SM need <= 102 registers per thread; with more than two activation rows the
+// digit planes leave room for one CTA only
+template <int MT>
+__global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
+gemv_stream_kernel(const __grid_constant__ ProgEntry one, int* __restrict__ err) {
+  __shared__ ProgPhase phase;
+  if (threadIdx.x == 0) phase = ProgPhase{0, 1, one.n_tiles, 0};
+  __syncthreads();
+  Work wk{&one, &phase, 1};
+  stream_body<MT, false>(wk, nullptr, 0ull, err);
+}
+
+template <int MT>
+__global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
+gemv_program_kernel(const ProgEntry* __restrict__ entries, const ProgPhase* __restrict__ phases, int n_phases,
+                    unsigned long long* __restrict__ counters, unsigned long long epoch, int* __restrict__ err) {
+  Work wk{entries, phases, n_phases};
+  stream_body<MT, true>(wk, counters, epoch, err);
+}
+
+template <class K>
+cudaError_t occupancy(K kern, int smem, int* blocks_per_sm) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  int n = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, NTHREADS, smem);
+  if (e != cudaSuccess) return e;
+  *blocks_per_sm = n > 0 ? n : 1;
+  return cudaSuccess;
+}
+
+template <int MT>
+cudaError_t launch_single(const MatView& m, const float* x, float* y, int tokens, cudaStream_t stream,
+                          int sm_count, int* err) {
+  auto kern = gemv_stream_kernel<MT>;
+  constexpr int smem = SLay<MT>::TOTAL;
+  static int blocks_per_sm = 0;  // per instantiation
+  if (blocks_per_sm == 0) {
+    cudaError_t e = occupancy(kern, smem, &blocks_per_sm);
+    if (e != cudaSuccess) return e;
+  }
+  ProgEntry E{m.w, x, y, m.row_bytes, (int)m.rows, (int)m.cols, m.dtype, tokens, 0, (int)((m.rows + 15) / 16)};
+  int grid = sm_count * blocks_per_sm;
+  if (grid > E.n_tiles) grid = E.n_tiles;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, E, err);
+}
+
+}  // namespace
+
+bool gemv_mma_supported(const MatView& m) {
+  if (m.dtype != DT_Q4_K && m.dtype != DT_Q6_K && m.dtype != DT_Q8_0) return false;
+  if (m.rows <= 0 || m.cols <= 0 || m.rows > (1 << 30) || m.cols > (1 << 30)) return false;
+  if (((uintptr_t)m.w & 15) != 0 || m.row_bytes % 16 != 0) return false;
+  if (m.cols % 256 != 0) return false;
+  // every column piece of a row must start and end on a 16-byte boundary
+  if (m.dtype == DT_Q6_K && m.cols % 2048 != 0) return false;
+  return true;
+}
+
+cudaError_t launch_gemv_mma(const MatView& m, const float* x, float* y, int64_t tokens,
+                            cudaStream_t stream, int sm_count, int* err, uint64_t* launches) {
+  for (int64_t t0 = 0; t0 < tokens; t0 += 8) {
+    const int nt = (int)(tokens - t0 < 8 ? tokens - t0 : 8);
+    const float* xp = x + t0 * m.cols;
+    float* yp = y + t0 * m.rows;
+    cudaError_t e;
+    if (nt == 1) e = launch_single<1>(m, xp, yp, nt, stream, sm_count, err);
+    else if (nt == 2) e = launch_single<2>(m, xp, yp, nt, stream, sm_count, err);
+    else if (nt <= 4) e = launch_single<4>(m, xp, yp, nt, stream, sm_count, err);
+    else e = launch_single<8>(m, xp, yp, nt, stream, sm_count, err);
+    if (e != cudaSuccess) return e;
+    if (launches) ++*launches;
+  }
+  return cudaSuccess;
+}
+
+// ------------------------------------------------------------------ programs
+struct Program {
+  ProgEntry* d_entries = nullptr;
+  ProgPhase* d_phases = nullptr;
+  unsigned long long* d_counters = nullptr;
+  int n_phases = 0, n_entries = 0, max_tokens = 1, grid = 0;
+  unsigned long long epoch = 0;
+};
+
+bool prog_entry_supported(const MatView& m) { return gemv_mma_supported(m); }
+
+template <int MT>
+static cudaError_t prog_prepare(int sm_count, int* grid) {
+  int bps = 0;
+  cudaError_t e = occupancy(gemv_program_kernel<MT>, SLay<MT>::TOTAL, &bps);
+  if (e != cudaSuccess) return e;
+  *grid = sm_count * bps;
+  return cudaSuccess;
+}
+
+template <int MT>
+static cudaError_t prog_launch(Program* p, cudaStream_t stream, int* err) {
+  auto kern = gemv_program_kernel<MT>;
+  ++p->epoch;
+  const ProgEntry* de = p->d_entries;
+  const ProgPhase* dp = p->d_phases;
+  int np = p->n_phases;
+  unsigned long long* dc = p->d_counters;
+  unsigned long long ep = p->epoch;
+  void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dc, (void*)&ep, (void*)&err};
+  // cooperative: every CTA must be resident, the phase counters are a grid-wide dependency
+  return cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)p->grid), dim3(NTHREADS), args,
+                                     SLay<MT>::TOTAL, stream);
+}
+
+cudaError_t program_create(const std::vector<ProgEntry>& entries_in, const std::vector<int>& phase_of,
+                           int sm_count, Program** out, std::string* msg) {
+  Program* p = new (std::nothrow) Program();
+  if (!p) return cudaErrorMemoryAllocation;
+  std::vector<ProgEntry> entries = entries_in;
+  std::vector<ProgPhase> phases;
+  for (size_t i = 0; i < entries.size(); ++i) {
+    ProgEntry& E = entries[i];
+    E.n_tiles = (E.rows + 15) / 16;
+    if (i == 0 || phase_of[i] != phase_of[i - 1]) phases.push_back(ProgPhase{(int)i, 0, 0, i == 0 ? 0 : 1});
+    ProgPhase& P = phases.back();
+    E.tile_begin = P.n_tiles;
+    P.n_tiles += E.n_tiles;
+    ++P.n_entries;
+    if (E.tokens > p->max_tokens) p->max_tokens = E.tokens;
+  }
+  p->n_phases = (int)phases.size();
+  p->n_entries = (int)entries.size();
+  cudaError_t e;
+  const int mt = p->max_tokens;
+  if (mt == 1) e = prog_prepare<1>(sm_count, &p->grid);
+  else if (mt == 2) e = prog_prepare<2>(sm_count, &p->grid);
+  else if (mt <= 4) e = prog_prepare<4>(sm_count, &p->grid);
+  else e = prog_prepare<8>(sm_count, &p->grid);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_entries, entries.size() * sizeof(ProgEntry));
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_phases, phases.size() * sizeof(ProgPhase));
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_counters, phases.size() * sizeof(unsigned long long));
+  if (e == cudaSuccess) e = cudaMemcpy(p->d_entries, entries.data(), entries.size() * sizeof(ProgEntry), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(p->d_phases, phases.data(), phases.size() * sizeof(ProgPhase), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemset(p->d_counters, 0, phases.size() * sizeof(unsigned long long));
+  if (e != cudaSuccess) {
+    if (msg) *msg = cudaGetErrorString(e);
+    program_destroy(p);
+    return e;
+  }
+  *out = p;
+  return cudaSuccess;
+}
+
+void program_destroy(Program* p) {
+  if (!p) return;
+  if (p->d_entries) cudaFree(p->d_entries);
+  if (p->d_phases) cudaFree(p->d_phases);
+  if (p->d_counters) cudaFree(p->d_counters);
+  delete p;
+}
+
+cudaError_t program_run(Program* p, cudaStream_t stream, int* err_flag, uint64_t* launches) {
+  cudaError_t e;
+  const int mt = p->max_tokens;
+  if (mt == 1) e = prog_launch<1>(p, stream, err_flag);
+  else if (mt == 2) e = prog_launch<2>(p, stream, err_flag);
+  else if (mt <= 4) e = prog_launch<4>(p, stream, err_flag);
+  else e = prog_launch<8>(p, stream, err_flag);
+  if (e == cudaSuccess && launches) ++*launches;
+  return e;
+}
+
+int program_phases(const Program* p) { return p->n_phases; }
+int program_entries(const Program* p) { return p->n_entries; }
+
+}  // namespace llr

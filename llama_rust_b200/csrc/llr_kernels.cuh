@@ -4,6 +4,9 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <string>
+#include <vector>
+
 namespace llr {
 
 // A resident packed matrix as the kernels see it.  `w` is 256-byte aligned and
@@ -38,6 +41,27 @@ cudaError_t launch_gemv_staged(const MatView& m, const float* x, float* y, int64
 bool gemv_mma_supported(const MatView& m);
 cudaError_t launch_gemv_mma(const MatView& m, const float* x, float* y, int64_t tokens,
                             cudaStream_t stream, int sm_count, int* err_flag, uint64_t* launches);
+
+// One matrix product of a program (llr_gemv_prog.cu).  tile_begin / n_tiles are filled in
+// by program_create.
+struct ProgEntry {
+  const uint8_t* w;
+  const float* x;
+  float* y;
+  int64_t row_bytes;
+  int rows, cols, dtype, tokens;
+  int tile_begin, n_tiles;
+};
+struct ProgPhase { int first_entry, n_entries, n_tiles, wait_prev; };
+struct Program;
+bool prog_entry_supported(const MatView& m);
+// phase_of[i] is non-decreasing; a change starts a phase that waits for the previous one
+cudaError_t program_create(const std::vector<ProgEntry>& entries, const std::vector<int>& phase_of,
+                           int sm_count, Program** out, std::string* msg);
+void program_destroy(Program* p);
+cudaError_t program_run(Program* p, cudaStream_t stream, int* err_flag, uint64_t* launches);
+int program_phases(const Program* p);
+int program_entries(const Program* p);
 
 // out[(r-row0)*cols + c] = dequantized W[r,c], bit-exact with the reference.
 cudaError_t launch_dequant(const MatView& m, int64_t row0, int64_t n_rows, float* out,

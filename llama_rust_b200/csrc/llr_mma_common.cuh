@@ -1,0 +1,297 @@
+// Device building blocks shared by the integer tensor-core decode kernels
+// (llr_gemv_mma.cu: one matrix per launch; llr_gemv_prog.cu: a whole list of
+// matrix products per launch): shared-memory geometry, TMA / mbarrier / mma.sync
+// wrappers, the per-format block routines and the activation digit split.
+#pragma once
+#include "llr_formats.cuh"
+
+namespace llr {
+namespace mma {
+
+constexpr int NWARP = 8;
+constexpr int NST = 2;          // chunks in flight per CTA
+constexpr int SPAN = 4096;      // columns whose digit planes live in shared memory
+constexpr int DS = SPAN + 32;   // digit plane stride: 32 mod 128 -> conflict-free 8-byte reads
+constexpr int SPIN_LIMIT = 1 << 22;
+
+template <int DT> struct Fmt;
+template <> struct Fmt<DT_Q4_K> { static constexpr int KSEG = 4096, BB = 144, BE = 256; };
+template <> struct Fmt<DT_Q6_K> { static constexpr int KSEG = 2048, BB = 210, BE = 256; };
+template <> struct Fmt<DT_Q8_0> { static constexpr int KSEG = 2048, BB = 34, BE = 32; };
+
+template <int DT, int MT> struct Lay {
+  using F = Fmt<DT>;
+  static constexpr int NT = (MT + 1) / 2;                       // n-tiles of 2 activation rows
+  static constexpr int SEGB = F::KSEG / F::BE * F::BB;          // bytes of one row segment
+  // row stride mod 128: 32 spreads the 8-byte fragment reads of eight rows over all banks,
+  // 16 does the same for the 4-byte reads of Q6_K
+  static constexpr int RMOD = DT == DT_Q6_K ? 16 : 32;
+  static constexpr int RS = SEGB + (RMOD + 128 - SEGB % 128) % 128;
+  static constexpr int CHUNK = 16 * RS;
+  static constexpr int RING = 0;
+  static constexpr int DIG = RING + NST * CHUNK;                // int8 [NT*8][DS]
+  static constexpr int SXF = DIG + NT * 8 * DS;                 // float [MT][SPAN/32]
+  static constexpr int XSI = SXF + MT * (SPAN / 32) * 4;        // float [MT][SPAN/256]
+  static constexpr int RED = XSI + MT * (SPAN / 256) * 4;       // float [2][NWARP][16][MT]
+  static constexpr int BAR = RED + 2 * NWARP * 16 * MT * 4;     // uint64 [NST]
+  static constexpr int TOTAL = BAR + NST * 8 + 16;
+  static_assert(RS % 16 == 0 && RS % 128 == RMOD, "row stride");
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+               : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// untiled bulk copy global -> this CTA's shared memory; both addresses and the
+// size are multiples of 16 bytes (checked on the host before this kernel is chosen)
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mma_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void mma_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+               : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+__device__ __forceinline__ float h2f(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+
+// four bytes at p (p is 2-byte aligned; `odd` says p % 4 == 2)
+__device__ __forceinline__ uint32_t lds32_a2(const uint8_t* p, bool odd) {
+  if (!odd) return *(const uint32_t*)p;
+  const uint32_t lo = *(const uint32_t*)(p - 2), hi = *(const uint32_t*)(p + 2);
+  return __funnelshift_r(lo, hi, 16);
+}
+// eight bytes at p, same alignment rule
+__device__ __forceinline__ uint2 lds64_a2(const uint8_t* p, bool odd) {
+  if (!odd) return make_uint2(*(const uint32_t*)p, *(const uint32_t*)(p + 4));
+  const uint32_t x0 = *(const uint32_t*)(p - 2), x1 = *(const uint32_t*)(p + 2), x2 = *(const uint32_t*)(p + 6);
+  return make_uint2(__funnelshift_r(x0, x1, 16), __funnelshift_r(x1, x2, 16));
+}
+// per byte: 6-bit code c (0..63) -> int8 (c - 32); no carries cross bytes
+__device__ __forceinline__ uint32_t recentre6(uint32_t c) {
+  return ((c | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
+}
+
+// Per-thread accumulators of one chunk: yacc[nt][0..1] row g, [2..3] row g+8,
+// columns 2t, 2t+1 of n-tile nt; ymin only for Q4_K.
+template <int MT> struct AccT {
+  static constexpr int NT = (MT + 1) / 2;
+  float y[NT][4];
+  float mn[2][MT];
+};
+template <int DT, int MT> using Acc = AccT<MT>;
+
+// One Q4_K super-block (256 columns) of rows g and g+8 against every n-tile.
+template <int MT>
+__device__ __forceinline__ void block_q4k(const uint8_t* rowA, const uint8_t* rowB, int b, int cb,
+                                          const uint8_t* dig, const float* sxf, const float* xsi,
+                                          int g, int t, Acc<DT_Q4_K, MT>& acc) {
+  constexpr int NT = (MT + 1) / 2;
+  const uint4 hA = *(const uint4*)(rowA + b * 144), hB = *(const uint4*)(rowB + b * 144);
+  // 6-bit scales and mins packed four to a word: bytes 0..3 = sub-blocks 0..3 (word 0), 4..7 (word 1)
+  const uint32_t scA0 = hA.y & 0x3f3f3f3fu, scA1 = (hA.w & 0x0f0f0f0fu) | ((hA.y >> 2) & 0x30303030u);
+  const uint32_t scB0 = hB.y & 0x3f3f3f3fu, scB1 = (hB.w & 0x0f0f0f0fu) | ((hB.y >> 2) & 0x30303030u);
+  int T[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) T[nt][i] = 0;
+#pragma unroll
+  for (int G = 0; G < 4; ++G) {
+    const uint2 wA = *(const uint2*)(rowA + b * 144 + 16 + G * 32 + 8 * t);
+    const uint2 wB = *(const uint2*)(rowB + b * 144 + 16 + G * 32 + 8 * t);
+    constexpr uint32_t M4 = 0x0f0f0f0fu;
+    const uint32_t scAp = G < 2 ? scA0 : scA1, scBp = G < 2 ? scB0 : scB1;
+    const int sAlo = (scAp >> (16 * (G & 1))) & 255, sAhi = (scAp >> (16 * (G & 1) + 8)) & 255;
+    const int sBlo = (scBp >> (16 * (G & 1))) & 255, sBhi = (scBp >> (16 * (G & 1) + 8)) & 255;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const uint8_t* dp = dig + (size_t)(nt * 8 + g) * DS + cb * 256 + G * 64 + 8 * t;
+      const uint2 blo = *(const uint2*)dp, bhi = *(const uint2*)(dp + 32);
+      int clo[4], chi[4];
+      mma_k32(clo, wA.x & M4, wB.x & M4, wA.y & M4, wB.y & M4, blo.x, blo.y);
+      mma_k32(chi, (wA.x >> 4) & M4, (wB.x >> 4) & M4, (wA.y >> 4) & M4, (wB.y >> 4) & M4, bhi.x, bhi.y);
+      T[nt][0] += sAlo * clo[0] + sAhi * chi[0];
+      T[nt][1] += sAlo * clo[1] + sAhi * chi[1];
+      T[nt][2] += sBlo * clo[2] + sBhi * chi[2];
+      T[nt][3] += sBlo * clo[3] + sBhi * chi[3];
+    }
+  }
+  const float dA = h2f(hA.x & 0xffffu), dminA = h2f(hA.x >> 16);
+  const float dB = h2f(hB.x & 0xffffu), dminB = h2f(hB.x >> 16);
+  // columns 2t, 2t+1 of an n-tile are activation row (t >> 1), digits 2(t&1) and 2(t&1)+1
+  const float pw0 = (t & 1) ? 16384.f : 1.f, pw1 = pw0 * 128.f;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int tok = 2 * nt + (t >> 1);
+    const float xs = tok < MT ? xsi[tok * (SPAN / 256) + cb] : 0.f;
+    acc.y[nt][0] = fmaf((float)T[nt][0], dA * xs * pw0, acc.y[nt][0]);
+    acc.y[nt][1] = fmaf((float)T[nt][1], dA * xs * pw1, acc.y[nt][1]);
+    acc.y[nt][2] = fmaf((float)T[nt][2], dB * xs * pw0, acc.y[nt][2]);
+    acc.y[nt][3] = fmaf((float)T[nt][3], dB * xs * pw1, acc.y[nt][3]);
+  }
+  // mins: this thread covers sub-blocks 2t, 2t+1 of both rows
+  const uint32_t mnA = t < 2 ? (hA.z & 0x3f3f3f3fu) : (((hA.w >> 4) & 0x0f0f0f0fu) | ((hA.z >> 2) & 0x30303030u));
+  const uint32_t mnB = t < 2 ? (hB.z & 0x3f3f3f3fu) : (((hB.w >> 4) & 0x0f0f0f0fu) | ((hB.z >> 2) & 0x30303030u));
+  const float a0 = dminA * (float)((mnA >> (16 * (t & 1))) & 255), a1 = dminA * (float)((mnA >> (16 * (t & 1) + 8)) & 255);
+  const float b0 = dminB * (float)((mnB >> (16 * (t & 1))) & 255), b1 = dminB * (float)((mnB >> (16 * (t & 1) + 8)) & 255);
+#pragma unroll
+  for (int k = 0; k < MT; ++k) {
+    const float s0 = sxf[k * (SPAN / 32) + cb * 8 + 2 * t], s1 = sxf[k * (SPAN / 32) + cb * 8 + 2 * t + 1];
+    acc.mn[0][k] = fmaf(a0, s0, fmaf(a1, s1, acc.mn[0][k]));
+    acc.mn[1][k] = fmaf(b0, s0, fmaf(b1, s1, acc.mn[1][k]));
+  }
+}
+
+// One Q6_K super-block: 16 scale groups of 16 columns, one m16n8k16 each.
+template <int MT>
+__device__ __forceinline__ void block_q6k(const uint8_t* rowA, const uint8_t* rowB, int b, int cb,
+                                          const uint8_t* dig, const float* xsi, int g, int t,
+                                          Acc<DT_Q6_K, MT>& acc) {
+  constexpr int NT = (MT + 1) / 2;
+  const uint8_t* pA = rowA + b * 210;
+  const uint8_t* pB = rowB + b * 210;
+  const bool odd = (b & 1) != 0;  // 210 b mod 4 is 2 for odd b (row segments start 16-byte aligned)
+  int T[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) T[nt][i] = 0;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+#pragma unroll
+    for (int hg = 0; hg < 2; ++hg) {  // l = 16*hg + 4t .. +3 of the 32-wide runs
+      const int l = 16 * hg + 4 * t;
+      const uint32_t qlA0 = lds32_a2(pA + half * 64 + l, odd), qlA1 = lds32_a2(pA + half * 64 + 32 + l, odd);
+      const uint32_t qhA = lds32_a2(pA + 128 + half * 32 + l, odd);
+      const uint32_t qlB0 = lds32_a2(pB + half * 64 + l, odd), qlB1 = lds32_a2(pB + half * 64 + 32 + l, odd);
+      const uint32_t qhB = lds32_a2(pB + 128 + half * 32 + l, odd);
+      constexpr uint32_t M4 = 0x0f0f0f0fu, M2 = 0x03030303u;
+#pragma unroll
+      for (int qtr = 0; qtr < 4; ++qtr) {
+        const uint32_t lA = (qtr & 1) ? qlA1 : qlA0, lB = (qtr & 1) ? qlB1 : qlB0;
+        const uint32_t cA = recentre6((((qtr & 2) ? (lA >> 4) : lA) & M4) | (((qhA >> (2 * qtr)) & M2) << 4));
+        const uint32_t cB = recentre6((((qtr & 2) ? (lB >> 4) : lB) & M4) | (((qhB >> (2 * qtr)) & M2) << 4));
+        const int sidx = 192 + half * 8 + hg + 2 * qtr;
+        const int sA = (int)(int8_t)pA[sidx], sB = (int)(int8_t)pB[sidx];
+        const int col = cb * 256 + half * 128 + qtr * 32 + l;  // first of this thread's 4 columns
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint32_t bd = *(const uint32_t*)(dig + (size_t)(nt * 8 + g) * DS + col);
+          int c[4];
+          mma_k16(c, cA, cB, bd);
+          T[nt][0] += sA * c[0]; T[nt][1] += sA * c[1];
+          T[nt][2] += sB * c[2]; T[nt][3] += sB * c[3];
+        }
+      }
+    }
+  }
+  const float dA = h2f(pA[208] | (pA[209] << 8)), dB = h2f(pB[208] | (pB[209] << 8));
+  const float pw0 = (t & 1) ? 16384.f : 1.f, pw1 = pw0 * 128.f;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int tok = 2 * nt + (t >> 1);
+    const float xs = tok < MT ? xsi[tok * (SPAN / 256) + cb] : 0.f;
+    acc.y[nt][0] = fmaf((float)T[nt][0], dA * xs * pw0, acc.y[nt][0]);
+    acc.y[nt][1] = fmaf((float)T[nt][1], dA * xs * pw1, acc.y[nt][1]);
+    acc.y[nt][2] = fmaf((float)T[nt][2], dB * xs * pw0, acc.y[nt][2]);
+    acc.y[nt][3] = fmaf((float)T[nt][3], dB * xs * pw1, acc.y[nt][3]);
+  }
+}
+
+// One Q8_0 block (32 columns): the int8 quants are the A fragment as they lie.
+template <int MT>
+__device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* rowB, int b, int c32,
+                                          const uint8_t* dig, const float* xsi, int g, int t,
+                                          Acc<DT_Q8_0, MT>& acc) {
+  constexpr int NT = (MT + 1) / 2;
+  const uint8_t* pA = rowA + b * 34;
+  const uint8_t* pB = rowB + b * 34;
+  const bool odd = (b & 1) == 0;  // quants start at 34 b + 2: 4-byte aligned for odd b only
+  const uint2 wA = lds64_a2(pA + 2 + 8 * t, odd), wB = lds64_a2(pB + 2 + 8 * t, odd);
+  const float dA = h2f(*(const uint16_t*)pA), dB = h2f(*(const uint16_t*)pB);
+  const float pw0 = (t & 1) ? 16384.f : 1.f, pw1 = pw0 * 128.f;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const uint2 bd = *(const uint2*)(dig + (size_t)(nt * 8 + g) * DS + c32 * 32 + 8 * t);
+    int c[4];
+    mma_k32(c, wA.x, wB.x, wA.y, wB.y, bd.x, bd.y);
+    const int tok = 2 * nt + (t >> 1);
+    const float xs = tok < MT ? xsi[tok * (SPAN / 256) + (c32 >> 3)] : 0.f;
+    acc.y[nt][0] = fmaf((float)c[0], dA * xs * pw0, acc.y[nt][0]);
+    acc.y[nt][1] = fmaf((float)c[1], dA * xs * pw1, acc.y[nt][1]);
+    acc.y[nt][2] = fmaf((float)c[2], dB * xs * pw0, acc.y[nt][2]);
+    acc.y[nt][3] = fmaf((float)c[3], dB * xs * pw1, acc.y[nt][3]);
+  }
+}
+
+
+// Activations of one span (nblk256 blocks of 256 columns starting at column col0, `tokens`
+// activation rows) -> four int8 digit planes per activation row, the f32 sums of x per 32
+// columns (Q4_K mins) and 2^-e per block.  One warp per (block, row); `coherent` selects
+// L2-coherent loads for activations that an earlier phase of the same launch produced.
+__device__ __forceinline__ void split_activations(const float* __restrict__ X, int cols, int col0,
+                                                  int nblk256, int tokens, uint8_t* dig, float* sxf,
+                                                  float* xsi, int warp, int lane, bool coherent) {
+  for (int job = warp; job < nblk256 * tokens; job += NWARP) {
+    const int b = job % nblk256, tok = job / nblk256;
+    const float4* xp = (const float4*)(X + (int64_t)tok * cols + col0 + b * 256 + 8 * lane);
+    const float4 va = coherent ? __ldcg(xp) : __ldg(xp), vb = coherent ? __ldcg(xp + 1) : __ldg(xp + 1);
+    const float v[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+    float m = 0.f, sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { m = fmaxf(m, fabsf(v[j])); sum += v[j]; }
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) bad = bad || !(fabsf(v[j]) <= 3.4028234e38f);
+#pragma unroll
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(~0u, m, o));
+    bad = __any_sync(~0u, bad);
+    sum += __shfl_xor_sync(~0u, sum, 1);
+    sum += __shfl_xor_sync(~0u, sum, 2);
+    const int be = (int)((__float_as_uint(m) >> 23) & 0xff);
+    float s = 0.f, sinv = 0.f;  // an all-zero (or denormal) block contributes nothing
+    if (be != 0 && !bad) {
+      int e = 26 - (be - 127);
+      e = e > 126 ? 126 : e;
+      s = __uint_as_float((uint32_t)(e + 127) << 23);
+      sinv = __uint_as_float((uint32_t)(127 - e) << 23);
+    }
+    uint32_t pk[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      int xi = bad ? 0 : __float2int_rn(v[j] * s);
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        const int d = p < 3 ? (((xi + 64) & 127) - 64) : xi;
+        xi = (xi - d) >> 7;
+        pk[p][j >> 2] |= (uint32_t)(d & 255) << (8 * (j & 3));
+      }
+    }
+    const int nt = tok >> 1, plane0 = (tok & 1) * 4;
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+      *(uint2*)(dig + (size_t)(nt * 8 + plane0 + p) * DS + b * 256 + 8 * lane) = make_uint2(pk[p][0], pk[p][1]);
+    if ((lane & 3) == 0) sxf[tok * (SPAN / 32) + b * 8 + (lane >> 2)] = sum;
+    // a non-finite activation makes the whole output row of that token NaN
+    if (lane == 0) xsi[tok * (SPAN / 256) + b] = bad ? __uint_as_float(0x7fc00000u) : sinv;
+  }
+}
+
+}  // namespace mma
+}  // namespace llr

@@ -79,6 +79,27 @@ class Matrix:
             pass
 
 
+class Program:
+    """A fixed list of decode products run by one persistent launch (llr_program_*)."""
+
+    def __init__(self, executor: "Executor", handle: int, n_entries: int):
+        self._exec, self._h, self.n_entries = executor, handle, n_entries
+
+    def run(self, stream: int = 0) -> None:
+        self._exec._check(lib().llr_program_run(self._exec._h, self._h, stream))
+
+    def free(self) -> None:
+        if self._h:
+            lib().llr_program_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class Executor:
     """One device, one stream, scratch reuse and weight residency (CudaGemv, gpu.rs:139)."""
 
@@ -152,6 +173,16 @@ class Executor:
 
     def matmul_device(self, m: Matrix, tokens: int, x_ptr: int, y_ptr: int, stream: int = 0) -> None:
         self._check(lib().llr_matmul_device(self._h, m._h, tokens, x_ptr, y_ptr, stream))
+
+    def program(self, entries) -> Program:
+        """entries: iterable of (matrix, x_ptr, y_ptr, tokens, phase); see llr_program_create."""
+        entries = list(entries)
+        arr = (_lib.ProgramEntry * len(entries))()
+        for i, (m, x, y, tokens, phase) in enumerate(entries):
+            arr[i] = _lib.ProgramEntry(m._h, x, y, tokens, phase)
+        h = C.c_void_p()
+        self._check(lib().llr_program_create(self._h, arr, len(entries), C.byref(h)))
+        return Program(self, h.value, len(entries))
 
     def dequant_rows(self, m: Matrix, row0: int = 0, n_rows: int | None = None) -> np.ndarray:
         n = m.rows - row0 if n_rows is None else n_rows
