@@ -103,7 +103,10 @@ __device__ __forceinline__ bool entry_range(const ProgEntry& E, int lo, int hi, 
   return *t0 < *t1;
 }
 
-template <int MT, bool PROGRAM>
+// DTFIX: the one format of a single-product launch (the other block routines are compiled
+// out, which keeps the consumers under the register budget of two CTAs per SM), or -1 for
+// programs, which switch per entry.
+template <int MT, bool PROGRAM, int DTFIX>
 __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* counters,
                                             unsigned long long epoch, int* err) {
   using L = SLay<MT>;
@@ -143,7 +146,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           const ProgEntry E = wk.entries[P.first_entry + ei];
           int t0, t1;
           if (!entry_range(E, lo, hi, &t0, &t1)) continue;
-          const Geom gm = geom_of(E.dtype);
+          const Geom gm = geom_of(DTFIX >= 0 ? DTFIX : E.dtype);
           const int n_span = (E.cols + SPAN - 1) / SPAN;
           for (int span = 0; span < n_span; ++span) {
             const int span_cols = min(SPAN, E.cols - span * SPAN);
@@ -209,10 +212,8 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
       if (PROGRAM) {
         // this CTA's share of the phase is written: publish it
         __syncwarp();
-        if (lane == 0) {
-          __threadfence();
-          atomicAdd(counters + ph, 1ull);
-        }
+        if (lane == 0)  // release: the y values written above are visible before the count
+          asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(counters + ph), "l"(1ull) : "memory");
       }
     }
     return;
@@ -249,7 +250,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
       const ProgEntry E = wk.entries[P.first_entry + ei];
       int t0, t1;
       if (!entry_range(E, lo, hi, &t0, &t1)) continue;
-      const Geom gm = geom_of(E.dtype);
+      const Geom gm = geom_of(DTFIX >= 0 ? DTFIX : E.dtype);
       const int n_span = (E.cols + SPAN - 1) / SPAN;
       for (int span = 0; span < n_span; ++span) {
         const int span_cols = min(SPAN, E.cols - span * SPAN), nblk256 = span_cols >> 8;
@@ -275,10 +276,11 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
             const uint8_t* rowA = chunk + g * gm.rs;
             const uint8_t* rowB = chunk + (g + 8) * gm.rs;
             const int seg_cols = min(gm.kseg, span_cols - sub * gm.kseg);
-            if (E.dtype == DT_Q4_K) {
+            const int dtype = DTFIX >= 0 ? DTFIX : E.dtype;
+            if (dtype == DT_Q4_K) {
               for (int b = warp; b < (seg_cols >> 8); b += CW)
                 block_q4k<MT>(rowA, rowB, b, sub * (gm.kseg / 256) + b, dig, sxf, xsi, g, t, acc);
-            } else if (E.dtype == DT_Q6_K) {
+            } else if (dtype == DT_Q6_K) {
               for (int b = warp; b < (seg_cols >> 8); b += CW)
                 block_q6k<MT>(rowA, rowB, b, sub * (gm.kseg / 256) + b, dig, xsi, g, t, acc);
             } else {
@@ -292,7 +294,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           const int rb = j % NRB;
           if (ok && !mbar_wait(&rempty[rb], (uint32_t)(((j / NRB) & 1) ^ 1))) { ok = false; if (lane == 0) atomicExch(err, 1); }
           float* myred = red + (rb * CW + warp) * 16 * MT;
-          if (E.dtype == DT_Q4_K) {
+          if ((DTFIX >= 0 ? DTFIX : E.dtype) == DT_Q4_K) {
 #pragma unroll
             for (int k = 0; k < MT; ++k)
 #pragma unroll
@@ -328,14 +330,14 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
 
 // two CTAs per SM need <= 102 registers per thread; with more than two activation rows the
 // digit planes leave room for one CTA only
-template <int MT>
+template <int MT, int DT>
 __global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
 gemv_stream_kernel(const __grid_constant__ ProgEntry one, int* __restrict__ err) {
   __shared__ ProgPhase phase;
   if (threadIdx.x == 0) phase = ProgPhase{0, 1, one.n_tiles, 0};
   __syncthreads();
   Work wk{&one, &phase, 1};
-  stream_body<MT, false>(wk, nullptr, 0ull, err);
+  stream_body<MT, false, DT>(wk, nullptr, 0ull, err);
 }
 
 template <int MT>
@@ -343,7 +345,7 @@ __global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
 gemv_program_kernel(const ProgEntry* __restrict__ entries, const ProgPhase* __restrict__ phases, int n_phases,
                     unsigned long long* __restrict__ counters, unsigned long long epoch, int* __restrict__ err) {
   Work wk{entries, phases, n_phases};
-  stream_body<MT, true>(wk, counters, epoch, err);
+  stream_body<MT, true, -1>(wk, counters, epoch, err);
 }
 
 template <class K>
@@ -357,10 +359,10 @@ cudaError_t occupancy(K kern, int smem, int* blocks_per_sm) {
   return cudaSuccess;
 }
 
-template <int MT>
+template <int MT, int DT>
 cudaError_t launch_single(const MatView& m, const float* x, float* y, int tokens, cudaStream_t stream,
                           int sm_count, int* err) {
-  auto kern = gemv_stream_kernel<MT>;
+  auto kern = gemv_stream_kernel<MT, DT>;
   constexpr int smem = SLay<MT>::TOTAL;
   static int blocks_per_sm = 0;  // per instantiation
   if (blocks_per_sm == 0) {
@@ -402,10 +404,15 @@ cudaError_t launch_gemv_mma(const MatView& m, const float* x, float* y, int64_t 
     const float* xp = x + t0 * m.cols;
     float* yp = y + t0 * m.rows;
     cudaError_t e;
-    if (nt == 1) e = launch_single<1>(m, xp, yp, nt, stream, sm_count, err);
-    else if (nt == 2) e = launch_single<2>(m, xp, yp, nt, stream, sm_count, err);
-    else if (nt <= 4) e = launch_single<4>(m, xp, yp, nt, stream, sm_count, err);
-    else e = launch_single<8>(m, xp, yp, nt, stream, sm_count, err);
+#define LLR_LAUNCH_DT(D)                                                                      \
+    (nt == 1 ? launch_single<1, D>(m, xp, yp, nt, stream, sm_count, err)                      \
+     : nt == 2 ? launch_single<2, D>(m, xp, yp, nt, stream, sm_count, err)                    \
+     : nt <= 4 ? launch_single<4, D>(m, xp, yp, nt, stream, sm_count, err)                    \
+               : launch_single<8, D>(m, xp, yp, nt, stream, sm_count, err))
+    if (m.dtype == DT_Q4_K) e = LLR_LAUNCH_DT(DT_Q4_K);
+    else if (m.dtype == DT_Q6_K) e = LLR_LAUNCH_DT(DT_Q6_K);
+    else e = LLR_LAUNCH_DT(DT_Q8_0);
+#undef LLR_LAUNCH_DT
     if (e != cudaSuccess) return e;
     if (launches) ++*launches;
   }

@@ -248,10 +248,25 @@ __device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* ro
 __device__ __forceinline__ void split_activations(const float* __restrict__ X, int cols, int col0,
                                                   int nblk256, int tokens, uint8_t* dig, float* sxf,
                                                   float* xsi, int warp, int lane, bool coherent) {
-  for (int job = warp; job < nblk256 * tokens; job += NWARP) {
+  // two jobs per warp and pass: both loads are in flight before either is used
+  const int njobs = nblk256 * tokens;
+  for (int job0 = warp; job0 < njobs; job0 += 2 * NWARP) {
+   float4 pa[2], pb[2];
+#pragma unroll
+   for (int u = 0; u < 2; ++u) {
+    const int job = job0 + u * NWARP;
+    if (job < njobs) {
+      const float4* xp = (const float4*)(X + (int64_t)(job / nblk256) * cols + col0 + (job % nblk256) * 256 + 8 * lane);
+      pa[u] = coherent ? __ldcg(xp) : __ldg(xp);
+      pb[u] = coherent ? __ldcg(xp + 1) : __ldg(xp + 1);
+    }
+   }
+#pragma unroll
+   for (int u = 0; u < 2; ++u) {
+    const int job = job0 + u * NWARP;
+    if (job >= njobs) break;
     const int b = job % nblk256, tok = job / nblk256;
-    const float4* xp = (const float4*)(X + (int64_t)tok * cols + col0 + b * 256 + 8 * lane);
-    const float4 va = coherent ? __ldcg(xp) : __ldg(xp), vb = coherent ? __ldcg(xp + 1) : __ldg(xp + 1);
+    const float4 va = pa[u], vb = pb[u];
     const float v[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
     float m = 0.f, sum = 0.f;
 #pragma unroll
@@ -290,6 +305,7 @@ __device__ __forceinline__ void split_activations(const float* __restrict__ X, i
     if ((lane & 3) == 0) sxf[tok * (SPAN / 32) + b * 8 + (lane >> 2)] = sum;
     // a non-finite activation makes the whole output row of that token NaN
     if (lane == 0) xsi[tok * (SPAN / 256) + b] = bad ? __uint_as_float(0x7fc00000u) : sinv;
+   }
   }
 }
 
