@@ -86,8 +86,12 @@ int llr_exec_counters(const llr_exec* exec, llr_counters* out);
  * (integer tensor-core kernel where the format and shape allow, else the
  * staged kernel, else the shape-agnostic one), 1 = the shape-agnostic byte-load
  * kernel, 2 = the shared-memory staged FMA kernel (falls back to 1 for shapes
- * it cannot take), 3 = same as 0.  Also read once from the environment
- * variable LLR_GEMV_PATH (generic|staged|mma) when the executor is created. */
+ * it cannot take), 3 = the integer tensor-core kernel for any number of
+ * activation rows (f32-faithful), 4 = the bf16 tcgen05 GEMM whenever it can take
+ * the call.  Automatic choice: up to 63 activation rows as 3, from 64 rows the
+ * bf16 tcgen05 GEMM for Q4_K/Q8_0/Q5_0/Q5_1 (looser tolerance).
+ * Also read once from the environment variable LLR_GEMV_PATH
+ * (generic|staged|mma|tc) when the executor is created. */
 int llr_exec_set_path(llr_exec* exec, int path);
 
 /* Packed bytes of one row of `cols` columns.  Replaces the <t>_row_bytes

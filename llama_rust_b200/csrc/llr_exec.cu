@@ -117,6 +117,7 @@ struct llr_exec {
   float* pin_y = nullptr; size_t pin_y_cap = 0;
   float* dev_x = nullptr; size_t dev_x_cap = 0;
   float* dev_y = nullptr; size_t dev_y_cap = 0;
+  uint8_t* dev_s = nullptr; size_t dev_s_cap = 0;  // kernel scratch (bf16 activations of the tensor-core GEMM)
   // residency
   std::list<CacheEntry> cache;  // front = least recently used
   bool limit_resolved = false;
@@ -271,6 +272,16 @@ MatView view_of(const llr_matrix* m) {
   return MatView{m->dev, m->dtype, m->rows, m->cols, m->row_bytes};
 }
 
+// scratch for the tensor-core GEMM; growing frees the old buffer, which synchronizes the device
+cudaError_t ensure_scratch(llr_exec* e, const llr_matrix* m, size_t tokens, void** out) {
+  *out = nullptr;
+  const MatView v = view_of(m);
+  if (!matmul_wants_tc(v, (int64_t)tokens, e->path)) return cudaSuccess;
+  cudaError_t ce = grow_device(&e->dev_s, &e->dev_s_cap, gemm_tc_scratch_bytes(v, (int64_t)tokens));
+  if (ce == cudaSuccess) *out = e->dev_s;
+  return ce;
+}
+
 bool is_pinned_host(const void* p) {
   cudaPointerAttributes a{};
   if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
@@ -296,10 +307,12 @@ int run_host(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, fl
     if ((ce = grow_pinned(&e->pin_y, &e->pin_y_cap, ny)) != cudaSuccess) return fail_cuda(e, ce, "pinned result staging");
     dst = e->pin_y;
   }
+  void* scratch = nullptr;
+  if ((ce = ensure_scratch(e, m, tokens, &scratch)) != cudaSuccess) return fail_cuda(e, ce, "kernel scratch");
   if ((ce = cudaMemcpyAsync(e->dev_x, src, nx * sizeof(float), cudaMemcpyHostToDevice, e->stream)) != cudaSuccess)
     return fail_cuda(e, ce, "activation upload");
   if ((ce = launch_matmul(view_of(m), e->dev_x, e->dev_y, (int64_t)tokens, e->stream, e->path,
-                          e->sm_count, e->err_flag, &e->ctr.launches)) != cudaSuccess)
+                          e->sm_count, e->err_flag, scratch, &e->ctr.launches)) != cudaSuccess)
     return fail_cuda(e, ce, "kernel launch");
   if ((ce = cudaMemcpyAsync(dst, e->dev_y, ny * sizeof(float), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess)
     return fail_cuda(e, ce, "result download");
@@ -321,10 +334,18 @@ int run_host(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, fl
 
 namespace llr {
 
+bool matmul_wants_tc(const MatView& m, int64_t tokens, int path) {
+  if (path == PATH_TC) return gemm_tc_supported(m, tokens);
+  return path == PATH_AUTO && tokens >= TC_MIN_TOKENS && gemm_tc_supported(m, tokens);
+}
+
 cudaError_t launch_matmul(const MatView& m, const float* x, float* y, int64_t tokens,
                           cudaStream_t stream, int path, int sm_count, int* err_flag,
-                          uint64_t* launches) {
+                          void* scratch, uint64_t* launches) {
   const bool x_aligned = ((uintptr_t)x & 15) == 0 && (m.cols % 4 == 0);
+  if (scratch && err_flag && x_aligned && matmul_wants_tc(m, tokens, path))
+    return launch_gemm_tc(m, x, y, tokens, scratch, stream, err_flag, launches);
+  if (path == PATH_TC) path = PATH_AUTO;
   if ((path == PATH_AUTO || path == PATH_MMA) && x_aligned && err_flag && gemv_mma_supported(m))
     return launch_gemv_mma(m, x, y, tokens, stream, sm_count, err_flag, launches);
   if (path != PATH_GENERIC && x_aligned && gemv_staged_supported(m))
@@ -382,6 +403,7 @@ int llr_exec_create(int device, llr_exec** out) {
     if (!std::strcmp(p, "generic")) e->path = PATH_GENERIC;
     else if (!std::strcmp(p, "staged")) e->path = PATH_STAGED;
     else if (!std::strcmp(p, "mma")) e->path = PATH_MMA;
+    else if (!std::strcmp(p, "tc")) e->path = PATH_TC;
   }
   *out = e;
   return LLR_OK;
@@ -401,6 +423,7 @@ int llr_exec_destroy(llr_exec* e) {
   if (e->pin_y) cudaFreeHost(e->pin_y);
   if (e->dev_x) cudaFree(e->dev_x);
   if (e->dev_y) cudaFree(e->dev_y);
+  if (e->dev_s) cudaFree(e->dev_s);
   if (e->err_flag) cudaFree(e->err_flag);
   cudaStreamDestroy(e->stream);
   cudaGetLastError();
@@ -425,7 +448,7 @@ int llr_exec_counters(const llr_exec* e, llr_counters* out) {
 }
 
 int llr_exec_set_path(llr_exec* e, int path) {
-  if (!e || path < PATH_AUTO || path > PATH_MMA) return LLR_ERR_INVALID;
+  if (!e || path < PATH_AUTO || path > PATH_TC) return LLR_ERR_INVALID;
   e->path = path;
   return LLR_OK;
 }
@@ -587,8 +610,11 @@ int llr_matmul_device(llr_exec* e, const llr_matrix* m, size_t tokens, const flo
     return fail(e, LLR_ERR_INVALID, "CUDA GEMM buffer lengths do not match shape");
   DeviceGuard guard(e->device);
   cudaStream_t s = stream ? (cudaStream_t)stream : e->stream;
-  cudaError_t ce = launch_matmul(view_of(m), x_dev, y_dev, (int64_t)tokens, s, e->path, e->sm_count,
-                                 e->err_flag, &e->ctr.launches);
+  void* scratch = nullptr;
+  cudaError_t ce = ensure_scratch(e, m, tokens, &scratch);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "kernel scratch");
+  ce = launch_matmul(view_of(m), x_dev, y_dev, (int64_t)tokens, s, e->path, e->sm_count, e->err_flag,
+                     scratch, &e->ctr.launches);
   if (ce != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
   return LLR_OK;
 }

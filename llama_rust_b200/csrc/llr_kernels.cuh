@@ -18,14 +18,17 @@ struct MatView {
   int64_t row_bytes;
 };
 
-enum GemvPath : int { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_STAGED = 2, PATH_MMA = 3 };
+enum GemvPath : int { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_STAGED = 2, PATH_MMA = 3, PATH_TC = 4 };
+constexpr int64_t TC_MIN_TOKENS = 64;  // from here on AUTO prefers the bf16 tcgen05 GEMM
 
 // y[t*rows + r] = sum_c W[r,c] * x[t*cols + c] for t < tokens.  Any shape the
 // entry points accept.  `launches` is incremented by the kernels launched.
 // `err_flag` is a device int that kernels with bounded waits set to non-zero when a wait ran out.
+// `scratch` (gemm_tc_scratch_bytes, or null) lets the tensor-core GEMM stage bf16 activations.
 cudaError_t launch_matmul(const MatView& m, const float* x, float* y, int64_t tokens,
                           cudaStream_t stream, int path, int sm_count, int* err_flag,
-                          uint64_t* launches);
+                          void* scratch, uint64_t* launches);
+bool matmul_wants_tc(const MatView& m, int64_t tokens, int path);
 
 // Always-available reference kernel: one warp per row, byte loads, any alignment.
 cudaError_t launch_gemv_generic(const MatView& m, const float* x, float* y, int64_t tokens,
@@ -62,6 +65,13 @@ void program_destroy(Program* p);
 cudaError_t program_run(Program* p, cudaStream_t stream, int* err_flag, uint64_t* launches);
 int program_phases(const Program* p);
 int program_entries(const Program* p);
+
+// dequant -> shared memory -> tcgen05/TMEM chunk GEMM (bf16 operands, f32 accumulate) for
+// Q4_K / Q8_0 / Q5_0 / Q5_1 with many activation rows; see llr_gemm_tc.cu.
+bool gemm_tc_supported(const MatView& m, int64_t tokens);
+size_t gemm_tc_scratch_bytes(const MatView& m, int64_t tokens);
+cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t tokens, void* scratch,
+                           cudaStream_t stream, int* err_flag, uint64_t* launches);
 
 // out[(r-row0)*cols + c] = dequantized W[r,c], bit-exact with the reference.
 cudaError_t launch_dequant(const MatView& m, int64_t row0, int64_t n_rows, float* out,

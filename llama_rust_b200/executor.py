@@ -19,7 +19,7 @@ F16, BF16, F32, Q5_0, Q5_1, Q4_0, Q8_0, Q4_K, Q6_K = 0, 1, 2, 6, 7, 12, 13, 17, 
 DTYPES = {"F16": F16, "BF16": BF16, "F32": F32, "Q5_0": Q5_0, "Q5_1": Q5_1, "Q4_0": Q4_0,
           "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K}
 OK, ERR_INVALID, ERR_UNALIGNED, ERR_DTYPE, ERR_OVERFLOW, ERR_FOREIGN, ERR_CUDA, ERR_OOM, ERR_CONFIG = range(9)
-PATH_AUTO, PATH_GENERIC, PATH_STAGED, PATH_MMA = 0, 1, 2, 3
+PATH_AUTO, PATH_GENERIC, PATH_STAGED, PATH_MMA, PATH_TC = 0, 1, 2, 3, 4
 
 _cdll = None
 

@@ -1,0 +1,64 @@
+"""Chunk GEMM on the tcgen05 tensor cores (bf16 operands, f32 accumulation in tensor memory)
+against the CPU f32 row kernels.  This is the path with the looser, separately stated bound:
+weights and activations are each rounded once to bfloat16 (relative 2^-9), so for K columns
+of random terms the error of one output is about 2^-9 * sqrt(2) * sqrt(sum (w_i x_i)^2).
+Asserted: relative L2 error of the whole result <= 4e-3 and every element within
+6 * 2^-8 * sqrt(sum (w_i x_i)^2) of the CPU value; the f32-faithful integer path is
+checked on the same inputs at its own tolerance."""
+import numpy as np
+import pytest
+
+from helpers import ALL, check_gemv, gemv_references, random_packed
+
+pytestmark = pytest.mark.gpu
+
+TC, MMA = 4, 3
+
+
+@pytest.fixture(scope="module")
+def ex():
+    from llama_rust_b200 import Executor
+    e = Executor(0)
+    yield e
+    e.close()
+
+
+def _bounds(kind, rows, cols, w, x, tokens, orc):
+    wf = orc.dequant_matrix(kind, rows, cols, w).astype(np.float64)
+    xt = np.asarray(x, np.float64).reshape(tokens, cols)
+    return np.sqrt((xt ** 2) @ (wf ** 2).T)  # sqrt(sum (w_i x_i)^2) per output
+
+
+@pytest.mark.parametrize("name,rows,cols", [("Q4_K", 300, 1024), ("Q8_0", 256, 1536), ("Q5_0", 130, 1024),
+                                            ("Q5_1", 128, 2048), ("Q4_K", 512, 4096)])
+@pytest.mark.parametrize("tokens", [64, 100, 256, 300])
+def test_tensor_core_gemm_matches_cpu_f32_reference(ex, orc, name, rows, cols, tokens):
+    kind = ALL[name]
+    rng = np.random.default_rng(0xC0 + kind + tokens)
+    w = random_packed(rng, kind, rows, cols)
+    x = rng.standard_normal(tokens * cols).astype(np.float32)
+    cpu = orc.gemm(kind, cols, tokens, w, x, rows, simd=True)
+    m = ex.upload(kind, rows, cols, w)
+    ex.set_path(TC)
+    y = np.full(rows * tokens, np.nan, np.float32)
+    ex.gemm_resident(m, tokens, x, y)
+    y = y.reshape(tokens, rows)
+    assert np.all(np.isfinite(y))
+    rel_l2 = np.linalg.norm(y - cpu) / np.linalg.norm(cpu)
+    assert rel_l2 <= 4e-3, f"{name} M={tokens}: relative L2 error {rel_l2:.3e}"
+    rms_terms = _bounds(kind, rows, cols, w, x, tokens, orc)
+    assert np.all(np.abs(y - cpu) <= 6 * 2.0 ** -8 * rms_terms + 1e-6), f"{name} M={tokens}: element outside the bf16 bound"
+    # automatic choice picks this path from 64 rows on; results identical
+    ex.set_path(0)
+    y2 = np.empty(rows * tokens, np.float32)
+    ex.gemm_resident(m, tokens, x, y2)
+    assert np.array_equal(y2.reshape(tokens, rows), y)
+    # the f32-faithful integer path on the same inputs
+    if name in ("Q4_K", "Q8_0"):
+        ex.set_path(MMA)
+        y3 = np.empty(rows * tokens, np.float32)
+        ex.gemm_resident(m, tokens, x, y3)
+        cpu2, exact, abs_sum = gemv_references(kind, rows, cols, w, x, tokens)
+        check_gemv(y3, cpu2, exact, abs_sum, cols, f"{name} integer path M={tokens}")
+    ex.set_path(0)
+    m.free()
