@@ -143,6 +143,32 @@ int llr_matmul(llr_exec* exec, uint8_t dtype, size_t rows, size_t cols, size_t t
  * [gpu.rs:301-334]. */
 int llr_matmul_device(llr_exec* exec, const llr_matrix* matrix, size_t tokens, const float* x_dev,
                       float* y_dev, void* stream);
+/* Chunk GEMM that allocates nothing.  No counterpart in the reference.
+ *
+ * For callers that must not touch the device allocator while they run: a serving
+ * loop whose KV pool and weights already fill the GPU, so a growing scratch
+ * buffer could fail or evict; code inside a region where the implicit device
+ * synchronization of cudaMalloc/cudaFree is not acceptable; hosts that hand this
+ * library a fixed memory budget up front.  Same tensor-core GEMM as the
+ * automatic path takes from 64 activation rows on (Q4_K, Q8_0, Q5_0, Q5_1;
+ * cols % 64 == 0; tokens >= 16; bf16 operands, f32 accumulation), but the bf16
+ * copy of the activations is staged in a fixed 32 MiB array built into the
+ * library (every GPU that loads the library holds it until the process exits)
+ * instead of an executor buffer.  x_dev / y_dev are device buffers of
+ * tokens*cols and tokens*rows floats, x_dev 16-byte aligned; the work is
+ * enqueued on `stream` (null = the executor's stream) without synchronizing.
+ * Limit: tokens * cols * 2 bytes <= 32 MiB, larger calls are rejected with
+ * LLR_ERR_INVALID and a message; nothing else is tried.
+ * The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.
+ * The call itself performs no cudaMalloc, cudaFree or other allocating call.
+ * All calls share the one array and it keeps the last call's contents: each
+ * call overwrites the part it uses before reading it, so nothing has to be
+ * cleared, but two calls that overlap on the GPU (different streams, or
+ * another executor) race on it; order them. */
+int llr_gemm_device_noalloc(llr_exec* exec, const llr_matrix* matrix, size_t tokens,
+                            const float* x_dev, float* y_dev, void* stream);
+
 /* Block the calling thread until the executor's own stream is idle; reports
  * LLR_ERR_CUDA if a kernel's bounded device-side wait gave up since the last check. */
 int llr_exec_synchronize(llr_exec* exec);

@@ -18,7 +18,7 @@ SYMBOLS = [
     "llr_matrix_upload_device", "llr_matrix_free", "llr_matrix_info", "llr_gemv_resident",
     "llr_gemm_resident", "llr_matmul", "llr_matmul_device", "llr_exec_synchronize",
     "llr_dequant_rows", "llr_matrix_synth", "llr_matrix_download", "llr_program_create",
-    "llr_program_run", "llr_program_free",
+    "llr_program_run", "llr_program_free", "llr_gemm_device_noalloc",
 ]
 
 
@@ -66,6 +66,7 @@ def load() -> C.CDLL:
     lib.llr_program_create.argtypes = [vp, C.POINTER(ProgramEntry), sz, C.POINTER(vp)]
     lib.llr_program_run.argtypes = [vp, vp, vp]
     lib.llr_program_free.argtypes = [vp]
+    lib.llr_gemm_device_noalloc.argtypes = [vp, vp, sz, vp, vp, vp]
     for s in SYMBOLS:
         if s != "llr_exec_last_error":
             getattr(lib, s).restype = C.c_int

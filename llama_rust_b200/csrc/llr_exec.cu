@@ -619,6 +619,28 @@ int llr_matmul_device(llr_exec* e, const llr_matrix* m, size_t tokens, const flo
   return LLR_OK;
 }
 
+int llr_gemm_device_noalloc(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x_dev,
+                            float* y_dev, void* stream) {
+  if (!e) return LLR_ERR_INVALID;
+  int rc = check_matrix(e, m);
+  if (rc) return rc;
+  if (tokens == 0 || !x_dev || !y_dev || ((uintptr_t)x_dev & 15) != 0)
+    return fail(e, LLR_ERR_INVALID, "CUDA GEMM buffer lengths do not match shape (x must be 16-byte aligned)");
+  const MatView v = view_of(m);
+  if (!gemm_tc_supported(v, (int64_t)tokens))
+    return fail(e, LLR_ERR_INVALID,
+                "the allocation-free GEMM takes Q4_K, Q8_0, Q5_0 or Q5_1 with cols % 64 == 0 and at least 16 activation rows");
+  size_t need = 0;
+  if (!mul_ok(tokens, (size_t)v.cols, &need) || !mul_ok(need, 2, &need) || need > gemm_tc_static_scratch_limit())
+    return fail(e, LLR_ERR_INVALID, "tokens * cols * 2 = " + std::to_string(need) + " bytes exceeds the built-in staging area of " +
+                                        std::to_string(gemm_tc_static_scratch_limit()) + " bytes; split the batch or use llr_matmul_device");
+  DeviceGuard guard(e->device);
+  cudaStream_t s = stream ? (cudaStream_t)stream : e->stream;
+  cudaError_t ce = launch_gemm_tc_static(e->device, v, x_dev, y_dev, (int64_t)tokens, s, e->err_flag, &e->ctr.launches);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
+  return LLR_OK;
+}
+
 int llr_exec_synchronize(llr_exec* e) {
   if (!e) return LLR_ERR_INVALID;
   DeviceGuard guard(e->device);

@@ -400,4 +400,28 @@ cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t t
   return e;
 }
 
+// ---- allocation-free variant ---------------------------------------------------------
+// The bf16 activation staging of the GEMM normally lives in a buffer the executor grows on
+// demand.  This variant uses a fixed array that is part of the library image instead, so the
+// call path contains no allocation at all.  Every GPU that loads the library holds these
+// bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[GEMM_STATIC_SCRATCH_BYTES];
+
+size_t gemm_tc_static_scratch_limit() { return GEMM_STATIC_SCRATCH_BYTES; }
+
+cudaError_t launch_gemm_tc_static(int device, const MatView& m, const float* x, float* y, int64_t tokens,
+                                  cudaStream_t stream, int* err_flag, uint64_t* launches) {
+  // In host code `g_static_scratch` is only a handle for the symbol, not a device address:
+  // the address is looked up once per device, with that device current.
+  static void* addr[64] = {nullptr};
+  if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+  if (!addr[device]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return e;
+    addr[device] = p;
+  }
+  return launch_gemm_tc(m, x, y, tokens, addr[device], stream, err_flag, launches);
+}
+
 }  // namespace llr

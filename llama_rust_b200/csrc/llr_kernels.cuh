@@ -73,6 +73,12 @@ size_t gemm_tc_scratch_bytes(const MatView& m, int64_t tokens);
 cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t tokens, void* scratch,
                            cudaStream_t stream, int* err_flag, uint64_t* launches);
 
+// Same kernels with the staging buffer in a file-scope __device__ array (no allocation).
+constexpr size_t GEMM_STATIC_SCRATCH_BYTES = 32u << 20;
+size_t gemm_tc_static_scratch_limit();
+cudaError_t launch_gemm_tc_static(int device, const MatView& m, const float* x, float* y, int64_t tokens,
+                                  cudaStream_t stream, int* err_flag, uint64_t* launches);
+
 // out[(r-row0)*cols + c] = dequantized W[r,c], bit-exact with the reference.
 cudaError_t launch_dequant(const MatView& m, int64_t row0, int64_t n_rows, float* out,
                            cudaStream_t stream, uint64_t* launches);
