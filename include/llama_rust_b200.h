@@ -199,6 +199,27 @@ int llr_program_create(llr_exec* exec, const llr_program_entry* entries, size_t 
 int llr_program_run(llr_exec* exec, llr_program* program, void* stream);
 int llr_program_free(llr_program* program);
 
+/* ---- routed-expert FFN layer ----------------------------------------------------
+ * One mixture-of-experts FFN layer as the reference runs it [langtax/src/decode.rs:
+ * softmax_routed_layer :9938 -> route_softmax_tokens :9969 (router product, softmax,
+ * top-k with ties to the lower id, weights optionally divided by max(sum, 2^-14))
+ * -> grouped_routed_ffn :10006 (experts in ascending id: gather rows, gate and up
+ * products, silu(g)*u, down product) -> scatter_expert_rows :10263 (out[t] += y*w)].
+ * Here the routing runs on the host exactly as there, everything else on the
+ * device.  router: n_expert x n_embd; gate[e], up[e]: n_ff x n_embd; down[e]:
+ * n_embd x n_ff (the ExpertParts of expertvm/src/store.rs:13-20, resident).
+ * x: tokens*n_embd floats, out: tokens*n_embd floats (host).  sel_ids / sel_w
+ * (tokens*n_used each, may be null) receive the routing decision. */
+typedef struct llr_moe_layer {
+  uint32_t n_expert, n_used, norm_w;
+  const llr_matrix* router;
+  const llr_matrix* const* gate;
+  const llr_matrix* const* up;
+  const llr_matrix* const* down;
+} llr_moe_layer;
+int llr_moe_ffn(llr_exec* exec, const llr_moe_layer* layer, size_t tokens, const float* x, size_t x_len,
+                float* out, size_t out_len, int32_t* sel_ids, float* sel_w);
+
 /* Dequantize rows [row0, row0+n_rows) of a resident matrix to f32 on the
  * device and copy them to out (n_rows*cols floats, host).  Bit-exact
  * counterpart of dequant_<t>_row [quant.rs:7511, 7533, 7734, 7884, 7918, 8046,

@@ -18,7 +18,7 @@ SYMBOLS = [
     "llr_matrix_upload_device", "llr_matrix_free", "llr_matrix_info", "llr_gemv_resident",
     "llr_gemm_resident", "llr_matmul", "llr_matmul_device", "llr_exec_synchronize",
     "llr_dequant_rows", "llr_matrix_synth", "llr_matrix_download", "llr_program_create",
-    "llr_program_run", "llr_program_free", "llr_gemm_device_noalloc",
+    "llr_program_run", "llr_program_free", "llr_gemm_device_noalloc", "llr_moe_ffn",
 ]
 
 
@@ -31,6 +31,12 @@ class Counters(C.Structure):
 class ProgramEntry(C.Structure):
     _fields_ = [("matrix", C.c_void_p), ("x_dev", C.c_void_p), ("y_dev", C.c_void_p),
                 ("tokens", C.c_uint32), ("phase", C.c_uint32)]
+
+
+class MoeLayer(C.Structure):
+    _fields_ = [("n_expert", C.c_uint32), ("n_used", C.c_uint32), ("norm_w", C.c_uint32),
+                ("router", C.c_void_p), ("gate", C.POINTER(C.c_void_p)), ("up", C.POINTER(C.c_void_p)),
+                ("down", C.POINTER(C.c_void_p))]
 
 
 def load() -> C.CDLL:
@@ -67,6 +73,7 @@ def load() -> C.CDLL:
     lib.llr_program_run.argtypes = [vp, vp, vp]
     lib.llr_program_free.argtypes = [vp]
     lib.llr_gemm_device_noalloc.argtypes = [vp, vp, sz, vp, vp, vp]
+    lib.llr_moe_ffn.argtypes = [vp, C.POINTER(MoeLayer), sz, vp, sz, vp, sz, vp, vp]
     for s in SYMBOLS:
         if s != "llr_exec_last_error":
             getattr(lib, s).restype = C.c_int

@@ -11,6 +11,8 @@
 // packed bytes only.
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>
 #include <list>
@@ -117,6 +119,7 @@ struct llr_exec {
   float* pin_y = nullptr; size_t pin_y_cap = 0;
   float* dev_x = nullptr; size_t dev_x_cap = 0;
   float* dev_y = nullptr; size_t dev_y_cap = 0;
+  float* dev_moe = nullptr; size_t dev_moe_cap = 0;  // workspace of the routed-expert layer
   uint8_t* dev_s = nullptr; size_t dev_s_cap = 0;  // kernel scratch (bf16 activations of the tensor-core GEMM)
   // residency
   std::list<CacheEntry> cache;  // front = least recently used
@@ -424,6 +427,7 @@ int llr_exec_destroy(llr_exec* e) {
   if (e->dev_x) cudaFree(e->dev_x);
   if (e->dev_y) cudaFree(e->dev_y);
   if (e->dev_s) cudaFree(e->dev_s);
+  if (e->dev_moe) cudaFree(e->dev_moe);
   if (e->err_flag) cudaFree(e->err_flag);
   cudaStreamDestroy(e->stream);
   cudaGetLastError();
@@ -652,6 +656,157 @@ int llr_exec_synchronize(llr_exec* e) {
     e->err_host = 0;
     return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations (copy engine did not deliver a weight tile)");
   }
+  return LLR_OK;
+}
+
+// ---------------------------------------------------------------- routed experts
+namespace {
+
+cudaError_t matmul_dev(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, float* y, int path) {
+  void* scratch = nullptr;
+  const int saved = e->path;
+  e->path = path;
+  cudaError_t ce = ensure_scratch(e, m, tokens, &scratch);
+  if (ce == cudaSuccess)
+    ce = launch_matmul(view_of(m), x, y, (int64_t)tokens, e->stream, path, e->sm_count, e->err_flag, scratch,
+                       &e->ctr.launches);
+  e->path = saved;
+  return ce;
+}
+
+}  // namespace
+
+int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float* x, size_t x_len, float* out,
+                size_t out_len, int32_t* sel_ids, float* sel_w) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!L || !L->router || !L->gate || !L->up || !L->down || L->n_expert == 0 || L->n_used == 0 ||
+      L->n_used > L->n_expert || L->n_expert > 4096)
+    return fail(e, LLR_ERR_INVALID, "expert_used_count");
+  int rc = check_matrix(e, L->router);
+  if (rc) return rc;
+  const size_t n_embd = (size_t)L->router->cols, n_exp = L->n_expert, n_used = L->n_used;
+  if ((size_t)L->router->rows != n_exp || n_embd % 4 != 0) return fail(e, LLR_ERR_INVALID, "ffn_gate_inp shape");
+  size_t n_ff = 0;
+  for (size_t i = 0; i < n_exp; ++i) {
+    if ((rc = check_matrix(e, L->gate[i])) || (rc = check_matrix(e, L->up[i])) || (rc = check_matrix(e, L->down[i]))) return rc;
+    if (i == 0) n_ff = (size_t)L->gate[0]->rows;
+    if ((size_t)L->gate[i]->rows != n_ff || (size_t)L->gate[i]->cols != n_embd || (size_t)L->up[i]->rows != n_ff ||
+        (size_t)L->up[i]->cols != n_embd || (size_t)L->down[i]->rows != n_embd || (size_t)L->down[i]->cols != n_ff)
+      return fail(e, LLR_ERR_INVALID, "expert matrix shapes do not match the layer");
+  }
+  size_t nx = 0;
+  if (tokens == 0 || !mul_ok(tokens, n_embd, &nx) || x_len != nx || out_len != nx || !x || !out || tokens > (1u << 24))
+    return fail(e, LLR_ERR_INVALID, "matrix dimensions must be positive and token-aligned");
+  DeviceGuard guard(e->device);
+  const size_t n_rows = tokens * n_used;
+  // device workspace, one block: x | logits | packed x | g | u | y | out | int tables | weights
+  const size_t f_x = nx, f_logits = tokens * n_exp, f_pack = n_rows * n_embd, f_g = n_rows * n_ff, f_y = n_rows * n_embd;
+  const size_t floats = f_x + f_logits + f_pack + 2 * f_g + f_y + nx + n_rows /*w*/ + 2 * n_rows /*int tables*/ + 64;
+  cudaError_t ce;
+  if ((ce = grow_device(&e->dev_moe, &e->dev_moe_cap, floats)) != cudaSuccess) return fail_cuda(e, ce, "expert workspace");
+  float* d_x = e->dev_moe;
+  float* d_logits = d_x + f_x;
+  float* d_pack = d_logits + ((f_logits + 3) & ~(size_t)3);
+  float* d_g = d_pack + f_pack;
+  float* d_u = d_g + f_g;
+  float* d_y = d_u + f_g;
+  float* d_out = d_y + f_y;
+  float* d_w = d_out + nx;
+  int* d_tok_of_row = (int*)(d_w + n_rows);
+  int* d_rows_of_tok = d_tok_of_row + n_rows;
+  if ((ce = cudaMemcpyAsync(d_x, x, nx * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess) return fail_cuda(e, ce, "activation upload");
+  // router product (decode.rs:9977), then routing on the host as the reference does
+  if ((ce = matmul_dev(e, L->router, tokens, d_x, d_logits, PATH_MMA)) != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
+  std::vector<float> logits(tokens * n_exp);
+  if ((ce = cudaMemcpyAsync(logits.data(), d_logits, logits.size() * 4, cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
+      (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)
+    return fail_cuda(e, ce, "router download");
+  std::vector<int32_t> ids(n_rows);
+  std::vector<float> wts(n_rows);
+  std::vector<std::vector<int>> buckets(n_exp);
+  std::vector<char> used(n_exp);
+  for (size_t t = 0; t < tokens; ++t) {
+    float* row = logits.data() + t * n_exp;
+    float mx = -INFINITY;  // softmax, decode.rs:12021
+    for (size_t i = 0; i < n_exp; ++i) mx = std::fmax(mx, row[i]);
+    float sum = 0.0f;
+    for (size_t i = 0; i < n_exp; ++i) { row[i] = std::exp(row[i] - mx); sum += row[i]; }
+    if (sum > 0.0f) for (size_t i = 0; i < n_exp; ++i) row[i] /= sum;
+    std::fill(used.begin(), used.end(), 0);
+    float wsum = 0.0f;
+    for (size_t j = 0; j < n_used; ++j) {  // top-k: descending value, ties to the lower index (:11363)
+      int best = -1;
+      for (size_t i = 0; i < n_exp; ++i)
+        if (!used[i] && (best < 0 || row[i] > row[best])) best = (int)i;
+      used[(size_t)best] = 1;
+      ids[t * n_used + j] = best;
+      wts[t * n_used + j] = row[best];
+      wsum += row[best];
+    }
+    if (L->norm_w) {  // fill_router_weights :11392, clamp 2^-14 :321
+      if (wsum < 1.0f / 16384.0f) wsum = 1.0f / 16384.0f;
+      for (size_t j = 0; j < n_used; ++j) wts[t * n_used + j] /= wsum;
+    }
+    for (size_t j = 0; j < n_used; ++j) buckets[(size_t)ids[t * n_used + j]].push_back((int)t);
+  }
+  // packed rows: experts ascending, tokens ascending inside an expert (grouped_routed_ffn :10006)
+  std::vector<int> tok_of_row(n_rows), rows_of_tok(n_rows, 0), fill(tokens, 0), first_row(n_exp + 1, 0);
+  std::vector<float> w_of_tok(n_rows, 0.0f);
+  size_t r = 0;
+  for (size_t ex = 0; ex < n_exp; ++ex) {
+    first_row[ex] = (int)r;
+    for (int t : buckets[ex]) {
+      tok_of_row[r] = t;
+      float w = 0.0f;
+      for (size_t j = 0; j < n_used; ++j)
+        if ((size_t)ids[(size_t)t * n_used + j] == ex) { w = wts[(size_t)t * n_used + j]; break; }
+      const int slot = fill[(size_t)t]++;  // ascending expert id = the reference's accumulation order
+      rows_of_tok[(size_t)t * n_used + slot] = (int)r;
+      w_of_tok[(size_t)t * n_used + slot] = w;
+      ++r;
+    }
+  }
+  first_row[n_exp] = (int)r;
+  if ((ce = cudaMemcpyAsync(d_tok_of_row, tok_of_row.data(), n_rows * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess ||
+      (ce = cudaMemcpyAsync(d_rows_of_tok, rows_of_tok.data(), n_rows * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess ||
+      (ce = cudaMemcpyAsync(d_w, w_of_tok.data(), n_rows * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess ||
+      (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)  // the host vectors go out of scope later, but keep it simple
+    return fail_cuda(e, ce, "routing upload");
+  if ((ce = launch_gather_rows(d_x, d_tok_of_row, d_pack, (int)n_rows, (int)n_embd, e->stream, &e->ctr.launches)) != cudaSuccess)
+    return fail_cuda(e, ce, "kernel launch");
+  for (size_t ex = 0; ex < n_exp; ++ex) {
+    const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
+    if (n == 0) continue;
+    if ((ce = matmul_dev(e, L->gate[ex], n, d_pack + r0 * n_embd, d_g + r0 * n_ff, e->path)) != cudaSuccess ||
+        (ce = matmul_dev(e, L->up[ex], n, d_pack + r0 * n_embd, d_u + r0 * n_ff, e->path)) != cudaSuccess)
+      return fail_cuda(e, ce, "kernel launch");
+  }
+  if ((ce = launch_silu_mul(d_g, d_u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess)
+    return fail_cuda(e, ce, "kernel launch");
+  for (size_t ex = 0; ex < n_exp; ++ex) {
+    const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
+    if (n == 0) continue;
+    if ((ce = matmul_dev(e, L->down[ex], n, d_g + r0 * n_ff, d_y + r0 * n_embd, e->path)) != cudaSuccess)
+      return fail_cuda(e, ce, "kernel launch");
+  }
+  if ((ce = launch_scatter_combine(d_y, d_rows_of_tok, d_w, d_out, (int)tokens, (int)n_used, (int)n_embd, e->stream,
+                                   &e->ctr.launches)) != cudaSuccess)
+    return fail_cuda(e, ce, "kernel launch");
+  if ((ce = grow_pinned(&e->pin_y, &e->pin_y_cap, nx)) != cudaSuccess) return fail_cuda(e, ce, "pinned result staging");
+  if ((ce = cudaMemcpyAsync(e->pin_y, d_out, nx * 4, cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
+      (ce = cudaMemcpyAsync(&e->err_host, e->err_flag, sizeof(int), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
+      (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)
+    return fail_cuda(e, ce, "result download");
+  if (e->err_host != 0) {
+    cudaMemsetAsync(e->err_flag, 0, sizeof(int), e->stream);
+    e->err_host = 0;
+    return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations");
+  }
+  std::memcpy(out, e->pin_y, nx * 4);
+  if (sel_ids) std::memcpy(sel_ids, ids.data(), n_rows * 4);
+  if (sel_w) std::memcpy(sel_w, wts.data(), n_rows * 4);
+  e->ctr.h2d_bytes += nx * 4 + 3 * n_rows * 4;
+  e->ctr.d2h_bytes += nx * 4 + logits.size() * 4;
   return LLR_OK;
 }
 

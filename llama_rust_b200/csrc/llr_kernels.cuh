@@ -79,6 +79,13 @@ size_t gemm_tc_static_scratch_limit();
 cudaError_t launch_gemm_tc_static(int device, const MatView& m, const float* x, float* y, int64_t tokens,
                                   cudaStream_t stream, int* err_flag, uint64_t* launches);
 
+// Routed-expert FFN glue (llr_moe.cu)
+cudaError_t launch_gather_rows(const float* x, const int* tok_of_row, float* packed, int n_rows, int n_embd,
+                               cudaStream_t s, uint64_t* launches);
+cudaError_t launch_silu_mul(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches);
+cudaError_t launch_scatter_combine(const float* y, const int* rows_of_tok, const float* w_of_tok, float* out,
+                                   int tokens, int n_used, int n_embd, cudaStream_t s, uint64_t* launches);
+
 // out[(r-row0)*cols + c] = dequantized W[r,c], bit-exact with the reference.
 cudaError_t launch_dequant(const MatView& m, int64_t row0, int64_t n_rows, float* out,
                            cudaStream_t stream, uint64_t* launches);

@@ -1,0 +1,74 @@
+// Routed-expert FFN layer: the small kernels around the expert matrix products.
+//
+// Follows langtax/src/decode.rs: grouped_one_expert :10062 gathers the rows routed to an
+// expert into a packed activation matrix, swiglu_expert_gemm :10148 runs gate and up
+// products, silu(g) * u (silu_inplace :11826), the down product, and
+// scatter_expert_rows :10263 adds y * w into the layer output.  The output of a token is
+// accumulated over its experts in ascending expert id, starting from zero, which fixes
+// the f32 rounding order exactly as the reference's `for e in 0..n_expert` loop does.
+#include "llr_kernels.cuh"
+
+namespace llr {
+namespace {
+
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ tok_of_row,
+                                   float* __restrict__ packed, int n_rows, int n_embd) {
+  const int row = blockIdx.x;
+  if (row >= n_rows) return;
+  const float4* src = (const float4*)(x + (int64_t)tok_of_row[row] * n_embd);
+  float4* dst = (float4*)(packed + (int64_t)row * n_embd);
+  for (int i = threadIdx.x; i < n_embd / 4; i += blockDim.x) dst[i] = src[i];
+}
+
+__global__ void silu_mul_kernel(float* __restrict__ g, const float* __restrict__ u, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = g[i];
+    g[i] = (v / (1.0f + expf(-v))) * u[i];
+  }
+}
+
+// rows_of_tok[t*n_used + j]: packed row of token t's j-th selection, selections ordered by
+// ascending expert id; w_of_tok the matching router weights.
+__global__ void scatter_combine_kernel(const float* __restrict__ y, const int* __restrict__ rows_of_tok,
+                                       const float* __restrict__ w_of_tok, float* __restrict__ out,
+                                       int tokens, int n_used, int n_embd) {
+  const int t = blockIdx.x;
+  if (t >= tokens) return;
+  for (int c = threadIdx.x; c < n_embd; c += blockDim.x) {
+    float acc = 0.0f;
+    for (int j = 0; j < n_used; ++j) {
+      const float term = __fmul_rn(y[(int64_t)rows_of_tok[t * n_used + j] * n_embd + c], w_of_tok[t * n_used + j]);
+      acc = __fadd_rn(acc, term);
+    }
+    out[(int64_t)t * n_embd + c] = acc;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_gather_rows(const float* x, const int* tok_of_row, float* packed, int n_rows, int n_embd,
+                               cudaStream_t s, uint64_t* launches) {
+  if (n_rows <= 0) return cudaSuccess;
+  gather_rows_kernel<<<n_rows, 256, 0, s>>>(x, tok_of_row, packed, n_rows, n_embd);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_silu_mul(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches) {
+  if (n <= 0) return cudaSuccess;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  silu_mul_kernel<<<(unsigned)blocks, 256, 0, s>>>(g, u, n);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_combine(const float* y, const int* rows_of_tok, const float* w_of_tok, float* out,
+                                   int tokens, int n_used, int n_embd, cudaStream_t s, uint64_t* launches) {
+  if (tokens <= 0) return cudaSuccess;
+  scatter_combine_kernel<<<tokens, 256, 0, s>>>(y, rows_of_tok, w_of_tok, out, tokens, n_used, n_embd);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+}  // namespace llr

@@ -108,6 +108,15 @@ float orc_silu(float v);                                                        
 int64_t orc_argmax(const float* v, int64_t n);                                  /* sample.rs:293 */
 void  orc_topk(const float* p, int64_t n, int64_t k, int32_t* ids);            /* :11363 */
 
+/* Routed-expert FFN layer (decode.rs:9938-10290): router GEMM, softmax, top-k (ties to the
+ * lower id), optional weight normalisation with the 2^-14 clamp, then experts in ascending
+ * order: gather rows, gate & up GEMM, silu(g)*u, down GEMM, out[t] += y * w. */
+int orc_moe_ffn(int n_expert, int n_used, int norm_w, int router_kind, const uint8_t* router,
+                int64_t router_len, int expert_kind, const uint8_t* const* gate,
+                const uint8_t* const* up, const uint8_t* const* down, int64_t n_embd, int64_t n_ff,
+                int64_t tokens, const float* x, float* out, int32_t* sel_ids, float* sel_w,
+                int threads);
+
 #ifdef __cplusplus
 }
 #endif

@@ -93,6 +93,8 @@ def _load() -> C.CDLL:
     lib.orc_argmax.argtypes = [f32p, i64]
     lib.orc_topk.restype = None
     lib.orc_topk.argtypes = [f32p, i64, i64, C.c_void_p]
+    lib.orc_moe_ffn.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, u8p, i64, C.c_int, C.c_void_p, C.c_void_p,
+                                C.c_void_p, i64, i64, i64, f32p, f32p, C.c_void_p, f32p, C.c_int]
     return lib
 
 
@@ -280,6 +282,23 @@ def demo_q8_0(n_cols: int, n_rows: int):
 def y_checksum(y) -> int:
     v = _f32(y)
     return lib.orc_y_checksum(_p(v), v.size)
+
+
+def moe_ffn(n_used: int, norm_w: bool, router_kind: int, router, expert_kind: int, gate, up, down,
+            n_embd: int, n_ff: int, x):
+    """Routed-expert FFN layer; returns (out[tokens, n_embd], sel_ids[tokens, n_used], sel_w)."""
+    n_expert = len(gate)
+    rt = _u8(router)
+    xs = _f32(x).reshape(-1, n_embd)
+    tokens = xs.shape[0]
+    keep = [[_u8(a) for a in lst] for lst in (gate, up, down)]
+    ptrs = [(C.c_void_p * n_expert)(*[a.ctypes.data for a in lst]) for lst in keep]
+    out = np.zeros((tokens, n_embd), np.float32)
+    ids = np.zeros((tokens, n_used), np.int32)
+    w = np.zeros((tokens, n_used), np.float32)
+    _check(lib.orc_moe_ffn(n_expert, n_used, int(norm_w), router_kind, _p(rt), rt.size, expert_kind,
+                           ptrs[0], ptrs[1], ptrs[2], n_embd, n_ff, tokens, _p(xs), _p(out), _p(ids), _p(w), 0))
+    return out, ids, w
 
 
 def ref_q8_gemv_binary() -> str | None:

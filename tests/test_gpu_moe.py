@@ -1,0 +1,61 @@
+"""Routed-expert FFN layer (llr_moe_ffn) against the oracle's restatement of the reference's
+MoE walk (langtax/src/decode.rs:9938-10290): identical routing decisions, router weights to
+f32 rounding, layer output within the matmul tolerances (integer path: relative 1e-5 of the
+output scale per product, three chained products; tensor-core path: the bf16 bound)."""
+import numpy as np
+import pytest
+
+from helpers import F32, Q4_K, random_packed
+
+pytestmark = pytest.mark.gpu
+
+
+def _layer(ex, rng, n_expert, n_embd, n_ff):
+    router_w = (rng.standard_normal((n_expert, n_embd)) * 0.05).astype(np.float32)
+    packs = {k: [random_packed(rng, Q4_K, r, c) for _ in range(n_expert)]
+             for k, (r, c) in {"gate": (n_ff, n_embd), "up": (n_ff, n_embd), "down": (n_embd, n_ff)}.items()}
+    mats = {k: [ex.upload(Q4_K, (n_ff if k != "down" else n_embd), (n_embd if k != "down" else n_ff), w) for w in v]
+            for k, v in packs.items()}
+    router = ex.upload(F32, n_expert, n_embd, router_w.view(np.uint8))
+    return router_w, packs, mats, router
+
+
+@pytest.mark.parametrize("tokens,path,tol", [(1, 0, 3e-5), (24, 0, 3e-5), (300, 3, 3e-5), (300, 0, 2e-2)])
+def test_moe_layer_matches_reference_walk(orc, tokens, path, tol):
+    from llama_rust_b200 import Executor
+    ex = Executor(0)
+    rng = np.random.default_rng(500 + tokens)
+    n_expert, n_used, n_embd, n_ff = 8, 2, 512, 1024
+    router_w, packs, mats, router = _layer(ex, rng, n_expert, n_embd, n_ff)
+    x = rng.standard_normal((tokens, n_embd)).astype(np.float32)
+    ref_out, ref_ids, ref_w = orc.moe_ffn(n_used, True, F32, router_w.view(np.uint8), Q4_K, packs["gate"], packs["up"],
+                                          packs["down"], n_embd, n_ff, x)
+    ex.set_path(path)
+    out, ids, w = ex.moe_ffn(router, mats["gate"], mats["up"], mats["down"], n_used, True, x)
+    assert np.array_equal(ids, ref_ids), "routing decisions differ"
+    assert np.allclose(w, ref_w, rtol=2e-6, atol=1e-7)
+    assert np.all(np.isfinite(out))
+    scale = max(1.0, float(np.abs(ref_out).max()))
+    assert np.abs(out - ref_out).max() <= tol * scale, f"max err {np.abs(out - ref_out).max():.3e} vs scale {scale:.3g}"
+    # every token's output is the weighted sum of exactly its two experts: zeroing x of one
+    # token must zero only that token's row
+    x2 = x.copy()
+    x2[0] = 0.0
+    out2, _, _ = ex.moe_ffn(router, mats["gate"], mats["up"], mats["down"], n_used, True, x2)
+    assert np.all(out2[0] == 0.0)
+    ex.close()
+
+
+def test_moe_layer_validates_shapes():
+    from llama_rust_b200 import Executor, NativeCudaError
+    ex = Executor(0)
+    rng = np.random.default_rng(9)
+    router_w, packs, mats, router = _layer(ex, rng, 4, 256, 512)
+    x = np.zeros((3, 256), np.float32)
+    with pytest.raises(NativeCudaError):
+        ex.moe_ffn(router, mats["gate"], mats["up"], mats["down"], 5, True, x)  # n_used > n_expert
+    with pytest.raises(NativeCudaError):
+        ex.moe_ffn(router, mats["down"], mats["up"], mats["down"], 2, True, x)  # wrong shapes
+    out, ids, w = ex.moe_ffn(router, mats["gate"], mats["up"], mats["down"], 2, False, x)
+    assert np.all(out == 0.0) and ids.shape == (3, 2)
+    ex.close()
