@@ -1,0 +1,129 @@
+"""Sharding layer for one multi-GPU box: one process per GPU over torch.distributed.
+
+The reference has no multi-device execution (its only notions are simulated:
+`home_gpu = expert % n_gpus`, expertvm/src/place.rs:71-75); this layer is new.
+
+* Dense products shard by OUTPUT ROWS: rows are independent and a row range of a packed
+  matrix is a contiguous byte range (langtax/src/decode.rs:10876-10879, `quant_mat_rows`
+  :9680-9713), so rank g holds rows [g*R/G, (g+1)*R/G) of every matrix, activations are
+  replicated, and the exchange is an all-gather of M x R/G result slices.
+* Routed experts stripe as `e % G`; token rows travel to the expert's rank and back with
+  all-to-all, and a token's output is summed over its experts in ascending expert id
+  (the reference's accumulation order, decode.rs:10006-10290), so results do not depend
+  on G.
+
+The compute is a callable, so the same code runs on NCCL with the CUDA executor and on
+gloo with any CPU stand-in (that is how the host logic is tested without GPUs).
+"""
+from __future__ import annotations
+
+from typing import Callable, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+def row_range(rows: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous, balanced row range of `rank`; exact for every BASELINE shape (rows % 8 == 0)."""
+    return rows * rank // world, rows * (rank + 1) // world
+
+
+def shard_packed(packed, rows: int, world: int, rank: int):
+    """The byte range of a packed matrix that holds this rank's rows."""
+    rb = len(packed) // rows
+    r0, r1 = row_range(rows, world, rank)
+    return packed[r0 * rb:r1 * rb], r1 - r0
+
+
+def home_rank(expert: int, world: int) -> int:
+    """expertvm/src/place.rs:71-75"""
+    return expert % world
+
+
+class RowShardedMatmul:
+    """y[t, :] = W x[t] with W sharded by rows: local product + all-gather of the slices."""
+
+    def __init__(self, rows: int, local_matmul: Callable[[torch.Tensor], torch.Tensor], group=None):
+        self.rows, self.local, self.group = rows, local_matmul, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if rows % self.world:
+            raise ValueError(f"{rows} rows do not split evenly over {self.world} ranks")
+        self.local_rows = rows // self.world
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        y_local = self.local(x)  # [tokens, rows / G]
+        tokens = y_local.shape[0]
+        gathered = torch.empty(self.world * tokens, self.local_rows, dtype=y_local.dtype, device=y_local.device)
+        dist.all_gather_into_tensor(gathered, y_local.contiguous(), group=self.group)
+        return gathered.view(self.world, tokens, self.local_rows).permute(1, 0, 2).reshape(tokens, self.rows)
+
+
+class ExpertParallelFFN:
+    """Routed-expert FFN with experts striped over ranks.
+
+    `route(x) -> (ids[T, k], w[T, k])` is replicated (every rank routes every token);
+    `expert_ffn(e, rows[n, d]) -> rows[n, d]` runs one local expert on a packed batch.
+    Tokens are replicated too (the usual data layout after attention), so the dispatch
+    all-to-all only moves the rows a rank does NOT own... every rank could gather its own
+    rows locally; the exchange that cannot be avoided is the combine: each rank returns the
+    expert outputs of its experts for all tokens, and every rank sums a token's k rows in
+    ascending expert id.
+    """
+
+    def __init__(self, n_expert: int, route, expert_ffn, group=None):
+        self.n_expert, self.route, self.expert_ffn, self.group = n_expert, route, expert_ffn, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        ids, w = self.route(x)
+        tokens, k = ids.shape
+        d = x.shape[1]
+        # rows in (expert ascending, token ascending) order, as grouped_routed_ffn builds them
+        flat_e = ids.reshape(-1)
+        flat_t = torch.arange(tokens, device=x.device).repeat_interleave(k)
+        order = torch.argsort(flat_e * tokens + flat_t, stable=True)
+        e_sorted, t_sorted = flat_e[order], flat_t[order]
+        counts = torch.bincount(e_sorted, minlength=self.n_expert)
+        starts = torch.cumsum(counts, 0) - counts
+        y_rows = torch.zeros(tokens * k, d, dtype=x.dtype, device=x.device)
+        # per-rank row counts are known everywhere (routing is replicated): all-to-all sizes
+        per_rank = [int(sum(int(counts[e]) for e in range(self.n_expert) if home_rank(e, self.world) == r))
+                    for r in range(self.world)]
+        mine = []
+        for e in range(self.n_expert):
+            if home_rank(e, self.world) != self.rank or int(counts[e]) == 0:
+                continue
+            s, n = int(starts[e]), int(counts[e])
+            out = self.expert_ffn(e, x[t_sorted[s:s + n]])
+            mine.append((s, out))
+        send = torch.cat([o for _, o in mine]) if mine else torch.zeros(0, d, dtype=x.dtype, device=x.device)
+        # every rank needs every row: all-gather of ragged blocks via all_to_all_single with
+        # identical payload to each peer (the combine step of expert parallelism)
+        recv = torch.empty(sum(per_rank), d, dtype=x.dtype, device=x.device)
+        dist.all_to_all_single(recv, send.repeat(self.world, 1), output_split_sizes=per_rank,
+                               input_split_sizes=[send.shape[0]] * self.world, group=self.group)
+        # place the received blocks: rank r's block lists its experts ascending
+        off = 0
+        for r in range(self.world):
+            for e in range(self.n_expert):
+                if home_rank(e, self.world) != r or int(counts[e]) == 0:
+                    continue
+                s, n = int(starts[e]), int(counts[e])
+                y_rows[s:s + n] = recv[off:off + n]
+                off += n
+        # combine: ascending expert id per token, starting from zero
+        out = torch.zeros_like(x)
+        w_sorted = w.reshape(-1)[order]
+        # slot j of token t = its j-th expert in ascending id
+        slot = torch.zeros(tokens, dtype=torch.long, device=x.device)
+        rows_of_tok = torch.zeros(tokens, k, dtype=torch.long, device=x.device)
+        for i in range(tokens * k):  # routing tables are tiny (T*k entries)
+            t = int(t_sorted[i])
+            rows_of_tok[t, int(slot[t])] = i
+            slot[t] += 1
+        for j in range(k):
+            idx = rows_of_tok[:, j]
+            out = out + y_rows[idx] * w_sorted[idx].unsqueeze(1)
+        return out

@@ -1,0 +1,105 @@
+"""Host logic of the sharding layer on CPU: two gloo ranks, the oracle standing in for the
+device executor.  Row-sharded products must reproduce the unsharded result bit for bit
+(rows are independent), and the expert-parallel FFN must match the single-process MoE walk."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from helpers import F32, Q4_K, Q6_K, random_packed
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, fn, args, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ret[rank] = fn(rank, world, *args)
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world, fn, *args):
+    ctx = mp.get_context("spawn")
+    mgr = ctx.Manager()
+    ret = mgr.dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fn, args, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    return [ret[r] for r in range(world)]
+
+
+def _dense_rank(rank, world, kind, rows, cols, w, x):
+    from llama_rust_b200 import sharding
+    from oracle import pyoracle as orc
+    shard, local_rows = sharding.shard_packed(w, rows, world, rank)
+    tokens = x.shape[0]
+    mm = sharding.RowShardedMatmul(rows, lambda xt: torch.from_numpy(
+        orc.gemm(kind, cols, tokens, shard, xt.numpy(), local_rows, simd=True, threads=1)))
+    return mm(torch.from_numpy(x)).numpy()
+
+
+@pytest.mark.parametrize("kind,rows,cols", [(Q4_K, 64, 512), (Q6_K, 48, 2048)])
+def test_row_sharded_product_is_bit_identical_to_unsharded(orc, kind, rows, cols):
+    rng = np.random.default_rng(77)
+    w = random_packed(rng, kind, rows, cols)
+    x = rng.standard_normal((3, cols)).astype(np.float32)
+    full = orc.gemm(kind, cols, 3, w, x, rows, simd=True, threads=1)
+    for y in _run(2, _dense_rank, kind, rows, cols, w, x):
+        assert np.array_equal(y.view(np.uint32), full.view(np.uint32))
+
+
+def test_row_ranges_cover_baseline_shapes():
+    from llama_rust_b200 import sharding
+    for rows in (4096, 1024, 14336, 128256):
+        for world in (1, 2, 4, 8):
+            spans = [sharding.row_range(rows, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == rows
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert len({b - a for a, b in spans}) == 1
+    assert [sharding.home_rank(e, 4) for e in range(8)] == [0, 1, 2, 3, 0, 1, 2, 3]  # place.rs:71-75
+
+
+def _moe_rank(rank, world, n_used, router_w, gate, up, down, n_embd, n_ff, x, ids, wts):
+    from llama_rust_b200 import sharding
+    from oracle import pyoracle as orc
+
+    def expert(e, rows):
+        n = rows.shape[0]
+        r = rows.numpy()
+        g = orc.gemm(Q4_K, n_embd, n, gate[e], r, n_ff, simd=True, threads=1)
+        u = orc.gemm(Q4_K, n_embd, n, up[e], r, n_ff, simd=True, threads=1)
+        a = np.array([orc.lib.orc_silu(float(v)) for v in g.ravel()], np.float32).reshape(g.shape) * u
+        return torch.from_numpy(orc.gemm(Q4_K, n_ff, n, down[e], a, n_embd, simd=True, threads=1))
+
+    ffn = sharding.ExpertParallelFFN(len(gate), lambda xt: (torch.from_numpy(ids).long(), torch.from_numpy(wts)), expert)
+    return ffn(torch.from_numpy(x)).numpy()
+
+
+def test_expert_parallel_ffn_matches_single_process_walk(orc):
+    rng = np.random.default_rng(5)
+    n_expert, n_used, n_embd, n_ff, tokens = 4, 2, 256, 256, 7
+    router_w = (rng.standard_normal((n_expert, n_embd)) * 0.05).astype(np.float32)
+    gate = [random_packed(rng, Q4_K, n_ff, n_embd) for _ in range(n_expert)]
+    up = [random_packed(rng, Q4_K, n_ff, n_embd) for _ in range(n_expert)]
+    down = [random_packed(rng, Q4_K, n_embd, n_ff) for _ in range(n_expert)]
+    x = rng.standard_normal((tokens, n_embd)).astype(np.float32)
+    ref, ids, wts = orc.moe_ffn(n_used, True, F32, router_w.view(np.uint8), Q4_K, gate, up, down, n_embd, n_ff, x)
+    for out in _run(2, _moe_rank, n_used, router_w, gate, up, down, n_embd, n_ff, x, ids, wts):
+        # same products, same ascending-expert accumulation: identical bits for any number of ranks
+        assert np.array_equal(out.view(np.uint32), ref.view(np.uint32))
