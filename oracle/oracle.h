@@ -117,6 +117,23 @@ int orc_moe_ffn(int n_expert, int n_used, int norm_w, int router_kind, const uin
                 int64_t tokens, const float* x, float* out, int32_t* sel_ids, float* sel_w,
                 int threads);
 
+/* Dense Llama walk (decode.rs:2710-3097, plain llama architecture, norm weights all ones):
+ * prefill of the whole prompt as one batch (LogitsKind::Last), then greedy decode.  Matrix
+ * products go through `cb` when given (tensor_id = layer*7 + {0 q,1 k,2 v,3 o,4 gate,5 up,
+ * 6 down}, n_layer*7 = output), else through the oracle's CPU kernels on tensors[]/kinds[].
+ * Embedding rows come from `embd_cb` when given, else from dequant_<t>_row of token_embd.
+ * out_margin[i] = top-1 minus top-2 logit at generated token i. */
+typedef int (*orc_matmul_cb)(void* user, int tensor_id, int64_t n_tokens, const float* x, float* y);
+typedef struct orc_llama_cfg {
+  int32_t n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab, n_ctx;
+  float rms_eps, rope_base;
+} orc_llama_cfg;
+int orc_llama_generate(const orc_llama_cfg* c, orc_matmul_cb cb, void* user, const uint8_t* const* tensors,
+                       const int* kinds, int embd_kind, const uint8_t* token_embd,
+                       int (*embd_cb)(void* user, int32_t token, float* row), const int32_t* prompt,
+                       int n_prompt, int n_gen, int32_t* out_ids, float* out_margin, float* last_logits,
+                       int threads);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,51 @@
+"""BASELINE config 3: greedy-token identity of the dense Llama walk, CUDA executor vs CPU
+reference kernels.  A small model is walked by both sides live; the full Llama-3-8B-shaped
+model (32 layers, 4.9 GB of packed weights, 512-token prompt, 128 greedy tokens) is compared
+with the ids the CPU oracle produced when tests/golden/make_config3.py was run."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import llama_walk as lw
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "config3_golden.json")
+
+
+def test_small_model_greedy_identity_and_logits(orc):
+    from llama_rust_b200 import Executor, synth
+    cfg = dict(n_layer=3, n_embd=512, n_head=8, n_head_kv=2, head_dim=64, n_ff=2048, n_vocab=3000)
+    n_prompt, n_gen = 24, 24
+    tl = lw.tensor_list(cfg)
+    weights = [synth.packed_matrix(dt, rows, cols, synth.tensor_seed(33, name)) for name, dt, rows, cols in tl]
+    embd = synth.packed_matrix(lw.Q4_K, cfg["n_vocab"], cfg["n_embd"], synth.tensor_seed(33, "token_embd.weight"))
+    prompt = lw.prompt_ids(n_prompt, cfg["n_vocab"], 99)
+    ids_cpu, margin, logits_cpu = lw.run_cpu(cfg, 64, weights, embd, prompt, n_gen, want_logits=True)
+    ex = Executor(0)
+    ex.set_path(3)  # f32-faithful products for every batch size (the identity run)
+    mats = [ex.upload(dt, rows, cols, w) for (name, dt, rows, cols), w in zip(tl, weights)]
+    embd_mat = ex.upload(lw.Q4_K, cfg["n_vocab"], cfg["n_embd"], embd)
+    ids_gpu, margin_gpu, logits_gpu = lw.run_gpu(cfg, 64, ex, mats, embd_mat, prompt, n_gen, want_logits=True)
+    assert np.array_equal(ids_gpu, ids_cpu), (ids_gpu, ids_cpu, margin)
+    scale = max(1.0, float(np.abs(logits_cpu).max()))
+    assert np.abs(logits_gpu - logits_cpu).max() <= 1e-3 * scale  # the reference's model-level tolerance
+    ex.close()
+
+
+def test_llama3_8b_shape_greedy_identity_against_cpu_golden():
+    if not os.path.exists(GOLDEN):
+        pytest.skip("tests/golden/config3_golden.json has not been generated")
+    from llama_rust_b200 import Executor, synth
+    g = json.load(open(GOLDEN))
+    cfg = lw.LLAMA3_8B
+    tl = lw.tensor_list(cfg)
+    ex = Executor(0)
+    ex.set_path(3)
+    mats = [ex.synth(dt, rows, cols, synth.tensor_seed(g["base_seed"], name)) for name, dt, rows, cols in tl]
+    embd_mat = ex.synth(lw.Q4_K, cfg["n_vocab"], cfg["n_embd"], synth.tensor_seed(g["base_seed"], "token_embd.weight"))
+    prompt = lw.prompt_ids(g["n_prompt"], cfg["n_vocab"], g["prompt_seed"])
+    ids, margin, _ = lw.run_gpu(cfg, g["n_prompt"] + g["n_gen"], ex, mats, embd_mat, prompt, g["n_gen"])
+    assert ids.tolist() == g["ids"], f"first difference at {int(np.argmax(ids != np.array(g['ids'])))}"
+    ex.close()
