@@ -12,7 +12,7 @@
 //
 // One CTA computes a 128-row x BN-token tile of y over the whole K.  Per 64-column
 // step: eight warps dequantize 128 x 64 weights (two threads per row, packed bytes
-// straight from global memory, next step prefetched in registers) into a K-major
+// straight from global memory, the next four steps prefetched in registers) into a K-major
 // 128-byte-swizzled bf16 tile; one thread TMA-loads the matching BN x 64 bf16
 // activation tile (2-D tensor map, 128-byte swizzle, out-of-range tokens read as
 // zero); one thread issues four tcgen05.mma (M=128, N=BN, K=16) whose commit
@@ -216,24 +216,32 @@ gemm_tc_kernel(const uint8_t* __restrict__ W, int64_t row_bytes, int rows, int c
     int grow = row0 + r;
     if (grow >= rows) grow = rows - 1;
     const uint8_t* wrow = W + (int64_t)grow * row_bytes;
-    Raw<DT> cur, nxt;
-    load_raw<DT>(wrow, 0, h, cur);
-    for (int ks = 0; ks < nk; ++ks) {
-      const int s = ks % NSTAGE;
-      if (ks + 1 < nk) load_raw<DT>(wrow, ks + 1, h, nxt);
-      uint32_t out[16];
-      dequant32<DT>(cur, ks, h, out);
-      if (ok && !bar_wait(&empty[s], (uint32_t)(((ks / NSTAGE) & 1) ^ 1))) { ok = false; atomicExch(err, 3); }
-      uint8_t* arow = sA + s * L::A_STAGE + (r >> 3) * 1024 + (r & 7) * 128;
+    // packed bytes of the next PF steps are in flight in registers while this one is decoded
+    constexpr int PF = 4;
+    Raw<DT> buf[PF];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int chunk = (4 * h + i) ^ (r & 7);  // 128-byte swizzle: 16-byte chunk index xor row-in-group
-        *(uint4*)(arow + chunk * 16) = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+    for (int i = 0; i < PF; ++i)
+      if (i < nk) load_raw<DT>(wrow, i, h, buf[i]);
+    for (int ks0 = 0; ks0 < nk; ks0 += PF) {
+#pragma unroll
+      for (int i = 0; i < PF; ++i) {
+        const int ks = ks0 + i;
+        if (ks >= nk) break;
+        const int s = ks % NSTAGE;
+        uint32_t out[16];
+        dequant32<DT>(buf[i], ks, h, out);
+        if (ks + PF < nk) load_raw<DT>(wrow, ks + PF, h, buf[i]);
+        if (ok && !bar_wait(&empty[s], (uint32_t)(((ks / NSTAGE) & 1) ^ 1))) { ok = false; atomicExch(err, 3); }
+        uint8_t* arow = sA + s * L::A_STAGE + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          const int chunk = (4 * h + c4) ^ (r & 7);  // 128-byte swizzle: 16-byte chunk index xor row-in-group
+          *(uint4*)(arow + chunk * 16) = make_uint4(out[4 * c4], out[4 * c4 + 1], out[4 * c4 + 2], out[4 * c4 + 3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
+        __syncwarp();
+        if (lane == 0) bar_arrive(&full_a[s]);
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
-      __syncwarp();
-      if (lane == 0) bar_arrive(&full_a[s]);
-      cur = nxt;
     }
     // --------------------------------------------------------------- epilogue
     if (ok && !bar_wait(acc_full, 0)) { ok = false; atomicExch(err, 3); }

@@ -98,3 +98,45 @@ def run_gpu(cfg, n_ctx, ex, mats, embd_mat, prompt, n_gen, want_logits=False):
         return _generate(c, cb, None, None, Q4_K, None, ecb, prompt, n_gen, 1, want_logits)
     except RuntimeError as e:
         raise RuntimeError(f"{e}: {errors[:1]}")
+
+
+def center_q4k(packed):
+    """Rewrites, in place, the scale fields of Q4_K super-blocks so that the decoded weights are
+    zero-mean: sc = old_sc % 5, m = 15*sc, dmin = d/2, hence w = d*sc*(q - 7.5).  The blocks stay
+    valid Q4_K (quants and d untouched).  With the plain recipe (independent uniform scale and
+    min fields) every Q4_K matrix has a large common offset and a random-init model emits one
+    token with a margin of hundreds, which makes greedy identity vacuous; this recipe gives a
+    model whose logits actually compete.  Field layout as get_scale_min_k4, quant.rs:7866."""
+    b = packed.reshape(-1, 144)
+    q = b[:, 4:16]
+    sc = np.empty((b.shape[0], 8), np.uint8)
+    sc[:, :4] = q[:, 0:4] & 63
+    sc[:, 4:] = (q[:, 8:12] & 0xF) | ((q[:, 0:4] >> 6) << 4)
+    sc %= 5
+    m = sc * 15
+    q[:, 0:4] = sc[:, :4]
+    q[:, 4:8] = m[:, :4] | ((m[:, 4:] >> 4) << 6)
+    q[:, 8:12] = sc[:, 4:] | ((m[:, 4:] & 0xF) << 4)
+    d = b[:, 0:2].copy().view(np.float16).astype(np.float32)
+    b[:, 2:4] = (d * 0.5).astype(np.float16).view(np.uint8)
+    return packed
+
+
+def centered_weights(cfg, base_seed):
+    """Packed weights of tensor_list(cfg) plus token_embd, Q4_K tensors centred."""
+    from llama_rust_b200 import synth
+    out = []
+    for name, dt, rows, cols in tensor_list(cfg):
+        w = synth.packed_matrix(dt, rows, cols, synth.tensor_seed(base_seed, name))
+        out.append(center_q4k(w) if dt == Q4_K else w)
+    embd = center_q4k(synth.packed_matrix(Q4_K, cfg["n_vocab"], cfg["n_embd"], synth.tensor_seed(base_seed, "token_embd.weight")))
+    return out, embd
+
+
+def compared_prefix(ids_ref, margin_ref, logit_scale, tol=1e-3):
+    """Number of leading generated tokens on which greedy identity is decidable: up to and
+    excluding the first step whose reference top-2 margin is below tol*logit_scale (the
+    reference's model-level logit tolerance) - past a genuine near-tie either argmax is a
+    correct answer and the two runs may legitimately part."""
+    near = np.nonzero(np.asarray(margin_ref) < tol * logit_scale)[0]
+    return int(near[0]) if near.size else len(ids_ref)
