@@ -4,24 +4,44 @@
 //
 // What it computes: gemm_<t>_f32 (langtax/src/quant.rs:6282, 6366, 6380, 6478 ->
 // gemm_f32_x :6760), y[t*rows + r] = sum_c W[r,c] x[t*cols + c], for Q4_K, Q8_0,
-// Q5_0 and Q5_1.  Operands are rounded to bfloat16 (weights after exact f32
+// Q5_0 and Q5_1.  Operands are rounded to bfloat16 (weights after f32
 // dequantization, activations once up front), products are exact, accumulation is
 // f32 in tensor memory: this is the tensor-core path with the looser, separately
 // stated tolerance (tests/test_gpu_gemm.py); the f32-faithful path for any number
 // of rows stays the integer kernel of llr_gemv_stream.cu.
 //
-// One CTA computes a 128-row x BN-token tile of y over the whole K.  Per 64-column
-// step: eight warps dequantize 128 x 64 weights (two threads per row, packed bytes
-// straight from global memory, the next four steps prefetched in registers) into a K-major
-// 128-byte-swizzled bf16 tile; one thread TMA-loads the matching BN x 64 bf16
-// activation tile (2-D tensor map, 128-byte swizzle, out-of-range tokens read as
-// zero); one thread issues four tcgen05.mma (M=128, N=BN, K=16) whose commit
-// releases the stage.  Four stages are in flight; all hand-offs are mbarriers
-// with bounded waits.  The epilogue reads the accumulators with tcgen05.ld (one
-// TMEM lane = one weight row per thread) and stores token-major, coalesced.
+// One CTA computes a 128-row x BN-token tile of y over the whole K.
+//   * packed bytes: the packed matrix is described to the TMA unit as a 2-D array of 32-bit
+//     words (row pitch = bytes per row); per 256-column macro-step one thread issues one
+//     tiled copy of a 128-row x (144 / 272 / 176 / 208)-byte box into a shared-memory ring
+//     (mbarrier transaction count).  The box width is an odd number of 16-byte chunks, so a
+//     warp whose lanes are consecutive rows reads 16-byte chunks without bank conflicts
+//     (Q5_1 copies 16 bytes more than its 192 to get there).  No load/store unit work per
+//     byte and as many bytes in flight as shared memory allows.
+//   * dequantization: sixteen warps in two groups that alternate 64-column steps; in a
+//     group two threads per row, 32 columns each.  Quants are turned into binary16 pairs
+//     with a mask-and-or against a magic exponent (1024+q, or 64+q for high nibbles),
+//     widened to f32, scaled with one FMA (the magic offset folded into the addend) and
+//     packed to bf16 pairs: no integer to float conversions, under one bit-operation per
+//     weight.
+//   * the dequantized tile never touches shared memory: a thread owns one weight row = one
+//     tensor-memory lane and writes its 32 bf16 with tcgen05.st into a ring of A-operand
+//     stages that lives in tensor memory next to the accumulator (32 columns per stage;
+//     14 / 12 / 8 stages for BN = 64 / 128 / 256).  The MMA takes A from tensor memory and
+//     B from shared memory.  A stage hand-off (store -> mma -> commit -> store) takes about
+//     a microsecond of barrier latency, so the ring depth, not the step time, is what keeps
+//     the tensor pipe fed; shared memory could not hold that many bf16 weight tiles.
+//   * one thread TMA-loads the matching BN x 64 bf16 activation tile (2-D tensor map,
+//     128-byte swizzle, out-of-range tokens read as zero) into a 128 KB ring; one thread
+//     issues four tcgen05.mma (M=128, N=BN, K=16) per step, whose commits release the stages.
+// All hand-offs are mbarriers with bounded waits.  The epilogue reads the accumulators
+// with tcgen05.ld (one TMEM lane = one weight row per thread) and stores token-major.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
+
+#include <type_traits>
 
 #include "llr_formats.cuh"
 #include "llr_kernels.cuh"
@@ -31,18 +51,39 @@ namespace {
 
 constexpr int BM = 128;     // weight rows per CTA = UMMA M
 constexpr int BK = 64;      // columns per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int NSTAGE = 4;
-constexpr int DQ_WARPS = 8; // dequant + epilogue warps
-constexpr int TC_THREADS = (DQ_WARPS + 2) * 32;
+constexpr int MACRO = 256;  // columns per packed-byte ring stage
+constexpr int DQ_WARPS = 16; // dequant warps: two groups of eight, alternating 64-column steps; the first eight also run the epilogue
+constexpr int W_PACKED = DQ_WARPS, W_ACT = DQ_WARPS + 1, W_MMA = DQ_WARPS + 2;
+constexpr int TC_THREADS = (DQ_WARPS + 3) * 32;
 constexpr int TC_SPIN = 1 << 24;
+constexpr int SMEM_LIMIT = 232448;  // 227 KB opt-in maximum per CTA
 
-template <int BN> struct GLay {
-  static constexpr int A_STAGE = BM * 128;
+// packed bytes per row per macro-step, and the ring's row pitch (odd multiple of 16 bytes)
+template <int DT> struct Pk;
+template <> struct Pk<DT_Q4_K> { static constexpr int RB = 144, PITCH = 144; };
+template <> struct Pk<DT_Q8_0> { static constexpr int RB = 272, PITCH = 272; };
+template <> struct Pk<DT_Q5_0> { static constexpr int RB = 176, PITCH = 176; };
+template <> struct Pk<DT_Q5_1> { static constexpr int RB = 192, PITCH = 208; };
+
+// Rings: A-operand stages in tensor memory (NA), activation tiles in shared memory (NB, 128 KB),
+// packed bytes in shared memory (NPK macro-steps, whatever is left, at most 6).
+template <int DT, int BN> struct GLay {
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int A_COLS = BK / 2;  // 64 bf16 per row = 32 columns of 32 bits
+  static constexpr int NA = (TMEM_COLS - BN) / A_COLS;
   static constexpr int B_STAGE = BN * 128;
-  static constexpr int A = 0;
-  static constexpr int B = A + NSTAGE * A_STAGE;
-  static constexpr int BAR = B + NSTAGE * B_STAGE;     // full_a, full_b, empty [NSTAGE]; acc_full; tmem slot
-  static constexpr int TOTAL = BAR + (3 * NSTAGE + 2) * 8 + 1024;  // + slack for the 1024-byte alignment
+  static constexpr int NB = (128 * 1024) / B_STAGE;
+  static constexpr int P_STAGE = BM * Pk<DT>::PITCH;
+  static constexpr int B = 0;
+  static constexpr int P = B + NB * B_STAGE;
+  static constexpr int FIXED = 1024 /*alignment slack*/ + 1024 /*barriers*/ + 64 /*chunk reads may pass a row's end*/;
+  static constexpr int NPK_FIT = (SMEM_LIMIT - FIXED - P) / P_STAGE;
+  static constexpr int NPK = NPK_FIT > 6 ? 6 : NPK_FIT;
+  static_assert(NPK >= 2, "packed ring needs two stages");
+  static constexpr int BAR = P + NPK * P_STAGE + 64;  // full_a, empty_a [NA]; full_b, empty_b [NB]; pk_full, pk_empty [NPK]; acc_full; tmem slot
+  static constexpr int TOTAL = BAR + 1024 + 1024;
+  static_assert((2 * NA + 2 * NB + 2 * NPK + 2) * 8 <= 1024, "barrier block");
+  static_assert(TOTAL <= SMEM_LIMIT, "shared memory");
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -65,14 +106,45 @@ __device__ __forceinline__ bool bar_wait(uint64_t* b, uint32_t parity) {
   return false;
 }
 
+// both barriers tested in one go, so that the two round trips to the barrier unit overlap
+__device__ __forceinline__ bool bar_wait2(uint64_t* a, uint32_t pa, uint64_t* b, uint32_t pb) {
+  for (int spins = 0; spins < TC_SPIN; ++spins) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p, q; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; mbarrier.try_wait.parity.shared::cta.b64 q, [%3], %4; "
+        "and.pred p, p, q; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok) : "r"(s32(a)), "r"(pa), "r"(s32(b)), "r"(pb) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+// two consecutive stages of each ring (adjacent barriers, same parity since the ring sizes are even)
+__device__ __forceinline__ bool bar_wait4(uint64_t* a, uint32_t pa, uint64_t* b, uint32_t pb) {
+  for (int spins = 0; spins < TC_SPIN; ++spins) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p, q, r, s; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; mbarrier.try_wait.parity.shared::cta.b64 q, [%1+8], %2; "
+        "mbarrier.try_wait.parity.shared::cta.b64 r, [%3], %4; mbarrier.try_wait.parity.shared::cta.b64 s, [%3+8], %4; "
+        "and.pred p, p, q; and.pred r, r, s; and.pred p, p, r; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok) : "r"(s32(a)), "r"(pa), "r"(s32(b)), "r"(pb) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{ .reg .pred p; elect.sync _|p, 0xffffffff; selp.u32 %0, 1, 0, p; }" : "=r"(pred));
+  return pred != 0;
+}
+
 // K-major, 128-byte swizzle shared-memory matrix descriptor: rows of 128 bytes, eight-row
 // groups 1024 bytes apart, descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc(const void* p) {
-  const uint64_t addr = (uint64_t)(s32(p) >> 4) & 0x3fffu;
+__device__ __forceinline__ uint64_t smem_desc_u(uint32_t saddr) {
+  const uint64_t addr = (uint64_t)(saddr >> 4) & 0x3fffu;
   return addr | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// kind::f16 instruction descriptor: D f32, A and B bf16, both K-major, M = 128, N = BN.
+// kind::f16 instruction descriptor: D f32, A (tensor memory) and B (shared, K-major) bf16, M = 128, N = BN.
 template <int BN> __host__ __device__ constexpr uint32_t instr_desc() {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
@@ -81,127 +153,153 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *(const uint32_t*)&v;
 }
-
 __device__ __forceinline__ float h2f(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
+__device__ __forceinline__ float2 hh2ff(uint32_t h2) { return __half22float2(*(const __half2*)&h2); }
 
-// NB bytes at a 2-byte aligned global address -> words holding bytes 0.., realigned
-template <int NW>
-__device__ __forceinline__ void load_words_a2(const uint8_t* p, uint32_t (&v)[NW]) {
-  const uintptr_t a = (uintptr_t)p;
-  const uint32_t* base = (const uint32_t*)(a & ~(uintptr_t)3);
-  if ((a & 2) == 0) {
+// 32 / 16 bits at a compile-time even byte offset of a word array
+template <int OFF> __device__ __forceinline__ uint32_t w_at(const uint32_t* w) {
+  if constexpr (OFF % 4 == 0) return w[OFF / 4];
+  else return __funnelshift_r(w[OFF / 4], w[OFF / 4 + 1], 16);
+}
+template <int OFF> __device__ __forceinline__ uint32_t h_at(const uint32_t* w) {
+  if constexpr (OFF % 4 == 0) return w[OFF / 4] & 0xffffu;
+  else return w[OFF / 4] >> 16;
+}
+// Shared memory is addressed through 32-bit shared-window addresses and explicit ld/st.shared:
+// the tile base is aligned by integer arithmetic, which would otherwise turn every access
+// into a generic-address load or store.
+template <int NCH> __device__ __forceinline__ void lds_chunks(uint32_t p, uint32_t (&w)[4 * NCH]) {
 #pragma unroll
-    for (int i = 0; i < NW; ++i) v[i] = __ldg(base + i);
-  } else {
-    uint32_t w[NW + 1];
-#pragma unroll
-    for (int i = 0; i <= NW; ++i) w[i] = __ldg(base + i);  // the matrix allocation is padded past its last row
-#pragma unroll
-    for (int i = 0; i < NW; ++i) v[i] = __funnelshift_r(w[i], w[i + 1], 16);
-  }
+  for (int i = 0; i < NCH; ++i)
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3]) : "r"(p + 16 * i));
+}
+__device__ __forceinline__ void sts128(uint32_t p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-// The packed bytes one dequant thread needs for its 32 columns of one 64-column step.
-template <int DT> struct Raw;
-template <> struct Raw<DT_Q4_K> { uint4 hdr, q0, q1; };
-template <> struct Raw<DT_Q8_0> { uint32_t w[9]; };
-template <> struct Raw<DT_Q5_0> { uint32_t w[6]; };
-template <> struct Raw<DT_Q5_1> { uint32_t w[6]; };
-
-template <int DT>
-__device__ __forceinline__ void load_raw(const uint8_t* row, int ks, int h, Raw<DT>& r) {
-  if constexpr (DT == DT_Q4_K) {
-    const uint8_t* blk = row + (ks >> 2) * 144;
-    r.hdr = __ldg((const uint4*)blk);
-    const uint4* q = (const uint4*)(blk + 16 + (ks & 3) * 32);
-    r.q0 = __ldg(q);
-    r.q1 = __ldg(q + 1);
-  } else if constexpr (DT == DT_Q8_0) {
-    load_words_a2<9>(row + (size_t)(2 * ks + h) * 34, r.w);
-  } else if constexpr (DT == DT_Q5_0) {
-    load_words_a2<6>(row + (size_t)(2 * ks + h) * 22, r.w);
-  } else {
-    load_words_a2<6>(row + (size_t)(2 * ks + h) * 24, r.w);
-  }
+// Four unsigned bytes c0..c3 (each < 1024) -> out[0] = bf16(c0*a+nb), bf16(c1*a+nb); out[1] = c2, c3.
+// MASK/MAGIC pick the bits and the binary16 exponent whose unit in the last place is one
+// quant step; nb already contains minus the magic offset times a.  XORM flips a sign bit (Q8_0).
+template <uint32_t MASK, uint32_t MAGIC>
+__device__ __forceinline__ void emit4(uint32_t w, float a, float nb, uint32_t& o0, uint32_t& o1) {
+  const float2 f = hh2ff((w & MASK) ^ MAGIC);         // elements 0 and 2
+  const float2 g = hh2ff(((w >> 8) & MASK) ^ MAGIC);  // elements 1 and 3
+  o0 = pack_bf16(fmaf(f.x, a, nb), fmaf(g.x, a, nb));
+  o1 = pack_bf16(fmaf(f.y, a, nb), fmaf(g.y, a, nb));
 }
 
-__device__ __forceinline__ uint32_t byte_of(const uint32_t* w, int i) { return (w[i >> 2] >> (8 * (i & 3))) & 255u; }
+// bit k of x (k = 0..3) -> bit 8k+4
+__device__ __forceinline__ uint32_t spread_hi(uint32_t x) { return (x * 0x02040810u) & 0x10101010u; }
 
-// 32 dequantized weights of this thread as 16 packed bf16 pairs (column order).
-template <int DT>
-__device__ __forceinline__ void dequant32(const Raw<DT>& r, int ks, int h, uint32_t (&out)[16]) {
+// Sub-block SB (32 columns; 0..7) of one row's 256-column macro-step, from the row's bytes in the
+// packed ring, as 16 packed bf16 pairs in column order.
+__device__ __forceinline__ void emit4r(uint32_t w, uint32_t mask, uint32_t magic, float a, float nb, uint32_t& o0, uint32_t& o1) {
+  const float2 f = hh2ff((w & mask) | magic);
+  const float2 g = hh2ff(((w >> 8) & mask) | magic);
+  o0 = pack_bf16(fmaf(f.x, a, nb), fmaf(g.x, a, nb));
+  o1 = pack_bf16(fmaf(f.y, a, nb), fmaf(g.y, a, nb));
+}
+
+// SB < 0: the sub-block index is the run-time value rsb (formats whose code does not depend on it)
+template <int DT, int SB>
+__device__ __forceinline__ void dequant_sub(uint32_t prow, uint32_t (&out)[16], int rsb = 0) {
   if constexpr (DT == DT_Q4_K) {
-    const float d = h2f(r.hdr.x & 0xffffu), dmin = h2f(r.hdr.x >> 16);
-    const int sub = 2 * (ks & 3) + h;
+    // SB enters only through shift counts, masks and an address: one code path for all eight
+    // sub-blocks keeps the dequant loop inside the instruction cache.
+    const int sb = SB < 0 ? rsb : SB;
+    uint32_t hdr[4], q[8];
+    lds_chunks<1>(prow, hdr);
+    lds_chunks<2>(prow + 16 + 32 * (sb >> 1), q);
+    const float d = h2f(hdr[0] & 0xffffu), dmin = h2f(hdr[0] >> 16);
+    // get_scale_min_k4: sub-blocks 0..3 use the low six bits of bytes sb / sb+4; 4..7 use a nibble of
+    // byte sb+4 plus the top two bits of bytes sb-4 / sb
+    const int j = sb & 3, sh = 8 * j;
+    const uint32_t b_lo = (hdr[1] >> sh) & 255u, b_mid = (hdr[2] >> sh) & 255u, b_hi = (hdr[3] >> sh) & 255u;
     uint32_t sc, mn;
-    if (sub < 4) {
-      sc = (r.hdr.y >> (8 * sub)) & 63u;
-      mn = (r.hdr.z >> (8 * sub)) & 63u;
-    } else {
-      const int jj = sub - 4;
-      const uint32_t hb = (r.hdr.w >> (8 * jj)) & 255u;
-      sc = (hb & 15u) | (((r.hdr.y >> (8 * jj + 6)) & 3u) << 4);
-      mn = (hb >> 4) | (((r.hdr.z >> (8 * jj + 6)) & 3u) << 4);
-    }
-    const float a = d * (float)sc, nb = -(dmin * (float)mn);
-    const uint32_t q[8] = {r.q0.x, r.q0.y, r.q0.z, r.q0.w, r.q1.x, r.q1.y, r.q1.z, r.q1.w};
+    if (sb < 4) { sc = b_lo & 63u; mn = b_mid & 63u; }
+    else { sc = (b_hi & 15u) | ((b_lo >> 6) << 4); mn = (b_hi >> 4) | ((b_mid >> 6) << 4); }
+    const float a = d * (float)sc;
+    // low nibbles: 0x6400 | q is binary16 1024 + q; high nibbles in place: 0x5400 | (q << 4) is 64 + q
+    const bool hi = sb & 1;
+    const uint32_t mask = hi ? 0x00f000f0u : 0x000f000fu, magic = hi ? 0x54005400u : 0x64006400u;
+    const float nb = fmaf(hi ? -64.0f : -1024.0f, a, -(dmin * (float)mn));
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t w4 = (h ? (q[i] >> 4) : q[i]) & 0x0f0f0f0fu;
-      out[2 * i] = pack_bf16(fmaf(a, (float)(w4 & 255u), nb), fmaf(a, (float)((w4 >> 8) & 255u), nb));
-      out[2 * i + 1] = pack_bf16(fmaf(a, (float)((w4 >> 16) & 255u), nb), fmaf(a, (float)(w4 >> 24), nb));
-    }
+    for (int i = 0; i < 8; ++i) emit4r(q[i], mask, magic, a, nb, out[2 * i], out[2 * i + 1]);
   } else if constexpr (DT == DT_Q8_0) {
-    const float d = h2f(r.w[0] & 0xffffu);
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-      out[i] = pack_bf16((float)(int)(int8_t)byte_of(r.w, 2 + 2 * i) * d, (float)(int)(int8_t)byte_of(r.w, 3 + 2 * i) * d);
+    constexpr int C0 = (34 * SB) / 16, OFF = 34 * SB - 16 * C0;
+    uint32_t w[12];
+    lds_chunks<3>(prow + 16 * C0, w);
+    const float d = h2f(h_at<OFF>(w));
+    const float nb = -1152.0f * d;  // byte ^ 0x80 = q + 128, magic adds 1024; exact
+    auto go = [&](auto I) {
+      constexpr int i = decltype(I)::value;
+      emit4<0x00ff00ffu, 0x64806480u>(w_at<OFF + 2 + 4 * i>(w), d, nb, out[2 * i], out[2 * i + 1]);
+    };
+    go(std::integral_constant<int, 0>{}); go(std::integral_constant<int, 1>{});
+    go(std::integral_constant<int, 2>{}); go(std::integral_constant<int, 3>{});
+    go(std::integral_constant<int, 4>{}); go(std::integral_constant<int, 5>{});
+    go(std::integral_constant<int, 6>{}); go(std::integral_constant<int, 7>{});
   } else {
-    constexpr int HDR = DT == DT_Q5_0 ? 2 : 4;
-    const float d = h2f(r.w[0] & 0xffffu);
-    const float m = DT == DT_Q5_1 ? h2f(r.w[0] >> 16) : 0.0f;
-    uint32_t qh = 0;
+    constexpr int BB = DT == DT_Q5_0 ? 22 : 24, HDR = DT == DT_Q5_0 ? 2 : 4;
+    constexpr int C0 = (BB * SB) / 16, OFF = BB * SB - 16 * C0, NCH = (OFF + BB + 15) / 16;
+    uint32_t w[4 * NCH + 1];
+    {
+      uint32_t t[4 * NCH];
+      lds_chunks<NCH>(prow + 16 * C0, t);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) qh |= byte_of(r.w, HDR + i) << (8 * i);
-    float wv[32];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const uint32_t p = byte_of(r.w, HDR + 4 + j);
-      const int c0 = (int)((p & 15u) | (((qh >> j) & 1u) << 4));
-      const int c1 = (int)((p >> 4) | (((qh >> (j + 16)) & 1u) << 4));
-      wv[j] = DT == DT_Q5_0 ? (float)(c0 - 16) * d : fmaf((float)c0, d, m);
-      wv[j + 16] = DT == DT_Q5_0 ? (float)(c1 - 16) * d : fmaf((float)c1, d, m);
+      for (int i = 0; i < 4 * NCH; ++i) w[i] = t[i];
+      w[4 * NCH] = 0;
     }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) out[i] = pack_bf16(wv[2 * i], wv[2 * i + 1]);
+    const float d = h2f(h_at<OFF>(w));
+    float nb;
+    if constexpr (DT == DT_Q5_0) nb = -1040.0f * d;  // (c - 16) * d with the magic 1024; exact
+    else nb = fmaf(-1024.0f, d, h2f(h_at<OFF + 2>(w)));
+    const uint32_t qh = w_at<OFF + HDR>(w);
+    auto go = [&](auto I) {
+      constexpr int i = decltype(I)::value;
+      const uint32_t qs = w_at<OFF + HDR + 4 + 4 * i>(w);
+      const uint32_t cl = (qs & 0x0f0f0f0fu) | spread_hi((qh >> (4 * i)) & 15u);          // columns 4i .. 4i+3
+      const uint32_t ch = ((qs >> 4) & 0x0f0f0f0fu) | spread_hi((qh >> (16 + 4 * i)) & 15u);  // columns 16+4i ..
+      emit4<0x00ff00ffu, 0x64006400u>(cl, d, nb, out[2 * i], out[2 * i + 1]);
+      emit4<0x00ff00ffu, 0x64006400u>(ch, d, nb, out[8 + 2 * i], out[8 + 2 * i + 1]);
+    };
+    go(std::integral_constant<int, 0>{}); go(std::integral_constant<int, 1>{});
+    go(std::integral_constant<int, 2>{}); go(std::integral_constant<int, 3>{});
   }
 }
 
 template <int DT, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_kernel(const uint8_t* __restrict__ W, int64_t row_bytes, int rows, int cols, int tokens,
+gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int tokens,
                const __grid_constant__ CUtensorMap xmap, float* __restrict__ Y, int* __restrict__ err) {
-  using L = GLay<BN>;
+  using L = GLay<DT, BN>;
+  constexpr int NA = L::NA, NB = L::NB, NPK = L::NPK, PITCH = Pk<DT>::PITCH, RB = Pk<DT>::RB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms are 1024 bytes
-  uint8_t* sA = smem + L::A;
   uint8_t* sB = smem + L::B;
+  uint8_t* sP = smem + L::P;
   uint64_t* full_a = (uint64_t*)(smem + L::BAR);
-  uint64_t* full_b = full_a + NSTAGE;
-  uint64_t* empty = full_b + NSTAGE;
-  uint64_t* acc_full = empty + NSTAGE;
+  uint64_t* empty_a = full_a + NA;
+  uint64_t* full_b = empty_a + NA;
+  uint64_t* empty_b = full_b + NB;
+  uint64_t* pk_full = empty_b + NB;
+  uint64_t* pk_empty = pk_full + NPK;
+  uint64_t* acc_full = pk_empty + NPK;
   uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row0 = blockIdx.x * BM, tok0 = blockIdx.y * BN;
-  const int nk = cols / BK;
+  const int nms = cols / MACRO, nk = nms * (MACRO / BK);
 
   if (tid == 0) {
-    for (int s = 0; s < NSTAGE; ++s) { bar_init(&full_a[s], DQ_WARPS); bar_init(&full_b[s], 1); bar_init(&empty[s], 1); }
+    for (int s = 0; s < NA; ++s) { bar_init(&full_a[s], DQ_WARPS / 2); bar_init(&empty_a[s], 1); }
+    for (int s = 0; s < NB; ++s) { bar_init(&full_b[s], 1); bar_init(&empty_b[s], 1); }
+    for (int s = 0; s < NPK; ++s) { bar_init(&pk_full[s], 1); bar_init(&pk_empty[s], DQ_WARPS); }
     bar_init(acc_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == DQ_WARPS + 1) {  // the MMA warp owns the tensor-memory allocation
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(BN < 32 ? 32 : BN) : "memory");
+  if (warp == W_MMA) {  // the MMA warp owns the tensor-memory allocation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(L::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -212,38 +310,45 @@ gemm_tc_kernel(const uint8_t* __restrict__ W, int64_t row_bytes, int rows, int c
 
   if (warp < DQ_WARPS) {
     // ---------------------------------------------------------------- dequant
-    const int r = tid & 127, h = tid >> 7;  // weight row inside the tile, column half of the step
-    int grow = row0 + r;
-    if (grow >= rows) grow = rows - 1;
-    const uint8_t* wrow = W + (int64_t)grow * row_bytes;
-    // packed bytes of the next PF steps are in flight in registers while this one is decoded
-    constexpr int PF = 4;
-    Raw<DT> buf[PF];
-#pragma unroll
-    for (int i = 0; i < PF; ++i)
-      if (i < nk) load_raw<DT>(wrow, i, h, buf[i]);
-    for (int ks0 = 0; ks0 < nk; ks0 += PF) {
-#pragma unroll
-      for (int i = 0; i < PF; ++i) {
-        const int ks = ks0 + i;
-        if (ks >= nk) break;
-        const int s = ks % NSTAGE;
-        uint32_t out[16];
-        dequant32<DT>(buf[i], ks, h, out);
-        if (ks + PF < nk) load_raw<DT>(wrow, ks + PF, h, buf[i]);
-        if (ok && !bar_wait(&empty[s], (uint32_t)(((ks / NSTAGE) & 1) ^ 1))) { ok = false; atomicExch(err, 3); }
-        uint8_t* arow = sA + s * L::A_STAGE + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-          const int chunk = (4 * h + c4) ^ (r & 7);  // 128-byte swizzle: 16-byte chunk index xor row-in-group
-          *(uint4*)(arow + chunk * 16) = make_uint4(out[4 * c4], out[4 * c4 + 1], out[4 * c4 + 2], out[4 * c4 + 3]);
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
-        __syncwarp();
-        if (lane == 0) bar_arrive(&full_a[s]);
+    // weight row inside the tile, column half of the step, step parity (the last two warp-uniform)
+    const int r = tid & 127, h = (tid >> 7) & 1, g = tid >> 8;
+    // this thread's A-operand words: lane = row (the warp's lane quarter is warp % 4), 16 columns per half
+    const uint32_t a_dst0 = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(BN + 16 * h);
+    auto step = [&](auto KQ, uint32_t prow, int ks) {
+      constexpr int kq = decltype(KQ)::value;
+      uint32_t out[16];
+      if constexpr (DT == DT_Q4_K) dequant_sub<DT, -1>(prow, out, 2 * kq + h);
+      else if (h == 0) dequant_sub<DT, 2 * kq>(prow, out);
+      else dequant_sub<DT, 2 * kq + 1>(prow, out);
+      const int s = ks % NA;
+      if (ok && !bar_wait(&empty_a[s], (uint32_t)(((ks / NA) & 1) ^ 1))) { ok = false; atomicExch(err, 3); }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      asm volatile(
+          "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+          ::"r"(a_dst0 + (uint32_t)(s * L::A_COLS)), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]),
+            "r"(out[6]), "r"(out[7]), "r"(out[8]), "r"(out[9]), "r"(out[10]), "r"(out[11]), "r"(out[12]), "r"(out[13]),
+            "r"(out[14]), "r"(out[15]) : "memory");
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) bar_arrive(&full_a[s]);
+    };
+    for (int ms = 0; ms < nms; ++ms) {
+      const int ps = ms % NPK;
+      if (ok && !bar_wait(&pk_full[ps], (uint32_t)((ms / NPK) & 1))) { ok = false; atomicExch(err, 3); }
+      const uint32_t prow = s32(sP) + ps * L::P_STAGE + r * PITCH;
+      if (g == 0) {
+        step(std::integral_constant<int, 0>{}, prow, 4 * ms);
+        step(std::integral_constant<int, 2>{}, prow, 4 * ms + 2);
+      } else {
+        step(std::integral_constant<int, 1>{}, prow, 4 * ms + 1);
+        step(std::integral_constant<int, 3>{}, prow, 4 * ms + 3);
       }
+      __syncwarp();
+      if (lane == 0) bar_arrive(&pk_empty[ps]);
     }
     // --------------------------------------------------------------- epilogue
+    if (warp < 8) {
     if (ok && !bar_wait(acc_full, 0)) { ok = false; atomicExch(err, 3); }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int q = warp & 3, half = warp >> 2;  // TMEM lane quarter of this warp, column half
@@ -271,46 +376,86 @@ gemm_tc_kernel(const uint8_t* __restrict__ W, int64_t row_bytes, int rows, int c
       }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  } else if (warp == DQ_WARPS) {
-    // ---------------------------------------------------- activation tiles (TMA)
+    }
+  } else if (warp == W_PACKED) {
+    // ------------------------------------- packed weight bytes (one 2-D TMA box per macro-step)
     if (lane == 0) {
-      for (int ks = 0; ks < nk; ++ks) {
-        const int s = ks % NSTAGE;
-        if (ok && !bar_wait(&empty[s], (uint32_t)(((ks / NSTAGE) & 1) ^ 1))) { ok = false; atomicExch(err, 3); }
+      for (int ms = 0; ms < nms; ++ms) {
+        const int ps = ms % NPK;
+        if (ok && !bar_wait(&pk_empty[ps], (uint32_t)(((ms / NPK) & 1) ^ 1))) { ok = false; atomicExch(err, 3); }
+        bar_expect(&pk_full[ps], BM * PITCH);
+        // x in 32-bit elements; x*4 = ms*RB is a multiple of 16 bytes.  Rows past the end read as zero.
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+            ::"r"(s32(sP + ps * L::P_STAGE)), "l"(&wmap), "r"(ms * (RB / 4)), "r"(row0), "r"(s32(&pk_full[ps])) : "memory");
+      }
+    }
+  } else if (warp == W_ACT) {
+    // ---------------------------------------------------- activation tiles (TMA)
+    // the warp walks the ring converged (uniform registers for the addresses), one elected lane issues
+    const uint32_t sb_u = __shfl_sync(0xffffffffu, s32(sB), 0);
+    for (int ks = 0; ks < nk; ++ks) {
+      const int s = ks % NB;
+      if (ok && !bar_wait(&empty_b[s], (uint32_t)(((ks / NB) & 1) ^ 1))) { ok = false; atomicExch(err, 3); }
+      if (elect_one()) {
         bar_expect(&full_b[s], BN * 128);
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-            ::"r"(s32(sB + s * L::B_STAGE)), "l"(&xmap), "r"(ks * BK), "r"(tok0), "r"(s32(&full_b[s])) : "memory");
+            ::"r"(sb_u + (uint32_t)(s * L::B_STAGE)), "l"(&xmap), "r"(ks * BK), "r"(tok0), "r"(s32(&full_b[s])) : "memory");
       }
+      __syncwarp();
     }
   } else {
     // ------------------------------------------------------------------- MMA
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc<BN>();
-      for (int ks = 0; ks < nk; ++ks) {
-        const int s = ks % NSTAGE;
-        const uint32_t par = (uint32_t)((ks / NSTAGE) & 1);
-        if (ok && !(bar_wait(&full_a[s], par) && bar_wait(&full_b[s], par))) { ok = false; atomicExch(err, 3); }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t da = smem_desc(sA + s * L::A_STAGE), db = smem_desc(sB + s * L::B_STAGE);
-#pragma unroll
-        for (int kk = 0; kk < BK / 16; ++kk) {
-          const uint32_t acc = (ks | kk) ? 1u : 0u;
-          // 16 bf16 = 32 bytes along K inside the swizzled row: advance the start address by 2 x 16 bytes
-          asm volatile(
-              "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
-              ::"r"(tmem), "l"(da + 2 * kk), "l"(db + 2 * kk), "r"(idesc), "r"(acc) : "memory");
-        }
-        // frees the stage once the MMAs that read it have completed
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&empty[s])) : "memory");
+    // The whole warp walks the loop converged and one elected lane issues: addresses, descriptors
+    // and the loop state then live in uniform registers, which is what the MMA instruction reads.
+    // A loop entered by a single lane pays a vector-to-uniform move per operand instead and
+    // becomes the bottleneck of the CTA at small BN.
+    constexpr uint32_t idesc = instr_desc<BN>();
+    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+    const uint32_t sb_u = __shfl_sync(0xffffffffu, s32(sB), 0);
+    // steps per iteration: two where the rings are deep (one barrier round trip for both), one at
+    // BN = 256, whose activation ring has only four stages
+    constexpr int U = BN > 128 ? 1 : 2;
+    static_assert(NA % U == 0 && NB % U == 0, "steps per iteration");
+    for (int ks = 0; ks < nk; ks += U) {  // nk is a multiple of 4
+      const int sa = ks % NA, sb = ks % NB;
+      const uint32_t pa = (uint32_t)((ks / NA) & 1), pb = (uint32_t)((ks / NB) & 1);
+      if (ok && !(U == 2 ? bar_wait4(&full_a[sa], pa, &full_b[sb], pb) : bar_wait2(&full_a[sa], pa, &full_b[sb], pb))) {
+        ok = false;
+        atomicExch(err, 3);
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(acc_full)) : "memory");
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (elect_one()) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint32_t ta = tmem_u + (uint32_t)(BN + (sa + u) * L::A_COLS);
+          const uint64_t db = smem_desc_u(sb_u + (uint32_t)((sb + u) * L::B_STAGE));
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            // 16 bf16 along K: eight 32-bit columns of A; 32 bytes inside B's swizzled row = 2 x 16-byte units
+            if (u == 0 && kk == 0 && ks == 0)
+              asm volatile("{ .reg .pred p; setp.ne.b32 p, 0, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
+                           ::"r"(tmem_u), "r"(ta), "l"(db), "r"(idesc) : "memory");
+            else
+              asm volatile("{ .reg .pred p; setp.eq.b32 p, 0, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
+                           ::"r"(tmem_u), "r"(ta + 8 * kk), "l"(db + 2 * kk), "r"(idesc) : "memory");
+          }
+          // free both stages once the MMAs that read them have completed
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&empty_a[sa + u])) : "memory");
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&empty_b[sb + u])) : "memory");
+        }
+      }
+      __syncwarp();
     }
+    if (elect_one())
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(acc_full)) : "memory");
+    __syncwarp();
   }
   __syncthreads();
-  if (warp == DQ_WARPS + 1) {
+  if (warp == W_MMA) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN < 32 ? 32 : BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(L::TMEM_COLS) : "memory");
   }
 }
 
@@ -343,9 +488,10 @@ EncodeTiledFn encode_fn() {
 }
 
 template <int DT, int BN>
-cudaError_t launch_bn(const MatView& m, const CUtensorMap& xmap, float* y, int tokens, cudaStream_t stream, int* err) {
+cudaError_t launch_bn(const MatView& m, const CUtensorMap& wmap, const CUtensorMap& xmap, float* y, int tokens,
+                      cudaStream_t stream, int* err) {
   auto kern = gemm_tc_kernel<DT, BN>;
-  constexpr int smem = GLay<BN>::TOTAL;
+  constexpr int smem = GLay<DT, BN>::TOTAL;
   static bool ready = false;
   if (!ready) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -353,7 +499,7 @@ cudaError_t launch_bn(const MatView& m, const CUtensorMap& xmap, float* y, int t
     ready = true;
   }
   dim3 grid((unsigned)((m.rows + BM - 1) / BM), (unsigned)((tokens + BN - 1) / BN));
-  kern<<<grid, TC_THREADS, smem, stream>>>(m.w, m.row_bytes, (int)m.rows, (int)m.cols, tokens, xmap, y, err);
+  kern<<<grid, TC_THREADS, smem, stream>>>(wmap, (int)m.rows, (int)m.cols, tokens, xmap, y, err);
   return cudaGetLastError();
 }
 
@@ -370,9 +516,17 @@ cudaError_t launch_dt(const MatView& m, const __nv_bfloat16* xb, float* y, int t
   if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)xb, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return cudaErrorInvalidValue;
-  if (bn == 256) return launch_bn<DT, 256>(m, xmap, y, tokens, stream, err);
-  if (bn == 128) return launch_bn<DT, 128>(m, xmap, y, tokens, stream, err);
-  return launch_bn<DT, 64>(m, xmap, y, tokens, stream, err);
+  // packed weights as rows of 32-bit words; one box = 128 rows x the ring pitch
+  CUtensorMap wmap;
+  const cuuint64_t wdims[2] = {(cuuint64_t)(m.row_bytes / 4), (cuuint64_t)m.rows};
+  const cuuint64_t wstrides[1] = {(cuuint64_t)m.row_bytes};
+  const cuuint32_t wbox[2] = {(cuuint32_t)(Pk<DT>::PITCH / 4), (cuuint32_t)BM};
+  if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)m.w, wdims, wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return cudaErrorInvalidValue;
+  if (bn == 256) return launch_bn<DT, 256>(m, wmap, xmap, y, tokens, stream, err);
+  if (bn == 128) return launch_bn<DT, 128>(m, wmap, xmap, y, tokens, stream, err);
+  return launch_bn<DT, 64>(m, wmap, xmap, y, tokens, stream, err);
 }
 
 }  // namespace
@@ -380,7 +534,7 @@ cudaError_t launch_dt(const MatView& m, const __nv_bfloat16* xb, float* y, int t
 bool gemm_tc_supported(const MatView& m, int64_t tokens) {
   if (m.dtype != DT_Q4_K && m.dtype != DT_Q8_0 && m.dtype != DT_Q5_0 && m.dtype != DT_Q5_1) return false;
   if (tokens < 16 || tokens > (1 << 24) || m.rows <= 0 || m.rows > (1 << 30)) return false;
-  if (m.cols % BK != 0 || m.cols <= 0 || m.cols > (1 << 30)) return false;
+  if (m.cols % MACRO != 0 || m.cols <= 0 || m.cols > (1 << 30)) return false;
   return ((uintptr_t)m.w & 15) == 0;
 }
 
