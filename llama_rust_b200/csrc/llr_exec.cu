@@ -112,8 +112,10 @@ struct llr_exec {
   std::string err;
   llr_counters ctr{};
   int path = PATH_AUTO;
-  int* err_flag = nullptr;  // device word set by a kernel whose bounded wait ran out
-  int err_host = 0;
+  int* err_flag = nullptr;  // device alias of err_pinned: set by a kernel whose bounded wait ran out
+  volatile int* err_pinned = nullptr;  // the same word, mapped pinned host memory
+  struct PinSeen { const void* p; bool pinned; } pin_seen[8] = {};
+  int pin_next = 0;
   // activation / result staging
   float* pin_x = nullptr; size_t pin_x_cap = 0;
   float* pin_y = nullptr; size_t pin_y_cap = 0;
@@ -285,10 +287,26 @@ cudaError_t ensure_scratch(llr_exec* e, const llr_matrix* m, size_t tokens, void
   return ce;
 }
 
-bool is_pinned_host(const void* p) {
+// Remembers the answer for the last few pointers: callers reuse their buffers, and a stale answer
+// is harmless either way (a pageable buffer taken for pinned is still copied correctly, only
+// slower; a pinned one taken for pageable goes through the staging buffer).
+bool is_pinned_host(llr_exec* e, const void* p) {
+  for (const auto& s : e->pin_seen)
+    if (s.p == p) return s.pinned;
   cudaPointerAttributes a{};
-  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
-  return a.type == cudaMemoryTypeHost;
+  bool pinned = false;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) cudaGetLastError();
+  else pinned = a.type == cudaMemoryTypeHost;
+  e->pin_seen[e->pin_next] = {p, pinned};
+  e->pin_next = (e->pin_next + 1) % 8;
+  return pinned;
+}
+
+// after a synchronize: non-zero when a device-side wait gave up since the last check
+int take_device_error(llr_exec* e) {
+  const int v = *e->err_pinned;
+  if (v != 0) *e->err_pinned = 0;
+  return v;
 }
 
 // H2D of the activations, launch, D2H of the result, synchronize (gpu.rs:301-334,
@@ -299,12 +317,12 @@ int run_host(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, fl
   if ((ce = grow_device(&e->dev_x, &e->dev_x_cap, nx)) != cudaSuccess) return fail_cuda(e, ce, "activation scratch");
   if ((ce = grow_device(&e->dev_y, &e->dev_y_cap, ny)) != cudaSuccess) return fail_cuda(e, ce, "result scratch");
   const float* src = x;
-  if (!is_pinned_host(x)) {
+  if (!is_pinned_host(e, x)) {
     if ((ce = grow_pinned(&e->pin_x, &e->pin_x_cap, nx)) != cudaSuccess) return fail_cuda(e, ce, "pinned activation staging");
     std::memcpy(e->pin_x, x, nx * sizeof(float));
     src = e->pin_x;
   }
-  const bool y_pinned = is_pinned_host(y);
+  const bool y_pinned = is_pinned_host(e, y);
   float* dst = y;
   if (!y_pinned) {
     if ((ce = grow_pinned(&e->pin_y, &e->pin_y_cap, ny)) != cudaSuccess) return fail_cuda(e, ce, "pinned result staging");
@@ -319,12 +337,8 @@ int run_host(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, fl
     return fail_cuda(e, ce, "kernel launch");
   if ((ce = cudaMemcpyAsync(dst, e->dev_y, ny * sizeof(float), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess)
     return fail_cuda(e, ce, "result download");
-  if ((ce = cudaMemcpyAsync(&e->err_host, e->err_flag, sizeof(int), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess)
-    return fail_cuda(e, ce, "status download");
   if ((ce = cudaStreamSynchronize(e->stream)) != cudaSuccess) return fail_cuda(e, ce, "stream synchronize");
-  if (e->err_host != 0) {
-    cudaMemsetAsync(e->err_flag, 0, sizeof(int), e->stream);
-    e->err_host = 0;
+  if (take_device_error(e) != 0) {
     return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations (copy engine did not deliver a weight tile)");
   }
   if (!y_pinned) std::memcpy(y, e->pin_y, ny * sizeof(float));
@@ -394,8 +408,14 @@ int llr_exec_create(int device, llr_exec** out) {
     return LLR_ERR_CUDA;
   }
   e->sm_count = prop.multiProcessorCount;
-  if ((ce = cudaMalloc((void**)&e->err_flag, sizeof(int))) != cudaSuccess ||
-      (ce = cudaMemset(e->err_flag, 0, sizeof(int))) != cudaSuccess) {
+  void* err_host = nullptr;
+  if ((ce = cudaHostAlloc(&err_host, sizeof(int), cudaHostAllocMapped)) == cudaSuccess) {
+    *(int*)err_host = 0;
+    e->err_pinned = (volatile int*)err_host;
+    ce = cudaHostGetDevicePointer((void**)&e->err_flag, err_host, 0);
+  }
+  if (ce != cudaSuccess) {
+    if (err_host) cudaFreeHost(err_host);
     cudaGetLastError();
     g_create_error = std::string("CUDA initialisation failed: ") + cudaGetErrorString(ce);
     cudaStreamDestroy(e->stream);
@@ -428,7 +448,7 @@ int llr_exec_destroy(llr_exec* e) {
   if (e->dev_y) cudaFree(e->dev_y);
   if (e->dev_s) cudaFree(e->dev_s);
   if (e->dev_moe) cudaFree(e->dev_moe);
-  if (e->err_flag) cudaFree(e->err_flag);
+  if (e->err_pinned) cudaFreeHost((void*)e->err_pinned);
   cudaStreamDestroy(e->stream);
   cudaGetLastError();
   delete e;
@@ -648,12 +668,9 @@ int llr_gemm_device_noalloc(llr_exec* e, const llr_matrix* m, size_t tokens, con
 int llr_exec_synchronize(llr_exec* e) {
   if (!e) return LLR_ERR_INVALID;
   DeviceGuard guard(e->device);
-  cudaError_t ce = cudaMemcpyAsync(&e->err_host, e->err_flag, sizeof(int), cudaMemcpyDeviceToHost, e->stream);
-  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+  cudaError_t ce = cudaStreamSynchronize(e->stream);
   if (ce != cudaSuccess) return fail_cuda(e, ce, "stream synchronize");
-  if (e->err_host != 0) {
-    cudaMemsetAsync(e->err_flag, 0, sizeof(int), e->stream);
-    e->err_host = 0;
+  if (take_device_error(e) != 0) {
     return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations (copy engine did not deliver a weight tile)");
   }
   return LLR_OK;
@@ -794,12 +811,9 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
     return fail_cuda(e, ce, "kernel launch");
   if ((ce = grow_pinned(&e->pin_y, &e->pin_y_cap, nx)) != cudaSuccess) return fail_cuda(e, ce, "pinned result staging");
   if ((ce = cudaMemcpyAsync(e->pin_y, d_out, nx * 4, cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
-      (ce = cudaMemcpyAsync(&e->err_host, e->err_flag, sizeof(int), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
       (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)
     return fail_cuda(e, ce, "result download");
-  if (e->err_host != 0) {
-    cudaMemsetAsync(e->err_flag, 0, sizeof(int), e->stream);
-    e->err_host = 0;
+  if (take_device_error(e) != 0) {
     return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations");
   }
   std::memcpy(out, e->pin_y, nx * 4);

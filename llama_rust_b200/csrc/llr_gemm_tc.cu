@@ -321,7 +321,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
       else if (h == 0) dequant_sub<DT, 2 * kq>(prow, out);
       else dequant_sub<DT, 2 * kq + 1>(prow, out);
       const int s = ks % NA;
-      if (ok && !bar_wait(&empty_a[s], (uint32_t)(((ks / NA) & 1) ^ 1))) { ok = false; atomicExch(err, 3); }
+      if (ok && !bar_wait(&empty_a[s], (uint32_t)(((ks / NA) & 1) ^ 1))) { ok = false; report_error(err, 3); }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       asm volatile(
           "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -335,7 +335,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
     };
     for (int ms = 0; ms < nms; ++ms) {
       const int ps = ms % NPK;
-      if (ok && !bar_wait(&pk_full[ps], (uint32_t)((ms / NPK) & 1))) { ok = false; atomicExch(err, 3); }
+      if (ok && !bar_wait(&pk_full[ps], (uint32_t)((ms / NPK) & 1))) { ok = false; report_error(err, 3); }
       const uint32_t prow = s32(sP) + ps * L::P_STAGE + r * PITCH;
       if (g == 0) {
         step(std::integral_constant<int, 0>{}, prow, 4 * ms);
@@ -349,7 +349,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
     }
     // --------------------------------------------------------------- epilogue
     if (warp < 8) {
-    if (ok && !bar_wait(acc_full, 0)) { ok = false; atomicExch(err, 3); }
+    if (ok && !bar_wait(acc_full, 0)) { ok = false; report_error(err, 3); }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int q = warp & 3, half = warp >> 2;  // TMEM lane quarter of this warp, column half
     const int out_row = row0 + 32 * q + lane;
@@ -382,7 +382,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
     if (lane == 0) {
       for (int ms = 0; ms < nms; ++ms) {
         const int ps = ms % NPK;
-        if (ok && !bar_wait(&pk_empty[ps], (uint32_t)(((ms / NPK) & 1) ^ 1))) { ok = false; atomicExch(err, 3); }
+        if (ok && !bar_wait(&pk_empty[ps], (uint32_t)(((ms / NPK) & 1) ^ 1))) { ok = false; report_error(err, 3); }
         bar_expect(&pk_full[ps], BM * PITCH);
         // x in 32-bit elements; x*4 = ms*RB is a multiple of 16 bytes.  Rows past the end read as zero.
         asm volatile(
@@ -396,7 +396,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
     const uint32_t sb_u = __shfl_sync(0xffffffffu, s32(sB), 0);
     for (int ks = 0; ks < nk; ++ks) {
       const int s = ks % NB;
-      if (ok && !bar_wait(&empty_b[s], (uint32_t)(((ks / NB) & 1) ^ 1))) { ok = false; atomicExch(err, 3); }
+      if (ok && !bar_wait(&empty_b[s], (uint32_t)(((ks / NB) & 1) ^ 1))) { ok = false; report_error(err, 3); }
       if (elect_one()) {
         bar_expect(&full_b[s], BN * 128);
         asm volatile(
@@ -423,7 +423,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
       const uint32_t pa = (uint32_t)((ks / NA) & 1), pb = (uint32_t)((ks / NB) & 1);
       if (ok && !(U == 2 ? bar_wait4(&full_a[sa], pa, &full_b[sb], pb) : bar_wait2(&full_a[sa], pa, &full_b[sb], pb))) {
         ok = false;
-        atomicExch(err, 3);
+        report_error(err, 3);
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (elect_one()) {

@@ -138,6 +138,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
     if (lane == 0) {
       int c = 0;
       bool ok = true;
+      const uint64_t stream_once = l2_policy_evict_first();
       for (int ph = 0; ph < wk.n_phases; ++ph) {
         const ProgPhase P = wk.phases[ph];
         int lo, hi;
@@ -154,7 +155,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
             for (int tile = t0; tile < t1; ++tile) {
               for (int sub = 0; sub < nsub; ++sub, ++c) {
                 const int stage = c % NST;
-                if (ok && !mbar_wait(&empty[stage], (uint32_t)(((c / NST) & 1) ^ 1))) { ok = false; atomicExch(err, 1); }
+                if (ok && !mbar_wait(&empty[stage], (uint32_t)(((c / NST) & 1) ^ 1))) { ok = false; report_error(err, 1); }
                 const int64_t seg_off = ((int64_t)span * (SPAN / gm.kseg) + sub) * gm.segb;
                 const int64_t left = E.row_bytes - seg_off;
                 const uint32_t bytes = (uint32_t)(left < gm.segb ? left : gm.segb);
@@ -164,7 +165,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
                 const int last = E.rows - 1 - tile * 16;  // rows beyond the matrix refetch the last one
 #pragma unroll 4
                 for (int r = 0; r < 16; ++r)
-                  bulk_g2s(dst + r * gm.rs, src + (int64_t)min(r, last) * E.row_bytes, bytes, &full[stage]);
+                  bulk_g2s_hint(dst + r * gm.rs, src + (int64_t)min(r, last) * E.row_bytes, bytes, &full[stage], stream_once);
               }
             }
           }
@@ -192,7 +193,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
         for (int span = 0; span < n_span; ++span) {
           for (int tile = t0; tile < t1; ++tile, ++j) {
             const int rb = j % NRB;
-            if (ok && !mbar_wait(&rfull[rb], (uint32_t)((j / NRB) & 1))) { ok = false; if (lane == 0) atomicExch(err, 1); }
+            if (ok && !mbar_wait(&rfull[rb], (uint32_t)((j / NRB) & 1))) { ok = false; if (lane == 0) report_error(err, 1); }
             const float* rp0 = red + rb * CW * 16 * MT;
             for (int idx = lane; idx < 16 * MT; idx += 32) {
               const int r = idx / MT, k = idx % MT, row = tile * 16 + r;
@@ -238,7 +239,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           unsigned long long v;
           asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(counters + ph - 1) : "memory");
           if (v >= want) break;
-          if (++polls > POLL_LIMIT) { atomicExch(err, 2); break; }
+          if (++polls > POLL_LIMIT) { report_error(err, 2); break; }
           __nanosleep(polls < 8 ? 64 : 256);  // hundreds of CTAs poll one word: keep the L2 bank free for the adds
         }
       }
@@ -271,7 +272,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           for (int k = 0; k < MT; ++k) acc.mn[0][k] = acc.mn[1][k] = 0.f;
           for (int sub = 0; sub < nsub; ++sub, ++c) {
             const int stage = c % NST;
-            if (ok && !mbar_wait(&full[stage], (uint32_t)((c / NST) & 1))) { ok = false; if (lane == 0) atomicExch(err, 1); }
+            if (ok && !mbar_wait(&full[stage], (uint32_t)((c / NST) & 1))) { ok = false; if (lane == 0) report_error(err, 1); }
             const uint8_t* chunk = ring + stage * MAX_CHUNK;
             const uint8_t* rowA = chunk + g * gm.rs;
             const uint8_t* rowB = chunk + (g + 8) * gm.rs;
@@ -292,7 +293,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           }
           // ---- hand this warp's partial sums of the tile to the reducer ----
           const int rb = j % NRB;
-          if (ok && !mbar_wait(&rempty[rb], (uint32_t)(((j / NRB) & 1) ^ 1))) { ok = false; if (lane == 0) atomicExch(err, 1); }
+          if (ok && !mbar_wait(&rempty[rb], (uint32_t)(((j / NRB) & 1) ^ 1))) { ok = false; if (lane == 0) report_error(err, 1); }
           float* myred = red + (rb * CW + warp) * 16 * MT;
           if ((DTFIX >= 0 ? DTFIX : E.dtype) == DT_Q4_K) {
 #pragma unroll

@@ -11,6 +11,13 @@ namespace llr {
 
 // A resident packed matrix as the kernels see it.  `w` is 256-byte aligned and
 // the allocation is padded so that 16-byte windows around any row are readable.
+// Error word of an executor: one int in mapped pinned host memory.  A kernel whose bounded wait
+// ran out stores a non-zero code with a plain store (any writer wins); the host reads the word
+// after synchronizing, with no copy on the path.
+#ifdef __CUDACC__
+__device__ __forceinline__ void report_error(int* err, int code) { *(volatile int*)err = code; }
+#endif
+
 struct MatView {
   const uint8_t* w;
   int dtype;

@@ -53,6 +53,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* b, uint32_t parity) {
 }
 // untiled bulk copy global -> this CTA's shared memory; both addresses and the
 // size are multiples of 16 bytes (checked on the host before this kernel is chosen)
+// L2 policies: weights are read once per token and must not push the (tiny, re-read by every
+// CTA) activations out of L2; activations are kept.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void bulk_g2s_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy) : "memory");
+}
+// 16 bytes of activations, L2-coherent (ld.global.cg semantics: never from a stale L1 line), kept in L2
+__device__ __forceinline__ float4 ld_x_keep(const float4* p, uint64_t policy) {
+  float4 v;
+  asm volatile("ld.global.cg.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(policy) : "memory");
+  return v;
+}
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
@@ -250,6 +273,8 @@ __device__ __forceinline__ void split_activations(const float* __restrict__ X, i
                                                   float* xsi, int warp, int lane, bool coherent) {
   // two jobs per warp and pass: both loads are in flight before either is used
   const int njobs = nblk256 * tokens;
+  const uint64_t keep = l2_policy_evict_last();
+  (void)coherent;  // one load flavour: L2-coherent, kept in L2
   for (int job0 = warp; job0 < njobs; job0 += 2 * NWARP) {
    float4 pa[2], pb[2];
 #pragma unroll
@@ -257,8 +282,8 @@ __device__ __forceinline__ void split_activations(const float* __restrict__ X, i
     const int job = job0 + u * NWARP;
     if (job < njobs) {
       const float4* xp = (const float4*)(X + (int64_t)(job / nblk256) * cols + col0 + (job % nblk256) * 256 + 8 * lane);
-      pa[u] = coherent ? __ldcg(xp) : __ldg(xp);
-      pb[u] = coherent ? __ldcg(xp + 1) : __ldg(xp + 1);
+      pa[u] = ld_x_keep(xp, keep);
+      pb[u] = ld_x_keep(xp + 1, keep);
     }
    }
 #pragma unroll
