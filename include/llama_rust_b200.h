@@ -199,6 +199,34 @@ int llr_program_create(llr_exec* exec, const llr_program_entry* entries, size_t 
 int llr_program_run(llr_exec* exec, llr_program* program, void* stream);
 int llr_program_free(llr_program* program);
 
+/* ---- row-sharded programs across GPUs -------------------------------------------
+ * No counterpart in the reference (it runs on one device).  One process per GPU; rank g
+ * holds rows [g*rows/G, (g+1)*rows/G) of every matrix as its own resident matrix and a
+ * full-width copy of every result vector.  A sharded program is a program whose reducer
+ * also stores each finished value into the same place of every other rank's result
+ * buffer (peer stores over NVLink) and whose phase counters count the CTAs of all ranks,
+ * so the all-gather of result slices is part of the launch: no collective call between
+ * products.  All ranks must create the same program (same entries, phases and shard
+ * shapes) and run it the same number of times.
+ *
+ * Buffers the peers write live in one arena per rank: llr_shared_alloc returns zeroed
+ * device memory and a 64-byte handle another process opens with llr_shared_open (CUDA
+ * IPC).  The first LLR_ARENA_HEADER_BYTES of an arena belong to the library (phase
+ * counters: at most 8192 phases); result buffers lie behind it, at the same offsets on
+ * every rank.  y_dev of an entry points at this rank's slice inside its own arena;
+ * y_ld[i] is the distance in floats between consecutive activation rows of that result
+ * (the full row count; NULL: the shard's row count).  peer_arenas[g] is rank g's arena
+ * as opened here (the entry of this rank itself is ignored).  world is 2..8. */
+#define LLR_ARENA_HEADER_BYTES 65536
+typedef struct llr_ipc_handle { unsigned char bytes[64]; } llr_ipc_handle;
+int llr_shared_alloc(llr_exec* exec, size_t bytes, void** dev, llr_ipc_handle* handle);
+int llr_shared_open(llr_exec* exec, const llr_ipc_handle* handle, void** dev);
+int llr_shared_close(llr_exec* exec, void* dev);
+int llr_shared_free(llr_exec* exec, void* dev);
+int llr_program_create_sharded(llr_exec* exec, const llr_program_entry* entries, const uint64_t* y_ld,
+                               size_t n_entries, void* arena, size_t arena_bytes, uint32_t world,
+                               uint32_t rank, void* const* peer_arenas, llr_program** out);
+
 /* ---- routed-expert FFN layer ----------------------------------------------------
  * One mixture-of-experts FFN layer as the reference runs it [langtax/src/decode.rs:
  * softmax_routed_layer :9938 -> route_softmax_tokens :9969 (router product, softmax,

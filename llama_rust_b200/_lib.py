@@ -19,7 +19,10 @@ SYMBOLS = [
     "llr_gemm_resident", "llr_matmul", "llr_matmul_device", "llr_exec_synchronize",
     "llr_dequant_rows", "llr_matrix_synth", "llr_matrix_download", "llr_program_create",
     "llr_program_run", "llr_program_free", "llr_gemm_device_noalloc", "llr_moe_ffn",
+    "llr_shared_alloc", "llr_shared_open", "llr_shared_close", "llr_shared_free",
+    "llr_program_create_sharded",
 ]
+ARENA_HEADER_BYTES = 65536
 
 
 class Counters(C.Structure):
@@ -74,6 +77,12 @@ def load() -> C.CDLL:
     lib.llr_program_free.argtypes = [vp]
     lib.llr_gemm_device_noalloc.argtypes = [vp, vp, sz, vp, vp, vp]
     lib.llr_moe_ffn.argtypes = [vp, C.POINTER(MoeLayer), sz, vp, sz, vp, sz, vp, vp]
+    lib.llr_shared_alloc.argtypes = [vp, sz, C.POINTER(vp), C.c_char_p]
+    lib.llr_shared_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]
+    lib.llr_shared_close.argtypes = [vp, vp]
+    lib.llr_shared_free.argtypes = [vp, vp]
+    lib.llr_program_create_sharded.argtypes = [vp, C.POINTER(ProgramEntry), C.POINTER(C.c_uint64), sz, vp, sz,
+                                               C.c_uint32, C.c_uint32, C.POINTER(vp), C.POINTER(vp)]
     for s in SYMBOLS:
         if s != "llr_exec_last_error":
             getattr(lib, s).restype = C.c_int

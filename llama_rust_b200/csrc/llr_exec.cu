@@ -829,13 +829,13 @@ struct llr_program {
   llr::Program* prog;
 };
 
-int llr_program_create(llr_exec* e, const llr_program_entry* entries, size_t n, llr_program** out) {
-  if (!e) return LLR_ERR_INVALID;
-  if (!out) return fail(e, LLR_ERR_INVALID, "null output pointer");
-  *out = nullptr;
+namespace {
+// validation shared by the two ways of creating a program
+int program_entries(llr_exec* e, const llr_program_entry* entries, const uint64_t* y_ld, size_t n,
+                    std::vector<ProgEntry>* pe, std::vector<int>* phase) {
   if (!entries || n == 0 || n > (1u << 20)) return fail(e, LLR_ERR_INVALID, "a program needs 1..2^20 entries");
-  std::vector<ProgEntry> pe(n);
-  std::vector<int> phase(n);
+  pe->resize(n);
+  phase->resize(n);
   for (size_t i = 0; i < n; ++i) {
     const llr_program_entry& in = entries[i];
     int rc = check_matrix(e, in.matrix);
@@ -848,13 +848,121 @@ int llr_program_create(llr_exec* e, const llr_program_entry* entries, size_t n, 
     if (!prog_entry_supported(v))
       return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) +
                                           ": only Q4_K, Q6_K (cols % 2048 == 0) and Q8_0 with cols % 256 == 0 run in programs");
-    pe[i] = ProgEntry{v.w, in.x_dev, in.y_dev, v.row_bytes, (int)v.rows, (int)v.cols, v.dtype, (int)in.tokens, 0, 0};
-    phase[i] = (int)in.phase;
+    const int64_t ld = y_ld ? (int64_t)y_ld[i] : v.rows;
+    if (ld < v.rows) return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) + ": y_ld is smaller than the row count");
+    (*pe)[i] = ProgEntry{v.w, in.x_dev, in.y_dev, v.row_bytes, (int)v.rows, (int)v.cols, v.dtype, (int)in.tokens, 0, 0, ld};
+    (*phase)[i] = (int)in.phase;
   }
+  return LLR_OK;
+}
+}  // namespace
+
+int llr_program_create(llr_exec* e, const llr_program_entry* entries, size_t n, llr_program** out) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!out) return fail(e, LLR_ERR_INVALID, "null output pointer");
+  *out = nullptr;
+  std::vector<ProgEntry> pe;
+  std::vector<int> phase;
+  int rc = program_entries(e, entries, nullptr, n, &pe, &phase);
+  if (rc) return rc;
   DeviceGuard guard(e->device);
   llr::Program* prog = nullptr;
   std::string msg;
   cudaError_t ce = program_create(pe, phase, e->sm_count, &prog, &msg);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "program creation");
+  llr_program* p = new (std::nothrow) llr_program{e, prog};
+  if (!p) { program_destroy(prog); return fail(e, LLR_ERR_OOM, "host allocation failed"); }
+  *out = p;
+  return LLR_OK;
+}
+
+// ---------------------------------------------------------------- row-sharded programs
+int llr_shared_alloc(llr_exec* e, size_t bytes, void** dev, llr_ipc_handle* handle) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!dev || !handle || bytes == 0) return fail(e, LLR_ERR_INVALID, "shared allocation needs a size, an address slot and a handle slot");
+  static_assert(sizeof(cudaIpcMemHandle_t) == sizeof(llr_ipc_handle), "handle size");
+  DeviceGuard guard(e->device);
+  void* p = nullptr;
+  cudaError_t ce = cudaMalloc(&p, bytes);
+  if (ce == cudaSuccess) ce = cudaMemset(p, 0, bytes);
+  cudaIpcMemHandle_t h;
+  if (ce == cudaSuccess) ce = cudaIpcGetMemHandle(&h, p);
+  if (ce != cudaSuccess) {
+    if (p) cudaFree(p);
+    return fail_cuda(e, ce, "shared allocation");
+  }
+  std::memcpy(handle->bytes, &h, sizeof(h));
+  *dev = p;
+  return LLR_OK;
+}
+
+int llr_shared_open(llr_exec* e, const llr_ipc_handle* handle, void** dev) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!dev || !handle) return fail(e, LLR_ERR_INVALID, "null handle or address slot");
+  DeviceGuard guard(e->device);
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle->bytes, sizeof(h));
+  void* p = nullptr;
+  cudaError_t ce = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "opening a peer's shared allocation");
+  *dev = p;
+  return LLR_OK;
+}
+
+int llr_shared_close(llr_exec* e, void* dev) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!dev) return LLR_OK;
+  DeviceGuard guard(e->device);
+  cudaError_t ce = cudaIpcCloseMemHandle(dev);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "closing a peer's shared allocation");
+  return LLR_OK;
+}
+
+int llr_shared_free(llr_exec* e, void* dev) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!dev) return LLR_OK;
+  DeviceGuard guard(e->device);
+  cudaError_t ce = cudaFree(dev);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "freeing a shared allocation");
+  return LLR_OK;
+}
+
+int llr_program_create_sharded(llr_exec* e, const llr_program_entry* entries, const uint64_t* y_ld, size_t n,
+                               void* arena, size_t arena_bytes, uint32_t world, uint32_t rank,
+                               void* const* peer_arenas, llr_program** out) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!out) return fail(e, LLR_ERR_INVALID, "null output pointer");
+  *out = nullptr;
+  if (world < 2 || world > 8 || rank >= world || !arena || !peer_arenas || arena_bytes <= LLR_ARENA_HEADER_BYTES)
+    return fail(e, LLR_ERR_INVALID, "a sharded program needs 2..8 ranks, an arena larger than its header and the peers' arenas");
+  std::vector<ProgEntry> pe;
+  std::vector<int> phase;
+  int rc = program_entries(e, entries, y_ld, n, &pe, &phase);
+  if (rc) return rc;
+  const char* lo = (const char*)arena + LLR_ARENA_HEADER_BYTES;
+  const char* hi = (const char*)arena + arena_bytes;
+  int n_phases = 0;
+  for (size_t i = 0; i < n; ++i) {
+    const char* y0 = (const char*)pe[i].y;
+    const char* y1 = y0 + ((size_t)(pe[i].tokens - 1) * (size_t)pe[i].y_ld + (size_t)pe[i].rows) * sizeof(float);
+    if (y0 < lo || y1 > hi)
+      return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) + ": the result slice is outside the arena");
+    if (i == 0 || phase[i] != phase[i - 1]) ++n_phases;
+  }
+  if ((size_t)n_phases * sizeof(unsigned long long) > LLR_ARENA_HEADER_BYTES)
+    return fail(e, LLR_ERR_INVALID, "a sharded program has at most 8192 phases");
+  PeerTable pt{};
+  for (uint32_t g = 0; g < world; ++g) {
+    if (g == rank) continue;
+    if (!peer_arenas[g]) return fail(e, LLR_ERR_INVALID, "missing arena of rank " + std::to_string(g));
+    pt.counters[pt.n_peers] = (unsigned long long*)peer_arenas[g];
+    pt.y_delta[pt.n_peers] = (long long)((const char*)peer_arenas[g] - (const char*)arena);
+    ++pt.n_peers;
+  }
+  DeviceGuard guard(e->device);
+  llr::Program* prog = nullptr;
+  std::string msg;
+  cudaError_t ce = program_create_sharded(pe, phase, e->sm_count, (unsigned long long*)arena, pt, &prog, &msg);
   if (ce != cudaSuccess) return fail_cuda(e, ce, "program creation");
   llr_program* p = new (std::nothrow) llr_program{e, prog};
   if (!p) { program_destroy(prog); return fail(e, LLR_ERR_OOM, "host allocation failed"); }

@@ -34,6 +34,13 @@
 // adds one after its share of the phase is written and fenced, consumers poll
 // with acquire loads.  Activations written during the launch are read with
 // L2-coherent loads.
+//
+// Row-sharded program (one process per GPU, each with a row slice of every matrix):
+// the exchange of result slices is part of the kernel.  The reducer stores each
+// finished value into its own y and into the same place of every peer's y (plain
+// peer stores over NVLink), then adds to its own and to every peer's phase counter
+// with system-scope release; consumers acquire at system scope and wait for the
+// CTAs of all ranks.  No collective library call, no multicast, every wait bounded.
 #include <cuda_runtime.h>
 
 #include <new>
@@ -90,6 +97,7 @@ struct Work {
   const ProgEntry* entries;
   const ProgPhase* phases;
   int n_phases;
+  const PeerTable* peers;  // row-sharded programs only
 };
 
 // Tile range of this CTA inside a phase, and inside one entry of it.
@@ -106,7 +114,7 @@ __device__ __forceinline__ bool entry_range(const ProgEntry& E, int lo, int hi, 
 // DTFIX: the one format of a single-product launch (the other block routines are compiled
 // out, which keeps the consumers under the register budget of two CTAs per SM), or -1 for
 // programs, which switch per entry.
-template <int MT, bool PROGRAM, int DTFIX>
+template <int MT, bool PROGRAM, int DTFIX, bool PEERS = false>
 __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* counters,
                                             unsigned long long epoch, int* err) {
   using L = SLay<MT>;
@@ -201,8 +209,13 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
 #pragma unroll
               for (int w = 0; w < CW; ++w) v += rp0[w * 16 * MT + idx];
               if (row < E.rows && k < E.tokens) {
-                float* yp = E.y + (int64_t)k * E.rows + row;
-                *yp = span == 0 ? v : *yp + v;
+                float* yp = E.y + (int64_t)k * E.y_ld + row;
+                if (span != 0) v += *yp;
+                *yp = v;
+                if (PEERS && span == n_span - 1) {
+                  const int np = wk.peers->n_peers;
+                  for (int p = 0; p < np; ++p) *(float*)((char*)yp + wk.peers->y_delta[p]) = v;
+                }
               }
             }
             __syncwarp();
@@ -212,9 +225,20 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
       }
       if (PROGRAM) {
         // this CTA's share of the phase is written: publish it
-        __syncwarp();
-        if (lane == 0)  // release: the y values written above are visible before the count
-          asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(counters + ph), "l"(1ull) : "memory");
+        if (PEERS) {
+          __threadfence_system();  // every lane's peer stores are performed before lane 0 publishes
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(counters + ph), "l"(1ull) : "memory");
+            const int np = wk.peers->n_peers;
+            for (int p = 0; p < np; ++p)
+              asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(wk.peers->counters[p] + ph), "l"(1ull) : "memory");
+          }
+        } else {
+          __syncwarp();
+          if (lane == 0)  // release: the y values written above are visible before the count
+            asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(counters + ph), "l"(1ull) : "memory");
+        }
       }
     }
     return;
@@ -231,13 +255,18 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
     const ProgPhase P = wk.phases[ph];
     int lo, hi;
     phase_range(P, bid, nb, &lo, &hi);
-    if (PROGRAM && P.wait_prev && ph > 0) {
+    // a sharded program also holds back the first phase of a run until every rank has finished
+    // the previous run (its peers' stores into this rank's buffers belong to that run)
+    if (PROGRAM && ((P.wait_prev && ph > 0) || (PEERS && ph == 0))) {
       if (tid == 0) {
-        const unsigned long long want = epoch * (unsigned long long)nb;
+        const unsigned long long ranks = PEERS ? (unsigned long long)(wk.peers->n_peers + 1) : 1ull;
+        const unsigned long long want = (ph > 0 ? epoch : epoch - 1) * (unsigned long long)nb * ranks;
+        const unsigned long long* cp = counters + (ph > 0 ? ph - 1 : wk.n_phases - 1);
         int polls = 0;
         for (;;) {
           unsigned long long v;
-          asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(counters + ph - 1) : "memory");
+          if (PEERS) asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(cp) : "memory");
+          else asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cp) : "memory");
           if (v >= want) break;
           if (++polls > POLL_LIMIT) { report_error(err, 2); break; }
           __nanosleep(polls < 8 ? 64 : 256);  // hundreds of CTAs poll one word: keep the L2 bank free for the adds
@@ -337,7 +366,7 @@ gemv_stream_kernel(const __grid_constant__ ProgEntry one, int* __restrict__ err)
   __shared__ ProgPhase phase;
   if (threadIdx.x == 0) phase = ProgPhase{0, 1, one.n_tiles, 0};
   __syncthreads();
-  Work wk{&one, &phase, 1};
+  Work wk{&one, &phase, 1, nullptr};
   stream_body<MT, false, DT>(wk, nullptr, 0ull, err);
 }
 
@@ -345,8 +374,17 @@ template <int MT>
 __global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
 gemv_program_kernel(const ProgEntry* __restrict__ entries, const ProgPhase* __restrict__ phases, int n_phases,
                     unsigned long long* __restrict__ counters, unsigned long long epoch, int* __restrict__ err) {
-  Work wk{entries, phases, n_phases};
+  Work wk{entries, phases, n_phases, nullptr};
   stream_body<MT, true, -1>(wk, counters, epoch, err);
+}
+
+template <int MT>
+__global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
+gemv_sharded_program_kernel(const ProgEntry* __restrict__ entries, const ProgPhase* __restrict__ phases, int n_phases,
+                            unsigned long long* __restrict__ counters, unsigned long long epoch,
+                            const PeerTable* __restrict__ peers, int* __restrict__ err) {
+  Work wk{entries, phases, n_phases, peers};
+  stream_body<MT, true, -1, true>(wk, counters, epoch, err);
 }
 
 template <class K>
@@ -370,7 +408,7 @@ cudaError_t launch_single(const MatView& m, const float* x, float* y, int tokens
     cudaError_t e = occupancy(kern, smem, &blocks_per_sm);
     if (e != cudaSuccess) return e;
   }
-  ProgEntry E{m.w, x, y, m.row_bytes, (int)m.rows, (int)m.cols, m.dtype, tokens, 0, (int)((m.rows + 15) / 16)};
+  ProgEntry E{m.w, x, y, m.row_bytes, (int)m.rows, (int)m.cols, m.dtype, tokens, 0, (int)((m.rows + 15) / 16), m.rows};
   int grid = sm_count * blocks_per_sm;
   if (grid > E.n_tiles) grid = E.n_tiles;
   cudaLaunchAttribute attr;
@@ -427,14 +465,17 @@ struct Program {
   unsigned long long* d_counters = nullptr;
   int n_phases = 0, n_entries = 0, max_tokens = 1, grid = 0;
   unsigned long long epoch = 0;
+  PeerTable* d_peers = nullptr;   // sharded programs: the peer table, and the counters are not ours
+  bool own_counters = true;
 };
 
 bool prog_entry_supported(const MatView& m) { return gemv_mma_supported(m); }
 
 template <int MT>
-static cudaError_t prog_prepare(int sm_count, int* grid) {
+static cudaError_t prog_prepare(int sm_count, int* grid, bool sharded) {
   int bps = 0;
-  cudaError_t e = occupancy(gemv_program_kernel<MT>, SLay<MT>::TOTAL, &bps);
+  cudaError_t e = sharded ? occupancy(gemv_sharded_program_kernel<MT>, SLay<MT>::TOTAL, &bps)
+                          : occupancy(gemv_program_kernel<MT>, SLay<MT>::TOTAL, &bps);
   if (e != cudaSuccess) return e;
   *grid = sm_count * bps;
   return cudaSuccess;
@@ -449,14 +490,21 @@ static cudaError_t prog_launch(Program* p, cudaStream_t stream, int* err) {
   int np = p->n_phases;
   unsigned long long* dc = p->d_counters;
   unsigned long long ep = p->epoch;
-  void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dc, (void*)&ep, (void*)&err};
   // cooperative: every CTA must be resident, the phase counters are a grid-wide dependency
+  if (p->d_peers) {
+    const PeerTable* pt = p->d_peers;
+    void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dc, (void*)&ep, (void*)&pt, (void*)&err};
+    return cudaLaunchCooperativeKernel((const void*)gemv_sharded_program_kernel<MT>, dim3((unsigned)p->grid),
+                                       dim3(NTHREADS), args, SLay<MT>::TOTAL, stream);
+  }
+  void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dc, (void*)&ep, (void*)&err};
   return cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)p->grid), dim3(NTHREADS), args,
                                      SLay<MT>::TOTAL, stream);
 }
 
-cudaError_t program_create(const std::vector<ProgEntry>& entries_in, const std::vector<int>& phase_of,
-                           int sm_count, Program** out, std::string* msg) {
+static cudaError_t program_build(const std::vector<ProgEntry>& entries_in, const std::vector<int>& phase_of,
+                                 int sm_count, unsigned long long* shared_counters, const PeerTable* peers,
+                                 Program** out, std::string* msg) {
   Program* p = new (std::nothrow) Program();
   if (!p) return cudaErrorMemoryAllocation;
   std::vector<ProgEntry> entries = entries_in;
@@ -464,6 +512,7 @@ cudaError_t program_create(const std::vector<ProgEntry>& entries_in, const std::
   for (size_t i = 0; i < entries.size(); ++i) {
     ProgEntry& E = entries[i];
     E.n_tiles = (E.rows + 15) / 16;
+    if (E.y_ld == 0) E.y_ld = E.rows;
     if (i == 0 || phase_of[i] != phase_of[i - 1]) phases.push_back(ProgPhase{(int)i, 0, 0, i == 0 ? 0 : 1});
     ProgPhase& P = phases.back();
     E.tile_begin = P.n_tiles;
@@ -475,16 +524,24 @@ cudaError_t program_create(const std::vector<ProgEntry>& entries_in, const std::
   p->n_entries = (int)entries.size();
   cudaError_t e;
   const int mt = p->max_tokens;
-  if (mt == 1) e = prog_prepare<1>(sm_count, &p->grid);
-  else if (mt == 2) e = prog_prepare<2>(sm_count, &p->grid);
-  else if (mt <= 4) e = prog_prepare<4>(sm_count, &p->grid);
-  else e = prog_prepare<8>(sm_count, &p->grid);
+  const bool sharded = peers != nullptr;
+  if (mt == 1) e = prog_prepare<1>(sm_count, &p->grid, sharded);
+  else if (mt == 2) e = prog_prepare<2>(sm_count, &p->grid, sharded);
+  else if (mt <= 4) e = prog_prepare<4>(sm_count, &p->grid, sharded);
+  else e = prog_prepare<8>(sm_count, &p->grid, sharded);
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_entries, entries.size() * sizeof(ProgEntry));
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_phases, phases.size() * sizeof(ProgPhase));
-  if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_counters, phases.size() * sizeof(unsigned long long));
+  if (sharded) {
+    p->own_counters = false;
+    p->d_counters = shared_counters;  // zeroed by whoever allocated them, before any rank runs
+    if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_peers, sizeof(PeerTable));
+    if (e == cudaSuccess) e = cudaMemcpy(p->d_peers, peers, sizeof(PeerTable), cudaMemcpyHostToDevice);
+  } else {
+    if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_counters, phases.size() * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemset(p->d_counters, 0, phases.size() * sizeof(unsigned long long));
+  }
   if (e == cudaSuccess) e = cudaMemcpy(p->d_entries, entries.data(), entries.size() * sizeof(ProgEntry), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(p->d_phases, phases.data(), phases.size() * sizeof(ProgPhase), cudaMemcpyHostToDevice);
-  if (e == cudaSuccess) e = cudaMemset(p->d_counters, 0, phases.size() * sizeof(unsigned long long));
   if (e != cudaSuccess) {
     if (msg) *msg = cudaGetErrorString(e);
     program_destroy(p);
@@ -494,11 +551,23 @@ cudaError_t program_create(const std::vector<ProgEntry>& entries_in, const std::
   return cudaSuccess;
 }
 
+cudaError_t program_create(const std::vector<ProgEntry>& entries, const std::vector<int>& phase_of,
+                           int sm_count, Program** out, std::string* msg) {
+  return program_build(entries, phase_of, sm_count, nullptr, nullptr, out, msg);
+}
+
+cudaError_t program_create_sharded(const std::vector<ProgEntry>& entries, const std::vector<int>& phase_of,
+                                   int sm_count, unsigned long long* counters, const PeerTable& peers,
+                                   Program** out, std::string* msg) {
+  return program_build(entries, phase_of, sm_count, counters, &peers, out, msg);
+}
+
 void program_destroy(Program* p) {
   if (!p) return;
   if (p->d_entries) cudaFree(p->d_entries);
   if (p->d_phases) cudaFree(p->d_phases);
-  if (p->d_counters) cudaFree(p->d_counters);
+  if (p->d_counters && p->own_counters) cudaFree(p->d_counters);
+  if (p->d_peers) cudaFree(p->d_peers);
   delete p;
 }
 

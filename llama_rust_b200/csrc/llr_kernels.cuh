@@ -61,6 +61,15 @@ struct ProgEntry {
   int64_t row_bytes;
   int rows, cols, dtype, tokens;
   int tile_begin, n_tiles;
+  int64_t y_ld;  // floats between consecutive activation rows of y (0: rows); larger when y is a slice of a wider vector
+};
+// Row-sharded programs across GPUs: where the other ranks keep their copies of the results
+// and of the phase counters.  peer y address = local y address + y_delta[g] bytes.
+struct PeerTable {
+  int n_peers;  // other ranks (world size - 1), at most 7
+  int pad;
+  unsigned long long* counters[7];
+  long long y_delta[7];
 };
 struct ProgPhase { int first_entry, n_entries, n_tiles, wait_prev; };
 struct Program;
@@ -68,6 +77,11 @@ bool prog_entry_supported(const MatView& m);
 // phase_of[i] is non-decreasing; a change starts a phase that waits for the previous one
 cudaError_t program_create(const std::vector<ProgEntry>& entries, const std::vector<int>& phase_of,
                            int sm_count, Program** out, std::string* msg);
+// Same, for one rank of a row-sharded program: `counters` (one per phase, zeroed, in memory the
+// peers can write) replaces the program's own counter array, `peers` says where the others are.
+cudaError_t program_create_sharded(const std::vector<ProgEntry>& entries, const std::vector<int>& phase_of,
+                                   int sm_count, unsigned long long* counters, const PeerTable& peers,
+                                   Program** out, std::string* msg);
 void program_destroy(Program* p);
 cudaError_t program_run(Program* p, cudaStream_t stream, int* err_flag, uint64_t* launches);
 int program_phases(const Program* p);

@@ -184,6 +184,39 @@ class Executor:
         self._check(lib().llr_program_create(self._h, arr, len(entries), C.byref(h)))
         return Program(self, h.value, len(entries))
 
+    # -- row-sharded programs across GPUs (llr_shared_*, llr_program_create_sharded) ----
+    def shared_alloc(self, nbytes: int) -> tuple[int, bytes]:
+        """Zeroed device memory that other processes can open: (device address, 64-byte handle)."""
+        dev = C.c_void_p()
+        handle = C.create_string_buffer(64)
+        self._check(lib().llr_shared_alloc(self._h, nbytes, C.byref(dev), handle))
+        return dev.value, handle.raw
+
+    def shared_open(self, handle: bytes) -> int:
+        dev = C.c_void_p()
+        self._check(lib().llr_shared_open(self._h, handle, C.byref(dev)))
+        return dev.value
+
+    def shared_close(self, dev: int) -> None:
+        self._check(lib().llr_shared_close(self._h, dev))
+
+    def shared_free(self, dev: int) -> None:
+        self._check(lib().llr_shared_free(self._h, dev))
+
+    def sharded_program(self, entries, y_ld, arena: int, arena_bytes: int, world: int, rank: int, peer_arenas) -> Program:
+        """entries as for program(); y_ld[i] = full row count of result i; peer_arenas[g] = rank g's arena
+        as opened in this process (own slot ignored)."""
+        entries = list(entries)
+        arr = (_lib.ProgramEntry * len(entries))()
+        for i, (m, x, y, tokens, phase) in enumerate(entries):
+            arr[i] = _lib.ProgramEntry(m._h, x, y, tokens, phase)
+        ld = (C.c_uint64 * len(entries))(*[int(v) for v in y_ld])
+        peers = (C.c_void_p * world)(*[int(p) if p else None for p in peer_arenas])
+        h = C.c_void_p()
+        self._check(lib().llr_program_create_sharded(self._h, arr, ld, len(entries), arena, arena_bytes, world, rank,
+                                                     peers, C.byref(h)))
+        return Program(self, h.value, len(entries))
+
     def moe_ffn(self, router: Matrix, gate, up, down, n_used: int, norm_w: bool, x):
         """One routed-expert FFN layer (llr_moe_ffn).  Returns (out, sel_ids, sel_w)."""
         n_expert = len(gate)

@@ -14,6 +14,11 @@ The reference has no multi-device execution (its only notions are simulated:
 
 The compute is a callable, so the same code runs on NCCL with the CUDA executor and on
 gloo with any CPU stand-in (that is how the host logic is tested without GPUs).
+
+`ShardedDecodeProgram` is the path that matters for decode: the exchange of result slices is
+done by the kernel itself (peer stores + phase counters counted over all ranks), one launch
+per rank and step, no collective call between products.  torch.distributed only carries
+the 64-byte memory handles at set-up time.
 """
 from __future__ import annotations
 
@@ -127,3 +132,63 @@ class ExpertParallelFFN:
             idx = rows_of_tok[:, j]
             out = out + y_rows[idx] * w_sorted[idx].unsqueeze(1)
         return out
+
+
+def arena_layout(row_counts: Sequence[int], tokens: int = 1) -> tuple[list[int], int]:
+    """Byte offsets of the full-width result buffers inside a rank's arena (behind the library's
+    header, 256-byte aligned) and the arena size.  Identical on every rank."""
+    from ._lib import ARENA_HEADER_BYTES
+    offs, cur = [], ARENA_HEADER_BYTES
+    for rows in row_counts:
+        offs.append(cur)
+        cur += (4 * rows * tokens + 255) // 256 * 256
+    return offs, cur
+
+
+class ShardedDecodeProgram:
+    """One decode step of row-sharded products as a single launch per rank.
+
+    specs: list of (shard_matrix, x, full_rows, phase) in execution order; shard_matrix is this
+    rank's resident row slice (rows = full_rows / world); x is a device address, or a callable
+    taking the arena's base address (for an input that is an earlier result: arena + its offset
+    from arena_layout).  Result i lives full width in every
+    rank's arena at `self.y_ptr(i)`; after `run()` + a device synchronize on EVERY rank and a host
+    barrier it holds the complete vector on every rank."""
+
+    def __init__(self, ex, specs, tokens: int = 1, group=None):
+        self.ex, self.group = ex, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.offsets, self.arena_bytes = arena_layout([s[2] for s in specs], tokens)
+        self.arena, handle = ex.shared_alloc(self.arena_bytes)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle, group=group)
+        self.peers = [None if g == self.rank else ex.shared_open(handles[g]) for g in range(self.world)]
+        entries, y_ld = [], []
+        for (mat, x_ptr, full_rows, phase), off in zip(specs, self.offsets):
+            r0, r1 = row_range(full_rows, self.world, self.rank)
+            if r1 - r0 != mat.rows:
+                raise ValueError(f"shard has {mat.rows} rows, rank {self.rank} of {self.world} owns {r1 - r0} of {full_rows}")
+            if callable(x_ptr):
+                x_ptr = x_ptr(self.arena)
+            entries.append((mat, x_ptr, self.arena + off + 4 * r0, tokens, phase))
+            y_ld.append(full_rows)
+        self.program = ex.sharded_program(entries, y_ld, self.arena, self.arena_bytes, self.world, self.rank, self.peers)
+        dist.barrier(group=group)  # every rank has opened every arena before anybody runs
+
+    def y_ptr(self, i: int) -> int:
+        return self.arena + self.offsets[i]
+
+    def run(self, stream: int = 0) -> None:
+        self.program.run(stream)
+
+    def close(self) -> None:
+        if self.program is not None:
+            self.ex.synchronize()
+            dist.barrier(group=self.group)  # nobody still stores into an arena that is about to go
+            self.program.free()
+            self.program = None
+            for p in self.peers:
+                if p:
+                    self.ex.shared_close(p)
+            dist.barrier(group=self.group)
+            self.ex.shared_free(self.arena)

@@ -1,0 +1,110 @@
+"""Row-sharded programs on two GPUs (one process per GPU): the reducer's peer stores and the
+phase counters counted over both ranks replace the all-gather.  Every rank must end up with
+the complete result vectors, bit-identical to the unsharded program on one GPU, also for
+phases whose input is a vector that the other rank helped to write.  Skipped with fewer than
+two GPUs.  The control plane (exchange of memory handles, barriers) is a gloo group."""
+import ctypes as C
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+Q4_K, Q6_K, Q8_0 = 17, 19, 13
+SHAPES = [  # name, dtype, full rows, cols, phase, input (None = x0)
+    ("a", Q4_K, 2048, 1024, 0, None), ("b", Q8_0, 1024, 1024, 0, None),
+    ("c", Q6_K, 512, 2048, 1, "a"),
+    ("d", Q4_K, 1024, 512, 2, "c"), ("e", Q8_0, 256, 512, 2, "c"),
+]
+
+
+def _d2h(ptr, n_floats):
+    rt = C.CDLL("libcudart.so.12")
+    rt.cudaMemcpy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+    out = np.empty(n_floats, np.float32)
+    assert rt.cudaMemcpy(out.ctypes.data, ptr, 4 * n_floats, 2) == 0
+    return out
+
+
+def _worker(rank, world, port, tokens, ret):
+    try:
+        import torch
+        import torch.distributed as dist
+        from llama_rust_b200 import Executor, synth
+        from llama_rust_b200.sharding import ShardedDecodeProgram, shard_packed
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        torch.cuda.set_device(rank)
+        ex = Executor(rank)
+        packed = {n: synth.packed_matrix(dt, rows, cols, 900 + i) for i, (n, dt, rows, cols, _, _) in enumerate(SHAPES)}
+        x0 = torch.from_numpy(synth.activations(tokens * 1024, 7).reshape(tokens, 1024) * np.float32(0.05)).cuda()
+        # unsharded reference on this GPU
+        full = {n: ex.upload(dt, rows, cols, packed[n]) for n, dt, rows, cols, _, _ in SHAPES}
+        ref = {n: torch.full((tokens, rows), float("nan"), device="cuda") for n, _, rows, _, _, _ in SHAPES}
+        prog1 = ex.program([(full[n], (x0 if src is None else ref[src]).data_ptr(), ref[n].data_ptr(), tokens, ph)
+                            for n, _, _, _, ph, src in SHAPES])
+        # sharded
+        shards = {}
+        for n, dt, rows, cols, _, _ in SHAPES:
+            b, r = shard_packed(packed[n], rows, world, rank)
+            shards[n] = ex.upload(dt, r, cols, np.ascontiguousarray(b))
+        idx = {n: i for i, (n, *_rest) in enumerate(SHAPES)}
+        from llama_rust_b200.sharding import arena_layout
+        offs, _ = arena_layout([rows for _, _, rows, _, _, _ in SHAPES], tokens)
+        # inputs: x0, or the producing entry's full-width buffer in the local arena
+        specs2 = [(shards[n], (lambda arena, src=src: x0.data_ptr() if src is None else arena + offs[idx[src]]), rows, ph)
+                  for n, _, rows, _, ph, src in SHAPES]
+        sp = ShardedDecodeProgram(ex, specs2, tokens)
+        stream = torch.cuda.Stream()
+        ok = True
+        for run in range(3):
+            x0.copy_(torch.from_numpy(synth.activations(tokens * 1024, 7 + run).reshape(tokens, 1024) * np.float32(0.05)))
+            torch.cuda.synchronize()
+            dist.barrier()
+            prog1.run(stream.cuda_stream)
+            sp.run(stream.cuda_stream)
+            ex.synchronize()
+            stream.synchronize()
+            dist.barrier()  # the other rank's stores into this arena are complete as well
+            for i, (n, _, rows, _, _, _) in enumerate(SHAPES):
+                got = _d2h(sp.y_ptr(i), tokens * rows)
+                want = ref[n].cpu().numpy().reshape(-1)
+                if not np.array_equal(got, want):
+                    ok = False
+                    ret[rank] = f"run {run} result {n}: {int((got != want).sum())} of {got.size} differ"
+                    break
+            if not ok:
+                break
+        sp.close()
+        prog1.free()
+        ex.close()
+        dist.destroy_process_group()
+        if ok:
+            ret[rank] = "ok"
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
+
+
+@pytest.mark.parametrize("tokens", [1, 3])
+def test_sharded_program_equals_unsharded_on_every_rank(tokens):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, tokens, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert dict(ret) == {0: "ok", 1: "ok"}, dict(ret)
