@@ -205,6 +205,19 @@ def run_ours(args):
     # lm_head; a phase starts only when the previous one is completely written.
     PHASE = {"attn_q": 0, "attn_k": 0, "attn_v": 0, "attn_output": 1, "ffn_gate": 2, "ffn_up": 2, "ffn_down": 3}
     prog = None
+    sharded = None
+    if world > 1 and args.mode == "program":
+        # Row-sharded program: one launch per rank and step; the reducer warps store their result
+        # slices into every rank's full-width result buffers and the phase counters count the CTAs
+        # of all ranks, so there is no collective call inside a step.
+        from llama_rust_b200.sharding import ShardedDecodeProgram
+        specs = []
+        for i, (name, dt, rows, cols, rs, m, x, y, yfull) in enumerate(mats):
+            parts = name.split(".")
+            phase = 4 * int(parts[1]) + PHASE[parts[2]] if parts[0] == "blk" else 4 * N_LAYER
+            specs.append((m, x.data_ptr(), rows, phase))
+        sharded = ShardedDecodeProgram(ex, specs, M)
+        prog = sharded.program
     if world == 1 and args.mode == "program":
         entries = []
         for i, (name, dt, rows, cols, rs, m, x, y, yfull) in enumerate(mats):
@@ -219,7 +232,7 @@ def run_ours(args):
             return
         for i, (name, dt, rows, cols, rs, m, x, y, yfull) in enumerate(mats):
             ex.matmul_device(m, M, x.data_ptr(), y.data_ptr(), sptr)
-            if world > 1:
+            if world > 1:  # --mode calls: the library baseline, a NCCL all-gather after every product
                 with torch.cuda.stream(stream):
                     dist.all_gather_into_tensor(yfull, y)
 
@@ -272,7 +285,7 @@ def run_ours(args):
     peak, peak_kind = load_peaks()
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "kernel": "gemv_mma_kernel<Q4_K, M>", "peak_kind": peak_kind,
+                "traffic": None, "kernel": "gemv_stream_kernel<M, Q4_K>", "peak_kind": peak_kind,
                 "launches_timed": reps * len(dom), "avg_launch_us": dom_ms * 1e3 / (reps * len(dom)),
                 "avg_bytes_per_launch": dom_bytes / (reps * len(dom)), "frac_of_8tbs_nominal": achieved / 8000.0}
 
@@ -305,6 +318,42 @@ def run_ours(args):
                "ms_per_step": dt_s * 1e3, "tok_s": M / dt_s,
                "api": "llr_gemm_resident with pinned host buffers: H2D x, kernel, D2H y, synchronize per matmul (225 per step)"}
 
+    if world > 1 and sharded is not None:
+        # end to end at N GPUs through the program API: per step every input vector goes host -> device,
+        # one sharded program launch per rank, every full-width result comes device -> host, synchronize
+        import ctypes as C
+        rt = C.CDLL("libcudart.so.12")
+        rt.cudaMemcpyAsync.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
+        hx = torch.randn(sum(M * cols for _, _, _, cols, *_ in mats)).pin_memory()
+        hy = torch.empty((sharded.arena_bytes - sharded.offsets[0]) // 4).pin_memory()
+        xoff, cur = [], 0
+        for _, _, _, cols, *_ in mats:
+            xoff.append(cur)
+            cur += M * cols
+
+        def e2e_step():
+            for (name, dt, rows, cols, rs, m, x, *_), off in zip(mats, xoff):
+                assert rt.cudaMemcpyAsync(x.data_ptr(), hx.data_ptr() + 4 * off, 4 * M * cols, 1, sptr) == 0
+            prog.run(sptr)
+            assert rt.cudaMemcpyAsync(hy.data_ptr(), sharded.arena + sharded.offsets[0], 4 * hy.numel(), 2, sptr) == 0
+            stream.synchronize()
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        n_e2e = max(2, min(args.steps, 10))
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            e2e_step()
+        barrier()
+        dt_s = (time.perf_counter() - t0) / n_e2e
+        tt = torch.tensor([dt_s], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt_s = float(tt.item())
+        e2e = {"value": total_bytes / dt_s / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": world * 4 * hx.numel(), "d2h_bytes_per_step": world * 4 * hy.numel(),
+               "ms_per_step": dt_s * 1e3, "tok_s": M / dt_s,
+               "api": "per rank and step: 225 pinned-host input vectors H2D, llr_program_run (sharded), all full-width results D2H, synchronize"}
+
     out = None
     if rank == 0:
         cpu = cpu_sweep(0, seconds_budget=15.0) if world == 1 and not args.no_cpu else None
@@ -312,12 +361,16 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "m": M, "launch": "one persistent program launch per step, 129 dependent phases" if prog is not None else "one PDL launch per matmul", "l2": "inputs larger than L2: every step streams 4.9 GB of distinct weights",
-                       "parallelism": f"rows/{world} per GPU + NCCL all-gather of output slices" if world > 1 else "single GPU"},
+            "config": {"workload": WORKLOAD, "m": M, "launch": ("one persistent program launch per rank and step, 129 dependent phases" if prog is not None else "one PDL launch per matmul"), "l2": "inputs larger than L2: every step streams 4.9 GB of distinct weights",
+                       "parallelism": ("single GPU" if world == 1 else
+                                       f"rows/{world} per GPU; result slices exchanged inside the kernel (peer stores + phase counters over all ranks)"
+                                       if sharded is not None else f"rows/{world} per GPU + NCCL all-gather of output slices after every product")},
             "tok_s": M / (ms_step * 1e-3), "frac_of_measured_hbm": value / peak, "frac_of_8tbs_nominal": value / 8000.0,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_rec,
         }
         print(json.dumps(out))
+    if sharded is not None:
+        sharded.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -212,7 +212,7 @@ int llr_program_free(llr_program* program);
  * Buffers the peers write live in one arena per rank: llr_shared_alloc returns zeroed
  * device memory and a 64-byte handle another process opens with llr_shared_open (CUDA
  * IPC).  The first LLR_ARENA_HEADER_BYTES of an arena belong to the library (phase
- * counters: at most 8192 phases); result buffers lie behind it, at the same offsets on
+ * counters: at most 4096 phases); result buffers lie behind it, at the same offsets on
  * every rank.  y_dev of an entry points at this rank's slice inside its own arena;
  * y_ld[i] is the distance in floats between consecutive activation rows of that result
  * (the full row count; NULL: the shard's row count).  peer_arenas[g] is rank g's arena

@@ -949,8 +949,7 @@ int llr_program_create_sharded(llr_exec* e, const llr_program_entry* entries, co
       return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) + ": the result slice is outside the arena");
     if (i == 0 || phase[i] != phase[i - 1]) ++n_phases;
   }
-  if ((size_t)n_phases * sizeof(unsigned long long) > LLR_ARENA_HEADER_BYTES)
-    return fail(e, LLR_ERR_INVALID, "a sharded program has at most 8192 phases");
+  if (n_phases > 4096) return fail(e, LLR_ERR_INVALID, "a sharded program has at most 4096 phases");
   PeerTable pt{};
   for (uint32_t g = 0; g < world; ++g) {
     if (g == rank) continue;

@@ -38,9 +38,10 @@
 // Row-sharded program (one process per GPU, each with a row slice of every matrix):
 // the exchange of result slices is part of the kernel.  The reducer stores each
 // finished value into its own y and into the same place of every peer's y (plain
-// peer stores over NVLink), then adds to its own and to every peer's phase counter
-// with system-scope release; consumers acquire at system scope and wait for the
-// CTAs of all ranks.  No collective library call, no multicast, every wait bounded.
+// peer stores over NVLink) and counts on its own rank's phase counter; the CTA that
+// completes the local count sends one system-scope release add to every peer.
+// Consumers wait for the local count and for one arrival per peer.  No collective
+// library call, no multicast, every wait bounded.
 #include <cuda_runtime.h>
 
 #include <new>
@@ -60,6 +61,9 @@ constexpr int NRB = 4;                    // reduction buffers
 constexpr int MAX_CHUNK = Lay<DT_Q4_K, 1>::CHUNK;
 static_assert(Lay<DT_Q6_K, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q8_0, 1>::CHUNK <= MAX_CHUNK, "ring stage");
 constexpr int POLL_LIMIT = 1 << 20;
+// Sharded programs keep two counter arrays in the arena header: [0, 4096) this rank's CTAs per
+// phase, [4096, 8192) arrivals of the peers per phase.
+constexpr int PEER_COUNTER_OFFSET = 4096;
 
 template <int MT> struct SLay {
   static constexpr int NT = (MT + 1) / 2;
@@ -226,13 +230,20 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
       if (PROGRAM) {
         // this CTA's share of the phase is written: publish it
         if (PEERS) {
+          // One signal per rank and phase crosses NVLink, not one per CTA (hundreds of remote atomics
+          // on one word serialise at tens of nanoseconds each): CTAs count locally, and the CTA
+          // that completes the local count tells every peer.
           __threadfence_system();  // every lane's peer stores are performed before lane 0 publishes
           __syncwarp();
           if (lane == 0) {
-            asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(counters + ph), "l"(1ull) : "memory");
-            const int np = wk.peers->n_peers;
-            for (int p = 0; p < np; ++p)
-              asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(wk.peers->counters[p] + ph), "l"(1ull) : "memory");
+            unsigned long long old;
+            asm volatile("atom.acq_rel.gpu.global.add.u64 %0, [%1], %2;" : "=l"(old) : "l"(counters + ph), "l"(1ull) : "memory");
+            if (old + 1 == epoch * (unsigned long long)nb) {  // the release of the add below is cumulative
+              const int np = wk.peers->n_peers;
+              for (int p = 0; p < np; ++p)
+                asm volatile("red.release.sys.global.add.u64 [%0], %1;"
+                             ::"l"(wk.peers->counters[p] + PEER_COUNTER_OFFSET + ph), "l"(1ull) : "memory");
+            }
           }
         } else {
           __syncwarp();
@@ -259,15 +270,19 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
     // the previous run (its peers' stores into this rank's buffers belong to that run)
     if (PROGRAM && ((P.wait_prev && ph > 0) || (PEERS && ph == 0))) {
       if (tid == 0) {
-        const unsigned long long ranks = PEERS ? (unsigned long long)(wk.peers->n_peers + 1) : 1ull;
-        const unsigned long long want = (ph > 0 ? epoch : epoch - 1) * (unsigned long long)nb * ranks;
-        const unsigned long long* cp = counters + (ph > 0 ? ph - 1 : wk.n_phases - 1);
+        const unsigned long long runs = ph > 0 ? epoch : epoch - 1;
+        const unsigned long long want = runs * (unsigned long long)nb;
+        const int dep = ph > 0 ? ph - 1 : wk.n_phases - 1;
+        const unsigned long long* cp = counters + dep;
+        // sharded: also one arrival per peer and run on this rank's copy of the peers' counter
+        const unsigned long long want_peers = PEERS ? runs * (unsigned long long)wk.peers->n_peers : 0ull;
+        const unsigned long long* pp = counters + PEER_COUNTER_OFFSET + dep;
         int polls = 0;
         for (;;) {
-          unsigned long long v;
-          if (PEERS) asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(cp) : "memory");
-          else asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cp) : "memory");
-          if (v >= want) break;
+          unsigned long long v, u = want_peers;
+          asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cp) : "memory");
+          if (PEERS) asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(u) : "l"(pp) : "memory");
+          if (v >= want && u >= want_peers) break;
           if (++polls > POLL_LIMIT) { report_error(err, 2); break; }
           __nanosleep(polls < 8 ? 64 : 256);  // hundreds of CTAs poll one word: keep the L2 bank free for the adds
         }
