@@ -233,7 +233,10 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           // One signal per rank and phase crosses NVLink, not one per CTA (hundreds of remote atomics
           // on one word serialise at tens of nanoseconds each): CTAs count locally, and the CTA
           // that completes the local count tells every peer.
-          __threadfence_system();  // every lane's peer stores are performed before lane 0 publishes
+          // Ordering: the lanes' peer stores -> __syncwarp -> lane 0's gpu-scope release on the
+          // local counter -> (last CTA) acquire of everybody's releases -> system-scope release
+          // to the peers.  Releases are cumulative, so one system-scope fence per rank and phase
+          // (inside the last CTA's red.release.sys) covers every CTA's peer stores.
           __syncwarp();
           if (lane == 0) {
             unsigned long long old;
