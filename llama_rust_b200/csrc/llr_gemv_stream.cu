@@ -265,10 +265,21 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
   const float* cur_x = nullptr;
   int cur_cols = -1, cur_span = -1, cur_tokens = -1;
   bool produced_here = false;
+  // Programs: the entries of a phase are fetched into shared memory before the dependency
+  // wait, so that after the wait the consumers do not pay a global-memory round trip for them.
+  static_assert(sizeof(ProgEntry) == 64, "entry copy below moves eight 8-byte words per entry");
+  constexpr int ENT_CACHE = 4;
+  __shared__ unsigned long long s_ent[2][ENT_CACHE][8];
   for (int ph = 0; ph < wk.n_phases; ++ph) {
     const ProgPhase P = wk.phases[ph];
     int lo, hi;
     phase_range(P, bid, nb, &lo, &hi);
+    const int n_cached = PROGRAM ? min(P.n_entries, ENT_CACHE) : 0;
+    if (PROGRAM && warp == 0) {
+      const unsigned long long* src = (const unsigned long long*)(wk.entries + P.first_entry);
+      if (lane < 8 * n_cached) s_ent[ph & 1][lane >> 3][lane & 7] = __ldg(src + lane);
+    }
+    if (PROGRAM && !((P.wait_prev && ph > 0) || (PEERS && ph == 0))) consumer_sync();  // publish the cached entries
     // a sharded program also holds back the first phase of a run until every rank has finished
     // the previous run (its peers' stores into this rank's buffers belong to that run)
     if (PROGRAM && ((P.wait_prev && ph > 0) || (PEERS && ph == 0))) {
@@ -295,7 +306,9 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
       cur_x = nullptr;  // the same buffer may hold new values now
     }
     for (int ei = 0; ei < P.n_entries && lo < hi; ++ei) {
-      const ProgEntry E = wk.entries[P.first_entry + ei];
+      ProgEntry E;
+      if (ei < n_cached) E = *(const ProgEntry*)&s_ent[ph & 1][ei][0];
+      else E = wk.entries[P.first_entry + ei];
       int t0, t1;
       if (!entry_range(E, lo, hi, &t0, &t1)) continue;
       const Geom gm = geom_of(DTFIX >= 0 ? DTFIX : E.dtype);

@@ -1,7 +1,15 @@
-// Device building blocks shared by the integer tensor-core decode kernels
-// (llr_gemv_mma.cu: one matrix per launch; llr_gemv_prog.cu: a whole list of
-// matrix products per launch): shared-memory geometry, TMA / mbarrier / mma.sync
-// wrappers, the per-format block routines and the activation digit split.
+// Device building blocks of the integer tensor-core decode kernels (llr_gemv_stream.cu):
+// shared-memory geometry, TMA / mbarrier / mma.sync wrappers, the per-format block routines
+// and the activation digit split.
+//
+// Arithmetic.  Per 256-column block an activation row is scaled by a power of two so that the
+// block maximum lands in [2^29, 2^30) and rounded to an integer X; X is written as four signed
+// base-256 digits, X = d0 + 256 d1 + 256^2 d2 + 256^3 d3 with d in [-128, 127]: the digits are
+// simply the bytes of (X + 0x80808080) ^ 0x80808080.  Each digit plane is an int8 B operand
+// of mma.sync, the quants are the A operand, the int32 sums are exact, sub-block scales are
+// folded in with integer multiply-adds, and one int->float conversion plus one FMA per (row,
+// super-block, digit) applies d * 2^-e * 256^p.  The conversion rounds once when a sum exceeds
+// 2^24 (relative 2^-25), everything before it is exact.
 #pragma once
 #include "llr_formats.cuh"
 
@@ -158,7 +166,7 @@ __device__ __forceinline__ void block_q4k(const uint8_t* rowA, const uint8_t* ro
   const float dA = h2f(hA.x & 0xffffu), dminA = h2f(hA.x >> 16);
   const float dB = h2f(hB.x & 0xffffu), dminB = h2f(hB.x >> 16);
   // columns 2t, 2t+1 of an n-tile are activation row (t >> 1), digits 2(t&1) and 2(t&1)+1
-  const float pw0 = (t & 1) ? 16384.f : 1.f, pw1 = pw0 * 128.f;
+  const float pw0 = (t & 1) ? 65536.f : 1.f, pw1 = pw0 * 256.f;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int tok = 2 * nt + (t >> 1);
@@ -225,7 +233,7 @@ __device__ __forceinline__ void block_q6k(const uint8_t* rowA, const uint8_t* ro
     }
   }
   const float dA = h2f(pA[208] | (pA[209] << 8)), dB = h2f(pB[208] | (pB[209] << 8));
-  const float pw0 = (t & 1) ? 16384.f : 1.f, pw1 = pw0 * 128.f;
+  const float pw0 = (t & 1) ? 65536.f : 1.f, pw1 = pw0 * 256.f;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int tok = 2 * nt + (t >> 1);
@@ -248,7 +256,7 @@ __device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* ro
   const bool odd = (b & 1) == 0;  // quants start at 34 b + 2: 4-byte aligned for odd b only
   const uint2 wA = lds64_a2(pA + 2 + 8 * t, odd), wB = lds64_a2(pB + 2 + 8 * t, odd);
   const float dA = h2f(*(const uint16_t*)pA), dB = h2f(*(const uint16_t*)pB);
-  const float pw0 = (t & 1) ? 16384.f : 1.f, pw1 = pw0 * 128.f;
+  const float pw0 = (t & 1) ? 65536.f : 1.f, pw1 = pw0 * 256.f;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const uint2 bd = *(const uint2*)(dig + (size_t)(nt * 8 + g) * DS + c32 * 32 + 8 * t);
@@ -307,21 +315,28 @@ __device__ __forceinline__ void split_activations(const float* __restrict__ X, i
     const int be = (int)((__float_as_uint(m) >> 23) & 0xff);
     float s = 0.f, sinv = 0.f;  // an all-zero (or denormal) block contributes nothing
     if (be != 0 && !bad) {
-      int e = 26 - (be - 127);
+      int e = 29 - (be - 127);
       e = e > 126 ? 126 : e;
       s = __uint_as_float((uint32_t)(e + 127) << 23);
       sinv = __uint_as_float((uint32_t)(127 - e) << 23);
     }
-    uint32_t pk[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};
+    // digits of a value = bytes of (X + 0x80808080) ^ 0x80808080; a 4 x 4 byte transpose (eight
+    // byte permutes) turns four values into one word per digit plane
+    uint32_t pk[4][2];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      int xi = bad ? 0 : __float2int_rn(v[j] * s);
+    for (int hq = 0; hq < 2; ++hq) {
+      uint32_t D[4];
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        const int d = p < 3 ? (((xi + 64) & 127) - 64) : xi;
-        xi = (xi - d) >> 7;
-        pk[p][j >> 2] |= (uint32_t)(d & 255) << (8 * (j & 3));
+      for (int j = 0; j < 4; ++j) {
+        const int xi = bad ? 0 : __float2int_rn(v[4 * hq + j] * s);
+        D[j] = ((uint32_t)xi + 0x80808080u) ^ 0x80808080u;
       }
+      const uint32_t t0 = __byte_perm(D[0], D[1], 0x5140), t1 = __byte_perm(D[2], D[3], 0x5140);
+      const uint32_t t2 = __byte_perm(D[0], D[1], 0x7362), t3 = __byte_perm(D[2], D[3], 0x7362);
+      pk[0][hq] = __byte_perm(t0, t1, 0x5410);
+      pk[1][hq] = __byte_perm(t0, t1, 0x7632);
+      pk[2][hq] = __byte_perm(t2, t3, 0x5410);
+      pk[3][hq] = __byte_perm(t2, t3, 0x7632);
     }
     const int nt = tok >> 1, plane0 = (tok & 1) * 4;
 #pragma unroll
