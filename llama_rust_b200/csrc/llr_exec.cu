@@ -14,6 +14,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
+#include <atomic>
 #include <cstring>
 #include <list>
 #include <new>
@@ -114,11 +115,20 @@ struct llr_exec {
   int path = PATH_AUTO;
   int* err_flag = nullptr;  // device alias of err_pinned: set by a kernel whose bounded wait ran out
   volatile int* err_pinned = nullptr;  // the same word, mapped pinned host memory
-  struct PinSeen { const void* p; bool pinned; } pin_seen[8] = {};
+  struct PinSeen { const void* p; bool pinned; void* alias; } pin_seen[8] = {};
   int pin_next = 0;
+  // result delivery by the kernel (HostOut): completion word (mapped pinned, after the error word),
+  // its device alias, a device counter of finished CTAs, the ticket of the last such launch
+  volatile int* done_pinned = nullptr;
+  int* done_dev = nullptr;
+  unsigned int* done_count = nullptr;
+  int ticket = 0;
+  bool host_delivery = true;
   // activation / result staging
   float* pin_x = nullptr; size_t pin_x_cap = 0;
-  float* pin_y = nullptr; size_t pin_y_cap = 0;
+  float* pin_y = nullptr;
+  void* pin_y_alias = nullptr;      // device alias of pin_y, valid while pin_y_alias_of == pin_y
+  const float* pin_y_alias_of = nullptr; size_t pin_y_cap = 0;
   float* dev_x = nullptr; size_t dev_x_cap = 0;
   float* dev_y = nullptr; size_t dev_y_cap = 0;
   float* dev_moe = nullptr; size_t dev_moe_cap = 0;  // workspace of the routed-expert layer
@@ -290,15 +300,23 @@ cudaError_t ensure_scratch(llr_exec* e, const llr_matrix* m, size_t tokens, void
 // Remembers the answer for the last few pointers: callers reuse their buffers, and a stale answer
 // is harmless either way (a pageable buffer taken for pinned is still copied correctly, only
 // slower; a pinned one taken for pageable goes through the staging buffer).
-bool is_pinned_host(llr_exec* e, const void* p) {
+bool is_pinned_host(llr_exec* e, const void* p, void** alias = nullptr) {
   for (const auto& s : e->pin_seen)
-    if (s.p == p) return s.pinned;
+    if (s.p == p) {
+      if (alias) *alias = s.alias;
+      return s.pinned;
+    }
   cudaPointerAttributes a{};
   bool pinned = false;
+  void* dev = nullptr;
   if (cudaPointerGetAttributes(&a, p) != cudaSuccess) cudaGetLastError();
-  else pinned = a.type == cudaMemoryTypeHost;
-  e->pin_seen[e->pin_next] = {p, pinned};
+  else {
+    pinned = a.type == cudaMemoryTypeHost;
+    dev = pinned ? a.devicePointer : nullptr;  // where kernels of this device can address it, if mapped
+  }
+  e->pin_seen[e->pin_next] = {p, pinned, dev};
   e->pin_next = (e->pin_next + 1) % 8;
+  if (alias) *alias = dev;
   return pinned;
 }
 
@@ -322,22 +340,56 @@ int run_host(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, fl
     std::memcpy(e->pin_x, x, nx * sizeof(float));
     src = e->pin_x;
   }
-  const bool y_pinned = is_pinned_host(e, y);
+  void* y_alias = nullptr;
+  const bool y_pinned = is_pinned_host(e, y, &y_alias);
   float* dst = y;
   if (!y_pinned) {
     if ((ce = grow_pinned(&e->pin_y, &e->pin_y_cap, ny)) != cudaSuccess) return fail_cuda(e, ce, "pinned result staging");
     dst = e->pin_y;
+    if (e->pin_y_alias_of != e->pin_y) {  // the staging buffer moved (it grows in several entry points)
+      void* a = nullptr;
+      e->pin_y_alias = cudaHostGetDevicePointer(&a, e->pin_y, 0) == cudaSuccess ? a : nullptr;
+      if (!e->pin_y_alias) cudaGetLastError();
+      e->pin_y_alias_of = e->pin_y;
+    }
+    y_alias = e->pin_y_alias;
   }
   void* scratch = nullptr;
   if ((ce = ensure_scratch(e, m, tokens, &scratch)) != cudaSuccess) return fail_cuda(e, ce, "kernel scratch");
   if ((ce = cudaMemcpyAsync(e->dev_x, src, nx * sizeof(float), cudaMemcpyHostToDevice, e->stream)) != cudaSuccess)
     return fail_cuda(e, ce, "activation upload");
-  if ((ce = launch_matmul(view_of(m), e->dev_x, e->dev_y, (int64_t)tokens, e->stream, e->path,
-                          e->sm_count, e->err_flag, scratch, &e->ctr.launches)) != cudaSuccess)
-    return fail_cuda(e, ce, "kernel launch");
-  if ((ce = cudaMemcpyAsync(dst, e->dev_y, ny * sizeof(float), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess)
-    return fail_cuda(e, ce, "result download");
-  if ((ce = cudaStreamSynchronize(e->stream)) != cudaSuccess) return fail_cuda(e, ce, "stream synchronize");
+  const MatView v = view_of(m);
+  // Decode-sized calls on the streaming kernel: the kernel stores the result into the host buffer and
+  // raises a completion word that this thread polls: no device-to-host copy, no stream synchronize.
+  const bool deliver = e->host_delivery && y_alias && !scratch && (e->path == PATH_AUTO || e->path == PATH_MMA) &&
+                       gemv_mma_hostout_ok(v, (int64_t)tokens);
+  if (deliver) {
+    const int ticket = ++e->ticket;
+    HostOut ho{(long long)((char*)y_alias - (char*)e->dev_y), e->done_dev, e->done_count, ticket};
+    if ((ce = launch_gemv_mma_hostout(v, e->dev_x, e->dev_y, (int64_t)tokens, ho, e->stream, e->sm_count, e->err_flag,
+                                      &e->ctr.launches)) != cudaSuccess)
+      return fail_cuda(e, ce, "kernel launch");
+    bool done = false;
+    for (uint64_t spins = 1; !done; ++spins) {
+      if (*e->done_pinned == ticket) { done = true; break; }
+      if ((spins & 4095) == 0) {  // a kernel that failed or was never run must not hang the caller
+        const cudaError_t q = cudaStreamQuery(e->stream);
+        if (q == cudaErrorNotReady) continue;
+        if (q != cudaSuccess) return fail_cuda(e, q, "kernel execution");
+        done = *e->done_pinned == ticket;
+        break;
+      }
+    }
+    std::atomic_thread_fence(std::memory_order_acquire);
+    if (!done) return fail(e, LLR_ERR_CUDA, "the kernel finished without delivering its result");
+  } else {
+    if ((ce = launch_matmul(v, e->dev_x, e->dev_y, (int64_t)tokens, e->stream, e->path,
+                            e->sm_count, e->err_flag, scratch, &e->ctr.launches)) != cudaSuccess)
+      return fail_cuda(e, ce, "kernel launch");
+    if ((ce = cudaMemcpyAsync(dst, e->dev_y, ny * sizeof(float), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess)
+      return fail_cuda(e, ce, "result download");
+    if ((ce = cudaStreamSynchronize(e->stream)) != cudaSuccess) return fail_cuda(e, ce, "stream synchronize");
+  }
   if (take_device_error(e) != 0) {
     return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations (copy engine did not deliver a weight tile)");
   }
@@ -409,11 +461,16 @@ int llr_exec_create(int device, llr_exec** out) {
   }
   e->sm_count = prop.multiProcessorCount;
   void* err_host = nullptr;
-  if ((ce = cudaHostAlloc(&err_host, sizeof(int), cudaHostAllocMapped)) == cudaSuccess) {
-    *(int*)err_host = 0;
+  if ((ce = cudaHostAlloc(&err_host, 2 * sizeof(int), cudaHostAllocMapped)) == cudaSuccess) {
+    ((int*)err_host)[0] = ((int*)err_host)[1] = 0;
     e->err_pinned = (volatile int*)err_host;
+    e->done_pinned = (volatile int*)err_host + 1;
     ce = cudaHostGetDevicePointer((void**)&e->err_flag, err_host, 0);
+    e->done_dev = e->err_flag + 1;
   }
+  if (ce == cudaSuccess && (ce = cudaMalloc((void**)&e->done_count, sizeof(unsigned int))) == cudaSuccess)
+    ce = cudaMemset(e->done_count, 0, sizeof(unsigned int));
+  if (const char* hd = std::getenv("LLR_HOST_DELIVERY")) e->host_delivery = std::strcmp(hd, "0") != 0;
   if (ce != cudaSuccess) {
     if (err_host) cudaFreeHost(err_host);
     cudaGetLastError();
@@ -449,6 +506,7 @@ int llr_exec_destroy(llr_exec* e) {
   if (e->dev_s) cudaFree(e->dev_s);
   if (e->dev_moe) cudaFree(e->dev_moe);
   if (e->err_pinned) cudaFreeHost((void*)e->err_pinned);
+  if (e->done_count) cudaFree(e->done_count);
   cudaStreamDestroy(e->stream);
   cudaGetLastError();
   delete e;

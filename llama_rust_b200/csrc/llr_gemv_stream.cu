@@ -102,6 +102,7 @@ struct Work {
   const ProgPhase* phases;
   int n_phases;
   const PeerTable* peers;  // row-sharded programs only
+  HostOut host;            // single products that deliver their result to the host themselves
 };
 
 // Tile range of this CTA inside a phase, and inside one entry of it.
@@ -118,7 +119,7 @@ __device__ __forceinline__ bool entry_range(const ProgEntry& E, int lo, int hi, 
 // DTFIX: the one format of a single-product launch (the other block routines are compiled
 // out, which keeps the consumers under the register budget of two CTAs per SM), or -1 for
 // programs, which switch per entry.
-template <int MT, bool PROGRAM, int DTFIX, bool PEERS = false>
+template <int MT, bool PROGRAM, int DTFIX, bool PEERS = false, bool HOSTOUT = false>
 __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* counters,
                                             unsigned long long epoch, int* err) {
   using L = SLay<MT>;
@@ -216,6 +217,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
                 float* yp = E.y + (int64_t)k * E.y_ld + row;
                 if (span != 0) v += *yp;
                 *yp = v;
+                if (HOSTOUT && span == n_span - 1) *(float*)((char*)yp + wk.host.y_delta) = v;
                 if (PEERS && span == n_span - 1) {
                   const int np = wk.peers->n_peers;
                   for (int p = 0; p < np; ++p) *(float*)((char*)yp + wk.peers->y_delta[p]) = v;
@@ -252,6 +254,20 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           __syncwarp();
           if (lane == 0)  // release: the y values written above are visible before the count
             asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(counters + ph), "l"(1ull) : "memory");
+        }
+      }
+    }
+    if (HOSTOUT) {
+      // this CTA's stores to host memory are performed; the CTA that counts last tells the host
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) {
+        unsigned int old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(wk.host.count) : "memory");
+        if (old + 1 == (unsigned int)nb) {
+          *wk.host.count = 0;  // the next launch counts from zero; its reducers run after this grid has completed
+          __threadfence_system();
+          *(volatile int*)wk.host.done = wk.host.ticket;
         }
       }
     }
@@ -397,15 +413,25 @@ gemv_stream_kernel(const __grid_constant__ ProgEntry one, int* __restrict__ err)
   __shared__ ProgPhase phase;
   if (threadIdx.x == 0) phase = ProgPhase{0, 1, one.n_tiles, 0};
   __syncthreads();
-  Work wk{&one, &phase, 1, nullptr};
+  Work wk{&one, &phase, 1, nullptr, HostOut{}};
   stream_body<MT, false, DT>(wk, nullptr, 0ull, err);
+}
+
+template <int MT, int DT>
+__global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
+gemv_stream_hostout_kernel(const __grid_constant__ ProgEntry one, const __grid_constant__ HostOut ho, int* __restrict__ err) {
+  __shared__ ProgPhase phase;
+  if (threadIdx.x == 0) phase = ProgPhase{0, 1, one.n_tiles, 0};
+  __syncthreads();
+  Work wk{&one, &phase, 1, nullptr, ho};
+  stream_body<MT, false, DT, false, true>(wk, nullptr, 0ull, err);
 }
 
 template <int MT>
 __global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
 gemv_program_kernel(const ProgEntry* __restrict__ entries, const ProgPhase* __restrict__ phases, int n_phases,
                     unsigned long long* __restrict__ counters, unsigned long long epoch, int* __restrict__ err) {
-  Work wk{entries, phases, n_phases, nullptr};
+  Work wk{entries, phases, n_phases, nullptr, HostOut{}};
   stream_body<MT, true, -1>(wk, counters, epoch, err);
 }
 
@@ -414,7 +440,7 @@ __global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
 gemv_sharded_program_kernel(const ProgEntry* __restrict__ entries, const ProgPhase* __restrict__ phases, int n_phases,
                             unsigned long long* __restrict__ counters, unsigned long long epoch,
                             const PeerTable* __restrict__ peers, int* __restrict__ err) {
-  Work wk{entries, phases, n_phases, peers};
+  Work wk{entries, phases, n_phases, peers, HostOut{}};
   stream_body<MT, true, -1, true>(wk, counters, epoch, err);
 }
 
@@ -431,16 +457,16 @@ cudaError_t occupancy(K kern, int smem, int* blocks_per_sm) {
 
 template <int MT, int DT>
 cudaError_t launch_single(const MatView& m, const float* x, float* y, int tokens, cudaStream_t stream,
-                          int sm_count, int* err) {
-  auto kern = gemv_stream_kernel<MT, DT>;
+                          int sm_count, int* err, const HostOut* ho) {
   constexpr int smem = SLay<MT>::TOTAL;
-  static int blocks_per_sm = 0;  // per instantiation
-  if (blocks_per_sm == 0) {
-    cudaError_t e = occupancy(kern, smem, &blocks_per_sm);
+  static int blocks_per_sm = 0, blocks_per_sm_ho = 0;  // per instantiation
+  int& bps = ho ? blocks_per_sm_ho : blocks_per_sm;
+  if (bps == 0) {
+    cudaError_t e = ho ? occupancy(gemv_stream_hostout_kernel<MT, DT>, smem, &bps) : occupancy(gemv_stream_kernel<MT, DT>, smem, &bps);
     if (e != cudaSuccess) return e;
   }
   ProgEntry E{m.w, x, y, m.row_bytes, (int)m.rows, (int)m.cols, m.dtype, tokens, 0, (int)((m.rows + 15) / 16), m.rows};
-  int grid = sm_count * blocks_per_sm;
+  int grid = sm_count * bps;
   if (grid > E.n_tiles) grid = E.n_tiles;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -452,7 +478,8 @@ cudaError_t launch_single(const MatView& m, const float* x, float* y, int tokens
   cfg.stream = stream;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, E, err);
+  if (ho) return cudaLaunchKernelEx(&cfg, gemv_stream_hostout_kernel<MT, DT>, E, *ho, err);
+  return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<MT, DT>, E, err);
 }
 
 }  // namespace
@@ -467,18 +494,18 @@ bool gemv_mma_supported(const MatView& m) {
   return true;
 }
 
-cudaError_t launch_gemv_mma(const MatView& m, const float* x, float* y, int64_t tokens,
-                            cudaStream_t stream, int sm_count, int* err, uint64_t* launches) {
+static cudaError_t launch_passes(const MatView& m, const float* x, float* y, int64_t tokens, cudaStream_t stream,
+                                 int sm_count, int* err, uint64_t* launches, const HostOut* ho) {
   for (int64_t t0 = 0; t0 < tokens; t0 += 8) {
     const int nt = (int)(tokens - t0 < 8 ? tokens - t0 : 8);
     const float* xp = x + t0 * m.cols;
     float* yp = y + t0 * m.rows;
     cudaError_t e;
 #define LLR_LAUNCH_DT(D)                                                                      \
-    (nt == 1 ? launch_single<1, D>(m, xp, yp, nt, stream, sm_count, err)                      \
-     : nt == 2 ? launch_single<2, D>(m, xp, yp, nt, stream, sm_count, err)                    \
-     : nt <= 4 ? launch_single<4, D>(m, xp, yp, nt, stream, sm_count, err)                    \
-               : launch_single<8, D>(m, xp, yp, nt, stream, sm_count, err))
+    (nt == 1 ? launch_single<1, D>(m, xp, yp, nt, stream, sm_count, err, ho)                  \
+     : nt == 2 ? launch_single<2, D>(m, xp, yp, nt, stream, sm_count, err, ho)                \
+     : nt <= 4 ? launch_single<4, D>(m, xp, yp, nt, stream, sm_count, err, ho)                \
+               : launch_single<8, D>(m, xp, yp, nt, stream, sm_count, err, ho))
     if (m.dtype == DT_Q4_K) e = LLR_LAUNCH_DT(DT_Q4_K);
     else if (m.dtype == DT_Q6_K) e = LLR_LAUNCH_DT(DT_Q6_K);
     else e = LLR_LAUNCH_DT(DT_Q8_0);
@@ -487,6 +514,19 @@ cudaError_t launch_gemv_mma(const MatView& m, const float* x, float* y, int64_t 
     if (launches) ++*launches;
   }
   return cudaSuccess;
+}
+
+cudaError_t launch_gemv_mma(const MatView& m, const float* x, float* y, int64_t tokens,
+                            cudaStream_t stream, int sm_count, int* err, uint64_t* launches) {
+  return launch_passes(m, x, y, tokens, stream, sm_count, err, launches, nullptr);
+}
+
+bool gemv_mma_hostout_ok(const MatView& m, int64_t tokens) { return tokens >= 1 && tokens <= 8 && gemv_mma_supported(m); }
+
+cudaError_t launch_gemv_mma_hostout(const MatView& m, const float* x, float* y, int64_t tokens, const HostOut& ho,
+                                    cudaStream_t stream, int sm_count, int* err, uint64_t* launches) {
+  if (!gemv_mma_hostout_ok(m, tokens)) return cudaErrorInvalidValue;
+  return launch_passes(m, x, y, tokens, stream, sm_count, err, launches, &ho);  // one pass
 }
 
 // ------------------------------------------------------------------ programs

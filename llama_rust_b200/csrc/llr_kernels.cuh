@@ -51,6 +51,20 @@ cudaError_t launch_gemv_staged(const MatView& m, const float* x, float* y, int64
 bool gemv_mma_supported(const MatView& m);
 cudaError_t launch_gemv_mma(const MatView& m, const float* x, float* y, int64_t tokens,
                             cudaStream_t stream, int sm_count, int* err_flag, uint64_t* launches);
+// Result delivery to the host by the kernel itself (host-pointer calls with at most 8 activation
+// rows): the reducer also stores each finished value at y + y_delta bytes, a device alias of
+// mapped pinned host memory, and the CTA that finishes last stores `ticket` into *done (mapped
+// pinned as well) after a system-scope fence.  The host polls *done instead of enqueuing a
+// device-to-host copy and synchronizing the stream.  count is a zeroed device word.
+struct HostOut {
+  long long y_delta;
+  int* done;
+  unsigned int* count;
+  int ticket;
+};
+bool gemv_mma_hostout_ok(const MatView& m, int64_t tokens);
+cudaError_t launch_gemv_mma_hostout(const MatView& m, const float* x, float* y, int64_t tokens, const HostOut& ho,
+                                    cudaStream_t stream, int sm_count, int* err_flag, uint64_t* launches);
 
 // One matrix product of a program (llr_gemv_prog.cu).  tile_begin / n_tiles are filled in
 // by program_create.
