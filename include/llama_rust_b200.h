@@ -117,7 +117,15 @@ int llr_gemv_resident(llr_exec* exec, const llr_matrix* matrix, const float* x, 
                       float* y, size_t y_len);
 
 /* y[t*rows + r] for `tokens` activation rows in one call.  Replaces
- * CudaGemv::gemm_resident [gpu.rs:351].  tokens == 0 is an error. */
+ * CudaGemv::gemm_resident [gpu.rs:351].  tokens == 0 is an error.
+ * Host-pointer calls return with y valid.  Every error detected before the
+ * launch (all shape and handle errors) leaves y untouched, as in the reference.
+ * For up to 8 activation rows on the streaming decode kernel, the kernel stores
+ * the result straight into y when y is pinned host memory (into a pinned staging
+ * buffer otherwise) and raises a completion word this call polls, instead of a
+ * device-to-host copy and a stream synchronize; if a device-side bounded wait
+ * runs out (status LLR_ERR_CUDA) a pinned y may then hold partial results.
+ * LLR_HOST_DELIVERY=0 in the environment selects the copy path always. */
 int llr_gemm_resident(llr_exec* exec, const llr_matrix* matrix, size_t tokens, const float* x,
                       size_t x_len, float* y, size_t y_len);
 
