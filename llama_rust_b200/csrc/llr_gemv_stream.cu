@@ -69,9 +69,9 @@ template <int MT> struct SLay {
   static constexpr int NT = (MT + 1) / 2;
   static constexpr int RING = 0;
   static constexpr int DIG = RING + NST * MAX_CHUNK;
-  static constexpr int SXF = DIG + NT * 8 * DS;
-  static constexpr int XSI = SXF + MT * (SPAN / 32) * 4;
-  static constexpr int RED = XSI + MT * (SPAN / 256) * 4;          // float [NRB][CW][16][MT]
+  static constexpr int SXF = DIG + Sp<MT>::PLANES * Sp<MT>::DS;
+  static constexpr int XSI = SXF + MT * (Sp<MT>::SPAN / 32) * 4;
+  static constexpr int RED = XSI + MT * (Sp<MT>::SPAN / 256) * 4;          // float [NRB][CW][16][MT]
   static constexpr int BAR = RED + NRB * CW * 16 * MT * 4;          // full[NST] empty[NST] rfull[NRB] rempty[NRB]
   static constexpr int TOTAL = BAR + (2 * NST + 2 * NRB) * 8 + 16;
 };
@@ -124,6 +124,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
                                             unsigned long long epoch, int* err) {
   using L = SLay<MT>;
   constexpr int NT = L::NT;
+  constexpr int SPAN = Sp<MT>::SPAN;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* ring = smem + L::RING;
   uint8_t* dig = smem + L::DIG;
@@ -143,7 +144,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
     for (int s = 0; s < NRB; ++s) { mbar_init(&rfull[s], CW); mbar_init(&rempty[s], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int i = tid; i < NT * 8 * DS / 16; i += NTHREADS) ((uint4*)dig)[i] = make_uint4(0, 0, 0, 0);
+  for (int i = tid; i < Sp<MT>::PLANES * Sp<MT>::DS / 16; i += NTHREADS) ((uint4*)dig)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
 
   if (warp == CW) {
@@ -333,7 +334,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
         const int span_cols = min(SPAN, E.cols - span * SPAN), nblk256 = span_cols >> 8;
         if (cur_x != E.x || cur_cols != E.cols || cur_span != span || cur_tokens != E.tokens) {
           consumer_sync();  // nobody still multiplies against the old planes
-          split_activations(E.x, E.cols, span * SPAN, nblk256, E.tokens, dig, sxf, xsi, warp, lane, produced_here);
+          split_activations<MT>(E.x, E.cols, span * SPAN, nblk256, E.tokens, dig, sxf, xsi, warp, lane, produced_here);
           consumer_sync();
           cur_x = E.x; cur_cols = E.cols; cur_span = span; cur_tokens = E.tokens;
         }

@@ -18,8 +18,21 @@ namespace mma {
 
 constexpr int NWARP = 8;
 constexpr int NST = 2;          // chunks in flight per CTA
-constexpr int SPAN = 4096;      // columns whose digit planes live in shared memory
-constexpr int DS = SPAN + 32;   // digit plane stride: 32 mod 128 -> conflict-free 8-byte reads
+// Columns whose digit planes live in shared memory at a time, and the plane pitch (32 mod 128
+// bytes: conflict-free 8-byte reads).  An n-tile has eight B columns = two activation rows x four
+// digits.  With a single activation row the second row's planes would be all zero: they are not
+// stored, and the span is twice as long in the same
+// shared memory, which halves the number of activation splits of a long row (ffn_down).
+template <int MT> struct Sp {
+  static constexpr int SPAN = MT == 1 ? 8192 : 4096;
+  static constexpr int DS = SPAN + 32;
+  static constexpr int PLANES = MT == 1 ? 4 : ((MT + 1) / 2) * 8;
+};
+// plane of B column g of n-tile nt; with one activation row columns 4..7 alias 0..3: their integer
+// sums are garbage, and are multiplied by the zero scale every routine applies to rows >= MT
+template <int MT> __device__ __forceinline__ const uint8_t* plane_of(const uint8_t* dig, int nt, int g) {
+  return dig + (size_t)(MT == 1 ? (g & 3) : nt * 8 + g) * Sp<MT>::DS;
+}
 constexpr int SPIN_LIMIT = 1 << 22;
 
 template <int DT> struct Fmt;
@@ -36,13 +49,6 @@ template <int DT, int MT> struct Lay {
   static constexpr int RMOD = DT == DT_Q6_K ? 16 : 32;
   static constexpr int RS = SEGB + (RMOD + 128 - SEGB % 128) % 128;
   static constexpr int CHUNK = 16 * RS;
-  static constexpr int RING = 0;
-  static constexpr int DIG = RING + NST * CHUNK;                // int8 [NT*8][DS]
-  static constexpr int SXF = DIG + NT * 8 * DS;                 // float [MT][SPAN/32]
-  static constexpr int XSI = SXF + MT * (SPAN / 32) * 4;        // float [MT][SPAN/256]
-  static constexpr int RED = XSI + MT * (SPAN / 256) * 4;       // float [2][NWARP][16][MT]
-  static constexpr int BAR = RED + 2 * NWARP * 16 * MT * 4;     // uint64 [NST]
-  static constexpr int TOTAL = BAR + NST * 8 + 16;
   static_assert(RS % 16 == 0 && RS % 128 == RMOD, "row stride");
 };
 
@@ -152,7 +158,7 @@ __device__ __forceinline__ void block_q4k(const uint8_t* rowA, const uint8_t* ro
     const int sBlo = (scBp >> (16 * (G & 1))) & 255, sBhi = (scBp >> (16 * (G & 1) + 8)) & 255;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      const uint8_t* dp = dig + (size_t)(nt * 8 + g) * DS + cb * 256 + G * 64 + 8 * t;
+      const uint8_t* dp = plane_of<MT>(dig, nt, g) + cb * 256 + G * 64 + 8 * t;
       const uint2 blo = *(const uint2*)dp, bhi = *(const uint2*)(dp + 32);
       int clo[4], chi[4];
       mma_k32(clo, wA.x & M4, wB.x & M4, wA.y & M4, wB.y & M4, blo.x, blo.y);
@@ -170,7 +176,7 @@ __device__ __forceinline__ void block_q4k(const uint8_t* rowA, const uint8_t* ro
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int tok = 2 * nt + (t >> 1);
-    const float xs = tok < MT ? xsi[tok * (SPAN / 256) + cb] : 0.f;
+    const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + cb] : 0.f;
     acc.y[nt][0] = fmaf((float)T[nt][0], dA * xs * pw0, acc.y[nt][0]);
     acc.y[nt][1] = fmaf((float)T[nt][1], dA * xs * pw1, acc.y[nt][1]);
     acc.y[nt][2] = fmaf((float)T[nt][2], dB * xs * pw0, acc.y[nt][2]);
@@ -183,7 +189,7 @@ __device__ __forceinline__ void block_q4k(const uint8_t* rowA, const uint8_t* ro
   const float b0 = dminB * (float)((mnB >> (16 * (t & 1))) & 255), b1 = dminB * (float)((mnB >> (16 * (t & 1) + 8)) & 255);
 #pragma unroll
   for (int k = 0; k < MT; ++k) {
-    const float s0 = sxf[k * (SPAN / 32) + cb * 8 + 2 * t], s1 = sxf[k * (SPAN / 32) + cb * 8 + 2 * t + 1];
+    const float s0 = sxf[k * (Sp<MT>::SPAN / 32) + cb * 8 + 2 * t], s1 = sxf[k * (Sp<MT>::SPAN / 32) + cb * 8 + 2 * t + 1];
     acc.mn[0][k] = fmaf(a0, s0, fmaf(a1, s1, acc.mn[0][k]));
     acc.mn[1][k] = fmaf(b0, s0, fmaf(b1, s1, acc.mn[1][k]));
   }
@@ -223,7 +229,7 @@ __device__ __forceinline__ void block_q6k(const uint8_t* rowA, const uint8_t* ro
         const int col = cb * 256 + half * 128 + qtr * 32 + l;  // first of this thread's 4 columns
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          const uint32_t bd = *(const uint32_t*)(dig + (size_t)(nt * 8 + g) * DS + col);
+          const uint32_t bd = *(const uint32_t*)(plane_of<MT>(dig, nt, g) + col);
           int c[4];
           mma_k16(c, cA, cB, bd);
           T[nt][0] += sA * c[0]; T[nt][1] += sA * c[1];
@@ -237,7 +243,7 @@ __device__ __forceinline__ void block_q6k(const uint8_t* rowA, const uint8_t* ro
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int tok = 2 * nt + (t >> 1);
-    const float xs = tok < MT ? xsi[tok * (SPAN / 256) + cb] : 0.f;
+    const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + cb] : 0.f;
     acc.y[nt][0] = fmaf((float)T[nt][0], dA * xs * pw0, acc.y[nt][0]);
     acc.y[nt][1] = fmaf((float)T[nt][1], dA * xs * pw1, acc.y[nt][1]);
     acc.y[nt][2] = fmaf((float)T[nt][2], dB * xs * pw0, acc.y[nt][2]);
@@ -259,11 +265,11 @@ __device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* ro
   const float pw0 = (t & 1) ? 65536.f : 1.f, pw1 = pw0 * 256.f;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
-    const uint2 bd = *(const uint2*)(dig + (size_t)(nt * 8 + g) * DS + c32 * 32 + 8 * t);
+    const uint2 bd = *(const uint2*)(plane_of<MT>(dig, nt, g) + c32 * 32 + 8 * t);
     int c[4];
     mma_k32(c, wA.x, wB.x, wA.y, wB.y, bd.x, bd.y);
     const int tok = 2 * nt + (t >> 1);
-    const float xs = tok < MT ? xsi[tok * (SPAN / 256) + (c32 >> 3)] : 0.f;
+    const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + (c32 >> 3)] : 0.f;
     acc.y[nt][0] = fmaf((float)c[0], dA * xs * pw0, acc.y[nt][0]);
     acc.y[nt][1] = fmaf((float)c[1], dA * xs * pw1, acc.y[nt][1]);
     acc.y[nt][2] = fmaf((float)c[2], dB * xs * pw0, acc.y[nt][2]);
@@ -276,6 +282,7 @@ __device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* ro
 // activation rows) -> four int8 digit planes per activation row, the f32 sums of x per 32
 // columns (Q4_K mins) and 2^-e per block.  One warp per (block, row); `coherent` selects
 // L2-coherent loads for activations that an earlier phase of the same launch produced.
+template <int MT>
 __device__ __forceinline__ void split_activations(const float* __restrict__ X, int cols, int col0,
                                                   int nblk256, int tokens, uint8_t* dig, float* sxf,
                                                   float* xsi, int warp, int lane, bool coherent) {
@@ -341,10 +348,10 @@ __device__ __forceinline__ void split_activations(const float* __restrict__ X, i
     const int nt = tok >> 1, plane0 = (tok & 1) * 4;
 #pragma unroll
     for (int p = 0; p < 4; ++p)
-      *(uint2*)(dig + (size_t)(nt * 8 + plane0 + p) * DS + b * 256 + 8 * lane) = make_uint2(pk[p][0], pk[p][1]);
-    if ((lane & 3) == 0) sxf[tok * (SPAN / 32) + b * 8 + (lane >> 2)] = sum;
+      *(uint2*)(dig + (size_t)(nt * 8 + plane0 + p) * Sp<MT>::DS + b * 256 + 8 * lane) = make_uint2(pk[p][0], pk[p][1]);
+    if ((lane & 3) == 0) sxf[tok * (Sp<MT>::SPAN / 32) + b * 8 + (lane >> 2)] = sum;
     // a non-finite activation makes the whole output row of that token NaN
-    if (lane == 0) xsi[tok * (SPAN / 256) + b] = bad ? __uint_as_float(0x7fc00000u) : sinv;
+    if (lane == 0) xsi[tok * (Sp<MT>::SPAN / 256) + b] = bad ? __uint_as_float(0x7fc00000u) : sinv;
    }
   }
 }
