@@ -34,6 +34,7 @@ struct llr_matrix {
   size_t bytes;      // packed bytes (allocation is padded beyond this)
   int dtype;
   int64_t rows, cols, row_bytes;
+  int f16_ok = -1;   // operand choice of the tensor-core GEMM, from the block headers at upload (-1: not examined)
 };
 
 namespace {
@@ -124,6 +125,7 @@ struct llr_exec {
   unsigned int* done_count = nullptr;
   int ticket = 0;
   bool host_delivery = true;
+  unsigned int* bound_dev = nullptr;  // result word of the weight range check
   // activation / result staging
   float* pin_x = nullptr; size_t pin_x_cap = 0;
   float* pin_y = nullptr;
@@ -284,7 +286,7 @@ int check_matrix(llr_exec* e, const llr_matrix* m) {
 }
 
 MatView view_of(const llr_matrix* m) {
-  return MatView{m->dev, m->dtype, m->rows, m->cols, m->row_bytes};
+  return MatView{m->dev, m->dtype, m->rows, m->cols, m->row_bytes, m->f16_ok};
 }
 
 // scratch for the tensor-core GEMM; growing frees the old buffer, which synchronizes the device
@@ -325,6 +327,19 @@ int take_device_error(llr_exec* e) {
   const int v = *e->err_pinned;
   if (v != 0) *e->err_pinned = 0;
   return v;
+}
+
+// Tensor-core GEMM operand choice for a freshly filled matrix: enqueues the header scan; the caller
+// synchronizes the stream anyway and then calls finish_range_check.
+cudaError_t begin_range_check(llr_exec* e, llr_matrix* m, unsigned int* host_word) {
+  const MatView v = view_of(m);
+  if (!gemm_tc_supported(v, 64) || !e->bound_dev) return cudaSuccess;
+  cudaError_t ce = launch_weight_bound(v, e->bound_dev, e->stream, &e->ctr.launches);
+  if (ce == cudaSuccess) ce = cudaMemcpyAsync(host_word, e->bound_dev, sizeof(unsigned int), cudaMemcpyDeviceToHost, e->stream);
+  return ce;
+}
+void finish_range_check(llr_matrix* m, unsigned int host_word, bool examined) {
+  if (examined) m->f16_ok = weight_bound_allows_f16(host_word) ? 1 : 0;
 }
 
 // H2D of the activations, launch, D2H of the result, synchronize (gpu.rs:301-334,
@@ -468,8 +483,11 @@ int llr_exec_create(int device, llr_exec** out) {
     ce = cudaHostGetDevicePointer((void**)&e->err_flag, err_host, 0);
     e->done_dev = e->err_flag + 1;
   }
-  if (ce == cudaSuccess && (ce = cudaMalloc((void**)&e->done_count, sizeof(unsigned int))) == cudaSuccess)
-    ce = cudaMemset(e->done_count, 0, sizeof(unsigned int));
+  if (ce == cudaSuccess && (ce = cudaMalloc((void**)&e->done_count, 2 * sizeof(unsigned int))) == cudaSuccess) {
+    ce = cudaMemset(e->done_count, 0, 2 * sizeof(unsigned int));
+    e->bound_dev = e->done_count + 1;
+  }
+  if (const char* bf = std::getenv("LLR_GEMM_BF16")) { if (std::strcmp(bf, "0") != 0) e->bound_dev = nullptr; }  // keep bfloat16 operands
   if (const char* hd = std::getenv("LLR_HOST_DELIVERY")) e->host_delivery = std::strcmp(hd, "0") != 0;
   if (ce != cudaSuccess) {
     if (err_host) cudaFreeHost(err_host);
@@ -560,8 +578,12 @@ static int upload_common(llr_exec* e, uint8_t dtype, size_t rows, size_t cols, c
   cudaError_t ce = cudaMemcpyAsync(m->dev, packed, expect,
                                    from_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice,
                                    e->stream);
+  unsigned int bound = 0;
+  const bool examine = gemm_tc_supported(view_of(m), 64) && e->bound_dev != nullptr;
+  if (ce == cudaSuccess) ce = begin_range_check(e, m, &bound);
   if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
   if (ce != cudaSuccess) { release_matrix(e, m); return fail_cuda(e, ce, "weight upload"); }
+  finish_range_check(m, bound, examine);
   ++e->ctr.uploads;
   e->ctr.upload_bytes += expect;
   *out = m;
@@ -711,7 +733,7 @@ int llr_gemm_device_noalloc(llr_exec* e, const llr_matrix* m, size_t tokens, con
   const MatView v = view_of(m);
   if (!gemm_tc_supported(v, (int64_t)tokens))
     return fail(e, LLR_ERR_INVALID,
-                "the allocation-free GEMM takes Q4_K, Q8_0, Q5_0 or Q5_1 with cols % 64 == 0 and at least 16 activation rows");
+                "the allocation-free GEMM takes Q4_K, Q8_0, Q5_0 or Q5_1 with cols % 256 == 0 and at least 16 activation rows");
   size_t need = 0;
   if (!mul_ok(tokens, (size_t)v.cols, &need) || !mul_ok(need, 2, &need) || need > gemm_tc_static_scratch_limit())
     return fail(e, LLR_ERR_INVALID, "tokens * cols * 2 = " + std::to_string(need) + " bytes exceeds the built-in staging area of " +
@@ -1089,8 +1111,12 @@ int llr_matrix_synth(llr_exec* e, uint8_t dtype, size_t rows, size_t cols, uint6
   if ((rc = alloc_matrix(e, dtype, rows, cols, rb, expect, &m)) != LLR_OK) return rc;
   cudaError_t ce = launch_synth(dtype, (int64_t)rows, (int64_t)cols, seed, m->dev, e->stream,
                                 &e->ctr.launches);
+  unsigned int bound = 0;
+  const bool examine = gemm_tc_supported(view_of(m), 64) && e->bound_dev != nullptr;
+  if (ce == cudaSuccess) ce = begin_range_check(e, m, &bound);
   if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
   if (ce != cudaSuccess) { release_matrix(e, m); return fail_cuda(e, ce, "synthetic fill"); }
+  finish_range_check(m, bound, examine);
   *out = m;
   return LLR_OK;
 }

@@ -41,6 +41,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstring>
 #include <type_traits>
 
 #include "llr_formats.cuh"
@@ -144,9 +145,10 @@ __device__ __forceinline__ uint64_t smem_desc_u(uint32_t saddr) {
   return addr | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// kind::f16 instruction descriptor: D f32, A (tensor memory) and B (shared, K-major) bf16, M = 128, N = BN.
-template <int BN> __host__ __device__ constexpr uint32_t instr_desc() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// kind::f16 instruction descriptor: D f32, A (tensor memory) and B (shared, K-major) both bf16 or both
+// binary16 (format code 1 / 0; the hardware rejects a mixed pair), M = 128, N = BN.
+template <int BN, bool F16> __host__ __device__ constexpr uint32_t instr_desc() {
+  return (1u << 4) | ((F16 ? 0u : 1u) << 7) | ((F16 ? 0u : 1u) << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -269,10 +271,94 @@ __device__ __forceinline__ void dequant_sub(uint32_t prow, uint32_t (&out)[16], 
   }
 }
 
-template <int DT, int BN>
+// ---- binary16 operand path ----------------------------------------------------------------
+// Same decoding, but the arithmetic stays in packed binary16: quants are masked into 1024+q (or
+// 64+q) pairs, the offset is subtracted exactly, and one HFMA2 applies scale and min to two
+// weights.  Under two instructions per weight instead of four to six, and 11 significant bits
+// instead of bfloat16's 8.  binary16 has a narrow range: the executor runs this path only for
+// matrices whose largest possible |weight| (from the block headers) is between 2^-8 and 30000,
+// and activations are rescaled per row by a power of two (undone in the epilogue).
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *(const uint32_t*)&v; }
+__device__ __forceinline__ __half2 bits_h2(uint32_t v) { return *(const __half2*)&v; }
+// bytes b0..b3 of w hold unsigned codes under MASK; out0 = (c0, c1) * a + nb, out1 = (c2, c3) * a + nb
+template <uint32_t MASK, uint32_t MAGIC>
+__device__ __forceinline__ void emit4h(uint32_t w, __half2 off, __half2 a, __half2 nb, uint32_t& o0, uint32_t& o1) {
+  const uint32_t p01 = __byte_perm(w, 0, 0x4140), p23 = __byte_perm(w, 0, 0x4342);  // (b0, b1), (b2, b3) in the low bytes of each half
+  const __half2 q01 = __hsub2(bits_h2((p01 & MASK) ^ MAGIC), off), q23 = __hsub2(bits_h2((p23 & MASK) ^ MAGIC), off);
+  o0 = h2_bits(__hfma2(q01, a, nb));
+  o1 = h2_bits(__hfma2(q23, a, nb));
+}
+
+template <int DT, int SB>
+__device__ __forceinline__ void dequant_sub_h(uint32_t prow, uint32_t (&out)[16], int rsb = 0) {
+  if constexpr (DT == DT_Q4_K) {
+    const int sb = SB < 0 ? rsb : SB;
+    uint32_t hdr[4], q[8];
+    lds_chunks<1>(prow, hdr);
+    lds_chunks<2>(prow + 16 + 32 * (sb >> 1), q);
+    const float d = h2f(hdr[0] & 0xffffu), dmin = h2f(hdr[0] >> 16);
+    const int sh = 8 * (sb & 3);
+    const uint32_t b_lo = (hdr[1] >> sh) & 255u, b_mid = (hdr[2] >> sh) & 255u, b_hi = (hdr[3] >> sh) & 255u;
+    uint32_t sc, mn;
+    if (sb < 4) { sc = b_lo & 63u; mn = b_mid & 63u; }
+    else { sc = (b_hi & 15u) | ((b_lo >> 6) << 4); mn = (b_hi >> 4) | ((b_mid >> 6) << 4); }
+    const __half2 a = __float2half2_rn(d * (float)sc), nb = __float2half2_rn(-(dmin * (float)mn));
+    if (sb & 1) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) emit4h<0x00f000f0u, 0x54005400u>(q[i], __float2half2_rn(64.f), a, nb, out[2 * i], out[2 * i + 1]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) emit4h<0x000f000fu, 0x64006400u>(q[i], __float2half2_rn(1024.f), a, nb, out[2 * i], out[2 * i + 1]);
+    }
+  } else if constexpr (DT == DT_Q8_0) {
+    constexpr int C0 = (34 * SB) / 16, OFF = 34 * SB - 16 * C0;
+    uint32_t w[12];
+    lds_chunks<3>(prow + 16 * C0, w);
+    const uint32_t dh = h_at<OFF>(w);
+    const __half2 d = bits_h2(dh | (dh << 16)), off = __float2half2_rn(1152.f), zero = __float2half2_rn(0.f);
+    auto go = [&](auto I) {
+      constexpr int i = decltype(I)::value;
+      emit4h<0x00ff00ffu, 0x64806480u>(w_at<OFF + 2 + 4 * i>(w), off, d, zero, out[2 * i], out[2 * i + 1]);
+    };
+    go(std::integral_constant<int, 0>{}); go(std::integral_constant<int, 1>{});
+    go(std::integral_constant<int, 2>{}); go(std::integral_constant<int, 3>{});
+    go(std::integral_constant<int, 4>{}); go(std::integral_constant<int, 5>{});
+    go(std::integral_constant<int, 6>{}); go(std::integral_constant<int, 7>{});
+  } else {
+    constexpr int BB = DT == DT_Q5_0 ? 22 : 24, HDR = DT == DT_Q5_0 ? 2 : 4;
+    constexpr int C0 = (BB * SB) / 16, OFF = BB * SB - 16 * C0, NCH = (OFF + BB + 15) / 16;
+    uint32_t w[4 * NCH + 1];
+    {
+      uint32_t t[4 * NCH];
+      lds_chunks<NCH>(prow + 16 * C0, t);
+#pragma unroll
+      for (int i = 0; i < 4 * NCH; ++i) w[i] = t[i];
+      w[4 * NCH] = 0;
+    }
+    const uint32_t dh = h_at<OFF>(w);
+    const __half2 d = bits_h2(dh | (dh << 16));
+    __half2 off, nb;
+    if constexpr (DT == DT_Q5_0) { off = __float2half2_rn(1040.f); nb = __float2half2_rn(0.f); }
+    else { const uint32_t mh = h_at<OFF + 2>(w); off = __float2half2_rn(1024.f); nb = bits_h2(mh | (mh << 16)); }
+    const uint32_t qh = w_at<OFF + HDR>(w);
+    auto go = [&](auto I) {
+      constexpr int i = decltype(I)::value;
+      const uint32_t qs = w_at<OFF + HDR + 4 + 4 * i>(w);
+      const uint32_t cl = (qs & 0x0f0f0f0fu) | spread_hi((qh >> (4 * i)) & 15u);
+      const uint32_t ch = ((qs >> 4) & 0x0f0f0f0fu) | spread_hi((qh >> (16 + 4 * i)) & 15u);
+      emit4h<0x00ff00ffu, 0x64006400u>(cl, off, d, nb, out[2 * i], out[2 * i + 1]);
+      emit4h<0x00ff00ffu, 0x64006400u>(ch, off, d, nb, out[8 + 2 * i], out[8 + 2 * i + 1]);
+    };
+    go(std::integral_constant<int, 0>{}); go(std::integral_constant<int, 1>{});
+    go(std::integral_constant<int, 2>{}); go(std::integral_constant<int, 3>{});
+  }
+}
+
+template <int DT, int BN, bool F16>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int tokens,
-               const __grid_constant__ CUtensorMap xmap, float* __restrict__ Y, int* __restrict__ err) {
+               const __grid_constant__ CUtensorMap xmap, const float* __restrict__ xscale, float* __restrict__ Y,
+               int* __restrict__ err) {
   using L = GLay<DT, BN>;
   constexpr int NA = L::NA, NB = L::NB, NPK = L::NPK, PITCH = Pk<DT>::PITCH, RB = Pk<DT>::RB;
   extern __shared__ uint8_t smem_raw[];
@@ -317,9 +403,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
     auto step = [&](auto KQ, uint32_t prow, int ks) {
       constexpr int kq = decltype(KQ)::value;
       uint32_t out[16];
-      if constexpr (DT == DT_Q4_K) dequant_sub<DT, -1>(prow, out, 2 * kq + h);
-      else if (h == 0) dequant_sub<DT, 2 * kq>(prow, out);
-      else dequant_sub<DT, 2 * kq + 1>(prow, out);
+      if constexpr (F16) {
+        if constexpr (DT == DT_Q4_K) dequant_sub_h<DT, -1>(prow, out, 2 * kq + h);
+        else if (h == 0) dequant_sub_h<DT, 2 * kq>(prow, out);
+        else dequant_sub_h<DT, 2 * kq + 1>(prow, out);
+      } else {
+        if constexpr (DT == DT_Q4_K) dequant_sub<DT, -1>(prow, out, 2 * kq + h);
+        else if (h == 0) dequant_sub<DT, 2 * kq>(prow, out);
+        else dequant_sub<DT, 2 * kq + 1>(prow, out);
+      }
       const int s = ks % NA;
       if (ok && !bar_wait(&empty_a[s], (uint32_t)(((ks / NA) & 1) ^ 1))) { ok = false; report_error(err, 3); }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -371,7 +463,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int tok = tok0 + c0 + j;
-          if (tok < tokens) Y[(int64_t)tok * rows + out_row] = __uint_as_float(v[j]);
+          if (tok < tokens) {
+            float r = __uint_as_float(v[j]);
+            if constexpr (F16) r *= __ldg(xscale + tok);  // undo the activation row's power-of-two scale
+            Y[(int64_t)tok * rows + out_row] = r;
+          }
         }
       }
     }
@@ -411,7 +507,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
     // and the loop state then live in uniform registers, which is what the MMA instruction reads.
     // A loop entered by a single lane pays a vector-to-uniform move per operand instead and
     // becomes the bottleneck of the CTA at small BN.
-    constexpr uint32_t idesc = instr_desc<BN>();
+    constexpr uint32_t idesc = instr_desc<BN, F16>();
     const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
     const uint32_t sb_u = __shfl_sync(0xffffffffu, s32(sB), 0);
     // steps per iteration: two where the rings are deep (one barrier round trip for both), one at
@@ -471,6 +567,64 @@ __global__ void to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __res
   }
 }
 
+// binary16 activations: one CTA per activation row.  The row is multiplied by the power of two that
+// puts its largest magnitude into [2^14, 2^15) (binary16 tops out at 65504), and the inverse goes
+// to inv_scale[row] for the epilogue.  A zero or non-finite row is left unscaled.
+__global__ void to_f16_rows_kernel(const float* __restrict__ x, __half* __restrict__ o, float* __restrict__ inv_scale, int cols) {
+  __shared__ float wmax[8];
+  const float* xr = x + (int64_t)blockIdx.x * cols;
+  __half* orow = o + (int64_t)blockIdx.x * cols;
+  float m = 0.f;
+  for (int i = threadIdx.x * 4; i < cols; i += blockDim.x * 4) {
+    const float4 v = *(const float4*)(xr + i);
+    m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+  }
+#pragma unroll
+  for (int o2 = 16; o2; o2 >>= 1) m = fmaxf(m, __shfl_xor_sync(~0u, m, o2));
+  if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = wmax[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) m = fmaxf(m, wmax[w]);
+  const int be = (int)((__float_as_uint(m) >> 23) & 0xff);
+  float s = 1.f, sinv = 1.f;
+  if (be != 0 && be != 255) {  // normal and finite: exponent of the scale = 14 - (be - 127), kept in the normal range
+    int e = 14 - (be - 127);
+    e = e > 126 ? 126 : (e < -126 ? -126 : e);
+    s = __uint_as_float((uint32_t)(e + 127) << 23);
+    sinv = __uint_as_float((uint32_t)(127 - e) << 23);
+  }
+  if (threadIdx.x == 0) inv_scale[blockIdx.x] = sinv;
+  for (int i = threadIdx.x * 4; i < cols; i += blockDim.x * 4) {
+    const float4 v = *(const float4*)(xr + i);
+    const __half2 a = __floats2half2_rn(v.x * s, v.y * s), b = __floats2half2_rn(v.z * s, v.w * s);
+    *(uint2*)(orow + i) = make_uint2(*(const uint32_t*)&a, *(const uint32_t*)&b);
+  }
+}
+
+// Largest |weight| any block of the matrix can decode to, from the block headers alone, as the bit
+// pattern of a non-negative float (so that an integer max orders it); NaN or infinite headers give
+// 0x7f800000 or more.
+template <int DT>
+__global__ void weight_bound_kernel(const uint8_t* __restrict__ W, int64_t n_blocks, unsigned int* __restrict__ out) {
+  constexpr int BB = DT == DT_Q4_K ? 144 : DT == DT_Q8_0 ? 34 : DT == DT_Q5_0 ? 22 : 24;
+  float m = 0.f;
+  for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks; b += (int64_t)gridDim.x * blockDim.x) {
+    const uint16_t* hp = (const uint16_t*)(W + b * BB);
+    const float d = fabsf(__half2float(__ushort_as_half(hp[0])));
+    float bound;
+    if (DT == DT_Q4_K) bound = d * (63.f * 15.f) + fabsf(__half2float(__ushort_as_half(hp[1]))) * 63.f;
+    else if (DT == DT_Q8_0) bound = d * 128.f;
+    else if (DT == DT_Q5_0) bound = d * 16.f;
+    else bound = d * 31.f + fabsf(__half2float(__ushort_as_half(hp[1])));
+    if (!(bound <= 3.4028234e38f)) bound = __uint_as_float(0x7f800000u);
+    m = fmaxf(m, bound);
+  }
+#pragma unroll
+  for (int o2 = 16; o2; o2 >>= 1) m = fmaxf(m, __shfl_xor_sync(~0u, m, o2));
+  if ((threadIdx.x & 31) == 0) atomicMax(out, __float_as_uint(m));
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -487,10 +641,10 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int DT, int BN>
-cudaError_t launch_bn(const MatView& m, const CUtensorMap& wmap, const CUtensorMap& xmap, float* y, int tokens,
-                      cudaStream_t stream, int* err) {
-  auto kern = gemm_tc_kernel<DT, BN>;
+template <int DT, int BN, bool F16>
+cudaError_t launch_bn(const MatView& m, const CUtensorMap& wmap, const CUtensorMap& xmap, const float* xscale, float* y,
+                      int tokens, cudaStream_t stream, int* err) {
+  auto kern = gemm_tc_kernel<DT, BN, F16>;
   constexpr int smem = GLay<DT, BN>::TOTAL;
   static bool ready = false;
   if (!ready) {
@@ -499,12 +653,13 @@ cudaError_t launch_bn(const MatView& m, const CUtensorMap& wmap, const CUtensorM
     ready = true;
   }
   dim3 grid((unsigned)((m.rows + BM - 1) / BM), (unsigned)((tokens + BN - 1) / BN));
-  kern<<<grid, TC_THREADS, smem, stream>>>(wmap, (int)m.rows, (int)m.cols, tokens, xmap, y, err);
+  kern<<<grid, TC_THREADS, smem, stream>>>(wmap, (int)m.rows, (int)m.cols, tokens, xmap, xscale, y, err);
   return cudaGetLastError();
 }
 
-template <int DT>
-cudaError_t launch_dt(const MatView& m, const __nv_bfloat16* xb, float* y, int tokens, cudaStream_t stream, int* err) {
+template <int DT, bool F16>
+cudaError_t launch_dt(const MatView& m, const void* xb, const float* xscale, float* y, int tokens, cudaStream_t stream,
+                      int* err) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
   const int bn = tokens > 128 ? 256 : tokens > 64 ? 128 : 64;
@@ -513,7 +668,7 @@ cudaError_t launch_dt(const MatView& m, const __nv_bfloat16* xb, float* y, int t
   const cuuint64_t strides[1] = {(cuuint64_t)m.cols * 2};
   const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)bn};
   const cuuint32_t estr[2] = {1, 1};
-  if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)xb, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  if (enc(&xmap, F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)xb, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return cudaErrorInvalidValue;
   // packed weights as rows of 32-bit words; one box = 128 rows x the ring pitch
@@ -524,9 +679,9 @@ cudaError_t launch_dt(const MatView& m, const __nv_bfloat16* xb, float* y, int t
   if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)m.w, wdims, wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return cudaErrorInvalidValue;
-  if (bn == 256) return launch_bn<DT, 256>(m, wmap, xmap, y, tokens, stream, err);
-  if (bn == 128) return launch_bn<DT, 128>(m, wmap, xmap, y, tokens, stream, err);
-  return launch_bn<DT, 64>(m, wmap, xmap, y, tokens, stream, err);
+  if (bn == 256) return launch_bn<DT, 256, F16>(m, wmap, xmap, xscale, y, tokens, stream, err);
+  if (bn == 128) return launch_bn<DT, 128, F16>(m, wmap, xmap, xscale, y, tokens, stream, err);
+  return launch_bn<DT, 64, F16>(m, wmap, xmap, xscale, y, tokens, stream, err);
 }
 
 }  // namespace
@@ -538,26 +693,61 @@ bool gemm_tc_supported(const MatView& m, int64_t tokens) {
   return ((uintptr_t)m.w & 15) == 0;
 }
 
-size_t gemm_tc_scratch_bytes(const MatView& m, int64_t tokens) { return (size_t)tokens * (size_t)m.cols * 2; }
+// 16-bit activations, then one f32 scale per activation row (binary16 path)
+size_t gemm_tc_scratch_bytes(const MatView& m, int64_t tokens) {
+  return ((size_t)tokens * (size_t)m.cols * 2 + 255) / 256 * 256 + (size_t)tokens * 4;
+}
+
+cudaError_t launch_weight_bound(const MatView& m, unsigned int* out_dev, cudaStream_t stream, uint64_t* launches) {
+  const int64_t nb = m.rows * (m.cols / (m.dtype == DT_Q4_K ? 256 : 32));
+  int64_t blocks = (nb + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  cudaError_t e = cudaMemsetAsync(out_dev, 0, sizeof(unsigned int), stream);
+  if (e != cudaSuccess) return e;
+  switch (m.dtype) {
+    case DT_Q4_K: weight_bound_kernel<DT_Q4_K><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
+    case DT_Q8_0: weight_bound_kernel<DT_Q8_0><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
+    case DT_Q5_0: weight_bound_kernel<DT_Q5_0><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
+    case DT_Q5_1: weight_bound_kernel<DT_Q5_1><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
+    default: return cudaErrorInvalidValue;
+  }
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+bool weight_bound_allows_f16(unsigned int bound_bits) {
+  float b;
+  static_assert(sizeof(b) == sizeof(bound_bits), "float bits");
+  memcpy(&b, &bound_bits, sizeof(b));
+  return bound_bits < 0x7f800000u && b < 30000.f && b > 1.f / 256.f;
+}
 
 cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t tokens, void* scratch,
                            cudaStream_t stream, int* err_flag, uint64_t* launches) {
-  __nv_bfloat16* xb = (__nv_bfloat16*)scratch;
   const int64_t n = tokens * m.cols;
-  int64_t blocks = (n / 4 + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  if (blocks < 1) blocks = 1;
-  to_bf16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, xb, n);
+  const bool f16 = m.f16_ok == 1;
+  float* xscale = (float*)((char*)scratch + ((size_t)n * 2 + 255) / 256 * 256);
+  if (f16) {
+    to_f16_rows_kernel<<<(unsigned)tokens, 256, 0, stream>>>(x, (__half*)scratch, xscale, (int)m.cols);
+  } else {
+    int64_t blocks = (n / 4 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
+    to_bf16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, (__nv_bfloat16*)scratch, n);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   if (launches) ++*launches;
+#define LLR_TC(D) (f16 ? launch_dt<D, true>(m, scratch, xscale, y, (int)tokens, stream, err_flag) \
+                       : launch_dt<D, false>(m, scratch, nullptr, y, (int)tokens, stream, err_flag))
   switch (m.dtype) {
-    case DT_Q4_K: e = launch_dt<DT_Q4_K>(m, xb, y, (int)tokens, stream, err_flag); break;
-    case DT_Q8_0: e = launch_dt<DT_Q8_0>(m, xb, y, (int)tokens, stream, err_flag); break;
-    case DT_Q5_0: e = launch_dt<DT_Q5_0>(m, xb, y, (int)tokens, stream, err_flag); break;
-    case DT_Q5_1: e = launch_dt<DT_Q5_1>(m, xb, y, (int)tokens, stream, err_flag); break;
+    case DT_Q4_K: e = LLR_TC(DT_Q4_K); break;
+    case DT_Q8_0: e = LLR_TC(DT_Q8_0); break;
+    case DT_Q5_0: e = LLR_TC(DT_Q5_0); break;
+    case DT_Q5_1: e = LLR_TC(DT_Q5_1); break;
     default: return cudaErrorInvalidValue;
   }
+#undef LLR_TC
   if (e == cudaSuccess && launches) ++*launches;
   return e;
 }
@@ -567,7 +757,9 @@ cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t t
 // demand.  This variant uses a fixed array that is part of the library image instead, so the
 // call path contains no allocation at all.  Every GPU that loads the library holds these
 // bytes until the process exits.
-static __device__ __align__(256) unsigned char g_static_scratch[GEMM_STATIC_SCRATCH_BYTES];
+// the stated limit applies to the 16-bit activations; the per-row scales of the binary16 path (at most
+// 256 KB for shapes within the limit) lie behind them
+static __device__ __align__(256) unsigned char g_static_scratch[GEMM_STATIC_SCRATCH_BYTES + (512 << 10)];
 
 size_t gemm_tc_static_scratch_limit() { return GEMM_STATIC_SCRATCH_BYTES; }
 

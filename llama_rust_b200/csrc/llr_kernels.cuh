@@ -23,6 +23,7 @@ struct MatView {
   int dtype;
   int64_t rows, cols;
   int64_t row_bytes;
+  int f16_ok = -1;  // tensor-core GEMM operand choice: 1 binary16 (weights fit its range), 0 bfloat16, -1 not examined (bfloat16)
 };
 
 enum GemvPath : int { PATH_AUTO = 0, PATH_GENERIC = 1, PATH_STAGED = 2, PATH_MMA = 3, PATH_TC = 4 };
@@ -104,6 +105,10 @@ int program_entries(const Program* p);
 // dequant -> shared memory -> tcgen05/TMEM chunk GEMM (bf16 operands, f32 accumulate) for
 // Q4_K / Q8_0 / Q5_0 / Q5_1 with many activation rows; see llr_gemm_tc.cu.
 bool gemm_tc_supported(const MatView& m, int64_t tokens);
+// Examines the block headers of a matrix the GEMM can take: writes the bit pattern of the largest
+// possible |weight| to *out_dev (device); weight_bound_allows_f16 turns that into the operand choice.
+cudaError_t launch_weight_bound(const MatView& m, unsigned int* out_dev, cudaStream_t stream, uint64_t* launches);
+bool weight_bound_allows_f16(unsigned int bound_bits);
 size_t gemm_tc_scratch_bytes(const MatView& m, int64_t tokens);
 cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t tokens, void* scratch,
                            cudaStream_t stream, int* err_flag, uint64_t* launches);
