@@ -759,6 +759,11 @@ int llr_exec_synchronize(llr_exec* e) {
 // ---------------------------------------------------------------- routed experts
 namespace {
 
+// Grouped expert products: with the automatic choice the tensor-core GEMM takes over from 16 routed
+// rows (two passes of the 8-row decode kernel already cost more than one GEMM launch); below that,
+// and for formats the GEMM does not take, the f32-faithful decode kernels run.
+int expert_path(const llr_exec* e, size_t n_rows) { return e->path == PATH_AUTO && n_rows >= 16 ? PATH_TC : e->path; }
+
 cudaError_t matmul_dev(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, float* y, int path) {
   void* scratch = nullptr;
   const int saved = e->path;
@@ -813,7 +818,12 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
   int* d_rows_of_tok = d_tok_of_row + n_rows;
   if ((ce = cudaMemcpyAsync(d_x, x, nx * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess) return fail_cuda(e, ce, "activation upload");
   // router product (decode.rs:9977), then routing on the host as the reference does
-  if ((ce = matmul_dev(e, L->router, tokens, d_x, d_logits, PATH_MMA)) != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
+  if (L->router->dtype == DT_F32 && ((uintptr_t)L->router->dev & 15) == 0)
+    ce = launch_router_logits((const float*)L->router->dev, d_x, d_logits, (int)tokens, (int)n_exp, (int)n_embd, e->stream,
+                              &e->ctr.launches);
+  else
+    ce = matmul_dev(e, L->router, tokens, d_x, d_logits, PATH_MMA);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
   std::vector<float> logits(tokens * n_exp);
   if ((ce = cudaMemcpyAsync(logits.data(), d_logits, logits.size() * 4, cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
       (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)
@@ -869,13 +879,23 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
       (ce = cudaMemcpyAsync(d_w, w_of_tok.data(), n_rows * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess ||
       (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)  // the host vectors go out of scope later, but keep it simple
     return fail_cuda(e, ce, "routing upload");
+  {  // size the GEMM staging buffer once, for the busiest expert's widest product: growing it between
+     // launches would free and reallocate, which synchronizes the device
+    size_t busiest = 0, most = 0;
+    for (size_t ex = 0; ex < n_exp; ++ex)
+      if ((size_t)(first_row[ex + 1] - first_row[ex]) > most) { most = (size_t)(first_row[ex + 1] - first_row[ex]); busiest = ex; }
+    void* unused = nullptr;
+    if (most > 0 && ((ce = ensure_scratch(e, L->down[busiest], most, &unused)) != cudaSuccess ||
+                     (ce = ensure_scratch(e, L->gate[busiest], most, &unused)) != cudaSuccess))
+      return fail_cuda(e, ce, "kernel scratch");
+  }
   if ((ce = launch_gather_rows(d_x, d_tok_of_row, d_pack, (int)n_rows, (int)n_embd, e->stream, &e->ctr.launches)) != cudaSuccess)
     return fail_cuda(e, ce, "kernel launch");
   for (size_t ex = 0; ex < n_exp; ++ex) {
     const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
     if (n == 0) continue;
-    if ((ce = matmul_dev(e, L->gate[ex], n, d_pack + r0 * n_embd, d_g + r0 * n_ff, e->path)) != cudaSuccess ||
-        (ce = matmul_dev(e, L->up[ex], n, d_pack + r0 * n_embd, d_u + r0 * n_ff, e->path)) != cudaSuccess)
+    if ((ce = matmul_dev(e, L->gate[ex], n, d_pack + r0 * n_embd, d_g + r0 * n_ff, expert_path(e, n))) != cudaSuccess ||
+        (ce = matmul_dev(e, L->up[ex], n, d_pack + r0 * n_embd, d_u + r0 * n_ff, expert_path(e, n))) != cudaSuccess)
       return fail_cuda(e, ce, "kernel launch");
   }
   if ((ce = launch_silu_mul(d_g, d_u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess)
@@ -883,20 +903,25 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
   for (size_t ex = 0; ex < n_exp; ++ex) {
     const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
     if (n == 0) continue;
-    if ((ce = matmul_dev(e, L->down[ex], n, d_g + r0 * n_ff, d_y + r0 * n_embd, e->path)) != cudaSuccess)
+    if ((ce = matmul_dev(e, L->down[ex], n, d_g + r0 * n_ff, d_y + r0 * n_embd, expert_path(e, n))) != cudaSuccess)
       return fail_cuda(e, ce, "kernel launch");
   }
   if ((ce = launch_scatter_combine(d_y, d_rows_of_tok, d_w, d_out, (int)tokens, (int)n_used, (int)n_embd, e->stream,
                                    &e->ctr.launches)) != cudaSuccess)
     return fail_cuda(e, ce, "kernel launch");
-  if ((ce = grow_pinned(&e->pin_y, &e->pin_y_cap, nx)) != cudaSuccess) return fail_cuda(e, ce, "pinned result staging");
-  if ((ce = cudaMemcpyAsync(e->pin_y, d_out, nx * 4, cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
+  const bool out_pinned = is_pinned_host(e, out);  // a pinned result buffer is written directly
+  float* dst = out;
+  if (!out_pinned) {
+    if ((ce = grow_pinned(&e->pin_y, &e->pin_y_cap, nx)) != cudaSuccess) return fail_cuda(e, ce, "pinned result staging");
+    dst = e->pin_y;
+  }
+  if ((ce = cudaMemcpyAsync(dst, d_out, nx * 4, cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
       (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)
     return fail_cuda(e, ce, "result download");
   if (take_device_error(e) != 0) {
     return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations");
   }
-  std::memcpy(out, e->pin_y, nx * 4);
+  if (!out_pinned) std::memcpy(out, e->pin_y, nx * 4);
   if (sel_ids) std::memcpy(sel_ids, ids.data(), n_rows * 4);
   if (sel_w) std::memcpy(sel_w, wts.data(), n_rows * 4);
   e->ctr.h2d_bytes += nx * 4 + 3 * n_rows * 4;

@@ -123,6 +123,9 @@ cudaError_t launch_gemm_tc_static(int device, const MatView& m, const float* x, 
 cudaError_t launch_gather_rows(const float* x, const int* tok_of_row, float* packed, int n_rows, int n_embd,
                                cudaStream_t s, uint64_t* launches);
 cudaError_t launch_silu_mul(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches);
+// logits[t*n_expert + e] = dot(w[e], x[t]) for an F32 router matrix (n_embd % 4 == 0, 16-byte aligned)
+cudaError_t launch_router_logits(const float* w, const float* x, float* logits, int tokens, int n_expert, int n_embd,
+                                 cudaStream_t s, uint64_t* launches);
 cudaError_t launch_scatter_combine(const float* y, const int* rows_of_tok, const float* w_of_tok, float* out,
                                    int tokens, int n_used, int n_embd, cudaStream_t s, uint64_t* launches);
 

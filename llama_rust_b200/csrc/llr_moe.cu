@@ -20,6 +20,27 @@ __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __res
   for (int i = threadIdx.x; i < n_embd / 4; i += blockDim.x) dst[i] = src[i];
 }
 
+// Router logits for an F32 router (ffn_gate_inp, decode.rs:9977): a matrix with a handful of rows
+// against every token.  One CTA per token, one warp per expert (striding when there are more
+// experts than warps), f32 FMA over float4 loads, warp-shuffle reduction.  The general decode
+// kernels are built for thousands of rows and leave the GPU idle on eight.
+__global__ void router_logits_kernel(const float* __restrict__ w, const float* __restrict__ x, float* __restrict__ logits,
+                                     int n_expert, int n_embd) {
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  const float4* xr = (const float4*)(x + (int64_t)t * n_embd);
+  for (int e = warp; e < n_expert; e += nwarp) {
+    const float4* wr = (const float4*)(w + (int64_t)e * n_embd);
+    float acc = 0.0f;
+    for (int i = lane; i < n_embd / 4; i += 32) {
+      const float4 a = __ldg(wr + i), b = xr[i];
+      acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(~0u, acc, o);
+    if (lane == 0) logits[(int64_t)t * n_expert + e] = acc;
+  }
+}
+
 __global__ void silu_mul_kernel(float* __restrict__ g, const float* __restrict__ u, int64_t n) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const float v = g[i];
@@ -50,6 +71,13 @@ cudaError_t launch_gather_rows(const float* x, const int* tok_of_row, float* pac
                                cudaStream_t s, uint64_t* launches) {
   if (n_rows <= 0) return cudaSuccess;
   gather_rows_kernel<<<n_rows, 256, 0, s>>>(x, tok_of_row, packed, n_rows, n_embd);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_router_logits(const float* w, const float* x, float* logits, int tokens, int n_expert, int n_embd,
+                                 cudaStream_t s, uint64_t* launches) {
+  router_logits_kernel<<<(unsigned)tokens, 256, 0, s>>>(w, x, logits, n_expert, n_embd);
   if (launches) ++*launches;
   return cudaGetLastError();
 }

@@ -217,14 +217,15 @@ class Executor:
                                                      peers, C.byref(h)))
         return Program(self, h.value, len(entries))
 
-    def moe_ffn(self, router: Matrix, gate, up, down, n_used: int, norm_w: bool, x):
-        """One routed-expert FFN layer (llr_moe_ffn).  Returns (out, sel_ids, sel_w)."""
+    def moe_ffn(self, router: Matrix, gate, up, down, n_used: int, norm_w: bool, x, out=None):
+        """One routed-expert FFN layer (llr_moe_ffn).  Returns (out, sel_ids, sel_w); `out` may be a
+        caller-owned (e.g. pinned) float32 array of x's shape."""
         n_expert = len(gate)
         arrs = [(C.c_void_p * n_expert)(*[m._h for m in lst]) for lst in (gate, up, down)]
         layer = _lib.MoeLayer(n_expert, n_used, int(norm_w), router._h, arrs[0], arrs[1], arrs[2])
         xs = np.ascontiguousarray(x, np.float32).reshape(-1, router.cols)
         tokens = xs.shape[0]
-        out = np.empty_like(xs)
+        out = np.empty_like(xs) if out is None else out
         ids = np.empty((tokens, n_used), np.int32)
         w = np.empty((tokens, n_used), np.float32)
         self._check(lib().llr_moe_ffn(self._h, C.byref(layer), tokens, xs.ctypes.data, xs.size, out.ctypes.data,
