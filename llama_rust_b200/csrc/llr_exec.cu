@@ -803,7 +803,9 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
   const size_t n_rows = tokens * n_used;
   // device workspace, one block: x | logits | packed x | g | u | y | out | int tables | weights
   const size_t f_x = nx, f_logits = tokens * n_exp, f_pack = n_rows * n_embd, f_g = n_rows * n_ff, f_y = n_rows * n_embd;
-  const size_t floats = f_x + f_logits + f_pack + 2 * f_g + f_y + nx + n_rows /*w*/ + 2 * n_rows /*int tables*/ + 64;
+  // grouped tensor-core path: 16-bit copies of the packed activations and of silu(g)*u, one scale per row, descriptors
+  const size_t f_x16 = (f_pack + f_g) / 2 + 2 * n_rows + 512, f_desc = gemm_tc_group_desc_bytes((int)(2 * n_exp)) / 4 + 64;
+  const size_t floats = f_x + f_logits + f_pack + 2 * f_g + f_y + nx + n_rows /*w*/ + 2 * n_rows /*int tables*/ + 64 + f_x16 + f_desc;
   cudaError_t ce;
   if ((ce = grow_device(&e->dev_moe, &e->dev_moe_cap, floats)) != cudaSuccess) return fail_cuda(e, ce, "expert workspace");
   float* d_x = e->dev_moe;
@@ -816,6 +818,12 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
   float* d_w = d_out + nx;
   int* d_tok_of_row = (int*)(d_w + n_rows);
   int* d_rows_of_tok = d_tok_of_row + n_rows;
+  auto align256 = [](void* p) { return (char*)(((uintptr_t)p + 255) & ~(uintptr_t)255); };
+  char* d_x16a = align256(d_rows_of_tok + n_rows);           // n_rows x n_embd, 16-bit
+  char* d_x16b = align256(d_x16a + n_rows * n_embd * 2);     // n_rows x n_ff, 16-bit
+  float* d_sa = (float*)align256(d_x16b + n_rows * n_ff * 2);
+  float* d_sb = d_sa + n_rows;
+  void* d_desc = align256(d_sb + n_rows);
   if ((ce = cudaMemcpyAsync(d_x, x, nx * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess) return fail_cuda(e, ce, "activation upload");
   // router product (decode.rs:9977), then routing on the host as the reference does
   if (L->router->dtype == DT_F32 && ((uintptr_t)L->router->dev & 15) == 0)
@@ -891,16 +899,50 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
   }
   if ((ce = launch_gather_rows(d_x, d_tok_of_row, d_pack, (int)n_rows, (int)n_embd, e->stream, &e->ctr.launches)) != cudaSuccess)
     return fail_cuda(e, ce, "kernel launch");
-  for (size_t ex = 0; ex < n_exp; ++ex) {
+  // Grouped tensor-core path (automatic choice, 64 routed rows or more, formats the GEMM takes): the tiles of
+  // all experts' gate and up products in one launch, silu(g)*u, all down products in one launch.
+  bool grouped = e->path == PATH_AUTO && n_rows >= 64;
+  int f16a = 1, f16b = 1;
+  for (size_t ex = 0; ex < n_exp && grouped; ++ex) {
+    const MatView vg = view_of(L->gate[ex]), vu = view_of(L->up[ex]), vd = view_of(L->down[ex]);
+    grouped = gemm_tc_supported(vg, 16) && gemm_tc_supported(vu, 16) && gemm_tc_supported(vd, 16) &&
+              vg.dtype == view_of(L->gate[0]).dtype && vu.dtype == vg.dtype && vd.dtype == view_of(L->down[0]).dtype;
+    if (vg.f16_ok != 1 || vu.f16_ok != 1) f16a = 0;
+    if (vd.f16_ok != 1) f16b = 0;
+  }
+  if (grouped) {
+    std::vector<GemmGroupSpec> specs;
+    for (size_t ex = 0; ex < n_exp; ++ex) {
+      const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
+      if (n == 0) continue;
+      specs.push_back(GemmGroupSpec{view_of(L->gate[ex]), d_x16a + r0 * n_embd * 2, d_sa + r0, d_g + r0 * n_ff, (int)n});
+      specs.push_back(GemmGroupSpec{view_of(L->up[ex]), d_x16a + r0 * n_embd * 2, d_sa + r0, d_u + r0 * n_ff, (int)n});
+    }
+    if ((ce = tc_convert_activations(d_pack, (int64_t)n_rows, (int)n_embd, f16a != 0, d_x16a, d_sa, e->stream, &e->ctr.launches)) != cudaSuccess ||
+        (ce = launch_gemm_tc_grouped(specs.data(), (int)specs.size(), f16a != 0, d_desc, e->stream, e->err_flag, &e->ctr.launches)) != cudaSuccess ||
+        (ce = launch_silu_mul(d_g, d_u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess)
+      return fail_cuda(e, ce, "kernel launch");
+    specs.clear();
+    for (size_t ex = 0; ex < n_exp; ++ex) {
+      const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
+      if (n == 0) continue;
+      specs.push_back(GemmGroupSpec{view_of(L->down[ex]), d_x16b + r0 * n_ff * 2, d_sb + r0, d_y + r0 * n_embd, (int)n});
+    }
+    // the descriptor buffer is reused: stream order puts this copy after the first grouped launch
+    if ((ce = tc_convert_activations(d_g, (int64_t)n_rows, (int)n_ff, f16b != 0, d_x16b, d_sb, e->stream, &e->ctr.launches)) != cudaSuccess ||
+        (ce = launch_gemm_tc_grouped(specs.data(), (int)specs.size(), f16b != 0, d_desc, e->stream, e->err_flag, &e->ctr.launches)) != cudaSuccess)
+      return fail_cuda(e, ce, "kernel launch");
+  }
+  for (size_t ex = 0; ex < n_exp && !grouped; ++ex) {
     const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
     if (n == 0) continue;
     if ((ce = matmul_dev(e, L->gate[ex], n, d_pack + r0 * n_embd, d_g + r0 * n_ff, expert_path(e, n))) != cudaSuccess ||
         (ce = matmul_dev(e, L->up[ex], n, d_pack + r0 * n_embd, d_u + r0 * n_ff, expert_path(e, n))) != cudaSuccess)
       return fail_cuda(e, ce, "kernel launch");
   }
-  if ((ce = launch_silu_mul(d_g, d_u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess)
+  if (!grouped && (ce = launch_silu_mul(d_g, d_u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess)
     return fail_cuda(e, ce, "kernel launch");
-  for (size_t ex = 0; ex < n_exp; ++ex) {
+  for (size_t ex = 0; ex < n_exp && !grouped; ++ex) {
     const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
     if (n == 0) continue;
     if ((ce = matmul_dev(e, L->down[ex], n, d_g + r0 * n_ff, d_y + r0 * n_embd, expert_path(e, n))) != cudaSuccess)

@@ -43,6 +43,7 @@
 
 #include <cstring>
 #include <type_traits>
+#include <vector>
 
 #include "llr_formats.cuh"
 #include "llr_kernels.cuh"
@@ -85,6 +86,14 @@ template <int DT, int BN> struct GLay {
   static constexpr int TOTAL = BAR + 1024 + 1024;
   static_assert((2 * NA + 2 * NB + 2 * NPK + 2) * 8 <= 1024, "barrier block");
   static_assert(TOTAL <= SMEM_LIMIT, "shared memory");
+};
+
+// one product of a grouped launch; tile_begin = first tile number of the product in the grid
+struct alignas(64) GemmGroup {
+  CUtensorMap wmap, xmap;
+  const float* xscale;
+  float* y;
+  int rows, cols, tokens, tile_begin;
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -354,11 +363,12 @@ __device__ __forceinline__ void dequant_sub_h(uint32_t prow, uint32_t (&out)[16]
   }
 }
 
+// One 128-row x BN-token tile.  The tensor maps are addressed generically: kernel parameters for a
+// single product, an array in global memory for a grouped launch.
 template <int DT, int BN, bool F16>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int tokens,
-               const __grid_constant__ CUtensorMap xmap, const float* __restrict__ xscale, float* __restrict__ Y,
-               int* __restrict__ err) {
+__device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CUtensorMap* xmap_p, int rows, int cols,
+                                             int tokens, const float* __restrict__ xscale, float* __restrict__ Y,
+                                             int row_tile, int tok_tile, int* __restrict__ err) {
   using L = GLay<DT, BN>;
   constexpr int NA = L::NA, NB = L::NB, NPK = L::NPK, PITCH = Pk<DT>::PITCH, RB = Pk<DT>::RB;
   extern __shared__ uint8_t smem_raw[];
@@ -374,7 +384,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
   uint64_t* acc_full = pk_empty + NPK;
   uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row0 = blockIdx.x * BM, tok0 = blockIdx.y * BN;
+  const int row0 = row_tile * BM, tok0 = tok_tile * BN;
   const int nms = cols / MACRO, nk = nms * (MACRO / BK);
 
   if (tid == 0) {
@@ -483,7 +493,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
         // x in 32-bit elements; x*4 = ms*RB is a multiple of 16 bytes.  Rows past the end read as zero.
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-            ::"r"(s32(sP + ps * L::P_STAGE)), "l"(&wmap), "r"(ms * (RB / 4)), "r"(row0), "r"(s32(&pk_full[ps])) : "memory");
+            ::"r"(s32(sP + ps * L::P_STAGE)), "l"(wmap_p), "r"(ms * (RB / 4)), "r"(row0), "r"(s32(&pk_full[ps])) : "memory");
       }
     }
   } else if (warp == W_ACT) {
@@ -497,7 +507,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
         bar_expect(&full_b[s], BN * 128);
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-            ::"r"(sb_u + (uint32_t)(s * L::B_STAGE)), "l"(&xmap), "r"(ks * BK), "r"(tok0), "r"(s32(&full_b[s])) : "memory");
+            ::"r"(sb_u + (uint32_t)(s * L::B_STAGE)), "l"(xmap_p), "r"(ks * BK), "r"(tok0), "r"(s32(&full_b[s])) : "memory");
       }
       __syncwarp();
     }
@@ -553,6 +563,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(L::TMEM_COLS) : "memory");
   }
+}
+
+template <int DT, int BN, bool F16>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int tokens,
+               const __grid_constant__ CUtensorMap xmap, const float* __restrict__ xscale, float* __restrict__ Y,
+               int* __restrict__ err) {
+  gemm_tc_tile<DT, BN, F16>(&wmap, &xmap, rows, cols, tokens, xscale, Y, (int)blockIdx.x, (int)blockIdx.y, err);
+}
+
+// Grouped launch (routed experts, decode.rs:10006 grouped_routed_ffn): the tiles of several
+// products in one grid.  groups[] lies in global memory; a CTA finds its product by its tile number.
+template <int DT, int BN, bool F16>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_grouped_kernel(const GemmGroup* __restrict__ groups, int n_groups, int* __restrict__ err) {
+  const int tile = (int)blockIdx.x;
+  int g = 0;
+  while (g + 1 < n_groups && tile >= groups[g + 1].tile_begin) ++g;
+  const GemmGroup* G = groups + g;
+  const int local = tile - G->tile_begin, row_tiles = (G->rows + BM - 1) / BM;
+  gemm_tc_tile<DT, BN, F16>(&G->wmap, &G->xmap, G->rows, G->cols, G->tokens, G->xscale, G->y, local % row_tiles,
+                            local / row_tiles, err);
 }
 
 __global__ void to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ o, int64_t n) {
@@ -748,6 +780,106 @@ cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t t
     default: return cudaErrorInvalidValue;
   }
 #undef LLR_TC
+  if (e == cudaSuccess && launches) ++*launches;
+  return e;
+}
+
+// ---- grouped launch --------------------------------------------------------------------
+namespace {
+template <int DT>
+bool encode_maps(const MatView& m, const void* x16, int tokens, int bn, bool f16, CUtensorMap* wmap, CUtensorMap* xmap) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)m.cols, (cuuint64_t)tokens};
+  const cuuint64_t strides[1] = {(cuuint64_t)m.cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)bn};
+  const cuuint32_t estr[2] = {1, 1};
+  if (enc(xmap, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)x16, dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  const cuuint64_t wdims[2] = {(cuuint64_t)(m.row_bytes / 4), (cuuint64_t)m.rows};
+  const cuuint64_t wstrides[1] = {(cuuint64_t)m.row_bytes};
+  const cuuint32_t wbox[2] = {(cuuint32_t)(Pk<DT>::PITCH / 4), (cuuint32_t)BM};
+  return enc(wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)m.w, wdims, wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int DT, int BN, bool F16>
+cudaError_t launch_grouped_bn(const GemmGroup* desc_dev, int n_groups, int tiles, cudaStream_t stream, int* err) {
+  auto kern = gemm_tc_grouped_kernel<DT, BN, F16>;
+  constexpr int smem = GLay<DT, BN>::TOTAL;
+  static bool ready = false;
+  if (!ready) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    ready = true;
+  }
+  kern<<<(unsigned)tiles, TC_THREADS, smem, stream>>>(desc_dev, n_groups, err);
+  return cudaGetLastError();
+}
+
+template <int DT>
+cudaError_t launch_grouped_dt(const GemmGroupSpec* specs, int n, bool f16, void* desc_dev, cudaStream_t stream, int* err) {
+  int max_tokens = 0;
+  for (int i = 0; i < n; ++i) max_tokens = specs[i].tokens > max_tokens ? specs[i].tokens : max_tokens;
+  const int bn = max_tokens > 128 ? 256 : max_tokens > 64 ? 128 : 64;
+  std::vector<GemmGroup> host((size_t)n);
+  int tiles = 0;
+  for (int i = 0; i < n; ++i) {
+    const GemmGroupSpec& sp = specs[i];
+    GemmGroup& g = host[(size_t)i];
+    if (!encode_maps<DT>(sp.m, sp.x16, sp.tokens, bn, f16, &g.wmap, &g.xmap)) return cudaErrorInvalidValue;
+    g.xscale = sp.xscale;
+    g.y = sp.y;
+    g.rows = (int)sp.m.rows;
+    g.cols = (int)sp.m.cols;
+    g.tokens = sp.tokens;
+    g.tile_begin = tiles;
+    tiles += (int)((sp.m.rows + BM - 1) / BM) * ((sp.tokens + bn - 1) / bn);
+  }
+  // pageable source: the copy is staged before this call returns, so `host` may go out of scope
+  cudaError_t e = cudaMemcpyAsync(desc_dev, host.data(), host.size() * sizeof(GemmGroup), cudaMemcpyHostToDevice, stream);
+  if (e != cudaSuccess) return e;
+  const GemmGroup* d = (const GemmGroup*)desc_dev;
+#define LLR_GROUPED(B) (f16 ? launch_grouped_bn<DT, B, true>(d, n, tiles, stream, err) : launch_grouped_bn<DT, B, false>(d, n, tiles, stream, err))
+  if (bn == 256) return LLR_GROUPED(256);
+  if (bn == 128) return LLR_GROUPED(128);
+  return LLR_GROUPED(64);
+#undef LLR_GROUPED
+}
+}  // namespace
+
+size_t gemm_tc_group_desc_bytes(int n_groups) { return (size_t)n_groups * sizeof(GemmGroup); }
+
+cudaError_t tc_convert_activations(const float* x, int64_t n_rows, int cols, bool f16, void* out16, float* xscale,
+                                   cudaStream_t stream, uint64_t* launches) {
+  if (f16) {
+    to_f16_rows_kernel<<<(unsigned)n_rows, 256, 0, stream>>>(x, (__half*)out16, xscale, cols);
+  } else {
+    const int64_t n = n_rows * cols;
+    int64_t blocks = (n / 4 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
+    to_bf16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, (__nv_bfloat16*)out16, n);
+  }
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gemm_tc_grouped(const GemmGroupSpec* specs, int n, bool f16, void* desc_dev, cudaStream_t stream,
+                                   int* err_flag, uint64_t* launches) {
+  if (n <= 0 || ((uintptr_t)desc_dev & 63) != 0) return cudaErrorInvalidValue;
+  for (int i = 0; i < n; ++i)
+    if (specs[i].m.dtype != specs[0].m.dtype || specs[i].tokens < 1 || !gemm_tc_supported(specs[i].m, 16)) return cudaErrorInvalidValue;
+  cudaError_t e;
+  switch (specs[0].m.dtype) {
+    case DT_Q4_K: e = launch_grouped_dt<DT_Q4_K>(specs, n, f16, desc_dev, stream, err_flag); break;
+    case DT_Q8_0: e = launch_grouped_dt<DT_Q8_0>(specs, n, f16, desc_dev, stream, err_flag); break;
+    case DT_Q5_0: e = launch_grouped_dt<DT_Q5_0>(specs, n, f16, desc_dev, stream, err_flag); break;
+    case DT_Q5_1: e = launch_grouped_dt<DT_Q5_1>(specs, n, f16, desc_dev, stream, err_flag); break;
+    default: return cudaErrorInvalidValue;
+  }
   if (e == cudaSuccess && launches) ++*launches;
   return e;
 }

@@ -109,6 +109,21 @@ bool gemm_tc_supported(const MatView& m, int64_t tokens);
 // possible |weight| to *out_dev (device); weight_bound_allows_f16 turns that into the operand choice.
 cudaError_t launch_weight_bound(const MatView& m, unsigned int* out_dev, cudaStream_t stream, uint64_t* launches);
 bool weight_bound_allows_f16(unsigned int bound_bits);
+// Grouped launch: several products of one dtype in one grid (routed experts).  x16 / xscale are
+// the group's activations as tc_convert_activations left them; desc_dev is device scratch of
+// gemm_tc_group_desc_bytes(n) bytes, 64-byte aligned.
+struct GemmGroupSpec {
+  MatView m;
+  const void* x16;
+  const float* xscale;
+  float* y;
+  int tokens;
+};
+size_t gemm_tc_group_desc_bytes(int n_groups);
+cudaError_t tc_convert_activations(const float* x, int64_t n_rows, int cols, bool f16, void* out16, float* xscale,
+                                   cudaStream_t stream, uint64_t* launches);
+cudaError_t launch_gemm_tc_grouped(const GemmGroupSpec* specs, int n_groups, bool f16, void* desc_dev,
+                                   cudaStream_t stream, int* err_flag, uint64_t* launches);
 size_t gemm_tc_scratch_bytes(const MatView& m, int64_t tokens);
 cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t tokens, void* scratch,
                            cudaStream_t stream, int* err_flag, uint64_t* launches);
