@@ -56,7 +56,7 @@ constexpr int BK = 64;      // columns per stage: 64 bf16 = one 128-byte swizzle
 constexpr int MACRO = 256;  // columns per packed-byte ring stage
 constexpr int DQ_WARPS = 16; // dequant warps: two groups of eight, alternating 64-column steps; the first eight also run the epilogue
 constexpr int W_PACKED = DQ_WARPS, W_ACT = DQ_WARPS + 1, W_MMA = DQ_WARPS + 2;
-constexpr int TC_THREADS = (DQ_WARPS + 3) * 32;
+constexpr int TC_THREADS = (DQ_WARPS + 4) * 32;  // + packed-byte, activation and two MMA issue warps
 constexpr int TC_SPIN = 1 << 24;
 constexpr int SMEM_LIMIT = 232448;  // 227 KB opt-in maximum per CTA
 
@@ -72,7 +72,12 @@ template <> struct Pk<DT_Q5_1> { static constexpr int RB = 192, PITCH = 208; };
 template <int DT, int BN> struct GLay {
   static constexpr int TMEM_COLS = 512;
   static constexpr int A_COLS = BK / 2;  // 64 bf16 per row = 32 columns of 32 bits
-  static constexpr int NA = (TMEM_COLS - BN) / A_COLS;
+  // MMA issue warps, each with its own accumulator (added in the epilogue): one thread can issue a
+  // 64-column step every ~475 cycles, which at BN <= 128 is slower than the tensor pipe and the
+  // dequant warps; two threads on alternating steps double that.  At BN = 256 tensor memory has no
+  // room for a second accumulator and the step is bound elsewhere.
+  static constexpr int NMMA = BN > 128 ? 1 : 2;
+  static constexpr int NA = (TMEM_COLS - NMMA * BN) / A_COLS;
   static constexpr int B_STAGE = BN * 128;
   static constexpr int NB = (128 * 1024) / B_STAGE;
   static constexpr int P_STAGE = BM * Pk<DT>::PITCH;
@@ -123,19 +128,6 @@ __device__ __forceinline__ bool bar_wait2(uint64_t* a, uint32_t pa, uint64_t* b,
     asm volatile(
         "{ .reg .pred p, q; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; mbarrier.try_wait.parity.shared::cta.b64 q, [%3], %4; "
         "and.pred p, p, q; selp.u32 %0, 1, 0, p; }"
-        : "=r"(ok) : "r"(s32(a)), "r"(pa), "r"(s32(b)), "r"(pb) : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-// two consecutive stages of each ring (adjacent barriers, same parity since the ring sizes are even)
-__device__ __forceinline__ bool bar_wait4(uint64_t* a, uint32_t pa, uint64_t* b, uint32_t pb) {
-  for (int spins = 0; spins < TC_SPIN; ++spins) {
-    uint32_t ok;
-    asm volatile(
-        "{ .reg .pred p, q, r, s; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; mbarrier.try_wait.parity.shared::cta.b64 q, [%1+8], %2; "
-        "mbarrier.try_wait.parity.shared::cta.b64 r, [%3], %4; mbarrier.try_wait.parity.shared::cta.b64 s, [%3+8], %4; "
-        "and.pred p, p, q; and.pred r, r, s; and.pred p, p, r; selp.u32 %0, 1, 0, p; }"
         : "=r"(ok) : "r"(s32(a)), "r"(pa), "r"(s32(b)), "r"(pb) : "memory");
     if (ok) return true;
   }
@@ -370,7 +362,7 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
                                              int tokens, const float* __restrict__ xscale, float* __restrict__ Y,
                                              int row_tile, int tok_tile, int* __restrict__ err) {
   using L = GLay<DT, BN>;
-  constexpr int NA = L::NA, NB = L::NB, NPK = L::NPK, PITCH = Pk<DT>::PITCH, RB = Pk<DT>::RB;
+  constexpr int NA = L::NA, NB = L::NB, NPK = L::NPK, NMMA = L::NMMA, PITCH = Pk<DT>::PITCH, RB = Pk<DT>::RB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms are 1024 bytes
   uint8_t* sB = smem + L::B;
@@ -391,7 +383,7 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
     for (int s = 0; s < NA; ++s) { bar_init(&full_a[s], DQ_WARPS / 2); bar_init(&empty_a[s], 1); }
     for (int s = 0; s < NB; ++s) { bar_init(&full_b[s], 1); bar_init(&empty_b[s], 1); }
     for (int s = 0; s < NPK; ++s) { bar_init(&pk_full[s], 1); bar_init(&pk_empty[s], DQ_WARPS); }
-    bar_init(acc_full, 1);
+    bar_init(acc_full, NMMA);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == W_MMA) {  // the MMA warp owns the tensor-memory allocation
@@ -409,10 +401,9 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
     // weight row inside the tile, column half of the step, step parity (the last two warp-uniform)
     const int r = tid & 127, h = (tid >> 7) & 1, g = tid >> 8;
     // this thread's A-operand words: lane = row (the warp's lane quarter is warp % 4), 16 columns per half
-    const uint32_t a_dst0 = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(BN + 16 * h);
-    auto step = [&](auto KQ, uint32_t prow, int ks) {
+    const uint32_t a_dst0 = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(NMMA * BN + 16 * h);
+    auto decode = [&](auto KQ, uint32_t prow, uint32_t (&out)[16]) {
       constexpr int kq = decltype(KQ)::value;
-      uint32_t out[16];
       if constexpr (F16) {
         if constexpr (DT == DT_Q4_K) dequant_sub_h<DT, -1>(prow, out, 2 * kq + h);
         else if (h == 0) dequant_sub_h<DT, 2 * kq>(prow, out);
@@ -422,32 +413,44 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
         else if (h == 0) dequant_sub<DT, 2 * kq>(prow, out);
         else dequant_sub<DT, 2 * kq + 1>(prow, out);
       }
-      const int s = ks % NA;
-      if (ok && !bar_wait(&empty_a[s], (uint32_t)(((ks / NA) & 1) ^ 1))) { ok = false; report_error(err, 3); }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    };
+    auto put = [&](const uint32_t (&out)[16], int s) {
       asm volatile(
           "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
           ::"r"(a_dst0 + (uint32_t)(s * L::A_COLS)), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]), "r"(out[4]), "r"(out[5]),
             "r"(out[6]), "r"(out[7]), "r"(out[8]), "r"(out[9]), "r"(out[10]), "r"(out[11]), "r"(out[12]), "r"(out[13]),
             "r"(out[14]), "r"(out[15]) : "memory");
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) bar_arrive(&full_a[s]);
     };
+    // Per macro-step a warp decodes both of its 64-column steps (g and g + 2) back to back: two
+    // independent instruction streams for the scheduler, and one round of barrier waits, tensor
+    // memory store completion and arrivals for two steps instead of one each.
+    static_assert(NA % 2 == 0 && NA >= 4, "a group's two steps of a macro-step use different stages");
     for (int ms = 0; ms < nms; ++ms) {
       const int ps = ms % NPK;
       if (ok && !bar_wait(&pk_full[ps], (uint32_t)((ms / NPK) & 1))) { ok = false; report_error(err, 3); }
       const uint32_t prow = s32(sP) + ps * L::P_STAGE + r * PITCH;
+      uint32_t o0[16], o1[16];
       if (g == 0) {
-        step(std::integral_constant<int, 0>{}, prow, 4 * ms);
-        step(std::integral_constant<int, 2>{}, prow, 4 * ms + 2);
+        decode(std::integral_constant<int, 0>{}, prow, o0);
+        decode(std::integral_constant<int, 2>{}, prow, o1);
       } else {
-        step(std::integral_constant<int, 1>{}, prow, 4 * ms + 1);
-        step(std::integral_constant<int, 3>{}, prow, 4 * ms + 3);
+        decode(std::integral_constant<int, 1>{}, prow, o0);
+        decode(std::integral_constant<int, 3>{}, prow, o1);
       }
       __syncwarp();
-      if (lane == 0) bar_arrive(&pk_empty[ps]);
+      if (lane == 0) bar_arrive(&pk_empty[ps]);  // the packed bytes are in registers now
+      const int ks0 = 4 * ms + g, ks1 = ks0 + 2, s0 = ks0 % NA, s1 = ks1 % NA;
+      if (ok && !bar_wait2(&empty_a[s0], (uint32_t)(((ks0 / NA) & 1) ^ 1), &empty_a[s1], (uint32_t)(((ks1 / NA) & 1) ^ 1))) {
+        ok = false;
+        report_error(err, 3);
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      put(o0, s0);
+      put(o1, s1);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) { bar_arrive(&full_a[s0]); bar_arrive(&full_a[s1]); }
     }
     // --------------------------------------------------------------- epilogue
     if (warp < 8) {
@@ -457,24 +460,27 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
     const int out_row = row0 + 32 * q + lane;
     constexpr int CPW = BN / 2;  // columns per warp
 #pragma unroll 1
-    for (int c0 = half * CPW; c0 < (half + 1) * CPW; c0 += 32) {
-      uint32_t v[32];
-      const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)c0;
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-          "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-            "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-            "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-            "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-          : "r"(taddr) : "memory");
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    for (int c0 = half * CPW; c0 < (half + 1) * CPW; c0 += 16) {
+      float acc[16];
+#pragma unroll
+      for (int a = 0; a < NMMA; ++a) {
+        uint32_t v[16];
+        const uint32_t taddr = tmem + ((uint32_t)(32 * q) << 16) + (uint32_t)(a * BN + c0);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+            : "r"(taddr) : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = a == 0 ? __uint_as_float(v[j]) : acc[j] + __uint_as_float(v[j]);
+      }
       if (out_row < rows) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < 16; ++j) {
           const int tok = tok0 + c0 + j;
           if (tok < tokens) {
-            float r = __uint_as_float(v[j]);
+            float r = acc[j];
             if constexpr (F16) r *= __ldg(xscale + tok);  // undo the activation row's power-of-two scale
             Y[(int64_t)tok * rows + out_row] = r;
           }
@@ -518,45 +524,41 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
     // A loop entered by a single lane pays a vector-to-uniform move per operand instead and
     // becomes the bottleneck of the CTA at small BN.
     constexpr uint32_t idesc = instr_desc<BN, F16>();
-    const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
-    const uint32_t sb_u = __shfl_sync(0xffffffffu, s32(sB), 0);
-    // steps per iteration: two where the rings are deep (one barrier round trip for both), one at
-    // BN = 256, whose activation ring has only four stages
-    constexpr int U = BN > 128 ? 1 : 2;
-    static_assert(NA % U == 0 && NB % U == 0, "steps per iteration");
-    for (int ks = 0; ks < nk; ks += U) {  // nk is a multiple of 4
-      const int sa = ks % NA, sb = ks % NB;
-      const uint32_t pa = (uint32_t)((ks / NA) & 1), pb = (uint32_t)((ks / NB) & 1);
-      if (ok && !(U == 2 ? bar_wait4(&full_a[sa], pa, &full_b[sb], pb) : bar_wait2(&full_a[sa], pa, &full_b[sb], pb))) {
-        ok = false;
-        report_error(err, 3);
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (elect_one()) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const uint32_t ta = tmem_u + (uint32_t)(BN + (sa + u) * L::A_COLS);
-          const uint64_t db = smem_desc_u(sb_u + (uint32_t)((sb + u) * L::B_STAGE));
+    const int mw = warp - W_MMA;  // which MMA warp: 64-column steps mw, mw + NMMA, ... into accumulator mw
+    if (mw < NMMA) {
+      const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+      const uint32_t sb_u = __shfl_sync(0xffffffffu, s32(sB), 0);
+      const uint32_t td = tmem_u + (uint32_t)(mw * BN);
+      for (int ks = mw; ks < nk; ks += NMMA) {  // nk is a multiple of 4
+        const int sa = ks % NA, sb = ks % NB;
+        if (ok && !bar_wait2(&full_a[sa], (uint32_t)((ks / NA) & 1), &full_b[sb], (uint32_t)((ks / NB) & 1))) {
+          ok = false;
+          report_error(err, 3);
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (elect_one()) {
+          const uint32_t ta = tmem_u + (uint32_t)(NMMA * BN + sa * L::A_COLS);
+          const uint64_t db = smem_desc_u(sb_u + (uint32_t)(sb * L::B_STAGE));
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
-            // 16 bf16 along K: eight 32-bit columns of A; 32 bytes inside B's swizzled row = 2 x 16-byte units
-            if (u == 0 && kk == 0 && ks == 0)
+            // 16 values along K: eight 32-bit columns of A; 32 bytes inside B's swizzled row = 2 x 16-byte units
+            if (kk == 0 && ks == mw)
               asm volatile("{ .reg .pred p; setp.ne.b32 p, 0, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
-                           ::"r"(tmem_u), "r"(ta), "l"(db), "r"(idesc) : "memory");
+                           ::"r"(td), "r"(ta), "l"(db), "r"(idesc) : "memory");
             else
               asm volatile("{ .reg .pred p; setp.eq.b32 p, 0, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
-                           ::"r"(tmem_u), "r"(ta + 8 * kk), "l"(db + 2 * kk), "r"(idesc) : "memory");
+                           ::"r"(td), "r"(ta + 8 * kk), "l"(db + 2 * kk), "r"(idesc) : "memory");
           }
           // free both stages once the MMAs that read them have completed
-          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&empty_a[sa + u])) : "memory");
-          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&empty_b[sb + u])) : "memory");
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&empty_a[sa])) : "memory");
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(&empty_b[sb])) : "memory");
         }
+        __syncwarp();
       }
+      if (elect_one())
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(acc_full)) : "memory");
       __syncwarp();
     }
-    if (elect_one())
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(acc_full)) : "memory");
-    __syncwarp();
   }
   __syncthreads();
   if (warp == W_MMA) {
