@@ -62,3 +62,40 @@ def test_tensor_core_gemm_matches_cpu_f32_reference(ex, orc, name, rows, cols, t
         check_gemv(y3, cpu2, exact, abs_sum, cols, f"{name} integer path M={tokens}")
     ex.set_path(0)
     m.free()
+
+
+def test_operand_format_follows_weight_range(ex, orc):
+    """binary16 operands (the default) are 8x more accurate than bfloat16 ones; a matrix whose block
+    scales would overflow binary16 is detected at upload and runs with bfloat16 operands instead of
+    producing infinities."""
+    kind, rows, cols, tokens = ALL["Q8_0"], 256, 1024, 64
+    rng = np.random.default_rng(77)
+    w = random_packed(rng, kind, rows, cols)
+    x = rng.standard_normal(tokens * cols).astype(np.float32)
+    cpu = orc.gemm(kind, cols, tokens, w, x, rows, simd=True)
+    ex.set_path(TC)
+    m = ex.upload(kind, rows, cols, w)
+    y = np.empty(rows * tokens, np.float32)
+    ex.gemm_resident(m, tokens, x, y)
+    rel = np.linalg.norm(y.reshape(tokens, rows) - cpu) / np.linalg.norm(cpu)
+    assert rel <= 8e-4, f"binary16 operands: relative L2 error {rel:.3e}"
+    m.free()
+    # the same quants with every block scale set to 2000: |w| up to 256000 does not fit binary16
+    big = w.copy().reshape(-1, 34)
+    big[:, 0:2] = np.frombuffer(np.float16(2000.0).tobytes(), np.uint8)
+    big = big.reshape(-1)
+    cpu_big = orc.gemm(kind, cols, tokens, big, x, rows, simd=True)
+    mb = ex.upload(kind, rows, cols, big)
+    yb = np.empty(rows * tokens, np.float32)
+    ex.gemm_resident(mb, tokens, x, yb)
+    assert np.all(np.isfinite(yb))
+    relb = np.linalg.norm(yb.reshape(tokens, rows) - cpu_big) / np.linalg.norm(cpu_big)
+    assert 8e-4 < relb <= 4e-3, f"bfloat16 operands expected for out-of-range weights: relative L2 error {relb:.3e}"
+    # huge activations do not matter: each activation row is rescaled by a power of two
+    ex.gemm_resident(m2 := ex.upload(kind, rows, cols, w), tokens, x * np.float32(1e20), y)
+    assert np.all(np.isfinite(y))
+    rel2 = np.linalg.norm(y.reshape(tokens, rows) - cpu * np.float32(1e20)) / np.linalg.norm(cpu * np.float32(1e20))
+    assert rel2 <= 8e-4
+    m2.free()
+    mb.free()
+    ex.set_path(0)

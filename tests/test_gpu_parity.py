@@ -343,3 +343,27 @@ def test_residency_is_content_addressed_and_bounded(monkeypatch, orc):
         e.matmul(Q8_0, 64, 256, 1, w[1], x, y)
     assert err.value.code == 8
     e.close()
+
+
+def test_pinned_and_pageable_buffers_give_the_same_bits():
+    """Decode-sized host-pointer calls deliver the result from the kernel into the caller's pinned
+    buffer (or a pinned staging buffer for pageable memory) and signal completion through a mapped
+    word; both routes and the copy-and-synchronize route must agree bit for bit."""
+    import torch
+    from llama_rust_b200 import Executor, synth
+    from helpers import Q4_K, Q6_K
+    ex = Executor(0)
+    for dt, rows, cols in ((Q4_K, 4096, 4096), (Q6_K, 1024, 14336)):
+        m = ex.synth(dt, rows, cols, 4242)
+        for tokens in (1, 3, 8, 11):
+            x = synth.activations(tokens * cols, 9).astype(np.float32)
+            y_pageable = np.full(tokens * rows, np.nan, np.float32)
+            ex.gemm_resident(m, tokens, x, y_pageable)
+            xp = torch.from_numpy(x).pin_memory()
+            yp = torch.full((tokens * rows,), float("nan")).pin_memory()
+            for _ in range(2):  # the completion ticket changes from call to call
+                yp.fill_(float("nan"))
+                ex.gemm_resident(m, tokens, xp.numpy(), yp.numpy())
+                assert np.array_equal(yp.numpy(), y_pageable)
+        m.free()
+    ex.close()
