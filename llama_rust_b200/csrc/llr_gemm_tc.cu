@@ -454,6 +454,7 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
     }
     // --------------------------------------------------------------- epilogue
     if (warp < 8) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // row scales from the conversion kernel; y may still be read by an earlier kernel
     if (ok && !bar_wait(acc_full, 0)) { ok = false; report_error(err, 3); }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int q = warp & 3, half = warp >> 2;  // TMEM lane quarter of this warp, column half
@@ -506,6 +507,7 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
     // ---------------------------------------------------- activation tiles (TMA)
     // the warp walks the ring converged (uniform registers for the addresses), one elected lane issues
     const uint32_t sb_u = __shfl_sync(0xffffffffu, s32(sB), 0);
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // the activations are the conversion kernel's output
     for (int ks = 0; ks < nk; ++ks) {
       const int s = ks % NB;
       if (ok && !bar_wait(&empty_b[s], (uint32_t)(((ks / NB) & 1) ^ 1))) { ok = false; report_error(err, 3); }
@@ -590,6 +592,8 @@ gemm_tc_grouped_kernel(const GemmGroup* __restrict__ groups, int n_groups, int* 
 }
 
 __global__ void to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ o, int64_t n) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
     if (i + 3 < n) {
       const float4 v = *(const float4*)(x + i);
@@ -606,6 +610,8 @@ __global__ void to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __res
 // to inv_scale[row] for the epilogue.  A zero or non-finite row is left unscaled.
 __global__ void to_f16_rows_kernel(const float* __restrict__ x, __half* __restrict__ o, float* __restrict__ inv_scale, int cols) {
   __shared__ float wmax[8];
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // x may come from the kernel before
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the GEMM may start its weight pipeline
   const float* xr = x + (int64_t)blockIdx.x * cols;
   __half* orow = o + (int64_t)blockIdx.x * cols;
   float m = 0.f;
@@ -686,9 +692,19 @@ cudaError_t launch_bn(const MatView& m, const CUtensorMap& wmap, const CUtensorM
     if (e != cudaSuccess) return e;
     ready = true;
   }
-  dim3 grid((unsigned)((m.rows + BM - 1) / BM), (unsigned)((tokens + BN - 1) / BN));
-  kern<<<grid, TC_THREADS, smem, stream>>>(wmap, (int)m.rows, (int)m.cols, tokens, xmap, xscale, y, err);
-  return cudaGetLastError();
+  // Programmatic dependent launch: the packed-weight pipeline and the dequantization start while the
+  // conversion kernel before it is still running; what depends on that kernel waits inside.
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((m.rows + BM - 1) / BM), (unsigned)((tokens + BN - 1) / BN));
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, wmap, (int)m.rows, (int)m.cols, tokens, xmap, xscale, y, err);
 }
 
 template <int DT, bool F16>

@@ -94,7 +94,8 @@ def test_operand_format_follows_weight_range(ex, orc):
     # huge activations do not matter: each activation row is rescaled by a power of two
     ex.gemm_resident(m2 := ex.upload(kind, rows, cols, w), tokens, x * np.float32(1e20), y)
     assert np.all(np.isfinite(y))
-    rel2 = np.linalg.norm(y.reshape(tokens, rows) - cpu * np.float32(1e20)) / np.linalg.norm(cpu * np.float32(1e20))
+    big_ref = cpu.astype(np.float64) * 1e20
+    rel2 = np.linalg.norm(y.reshape(tokens, rows).astype(np.float64) - big_ref) / np.linalg.norm(big_ref)
     assert rel2 <= 8e-4
     m2.free()
     mb.free()
