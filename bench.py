@@ -316,7 +316,7 @@ def run_ours(args):
                "h2d_bytes_per_step": sum(4 * M * cols for _, _, _, cols, *_ in mats),
                "d2h_bytes_per_step": sum(4 * M * rows for _, _, rows, *_ in mats),
                "ms_per_step": dt_s * 1e3, "tok_s": M / dt_s,
-               "api": "llr_gemm_resident with pinned host buffers: H2D x, kernel, D2H y, synchronize per matmul (225 per step)"}
+               "api": "llr_gemm_resident with pinned host buffers, 225 synchronous calls per step: H2D copy of x, kernel, the kernel stores y into the pinned host buffer and raises a completion word the call polls"}
 
     if world > 1 and sharded is not None:
         # end to end at N GPUs through the program API: per step every input vector goes host -> device,
