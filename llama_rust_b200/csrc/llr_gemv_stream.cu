@@ -281,7 +281,6 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
   bool ok = true;
   const float* cur_x = nullptr;
   int cur_cols = -1, cur_span = -1, cur_tokens = -1;
-  bool produced_here = false;
   // Programs: the entries of a phase are fetched into shared memory before the dependency
   // wait, so that after the wait the consumers do not pay a global-memory round trip for them.
   static_assert(sizeof(ProgEntry) == 64, "entry copy below moves eight 8-byte words per entry");
@@ -319,7 +318,6 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
         }
       }
       consumer_sync();
-      produced_here = true;
       cur_x = nullptr;  // the same buffer may hold new values now
     }
     for (int ei = 0; ei < P.n_entries && lo < hi; ++ei) {
@@ -334,7 +332,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
         const int span_cols = min(SPAN, E.cols - span * SPAN), nblk256 = span_cols >> 8;
         if (cur_x != E.x || cur_cols != E.cols || cur_span != span || cur_tokens != E.tokens) {
           consumer_sync();  // nobody still multiplies against the old planes
-          split_activations<MT>(E.x, E.cols, span * SPAN, nblk256, E.tokens, dig, sxf, xsi, warp, lane, produced_here);
+          split_activations<MT>(E.x, E.cols, span * SPAN, nblk256, E.tokens, dig, sxf, xsi, warp, lane);
           consumer_sync();
           cur_x = E.x; cur_cols = E.cols; cur_span = span; cur_tokens = E.tokens;
         }

@@ -48,7 +48,7 @@ cudaError_t launch_gemv_staged(const MatView& m, const float* x, float* y, int64
                                cudaStream_t stream, int sm_count, uint64_t* launches);
 
 // Integer tensor-core decode GEMV for Q4_K / Q6_K / Q8_0 (tokens <= 8 per pass); see
-// llr_gemv_mma.cu.  Launched with programmatic stream serialization.
+// llr_gemv_stream.cu.  Launched with programmatic stream serialization.
 bool gemv_mma_supported(const MatView& m);
 cudaError_t launch_gemv_mma(const MatView& m, const float* x, float* y, int64_t tokens,
                             cudaStream_t stream, int sm_count, int* err_flag, uint64_t* launches);
@@ -67,7 +67,7 @@ bool gemv_mma_hostout_ok(const MatView& m, int64_t tokens);
 cudaError_t launch_gemv_mma_hostout(const MatView& m, const float* x, float* y, int64_t tokens, const HostOut& ho,
                                     cudaStream_t stream, int sm_count, int* err_flag, uint64_t* launches);
 
-// One matrix product of a program (llr_gemv_prog.cu).  tile_begin / n_tiles are filled in
+// One matrix product of a program (llr_gemv_stream.cu).  tile_begin / n_tiles are filled in
 // by program_create.
 struct ProgEntry {
   const uint8_t* w;

@@ -280,16 +280,15 @@ __device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* ro
 
 // Activations of one span (nblk256 blocks of 256 columns starting at column col0, `tokens`
 // activation rows) -> four int8 digit planes per activation row, the f32 sums of x per 32
-// columns (Q4_K mins) and 2^-e per block.  One warp per (block, row); `coherent` selects
-// L2-coherent loads for activations that an earlier phase of the same launch produced.
+// columns (Q4_K mins) and 2^-e per block.  One warp per (block, row).  Loads are L2-coherent
+// (the activations may have been produced by an earlier phase of the same launch) and kept in L2.
 template <int MT>
 __device__ __forceinline__ void split_activations(const float* __restrict__ X, int cols, int col0,
                                                   int nblk256, int tokens, uint8_t* dig, float* sxf,
-                                                  float* xsi, int warp, int lane, bool coherent) {
+                                                  float* xsi, int warp, int lane) {
   // two jobs per warp and pass: both loads are in flight before either is used
   const int njobs = nblk256 * tokens;
   const uint64_t keep = l2_policy_evict_last();
-  (void)coherent;  // one load flavour: L2-coherent, kept in L2
   for (int job0 = warp; job0 < njobs; job0 += 2 * NWARP) {
    float4 pa[2], pb[2];
 #pragma unroll
