@@ -14,8 +14,9 @@ Prints one JSON line (rank 0).  `value` is the whole-job achieved HBM GB/s
 (algorithmic bytes of the sweep / device time, inputs resident in HBM); `e2e`
 is the same metric through the reference-facing host-pointer call
 (llr_gemv_resident: H2D of x, kernel, D2H of y and a synchronize per matmul);
-`roofline` is the dominant kernel (Q4_K decode GEMV) against the measured HBM
-peak; `cpu_baseline` is the CPU oracle (AVX2 row kernels, reference threading)
+`roofline` is the kernel the timed region consists of (the persistent program
+kernel; the Q4_K single-product launches are reported beside it) against the
+measured HBM peak; `cpu_baseline` is the CPU oracle (AVX2 row kernels, reference threading)
 on a bounded sample of the same sweep.
 """
 from __future__ import annotations
@@ -284,10 +285,26 @@ def run_ours(args):
     clock_rec = clocks.stop() if rank == 0 else None
     peak, peak_kind = load_peaks()
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "kernel": "gemv_stream_kernel<M, Q4_K>", "peak_kind": peak_kind,
-                "launches_timed": reps * len(dom), "avg_launch_us": dom_ms * 1e3 / (reps * len(dom)),
-                "avg_bytes_per_launch": dom_bytes / (reps * len(dom)), "frac_of_8tbs_nominal": achieved / 8000.0}
+    single = {"kernel": "gemv_stream_kernel<M, Q4_K> (one product per launch, programmatic dependent launch)",
+              "achieved": achieved, "frac": achieved / peak, "launches_timed": reps * len(dom),
+              "avg_launch_us": dom_ms * 1e3 / (reps * len(dom)), "avg_bytes_per_launch": dom_bytes / (reps * len(dom))}
+    if prog is not None:
+        # The timed region consists of launches of one kernel, the persistent program kernel (one per
+        # rank and step): its average launch duration is ms_step, its algorithmic bytes per launch are
+        # this rank's share of the sweep.  traffic: ncu dram bytes of the streaming kernel equal the
+        # algorithmic bytes within 0.03 % (profiles/gemv_stream_q4k_65536x4096_m1.md); not re-measured here.
+        per_rank = total_bytes / world
+        ach = per_rank / (ms_step * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                    "kernel": "gemv_sharded_program_kernel<M>" if world > 1 else "gemv_program_kernel<M>",
+                    "peak_kind": peak_kind, "launches_timed": args.steps, "avg_launch_us": ms_step * 1e3,
+                    "avg_bytes_per_launch": per_rank, "frac_of_8tbs_nominal": ach / 8000.0,
+                    "single_product_launches": single}
+    else:
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": None, "kernel": single["kernel"], "peak_kind": peak_kind,
+                    "launches_timed": single["launches_timed"], "avg_launch_us": single["avg_launch_us"],
+                    "avg_bytes_per_launch": single["avg_bytes_per_launch"], "frac_of_8tbs_nominal": achieved / 8000.0}
 
     # end to end through the reference-facing call: host buffers, copies inside the timed region
     e2e = None
