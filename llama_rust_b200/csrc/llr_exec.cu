@@ -116,7 +116,7 @@ struct llr_exec {
   int path = PATH_AUTO;
   int* err_flag = nullptr;  // device alias of err_pinned: set by a kernel whose bounded wait ran out
   volatile int* err_pinned = nullptr;  // the same word, mapped pinned host memory
-  struct PinSeen { const void* p; bool pinned; void* alias; } pin_seen[8] = {};
+  struct PinSeen { const void* p; bool pinned; } pin_seen[8] = {};
   int pin_next = 0;
   // result delivery by the kernel (HostOut): completion word (mapped pinned, after the error word),
   // its device alias, a device counter of finished CTAs, the ticket of the last such launch
@@ -299,26 +299,29 @@ cudaError_t ensure_scratch(llr_exec* e, const llr_matrix* m, size_t tokens, void
   return ce;
 }
 
-// Remembers the answer for the last few pointers: callers reuse their buffers, and a stale answer
-// is harmless either way (a pageable buffer taken for pinned is still copied correctly, only
-// slower; a pinned one taken for pageable goes through the staging buffer).
-bool is_pinned_host(llr_exec* e, const void* p, void** alias = nullptr) {
-  for (const auto& s : e->pin_seen)
-    if (s.p == p) {
-      if (alias) *alias = s.alias;
-      return s.pinned;
-    }
+// Is p pinned host memory, and where can kernels of this device address it?  Asked of the driver on
+// every call: the answer decides whether a kernel stores through the alias, and a remembered
+// answer for memory that has since been freed would turn into a wild store.
+bool pinned_alias(const void* p, void** alias) {
   cudaPointerAttributes a{};
-  bool pinned = false;
-  void* dev = nullptr;
-  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) cudaGetLastError();
-  else {
-    pinned = a.type == cudaMemoryTypeHost;
-    dev = pinned ? a.devicePointer : nullptr;  // where kernels of this device can address it, if mapped
-  }
-  e->pin_seen[e->pin_next] = {p, pinned, dev};
+  *alias = nullptr;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+  if (a.type != cudaMemoryTypeHost) return false;
+  *alias = a.devicePointer;
+  return true;
+}
+
+// Same question for buffers that are only copied from or to.  Remembers the answer for the last few
+// pointers: callers reuse their buffers, and a stale answer is harmless here (a pageable buffer taken
+// for pinned is still copied correctly, only slower; a pinned one taken for pageable goes through
+// the staging buffer).
+bool is_pinned_host(llr_exec* e, const void* p) {
+  for (const auto& s : e->pin_seen)
+    if (s.p == p) return s.pinned;
+  void* unused = nullptr;
+  const bool pinned = pinned_alias(p, &unused);
+  e->pin_seen[e->pin_next] = {p, pinned};
   e->pin_next = (e->pin_next + 1) % 8;
-  if (alias) *alias = dev;
   return pinned;
 }
 
@@ -356,7 +359,7 @@ int run_host(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, fl
     src = e->pin_x;
   }
   void* y_alias = nullptr;
-  const bool y_pinned = is_pinned_host(e, y, &y_alias);
+  const bool y_pinned = pinned_alias(y, &y_alias);
   float* dst = y;
   if (!y_pinned) {
     if ((ce = grow_pinned(&e->pin_y, &e->pin_y_cap, ny)) != cudaSuccess) return fail_cuda(e, ce, "pinned result staging");
