@@ -77,3 +77,38 @@ def test_program_rejects_what_it_cannot_run():
     assert e.value.code == 5
     other.close()
     ex.close()
+
+
+def test_sharded_program_validation_on_one_gpu():
+    """The argument checks of llr_program_create_sharded and the shared-arena calls need no second GPU."""
+    import torch
+    from llama_rust_b200 import Executor, NativeCudaError
+    from llama_rust_b200._lib import ARENA_HEADER_BYTES
+    ex = Executor(0)
+    m = ex.synth(Q4_K, 64, 4096, 1)          # this rank's 64 rows of a 128-row matrix
+    x = torch.zeros(4096, device="cuda")
+    arena_bytes = ARENA_HEADER_BYTES + 4 * 128
+    arena, handle = ex.shared_alloc(arena_bytes)
+    assert len(handle) == 64 and arena % 256 == 0
+    other, _ = ex.shared_alloc(arena_bytes)  # stands in for the peer's arena (same process: no IPC open needed)
+    y = arena + ARENA_HEADER_BYTES
+    ok = ex.sharded_program([(m, x.data_ptr(), y, 1, 0)], [128], arena, arena_bytes, 2, 0, [None, other])
+    ok.free()
+    bad = [
+        dict(world=1, rank=0, peers=[None]),                       # a sharded program needs at least two ranks
+        dict(world=9, rank=0, peers=[None] + [other] * 8),         # at most eight
+        dict(world=2, rank=2, peers=[None, other]),                # rank out of range
+        dict(world=2, rank=0, peers=[None, None]),                 # missing peer arena
+    ]
+    for kw in bad:
+        with pytest.raises(NativeCudaError):
+            ex.sharded_program([(m, x.data_ptr(), y, 1, 0)], [128], arena, arena_bytes, kw["world"], kw["rank"], kw["peers"])
+    with pytest.raises(NativeCudaError):  # result slice outside the arena
+        ex.sharded_program([(m, x.data_ptr(), arena + arena_bytes - 64, 1, 0)], [128], arena, arena_bytes, 2, 0, [None, other])
+    with pytest.raises(NativeCudaError):  # result slice inside the library's header
+        ex.sharded_program([(m, x.data_ptr(), arena, 1, 0)], [128], arena, arena_bytes, 2, 0, [None, other])
+    with pytest.raises(NativeCudaError):  # leading dimension smaller than the shard
+        ex.sharded_program([(m, x.data_ptr(), y, 1, 0)], [32], arena, arena_bytes, 2, 0, [None, other])
+    ex.shared_free(other)
+    ex.shared_free(arena)
+    ex.close()
