@@ -431,7 +431,7 @@ cudaError_t launch_matmul(const MatView& m, const float* x, float* y, int64_t to
                           void* scratch, uint64_t* launches) {
   const bool x_aligned = ((uintptr_t)x & 15) == 0 && (m.cols % 4 == 0);
   if (scratch && err_flag && x_aligned && matmul_wants_tc(m, tokens, path))
-    return launch_gemm_tc(m, x, y, tokens, scratch, stream, err_flag, launches);
+    return launch_gemm_tc(m, x, y, tokens, scratch, gemm_tc_scratch_bytes(m, tokens), stream, err_flag, launches);
   if (path == PATH_TC) path = PATH_AUTO;
   if ((path == PATH_AUTO || path == PATH_MMA) && x_aligned && err_flag && gemv_mma_supported(m))
     return launch_gemv_mma(m, x, y, tokens, stream, sm_count, err_flag, launches);

@@ -358,9 +358,9 @@ __device__ __forceinline__ void dequant_sub_h(uint32_t prow, uint32_t (&out)[16]
 // One 128-row x BN-token tile.  The tensor maps are addressed generically: kernel parameters for a
 // single product, an array in global memory for a grouped launch.
 template <int DT, int BN, bool F16>
-__device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CUtensorMap* xmap_p, int rows, int cols,
-                                             int tokens, const float* __restrict__ xscale, float* __restrict__ Y,
-                                             int row_tile, int tok_tile, int* __restrict__ err) {
+__device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CUtensorMap* xmap_p, int rows, int ms_begin,
+                                             int ms_count, int tokens, const float* __restrict__ xscale,
+                                             float* __restrict__ Y, int row_tile, int tok_tile, int* __restrict__ err) {
   using L = GLay<DT, BN>;
   constexpr int NA = L::NA, NB = L::NB, NPK = L::NPK, NMMA = L::NMMA, PITCH = Pk<DT>::PITCH, RB = Pk<DT>::RB;
   extern __shared__ uint8_t smem_raw[];
@@ -377,7 +377,7 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
   uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int row0 = row_tile * BM, tok0 = tok_tile * BN;
-  const int nms = cols / MACRO, nk = nms * (MACRO / BK);
+  const int nms = ms_count, nk = nms * (MACRO / BK);  // this CTA's share of K: macro-steps ms_begin .. ms_begin + nms
 
   if (tid == 0) {
     for (int s = 0; s < NA; ++s) { bar_init(&full_a[s], DQ_WARPS / 2); bar_init(&empty_a[s], 1); }
@@ -500,7 +500,7 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
         // x in 32-bit elements; x*4 = ms*RB is a multiple of 16 bytes.  Rows past the end read as zero.
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-            ::"r"(s32(sP + ps * L::P_STAGE)), "l"(wmap_p), "r"(ms * (RB / 4)), "r"(row0), "r"(s32(&pk_full[ps])) : "memory");
+            ::"r"(s32(sP + ps * L::P_STAGE)), "l"(wmap_p), "r"((ms_begin + ms) * (RB / 4)), "r"(row0), "r"(s32(&pk_full[ps])) : "memory");
       }
     }
   } else if (warp == W_ACT) {
@@ -515,7 +515,7 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
         bar_expect(&full_b[s], BN * 128);
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-            ::"r"(sb_u + (uint32_t)(s * L::B_STAGE)), "l"(xmap_p), "r"(ks * BK), "r"(tok0), "r"(s32(&full_b[s])) : "memory");
+            ::"r"(sb_u + (uint32_t)(s * L::B_STAGE)), "l"(xmap_p), "r"((ms_begin * (MACRO / BK) + ks) * BK), "r"(tok0), "r"(s32(&full_b[s])) : "memory");
       }
       __syncwarp();
     }
@@ -574,7 +574,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, int rows, int cols, int tokens,
                const __grid_constant__ CUtensorMap xmap, const float* __restrict__ xscale, float* __restrict__ Y,
                int* __restrict__ err) {
-  gemm_tc_tile<DT, BN, F16>(&wmap, &xmap, rows, cols, tokens, xscale, Y, (int)blockIdx.x, (int)blockIdx.y, err);
+  // split-K: gridDim.z CTAs share a tile's K range; slice z writes its partial sums to Y + z * tokens * rows
+  // (with one slice Y is the result itself), and a second kernel adds the slices in order
+  const int per = cols / MACRO / (int)gridDim.z;
+  gemm_tc_tile<DT, BN, F16>(&wmap, &xmap, rows, (int)blockIdx.z * per, per, tokens, xscale,
+                            Y + (size_t)blockIdx.z * (size_t)tokens * (size_t)rows, (int)blockIdx.x, (int)blockIdx.y, err);
+}
+
+__global__ void add_slices_kernel(const float* __restrict__ part, float* __restrict__ y, int64_t n, int slices) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
+    float4 acc = *(const float4*)(part + i);
+    for (int z = 1; z < slices; ++z) {  // ascending slice order: the result does not depend on scheduling
+      const float4 v = *(const float4*)(part + (int64_t)z * n + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *(float4*)(y + i) = acc;
+  }
 }
 
 // Grouped launch (routed experts, decode.rs:10006 grouped_routed_ffn): the tiles of several
@@ -587,7 +603,7 @@ gemm_tc_grouped_kernel(const GemmGroup* __restrict__ groups, int n_groups, int* 
   while (g + 1 < n_groups && tile >= groups[g + 1].tile_begin) ++g;
   const GemmGroup* G = groups + g;
   const int local = tile - G->tile_begin, row_tiles = (G->rows + BM - 1) / BM;
-  gemm_tc_tile<DT, BN, F16>(&G->wmap, &G->xmap, G->rows, G->cols, G->tokens, G->xscale, G->y, local % row_tiles,
+  gemm_tc_tile<DT, BN, F16>(&G->wmap, &G->xmap, G->rows, 0, G->cols / MACRO, G->tokens, G->xscale, G->y, local % row_tiles,
                             local / row_tiles, err);
 }
 
@@ -683,7 +699,7 @@ EncodeTiledFn encode_fn() {
 
 template <int DT, int BN, bool F16>
 cudaError_t launch_bn(const MatView& m, const CUtensorMap& wmap, const CUtensorMap& xmap, const float* xscale, float* y,
-                      int tokens, cudaStream_t stream, int* err) {
+                      int tokens, int splits, cudaStream_t stream, int* err) {
   auto kern = gemm_tc_kernel<DT, BN, F16>;
   constexpr int smem = GLay<DT, BN>::TOTAL;
   static bool ready = false;
@@ -698,7 +714,7 @@ cudaError_t launch_bn(const MatView& m, const CUtensorMap& wmap, const CUtensorM
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)((m.rows + BM - 1) / BM), (unsigned)((tokens + BN - 1) / BN));
+  cfg.gridDim = dim3((unsigned)((m.rows + BM - 1) / BM), (unsigned)((tokens + BN - 1) / BN), (unsigned)splits);
   cfg.blockDim = dim3(TC_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -708,8 +724,8 @@ cudaError_t launch_bn(const MatView& m, const CUtensorMap& wmap, const CUtensorM
 }
 
 template <int DT, bool F16>
-cudaError_t launch_dt(const MatView& m, const void* xb, const float* xscale, float* y, int tokens, cudaStream_t stream,
-                      int* err) {
+cudaError_t launch_dt(const MatView& m, const void* xb, const float* xscale, float* y, int tokens, int splits,
+                      cudaStream_t stream, int* err) {
   EncodeTiledFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
   const int bn = tokens > 128 ? 256 : tokens > 64 ? 128 : 64;
@@ -729,9 +745,9 @@ cudaError_t launch_dt(const MatView& m, const void* xb, const float* xscale, flo
   if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, (void*)m.w, wdims, wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return cudaErrorInvalidValue;
-  if (bn == 256) return launch_bn<DT, 256, F16>(m, wmap, xmap, xscale, y, tokens, stream, err);
-  if (bn == 128) return launch_bn<DT, 128, F16>(m, wmap, xmap, xscale, y, tokens, stream, err);
-  return launch_bn<DT, 64, F16>(m, wmap, xmap, xscale, y, tokens, stream, err);
+  if (bn == 256) return launch_bn<DT, 256, F16>(m, wmap, xmap, xscale, y, tokens, splits, stream, err);
+  if (bn == 128) return launch_bn<DT, 128, F16>(m, wmap, xmap, xscale, y, tokens, splits, stream, err);
+  return launch_bn<DT, 64, F16>(m, wmap, xmap, xscale, y, tokens, splits, stream, err);
 }
 
 }  // namespace
@@ -743,9 +759,24 @@ bool gemm_tc_supported(const MatView& m, int64_t tokens) {
   return ((uintptr_t)m.w & 15) == 0;
 }
 
-// 16-bit activations, then one f32 scale per activation row (binary16 path)
+// Split-K: a shape with few 128-row tiles and a long K (ffn_down: 32 tiles of 224 steps) would leave
+// most SMs idle.  The K range is cut into the largest power of two of slices that keeps the grid within
+// one wave of the 148 SMs and every slice at least 1024 columns long and a whole number of macro-steps.
+int gemm_tc_splits(const MatView& m, int64_t tokens) {
+  const int bn = tokens > 128 ? 256 : tokens > 64 ? 128 : 64;
+  const int64_t tiles = ((m.rows + BM - 1) / BM) * ((tokens + bn - 1) / bn);
+  const int64_t nms = m.cols / MACRO;
+  int s = 1;
+  while (s < 8 && tiles * (s * 2) <= 148 && nms % (s * 2) == 0 && nms / (s * 2) >= 4) s *= 2;
+  return s;
+}
+
+// 16-bit activations, one f32 scale per activation row (binary16 path), split-K partial sums
+static size_t tc_x16_bytes(const MatView& m, int64_t tokens) { return ((size_t)tokens * (size_t)m.cols * 2 + 255) / 256 * 256; }
+static size_t tc_scale_bytes(int64_t tokens) { return ((size_t)tokens * 4 + 255) / 256 * 256; }
 size_t gemm_tc_scratch_bytes(const MatView& m, int64_t tokens) {
-  return ((size_t)tokens * (size_t)m.cols * 2 + 255) / 256 * 256 + (size_t)tokens * 4;
+  const int s = gemm_tc_splits(m, tokens);
+  return tc_x16_bytes(m, tokens) + tc_scale_bytes(tokens) + (s > 1 ? (size_t)s * (size_t)tokens * (size_t)m.rows * 4 : 0);
 }
 
 cudaError_t launch_weight_bound(const MatView& m, unsigned int* out_dev, cudaStream_t stream, uint64_t* launches) {
@@ -772,11 +803,15 @@ bool weight_bound_allows_f16(unsigned int bound_bits) {
   return bound_bits < 0x7f800000u && b < 30000.f && b > 1.f / 256.f;
 }
 
-cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t tokens, void* scratch,
+cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t tokens, void* scratch, size_t scratch_bytes,
                            cudaStream_t stream, int* err_flag, uint64_t* launches) {
   const int64_t n = tokens * m.cols;
   const bool f16 = m.f16_ok == 1;
-  float* xscale = (float*)((char*)scratch + ((size_t)n * 2 + 255) / 256 * 256);
+  float* xscale = (float*)((char*)scratch + tc_x16_bytes(m, tokens));
+  float* part = (float*)((char*)xscale + tc_scale_bytes(tokens));
+  int splits = gemm_tc_splits(m, tokens);
+  if (scratch_bytes < gemm_tc_scratch_bytes(m, tokens)) splits = 1;  // a fixed-size staging area may not hold the slices
+  if (((uintptr_t)y & 15) != 0 || (tokens * m.rows) % 4 != 0) splits = 1;  // the slice adder works on aligned float4
   if (f16) {
     to_f16_rows_kernel<<<(unsigned)tokens, 256, 0, stream>>>(x, (__half*)scratch, xscale, (int)m.cols);
   } else {
@@ -788,8 +823,9 @@ cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t t
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   if (launches) ++*launches;
-#define LLR_TC(D) (f16 ? launch_dt<D, true>(m, scratch, xscale, y, (int)tokens, stream, err_flag) \
-                       : launch_dt<D, false>(m, scratch, nullptr, y, (int)tokens, stream, err_flag))
+  float* dst = splits > 1 ? part : y;
+#define LLR_TC(D) (f16 ? launch_dt<D, true>(m, scratch, xscale, dst, (int)tokens, splits, stream, err_flag) \
+                       : launch_dt<D, false>(m, scratch, nullptr, dst, (int)tokens, splits, stream, err_flag))
   switch (m.dtype) {
     case DT_Q4_K: e = LLR_TC(DT_Q4_K); break;
     case DT_Q8_0: e = LLR_TC(DT_Q8_0); break;
@@ -798,7 +834,16 @@ cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t t
     default: return cudaErrorInvalidValue;
   }
 #undef LLR_TC
-  if (e == cudaSuccess && launches) ++*launches;
+  if (e != cudaSuccess) return e;
+  if (launches) ++*launches;
+  if (splits > 1) {
+    const int64_t ny = tokens * m.rows;
+    int64_t blocks = (ny / 4 + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    add_slices_kernel<<<(unsigned)blocks, 256, 0, stream>>>(part, y, ny, splits);
+    e = cudaGetLastError();
+    if (e == cudaSuccess && launches) ++*launches;
+  }
   return e;
 }
 
@@ -925,7 +970,7 @@ cudaError_t launch_gemm_tc_static(int device, const MatView& m, const float* x, 
     if (e != cudaSuccess) return e;
     addr[device] = p;
   }
-  return launch_gemm_tc(m, x, y, tokens, addr[device], stream, err_flag, launches);
+  return launch_gemm_tc(m, x, y, tokens, addr[device], GEMM_STATIC_SCRATCH_BYTES + (512 << 10), stream, err_flag, launches);
 }
 
 }  // namespace llr

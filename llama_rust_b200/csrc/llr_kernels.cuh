@@ -125,7 +125,7 @@ cudaError_t tc_convert_activations(const float* x, int64_t n_rows, int cols, boo
 cudaError_t launch_gemm_tc_grouped(const GemmGroupSpec* specs, int n_groups, bool f16, void* desc_dev,
                                    cudaStream_t stream, int* err_flag, uint64_t* launches);
 size_t gemm_tc_scratch_bytes(const MatView& m, int64_t tokens);
-cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t tokens, void* scratch,
+cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t tokens, void* scratch, size_t scratch_bytes,
                            cudaStream_t stream, int* err_flag, uint64_t* launches);
 
 // Same kernels with the staging buffer in a file-scope __device__ array (no allocation).
