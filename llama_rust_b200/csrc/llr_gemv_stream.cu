@@ -41,7 +41,7 @@
 // peer stores over NVLink) and counts on its own rank's phase counter; the CTA that
 // completes the local count sends one system-scope release add to every peer.
 // Consumers wait for the local count and for one arrival per peer.  No collective
-// library call, no multicast, every wait bounded.
+// library call, plain stores and atomics only, every wait bounded.
 #include <cuda_runtime.h>
 
 #include <new>
