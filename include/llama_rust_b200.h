@@ -245,7 +245,12 @@ int llr_program_create_sharded(llr_exec* exec, const llr_program_entry* entries,
  * device.  router: n_expert x n_embd; gate[e], up[e]: n_ff x n_embd; down[e]:
  * n_embd x n_ff (the ExpertParts of expertvm/src/store.rs:13-20, resident).
  * x: tokens*n_embd floats, out: tokens*n_embd floats (host).  sel_ids / sel_w
- * (tokens*n_used each, may be null) receive the routing decision. */
+ * (tokens*n_used each, may be null) receive the routing decision.
+ * Experts striped over GPUs (expert e on rank e % G, expertvm/src/place.rs:71-75): an
+ * expert whose gate, up and down entries are all NULL is resident elsewhere; it takes part
+ * in the routing, and its rows contribute zero to `out`, which is then this rank's partial
+ * sum.  With two experts per token the sum of the ranks' partial outputs is bit-identical
+ * to the single-device result (at most two non-zero terms per element). */
 typedef struct llr_moe_layer {
   uint32_t n_expert, n_used, norm_w;
   const llr_matrix* router;

@@ -791,14 +791,20 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
   if (rc) return rc;
   const size_t n_embd = (size_t)L->router->cols, n_exp = L->n_expert, n_used = L->n_used;
   if ((size_t)L->router->rows != n_exp || n_embd % 4 != 0) return fail(e, LLR_ERR_INVALID, "ffn_gate_inp shape");
+  // An expert whose three matrices are all null lives on another rank (experts striped over GPUs):
+  // it takes part in the routing, its rows are not computed here and contribute zero to `out`.
   size_t n_ff = 0;
+  bool any_remote = false;
+  std::vector<char> local(n_exp, 1);
   for (size_t i = 0; i < n_exp; ++i) {
+    if (!L->gate[i] && !L->up[i] && !L->down[i]) { local[i] = 0; any_remote = true; continue; }
     if ((rc = check_matrix(e, L->gate[i])) || (rc = check_matrix(e, L->up[i])) || (rc = check_matrix(e, L->down[i]))) return rc;
-    if (i == 0) n_ff = (size_t)L->gate[0]->rows;
+    if (n_ff == 0) n_ff = (size_t)L->gate[i]->rows;
     if ((size_t)L->gate[i]->rows != n_ff || (size_t)L->gate[i]->cols != n_embd || (size_t)L->up[i]->rows != n_ff ||
         (size_t)L->up[i]->cols != n_embd || (size_t)L->down[i]->rows != n_embd || (size_t)L->down[i]->cols != n_ff)
       return fail(e, LLR_ERR_INVALID, "expert matrix shapes do not match the layer");
   }
+  if (n_ff == 0) return fail(e, LLR_ERR_INVALID, "no expert of the layer is resident on this executor");
   size_t nx = 0;
   if (tokens == 0 || !mul_ok(tokens, n_embd, &nx) || x_len != nx || out_len != nx || !x || !out || tokens > (1u << 24))
     return fail(e, LLR_ERR_INVALID, "matrix dimensions must be positive and token-aligned");
@@ -880,7 +886,7 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
         if ((size_t)ids[(size_t)t * n_used + j] == ex) { w = wts[(size_t)t * n_used + j]; break; }
       const int slot = fill[(size_t)t]++;  // ascending expert id = the reference's accumulation order
       rows_of_tok[(size_t)t * n_used + slot] = (int)r;
-      w_of_tok[(size_t)t * n_used + slot] = w;
+      w_of_tok[(size_t)t * n_used + slot] = local[ex] ? w : 0.0f;
       ++r;
     }
   }
@@ -890,11 +896,13 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
       (ce = cudaMemcpyAsync(d_w, w_of_tok.data(), n_rows * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess ||
       (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)  // the host vectors go out of scope later, but keep it simple
     return fail_cuda(e, ce, "routing upload");
+  if (any_remote && (ce = cudaMemsetAsync(d_y, 0, f_y * 4, e->stream)) != cudaSuccess)  // rows nobody computes here
+    return fail_cuda(e, ce, "expert workspace");
   {  // size the GEMM staging buffer once, for the busiest expert's widest product: growing it between
      // launches would free and reallocate, which synchronizes the device
     size_t busiest = 0, most = 0;
     for (size_t ex = 0; ex < n_exp; ++ex)
-      if ((size_t)(first_row[ex + 1] - first_row[ex]) > most) { most = (size_t)(first_row[ex + 1] - first_row[ex]); busiest = ex; }
+      if (local[ex] && (size_t)(first_row[ex + 1] - first_row[ex]) > most) { most = (size_t)(first_row[ex + 1] - first_row[ex]); busiest = ex; }
     void* unused = nullptr;
     if (most > 0 && ((ce = ensure_scratch(e, L->down[busiest], most, &unused)) != cudaSuccess ||
                      (ce = ensure_scratch(e, L->gate[busiest], most, &unused)) != cudaSuccess))
@@ -906,18 +914,25 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
   // all experts' gate and up products in one launch, silu(g)*u, all down products in one launch.
   bool grouped = e->path == PATH_AUTO && n_rows >= 64;
   int f16a = 1, f16b = 1;
+  size_t first_local = 0;
+  while (!local[first_local]) ++first_local;
   for (size_t ex = 0; ex < n_exp && grouped; ++ex) {
+    if (!local[ex]) continue;
     const MatView vg = view_of(L->gate[ex]), vu = view_of(L->up[ex]), vd = view_of(L->down[ex]);
     grouped = gemm_tc_supported(vg, 16) && gemm_tc_supported(vu, 16) && gemm_tc_supported(vd, 16) &&
-              vg.dtype == view_of(L->gate[0]).dtype && vu.dtype == vg.dtype && vd.dtype == view_of(L->down[0]).dtype;
+              vg.dtype == view_of(L->gate[first_local]).dtype && vu.dtype == vg.dtype &&
+              vd.dtype == view_of(L->down[first_local]).dtype;
     if (vg.f16_ok != 1 || vu.f16_ok != 1) f16a = 0;
     if (vd.f16_ok != 1) f16b = 0;
   }
+  bool any_local_rows = false;
+  for (size_t ex = 0; ex < n_exp; ++ex) any_local_rows = any_local_rows || (local[ex] && first_row[ex + 1] > first_row[ex]);
+  if (!any_local_rows) grouped = false;  // nothing routed to a resident expert: the loops below do nothing either
   if (grouped) {
     std::vector<GemmGroupSpec> specs;
     for (size_t ex = 0; ex < n_exp; ++ex) {
       const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
-      if (n == 0) continue;
+      if (n == 0 || !local[ex]) continue;
       specs.push_back(GemmGroupSpec{view_of(L->gate[ex]), d_x16a + r0 * n_embd * 2, d_sa + r0, d_g + r0 * n_ff, (int)n});
       specs.push_back(GemmGroupSpec{view_of(L->up[ex]), d_x16a + r0 * n_embd * 2, d_sa + r0, d_u + r0 * n_ff, (int)n});
     }
@@ -928,7 +943,7 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
     specs.clear();
     for (size_t ex = 0; ex < n_exp; ++ex) {
       const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
-      if (n == 0) continue;
+      if (n == 0 || !local[ex]) continue;
       specs.push_back(GemmGroupSpec{view_of(L->down[ex]), d_x16b + r0 * n_ff * 2, d_sb + r0, d_y + r0 * n_embd, (int)n});
     }
     // the descriptor buffer is reused: stream order puts this copy after the first grouped launch
@@ -938,16 +953,16 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
   }
   for (size_t ex = 0; ex < n_exp && !grouped; ++ex) {
     const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
-    if (n == 0) continue;
+    if (n == 0 || !local[ex]) continue;
     if ((ce = matmul_dev(e, L->gate[ex], n, d_pack + r0 * n_embd, d_g + r0 * n_ff, expert_path(e, n))) != cudaSuccess ||
         (ce = matmul_dev(e, L->up[ex], n, d_pack + r0 * n_embd, d_u + r0 * n_ff, expert_path(e, n))) != cudaSuccess)
       return fail_cuda(e, ce, "kernel launch");
   }
-  if (!grouped && (ce = launch_silu_mul(d_g, d_u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess)
+  if (!grouped && any_local_rows && (ce = launch_silu_mul(d_g, d_u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess)
     return fail_cuda(e, ce, "kernel launch");
   for (size_t ex = 0; ex < n_exp && !grouped; ++ex) {
     const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
-    if (n == 0) continue;
+    if (n == 0 || !local[ex]) continue;
     if ((ce = matmul_dev(e, L->down[ex], n, d_g + r0 * n_ff, d_y + r0 * n_embd, expert_path(e, n))) != cudaSuccess)
       return fail_cuda(e, ce, "kernel launch");
   }

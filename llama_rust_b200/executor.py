@@ -221,7 +221,7 @@ class Executor:
         """One routed-expert FFN layer (llr_moe_ffn).  Returns (out, sel_ids, sel_w); `out` may be a
         caller-owned (e.g. pinned) float32 array of x's shape."""
         n_expert = len(gate)
-        arrs = [(C.c_void_p * n_expert)(*[m._h for m in lst]) for lst in (gate, up, down)]
+        arrs = [(C.c_void_p * n_expert)(*[None if m is None else m._h for m in lst]) for lst in (gate, up, down)]  # None: expert resident on another rank
         layer = _lib.MoeLayer(n_expert, n_used, int(norm_w), router._h, arrs[0], arrs[1], arrs[2])
         xs = np.ascontiguousarray(x, np.float32).reshape(-1, router.cols)
         tokens = xs.shape[0]

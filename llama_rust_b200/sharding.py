@@ -24,6 +24,7 @@ from __future__ import annotations
 
 from typing import Callable, Sequence
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
@@ -192,3 +193,39 @@ class ShardedDecodeProgram:
                     self.ex.shared_close(p)
             dist.barrier(group=self.group)
             self.ex.shared_free(self.arena)
+
+
+class StripedExperts:
+    """Routed-expert FFN layer with the experts striped over the ranks (expert e on rank e % G,
+    expertvm/src/place.rs:71-75), on the CUDA executor.  Every rank routes every token (the router
+    is replicated) and runs llr_moe_ffn with only its own experts resident; the exchange step is one
+    sum of the ranks' partial outputs (NCCL all-reduce, or gloo).  With two experts per token at most
+    two terms of that sum are non-zero for any element, so the result is bit-identical to the
+    single-device layer whatever order the collective adds in."""
+
+    def __init__(self, ex, router, gate, up, down, n_used: int, norm_w: bool, group=None):
+        self.ex, self.router, self.n_used, self.norm_w, self.group = ex, router, n_used, norm_w, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        keep = [home_rank(e, self.world) == self.rank for e in range(len(gate))]
+        self.gate = [m if k else None for m, k in zip(gate, keep)]
+        self.up = [m if k else None for m, k in zip(up, keep)]
+        self.down = [m if k else None for m, k in zip(down, keep)]
+
+    def __call__(self, x, device=None):
+        """x: [tokens, n_embd] float32 numpy array (host).  Returns (out, ids, weights) as numpy arrays
+        (out is a view of a pinned buffer that the next call reuses)."""
+        shape = tuple(np.asarray(x).reshape(-1, self.router.cols).shape)
+        if getattr(self, "_pin", None) is None or tuple(self._pin.shape) != shape:
+            self._pin = torch.empty(shape, dtype=torch.float32)
+            if device is not None:
+                self._pin = self._pin.pin_memory()  # the executor writes its partial sums straight into it
+        partial, ids, w = self.ex.moe_ffn(self.router, self.gate, self.up, self.down, self.n_used, self.norm_w, x,
+                                          out=self._pin.numpy())
+        if device is None:
+            dist.all_reduce(self._pin, op=dist.ReduceOp.SUM, group=self.group)
+        else:
+            t = self._pin.to(device, non_blocking=True)
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+            self._pin.copy_(t, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        return self._pin.numpy(), ids, w

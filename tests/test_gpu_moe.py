@@ -59,3 +59,33 @@ def test_moe_layer_validates_shapes():
     out, ids, w = ex.moe_ffn(router, mats["gate"], mats["up"], mats["down"], 2, False, x)
     assert np.all(out == 0.0) and ids.shape == (3, 2)
     ex.close()
+
+
+def test_striped_experts_partials_sum_to_the_single_device_layer(orc):
+    """Experts striped e % G: each "rank" runs the layer with only its experts resident (the others
+    NULL) and the partial outputs are added.  With two experts per token that sum is bit-identical
+    to the layer with every expert resident.  One GPU plays both ranks here; the two-process
+    variant is in test_gpu_sharded_program.py."""
+    from llama_rust_b200 import Executor, NativeCudaError
+    n_expert, n_used, n_embd, n_ff = 8, 2, 1024, 2048
+    ex = Executor(0)
+    gate = [ex.synth(Q4_K, n_ff, n_embd, 10 + e) for e in range(n_expert)]
+    up = [ex.synth(Q4_K, n_ff, n_embd, 30 + e) for e in range(n_expert)]
+    down = [ex.synth(Q4_K, n_embd, n_ff, 50 + e) for e in range(n_expert)]
+    rng = np.random.default_rng(3)
+    router = ex.upload(F32, n_expert, n_embd, (rng.standard_normal((n_expert, n_embd)) * 0.05).astype(np.float32).view(np.uint8).reshape(-1))
+    for tokens in (5, 96):  # per-expert decode kernels, grouped tensor-core launches
+        x = rng.standard_normal((tokens, n_embd)).astype(np.float32)
+        full, ids, w = ex.moe_ffn(router, gate, up, down, n_used, True, x)
+        total = np.zeros_like(full)
+        for world, rank in ((2, 0), (2, 1)):
+            keep = [e % world == rank for e in range(n_expert)]
+            part, ids_r, w_r = ex.moe_ffn(router, [m if k else None for m, k in zip(gate, keep)],
+                                          [m if k else None for m, k in zip(up, keep)],
+                                          [m if k else None for m, k in zip(down, keep)], n_used, True, x)
+            assert np.array_equal(ids_r, ids) and np.array_equal(w_r, w)
+            total = total + part
+        assert np.array_equal(total, full), f"tokens={tokens}: {np.abs(total - full).max()}"
+    with pytest.raises(NativeCudaError):  # no resident expert at all
+        ex.moe_ffn(router, [None] * n_expert, [None] * n_expert, [None] * n_expert, n_used, True, x)
+    ex.close()

@@ -108,3 +108,61 @@ def test_sharded_program_equals_unsharded_on_every_rank(tokens):
         if p.is_alive():
             p.terminate()
     assert dict(ret) == {0: "ok", 1: "ok"}, dict(ret)
+
+
+def _moe_worker(rank, world, port, ret):
+    try:
+        import torch
+        import torch.distributed as dist
+        from llama_rust_b200 import Executor
+        from llama_rust_b200.sharding import StripedExperts
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        torch.cuda.set_device(rank)
+        nccl = dist.new_group(backend="nccl")
+        ex = Executor(rank)
+        F32 = 2
+        n_expert, n_used, n_embd, n_ff = 8, 2, 1024, 2048
+        # every rank builds all experts here (to have the single-device answer); a deployment keeps only its own
+        gate = [ex.synth(Q4_K, n_ff, n_embd, 10 + e) for e in range(n_expert)]
+        up = [ex.synth(Q4_K, n_ff, n_embd, 30 + e) for e in range(n_expert)]
+        down = [ex.synth(Q4_K, n_embd, n_ff, 50 + e) for e in range(n_expert)]
+        rng = np.random.default_rng(3)
+        router = ex.upload(F32, n_expert, n_embd, (rng.standard_normal((n_expert, n_embd)) * 0.05).astype(np.float32).view(np.uint8).reshape(-1))
+        layer = StripedExperts(ex, router, gate, up, down, n_used, True, group=nccl)
+        ok = "ok"
+        for tokens in (7, 128):
+            x = rng.standard_normal((tokens, n_embd)).astype(np.float32)
+            full, ids, w = ex.moe_ffn(router, gate, up, down, n_used, True, x)
+            out, ids_s, w_s = layer(x, device=f"cuda:{rank}")
+            if not (np.array_equal(out, full) and np.array_equal(ids_s, ids) and np.array_equal(w_s, w)):
+                ok = f"tokens={tokens}: striped result differs, max {np.abs(out - full).max()}"
+                break
+        ex.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        ret[rank] = ok
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
+
+
+def test_striped_experts_over_two_gpus_equal_the_single_device_layer():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_moe_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert dict(ret) == {0: "ok", 1: "ok"}, dict(ret)
