@@ -1,39 +1,43 @@
-// Chunk GEMM for many activation rows (prefill / continuous-batching chunks):
-// packed GGUF weights are dequantized tile by tile into shared memory and fed to
-// the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
+// Chunk GEMM for many activation rows (prefill / continuous-batching chunks, routed experts):
+// packed GGUF weights are dequantized tile by tile into tensor memory and fed to the
+// 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
 //
 // What it computes: gemm_<t>_f32 (langtax/src/quant.rs:6282, 6366, 6380, 6478 ->
 // gemm_f32_x :6760), y[t*rows + r] = sum_c W[r,c] x[t*cols + c], for Q4_K, Q8_0,
-// Q5_0 and Q5_1.  Operands are rounded to bfloat16 (weights after f32
-// dequantization, activations once up front), products are exact, accumulation is
-// f32 in tensor memory: this is the tensor-core path with the looser, separately
-// stated tolerance (tests/test_gpu_gemm.py); the f32-faithful path for any number
-// of rows stays the integer kernel of llr_gemv_stream.cu.
+// Q5_0 and Q5_1.  Operands are 16-bit (binary16 when the matrix's weights fit its range,
+// bfloat16 otherwise; see dequant_sub_h), products are exact, accumulation is f32 in
+// tensor memory: this is the tensor-core path with the looser, separately stated tolerance
+// (tests/test_gpu_gemm.py); the f32-faithful path for any number of rows stays the
+// integer kernel of llr_gemv_stream.cu.
 //
-// One CTA computes a 128-row x BN-token tile of y over the whole K.
+// One CTA computes a 128-row x BN-token tile of y over its K range; twenty warps:
 //   * packed bytes: the packed matrix is described to the TMA unit as a 2-D array of 32-bit
-//     words (row pitch = bytes per row); per 256-column macro-step one thread issues one
+//     words (row pitch = bytes per row); per 256-column macro-step one elected lane issues one
 //     tiled copy of a 128-row x (144 / 272 / 176 / 208)-byte box into a shared-memory ring
 //     (mbarrier transaction count).  The box width is an odd number of 16-byte chunks, so a
 //     warp whose lanes are consecutive rows reads 16-byte chunks without bank conflicts
-//     (Q5_1 copies 16 bytes more than its 192 to get there).  No load/store unit work per
-//     byte and as many bytes in flight as shared memory allows.
+//     (Q5_1 copies 16 bytes more than its 192 to get there).
 //   * dequantization: sixteen warps in two groups that alternate 64-column steps; in a
-//     group two threads per row, 32 columns each.  Quants are turned into binary16 pairs
-//     with a mask-and-or against a magic exponent (1024+q, or 64+q for high nibbles),
-//     widened to f32, scaled with one FMA (the magic offset folded into the addend) and
-//     packed to bf16 pairs: no integer to float conversions, under one bit-operation per
-//     weight.
+//     group two threads per row, 32 columns each.  A warp decodes both of its steps of a
+//     macro-step back to back, then does one round of barrier waits, tensor-memory stores
+//     and arrivals for the two.  Quants are turned into binary16 pairs with a mask-and-or
+//     against a magic exponent (1024+q, or 64+q for high nibbles): no integer to float
+//     conversions.  binary16 path: exact offset subtraction and one HFMA2 per two weights;
+//     bfloat16 path: widen, one FMA, pack.
 //   * the dequantized tile never touches shared memory: a thread owns one weight row = one
-//     tensor-memory lane and writes its 32 bf16 with tcgen05.st into a ring of A-operand
-//     stages that lives in tensor memory next to the accumulator (32 columns per stage;
-//     14 / 12 / 8 stages for BN = 64 / 128 / 256).  The MMA takes A from tensor memory and
+//     tensor-memory lane and writes its 32 values with tcgen05.st into a ring of A-operand
+//     stages that lives in tensor memory next to the accumulators (32 columns per stage;
+//     12 / 8 / 8 stages for BN = 64 / 128 / 256).  The MMA takes A from tensor memory and
 //     B from shared memory.  A stage hand-off (store -> mma -> commit -> store) takes about
 //     a microsecond of barrier latency, so the ring depth, not the step time, is what keeps
-//     the tensor pipe fed; shared memory could not hold that many bf16 weight tiles.
-//   * one thread TMA-loads the matching BN x 64 bf16 activation tile (2-D tensor map,
-//     128-byte swizzle, out-of-range tokens read as zero) into a 128 KB ring; one thread
-//     issues four tcgen05.mma (M=128, N=BN, K=16) per step, whose commits release the stages.
+//     the tensor pipe fed; shared memory could not hold that many 16-bit weight tiles.
+//   * one warp TMA-loads the matching BN x 64 activation tiles (2-D tensor map, 128-byte
+//     swizzle, out-of-range tokens read as zero) into a 128 KB ring; one MMA warp (two with
+//     separate accumulators at BN <= 128) issues four tcgen05.mma (M=128, N=BN, K=16) per
+//     step, whose commits release the stages.  The issue warps run their loops converged and
+//     issue through one elected lane.
+// Launch forms: one product (split along K when it has few row tiles, slices added in
+// order by a second kernel), or a grouped launch with the tiles of several products.
 // All hand-offs are mbarriers with bounded waits.  The epilogue reads the accumulators
 // with tcgen05.ld (one TMEM lane = one weight row per thread) and stores token-major.
 #include <cuda.h>
