@@ -13,7 +13,9 @@ is needed between steps.
 Prints one JSON line (rank 0).  `value` is the whole-job achieved HBM GB/s
 (algorithmic bytes of the sweep / device time, inputs resident in HBM); `e2e`
 is the same metric through the reference-facing host-pointer call
-(llr_gemv_resident: H2D of x, kernel, D2H of y and a synchronize per matmul);
+(llr_gemm_resident, 225 synchronous calls per step, pinned host buffers);
+`e2e_program` is the same through the program API (one copy in, one launch,
+one copy out per step; at N > 1 this is `e2e`);
 `roofline` is the kernel the timed region consists of (the persistent program
 kernel; the Q4_K single-product launches are reported beside it) against the
 measured HBM peak; `cpu_baseline` is the CPU oracle (AVX2 row kernels, reference threading)
@@ -189,13 +191,21 @@ def run_ours(args):
 
     # every matrix sharded by output rows (all row counts divide by 8); activations replicated
     mats = []
-    for name, dt, rows, cols in model_matrices():
+    specs_all = model_matrices()
+    # all input vectors in one device buffer and all (local) results in another, so that the end-to-end
+    # legs move them with one copy each way
+    xbig = torch.randn(sum(M * cols for _, _, _, cols in specs_all), device="cuda", dtype=torch.float32)
+    ybig = torch.empty(sum(M * (rows // world) for _, _, rows, _ in specs_all), device="cuda", dtype=torch.float32)
+    xo = yo = 0
+    for name, dt, rows, cols in specs_all:
         assert rows % world == 0
         rs = rows // world
         # each rank generates its own shard from its own stream: rank r's rows are blocks of stream (name, r)
         m = ex.synth(dt, rs, cols, synth.tensor_seed(rank, name))
-        x = torch.randn(M, cols, device="cuda", dtype=torch.float32)
-        y = torch.empty(M, rs, device="cuda", dtype=torch.float32)
+        x = xbig[xo:xo + M * cols].view(M, cols)
+        y = ybig[yo:yo + M * rs].view(M, rs)
+        xo += M * cols
+        yo += M * rs
         yfull = torch.empty(world, M, rs, device="cuda", dtype=torch.float32) if world > 1 else None
         mats.append((name, dt, rows, cols, rs, m, x, y, yfull))
     total_bytes = sum(algorithmic_bytes(dt, rows, cols, M) for _, dt, rows, cols, *_ in mats)
@@ -335,41 +345,45 @@ def run_ours(args):
                "ms_per_step": dt_s * 1e3, "tok_s": M / dt_s,
                "api": "llr_gemm_resident with pinned host buffers, 225 synchronous calls per step: H2D copy of x, kernel, the kernel stores y into the pinned host buffer and raises a completion word the call polls"}
 
-    if world > 1 and sharded is not None:
-        # end to end at N GPUs through the program API: per step every input vector goes host -> device,
-        # one sharded program launch per rank, every full-width result comes device -> host, synchronize
+    e2e_program = None
+    if prog is not None:
+        # End to end through the program API (llr_program_run): per step all input vectors go host -> device in one
+        # copy, one program launch per rank, all results come device -> host in one copy, synchronize.
         import ctypes as C
         rt = C.CDLL("libcudart.so.12")
         rt.cudaMemcpyAsync.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
-        hx = torch.randn(sum(M * cols for _, _, _, cols, *_ in mats)).pin_memory()
-        hy = torch.empty((sharded.arena_bytes - sharded.offsets[0]) // 4).pin_memory()
-        xoff, cur = [], 0
-        for _, _, _, cols, *_ in mats:
-            xoff.append(cur)
-            cur += M * cols
+        hxb = torch.randn(xbig.numel()).pin_memory()
+        if sharded is not None:
+            y_dev, y_floats = sharded.arena + sharded.offsets[0], (sharded.arena_bytes - sharded.offsets[0]) // 4
+        else:
+            y_dev, y_floats = ybig.data_ptr(), ybig.numel()
+        hyb = torch.empty(y_floats).pin_memory()
 
-        def e2e_step():
-            for (name, dt, rows, cols, rs, m, x, *_), off in zip(mats, xoff):
-                assert rt.cudaMemcpyAsync(x.data_ptr(), hx.data_ptr() + 4 * off, 4 * M * cols, 1, sptr) == 0
+        def e2e_prog_step():
+            assert rt.cudaMemcpyAsync(xbig.data_ptr(), hxb.data_ptr(), 4 * hxb.numel(), 1, sptr) == 0
             prog.run(sptr)
-            assert rt.cudaMemcpyAsync(hy.data_ptr(), sharded.arena + sharded.offsets[0], 4 * hy.numel(), 2, sptr) == 0
+            assert rt.cudaMemcpyAsync(hyb.data_ptr(), y_dev, 4 * y_floats, 2, sptr) == 0
             stream.synchronize()
         for _ in range(2):
-            e2e_step()
+            e2e_prog_step()
         barrier()
         n_e2e = max(2, min(args.steps, 10))
         t0 = time.perf_counter()
         for _ in range(n_e2e):
-            e2e_step()
+            e2e_prog_step()
         barrier()
         dt_s = (time.perf_counter() - t0) / n_e2e
-        tt = torch.tensor([dt_s], device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        dt_s = float(tt.item())
-        e2e = {"value": total_bytes / dt_s / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": world * 4 * hx.numel(), "d2h_bytes_per_step": world * 4 * hy.numel(),
-               "ms_per_step": dt_s * 1e3, "tok_s": M / dt_s,
-               "api": "per rank and step: 225 pinned-host input vectors H2D, llr_program_run (sharded), all full-width results D2H, synchronize"}
+        if world > 1:
+            tt = torch.tensor([dt_s], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dt_s = float(tt.item())
+        e2e_program = {"value": total_bytes / dt_s / 1e9, "unit": "GB/s",
+                       "h2d_bytes_per_step": world * 4 * hxb.numel(), "d2h_bytes_per_step": world * 4 * y_floats,
+                       "ms_per_step": dt_s * 1e3, "tok_s": M / dt_s,
+                       "api": "per rank and step: all 225 input vectors H2D from pinned memory (one copy), llr_program_run, "
+                              "all results D2H (one copy), synchronize"}
+        if world > 1:
+            e2e = e2e_program  # one call per product would need a collective per product; the program is the N-GPU API
 
     out = None
     if rank == 0:
@@ -383,7 +397,8 @@ def run_ours(args):
                                        f"rows/{world} per GPU; result slices exchanged inside the kernel (peer stores + phase counters over all ranks)"
                                        if sharded is not None else f"rows/{world} per GPU + NCCL all-gather of output slices after every product")},
             "tok_s": M / (ms_step * 1e-3), "frac_of_measured_hbm": value / peak, "frac_of_8tbs_nominal": value / 8000.0,
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_rec,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_program": e2e_program, "gpu_launches": int(launches),
+            "clocks": clock_rec,
         }
         print(json.dumps(out))
     if sharded is not None:
