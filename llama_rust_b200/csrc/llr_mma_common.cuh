@@ -295,7 +295,9 @@ __device__ __forceinline__ void split_activations(const float* __restrict__ X, i
    for (int u = 0; u < 2; ++u) {
     const int job = job0 + u * NWARP;
     if (job < njobs) {
-      const float4* xp = (const float4*)(X + (int64_t)(job / nblk256) * cols + col0 + (job % nblk256) * 256 + 8 * lane);
+      // one activation row: job = block (no integer division on the critical path of every phase)
+      const int jt = MT == 1 ? 0 : job / nblk256, jb = MT == 1 ? job : job - jt * nblk256;
+      const float4* xp = (const float4*)(X + (int64_t)jt * cols + col0 + jb * 256 + 8 * lane);
       pa[u] = ld_x_keep(xp, keep);
       pb[u] = ld_x_keep(xp + 1, keep);
     }
@@ -304,7 +306,7 @@ __device__ __forceinline__ void split_activations(const float* __restrict__ X, i
    for (int u = 0; u < 2; ++u) {
     const int job = job0 + u * NWARP;
     if (job >= njobs) break;
-    const int b = job % nblk256, tok = job / nblk256;
+    const int tok = MT == 1 ? 0 : job / nblk256, b = MT == 1 ? job : job - tok * nblk256;
     const float4 va = pa[u], vb = pb[u];
     const float v[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
     float m = 0.f, sum = 0.f;
