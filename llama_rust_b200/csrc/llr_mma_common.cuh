@@ -309,18 +309,18 @@ __device__ __forceinline__ void split_activations(const float* __restrict__ X, i
     const int tok = MT == 1 ? 0 : job / nblk256, b = MT == 1 ? job : job - tok * nblk256;
     const float4 va = pa[u], vb = pb[u];
     const float v[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
-    float m = 0.f, sum = 0.f;
+    // Largest magnitude of the block as a bit pattern: for non-negative floats the unsigned order of
+    // the bits is the numeric order, infinities and NaNs sort above every finite value, and one
+    // redux.sync replaces a five-step shuffle reduction on the latency-critical start of a phase.
+    uint32_t mb = 0;
+    float sum = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { m = fmaxf(m, fabsf(v[j])); sum += v[j]; }
-    bool bad = false;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) bad = bad || !(fabsf(v[j]) <= 3.4028234e38f);
-#pragma unroll
-    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(~0u, m, o));
-    bad = __any_sync(~0u, bad);
+    for (int j = 0; j < 8; ++j) { mb = max(mb, __float_as_uint(v[j]) & 0x7fffffffu); sum += v[j]; }
+    mb = __reduce_max_sync(~0u, mb);
+    const bool bad = mb >= 0x7f800000u;  // a non-finite activation anywhere in the block
     sum += __shfl_xor_sync(~0u, sum, 1);
     sum += __shfl_xor_sync(~0u, sum, 2);
-    const int be = (int)((__float_as_uint(m) >> 23) & 0xff);
+    const int be = (int)(mb >> 23);
     float s = 0.f, sinv = 0.f;  // an all-zero (or denormal) block contributes nothing
     if (be != 0 && !bad) {
       int e = 29 - (be - 127);
