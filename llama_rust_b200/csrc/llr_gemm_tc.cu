@@ -51,6 +51,7 @@
 
 #include "llr_formats.cuh"
 #include "llr_kernels.cuh"
+#include "llr_tmap.cuh"
 
 namespace llr {
 namespace {
@@ -685,21 +686,7 @@ __global__ void weight_bound_kernel(const uint8_t* __restrict__ W, int64_t n_blo
   if ((threadIdx.x & 31) == 0) atomicMax(out, __float_as_uint(m));
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
+inline EncodeTiledFn encode_fn() { return tensor_map_encoder(); }
 
 template <int DT, int BN, bool F16>
 cudaError_t launch_bn(const MatView& m, const CUtensorMap& wmap, const CUtensorMap& xmap, const float* xscale, float* y,

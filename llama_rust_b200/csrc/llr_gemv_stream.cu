@@ -44,12 +44,14 @@
 // library call, plain stores and atomics only, every wait bounded.
 #include <cuda_runtime.h>
 
+#include <cstring>
 #include <new>
 #include <string>
 #include <vector>
 
 #include "llr_kernels.cuh"
 #include "llr_mma_common.cuh"
+#include "llr_tmap.cuh"
 
 namespace llr {
 namespace {
@@ -76,12 +78,21 @@ template <int MT> struct SLay {
   static constexpr int TOTAL = BAR + (2 * NST + 2 * NRB) * 8 + 16;
 };
 
-struct Geom { int kseg, segb, rs; };
+// How a stage of 16 rows x kseg columns reaches shared memory.
+//   Q4_K: one 3-D TMA box over (36 words of a block, rows, blocks of the row): the stage is laid
+//         out [block][row][144 bytes], whose fragment reads are conflict-free without padding;
+//   Q6_K: one 2-D box over (8-byte words of the row, rows): rows 1680 bytes apart (16 mod 128);
+//   Q8_0: one bulk copy per row into a padded pitch (its 2176-byte pieces exceed a box row).
+// One instruction per stage matters: the TMA unit of an SM accepts a bulk copy every ~40 ns
+// whatever its size, which capped sixteen 1680-byte row copies per stage at 87 % of the copy peak.
+struct Geom { int kseg, segb, rs, box_bytes; };
+constexpr int Q4K_STAGE_BLOCKS = Fmt<DT_Q4_K>::KSEG / 256;
 __device__ __forceinline__ Geom geom_of(int dtype) {
-  if (dtype == DT_Q4_K) return {Fmt<DT_Q4_K>::KSEG, Lay<DT_Q4_K, 1>::SEGB, Lay<DT_Q4_K, 1>::RS};
-  if (dtype == DT_Q6_K) return {Fmt<DT_Q6_K>::KSEG, Lay<DT_Q6_K, 1>::SEGB, Lay<DT_Q6_K, 1>::RS};
-  return {Fmt<DT_Q8_0>::KSEG, Lay<DT_Q8_0, 1>::SEGB, Lay<DT_Q8_0, 1>::RS};
+  if (dtype == DT_Q4_K) return {Fmt<DT_Q4_K>::KSEG, Lay<DT_Q4_K, 1>::SEGB, Lay<DT_Q4_K, 1>::RS, Q4K_STAGE_BLOCKS * 16 * 144};
+  if (dtype == DT_Q6_K) return {Fmt<DT_Q6_K>::KSEG, Lay<DT_Q6_K, 1>::SEGB, Lay<DT_Q6_K, 1>::RS, 16 * Lay<DT_Q6_K, 1>::SEGB};
+  return {Fmt<DT_Q8_0>::KSEG, Lay<DT_Q8_0, 1>::SEGB, Lay<DT_Q8_0, 1>::RS, 0};
 }
+static_assert(Lay<DT_Q6_K, 1>::RS == Lay<DT_Q6_K, 1>::SEGB, "Q6_K rows lie densely in a stage");
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* b) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
@@ -103,6 +114,7 @@ struct Work {
   int n_phases;
   const PeerTable* peers;  // row-sharded programs only
   HostOut host;            // single products that deliver their result to the host themselves
+  const CUtensorMap* maps; // one per entry (Q4_K, Q6_K; unused for Q8_0)
 };
 
 // Tile range of this CTA inside a phase, and inside one entry of it.
@@ -161,7 +173,9 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           const ProgEntry E = wk.entries[P.first_entry + ei];
           int t0, t1;
           if (!entry_range(E, lo, hi, &t0, &t1)) continue;
-          const Geom gm = geom_of(DTFIX >= 0 ? DTFIX : E.dtype);
+          const int dtype = DTFIX >= 0 ? DTFIX : E.dtype;
+          const Geom gm = geom_of(dtype);
+          const CUtensorMap* map = wk.maps + (PROGRAM ? P.first_entry + ei : 0);
           const int n_span = (E.cols + SPAN - 1) / SPAN;
           for (int span = 0; span < n_span; ++span) {
             const int span_cols = min(SPAN, E.cols - span * SPAN);
@@ -170,12 +184,20 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
               for (int sub = 0; sub < nsub; ++sub, ++c) {
                 const int stage = c % NST;
                 if (ok && !mbar_wait(&empty[stage], (uint32_t)(((c / NST) & 1) ^ 1))) { ok = false; report_error(err, 1); }
-                const int64_t seg_off = ((int64_t)span * (SPAN / gm.kseg) + sub) * gm.segb;
+                uint8_t* dst = ring + stage * MAX_CHUNK;
+                const int seg = span * (SPAN / gm.kseg) + sub;
+                if (gm.box_bytes) {
+                  // rows and blocks beyond the matrix are filled with zeros and still counted
+                  mbar_expect_tx(&full[stage], (uint32_t)gm.box_bytes);
+                  if (dtype == DT_Q4_K) tma_box_3d(dst, map, 0, tile * 16, seg * Q4K_STAGE_BLOCKS, &full[stage], stream_once);
+                  else tma_box_2d(dst, map, seg * (Lay<DT_Q6_K, 1>::SEGB / 8), tile * 16, &full[stage], stream_once);
+                  continue;
+                }
+                const int64_t seg_off = (int64_t)seg * gm.segb;
                 const int64_t left = E.row_bytes - seg_off;
                 const uint32_t bytes = (uint32_t)(left < gm.segb ? left : gm.segb);
                 mbar_expect_tx(&full[stage], 16 * bytes);
                 const uint8_t* src = E.w + (int64_t)(tile * 16) * E.row_bytes + seg_off;
-                uint8_t* dst = ring + stage * MAX_CHUNK;
                 const int last = E.rows - 1 - tile * 16;  // rows beyond the matrix refetch the last one
 #pragma unroll 4
                 for (int r = 0; r < 16; ++r)
@@ -354,8 +376,8 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
             const int seg_cols = min(gm.kseg, span_cols - sub * gm.kseg);
             const int dtype = DTFIX >= 0 ? DTFIX : E.dtype;
             if (dtype == DT_Q4_K) {
-              for (int b = warp; b < (seg_cols >> 8); b += CW)
-                block_q4k<MT>(rowA, rowB, b, sub * (gm.kseg / 256) + b, dig, sxf, xsi, g, t, acc);
+              for (int b = warp; b < (seg_cols >> 8); b += CW)  // stage layout [block][row][144]
+                block_q4k<MT>(chunk + (b * 16 + g) * 144, chunk + (b * 16 + g + 8) * 144, sub * (gm.kseg / 256) + b, dig, sxf, xsi, g, t, acc);
             } else if (dtype == DT_Q6_K) {
               for (int b = warp; b < (seg_cols >> 8); b += CW)
                 block_q6k<MT>(rowA, rowB, b, sub * (gm.kseg / 256) + b, dig, xsi, g, t, acc);
@@ -408,39 +430,63 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
 // digit planes leave room for one CTA only
 template <int MT, int DT>
 __global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
-gemv_stream_kernel(const __grid_constant__ ProgEntry one, int* __restrict__ err) {
+gemv_stream_kernel(const __grid_constant__ ProgEntry one, const __grid_constant__ CUtensorMap map, int* __restrict__ err) {
   __shared__ ProgPhase phase;
   if (threadIdx.x == 0) phase = ProgPhase{0, 1, one.n_tiles, 0};
   __syncthreads();
-  Work wk{&one, &phase, 1, nullptr, HostOut{}};
+  Work wk{&one, &phase, 1, nullptr, HostOut{}, &map};
   stream_body<MT, false, DT>(wk, nullptr, 0ull, err);
 }
 
 template <int MT, int DT>
 __global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
-gemv_stream_hostout_kernel(const __grid_constant__ ProgEntry one, const __grid_constant__ HostOut ho, int* __restrict__ err) {
+gemv_stream_hostout_kernel(const __grid_constant__ ProgEntry one, const __grid_constant__ CUtensorMap map,
+                           const __grid_constant__ HostOut ho, int* __restrict__ err) {
   __shared__ ProgPhase phase;
   if (threadIdx.x == 0) phase = ProgPhase{0, 1, one.n_tiles, 0};
   __syncthreads();
-  Work wk{&one, &phase, 1, nullptr, ho};
+  Work wk{&one, &phase, 1, nullptr, ho, &map};
   stream_body<MT, false, DT, false, true>(wk, nullptr, 0ull, err);
 }
 
 template <int MT>
 __global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
 gemv_program_kernel(const ProgEntry* __restrict__ entries, const ProgPhase* __restrict__ phases, int n_phases,
-                    unsigned long long* __restrict__ counters, unsigned long long epoch, int* __restrict__ err) {
-  Work wk{entries, phases, n_phases, nullptr, HostOut{}};
+                    const CUtensorMap* __restrict__ maps, unsigned long long* __restrict__ counters,
+                    unsigned long long epoch, int* __restrict__ err) {
+  Work wk{entries, phases, n_phases, nullptr, HostOut{}, maps};
   stream_body<MT, true, -1>(wk, counters, epoch, err);
 }
 
 template <int MT>
 __global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
 gemv_sharded_program_kernel(const ProgEntry* __restrict__ entries, const ProgPhase* __restrict__ phases, int n_phases,
-                            unsigned long long* __restrict__ counters, unsigned long long epoch,
-                            const PeerTable* __restrict__ peers, int* __restrict__ err) {
-  Work wk{entries, phases, n_phases, peers, HostOut{}};
+                            const CUtensorMap* __restrict__ maps, unsigned long long* __restrict__ counters,
+                            unsigned long long epoch, const PeerTable* __restrict__ peers, int* __restrict__ err) {
+  Work wk{entries, phases, n_phases, peers, HostOut{}, maps};
   stream_body<MT, true, -1, true>(wk, counters, epoch, err);
+}
+
+// Tensor map of one matrix for the stage loads (see Geom).  Q8_0 is copied row by row: its map
+// stays zeroed and is never used.
+bool encode_weight_map(const uint8_t* w, int dtype, int64_t rows, int64_t cols, int64_t row_bytes, CUtensorMap* map) {
+  memset(map, 0, sizeof(*map));
+  if (dtype != DT_Q4_K && dtype != DT_Q6_K) return true;
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc) return false;
+  const cuuint32_t estr[3] = {1, 1, 1};
+  if (dtype == DT_Q4_K) {
+    const cuuint64_t dims[3] = {36, (cuuint64_t)rows, (cuuint64_t)(cols / 256)};
+    const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, 144};
+    const cuuint32_t box[3] = {36, 16, (cuuint32_t)Q4K_STAGE_BLOCKS};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (void*)w, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(Lay<DT_Q6_K, 1>::SEGB / 8), 16};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, (void*)w, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <class K>
@@ -465,6 +511,8 @@ cudaError_t launch_single(const MatView& m, const float* x, float* y, int tokens
     if (e != cudaSuccess) return e;
   }
   ProgEntry E{m.w, x, y, m.row_bytes, (int)m.rows, (int)m.cols, m.dtype, tokens, 0, (int)((m.rows + 15) / 16), m.rows};
+  CUtensorMap map;
+  if (!encode_weight_map(m.w, m.dtype, m.rows, m.cols, m.row_bytes, &map)) return cudaErrorNotSupported;
   int grid = sm_count * bps;
   if (grid > E.n_tiles) grid = E.n_tiles;
   cudaLaunchAttribute attr;
@@ -477,8 +525,8 @@ cudaError_t launch_single(const MatView& m, const float* x, float* y, int tokens
   cfg.stream = stream;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  if (ho) return cudaLaunchKernelEx(&cfg, gemv_stream_hostout_kernel<MT, DT>, E, *ho, err);
-  return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<MT, DT>, E, err);
+  if (ho) return cudaLaunchKernelEx(&cfg, gemv_stream_hostout_kernel<MT, DT>, E, map, *ho, err);
+  return cudaLaunchKernelEx(&cfg, gemv_stream_kernel<MT, DT>, E, map, err);
 }
 
 }  // namespace
@@ -532,6 +580,7 @@ cudaError_t launch_gemv_mma_hostout(const MatView& m, const float* x, float* y, 
 struct Program {
   ProgEntry* d_entries = nullptr;
   ProgPhase* d_phases = nullptr;
+  CUtensorMap* d_maps = nullptr;  // one per entry
   unsigned long long* d_counters = nullptr;
   int n_phases = 0, n_entries = 0, max_tokens = 1, grid = 0;
   unsigned long long epoch = 0;
@@ -558,16 +607,17 @@ static cudaError_t prog_launch(Program* p, cudaStream_t stream, int* err) {
   const ProgEntry* de = p->d_entries;
   const ProgPhase* dp = p->d_phases;
   int np = p->n_phases;
+  const CUtensorMap* dm = p->d_maps;
   unsigned long long* dc = p->d_counters;
   unsigned long long ep = p->epoch;
   // cooperative: every CTA must be resident, the phase counters are a grid-wide dependency
   if (p->d_peers) {
     const PeerTable* pt = p->d_peers;
-    void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dc, (void*)&ep, (void*)&pt, (void*)&err};
+    void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dm, (void*)&dc, (void*)&ep, (void*)&pt, (void*)&err};
     return cudaLaunchCooperativeKernel((const void*)gemv_sharded_program_kernel<MT>, dim3((unsigned)p->grid),
                                        dim3(NTHREADS), args, SLay<MT>::TOTAL, stream);
   }
-  void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dc, (void*)&ep, (void*)&err};
+  void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dm, (void*)&dc, (void*)&ep, (void*)&err};
   return cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)p->grid), dim3(NTHREADS), args,
                                      SLay<MT>::TOTAL, stream);
 }
@@ -579,8 +629,14 @@ static cudaError_t program_build(const std::vector<ProgEntry>& entries_in, const
   if (!p) return cudaErrorMemoryAllocation;
   std::vector<ProgEntry> entries = entries_in;
   std::vector<ProgPhase> phases;
+  std::vector<CUtensorMap> maps(entries.size());
   for (size_t i = 0; i < entries.size(); ++i) {
     ProgEntry& E = entries[i];
+    if (!encode_weight_map(E.w, E.dtype, E.rows, E.cols, E.row_bytes, &maps[i])) {
+      if (msg) *msg = "tensor map of an entry could not be encoded";
+      delete p;
+      return cudaErrorNotSupported;
+    }
     E.n_tiles = (E.rows + 15) / 16;
     if (E.y_ld == 0) E.y_ld = E.rows;
     if (i == 0 || phase_of[i] != phase_of[i - 1]) phases.push_back(ProgPhase{(int)i, 0, 0, i == 0 ? 0 : 1});
@@ -601,6 +657,8 @@ static cudaError_t program_build(const std::vector<ProgEntry>& entries_in, const
   else e = prog_prepare<8>(sm_count, &p->grid, sharded);
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_entries, entries.size() * sizeof(ProgEntry));
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_phases, phases.size() * sizeof(ProgPhase));
+  if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_maps, maps.size() * sizeof(CUtensorMap));
+  if (e == cudaSuccess) e = cudaMemcpy(p->d_maps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
   if (sharded) {
     p->own_counters = false;
     p->d_counters = shared_counters;  // zeroed by whoever allocated them, before any rank runs
@@ -636,6 +694,7 @@ void program_destroy(Program* p) {
   if (!p) return;
   if (p->d_entries) cudaFree(p->d_entries);
   if (p->d_phases) cudaFree(p->d_phases);
+  if (p->d_maps) cudaFree(p->d_maps);
   if (p->d_counters && p->own_counters) cudaFree(p->d_counters);
   if (p->d_peers) cudaFree(p->d_peers);
   delete p;

@@ -94,9 +94,26 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+// tiled TMA loads (global -> this CTA's shared memory) with an L2 policy; the innermost
+// coordinate times the element size is a multiple of 16 bytes at every call site
+__device__ __forceinline__ void tma_box_2d(void* dst, const void* map, int x, int y, uint64_t* bar, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void tma_box_3d(void* dst, const void* map, int x, int y, int z, uint64_t* bar, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)), "l"(policy) : "memory");
+}
 __device__ __forceinline__ void mma_k32(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+// unsigned A operand (bytes 0..255) against signed B
+__device__ __forceinline__ void mma_k32_us(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
@@ -133,63 +150,74 @@ template <int MT> struct AccT {
 };
 template <int DT, int MT> using Acc = AccT<MT>;
 
-// One Q4_K super-block (256 columns) of rows g and g+8 against every n-tile.
+// One Q4_K super-block (256 columns) of rows g and g+8 against every n-tile; pA / pB point at
+// the 144 bytes of the block in row g / g+8.
+// Low nibbles are an int8 A operand after one AND.  High nibbles stay where they are: the bytes
+// 16 q are an unsigned A operand, their sums go to a second accumulator, and the 1/16 is part of
+// the final scale (a power of two, so the int -> float rounding is the same).
 template <int MT>
-__device__ __forceinline__ void block_q4k(const uint8_t* rowA, const uint8_t* rowB, int b, int cb,
+__device__ __forceinline__ void block_q4k(const uint8_t* pA, const uint8_t* pB, int cb,
                                           const uint8_t* dig, const float* sxf, const float* xsi,
                                           int g, int t, Acc<DT_Q4_K, MT>& acc) {
   constexpr int NT = (MT + 1) / 2;
-  const uint4 hA = *(const uint4*)(rowA + b * 144), hB = *(const uint4*)(rowB + b * 144);
+  const uint4 hA = *(const uint4*)pA, hB = *(const uint4*)pB;
   // 6-bit scales and mins packed four to a word: bytes 0..3 = sub-blocks 0..3 (word 0), 4..7 (word 1)
   const uint32_t scA0 = hA.y & 0x3f3f3f3fu, scA1 = (hA.w & 0x0f0f0f0fu) | ((hA.y >> 2) & 0x30303030u);
   const uint32_t scB0 = hB.y & 0x3f3f3f3fu, scB1 = (hB.w & 0x0f0f0f0fu) | ((hB.y >> 2) & 0x30303030u);
-  int T[NT][4];
+  int Tl[NT][4], Th[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) T[nt][i] = 0;
+    for (int i = 0; i < 4; ++i) Tl[nt][i] = Th[nt][i] = 0;
 #pragma unroll
   for (int G = 0; G < 4; ++G) {
-    const uint2 wA = *(const uint2*)(rowA + b * 144 + 16 + G * 32 + 8 * t);
-    const uint2 wB = *(const uint2*)(rowB + b * 144 + 16 + G * 32 + 8 * t);
-    constexpr uint32_t M4 = 0x0f0f0f0fu;
+    const uint2 wA = *(const uint2*)(pA + 16 + G * 32 + 8 * t);
+    const uint2 wB = *(const uint2*)(pB + 16 + G * 32 + 8 * t);
+    constexpr uint32_t M4 = 0x0f0f0f0fu, MH = 0xf0f0f0f0u;
     const uint32_t scAp = G < 2 ? scA0 : scA1, scBp = G < 2 ? scB0 : scB1;
-    const int sAlo = (scAp >> (16 * (G & 1))) & 255, sAhi = (scAp >> (16 * (G & 1) + 8)) & 255;
-    const int sBlo = (scBp >> (16 * (G & 1))) & 255, sBhi = (scBp >> (16 * (G & 1) + 8)) & 255;
+    // byte 2 (G & 1) and the next one, zero-extended: one byte permute each
+    const int sAlo = (int)__byte_perm(scAp, 0, 0x4440 + 2 * (G & 1)), sAhi = (int)__byte_perm(scAp, 0, 0x4441 + 2 * (G & 1));
+    const int sBlo = (int)__byte_perm(scBp, 0, 0x4440 + 2 * (G & 1)), sBhi = (int)__byte_perm(scBp, 0, 0x4441 + 2 * (G & 1));
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const uint8_t* dp = plane_of<MT>(dig, nt, g) + cb * 256 + G * 64 + 8 * t;
       const uint2 blo = *(const uint2*)dp, bhi = *(const uint2*)(dp + 32);
       int clo[4], chi[4];
       mma_k32(clo, wA.x & M4, wB.x & M4, wA.y & M4, wB.y & M4, blo.x, blo.y);
-      mma_k32(chi, (wA.x >> 4) & M4, (wB.x >> 4) & M4, (wA.y >> 4) & M4, (wB.y >> 4) & M4, bhi.x, bhi.y);
-      T[nt][0] += sAlo * clo[0] + sAhi * chi[0];
-      T[nt][1] += sAlo * clo[1] + sAhi * chi[1];
-      T[nt][2] += sBlo * clo[2] + sBhi * chi[2];
-      T[nt][3] += sBlo * clo[3] + sBhi * chi[3];
+      mma_k32_us(chi, wA.x & MH, wB.x & MH, wA.y & MH, wB.y & MH, bhi.x, bhi.y);
+      Tl[nt][0] += sAlo * clo[0]; Th[nt][0] += sAhi * chi[0];
+      Tl[nt][1] += sAlo * clo[1]; Th[nt][1] += sAhi * chi[1];
+      Tl[nt][2] += sBlo * clo[2]; Th[nt][2] += sBhi * chi[2];
+      Tl[nt][3] += sBlo * clo[3]; Th[nt][3] += sBhi * chi[3];
     }
   }
   const float dA = h2f(hA.x & 0xffffu), dminA = h2f(hA.x >> 16);
   const float dB = h2f(hB.x & 0xffffu), dminB = h2f(hB.x >> 16);
-  // columns 2t, 2t+1 of an n-tile are activation row (t >> 1), digits 2(t&1) and 2(t&1)+1
-  const float pw0 = (t & 1) ? 65536.f : 1.f, pw1 = pw0 * 256.f;
+  // columns 2t, 2t+1 of an n-tile are activation row (t >> 1), digits 2(t&1) and 2(t&1)+1;
+  // the weights are 256^digit / 16
+  const float pw0 = (t & 1) ? 4096.f : 0.0625f, pw1 = pw0 * 256.f;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int tok = 2 * nt + (t >> 1);
     const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + cb] : 0.f;
-    acc.y[nt][0] = fmaf((float)T[nt][0], dA * xs * pw0, acc.y[nt][0]);
-    acc.y[nt][1] = fmaf((float)T[nt][1], dA * xs * pw1, acc.y[nt][1]);
-    acc.y[nt][2] = fmaf((float)T[nt][2], dB * xs * pw0, acc.y[nt][2]);
-    acc.y[nt][3] = fmaf((float)T[nt][3], dB * xs * pw1, acc.y[nt][3]);
+    // 16 Tl + Th < 2^31: |Tl| <= 4 * 63 * 32 * 15 * 128 < 2^24 and |Th| <= 16 times that
+    acc.y[nt][0] = fmaf((float)(Tl[nt][0] * 16 + Th[nt][0]), dA * xs * pw0, acc.y[nt][0]);
+    acc.y[nt][1] = fmaf((float)(Tl[nt][1] * 16 + Th[nt][1]), dA * xs * pw1, acc.y[nt][1]);
+    acc.y[nt][2] = fmaf((float)(Tl[nt][2] * 16 + Th[nt][2]), dB * xs * pw0, acc.y[nt][2]);
+    acc.y[nt][3] = fmaf((float)(Tl[nt][3] * 16 + Th[nt][3]), dB * xs * pw1, acc.y[nt][3]);
   }
-  // mins: this thread covers sub-blocks 2t, 2t+1 of both rows
-  const uint32_t mnA = t < 2 ? (hA.z & 0x3f3f3f3fu) : (((hA.w >> 4) & 0x0f0f0f0fu) | ((hA.z >> 2) & 0x30303030u));
-  const uint32_t mnB = t < 2 ? (hB.z & 0x3f3f3f3fu) : (((hB.w >> 4) & 0x0f0f0f0fu) | ((hB.z >> 2) & 0x30303030u));
-  const float a0 = dminA * (float)((mnA >> (16 * (t & 1))) & 255), a1 = dminA * (float)((mnA >> (16 * (t & 1) + 8)) & 255);
-  const float b0 = dminB * (float)((mnB >> (16 * (t & 1))) & 255), b1 = dminB * (float)((mnB >> (16 * (t & 1) + 8)) & 255);
+  // mins: this thread covers sub-blocks t and t + 4 of both rows.  Byte t of header words 2 and 3
+  // of both rows side by side (row g in byte 0, row g+8 in byte 2), so that the 6-bit fields of
+  // the two rows are assembled together.
+  const uint32_t sel = 0x4040u + (uint32_t)t + ((uint32_t)(4 + t) << 8);  // bytes 1 and 3 are masked off below
+  const uint32_t zz = __byte_perm(hA.z, hB.z, sel), ww = __byte_perm(hA.w, hB.w, sel);
+  const uint32_t mlo = zz & 0x003f003fu;
+  const uint32_t mhi = ((ww >> 4) & 0x000f000fu) | ((zz >> 2) & 0x00300030u);
+  const float a0 = dminA * (float)(mlo & 0xffu), a1 = dminA * (float)(mhi & 0xffu);
+  const float b0 = dminB * (float)((mlo >> 16) & 0xffu), b1 = dminB * (float)((mhi >> 16) & 0xffu);
 #pragma unroll
   for (int k = 0; k < MT; ++k) {
-    const float s0 = sxf[k * (Sp<MT>::SPAN / 32) + cb * 8 + 2 * t], s1 = sxf[k * (Sp<MT>::SPAN / 32) + cb * 8 + 2 * t + 1];
+    const float s0 = sxf[k * (Sp<MT>::SPAN / 32) + cb * 8 + t], s1 = sxf[k * (Sp<MT>::SPAN / 32) + cb * 8 + t + 4];
     acc.mn[0][k] = fmaf(a0, s0, fmaf(a1, s1, acc.mn[0][k]));
     acc.mn[1][k] = fmaf(b0, s0, fmaf(b1, s1, acc.mn[1][k]));
   }
