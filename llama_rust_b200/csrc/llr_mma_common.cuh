@@ -124,23 +124,6 @@ __device__ __forceinline__ void mma_k16(int (&c)[4], uint32_t a0, uint32_t a1, u
 }
 __device__ __forceinline__ float h2f(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
 
-// four bytes at p (p is 2-byte aligned; `odd` says p % 4 == 2)
-__device__ __forceinline__ uint32_t lds32_a2(const uint8_t* p, bool odd) {
-  if (!odd) return *(const uint32_t*)p;
-  const uint32_t lo = *(const uint32_t*)(p - 2), hi = *(const uint32_t*)(p + 2);
-  return __funnelshift_r(lo, hi, 16);
-}
-// eight bytes at p, same alignment rule
-__device__ __forceinline__ uint2 lds64_a2(const uint8_t* p, bool odd) {
-  if (!odd) return make_uint2(*(const uint32_t*)p, *(const uint32_t*)(p + 4));
-  const uint32_t x0 = *(const uint32_t*)(p - 2), x1 = *(const uint32_t*)(p + 2), x2 = *(const uint32_t*)(p + 6);
-  return make_uint2(__funnelshift_r(x0, x1, 16), __funnelshift_r(x1, x2, 16));
-}
-// per byte: 6-bit code c (0..63) -> int8 (c - 32); no carries cross bytes
-__device__ __forceinline__ uint32_t recentre6(uint32_t c) {
-  return ((c | 0x80808080u) - 0x20202020u) ^ 0x80808080u;
-}
-
 // Per-thread accumulators of one chunk: yacc[nt][0..1] row g, [2..3] row g+8,
 // columns 2t, 2t+1 of n-tile nt; ymin only for Q4_K.
 template <int MT> struct AccT {
@@ -223,15 +206,25 @@ __device__ __forceinline__ void block_q4k(const uint8_t* pA, const uint8_t* pB, 
   }
 }
 
-// One Q6_K super-block: 16 scale groups of 16 columns, one m16n8k16 each.
-template <int MT>
-__device__ __forceinline__ void block_q6k(const uint8_t* rowA, const uint8_t* rowB, int b, int cb,
-                                          const uint8_t* dig, const float* xsi, int g, int t,
-                                          Acc<DT_Q6_K, MT>& acc) {
+// Four bytes at p.  Q6_K blocks are 210 bytes long and row pieces start 16-byte aligned, so the
+// bytes of an odd block sit 2 bytes off a word boundary: two aligned words and a funnel shift.
+template <bool ODD> __device__ __forceinline__ uint32_t lds32_par(const uint8_t* p) {
+  if (!ODD) return *(const uint32_t*)p;
+  return __funnelshift_r(*(const uint32_t*)(p - 2), *(const uint32_t*)(p + 2), 16);
+}
+
+// One Q6_K super-block: 16 scale groups of 16 columns, one m16n8k16 each; pA / pB point at the
+// 210 bytes of the block in row g / g+8, ODD says whether they are 2 bytes off a word boundary
+// (a template parameter: with a run-time flag the compiler issued the loads of both cases).
+// The A operand is (code << 2) ^ 0x80 per byte = 4 (code - 32) as int8: the two high bits come
+// from qh, whose bit 1 of every 2-bit field is flipped once per word, the four low bits from
+// ql shifted by two; the 1/4 is part of the final scale (a power of two, so the int -> float
+// rounding is the same).
+template <int MT, bool ODD>
+__device__ __forceinline__ void block_q6k_par(const uint8_t* pA, const uint8_t* pB, int cb,
+                                              const uint8_t* dig, const float* xsi, int g, int t,
+                                              Acc<DT_Q6_K, MT>& acc) {
   constexpr int NT = (MT + 1) / 2;
-  const uint8_t* pA = rowA + b * 210;
-  const uint8_t* pB = rowB + b * 210;
-  const bool odd = (b & 1) != 0;  // 210 b mod 4 is 2 for odd b (row segments start 16-byte aligned)
   int T[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
@@ -242,16 +235,17 @@ __device__ __forceinline__ void block_q6k(const uint8_t* rowA, const uint8_t* ro
 #pragma unroll
     for (int hg = 0; hg < 2; ++hg) {  // l = 16*hg + 4t .. +3 of the 32-wide runs
       const int l = 16 * hg + 4 * t;
-      const uint32_t qlA0 = lds32_a2(pA + half * 64 + l, odd), qlA1 = lds32_a2(pA + half * 64 + 32 + l, odd);
-      const uint32_t qhA = lds32_a2(pA + 128 + half * 32 + l, odd);
-      const uint32_t qlB0 = lds32_a2(pB + half * 64 + l, odd), qlB1 = lds32_a2(pB + half * 64 + 32 + l, odd);
-      const uint32_t qhB = lds32_a2(pB + 128 + half * 32 + l, odd);
-      constexpr uint32_t M4 = 0x0f0f0f0fu, M2 = 0x03030303u;
+      const uint32_t qlA0 = lds32_par<ODD>(pA + half * 64 + l), qlA1 = lds32_par<ODD>(pA + half * 64 + 32 + l);
+      const uint32_t qhA = lds32_par<ODD>(pA + 128 + half * 32 + l) ^ 0xaaaaaaaau;
+      const uint32_t qlB0 = lds32_par<ODD>(pB + half * 64 + l), qlB1 = lds32_par<ODD>(pB + half * 64 + 32 + l);
+      const uint32_t qhB = lds32_par<ODD>(pB + 128 + half * 32 + l) ^ 0xaaaaaaaau;
+      constexpr uint32_t ML = 0x3c3c3c3cu, MH = 0xc0c0c0c0u;
 #pragma unroll
       for (int qtr = 0; qtr < 4; ++qtr) {
         const uint32_t lA = (qtr & 1) ? qlA1 : qlA0, lB = (qtr & 1) ? qlB1 : qlB0;
-        const uint32_t cA = recentre6((((qtr & 2) ? (lA >> 4) : lA) & M4) | (((qhA >> (2 * qtr)) & M2) << 4));
-        const uint32_t cB = recentre6((((qtr & 2) ? (lB >> 4) : lB) & M4) | (((qhB >> (2 * qtr)) & M2) << 4));
+        const uint32_t lsA = (qtr & 2) ? (lA >> 2) : (lA << 2), lsB = (qtr & 2) ? (lB >> 2) : (lB << 2);
+        const uint32_t cA = (lsA & ML) | ((qhA << (6 - 2 * qtr)) & MH);
+        const uint32_t cB = (lsB & ML) | ((qhB << (6 - 2 * qtr)) & MH);
         const int sidx = 192 + half * 8 + hg + 2 * qtr;
         const int sA = (int)(int8_t)pA[sidx], sB = (int)(int8_t)pB[sidx];
         const int col = cb * 256 + half * 128 + qtr * 32 + l;  // first of this thread's 4 columns
@@ -266,8 +260,9 @@ __device__ __forceinline__ void block_q6k(const uint8_t* rowA, const uint8_t* ro
       }
     }
   }
-  const float dA = h2f(pA[208] | (pA[209] << 8)), dB = h2f(pB[208] | (pB[209] << 8));
-  const float pw0 = (t & 1) ? 65536.f : 1.f, pw1 = pw0 * 256.f;
+  // |T| <= 16 groups * 128 * 16 columns * 128 * 128 < 2^31
+  const float dA = h2f(*(const uint16_t*)(pA + 208)), dB = h2f(*(const uint16_t*)(pB + 208));
+  const float pw0 = (t & 1) ? 16384.f : 0.25f, pw1 = pw0 * 256.f;  // 256^digit / 4
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int tok = 2 * nt + (t >> 1);
@@ -278,17 +273,32 @@ __device__ __forceinline__ void block_q6k(const uint8_t* rowA, const uint8_t* ro
     acc.y[nt][3] = fmaf((float)T[nt][3], dB * xs * pw1, acc.y[nt][3]);
   }
 }
-
-// One Q8_0 block (32 columns): the int8 quants are the A fragment as they lie.
+// block b of the row pieces rowA / rowB
 template <int MT>
-__device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* rowB, int b, int c32,
+__device__ __forceinline__ void block_q6k(const uint8_t* rowA, const uint8_t* rowB, int b, int cb,
                                           const uint8_t* dig, const float* xsi, int g, int t,
-                                          Acc<DT_Q8_0, MT>& acc) {
+                                          Acc<DT_Q6_K, MT>& acc) {
+  if (b & 1) block_q6k_par<MT, true>(rowA + b * 210, rowB + b * 210, cb, dig, xsi, g, t, acc);
+  else block_q6k_par<MT, false>(rowA + b * 210, rowB + b * 210, cb, dig, xsi, g, t, acc);
+}
+
+// One Q8_0 block (32 columns): the int8 quants are the A fragment as they lie.  Blocks are 34
+// bytes long: the quants of an even block start 2 bytes off a word boundary (OFF).
+template <int MT, bool OFF>
+__device__ __forceinline__ void block_q80_par(const uint8_t* pA, const uint8_t* pB, int c32,
+                                              const uint8_t* dig, const float* xsi, int g, int t,
+                                              Acc<DT_Q8_0, MT>& acc) {
   constexpr int NT = (MT + 1) / 2;
-  const uint8_t* pA = rowA + b * 34;
-  const uint8_t* pB = rowB + b * 34;
-  const bool odd = (b & 1) == 0;  // quants start at 34 b + 2: 4-byte aligned for odd b only
-  const uint2 wA = lds64_a2(pA + 2 + 8 * t, odd), wB = lds64_a2(pB + 2 + 8 * t, odd);
+  uint2 wA, wB;
+  if (!OFF) {
+    wA = make_uint2(*(const uint32_t*)(pA + 2 + 8 * t), *(const uint32_t*)(pA + 6 + 8 * t));
+    wB = make_uint2(*(const uint32_t*)(pB + 2 + 8 * t), *(const uint32_t*)(pB + 6 + 8 * t));
+  } else {
+    const uint32_t a0 = *(const uint32_t*)(pA + 8 * t), a1 = *(const uint32_t*)(pA + 4 + 8 * t), a2 = *(const uint32_t*)(pA + 8 + 8 * t);
+    const uint32_t b0 = *(const uint32_t*)(pB + 8 * t), b1 = *(const uint32_t*)(pB + 4 + 8 * t), b2 = *(const uint32_t*)(pB + 8 + 8 * t);
+    wA = make_uint2(__funnelshift_r(a0, a1, 16), __funnelshift_r(a1, a2, 16));
+    wB = make_uint2(__funnelshift_r(b0, b1, 16), __funnelshift_r(b1, b2, 16));
+  }
   const float dA = h2f(*(const uint16_t*)pA), dB = h2f(*(const uint16_t*)pB);
   const float pw0 = (t & 1) ? 65536.f : 1.f, pw1 = pw0 * 256.f;
 #pragma unroll
@@ -303,6 +313,14 @@ __device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* ro
     acc.y[nt][2] = fmaf((float)c[2], dB * xs * pw0, acc.y[nt][2]);
     acc.y[nt][3] = fmaf((float)c[3], dB * xs * pw1, acc.y[nt][3]);
   }
+}
+// block b of the row pieces rowA / rowB (row pieces start 16-byte aligned)
+template <int MT>
+__device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* rowB, int b, int c32,
+                                          const uint8_t* dig, const float* xsi, int g, int t,
+                                          Acc<DT_Q8_0, MT>& acc) {
+  if (b & 1) block_q80_par<MT, false>(rowA + b * 34, rowB + b * 34, c32, dig, xsi, g, t, acc);
+  else block_q80_par<MT, true>(rowA + b * 34, rowB + b * 34, c32, dig, xsi, g, t, acc);
 }
 
 
