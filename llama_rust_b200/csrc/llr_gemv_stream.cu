@@ -303,6 +303,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
   bool ok = true;
   const float* cur_x = nullptr;
   int cur_cols = -1, cur_span = -1, cur_tokens = -1;
+  const uint64_t keep = l2_policy_evict_last();
   // Programs: the entries of a phase are fetched into shared memory before the dependency
   // wait, so that after the wait the consumers do not pay a global-memory round trip for them.
   static_assert(sizeof(ProgEntry) == 64, "entry copy below moves eight 8-byte words per entry");
@@ -317,31 +318,14 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
       const unsigned long long* src = (const unsigned long long*)(wk.entries + P.first_entry);
       if (lane < 8 * n_cached) s_ent[ph & 1][lane >> 3][lane & 7] = __ldg(src + lane);
     }
-    if (PROGRAM && !((P.wait_prev && ph > 0) || (PEERS && ph == 0))) consumer_sync();  // publish the cached entries
-    // a sharded program also holds back the first phase of a run until every rank has finished
-    // the previous run (its peers' stores into this rank's buffers belong to that run)
-    if (PROGRAM && ((P.wait_prev && ph > 0) || (PEERS && ph == 0))) {
-      if (tid == 0) {
-        const unsigned long long runs = ph > 0 ? epoch : epoch - 1;
-        const unsigned long long want = runs * (unsigned long long)nb;
-        const int dep = ph > 0 ? ph - 1 : wk.n_phases - 1;
-        const unsigned long long* cp = counters + dep;
-        // sharded: also one arrival per peer and run on this rank's copy of the peers' counter
-        const unsigned long long want_peers = PEERS ? runs * (unsigned long long)wk.peers->n_peers : 0ull;
-        const unsigned long long* pp = counters + PEER_COUNTER_OFFSET + dep;
-        int polls = 0;
-        for (;;) {
-          unsigned long long v, u = want_peers;
-          asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cp) : "memory");
-          if (PEERS) asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(u) : "l"(pp) : "memory");
-          if (v >= want && u >= want_peers) break;
-          if (++polls > POLL_LIMIT) { report_error(err, 2); break; }
-          __nanosleep(polls < 8 ? 64 : 256);  // hundreds of CTAs poll one word: keep the L2 bank free for the adds
-        }
-      }
-      consumer_sync();
-      cur_x = nullptr;  // the same buffer may hold new values now
-    }
+    if (PROGRAM) consumer_sync();  // publish the cached entries
+    // The dependency of the phase is awaited as late as possible: everything that does not need
+    // the activations (entry, geometry) is done first, so that the loads of the split are the
+    // first thing after the wait.  A CTA without tiles in the phase does not wait at all: the
+    // counters it waits for in its next phase imply this one.
+    // A sharded program also holds back the first phase of a run until every rank has finished
+    // the previous run (its peers' stores into this rank's buffers belong to that run).
+    bool waited = !(PROGRAM && ((P.wait_prev && ph > 0) || (PEERS && ph == 0)));
     for (int ei = 0; ei < P.n_entries && lo < hi; ++ei) {
       ProgEntry E;
       if (ei < n_cached) E = *(const ProgEntry*)&s_ent[ph & 1][ei][0];
@@ -352,10 +336,33 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
       const int n_span = (E.cols + SPAN - 1) / SPAN;
       for (int span = 0; span < n_span; ++span) {
         const int span_cols = min(SPAN, E.cols - span * SPAN), nblk256 = span_cols >> 8;
-        if (cur_x != E.x || cur_cols != E.cols || cur_span != span || cur_tokens != E.tokens) {
-          consumer_sync();  // nobody still multiplies against the old planes
-          split_activations<MT>(E.x, E.cols, span * SPAN, nblk256, E.tokens, dig, sxf, xsi, warp, lane);
-          consumer_sync();
+        if (!waited || cur_x != E.x || cur_cols != E.cols || cur_span != span || cur_tokens != E.tokens) {
+          if (!waited) {
+            if (tid == 0) {
+              const unsigned long long runs = ph > 0 ? epoch : epoch - 1;
+              const unsigned long long want = runs * (unsigned long long)nb;
+              const int dep = ph > 0 ? ph - 1 : wk.n_phases - 1;
+              const unsigned long long* cp = counters + dep;
+              // sharded: also one arrival per peer and run on this rank's copy of the peers' counter
+              const unsigned long long want_peers = PEERS ? runs * (unsigned long long)wk.peers->n_peers : 0ull;
+              const unsigned long long* pp = counters + PEER_COUNTER_OFFSET + dep;
+              int polls = 0;
+              for (;;) {
+                unsigned long long v, u = want_peers;
+                asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cp) : "memory");
+                if (PEERS) asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(u) : "l"(pp) : "memory");
+                if (v >= want && u >= want_peers) break;
+                if (++polls > POLL_LIMIT) { report_error(err, 2); break; }
+                __nanosleep(polls < 8 ? 64 : 256);  // hundreds of CTAs poll one word: keep the L2 bank free for the adds
+              }
+            }
+            consumer_sync();
+            waited = true;
+          }
+          // the planes a warp overwrites are the ones it alone reads (see split_activations)
+          __syncwarp();
+          split_activations<MT>(E.x, E.cols, span * SPAN, nblk256, E.tokens, dig, sxf, xsi, warp, lane, keep);
+          __syncwarp();
           cur_x = E.x; cur_cols = E.cols; cur_span = span; cur_tokens = E.tokens;
         }
         const int nsub = (span_cols + gm.kseg - 1) / gm.kseg;
@@ -382,8 +389,10 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
               for (int b = warp; b < (seg_cols >> 8); b += CW)
                 block_q6k<MT>(rowA, rowB, b, sub * (gm.kseg / 256) + b, dig, xsi, g, t, acc);
             } else {
-              for (int b = warp; b < (seg_cols >> 5); b += CW)
-                block_q80<MT>(rowA, rowB, b, sub * (gm.kseg / 32) + b, dig, xsi, g, t, acc);
+              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW)  // the eight blocks of 256 columns b8
+#pragma unroll 2
+                for (int i = 0; i < 8; ++i)
+                  block_q80<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, xsi, g, t, acc);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[stage]);  // this warp no longer reads the stage

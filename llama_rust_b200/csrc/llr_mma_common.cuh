@@ -326,23 +326,24 @@ __device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* ro
 
 // Activations of one span (nblk256 blocks of 256 columns starting at column col0, `tokens`
 // activation rows) -> four int8 digit planes per activation row, the f32 sums of x per 32
-// columns (Q4_K mins) and 2^-e per block.  One warp per (block, row).  Loads are L2-coherent
-// (the activations may have been produced by an earlier phase of the same launch) and kept in L2.
+// columns (Q4_K mins) and 2^-e per block.  Loads are L2-coherent (the activations may have been
+// produced by an earlier phase of the same launch) and kept in L2 (policy `keep`).
+// Warp w of the eight consumer warps splits the blocks b = w (mod 8) of every activation row, and
+// those are exactly the blocks whose planes, sums and scales it reads in the block routines: no
+// other warp depends on what it writes here, so a __syncwarp() is all the caller needs.
 template <int MT>
 __device__ __forceinline__ void split_activations(const float* __restrict__ X, int cols, int col0,
                                                   int nblk256, int tokens, uint8_t* dig, float* sxf,
-                                                  float* xsi, int warp, int lane) {
-  // two jobs per warp and pass: both loads are in flight before either is used
-  const int njobs = nblk256 * tokens;
-  const uint64_t keep = l2_policy_evict_last();
-  for (int job0 = warp; job0 < njobs; job0 += 2 * NWARP) {
+                                                  float* xsi, int warp, int lane, uint64_t keep) {
+  // two jobs per pass: both loads are in flight before either is used.  One activation row: blocks
+  // b0 and b0 + 8; several: rows tok0 and tok0 + 1 of block b0.
+  for (int b0 = warp; b0 < nblk256; b0 += (MT == 1 ? 2 * NWARP : NWARP))
+  for (int tok0 = 0; tok0 < tokens; tok0 += (MT == 1 ? 1 : 2)) {
    float4 pa[2], pb[2];
 #pragma unroll
    for (int u = 0; u < 2; ++u) {
-    const int job = job0 + u * NWARP;
-    if (job < njobs) {
-      // one activation row: job = block (no integer division on the critical path of every phase)
-      const int jt = MT == 1 ? 0 : job / nblk256, jb = MT == 1 ? job : job - jt * nblk256;
+    const int jb = MT == 1 ? b0 + u * NWARP : b0, jt = MT == 1 ? 0 : tok0 + u;
+    if (MT == 1 ? jb < nblk256 : jt < tokens) {
       const float4* xp = (const float4*)(X + (int64_t)jt * cols + col0 + jb * 256 + 8 * lane);
       pa[u] = ld_x_keep(xp, keep);
       pb[u] = ld_x_keep(xp + 1, keep);
@@ -350,9 +351,8 @@ __device__ __forceinline__ void split_activations(const float* __restrict__ X, i
    }
 #pragma unroll
    for (int u = 0; u < 2; ++u) {
-    const int job = job0 + u * NWARP;
-    if (job >= njobs) break;
-    const int tok = MT == 1 ? 0 : job / nblk256, b = MT == 1 ? job : job - tok * nblk256;
+    const int b = MT == 1 ? b0 + u * NWARP : b0, tok = MT == 1 ? 0 : tok0 + u;
+    if (MT == 1 ? b >= nblk256 : tok >= tokens) break;
     const float4 va = pa[u], vb = pb[u];
     const float v[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
     // Largest magnitude of the block as a bit pattern: for non-negative floats the unsigned order of
