@@ -104,6 +104,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity) {
     if (++spins > SPIN_LIMIT) return false;
   return true;
 }
+// Q4_K stages lie [block][row][144 bytes]: rows 144 bytes apart are 16 bytes apart modulo
+// 128, so the 8-byte fragment reads of four consecutive rows (one half-warp) would overlap in
+// the banks.  Fragment row g therefore reads tile row 2 (g & 3) + (g >> 2): the four rows of a
+// half-warp are 288 bytes apart (32 modulo 128) and cover all banks once.
+__device__ __forceinline__ int q4k_row(int g) { return 2 * (g & 3) + (g >> 2); }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory"); }
 
 // What a launch works on: a list of entries in global memory (program) or one entry
@@ -383,8 +388,9 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
             const int seg_cols = min(gm.kseg, span_cols - sub * gm.kseg);
             const int dtype = DTFIX >= 0 ? DTFIX : E.dtype;
             if (dtype == DT_Q4_K) {
-              for (int b = warp; b < (seg_cols >> 8); b += CW)  // stage layout [block][row][144]
-                block_q4k<MT>(chunk + (b * 16 + g) * 144, chunk + (b * 16 + g + 8) * 144, sub * (gm.kseg / 256) + b, dig, sxf, xsi, g, t, acc);
+              // stage layout [block][row][144]; fragment row g is tile row q4k_row(g), see there
+              for (int b = warp; b < (seg_cols >> 8); b += CW)
+                block_q4k<MT>(chunk + (b * 16 + q4k_row(g)) * 144, chunk + (b * 16 + q4k_row(g) + 8) * 144, sub * (gm.kseg / 256) + b, dig, sxf, xsi, g, t, acc);
             } else if (dtype == DT_Q6_K) {
               for (int b = warp; b < (seg_cols >> 8); b += CW)
                 block_q6k<MT>(rowA, rowB, b, sub * (gm.kseg / 256) + b, dig, xsi, g, t, acc);
@@ -423,8 +429,9 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
 #pragma unroll
               for (int k = 0; k < MT; ++k)
                 if (k == tok) { mA = acc.mn[0][k]; mB = acc.mn[1][k]; }
-              myred[g * MT + tok] = vA - mA;
-              myred[(g + 8) * MT + tok] = vB - mB;
+              const int gr = (DTFIX >= 0 ? DTFIX : E.dtype) == DT_Q4_K ? q4k_row(g) : g;
+              myred[gr * MT + tok] = vA - mA;
+              myred[(gr + 8) * MT + tok] = vB - mB;
             }
           }
           __syncwarp();
