@@ -123,9 +123,14 @@ struct Work {
 };
 
 // Tile range of this CTA inside a phase, and inside one entry of it.
+// The grid is two CTAs per SM and CTAs b and b + nb/2 usually share an SM.  Slices are dealt so
+// that those two get neighbouring slices: the slices with one tile more than the rest (or one
+// less) then spread over the SMs instead of meeting in pairs on a few of them.
 __device__ __forceinline__ void phase_range(const ProgPhase& P, int bid, int nb, int* lo, int* hi) {
-  *lo = (int)((int64_t)P.n_tiles * bid / nb);
-  *hi = (int)((int64_t)P.n_tiles * (bid + 1) / nb);
+  const int half = nb >> 1;
+  const int slot = (nb & 1) ? bid : (bid < half ? 2 * bid : 2 * (bid - half) + 1);
+  *lo = (int)((int64_t)P.n_tiles * slot / nb);
+  *hi = (int)((int64_t)P.n_tiles * (slot + 1) / nb);
 }
 __device__ __forceinline__ bool entry_range(const ProgEntry& E, int lo, int hi, int* t0, int* t1) {
   *t0 = max(lo, E.tile_begin) - E.tile_begin;
