@@ -48,6 +48,19 @@ __global__ void silu_mul_kernel(float* __restrict__ g, const float* __restrict__
   }
 }
 
+// the same, four elements per thread and pass (both arrays 16-byte aligned, n4 = n / 4)
+__global__ void silu_mul4_kernel(float4* __restrict__ g, const float4* __restrict__ u, int64_t n4) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 v = g[i];
+    const float4 w = __ldg(u + i);
+    v.x = (v.x / (1.0f + expf(-v.x))) * w.x;
+    v.y = (v.y / (1.0f + expf(-v.y))) * w.y;
+    v.z = (v.z / (1.0f + expf(-v.z))) * w.z;
+    v.w = (v.w / (1.0f + expf(-v.w))) * w.w;
+    g[i] = v;
+  }
+}
+
 // rows_of_tok[t*n_used + j]: packed row of token t's j-th selection, selections ordered by
 // ascending expert id; w_of_tok the matching router weights.
 __global__ void scatter_combine_kernel(const float* __restrict__ y, const int* __restrict__ rows_of_tok,
@@ -84,9 +97,15 @@ cudaError_t launch_router_logits(const float* w, const float* x, float* logits, 
 
 cudaError_t launch_silu_mul(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches) {
   if (n <= 0) return cudaSuccess;
-  int64_t blocks = (n + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  silu_mul_kernel<<<(unsigned)blocks, 256, 0, s>>>(g, u, n);
+  if (n % 4 == 0 && (((uintptr_t)g | (uintptr_t)u) & 15) == 0) {
+    int64_t blocks = (n / 4 + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    silu_mul4_kernel<<<(unsigned)blocks, 256, 0, s>>>((float4*)g, (const float4*)u, n / 4);
+  } else {
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    silu_mul_kernel<<<(unsigned)blocks, 256, 0, s>>>(g, u, n);
+  }
   if (launches) ++*launches;
   return cudaGetLastError();
 }
