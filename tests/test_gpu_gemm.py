@@ -100,3 +100,35 @@ def test_operand_format_follows_weight_range(ex, orc):
     m2.free()
     mb.free()
     ex.set_path(0)
+
+
+@pytest.mark.parametrize("name,rows,cols", [("Q4_K", 14336, 4096), ("Q8_0", 4096, 14336), ("Q5_0", 4096, 4096),
+                                            ("Q5_1", 4096, 4096)])
+@pytest.mark.parametrize("tokens", [64, 1024])
+def test_config4_full_size_shapes_on_sampled_rows(ex, orc, name, rows, cols, tokens):
+    """BASELINE config 4 at its full sizes (Q8_0 4096x14336 runs split along K).  The device
+    computes the whole product; the CPU f32 row kernels are run on a sample of the weight rows
+    (the first and last row tile and 64 rows spread over the matrix), which keeps the CPU side
+    to seconds, and the same bounds as above are asserted on those outputs.  Every output is
+    checked to be finite."""
+    from llama_rust_b200 import row_bytes, synth
+    kind = ALL[name]
+    m = ex.synth(kind, rows, cols, synth.tensor_seed(4, f"config4.{name}.{rows}x{cols}"))
+    w = ex.download(m)
+    x = synth.activations(tokens * cols, synth.tensor_seed(4, f"x.{tokens}.{cols}"))
+    ex.set_path(0)  # automatic choice: the tensor-core GEMM from 64 rows on
+    y = np.full(rows * tokens, np.nan, np.float32)
+    ex.gemm_resident(m, tokens, x, y)
+    y = y.reshape(tokens, rows)
+    assert np.all(np.isfinite(y))
+    rng = np.random.default_rng(rows + cols + tokens)
+    sel = np.unique(np.concatenate([np.arange(128), np.arange(rows - 128, rows), rng.integers(0, rows, 64)]))
+    rb = row_bytes(kind, cols)
+    wsel = np.ascontiguousarray(w.reshape(rows, rb)[sel]).reshape(-1)
+    cpu = orc.gemm(kind, cols, tokens, wsel, x, len(sel), simd=True)
+    got = y[:, sel]
+    rel_l2 = np.linalg.norm(got - cpu) / np.linalg.norm(cpu)
+    assert rel_l2 <= 4e-3, f"{name} {rows}x{cols} M={tokens}: relative L2 error {rel_l2:.3e}"
+    rms_terms = _bounds(kind, len(sel), cols, wsel, x, tokens, orc)
+    assert np.all(np.abs(got - cpu) <= 6 * 2.0 ** -8 * rms_terms + 1e-6), f"{name} M={tokens}: element outside the bound"
+    m.free()

@@ -89,3 +89,32 @@ def test_striped_experts_partials_sum_to_the_single_device_layer(orc):
     with pytest.raises(NativeCudaError):  # no resident expert at all
         ex.moe_ffn(router, [None] * n_expert, [None] * n_expert, [None] * n_expert, n_used, True, x)
     ex.close()
+
+
+def test_config5_full_size_layer(orc):
+    """BASELINE config 5 at its full size: 8 experts, top-2, 4096 / 14336, Q4_K experts generated on
+    the device from seeds (792 MB), F32 router, 64 tokens.  One CPU walk of the layer (the
+    oracle, 4.5e10 FLOP) is compared with the f32-faithful decode path and with the automatic
+    choice (grouped tensor-core launches)."""
+    from llama_rust_b200 import Executor, synth
+    n_expert, n_used, n_embd, n_ff, tokens = 8, 2, 4096, 14336, 64
+    with Executor(0) as ex:
+        mats = {k: [ex.synth(Q4_K, r, c, synth.tensor_seed(5, f"config5.{k}.{e}")) for e in range(n_expert)]
+                for k, (r, c) in {"gate": (n_ff, n_embd), "up": (n_ff, n_embd), "down": (n_embd, n_ff)}.items()}
+        packs = {k: [ex.download(m) for m in v] for k, v in mats.items()}
+        router_w = (synth.activations(n_expert * n_embd, synth.tensor_seed(5, "config5.router")) * np.float32(0.05)).reshape(n_expert, n_embd)
+        router = ex.upload(F32, n_expert, n_embd, router_w.view(np.uint8).reshape(-1))
+        x = synth.activations(tokens * n_embd, synth.tensor_seed(5, "config5.x")).reshape(tokens, n_embd)
+        ref_out, ref_ids, ref_w = orc.moe_ffn(n_used, True, F32, router_w.view(np.uint8).reshape(-1), Q4_K, packs["gate"],
+                                              packs["up"], packs["down"], n_embd, n_ff, x)
+        scale = max(1.0, float(np.abs(ref_out).max()))
+        for path, tol in ((3, 3e-5), (0, 2e-2)):
+            ex.set_path(path)
+            out, ids, w = ex.moe_ffn(router, mats["gate"], mats["up"], mats["down"], n_used, True, x)
+            assert np.array_equal(ids, ref_ids), "routing decisions differ"
+            # router logits are 4096-term f32 sums in another order than the CPU's: 1e-5 relative, the
+            # reference's tolerance for its own row kernels
+            assert np.allclose(w, ref_w, rtol=1e-5, atol=1e-6)
+            assert np.all(np.isfinite(out))
+            err = float(np.abs(out - ref_out).max())
+            assert err <= tol * scale, f"path {path}: max err {err:.3e} vs scale {scale:.3g}"
