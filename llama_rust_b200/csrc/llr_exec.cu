@@ -908,8 +908,6 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
                      (ce = ensure_scratch(e, L->gate[busiest], most, &unused)) != cudaSuccess))
       return fail_cuda(e, ce, "kernel scratch");
   }
-  if ((ce = launch_gather_rows(d_x, d_tok_of_row, d_pack, (int)n_rows, (int)n_embd, e->stream, &e->ctr.launches)) != cudaSuccess)
-    return fail_cuda(e, ce, "kernel launch");
   // Grouped tensor-core path (automatic choice, 64 routed rows or more, formats the GEMM takes): the tiles of
   // all experts' gate and up products in one launch, silu(g)*u, all down products in one launch.
   bool grouped = e->path == PATH_AUTO && n_rows >= 64;
@@ -928,6 +926,9 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
   bool any_local_rows = false;
   for (size_t ex = 0; ex < n_exp; ++ex) any_local_rows = any_local_rows || (local[ex] && first_row[ex + 1] > first_row[ex]);
   if (!any_local_rows) grouped = false;  // nothing routed to a resident expert: the loops below do nothing either
+  // the grouped path gathers and converts in one kernel and never needs the packed f32 rows
+  if (!grouped && (ce = launch_gather_rows(d_x, d_tok_of_row, d_pack, (int)n_rows, (int)n_embd, e->stream, &e->ctr.launches)) != cudaSuccess)
+    return fail_cuda(e, ce, "kernel launch");
   if (grouped) {
     std::vector<GemmGroupSpec> specs;
     for (size_t ex = 0; ex < n_exp; ++ex) {
@@ -936,7 +937,8 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
       specs.push_back(GemmGroupSpec{view_of(L->gate[ex]), d_x16a + r0 * n_embd * 2, d_sa + r0, d_g + r0 * n_ff, (int)n});
       specs.push_back(GemmGroupSpec{view_of(L->up[ex]), d_x16a + r0 * n_embd * 2, d_sa + r0, d_u + r0 * n_ff, (int)n});
     }
-    if ((ce = tc_convert_activations(d_pack, (int64_t)n_rows, (int)n_embd, f16a != 0, d_x16a, d_sa, e->stream, &e->ctr.launches)) != cudaSuccess ||
+    if ((ce = tc_convert_expert_rows(d_x, d_tok_of_row, (int64_t)n_rows, (int)n_embd, f16a != 0, d_x16a, d_sa, e->stream,
+                                     &e->ctr.launches)) != cudaSuccess ||
         (ce = launch_gemm_tc_grouped(specs.data(), (int)specs.size(), f16a != 0, d_desc, e->stream, e->err_flag, &e->ctr.launches)) != cudaSuccess ||
         (ce = launch_silu_mul(d_g, d_u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess)
       return fail_cuda(e, ce, "kernel launch");

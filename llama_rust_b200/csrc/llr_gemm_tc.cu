@@ -663,6 +663,58 @@ __global__ void to_f16_rows_kernel(const float* __restrict__ x, __half* __restri
   }
 }
 
+// Routed-expert layer: the 16-bit operand rows of the gate / up products gathered straight from the
+// layer's activations, one CTA per packed row: row r is read from row src_row[r] of x (the gather
+// of the rows routed to an expert, decode.rs:10062) and no packed f32 copy is made.  F16: per-row
+// power-of-two scaling as in to_f16_rows_kernel; otherwise bfloat16 without scaling.
+// (silu(g) * u was tried in here as well: with one CTA per row it took longer than the two
+// separate element-wise kernels.)
+template <bool F16>
+__global__ void expert_rows_16bit_kernel(const float* __restrict__ x, const int* __restrict__ src_row,
+                                         void* __restrict__ o, float* __restrict__ inv_scale, int cols) {
+  __shared__ float wmax[8];
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int64_t r = blockIdx.x;
+  const float* xr = x + (int64_t)src_row[r] * cols;
+  float s = 1.f;
+  if (F16) {
+    float m = 0.f;
+    for (int i = threadIdx.x * 4; i < cols; i += blockDim.x * 4) {
+      const float4 v = *(const float4*)(xr + i);
+      m = fmaxf(fmaxf(m, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    }
+#pragma unroll
+    for (int o2 = 16; o2; o2 >>= 1) m = fmaxf(m, __shfl_xor_sync(~0u, m, o2));
+    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = wmax[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, wmax[w]);
+    const int be = (int)((__float_as_uint(m) >> 23) & 0xff);
+    float sinv = 1.f;
+    if (be != 0 && be != 255) {
+      int e = 14 - (be - 127);
+      e = e > 126 ? 126 : (e < -126 ? -126 : e);
+      s = __uint_as_float((uint32_t)(e + 127) << 23);
+      sinv = __uint_as_float((uint32_t)(127 - e) << 23);
+    }
+    if (threadIdx.x == 0) inv_scale[r] = sinv;
+  }
+  for (int i = threadIdx.x * 4; i < cols; i += blockDim.x * 4) {
+    const float4 v = *(const float4*)(xr + i);
+    uint2 packed;
+    if (F16) {
+      const __half2 a = __floats2half2_rn(v.x * s, v.y * s), b = __floats2half2_rn(v.z * s, v.w * s);
+      packed = make_uint2(*(const uint32_t*)&a, *(const uint32_t*)&b);
+    } else {
+      const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+      packed = make_uint2(*(const uint32_t*)&a, *(const uint32_t*)&b);
+    }
+    *(uint2*)((uint16_t*)o + r * cols + i) = packed;
+  }
+}
+
 // Largest |weight| any block of the matrix can decode to, from the block headers alone, as the bit
 // pattern of a non-negative float (so that an integer max orders it); NaN or infinite headers give
 // 0x7f800000 or more.
@@ -917,6 +969,15 @@ cudaError_t tc_convert_activations(const float* x, int64_t n_rows, int cols, boo
     if (blocks < 1) blocks = 1;
     to_bf16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, (__nv_bfloat16*)out16, n);
   }
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t tc_convert_expert_rows(const float* x, const int* src_row, int64_t n_rows, int cols, bool f16,
+                                   void* out16, float* xscale, cudaStream_t stream, uint64_t* launches) {
+  if (n_rows <= 0) return cudaSuccess;
+  if (f16) expert_rows_16bit_kernel<true><<<(unsigned)n_rows, 256, 0, stream>>>(x, src_row, out16, xscale, cols);
+  else expert_rows_16bit_kernel<false><<<(unsigned)n_rows, 256, 0, stream>>>(x, src_row, out16, xscale, cols);
   if (launches) ++*launches;
   return cudaGetLastError();
 }

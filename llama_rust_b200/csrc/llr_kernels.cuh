@@ -122,6 +122,10 @@ struct GemmGroupSpec {
 size_t gemm_tc_group_desc_bytes(int n_groups);
 cudaError_t tc_convert_activations(const float* x, int64_t n_rows, int cols, bool f16, void* out16, float* xscale,
                                    cudaStream_t stream, uint64_t* launches);
+// Routed-expert layer: 16-bit operand row r from row src_row[r] of x (cols a multiple of 4, rows
+// 16-byte aligned).
+cudaError_t tc_convert_expert_rows(const float* x, const int* src_row, int64_t n_rows, int cols, bool f16,
+                                   void* out16, float* xscale, cudaStream_t stream, uint64_t* launches);
 cudaError_t launch_gemm_tc_grouped(const GemmGroupSpec* specs, int n_groups, bool f16, void* desc_dev,
                                    cudaStream_t stream, int* err_flag, uint64_t* launches);
 size_t gemm_tc_scratch_bytes(const MatView& m, int64_t tokens);
