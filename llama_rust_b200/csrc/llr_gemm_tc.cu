@@ -82,7 +82,7 @@ template <int DT, int BN> struct GLay {
   // dequant warps; two threads on alternating steps double that.  At BN = 256 tensor memory has no
   // room for a second accumulator and the step is bound elsewhere.
   static constexpr int NMMA = BN > 128 ? 1 : 2;
-  static constexpr int NA = (TMEM_COLS - NMMA * BN) / A_COLS;
+  static constexpr int NA = ((TMEM_COLS - NMMA * BN) / A_COLS) & ~1;  // even: see the dequant loop
   static constexpr int B_STAGE = BN * 128;
   static constexpr int NB = (128 * 1024) / B_STAGE;
   static constexpr int P_STAGE = BM * Pk<DT>::PITCH;
@@ -929,7 +929,9 @@ template <int DT>
 cudaError_t launch_grouped_dt(const GemmGroupSpec* specs, int n, bool f16, void* desc_dev, cudaStream_t stream, int* err) {
   int max_tokens = 0;
   for (int i = 0; i < n; ++i) max_tokens = specs[i].tokens > max_tokens ? specs[i].tokens : max_tokens;
-  const int bn = max_tokens > 128 ? 256 : max_tokens > 64 ? 128 : 64;
+  // the narrowest tile that holds the busiest product's rows: the MMA and activation-tile work of a
+  // tile grows with its width, padding included (512 tokens over 8 experts, top-2: 113-144 rows each)
+  const int bn = max_tokens > 192 ? 256 : max_tokens > 160 ? 192 : max_tokens > 128 ? 160 : max_tokens > 64 ? 128 : 64;
   std::vector<GemmGroup> host((size_t)n);
   int tiles = 0;
   for (int i = 0; i < n; ++i) {
@@ -950,6 +952,8 @@ cudaError_t launch_grouped_dt(const GemmGroupSpec* specs, int n, bool f16, void*
   const GemmGroup* d = (const GemmGroup*)desc_dev;
 #define LLR_GROUPED(B) (f16 ? launch_grouped_bn<DT, B, true>(d, n, tiles, stream, err) : launch_grouped_bn<DT, B, false>(d, n, tiles, stream, err))
   if (bn == 256) return LLR_GROUPED(256);
+  if (bn == 192) return LLR_GROUPED(192);
+  if (bn == 160) return LLR_GROUPED(160);
   if (bn == 128) return LLR_GROUPED(128);
   return LLR_GROUPED(64);
 #undef LLR_GROUPED
