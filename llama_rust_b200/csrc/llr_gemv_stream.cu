@@ -361,7 +361,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
                 unsigned long long v, u = want_peers;
                 asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cp) : "memory");
                 if (PEERS) asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(u) : "l"(pp) : "memory");
-                if (v >= want && u >= want_peers) break;
+                if (v >= want && (!PEERS || u >= want_peers)) break;
                 if (++polls > POLL_LIMIT) { report_error(err, 2); break; }
                 __nanosleep(polls < 8 ? 64 : 256);  // hundreds of CTAs poll one word: keep the L2 bank free for the adds
               }
