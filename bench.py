@@ -62,7 +62,7 @@ def row_bytes(dt, cols):
 
 
 def algorithmic_bytes(dt, rows, cols, m):
-    """packed W once + 4*M*(cols+rows)."""
+    """Algorithmic bytes of one product: the packed weights once + 4*M*(cols+rows) of activations and results."""
     return rows * row_bytes(dt, cols) + 4 * m * (cols + rows)
 
 

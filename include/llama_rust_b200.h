@@ -89,7 +89,8 @@ int llr_exec_counters(const llr_exec* exec, llr_counters* out);
  * it cannot take), 3 = the integer tensor-core kernel for any number of
  * activation rows (f32-faithful), 4 = the bf16 tcgen05 GEMM whenever it can take
  * the call.  Automatic choice: up to 63 activation rows as 3, from 64 rows the
- * bf16 tcgen05 GEMM for Q4_K/Q8_0/Q5_0/Q5_1 (looser tolerance).
+ * bf16 tcgen05 GEMM for Q4_K/Q8_0/Q5_0/Q5_1 (16-bit operands: relative L2 error of a
+ * result up to 4e-3 against the f32 row kernels).
  * Also read once from the environment variable LLR_GEMV_PATH
  * (generic|staged|mma|tc) when the executor is created. */
 int llr_exec_set_path(llr_exec* exec, int path);

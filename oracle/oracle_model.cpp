@@ -91,7 +91,7 @@ int orc_moe_ffn(int n_expert, int n_used, int norm_w, int router_kind, const uin
 
 // tensors[layer*7 + {0 q,1 k,2 v,3 o,4 gate,5 up,6 down}], tensors[n_layer*7] = output;
 // token_embd separately.  kinds[] parallel.  norms are all-ones F32 (attn_norm, ffn_norm,
-// output_norm), stated in DESIGN.md.
+// output_norm): the synthetic model of the greedy-identity tests has no trained norms.
 static int walk_matmul(const orc_llama_cfg* c, orc_matmul_cb cb, void* user, const uint8_t* const* tensors,
                        const int* kinds, int id, int64_t rows, int64_t cols, int64_t n, const float* x,
                        float* y, int threads) {
