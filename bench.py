@@ -170,6 +170,152 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------- GPU arm
+def decode_step_ops(mat_of, addr_of, h0, ones, M):
+    """The 225 products of one decode step as a data-flow chain (llr_program_op), in the walk's order
+    (decode.rs:2737-3097): rmsnorm(h) -> q|k|v; o (+ h); rmsnorm -> gate|up; silu(gate)*up -> down (+ h').
+    The attention itself is not a matrix product and not part of this sweep: attn_output reads the q
+    result in its place.  mat_of(name) -> resident matrix (this rank's rows), addr_of(name) -> device
+    address of that product's full-width result."""
+    from llama_rust_b200 import XOP_NONE, XOP_RMSNORM, XOP_SWIGLU
+    ops, phase = [], 0
+    h = h0
+    for layer in range(N_LAYER):
+        n = lambda t: f"blk.{layer}.{t}.weight"  # noqa: E731
+        for t in ("attn_q", "attn_k", "attn_v"):
+            ops.append(dict(name=n(t), x=h, x2=ones, x_op=XOP_RMSNORM, eps=1e-5, phase=phase))
+        phase += 1
+        ops.append(dict(name=n("attn_output"), x=addr_of(n("attn_q")), resid=h, x_op=XOP_NONE, phase=phase))
+        phase += 1
+        h1 = addr_of(n("attn_output"))
+        for t in ("ffn_gate", "ffn_up"):
+            ops.append(dict(name=n(t), x=h1, x2=ones, x_op=XOP_RMSNORM, eps=1e-5, phase=phase))
+        phase += 1
+        ops.append(dict(name=n("ffn_down"), x=addr_of(n("ffn_gate")), x2=addr_of(n("ffn_up")), resid=h1,
+                        x_op=XOP_SWIGLU, phase=phase))
+        phase += 1
+        h = addr_of(n("ffn_down"))
+    ops.append(dict(name="output.weight", x=h, x2=ones, x_op=XOP_RMSNORM, eps=1e-5, phase=phase))
+    for o in ops:
+        o["matrix"] = mat_of(o["name"])
+        o["tokens"] = M
+    return ops
+
+
+def timed(stream, fn, reps):
+    """Average device time of fn() in ms over reps calls on `stream` (CUDA events on that stream)."""
+    import torch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(reps):
+        fn()
+    e1.record(stream)
+    e1.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def config_legs(ex, stream, peak_hbm, peaks):
+    """Driver-visible numbers for BASELINE configs 1, 4 and 5 on one GPU (device time, CUDA events):
+    config 1 the single Q8_0 product, config 4 the chunk GEMM (tensor-core path, 16-bit operands) for
+    four formats at three batch sizes, config 5 the routed-expert layer at 64 and 512 tokens."""
+    import torch
+    from llama_rust_b200 import DTYPES
+    out = {}
+    sptr = stream.cuda_stream
+    Q8_0, Q5_0, Q5_1 = DTYPES["Q8_0"], DTYPES["Q5_0"], DTYPES["Q5_1"]
+    rb = lambda dt, cols: {Q4_K: 144 * (cols // 256), Q6_K: 210 * (cols // 256), Q8_0: 34 * (cols // 32),  # noqa: E731
+                           Q5_0: 22 * (cols // 32), Q5_1: 24 * (cols // 32)}[dt]
+    # config 1: 4096 x 4096 Q8_0, one activation row, 8 distinct matrices round-robin (142 MB > L2)
+    mats = [ex.synth(Q8_0, 4096, 4096, 500 + i) for i in range(8)]
+    x = torch.randn(4096, device="cuda")
+    y = torch.empty(4096, device="cuda")
+    it = [0]
+
+    def one():
+        ex.matmul_device(mats[it[0] % 8], 1, x.data_ptr(), y.data_ptr(), sptr)
+        it[0] += 1
+    timed(stream, one, 16)
+    ms = timed(stream, one, 64)
+    nbytes = 4096 * rb(Q8_0, 4096) + 4 * 2 * 4096
+    out["config1_q8_0_4096x4096_m1"] = {"us_per_product": ms * 1e3, "GB_per_s": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak_hbm,
+                                       "algorithmic_bytes": nbytes, "launch": "one PDL launch per product, 8 distinct matrices"}
+    for m in mats:
+        m.free()
+    # config 4
+    burst, sustained = peaks.get("bf16_tflops", 1619.1), peaks.get("bf16_tflops_sustained", 1354.7)
+    c4 = {}
+    for name, dt, rows, cols in (("q4_k_14336x4096", Q4_K, 14336, 4096), ("q8_0_4096x14336", Q8_0, 4096, 14336),
+                                 ("q5_0_4096x4096", Q5_0, 4096, 4096), ("q5_1_4096x4096", Q5_1, 4096, 4096)):
+        mats = [ex.synth(dt, rows, cols, 600 + i) for i in range(6)]
+        for M in (64, 256, 1024):
+            x = torch.randn(M, cols, device="cuda")
+            y = torch.empty(M, rows, device="cuda")
+            it = [0]
+
+            def one():
+                ex.matmul_device(mats[it[0] % 6], M, x.data_ptr(), y.data_ptr(), sptr)
+                it[0] += 1
+            timed(stream, one, 6)
+            ms = timed(stream, one, 30)
+            flops = 2.0 * M * rows * cols
+            nbytes = rows * rb(dt, cols) + 4 * M * (rows + cols)
+            floor_us = max(nbytes / (peak_hbm * 1e9), flops / (sustained * 1e12)) * 1e6
+            c4[f"{name}_m{M}"] = {"us_per_call": ms * 1e3, "TFLOP_per_s": flops / ms / 1e9, "frac_of_burst": flops / ms / 1e9 / burst,
+                                  "frac_of_sustained": flops / ms / 1e9 / sustained, "roofline_us": floor_us,
+                                  "frac_of_roofline": floor_us / (ms * 1e3)}
+        for m in mats:
+            m.free()
+    out["config4_chunk_gemm"] = c4
+    # config 5
+    out["config5_moe_layer"] = moe_leg(ex, None, 0, 1, peak_hbm, sustained)
+    return out
+
+
+def moe_leg(ex, group, rank, world, peak_hbm, sustained):
+    """Routed-expert layer of BASELINE config 5 (8 experts, top-2, 4096 / 14336, Q4_K experts, F32 router) through
+    the host-buffer entry point with pinned buffers: wall ms per layer call.  world > 1: experts striped e % world,
+    partial outputs summed over the ranks; the result is compared bit for bit with the single-device layer."""
+    import torch
+    from llama_rust_b200 import DTYPES
+    n_exp, d_model, d_ff = 8, 4096, 14336
+    gate = [ex.synth(Q4_K, d_ff, d_model, 100 + e) for e in range(n_exp)]
+    up = [ex.synth(Q4_K, d_ff, d_model, 200 + e) for e in range(n_exp)]
+    down = [ex.synth(Q4_K, d_model, d_ff, 300 + e) for e in range(n_exp)]
+    rng = np.random.default_rng(1)
+    w = (rng.standard_normal((n_exp, d_model)) * 0.05).astype(np.float32)
+    router = ex.upload(DTYPES["F32"], n_exp, d_model, w.view(np.uint8).reshape(-1))
+    res = {}
+    layer = None
+    if world > 1:
+        from llama_rust_b200.sharding import StripedExperts
+        layer = StripedExperts(ex, router, gate, up, down, 2, True, group=group)
+    for tokens in (64, 512):
+        x = torch.from_numpy(np.random.default_rng(tokens).standard_normal((tokens, d_model)).astype(np.float32)).pin_memory().numpy()
+        out = torch.empty(tokens, d_model).pin_memory().numpy()
+        call = (lambda: layer(x, device=f"cuda:{torch.cuda.current_device()}")) if layer else \
+               (lambda: ex.moe_ffn(router, gate, up, down, 2, True, x, out))
+        for _ in range(2):
+            call()
+        n = 5
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            r = call()
+        ms = (time.perf_counter() - t0) / n * 1e3
+        flops = 2.0 * tokens * 2 * 3 * d_model * d_ff
+        nbytes = n_exp * 3 * d_ff * 144 * (d_model // 256)
+        floor_ms = max(nbytes / world / (peak_hbm * 1e9), flops / world / (sustained * 1e12)) * 1e3
+        rec = {"ms_per_layer_call": ms, "TFLOP_per_s": flops / ms / 1e9, "roofline_ms": floor_ms, "frac_of_roofline": floor_ms / ms}
+        if world > 1:
+            full = ex.moe_ffn(router, gate, up, down, 2, True, x)[0]
+            rec["bit_identical_to_single_device"] = bool(np.array_equal(np.asarray(r[0]), full))
+        res[f"tokens_{tokens}"] = rec
+    for m in gate + up + down + [router]:
+        m.free()
+    return res
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -184,68 +330,77 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     M = args.m
-    torch.manual_seed(1234)  # activations are replicated: the same values on every rank
+    torch.manual_seed(1234)  # the step's input is replicated: the same values on every rank
     ex = Executor(local)
     stream = torch.cuda.Stream(device=local)
     sptr = stream.cuda_stream
+    peak, peak_kind = load_peaks()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except Exception:
+        peaks = {}
 
-    # every matrix sharded by output rows (all row counts divide by 8); activations replicated
-    mats = []
+    # every matrix sharded by output rows (all row counts divide by 8)
     specs_all = model_matrices()
-    # all input vectors in one device buffer and all (local) results in another, so that the end-to-end
-    # legs move them with one copy each way
-    xbig = torch.randn(sum(M * cols for _, _, _, cols in specs_all), device="cuda", dtype=torch.float32)
-    ybig = torch.empty(sum(M * (rows // world) for _, _, rows, _ in specs_all), device="cuda", dtype=torch.float32)
-    xo = yo = 0
+    mats = {}
     for name, dt, rows, cols in specs_all:
         assert rows % world == 0
-        rs = rows // world
         # each rank generates its own shard from its own stream: rank r's rows are blocks of stream (name, r)
-        m = ex.synth(dt, rs, cols, synth.tensor_seed(rank, name))
-        x = xbig[xo:xo + M * cols].view(M, cols)
-        y = ybig[yo:yo + M * rs].view(M, rs)
-        xo += M * cols
-        yo += M * rs
-        yfull = torch.empty(world, M, rs, device="cuda", dtype=torch.float32) if world > 1 else None
-        mats.append((name, dt, rows, cols, rs, m, x, y, yfull))
-    total_bytes = sum(algorithmic_bytes(dt, rows, cols, M) for _, dt, rows, cols, *_ in mats)
+        mats[name] = ex.synth(dt, rows // world, cols, synth.tensor_seed(rank, name))
+    shape_of = {name: (dt, rows, cols) for name, dt, rows, cols in specs_all}
+    total_bytes = sum(algorithmic_bytes(dt, rows, cols, M) for _, dt, rows, cols in specs_all)
+    h0 = torch.randn(M, D_MODEL, device="cuda", dtype=torch.float32)
+    ones = torch.ones(D_MODEL, device="cuda", dtype=torch.float32)
+    # independent inputs for the one-launch-per-product legs
+    xin = {cols: torch.randn(M, cols, device="cuda") for cols in (D_MODEL, D_FF)}
     torch.cuda.synchronize()
 
-    # Single GPU: the whole sweep is one program (one persistent launch).  Phases follow the
-    # model's dependency structure: {q,k,v} -> {o} -> {gate,up} -> {down} per layer, then the
-    # lm_head; a phase starts only when the previous one is completely written.
+    prog = sharded = ybig = chain = None
+    offs = {}
     PHASE = {"attn_q": 0, "attn_k": 0, "attn_v": 0, "attn_output": 1, "ffn_gate": 2, "ffn_up": 2, "ffn_down": 3}
-    prog = None
-    sharded = None
-    if world > 1 and args.mode == "program":
-        # Row-sharded program: one launch per rank and step; the reducer warps store their result
-        # slices into every rank's full-width result buffers and the phase counters count the CTAs
-        # of all ranks, so there is no collective call inside a step.
-        from llama_rust_b200.sharding import ShardedDecodeProgram
-        specs = []
-        for i, (name, dt, rows, cols, rs, m, x, y, yfull) in enumerate(mats):
-            parts = name.split(".")
-            phase = 4 * int(parts[1]) + PHASE[parts[2]] if parts[0] == "blk" else 4 * N_LAYER
-            specs.append((m, x.data_ptr(), rows, phase))
-        sharded = ShardedDecodeProgram(ex, specs, M)
-        prog = sharded.program
-    if world == 1 and args.mode == "program":
-        entries = []
-        for i, (name, dt, rows, cols, rs, m, x, y, yfull) in enumerate(mats):
-            parts = name.split(".")
-            phase = 4 * int(parts[1]) + PHASE[parts[2]] if parts[0] == "blk" else 4 * N_LAYER
-            entries.append((m, x.data_ptr(), y.data_ptr(), M, phase))
-        prog = ex.program(entries)
+
+    def phase_of(name):
+        parts = name.split(".")
+        return 4 * int(parts[1]) + PHASE[parts[2]] if parts[0] == "blk" else 4 * N_LAYER
+    if args.mode == "program":
+        # One persistent launch per rank and step.  Phases follow the model's dependency structure: {q,k,v} -> {o} ->
+        # {gate,up} -> {down} per layer, then the lm_head; a phase starts only when the previous one is completely
+        # written (strict phases: one counter per phase).
+        if world == 1:
+            cur = 0
+            for name, dt, rows, cols in specs_all:
+                offs[name] = cur
+                cur += M * rows
+            ybig = torch.empty(cur, device="cuda", dtype=torch.float32)
+            prog = ex.program([(mats[n], xin[cols].data_ptr(), ybig.data_ptr() + 4 * offs[n], M, phase_of(n))
+                               for n, dt, rows, cols in specs_all])
+            # the same step as a data-flow chain: results travel from product to product inside the launch, RMSNorm /
+            # SwiGLU / residual adds applied by the readers and writers (reported beside the headline, see `fused_chain`)
+            ops = decode_step_ops(lambda n: mats[n], lambda n: ybig.data_ptr() + 4 * offs[n], h0.data_ptr(), ones.data_ptr(), M)
+            for o in ops:
+                o["y"] = ybig.data_ptr() + 4 * offs[o["name"]]
+            chain = ex.program_ops(ops)
+        else:
+            from llama_rust_b200.sharding import ShardedDecodeProgram, arena_layout
+            order = [n for n, *_ in specs_all]
+            aoffs, _ = arena_layout([shape_of[n][1] for n in order], M)
+            offs = dict(zip(order, aoffs))
+            sharded = ShardedDecodeProgram(ex, [(mats[n], xin[cols].data_ptr(), rows, phase_of(n)) for n, dt, rows, cols in specs_all], M)
+            prog = sharded.program
+        info = prog.info()
 
     def step():
         if prog is not None:
             prog.run(sptr)
             return
-        for i, (name, dt, rows, cols, rs, m, x, y, yfull) in enumerate(mats):
-            ex.matmul_device(m, M, x.data_ptr(), y.data_ptr(), sptr)
-            if world > 1:  # --mode calls: the library baseline, a NCCL all-gather after every product
+        for name, dt, rows, cols in specs_all:  # --mode calls: one launch per product, independent inputs
+            ex.matmul_device(mats[name], M, xin[cols].data_ptr(), ycall.data_ptr(), sptr)
+            if world > 1:  # the library baseline: a NCCL all-gather after every product
                 with torch.cuda.stream(stream):
-                    dist.all_gather_into_tensor(yfull, y)
+                    dist.all_gather_into_tensor(ygather[:world * M * (rows // world)], ycall[:M * (rows // world)])
+    ycall = torch.empty(M * VOCAB, device="cuda")
+    ygather = torch.empty(M * VOCAB, device="cuda") if world > 1 else None
 
     def barrier():
         if world > 1:
@@ -258,6 +413,19 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+    ex.synchronize()
+
+    # ---- untimed check of the sharded program: every rank compares the first layers' full-width results in its
+    # arena, bit for bit, with the same products run unsharded on its own GPU
+    sharded_check = None
+    if sharded is not None:
+        sharded_check = check_sharded(ex, sharded, offs, shape_of, xin, phase_of, M, world, rank, sptr, stream)
+        flag = torch.tensor([1 if sharded_check["bit_identical"] else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        sharded_check["bit_identical"] = bool(flag.item())
+        sharded_check["ranks"] = world
+        barrier()
+
     launches0 = ex.counters()["launches"]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -268,32 +436,30 @@ def run_ours(args):
     barrier()
     ms_total = e0.elapsed_time(e1)
     launches = ex.counters()["launches"] - launches0
+    per_rank_ms = [ms_total / args.steps]
     if world > 1:
         t = torch.tensor([ms_total], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+        allt = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(allt, t)
+        per_rank_ms = [float(v.item()) / args.steps for v in allt]
+        ms_total = max(float(v.item()) for v in allt)
         launches *= world
     ms_step = ms_total / args.steps
     value = total_bytes / (ms_step * 1e-3) / 1e9
 
-    # dominant kernel: the Q4_K decode GEMV (57% of the sweep's bytes).  Its launches alone,
-    # back to back on the same stream in the launch mode the sweep uses (programmatic
-    # dependent launch), every matrix distinct (2.8 GB per pass, no L2 reuse): CUDA events
-    # around each pass, average duration per launch.
-    dom = [t for t in mats if t[1] == Q4_K]
+    # Q4_K decode products one per launch (57% of the sweep's bytes), back to back on the same stream with
+    # programmatic dependent launch, every matrix distinct (2.8 GB per pass, no L2 reuse)
+    dom = [(n, dt, rows, cols) for n, dt, rows, cols in specs_all if dt == Q4_K]
     reps = max(3, min(args.steps, 20))
-    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def dom_pass():
+        for n, dt, rows, cols in dom:
+            ex.matmul_device(mats[n], M, xin[cols].data_ptr(), ycall.data_ptr(), sptr)
     barrier()
-    d0.record(stream)
-    for _ in range(reps):
-        for (name, dt, rows, cols, rs, m, x, y, yfull) in dom:
-            ex.matmul_device(m, M, x.data_ptr(), y.data_ptr(), sptr)
-    d1.record(stream)
+    dom_ms = timed(stream, dom_pass, reps) * reps
     torch.cuda.synchronize()
-    dom_ms = d0.elapsed_time(d1)
-    dom_bytes = reps * sum(rs * row_bytes(dt, cols) + 4 * M * (cols + rs) for (_, dt, _, cols, rs, *_r) in dom)
+    dom_bytes = reps * sum((rows // world) * row_bytes(dt, cols) + 4 * M * (cols + rows // world) for _, dt, rows, cols in dom)
     clock_rec = clocks.stop() if rank == 0 else None
-    peak, peak_kind = load_peaks()
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     single = {"kernel": "gemv_stream_kernel<M, Q4_K> (one product per launch, programmatic dependent launch)",
               "achieved": achieved, "frac": achieved / peak, "launches_timed": reps * len(dom),
@@ -317,17 +483,17 @@ def run_ours(args):
                     "avg_bytes_per_launch": single["avg_bytes_per_launch"], "frac_of_8tbs_nominal": achieved / 8000.0}
 
     # end to end through the reference-facing call: host buffers, copies inside the timed region
-    e2e = None
+    e2e_calls = None
     if world == 1:
-        hx = [torch.randn(M, cols).pin_memory() for _, _, _, cols, *_ in mats]
-        hy = [torch.empty(M, rows).pin_memory() for _, _, rows, *_ in mats]
-        import ctypes as C
+        hx = {cols: torch.randn(M, cols).pin_memory() for cols in (D_MODEL, D_FF)}
+        hy = torch.empty(M, VOCAB).pin_memory()
         from llama_rust_b200.executor import lib
         L, h = lib(), ex._h
 
         def e2e_step():
-            for (name, dt, rows, cols, rs, m, *_), a, b in zip(mats, hx, hy):
-                rc = L.llr_gemm_resident(h, m._h, M, a.data_ptr(), a.numel(), b.data_ptr(), b.numel())
+            for name, dt, rows, cols in specs_all:
+                a = hx[cols]
+                rc = L.llr_gemm_resident(h, mats[name]._h, M, a.data_ptr(), a.numel(), hy.data_ptr(), M * rows)
                 if rc:
                     raise RuntimeError(L.llr_exec_last_error(h).decode())
         for _ in range(2):
@@ -339,30 +505,29 @@ def run_ours(args):
             e2e_step()
         torch.cuda.synchronize()
         dt_s = (time.perf_counter() - t0) / n_e2e
-        e2e = {"value": total_bytes / dt_s / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": sum(4 * M * cols for _, _, _, cols, *_ in mats),
-               "d2h_bytes_per_step": sum(4 * M * rows for _, _, rows, *_ in mats),
-               "ms_per_step": dt_s * 1e3, "tok_s": M / dt_s,
-               "api": "llr_gemm_resident with pinned host buffers, 225 synchronous calls per step: H2D copy of x, kernel, the kernel stores y into the pinned host buffer and raises a completion word the call polls"}
+        e2e_calls = {"value": total_bytes / dt_s / 1e9, "unit": "GB/s",
+                     "h2d_bytes_per_step": sum(4 * M * cols for _, _, _, cols in specs_all),
+                     "d2h_bytes_per_step": sum(4 * M * rows for _, _, rows, _ in specs_all),
+                     "ms_per_step": dt_s * 1e3, "tok_s": M / dt_s,
+                     "api": "llr_gemm_resident with pinned host buffers, 225 synchronous calls per step: H2D copy of x, kernel, the kernel stores y into the pinned host buffer and raises a completion word the call polls"}
 
     e2e_program = None
     if prog is not None:
-        # End to end through the program API (llr_program_run): per step all input vectors go host -> device in one
-        # copy, one program launch per rank, all results come device -> host in one copy, synchronize.
+        # End to end through the program API (llr_program_run): per rank and step the step's input (the hidden state,
+        # pinned host memory) goes host -> device, one program launch, the step's result (the logits) comes device ->
+        # host, synchronize.  Everything between the 225 products stays on the device.
         import ctypes as C
         rt = C.CDLL("libcudart.so.12")
         rt.cudaMemcpyAsync.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]
-        hxb = torch.randn(xbig.numel()).pin_memory()
-        if sharded is not None:
-            y_dev, y_floats = sharded.arena + sharded.offsets[0], (sharded.arena_bytes - sharded.offsets[0]) // 4
-        else:
-            y_dev, y_floats = ybig.data_ptr(), ybig.numel()
-        hyb = torch.empty(y_floats).pin_memory()
+        hxb = torch.randn(M, D_MODEL).pin_memory()
+        h0 = xin[D_MODEL]  # the hidden state of the step: what attn_q/k/v, attn_output, ffn_gate/up and the lm_head read
+        logits_dev = (sharded.arena + offs["output.weight"]) if sharded is not None else ybig.data_ptr() + 4 * offs["output.weight"]
+        hyb = torch.empty(M, VOCAB).pin_memory()
 
         def e2e_prog_step():
-            assert rt.cudaMemcpyAsync(xbig.data_ptr(), hxb.data_ptr(), 4 * hxb.numel(), 1, sptr) == 0
+            assert rt.cudaMemcpyAsync(h0.data_ptr(), hxb.data_ptr(), 4 * hxb.numel(), 1, sptr) == 0
             prog.run(sptr)
-            assert rt.cudaMemcpyAsync(hyb.data_ptr(), y_dev, 4 * y_floats, 2, sptr) == 0
+            assert rt.cudaMemcpyAsync(hyb.data_ptr(), logits_dev, 4 * hyb.numel(), 2, sptr) == 0
             stream.synchronize()
         for _ in range(2):
             e2e_prog_step()
@@ -378,12 +543,35 @@ def run_ours(args):
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             dt_s = float(tt.item())
         e2e_program = {"value": total_bytes / dt_s / 1e9, "unit": "GB/s",
-                       "h2d_bytes_per_step": world * 4 * hxb.numel(), "d2h_bytes_per_step": world * 4 * y_floats,
+                       "h2d_bytes_per_step": world * 4 * hxb.numel(), "d2h_bytes_per_step": world * 4 * hyb.numel(),
                        "ms_per_step": dt_s * 1e3, "tok_s": M / dt_s,
-                       "api": "per rank and step: all 225 input vectors H2D from pinned memory (one copy), llr_program_run, "
-                              "all results D2H (one copy), synchronize"}
-        if world > 1:
-            e2e = e2e_program  # one call per product would need a collective per product; the program is the N-GPU API
+                       "api": "per rank and step: the step's input (hidden state) H2D from pinned memory, llr_program_run (225 products), "
+                              "the step's result (logits) D2H, synchronize; intermediate results stay on the device"}
+    # `e2e`: the reference-facing per-product call on one GPU; a row-sharded product per call would need a collective
+    # per product, so on several GPUs it is the program API.  `e2e_program` is the series that is comparable over N.
+    e2e = e2e_calls if world == 1 else e2e_program
+    if e2e is not None:
+        e2e = dict(e2e, kind="per-product calls (reference call contract)" if world == 1 else "program API")
+
+    fused_chain = None
+    if chain is not None:
+        for _ in range(3):
+            chain.run(sptr)
+        cms = timed(stream, lambda: chain.run(sptr), max(3, min(args.steps, 20)))
+        ex.synchronize()
+        ci = chain.info()
+        fused_chain = {"ms_per_step": cms, "GB_per_s": total_bytes / cms / 1e6, "frac_of_hbm_peak": total_bytes / cms / 1e6 / peak,
+                       "phases": ci["phases"], "counter_phases": ci["counter_phases"], "ctas": ci["ctas"],
+                       "what": "the same 225 products as a data-flow program (llr_program_create_ops): each product reads earlier results as tagged "
+                               "pairs, RMSNorm / SwiGLU / residual adds run inside the launch, attn_output reads the q result in place of the attention output"}
+        chain.free()
+    configs = None
+    if not args.no_configs and args.mode == "program":
+        if world == 1:
+            configs = config_legs(ex, stream, peak, peaks)
+        else:
+            sustained = peaks.get("bf16_tflops_sustained", 1354.7)
+            configs = {"config5_moe_layer_striped": moe_leg(ex, None, rank, world, peak, sustained)}
 
     out = None
     if rank == 0:
@@ -392,12 +580,17 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "m": M, "launch": ("one persistent program launch per rank and step, 129 dependent phases" if prog is not None else "one PDL launch per matmul"), "l2": "inputs larger than L2: every step streams 4.9 GB of distinct weights",
+            "config": {"workload": WORKLOAD, "m": M,
+                       "launch": (f"one persistent program launch per rank and step, {info['phases']} dependent phases "
+                                  f"(a phase starts when the previous one is completely written), {info['ctas']} CTAs"
+                                  if prog is not None else "one PDL launch per matmul"),
+                       "l2": "inputs larger than L2: every step streams 4.9 GB of distinct weights",
                        "parallelism": ("single GPU" if world == 1 else
-                                       f"rows/{world} per GPU; result slices exchanged inside the kernel (peer stores + phase counters over all ranks)"
+                                       f"rows/{world} per GPU; result slices exchanged inside the kernel (peer stores over NVLink + phase counters over all ranks)"
                                        if sharded is not None else f"rows/{world} per GPU + NCCL all-gather of output slices after every product")},
             "tok_s": M / (ms_step * 1e-3), "frac_of_measured_hbm": value / peak, "frac_of_8tbs_nominal": value / 8000.0,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "e2e_program": e2e_program, "gpu_launches": int(launches),
+            "per_rank_ms_per_step": per_rank_ms, "sharded_check": sharded_check, "fused_chain": fused_chain, "configs": configs,
             "clocks": clock_rec,
         }
         print(json.dumps(out))
@@ -406,7 +599,59 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if sharded_check is not None and not sharded_check["bit_identical"]:
+        raise SystemExit("sharded program results differ from the unsharded program")
     return out
+
+
+def check_sharded(ex, sharded, offs, shape_of, xin, phase_of, M, world, rank, sptr, stream, layers=2):
+    """Runs the first `layers` layers unsharded on this GPU (full matrices rebuilt from every rank's shard stream)
+    with the same input and compares their results, bit for bit, with what the sharded program left in this
+    rank's arena (this rank's rows and the rows the peers stored)."""
+    import ctypes as C
+
+    import torch
+    import torch.distributed as dist
+    from llama_rust_b200 import synth
+    rt = C.CDLL("libcudart.so.12")
+    rt.cudaMemcpy.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+    names = [f"blk.{layer}.{t}.weight" for layer in range(layers) for t, *_ in LAYER]
+    full = {}
+    for n in names:
+        dt, rows, cols = shape_of[n]
+        parts = []
+        for g in range(world):
+            m = ex.synth(dt, rows // world, cols, synth.tensor_seed(g, n))
+            parts.append(ex.download(m))
+            m.free()
+        full[n] = ex.upload(dt, rows, cols, np.concatenate(parts))
+    cur, roffs = 0, {}
+    for n in names:
+        roffs[n] = cur
+        cur += M * shape_of[n][1]
+    yref = torch.full((cur,), float("nan"), device="cuda")
+    ref = ex.program([(full[n], xin[shape_of[n][2]].data_ptr(), yref.data_ptr() + 4 * roffs[n], M, phase_of(n)) for n in names])
+    dist.barrier()
+    sharded.run(sptr)
+    ref.run(sptr)
+    ex.synchronize()
+    stream.synchronize()
+    dist.barrier()  # the peers' stores into this arena are complete as well
+    ok, n_bad = True, 0
+    host = yref.cpu().numpy()
+    for n in names:
+        rows = shape_of[n][1]
+        got = np.empty(M * rows, np.float32)
+        assert rt.cudaMemcpy(got.ctypes.data, sharded.arena + offs[n], 4 * M * rows, 2) == 0
+        want = host[roffs[n]:roffs[n] + M * rows]
+        same = np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        ok = ok and same
+        n_bad += 0 if same else 1
+    ref.free()
+    for m in full.values():
+        m.free()
+    return {"bit_identical": ok, "entries": len(names), "entries_differing_on_rank0": n_bad, "layers": layers,
+            "how": "first layers of the sharded program vs the same products unsharded on each rank's own GPU, all rows, uint32 compare"}
 
 
 def main():
@@ -417,6 +662,7 @@ def main():
     ap.add_argument("--m", type=int, default=1, help="activation rows per matmul (1..8)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-configs", action="store_true", help="skip the legs for BASELINE configs 1, 4 and 5")
     ap.add_argument("--mode", default="program", choices=["program", "calls"],
                     help="program: the sweep as one persistent launch; calls: one launch per matmul")
     args = ap.parse_args()

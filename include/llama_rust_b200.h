@@ -160,14 +160,19 @@ int llr_matmul_device(llr_exec* exec, const llr_matrix* matrix, size_t tokens, c
  * synchronization of cudaMalloc/cudaFree is not acceptable; hosts that hand this
  * library a fixed memory budget up front.  Same tensor-core GEMM as the
  * automatic path takes from 64 activation rows on (Q4_K, Q8_0, Q5_0, Q5_1;
- * cols % 64 == 0; tokens >= 16; bf16 operands, f32 accumulation), but the bf16
- * copy of the activations is staged in a fixed 32 MiB array built into the
+ * cols % 256 == 0; tokens >= 16; 16-bit operands -- binary16 when the matrix's
+ * weights fit its range, else bfloat16 -- with f32 accumulation), but the
+ * 16-bit copy of the activations is staged in a fixed 32 MiB array built into the
  * library (every GPU that loads the library holds it until the process exits)
  * instead of an executor buffer.  x_dev / y_dev are device buffers of
  * tokens*cols and tokens*rows floats, x_dev 16-byte aligned; the work is
  * enqueued on `stream` (null = the executor's stream) without synchronizing.
  * Limit: tokens * cols * 2 bytes <= 32 MiB, larger calls are rejected with
  * LLR_ERR_INVALID and a message; nothing else is tried.
+ * A long row that llr_matmul_device would cut along K into slices (partial sums in
+ * executor scratch) is computed in one piece here when the slices do not fit
+ * the fixed array: the result then differs from llr_matmul_device's in summation
+ * order only.
  * The first call on a device looks up the array's device address
  * (cudaGetSymbolAddress); make that first call outside any stream capture.
  * The call itself performs no cudaMalloc, cudaFree or other allocating call.
@@ -184,17 +189,31 @@ int llr_exec_synchronize(llr_exec* exec);
 
 /* ---- programs: many decode products in one persistent launch -----------------
  * An extension with no counterpart in the reference, which launches and
- * synchronizes once per product [gpu.rs:301-334].  A program is a fixed list of
- * products over resident matrices with device activation / result buffers.
- * Entries with the same `phase` value are independent of each other; a phase
- * starts only after every product of the previous phase has been written, so a
- * later entry may read an earlier phase's y as its x.  `phase` must be
+ * synchronizes once per product [gpu.rs:301-334]; it stands where the per-token
+ * sequence of gemm_into calls of Llama::forward_layers stands
+ * [langtax/src/decode.rs:2737-3097].  A program is a fixed list of products over
+ * resident matrices with device activation / result buffers.  Entries with the
+ * same `phase` value are independent of each other; `phase` must be
  * non-decreasing along the list.  Supported: Q4_K, Q6_K (cols % 2048 == 0) and
  * Q8_0 matrices with cols % 256 == 0, tokens 1..8, buffers 16-byte aligned.
  * One launch (cooperative: the whole grid is resident) runs the list;
- * llr_program_run returns without synchronizing.  A program owns a few bytes
- * of device scratch (one counter per phase); two runs of the same program must
- * not overlap on the device. */
+ * llr_program_run returns without synchronizing.  Two runs of the same program
+ * must not overlap on the device.
+ *
+ * How a later entry gets an earlier entry's result: when an input pointer
+ * (x_dev, and for llr_program_op also x2_dev of SwiGLU and resid_dev) is exactly
+ * the y_dev of an earlier-phase entry with the same `tokens` and as many rows as
+ * the reader has columns (one token: any 16-byte aligned part of that result will
+ * do), the result travels inside the launch as 8-byte pairs {value, tag of run
+ * and phase} in scratch the program owns: the reader spins (bounded) on the pairs
+ * it needs, so nothing else separates the two phases.  y_dev still receives the
+ * plain floats.
+ * llr_program_create keeps strict phases on top: a phase with an input that is
+ * NOT such a result starts only after every product of the previous phase has
+ * been written (a counter per phase), so that x may alias earlier results in any
+ * other way.  llr_program_create_ops does not: inputs that are not results of
+ * the program are read as they are when the launch starts and must not be
+ * written during it. */
 typedef struct llr_program llr_program;
 typedef struct llr_program_entry {
   const llr_matrix* matrix;
@@ -207,31 +226,83 @@ int llr_program_create(llr_exec* exec, const llr_program_entry* entries, size_t 
                        llr_program** out);
 int llr_program_run(llr_exec* exec, llr_program* program, void* stream);
 int llr_program_free(llr_program* program);
+/* entries, phases, phases that synchronise through a counter, CTAs of the launch (any pointer may be null) */
+int llr_program_info(const llr_program* program, uint32_t* entries, uint32_t* phases, uint32_t* counter_phases,
+                     uint32_t* ctas);
+
+/* Products with the element-wise step that precedes them in the model and the
+ * residual add that follows, so that a chain of products needs no other kernel
+ * [the walk of decode.rs:2737-3097: rmsnorm_inplace :11498 before q/k/v, gate/up
+ * and the output matrix; silu(gate) * up :2972-2996 before ffn_down; `+ residual`
+ * after attn_output and ffn_down].
+ *   LLR_XOP_NONE     y = W x
+ *   LLR_XOP_RMSNORM  y = W ((x * 1/sqrt(mean(x^2) + eps)) * x2), x2 = cols norm weights
+ *                    (plain device floats, NULL = all ones); the sum of squares is added
+ *                    in a fixed tree order, not sequentially as the reference does
+ *   LLR_XOP_SWIGLU   y = W (silu(x) * x2), x2 = tokens * cols floats (the `up` result)
+ * resid_dev (optional, tokens * y_ld floats, indexed like the full-width result):
+ * y += resid.  y_ld = floats between consecutive activation rows of y (0: rows). */
+#define LLR_XOP_NONE 0
+#define LLR_XOP_RMSNORM 1
+#define LLR_XOP_SWIGLU 2
+typedef struct llr_program_op {
+  const llr_matrix* matrix;
+  const float* x_dev;
+  const float* x2_dev;
+  const float* resid_dev;
+  float* y_dev;
+  uint64_t y_ld;
+  uint32_t tokens, phase;
+  uint32_t x_op;
+  float eps;
+} llr_program_op;
+/* shard == NULL: one GPU.  Otherwise this rank's part of a row-sharded program, see below. */
+typedef struct llr_program_shard {
+  void* arena;
+  size_t arena_bytes;
+  uint32_t world, rank;
+  void* const* peer_arenas;
+} llr_program_shard;
+int llr_program_create_ops(llr_exec* exec, const llr_program_op* ops, size_t n_ops,
+                           const llr_program_shard* shard, llr_program** out);
+
+/* Bound of the device-side waits of programs on data another CTA or rank produces, in
+ * polls of roughly 0.1-0.3 us (default 2^20).  When a wait runs out the kernel records it,
+ * every later wait of that launch returns at once, the launch finishes, and
+ * llr_exec_synchronize reports LLR_ERR_CUDA; the executor stays usable [the reference's
+ * executor stays usable after an error: native-cuda/src/main.rs:48-66]. */
+int llr_exec_set_wait_limit(llr_exec* exec, uint32_t polls);
 
 /* ---- row-sharded programs across GPUs -------------------------------------------
  * No counterpart in the reference (it runs on one device).  One process per GPU; rank g
  * holds rows [g*rows/G, (g+1)*rows/G) of every matrix as its own resident matrix and a
  * full-width copy of every result vector.  A sharded program is a program whose reducer
- * also stores each finished value into the same place of every other rank's result
- * buffer (peer stores over NVLink) and whose phase counters count the CTAs of all ranks,
- * so the all-gather of result slices is part of the launch: no collective call between
- * products.  All ranks must create the same program (same entries, phases and shard
- * shapes) and run it the same number of times.
+ * also stores each finished value, plain and tagged, into the same place of every other
+ * rank's buffers (peer stores over NVLink), so the all-gather of result slices is part of
+ * the launch: no collective call between products, and a reader spins on its own GPU's
+ * copy of the pairs.  All ranks must create the same program (same entries, phases and
+ * shard shapes) before any rank runs it, and run it the same number of times.  After a run,
+ * a rank's plain results are complete once every rank has synchronized its stream.
+ * A device-side wait is bounded (llr_exec_set_wait_limit): ranks must start a run within
+ * that bound of each other (default about 0.2 s) or the run fails with LLR_ERR_CUDA.
  *
  * Buffers the peers write live in one arena per rank: llr_shared_alloc returns zeroed
  * device memory and a 64-byte handle another process opens with llr_shared_open (CUDA
- * IPC).  The first LLR_ARENA_HEADER_BYTES of an arena belong to the library (phase
- * counters: at most 4096 phases); result buffers lie behind it, at the same offsets on
+ * IPC).  An arena is: LLR_ARENA_HEADER_BYTES that belong to the library | a result area
+ * of R bytes | 2 R bytes for the tagged copies, R = ((arena_bytes - header) / 3) rounded
+ * down to a multiple of 256.  Result buffers lie in the result area, at the same offsets on
  * every rank.  y_dev of an entry points at this rank's slice inside its own arena;
- * y_ld[i] is the distance in floats between consecutive activation rows of that result
- * (the full row count; NULL: the shard's row count).  peer_arenas[g] is rank g's arena
- * as opened here (the entry of this rank itself is ignored).  world is 2..8. */
+ * y_ld is the full row count (world * shard rows for a result that later entries read).
+ * peer_arenas[g] is rank g's arena as opened here (the entry of this rank itself is
+ * ignored).  world is 2..8; at most 4095 phases.  Arenas may be reused by a later
+ * program once no rank is running the earlier one. */
 #define LLR_ARENA_HEADER_BYTES 65536
 typedef struct llr_ipc_handle { unsigned char bytes[64]; } llr_ipc_handle;
 int llr_shared_alloc(llr_exec* exec, size_t bytes, void** dev, llr_ipc_handle* handle);
 int llr_shared_open(llr_exec* exec, const llr_ipc_handle* handle, void** dev);
 int llr_shared_close(llr_exec* exec, void* dev);
 int llr_shared_free(llr_exec* exec, void* dev);
+/* Strict phases, as llr_program_create; y_ld[i] as llr_program_op.y_ld (NULL: shard rows). */
 int llr_program_create_sharded(llr_exec* exec, const llr_program_entry* entries, const uint64_t* y_ld,
                                size_t n_entries, void* arena, size_t arena_bytes, uint32_t world,
                                uint32_t rank, void* const* peer_arenas, llr_program** out);

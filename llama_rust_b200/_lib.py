@@ -20,7 +20,7 @@ SYMBOLS = [
     "llr_dequant_rows", "llr_matrix_synth", "llr_matrix_download", "llr_program_create",
     "llr_program_run", "llr_program_free", "llr_gemm_device_noalloc", "llr_moe_ffn",
     "llr_shared_alloc", "llr_shared_open", "llr_shared_close", "llr_shared_free",
-    "llr_program_create_sharded",
+    "llr_program_create_sharded", "llr_program_create_ops", "llr_program_info", "llr_exec_set_wait_limit",
 ]
 ARENA_HEADER_BYTES = 65536
 
@@ -34,6 +34,17 @@ class Counters(C.Structure):
 class ProgramEntry(C.Structure):
     _fields_ = [("matrix", C.c_void_p), ("x_dev", C.c_void_p), ("y_dev", C.c_void_p),
                 ("tokens", C.c_uint32), ("phase", C.c_uint32)]
+
+
+class ProgramOp(C.Structure):
+    _fields_ = [("matrix", C.c_void_p), ("x_dev", C.c_void_p), ("x2_dev", C.c_void_p), ("resid_dev", C.c_void_p),
+                ("y_dev", C.c_void_p), ("y_ld", C.c_uint64), ("tokens", C.c_uint32), ("phase", C.c_uint32),
+                ("x_op", C.c_uint32), ("eps", C.c_float)]
+
+
+class ProgramShard(C.Structure):
+    _fields_ = [("arena", C.c_void_p), ("arena_bytes", C.c_size_t), ("world", C.c_uint32), ("rank", C.c_uint32),
+                ("peer_arenas", C.POINTER(C.c_void_p))]
 
 
 class MoeLayer(C.Structure):
@@ -83,6 +94,9 @@ def load() -> C.CDLL:
     lib.llr_shared_free.argtypes = [vp, vp]
     lib.llr_program_create_sharded.argtypes = [vp, C.POINTER(ProgramEntry), C.POINTER(C.c_uint64), sz, vp, sz,
                                                C.c_uint32, C.c_uint32, C.POINTER(vp), C.POINTER(vp)]
+    lib.llr_program_create_ops.argtypes = [vp, C.POINTER(ProgramOp), sz, C.POINTER(ProgramShard), C.POINTER(vp)]
+    lib.llr_program_info.argtypes = [vp, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]
+    lib.llr_exec_set_wait_limit.argtypes = [vp, C.c_uint32]
     for s in SYMBOLS:
         if s != "llr_exec_last_error":
             getattr(lib, s).restype = C.c_int

@@ -114,6 +114,7 @@ struct llr_exec {
   std::string err;
   llr_counters ctr{};
   int path = PATH_AUTO;
+  int poll_limit = 1 << 20;  // iterations a device-side wait for another CTA's or rank's data may take
   int* err_flag = nullptr;  // device alias of err_pinned: set by a kernel whose bounded wait ran out
   volatile int* err_pinned = nullptr;  // the same word, mapped pinned host memory
   struct PinSeen { const void* p; bool pinned; } pin_seen[8] = {};
@@ -693,10 +694,26 @@ int llr_matmul(llr_exec* e, uint8_t dtype, size_t rows, size_t cols, size_t toke
   llr_matrix* m = nullptr;
   if ((rc = alloc_matrix(e, dtype, rows, cols, rb, expect, &m)) != LLR_OK) return rc;
   cudaError_t ce = cudaMemcpyAsync(m->dev, packed, expect, cudaMemcpyHostToDevice, e->stream);
-  if (ce != cudaSuccess) { release_matrix(e, m); return fail_cuda(e, ce, "weight upload"); }
+  // Operand choice of the tensor-core GEMM, as llr_matrix_upload makes it: a scan of the block headers behind
+  // the upload.  Without it every product that arrives here with 64 or more activation rows would take the
+  // bfloat16 operands (8 significant bits) although the weights fit binary16 (11 bits).  The scan's answer is
+  // needed only when this very call runs the GEMM; otherwise it is collected without an extra wait: the
+  // host-pointer product below synchronizes with the stream before it returns.
+  unsigned int bound = 0;
+  const bool examine = gemm_tc_supported(view_of(m), 64) && e->bound_dev != nullptr;
+  if (ce == cudaSuccess) ce = begin_range_check(e, m, &bound);
+  if (ce == cudaSuccess && examine && matmul_wants_tc(view_of(m), (int64_t)tokens, e->path)) {
+    ce = cudaStreamSynchronize(e->stream);
+    if (ce == cudaSuccess) finish_range_check(m, bound, true);
+  }
+  if (ce != cudaSuccess) { cudaStreamSynchronize(e->stream); release_matrix(e, m); return fail_cuda(e, ce, "weight upload"); }
   ++e->ctr.uploads;
   e->ctr.upload_bytes += expect;
   rc = run_host(e, m, tokens, x, y);
+  if (rc == LLR_OK && examine && m->f16_ok < 0) {
+    cudaStreamSynchronize(e->stream);  // decode-sized calls return on a completion word, not on the stream
+    finish_range_check(m, bound, true);
+  }
   if (rc != LLR_OK) { cudaStreamSynchronize(e->stream); cudaGetLastError(); release_matrix(e, m); return rc; }
   // oversized matrices run once and are released (native_gpu.rs:199-211)
   if (expect <= e->limit) {
@@ -997,49 +1014,135 @@ struct llr_program {
 };
 
 namespace {
-// validation shared by the two ways of creating a program
-int program_entries(llr_exec* e, const llr_program_entry* entries, const uint64_t* y_ld, size_t n,
-                    std::vector<ProgEntry>* pe, std::vector<int>* phase) {
-  if (!entries || n == 0 || n > (1u << 20)) return fail(e, LLR_ERR_INVALID, "a program needs 1..2^20 entries");
+// validation shared by the ways of creating a program; ops may carry an operation on the input and a residual
+int program_entries(llr_exec* e, const llr_program_op* ops, size_t n, std::vector<ProgEntry>* pe, std::vector<int>* phase) {
+  if (!ops || n == 0 || n > (1u << 20)) return fail(e, LLR_ERR_INVALID, "a program needs 1..2^20 entries");
   pe->resize(n);
   phase->resize(n);
   for (size_t i = 0; i < n; ++i) {
-    const llr_program_entry& in = entries[i];
+    const llr_program_op& in = ops[i];
+    const std::string which = "program entry " + std::to_string(i);
     int rc = check_matrix(e, in.matrix);
     if (rc) return rc;
     if (in.tokens == 0 || in.tokens > 8 || !in.x_dev || !in.y_dev || ((uintptr_t)in.x_dev & 15) != 0)
-      return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) + ": tokens must be 1..8 and buffers 16-byte aligned");
-    if (i > 0 && in.phase < entries[i - 1].phase)
-      return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) + ": phase must be non-decreasing");
+      return fail(e, LLR_ERR_INVALID, which + ": tokens must be 1..8 and buffers 16-byte aligned");
+    if (i > 0 && in.phase < ops[i - 1].phase) return fail(e, LLR_ERR_INVALID, which + ": phase must be non-decreasing");
     const MatView v = view_of(in.matrix);
     if (!prog_entry_supported(v))
-      return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) +
-                                          ": only Q4_K, Q6_K (cols % 2048 == 0) and Q8_0 with cols % 256 == 0 run in programs");
-    const int64_t ld = y_ld ? (int64_t)y_ld[i] : v.rows;
-    if (ld < v.rows) return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) + ": y_ld is smaller than the row count");
-    (*pe)[i] = ProgEntry{v.w, in.x_dev, in.y_dev, v.row_bytes, (int)v.rows, (int)v.cols, v.dtype, (int)in.tokens, 0, 0, ld};
+      return fail(e, LLR_ERR_INVALID, which + ": only Q4_K, Q6_K (cols % 2048 == 0) and Q8_0 with cols % 256 == 0 run in programs");
+    const int64_t ld = in.y_ld ? (int64_t)in.y_ld : v.rows;
+    if (ld < v.rows) return fail(e, LLR_ERR_INVALID, which + ": y_ld is smaller than the row count");
+    if (in.x_op > LLR_XOP_SWIGLU) return fail(e, LLR_ERR_INVALID, which + ": unknown input operation");
+    if (in.x_op == LLR_XOP_SWIGLU && (!in.x2_dev || ((uintptr_t)in.x2_dev & 15) != 0))
+      return fail(e, LLR_ERR_INVALID, which + ": SwiGLU needs its second input, 16-byte aligned");
+    if (in.x_op == LLR_XOP_RMSNORM && (((uintptr_t)in.x2_dev & 15) != 0 || !(in.eps >= 0.0f)))
+      return fail(e, LLR_ERR_INVALID, which + ": RMSNorm weights must be 16-byte aligned and eps non-negative");
+    if (((uintptr_t)in.resid_dev & 3) != 0 || ((uintptr_t)in.y_dev & 3) != 0)
+      return fail(e, LLR_ERR_INVALID, which + ": result and residual must be 4-byte aligned");
+    ProgEntry E{};
+    E.w = v.w; E.x = in.x_dev; E.y = in.y_dev; E.row_bytes = v.row_bytes;
+    E.rows = (int)v.rows; E.cols = (int)v.cols; E.dtype = v.dtype; E.tokens = (int)in.tokens;
+    E.y_ld = ld;
+    E.x2 = in.x_op == LLR_XOP_NONE ? nullptr : in.x2_dev;
+    E.resid = in.resid_dev;
+    E.x_op = (int)in.x_op; E.eps = in.eps;
+    E.x_phase = E.x2_phase = E.resid_phase = -1;
+    (*pe)[i] = E;
     (*phase)[i] = (int)in.phase;
   }
   return LLR_OK;
+}
+
+int program_from(llr_exec* e, const llr_program_op* ops, size_t n, bool strict, const llr_program_shard* sh, llr_program** out) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!out) return fail(e, LLR_ERR_INVALID, "null output pointer");
+  *out = nullptr;
+  if (sh && (sh->world < 2 || sh->world > 8 || sh->rank >= sh->world || !sh->arena || !sh->peer_arenas ||
+             sh->arena_bytes <= LLR_ARENA_HEADER_BYTES))
+    return fail(e, LLR_ERR_INVALID, "a sharded program needs 2..8 ranks, an arena larger than its header and the peers' arenas");
+  std::vector<ProgEntry> pe;
+  std::vector<int> phase;
+  int rc = program_entries(e, ops, n, &pe, &phase);
+  if (rc) return rc;
+  ShardInfo si{};
+  if (sh) {
+    // header | results | tagged copies of the results (twice as large)
+    const size_t result_bytes = ((sh->arena_bytes - LLR_ARENA_HEADER_BYTES) / 3) & ~(size_t)255;
+    const char* lo = (const char*)sh->arena + LLR_ARENA_HEADER_BYTES;
+    const char* hi = lo + result_bytes;
+    int n_phases = 0;
+    for (size_t i = 0; i < n; ++i) {
+      const char* y0 = (const char*)pe[i].y;
+      const char* y1 = y0 + ((size_t)(pe[i].tokens - 1) * (size_t)pe[i].y_ld + (size_t)pe[i].rows) * sizeof(float);
+      if (y0 < lo || y1 > hi)
+        return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) + ": the result slice is outside the arena's result area");
+      if (i == 0 || phase[i] != phase[i - 1]) ++n_phases;
+    }
+    if (n_phases > 4095) return fail(e, LLR_ERR_INVALID, "a sharded program has at most 4095 phases");
+    for (uint32_t g = 0; g < sh->world; ++g) {
+      if (g == sh->rank) continue;
+      if (!sh->peer_arenas[g]) return fail(e, LLR_ERR_INVALID, "missing arena of rank " + std::to_string(g));
+      si.peers.counters[si.peers.n_peers] = (unsigned long long*)sh->peer_arenas[g];
+      si.peers.y_delta[si.peers.n_peers] = (long long)((const char*)sh->peer_arenas[g] - (const char*)sh->arena);
+      ++si.peers.n_peers;
+    }
+    si.counters = (unsigned long long*)sh->arena;
+    si.arena = (char*)sh->arena;
+    si.result_bytes = result_bytes;
+    si.world = (int)sh->world;
+    si.rank = (int)sh->rank;
+  }
+  DeviceGuard guard(e->device);
+  llr::Program* prog = nullptr;
+  std::string msg;
+  cudaError_t ce = program_create(pe, phase, e->sm_count, strict, sh ? &si : nullptr, &prog, &msg);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, msg.empty() ? "program creation" : msg.c_str());
+  llr_program* p = new (std::nothrow) llr_program{e, prog};
+  if (!p) { program_destroy(prog); return fail(e, LLR_ERR_OOM, "host allocation failed"); }
+  *out = p;
+  return LLR_OK;
+}
+
+std::vector<llr_program_op> ops_of(const llr_program_entry* entries, const uint64_t* y_ld, size_t n) {
+  std::vector<llr_program_op> ops(entries ? n : 0);
+  for (size_t i = 0; i < ops.size(); ++i) {
+    ops[i] = llr_program_op{};
+    ops[i].matrix = entries[i].matrix;
+    ops[i].x_dev = entries[i].x_dev;
+    ops[i].y_dev = entries[i].y_dev;
+    ops[i].y_ld = y_ld ? y_ld[i] : 0;
+    ops[i].tokens = entries[i].tokens;
+    ops[i].phase = entries[i].phase;
+  }
+  return ops;
 }
 }  // namespace
 
 int llr_program_create(llr_exec* e, const llr_program_entry* entries, size_t n, llr_program** out) {
   if (!e) return LLR_ERR_INVALID;
-  if (!out) return fail(e, LLR_ERR_INVALID, "null output pointer");
-  *out = nullptr;
-  std::vector<ProgEntry> pe;
-  std::vector<int> phase;
-  int rc = program_entries(e, entries, nullptr, n, &pe, &phase);
-  if (rc) return rc;
-  DeviceGuard guard(e->device);
-  llr::Program* prog = nullptr;
-  std::string msg;
-  cudaError_t ce = program_create(pe, phase, e->sm_count, &prog, &msg);
-  if (ce != cudaSuccess) return fail_cuda(e, ce, "program creation");
-  llr_program* p = new (std::nothrow) llr_program{e, prog};
-  if (!p) { program_destroy(prog); return fail(e, LLR_ERR_OOM, "host allocation failed"); }
-  *out = p;
+  if (n > (1u << 20)) return fail(e, LLR_ERR_INVALID, "a program needs 1..2^20 entries");
+  const std::vector<llr_program_op> ops = ops_of(entries, nullptr, n);
+  return program_from(e, ops.empty() ? nullptr : ops.data(), n, true, nullptr, out);
+}
+
+int llr_program_create_ops(llr_exec* e, const llr_program_op* ops, size_t n, const llr_program_shard* shard,
+                           llr_program** out) {
+  return program_from(e, ops, n, false, shard, out);
+}
+
+int llr_program_info(const llr_program* p, uint32_t* entries, uint32_t* phases, uint32_t* counter_phases, uint32_t* ctas) {
+  if (!p || !p->prog) return LLR_ERR_INVALID;
+  if (entries) *entries = (uint32_t)llr::program_entries(p->prog);
+  if (phases) *phases = (uint32_t)llr::program_phases(p->prog);
+  if (counter_phases) *counter_phases = (uint32_t)llr::program_counter_phases(p->prog);
+  if (ctas) *ctas = (uint32_t)llr::program_grid(p->prog);
+  return LLR_OK;
+}
+
+int llr_exec_set_wait_limit(llr_exec* e, uint32_t polls) {
+  if (!e) return LLR_ERR_INVALID;
+  if (polls == 0 || polls > (1u << 30)) return fail(e, LLR_ERR_INVALID, "the wait limit must be 1..2^30 polls");
+  e->poll_limit = (int)polls;
   return LLR_OK;
 }
 
@@ -1098,42 +1201,10 @@ int llr_program_create_sharded(llr_exec* e, const llr_program_entry* entries, co
                                void* arena, size_t arena_bytes, uint32_t world, uint32_t rank,
                                void* const* peer_arenas, llr_program** out) {
   if (!e) return LLR_ERR_INVALID;
-  if (!out) return fail(e, LLR_ERR_INVALID, "null output pointer");
-  *out = nullptr;
-  if (world < 2 || world > 8 || rank >= world || !arena || !peer_arenas || arena_bytes <= LLR_ARENA_HEADER_BYTES)
-    return fail(e, LLR_ERR_INVALID, "a sharded program needs 2..8 ranks, an arena larger than its header and the peers' arenas");
-  std::vector<ProgEntry> pe;
-  std::vector<int> phase;
-  int rc = program_entries(e, entries, y_ld, n, &pe, &phase);
-  if (rc) return rc;
-  const char* lo = (const char*)arena + LLR_ARENA_HEADER_BYTES;
-  const char* hi = (const char*)arena + arena_bytes;
-  int n_phases = 0;
-  for (size_t i = 0; i < n; ++i) {
-    const char* y0 = (const char*)pe[i].y;
-    const char* y1 = y0 + ((size_t)(pe[i].tokens - 1) * (size_t)pe[i].y_ld + (size_t)pe[i].rows) * sizeof(float);
-    if (y0 < lo || y1 > hi)
-      return fail(e, LLR_ERR_INVALID, "program entry " + std::to_string(i) + ": the result slice is outside the arena");
-    if (i == 0 || phase[i] != phase[i - 1]) ++n_phases;
-  }
-  if (n_phases > 4096) return fail(e, LLR_ERR_INVALID, "a sharded program has at most 4096 phases");
-  PeerTable pt{};
-  for (uint32_t g = 0; g < world; ++g) {
-    if (g == rank) continue;
-    if (!peer_arenas[g]) return fail(e, LLR_ERR_INVALID, "missing arena of rank " + std::to_string(g));
-    pt.counters[pt.n_peers] = (unsigned long long*)peer_arenas[g];
-    pt.y_delta[pt.n_peers] = (long long)((const char*)peer_arenas[g] - (const char*)arena);
-    ++pt.n_peers;
-  }
-  DeviceGuard guard(e->device);
-  llr::Program* prog = nullptr;
-  std::string msg;
-  cudaError_t ce = program_create_sharded(pe, phase, e->sm_count, (unsigned long long*)arena, pt, &prog, &msg);
-  if (ce != cudaSuccess) return fail_cuda(e, ce, "program creation");
-  llr_program* p = new (std::nothrow) llr_program{e, prog};
-  if (!p) { program_destroy(prog); return fail(e, LLR_ERR_OOM, "host allocation failed"); }
-  *out = p;
-  return LLR_OK;
+  if (n > (1u << 20)) return fail(e, LLR_ERR_INVALID, "a program needs 1..2^20 entries");
+  const std::vector<llr_program_op> ops = ops_of(entries, y_ld, n);
+  const llr_program_shard sh{arena, arena_bytes, world, rank, peer_arenas};
+  return program_from(e, ops.empty() ? nullptr : ops.data(), n, true, &sh, out);
 }
 
 int llr_program_run(llr_exec* e, llr_program* p, void* stream) {
@@ -1141,7 +1212,7 @@ int llr_program_run(llr_exec* e, llr_program* p, void* stream) {
   if (!p || p->owner != e) return fail(e, LLR_ERR_FOREIGN, "program belongs to a different executor");
   DeviceGuard guard(e->device);
   cudaStream_t s = stream ? (cudaStream_t)stream : e->stream;
-  cudaError_t ce = program_run(p->prog, s, e->err_flag, &e->ctr.launches);
+  cudaError_t ce = program_run(p->prog, s, e->err_flag, e->poll_limit, &e->ctr.launches);
   if (ce != cudaSuccess) return fail_cuda(e, ce, "program launch");
   return LLR_OK;
 }

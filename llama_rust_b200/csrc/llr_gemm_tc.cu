@@ -45,6 +45,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include <cstring>
 #include <type_traits>
 #include <vector>
@@ -1018,15 +1020,17 @@ cudaError_t launch_gemm_tc_static(int device, const MatView& m, const float* x, 
                                   cudaStream_t stream, int* err_flag, uint64_t* launches) {
   // In host code `g_static_scratch` is only a handle for the symbol, not a device address:
   // the address is looked up once per device, with that device current.
-  static void* addr[64] = {nullptr};
+  // Executors on different threads may make their first call at the same time: the slot is atomic, and
+  // two threads that both look the address up store the same value.
+  static std::atomic<void*> addr[64];
   if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
-  if (!addr[device]) {
-    void* p = nullptr;
+  void* p = addr[device].load(std::memory_order_acquire);
+  if (!p) {
     const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
     if (e != cudaSuccess) return e;
-    addr[device] = p;
+    addr[device].store(p, std::memory_order_release);
   }
-  return launch_gemm_tc(m, x, y, tokens, addr[device], GEMM_STATIC_SCRATCH_BYTES + (512 << 10), stream, err_flag, launches);
+  return launch_gemm_tc(m, x, y, tokens, p, GEMM_STATIC_SCRATCH_BYTES + (512 << 10), stream, err_flag, launches);
 }
 
 }  // namespace llr

@@ -11,8 +11,7 @@
 // Pipeline.  A CTA has ten warps with three roles and no CTA-wide barrier in
 // its steady state:
 //   * producer warp: walks the CTA's chunk list (16 rows x one column piece)
-//     and keeps NST TMA bulk copies in flight, one cp.async.bulk per row into a
-//     padded shared-memory stride; a stage is refilled as soon as the eight
+//     and keeps NST TMA copies in flight; a stage is refilled as soon as the eight
 //     consumer warps have released it (mbarrier `empty`), not at a barrier;
 //   * eight consumer warps: wait for a stage (`full`), turn their share of its
 //     columns into A fragments and MMAs, release the stage, and at the end of a
@@ -27,21 +26,24 @@
 // on earlier kernels, everything that touches activations or results waits.
 //
 // Program: one cooperative launch runs a list of products grouped in phases
-// (independent products share a phase, e.g. attn_q|k|v; a phase starts when the
-// previous one is completely written).  The producer runs ahead across product
-// and phase boundaries, so the next weights stream in while the CTA waits for
-// the dependency, which is a per-phase counter in global memory: the reducer
-// adds one after its share of the phase is written and fenced, consumers poll
-// with acquire loads.  Activations written during the launch are read with
-// L2-coherent loads.
+// (independent products share a phase, e.g. attn_q|k|v).  The producer runs ahead
+// across product and phase boundaries, so the next weights stream in while the
+// CTA waits for its input.  A result that a later entry reads travels as tagged
+// pairs {f32 bits, tag of run and phase}: the reducer stores each finished value
+// with its tag, the consumers' activation split loads the pairs and spins
+// (bounded) until the tags are the expected ones.  The value is its own arrival
+// signal: no counter, no fence, no poll between two phases.  The split can apply
+// the element-wise step that stands between two products in the model (RMSNorm,
+// SwiGLU), and the reducer can add a residual vector, so a chain of products needs
+// no other kernel.  Inputs that are not results of the program are plain f32; a
+// program created with strict phases makes a phase with such an input wait for a
+// per-phase counter (release add by every reducer, acquire polling), as a barrier.
 //
 // Row-sharded program (one process per GPU, each with a row slice of every matrix):
 // the exchange of result slices is part of the kernel.  The reducer stores each
-// finished value into its own y and into the same place of every peer's y (plain
-// peer stores over NVLink) and counts on its own rank's phase counter; the CTA that
-// completes the local count sends one system-scope release add to every peer.
-// Consumers wait for the local count and for one arrival per peer.  No collective
-// library call, plain stores and atomics only, every wait bounded.
+// finished value (plain and tagged) into its own buffers and into the same place of
+// every peer's (peer stores over NVLink); consumers spin on their own GPU's copy.
+// No collective library call, plain 4- and 8-byte stores only, every wait bounded.
 #include <cuda_runtime.h>
 
 #include <cstring>
@@ -53,6 +55,22 @@
 #include "llr_mma_common.cuh"
 #include "llr_tmap.cuh"
 
+#define LLR_ARENA_HEADER_BYTES_INTERNAL 65536  // LLR_ARENA_HEADER_BYTES of the public header
+
+#ifdef LLR_TRACE
+// Debug build only: clock64 stamps of CTAs 0 and 150, [cta][phase][event].
+__device__ long long g_trace[2][1024][8];
+__device__ unsigned long long g_trace_all[304][132][4];  // [cta][phase][event 0 phase start, 2 dependency met, 4 consumer done, 5 published], globaltimer ns
+__device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define LLR_STAMP(ev) do { if (PROGRAM && lane == 0 && (warp == 0 || warp == CW + 1) && ph < 132) { \
+    if ((bid == 0 || bid == 150)) g_trace[bid != 0][ph][ev] = clock64(); \
+    if (bid < 304 && (ev == 0 || ev == 2 || ev == 4 || ev == 5)) g_trace_all[bid][ph][ev == 0 ? 0 : ev == 2 ? 1 : ev == 4 ? 2 : 3] = gtimer(); } } while (0)
+extern "C" int llr_debug_trace(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)); }
+extern "C" int llr_debug_trace_all(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_trace_all, sizeof(g_trace_all)); }
+#else
+#define LLR_STAMP(ev) do {} while (0)
+#endif
+
 namespace llr {
 namespace {
 using namespace mma;
@@ -62,10 +80,10 @@ constexpr int NTHREADS = (CW + 2) * 32;   // + producer + reducer
 constexpr int NRB = 4;                    // reduction buffers
 constexpr int MAX_CHUNK = Lay<DT_Q4_K, 1>::CHUNK;
 static_assert(Lay<DT_Q6_K, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q8_0, 1>::CHUNK <= MAX_CHUNK, "ring stage");
-constexpr int POLL_LIMIT = 1 << 20;
 // Sharded programs keep two counter arrays in the arena header: [0, 4096) this rank's CTAs per
 // phase, [4096, 8192) arrivals of the peers per phase.
 constexpr int PEER_COUNTER_OFFSET = 4096;
+constexpr int COUNTER_WORDS = 8192;
 
 template <int MT> struct SLay {
   static constexpr int NT = (MT + 1) / 2;
@@ -120,7 +138,14 @@ struct Work {
   const PeerTable* peers;  // row-sharded programs only
   HostOut host;            // single products that deliver their result to the host themselves
   const CUtensorMap* maps; // one per entry (Q4_K, Q6_K; unused for Q8_0)
+  int n_entries;           // entries of the program
+  uint32_t tag_base;       // tag of phase p in this run = tag_base + p
+  int poll_limit;          // bound of the waits on other CTAs' or ranks' data
 };
+// Slots of the counter array beside the per-phase counters ([0, 4095) this rank's CTAs per phase,
+// [4096, 8191) arrivals of the peers per phase).
+constexpr int TAG_SLOT = 4095;                          // first tag the next run may use (read at creation)
+constexpr int ABORT_SLOT = PEER_COUNTER_OFFSET + 4095;  // epoch of a run in which a wait ran out
 
 // Tile range of this CTA inside a phase, and inside one entry of it.
 // The grid is two CTAs per SM and CTAs b and b + nb/2 usually share an SM.  Slices are dealt so
@@ -138,10 +163,39 @@ __device__ __forceinline__ bool entry_range(const ProgEntry& E, int lo, int hi, 
   return *t0 < *t1;
 }
 
+// Everything between "the input exists" and "its digit planes are in shared memory": the 1/rms of an
+// RMSNorm input (all consumer warps, when need_rms) and this warp's share of the activation split.
+// Not inlined: it runs once per entry and span, and its registers (sixteen pairs in flight per lane)
+// must not compete with the accumulators of the block routines.
+#ifndef LLR_PREP_INLINE
+#define LLR_PREP_INLINE __forceinline__
+#endif
+template <int MT, bool PEERS, bool FLOW>
+__device__ LLR_PREP_INLINE bool prepare_activations(const XSrc src, int cols, int tokens, float eps, int span, int nblk256, bool need_rms,
+                                                 uint8_t* dig, float* sxf, float* xsi, float* s_part, float* s_inv, WaitCtx wc) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t keep = l2_policy_evict_last();
+  if (FLOW && need_rms) row_inv_rms<MT, PEERS>(src, cols, tokens, eps, s_part, s_inv, warp, lane, wc, keep);
+  split_activations<MT, PEERS, FLOW>(src, cols, span * Sp<MT>::SPAN, nblk256, tokens, dig, sxf, xsi, s_inv, warp, lane, wc, keep);
+  return wc.dead;
+}
+
+// What the digit planes in shared memory were made from; kept in shared memory, one record per consumer
+// warp (warps pass an entry at different times), because it is looked at once per entry and span and
+// would otherwise occupy registers throughout the block routines.
+struct SplitKey {
+  const void* x;
+  const void* x2;
+  int cols, span, tokens, op, ph, pad;
+};
+
 // DTFIX: the one format of a single-product launch (the other block routines are compiled
 // out, which keeps the consumers under the register budget of two CTAs per SM), or -1 for
 // programs, which switch per entry.
-template <int MT, bool PROGRAM, int DTFIX, bool PEERS = false, bool HOSTOUT = false>
+// FLOW: the program may carry results from entry to entry as tagged pairs and apply RMSNorm / SwiGLU /
+// residual adds; compiled out otherwise (the plain split and the per-phase counters need fewer registers
+// around the block routines, which run at the register limit of two CTAs per SM).
+template <int MT, bool PROGRAM, int DTFIX, bool PEERS = false, bool HOSTOUT = false, bool FLOW = false>
 __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* counters,
                                             unsigned long long epoch, int* err) {
   using L = SLay<MT>;
@@ -180,15 +234,18 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
         int lo, hi;
         phase_range(P, bid, nb, &lo, &hi);
         for (int ei = 0; ei < P.n_entries && lo < hi; ++ei) {
-          const ProgEntry E = wk.entries[P.first_entry + ei];
+          const ProgEntry& E = wk.entries[P.first_entry + ei];
           int t0, t1;
           if (!entry_range(E, lo, hi, &t0, &t1)) continue;
           const int dtype = DTFIX >= 0 ? DTFIX : E.dtype;
           const Geom gm = geom_of(dtype);
           const CUtensorMap* map = wk.maps + (PROGRAM ? P.first_entry + ei : 0);
-          const int n_span = (E.cols + SPAN - 1) / SPAN;
+          const int cols = E.cols, rows = E.rows;
+          const int64_t row_bytes = E.row_bytes;
+          const uint8_t* w = E.w;
+          const int n_span = (cols + SPAN - 1) / SPAN;
           for (int span = 0; span < n_span; ++span) {
-            const int span_cols = min(SPAN, E.cols - span * SPAN);
+            const int span_cols = min(SPAN, cols - span * SPAN);
             const int nsub = (span_cols + gm.kseg - 1) / gm.kseg;
             for (int tile = t0; tile < t1; ++tile) {
               for (int sub = 0; sub < nsub; ++sub, ++c) {
@@ -204,14 +261,14 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
                   continue;
                 }
                 const int64_t seg_off = (int64_t)seg * gm.segb;
-                const int64_t left = E.row_bytes - seg_off;
+                const int64_t left = row_bytes - seg_off;
                 const uint32_t bytes = (uint32_t)(left < gm.segb ? left : gm.segb);
                 mbar_expect_tx(&full[stage], 16 * bytes);
-                const uint8_t* src = E.w + (int64_t)(tile * 16) * E.row_bytes + seg_off;
-                const int last = E.rows - 1 - tile * 16;  // rows beyond the matrix refetch the last one
+                const uint8_t* src = w + (int64_t)(tile * 16) * row_bytes + seg_off;
+                const int last = rows - 1 - tile * 16;  // rows beyond the matrix refetch the last one
 #pragma unroll 4
                 for (int r = 0; r < 16; ++r)
-                  bulk_g2s_hint(dst + r * gm.rs, src + (int64_t)min(r, last) * E.row_bytes, bytes, &full[stage], stream_once);
+                  bulk_g2s_hint(dst + r * gm.rs, src + (int64_t)min(r, last) * row_bytes, bytes, &full[stage], stream_once);
               }
             }
           }
@@ -227,6 +284,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
     // -------------------------------------------------------------- reducer
     int j = 0;  // tiles reduced by this CTA
     bool ok = true;
+    WaitCtx wc{err, counters ? counters + ABORT_SLOT : nullptr, epoch, wk.poll_limit, false};
     for (int ph = 0; ph < wk.n_phases; ++ph) {
       const ProgPhase P = wk.phases[ph];
       int lo, hi;
@@ -247,13 +305,32 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
 #pragma unroll
               for (int w = 0; w < CW; ++w) v += rp0[w * 16 * MT + idx];
               if (row < E.rows && k < E.tokens) {
-                float* yp = E.y + (int64_t)k * E.y_ld + row;
+                const int64_t at = (int64_t)k * E.y_ld + row;
+                float* yp = E.y + at;
                 if (span != 0) v += *yp;
+                if (span != n_span - 1) { *yp = v; continue; }
+                if (FLOW && E.resid) {  // residual add: result + residual, as the walk adds them (decode.rs:2938, :3050)
+                  if (E.resid_phase >= 0) {
+                    const uint2* rp = (const uint2*)E.resid + at;
+                    unsigned long long a = ld_pair<PEERS>(rp);
+                    if ((uint32_t)(a >> 32) != wk.tag_base + (uint32_t)E.resid_phase && !wc.dead) {
+                      poll_pair<PEERS>(rp, wk.tag_base + (uint32_t)E.resid_phase, wc);
+                      a = ld_pair<PEERS>(rp);
+                    }
+                    v = __fadd_rn(v, __uint_as_float((uint32_t)a));
+                  } else {
+                    v = __fadd_rn(v, ((const float*)E.resid)[at]);
+                  }
+                }
                 *yp = v;
-                if (HOSTOUT && span == n_span - 1) *(float*)((char*)yp + wk.host.y_delta) = v;
-                if (PEERS && span == n_span - 1) {
+                if (HOSTOUT) *(float*)((char*)yp + wk.host.y_delta) = v;
+                if (FLOW && E.yt) st_pair<false>((uint2*)E.yt + at, v, wk.tag_base + (uint32_t)ph);
+                if (PEERS) {
                   const int np = wk.peers->n_peers;
-                  for (int p = 0; p < np; ++p) *(float*)((char*)yp + wk.peers->y_delta[p]) = v;
+                  for (int p = 0; p < np; ++p) {
+                    *(float*)((char*)yp + wk.peers->y_delta[p]) = v;
+                    if (FLOW && E.yt) st_pair<true>((char*)((uint2*)E.yt + at) + wk.peers->y_delta[p], v, wk.tag_base + (uint32_t)ph);
+                  }
                 }
               }
             }
@@ -262,8 +339,8 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           }
         }
       }
-      if (PROGRAM) {
-        // this CTA's share of the phase is written: publish it
+      if (PROGRAM && (P.wait_prev & 2)) {
+        // this CTA's share of the phase is written and a later phase waits for the counter: publish it
         if (PEERS) {
           // One signal per rank and phase crosses NVLink, not one per CTA (hundreds of remote atomics
           // on one word serialise at tens of nanoseconds each): CTAs count locally, and the CTA
@@ -289,6 +366,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
             asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(counters + ph), "l"(1ull) : "memory");
         }
       }
+      LLR_STAMP(5);
     }
     if (HOSTOUT) {
       // this CTA's stores to host memory are performed; the CTA that counts last tells the host
@@ -311,44 +389,65 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
   const int g = lane >> 2, t = lane & 3;
   int c = 0, j = 0;
   bool ok = true;
-  const float* cur_x = nullptr;
-  int cur_cols = -1, cur_span = -1, cur_tokens = -1;
-  const uint64_t keep = l2_policy_evict_last();
+  __shared__ SplitKey s_key[CW];
+  if (lane == 0) s_key[warp] = SplitKey{nullptr, nullptr, -1, -1, -1, -1, -1, 0};
+  __syncwarp();
+  bool dead = false;  // a wait of this warp ran out, or another CTA said so: later waits return at once
   // Programs: the entries of a phase are fetched into shared memory before the dependency
   // wait, so that after the wait the consumers do not pay a global-memory round trip for them.
-  static_assert(sizeof(ProgEntry) == 64, "entry copy below moves eight 8-byte words per entry");
-  constexpr int ENT_CACHE = 4;
-  __shared__ unsigned long long s_ent[2][ENT_CACHE][8];
+  constexpr int ENT_CACHE = 4, ENT_WORDS = sizeof(ProgEntry) / 8;
+  __shared__ __align__(16) unsigned long long s_ent[2][ENT_CACHE][ENT_WORDS];
+  __shared__ float s_part[CW * 8], s_inv[8];
+  __shared__ __align__(16) ProgPhase s_phase[2];
+  // Programs: phase descriptors and the first entries of a phase reach shared memory one phase ahead
+  // (asynchronous copies issued by warp 0 while the previous phase is being computed), so that a new
+  // phase starts without a round trip to global memory for its own description.
+  auto prefetch_phase = [&](int q, int first_entry) {  // warp 0: phase q, whose entries start at first_entry
+    if (lane == 0) cp_async16(&s_phase[q & 1], wk.phases + q);
+    const int chunk = lane;  // 32 chunks of 16 bytes = ENT_CACHE entries of 128 bytes
+    if (first_entry + chunk / 8 < wk.n_entries)
+      cp_async16((char*)&s_ent[q & 1][0][0] + 16 * chunk, (const char*)(wk.entries + first_entry) + 16 * chunk);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  static_assert(ENT_CACHE * sizeof(ProgEntry) == 32 * 16, "one 16-byte chunk per lane");
+  if (PROGRAM && warp == 0) prefetch_phase(0, 0);
   for (int ph = 0; ph < wk.n_phases; ++ph) {
-    const ProgPhase P = wk.phases[ph];
+    LLR_STAMP(0);
+    if (PROGRAM) {
+      if (warp == 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
+      consumer_sync();  // publish the descriptor and the cached entries of this phase
+    }
+    LLR_STAMP(1);
+    const ProgPhase P = PROGRAM ? s_phase[ph & 1] : wk.phases[ph];
+    // everybody is in phase ph now: the buffers of phase ph - 1 are free for phase ph + 1
+    if (PROGRAM && warp == 0 && ph + 1 < wk.n_phases) prefetch_phase(ph + 1, P.first_entry + P.n_entries);
     int lo, hi;
     phase_range(P, bid, nb, &lo, &hi);
     const int n_cached = PROGRAM ? min(P.n_entries, ENT_CACHE) : 0;
-    if (PROGRAM && warp == 0) {
-      const unsigned long long* src = (const unsigned long long*)(wk.entries + P.first_entry);
-      if (lane < 8 * n_cached) s_ent[ph & 1][lane >> 3][lane & 7] = __ldg(src + lane);
-    }
-    if (PROGRAM) consumer_sync();  // publish the cached entries
-    // The dependency of the phase is awaited as late as possible: everything that does not need
-    // the activations (entry, geometry) is done first, so that the loads of the split are the
-    // first thing after the wait.  A CTA without tiles in the phase does not wait at all: the
-    // counters it waits for in its next phase imply this one.
-    // A sharded program also holds back the first phase of a run until every rank has finished
-    // the previous run (its peers' stores into this rank's buffers belong to that run).
-    bool waited = !(PROGRAM && ((P.wait_prev && ph > 0) || (PEERS && ph == 0)));
+    // Counter dependencies (strict phases with an input that is not a result of the program) are
+    // awaited as late as possible: everything that does not need the activations (entry, geometry)
+    // is done first, so that the loads of the split are the first thing after the wait.  A CTA
+    // without tiles in the phase does not wait at all: the counters it waits for in its next
+    // phase imply this one.  Tagged inputs need none of this: their loads are the wait.
+    // A sharded program with counters also holds back the first phase of a run until every rank
+    // has finished the previous run (its peers' stores into this rank's buffers belong to that run).
+    bool waited = !(PROGRAM && (((P.wait_prev & 1) && ph > 0) || (PEERS && ph == 0 && (P.wait_prev & 4))));
     for (int ei = 0; ei < P.n_entries && lo < hi; ++ei) {
-      ProgEntry E;
-      if (ei < n_cached) E = *(const ProgEntry*)&s_ent[ph & 1][ei][0];
-      else E = wk.entries[P.first_entry + ei];
+      const ProgEntry& Eref = ei < n_cached ? *(const ProgEntry*)&s_ent[ph & 1][ei][0] : wk.entries[P.first_entry + ei];
+      const ProgEntry E = Eref;  // a copy: fields stay in registers across the waits below (those clobber memory)
       int t0, t1;
       if (!entry_range(E, lo, hi, &t0, &t1)) continue;
       const Geom gm = geom_of(DTFIX >= 0 ? DTFIX : E.dtype);
       const int n_span = (E.cols + SPAN - 1) / SPAN;
+      const void* xkey = FLOW && E.xt ? E.xt : (const void*)E.x;
       for (int span = 0; span < n_span; ++span) {
         const int span_cols = min(SPAN, E.cols - span * SPAN), nblk256 = span_cols >> 8;
-        if (!waited || cur_x != E.x || cur_cols != E.cols || cur_span != span || cur_tokens != E.tokens) {
+        // (a buffer may be rewritten by a later phase: digit planes are never carried across phases)
+        const SplitKey have = s_key[warp];
+        if (!waited || have.x != xkey || have.cols != E.cols || have.span != span || have.tokens != E.tokens ||
+            (PROGRAM && have.ph != ph) || (FLOW && (have.op != E.x_op || have.x2 != E.x2))) {
           if (!waited) {
-            if (tid == 0) {
+            if (tid == 0 && !dead) {
               const unsigned long long runs = ph > 0 ? epoch : epoch - 1;
               const unsigned long long want = runs * (unsigned long long)nb;
               const int dep = ph > 0 ? ph - 1 : wk.n_phases - 1;
@@ -362,18 +461,37 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
                 asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(cp) : "memory");
                 if (PEERS) asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(u) : "l"(pp) : "memory");
                 if (v >= want && (!PEERS || u >= want_peers)) break;
-                if (++polls > POLL_LIMIT) { report_error(err, 2); break; }
+                if ((polls & 15) == 15 && ld_pair<false>(counters + ABORT_SLOT) == epoch) break;
+                if (++polls > wk.poll_limit) {
+                  *(volatile unsigned long long*)(counters + ABORT_SLOT) = epoch;
+                  report_error(err, 2);
+                  break;
+                }
                 __nanosleep(polls < 8 ? 64 : 256);  // hundreds of CTAs poll one word: keep the L2 bank free for the adds
               }
             }
             consumer_sync();
             waited = true;
           }
+          LLR_STAMP(2);
           // the planes a warp overwrites are the ones it alone reads (see split_activations)
           __syncwarp();
-          split_activations<MT>(E.x, E.cols, span * SPAN, nblk256, E.tokens, dig, sxf, xsi, warp, lane, keep);
+          // the 1/rms of the row belongs to the whole row: computed when its first span is split
+          const bool need_rms = FLOW && E.x_op == XOP_RMSNORM && span == 0;
+          XSrc src{E.x, nullptr, nullptr, 0u, 0u, XOP_NONE, 0};
+          if (FLOW) {
+            src.xt = (const uint2*)E.xt;
+            src.x2 = E.x2;
+            src.tag = wk.tag_base + (uint32_t)E.x_phase;
+            src.tag2 = wk.tag_base + (uint32_t)E.x2_phase;
+            src.op = E.x_op;
+            src.x2_tagged = E.x2_phase >= 0;
+          }
+          dead = prepare_activations<MT, PEERS, FLOW>(src, E.cols, E.tokens, FLOW ? E.eps : 0.f, span, nblk256, need_rms, dig, sxf, xsi,
+                                                s_part, s_inv, WaitCtx{err, PROGRAM ? counters + ABORT_SLOT : nullptr, epoch, wk.poll_limit, dead});
+          LLR_STAMP(3);
+          if (lane == 0) s_key[warp] = SplitKey{xkey, FLOW ? E.x2 : nullptr, E.cols, span, E.tokens, FLOW ? E.x_op : 0, ph, 0};
           __syncwarp();
-          cur_x = E.x; cur_cols = E.cols; cur_span = span; cur_tokens = E.tokens;
         }
         const int nsub = (span_cols + gm.kseg - 1) / gm.kseg;
         for (int tile = t0; tile < t1; ++tile, ++j) {
@@ -444,6 +562,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
         }
       }
     }
+    LLR_STAMP(4);
   }
 }
 
@@ -455,7 +574,7 @@ gemv_stream_kernel(const __grid_constant__ ProgEntry one, const __grid_constant_
   __shared__ ProgPhase phase;
   if (threadIdx.x == 0) phase = ProgPhase{0, 1, one.n_tiles, 0};
   __syncthreads();
-  Work wk{&one, &phase, 1, nullptr, HostOut{}, &map};
+  Work wk{&one, &phase, 1, nullptr, HostOut{}, &map, 1, 0u, 0};
   stream_body<MT, false, DT>(wk, nullptr, 0ull, err);
 }
 
@@ -466,26 +585,39 @@ gemv_stream_hostout_kernel(const __grid_constant__ ProgEntry one, const __grid_c
   __shared__ ProgPhase phase;
   if (threadIdx.x == 0) phase = ProgPhase{0, 1, one.n_tiles, 0};
   __syncthreads();
-  Work wk{&one, &phase, 1, nullptr, ho, &map};
+  Work wk{&one, &phase, 1, nullptr, ho, &map, 1, 0u, 0};
   stream_body<MT, false, DT, false, true>(wk, nullptr, 0ull, err);
 }
 
-template <int MT>
-__global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
+// What changes from run to run of a program.
+struct RunArgs {
+  unsigned long long epoch;     // runs of this program so far, this one included (what the counters count in)
+  unsigned long long tag_next;  // first tag after this run's
+  uint32_t tag_base;
+  int poll_limit;
+  int n_entries;
+};
+
+// (FLOW kernels keep sixteen tagged pairs per lane in flight and carry the element-wise operations: they do not
+// fit the 96 registers of two CTAs per SM without spilling into the block routines, so they run one CTA per SM.)
+template <int MT, bool FLOW>
+__global__ void __launch_bounds__(NTHREADS, (MT <= 2 && !FLOW ? 2 : 1))
 gemv_program_kernel(const ProgEntry* __restrict__ entries, const ProgPhase* __restrict__ phases, int n_phases,
                     const CUtensorMap* __restrict__ maps, unsigned long long* __restrict__ counters,
-                    unsigned long long epoch, int* __restrict__ err) {
-  Work wk{entries, phases, n_phases, nullptr, HostOut{}, maps};
-  stream_body<MT, true, -1>(wk, counters, epoch, err);
+                    const RunArgs run, int* __restrict__ err) {
+  Work wk{entries, phases, n_phases, nullptr, HostOut{}, maps, run.n_entries, run.tag_base, run.poll_limit};
+  if (blockIdx.x == 0 && threadIdx.x == 0) counters[TAG_SLOT] = run.tag_next;
+  stream_body<MT, true, -1, false, false, FLOW>(wk, counters, run.epoch, err);
 }
 
-template <int MT>
-__global__ void __launch_bounds__(NTHREADS, (MT <= 2 ? 2 : 1))
+template <int MT, bool FLOW>
+__global__ void __launch_bounds__(NTHREADS, (MT <= 2 && !FLOW ? 2 : 1))
 gemv_sharded_program_kernel(const ProgEntry* __restrict__ entries, const ProgPhase* __restrict__ phases, int n_phases,
                             const CUtensorMap* __restrict__ maps, unsigned long long* __restrict__ counters,
-                            unsigned long long epoch, const PeerTable* __restrict__ peers, int* __restrict__ err) {
-  Work wk{entries, phases, n_phases, peers, HostOut{}, maps};
-  stream_body<MT, true, -1, true>(wk, counters, epoch, err);
+                            const RunArgs run, const PeerTable* __restrict__ peers, int* __restrict__ err) {
+  Work wk{entries, phases, n_phases, peers, HostOut{}, maps, run.n_entries, run.tag_base, run.poll_limit};
+  if (blockIdx.x == 0 && threadIdx.x == 0) counters[TAG_SLOT] = run.tag_next;
+  stream_body<MT, true, -1, true, false, FLOW>(wk, counters, run.epoch, err);
 }
 
 // Tensor map of one matrix for the stage loads (see Geom).  Q8_0 is copied row by row: its map
@@ -602,92 +734,219 @@ struct Program {
   ProgEntry* d_entries = nullptr;
   ProgPhase* d_phases = nullptr;
   CUtensorMap* d_maps = nullptr;  // one per entry
-  unsigned long long* d_counters = nullptr;
-  int n_phases = 0, n_entries = 0, max_tokens = 1, grid = 0;
+  unsigned long long* d_counters = nullptr;  // COUNTER_WORDS words: phase counters, epoch and abort slots
+  void* d_tagged = nullptr;       // tagged copies of the results later entries read (single GPU; sharded: in the arena)
+  int n_phases = 0, n_entries = 0, max_tokens = 1, grid = 0, counter_phases = 0;
+  bool flow = false;  // some entry reads tagged pairs, applies an operation or adds a residual
   unsigned long long epoch = 0;
+  unsigned long long tag_next = 1;  // tags are never reused, whatever programs ran on the same buffers before; 0 marks fresh memory
   PeerTable* d_peers = nullptr;   // sharded programs: the peer table, and the counters are not ours
   bool own_counters = true;
 };
 
 bool prog_entry_supported(const MatView& m) { return gemv_mma_supported(m); }
 
-template <int MT>
+template <int MT, bool FLOW>
 static cudaError_t prog_prepare(int sm_count, int* grid, bool sharded) {
   int bps = 0;
-  cudaError_t e = sharded ? occupancy(gemv_sharded_program_kernel<MT>, SLay<MT>::TOTAL, &bps)
-                          : occupancy(gemv_program_kernel<MT>, SLay<MT>::TOTAL, &bps);
+  cudaError_t e = sharded ? occupancy(gemv_sharded_program_kernel<MT, FLOW>, SLay<MT>::TOTAL, &bps)
+                          : occupancy(gemv_program_kernel<MT, FLOW>, SLay<MT>::TOTAL, &bps);
   if (e != cudaSuccess) return e;
+  if (FLOW) bps = 1;  // see the kernels' launch bounds
   *grid = sm_count * bps;
   return cudaSuccess;
 }
 
-template <int MT>
-static cudaError_t prog_launch(Program* p, cudaStream_t stream, int* err) {
-  auto kern = gemv_program_kernel<MT>;
+template <int MT, bool FLOW>
+static cudaError_t prog_launch(Program* p, cudaStream_t stream, int* err, int poll_limit) {
+  auto kern = gemv_program_kernel<MT, FLOW>;
   ++p->epoch;
   const ProgEntry* de = p->d_entries;
   const ProgPhase* dp = p->d_phases;
   int np = p->n_phases;
   const CUtensorMap* dm = p->d_maps;
   unsigned long long* dc = p->d_counters;
-  unsigned long long ep = p->epoch;
-  // cooperative: every CTA must be resident, the phase counters are a grid-wide dependency
+  // tags of a run: tag_base + phase (32 bits of a counter that only grows; a tag would have to survive
+  // 2^32 / phases runs in a buffer that every run rewrites to be mistaken for a new one)
+  if ((uint32_t)p->tag_next > 0xffffffffu - (uint32_t)p->n_phases) p->tag_next += 2ull * (unsigned long long)p->n_phases;  // skip the wrap through 0
+  RunArgs run{p->epoch, p->tag_next + (unsigned long long)p->n_phases, (uint32_t)p->tag_next, poll_limit, p->n_entries};
+  p->tag_next = run.tag_next;
+  cudaError_t e;
+  // cooperative: every CTA must be resident, the waits between phases are grid-wide dependencies
   if (p->d_peers) {
     const PeerTable* pt = p->d_peers;
-    void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dm, (void*)&dc, (void*)&ep, (void*)&pt, (void*)&err};
-    return cudaLaunchCooperativeKernel((const void*)gemv_sharded_program_kernel<MT>, dim3((unsigned)p->grid),
-                                       dim3(NTHREADS), args, SLay<MT>::TOTAL, stream);
+    void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dm, (void*)&dc, (void*)&run, (void*)&pt, (void*)&err};
+    e = cudaLaunchCooperativeKernel((const void*)gemv_sharded_program_kernel<MT, FLOW>, dim3((unsigned)p->grid),
+                                    dim3(NTHREADS), args, SLay<MT>::TOTAL, stream);
+  } else {
+    void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dm, (void*)&dc, (void*)&run, (void*)&err};
+    e = cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)p->grid), dim3(NTHREADS), args,
+                                    SLay<MT>::TOTAL, stream);
   }
-  void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dm, (void*)&dc, (void*)&ep, (void*)&err};
-  return cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)p->grid), dim3(NTHREADS), args,
-                                     SLay<MT>::TOTAL, stream);
+  if (e != cudaSuccess) {  // nothing ran: counters, tags and the peers stay where they were
+    --p->epoch;
+    p->tag_next -= (unsigned long long)p->n_phases;
+  }
+  return e;
 }
 
-static cudaError_t program_build(const std::vector<ProgEntry>& entries_in, const std::vector<int>& phase_of,
-                                 int sm_count, unsigned long long* shared_counters, const PeerTable* peers,
-                                 Program** out, std::string* msg) {
+namespace {
+// A result of the program as later entries can address it: the full-width vector (all ranks' rows).
+struct Produced {
+  const char* base;   // address of row 0, activation row 0
+  int64_t ld;         // floats per activation row
+  int tokens, phase;
+  size_t tagged_off;  // single GPU: byte offset of its tagged copy in Program::d_tagged (SIZE_MAX: none yet)
+  bool addressable;   // sharded: ld == world * rows, so the slice's place in the full vector is known
+  bool consumed;      // a later entry reads it
+};
+}  // namespace
+
+cudaError_t program_create(const std::vector<ProgEntry>& entries_in, const std::vector<int>& phase_of,
+                           int sm_count, bool strict_phases, const ShardInfo* shard, Program** out, std::string* msg) {
   Program* p = new (std::nothrow) Program();
   if (!p) return cudaErrorMemoryAllocation;
   std::vector<ProgEntry> entries = entries_in;
   std::vector<ProgPhase> phases;
   std::vector<CUtensorMap> maps(entries.size());
+  std::vector<Produced> made(entries.size());
+  std::vector<int> phase_idx(entries.size());
+  const int world = shard ? shard->world : 1, rank = shard ? shard->rank : 0;
+  size_t tagged_bytes = 0;
+  auto fail = [&](const char* m, cudaError_t e) {
+    if (msg) *msg = m;
+    delete p;
+    return e;
+  };
+  // sharded: the tagged pair of the float at arena address a
+  auto arena_tagged = [&](const char* a) -> char* {
+    const char* res0 = shard->arena + LLR_ARENA_HEADER_BYTES_INTERNAL;
+    return shard->arena + LLR_ARENA_HEADER_BYTES_INTERNAL + shard->result_bytes + 2 * (a - res0);
+  };
   for (size_t i = 0; i < entries.size(); ++i) {
     ProgEntry& E = entries[i];
-    if (!encode_weight_map(E.w, E.dtype, E.rows, E.cols, E.row_bytes, &maps[i])) {
-      if (msg) *msg = "tensor map of an entry could not be encoded";
-      delete p;
-      return cudaErrorNotSupported;
-    }
+    if (!encode_weight_map(E.w, E.dtype, E.rows, E.cols, E.row_bytes, &maps[i]))
+      return fail("tensor map of an entry could not be encoded", cudaErrorNotSupported);
     E.n_tiles = (E.rows + 15) / 16;
     if (E.y_ld == 0) E.y_ld = E.rows;
-    if (i == 0 || phase_of[i] != phase_of[i - 1]) phases.push_back(ProgPhase{(int)i, 0, 0, i == 0 ? 0 : 1});
+    if (i == 0 || phase_of[i] != phase_of[i - 1]) phases.push_back(ProgPhase{(int)i, 0, 0, 0});
     ProgPhase& P = phases.back();
+    const int ph = (int)phases.size() - 1;
+    phase_idx[i] = ph;
     E.tile_begin = P.n_tiles;
     P.n_tiles += E.n_tiles;
     ++P.n_entries;
     if (E.tokens > p->max_tokens) p->max_tokens = E.tokens;
+    const bool addressable = world == 1 || E.y_ld == (int64_t)world * E.rows;
+    const int64_t row0 = world == 1 ? 0 : (int64_t)rank * E.rows;
+    made[i] = Produced{(const char*)E.y - 4 * row0, E.y_ld, E.tokens, ph, SIZE_MAX, addressable, false};
+    // Resolve each input: the latest earlier-phase result that contains it becomes a tagged source.
+    // width floats per activation row are read starting at ptr.
+    auto resolve = [&](const void* ptr, int64_t width, int* src_phase) -> const void* {
+      *src_phase = -1;
+      if (!ptr) return nullptr;
+      if (strict_phases) return ptr;  // strict programs synchronise phase by phase; their results travel as plain floats
+      for (size_t j = i; j-- > 0;) {
+        Produced& Q = made[j];
+        if (Q.phase >= ph || !Q.addressable || Q.tokens != E.tokens) continue;
+        const char* c = (const char*)ptr;
+        const bool whole = c == Q.base && width == Q.ld;
+        const bool part = E.tokens == 1 && c >= Q.base && c + 4 * width <= Q.base + 4 * Q.ld && (c - Q.base) % 16 == 0;
+        if (!whole && !part) continue;
+        *src_phase = Q.phase;
+        Q.consumed = true;
+        if (shard) return arena_tagged(c);
+        if (Q.tagged_off == SIZE_MAX) {
+          Q.tagged_off = tagged_bytes;
+          tagged_bytes += ((size_t)Q.tokens * (size_t)Q.ld * 8 + 255) & ~(size_t)255;
+        }
+        return (const void*)(uintptr_t)(Q.tagged_off + 2 * (size_t)(c - Q.base) + 1);  // offset + 1, rebased below
+      }
+      return ptr;
+    };
+    bool unresolved = false;
+    int sp = -1;
+    const void* r = resolve(E.x, E.cols, &sp);
+    E.x_phase = sp;
+    E.xt = sp >= 0 ? r : nullptr;
+    unresolved = unresolved || sp < 0;
+    if (E.x_op == XOP_SWIGLU) {
+      if (!E.x2) return fail("a SwiGLU entry needs its second input", cudaErrorInvalidValue);
+      E.x2 = resolve(E.x2, E.cols, &sp);
+      E.x2_phase = sp;
+      unresolved = unresolved || sp < 0;
+    } else {
+      E.x2_phase = -1;
+    }
+    if (E.resid) {
+      const void* rr = resolve(E.resid, E.y_ld, &sp);
+      E.resid_phase = sp;
+      // indexed like y: this rank's slice
+      if (sp >= 0) E.resid = shard ? (const void*)((const char*)rr + 8 * row0) : (const void*)((uintptr_t)rr + 8 * (size_t)row0);
+      else E.resid = (const char*)E.resid + 4 * row0;
+      unresolved = unresolved || sp < 0;
+    } else {
+      E.resid_phase = -1;
+    }
+    if (strict_phases && unresolved && ph > 0) P.wait_prev |= 1;
+    if (E.x_phase >= 0 || E.x2_phase >= 0 || E.resid_phase >= 0 || E.x_op != XOP_NONE || E.resid) p->flow = true;
+  }
+  for (size_t k = 0; k < phases.size(); ++k) p->counter_phases += phases[k].wait_prev & 1;
+  if (p->counter_phases > 0) {
+    // a counter phase needs its predecessor's count, and a sharded run must not overtake its predecessor:
+    // every phase publishes (the grid is the same in every phase, so the counts stay in step)
+    for (size_t k = 0; k < phases.size(); ++k) phases[k].wait_prev |= 2;
+    if (shard) phases[0].wait_prev |= 4;
   }
   p->n_phases = (int)phases.size();
   p->n_entries = (int)entries.size();
   cudaError_t e;
   const int mt = p->max_tokens;
-  const bool sharded = peers != nullptr;
-  if (mt == 1) e = prog_prepare<1>(sm_count, &p->grid, sharded);
-  else if (mt == 2) e = prog_prepare<2>(sm_count, &p->grid, sharded);
-  else if (mt <= 4) e = prog_prepare<4>(sm_count, &p->grid, sharded);
-  else e = prog_prepare<8>(sm_count, &p->grid, sharded);
+  const bool sharded = shard != nullptr;
+#define LLR_PREP(MT) (p->flow ? prog_prepare<MT, true>(sm_count, &p->grid, sharded) : prog_prepare<MT, false>(sm_count, &p->grid, sharded))
+  if (mt == 1) e = LLR_PREP(1);
+  else if (mt == 2) e = LLR_PREP(2);
+  else if (mt <= 4) e = LLR_PREP(4);
+  else e = LLR_PREP(8);
+#undef LLR_PREP
+  if (e == cudaSuccess && !sharded && tagged_bytes > 0) {
+    e = cudaMalloc(&p->d_tagged, tagged_bytes);
+    if (e == cudaSuccess) e = cudaMemset(p->d_tagged, 0, tagged_bytes);
+  }
+  // tagged addresses: single GPU offsets become pointers; producers learn where their tagged copy goes
+  for (size_t i = 0; i < entries.size() && e == cudaSuccess; ++i) {
+    ProgEntry& E = entries[i];
+    if (!sharded) {
+      auto rebase = [&](const void* v) { return (const void*)((char*)p->d_tagged + ((uintptr_t)v - 1)); };
+      if (E.x_phase >= 0) E.xt = rebase(E.xt);
+      if (E.x2_phase >= 0) E.x2 = rebase(E.x2);
+      if (E.resid_phase >= 0) E.resid = rebase(E.resid);
+      E.yt = made[i].tagged_off == SIZE_MAX ? nullptr : (char*)p->d_tagged + made[i].tagged_off;
+    } else {
+      // every rank creates the same program, so what is read here is read on the peers too
+      E.yt = made[i].consumed ? (void*)arena_tagged((const char*)E.y) : nullptr;
+    }
+  }
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_entries, entries.size() * sizeof(ProgEntry));
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_phases, phases.size() * sizeof(ProgPhase));
   if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_maps, maps.size() * sizeof(CUtensorMap));
   if (e == cudaSuccess) e = cudaMemcpy(p->d_maps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
   if (sharded) {
     p->own_counters = false;
-    p->d_counters = shared_counters;  // zeroed by whoever allocated them, before any rank runs
+    p->d_counters = shard->counters;  // zeroed by whoever allocated the arena, before any rank runs
     if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_peers, sizeof(PeerTable));
-    if (e == cudaSuccess) e = cudaMemcpy(p->d_peers, peers, sizeof(PeerTable), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(p->d_peers, &shard->peers, sizeof(PeerTable), cudaMemcpyHostToDevice);
+    // An arena that served an earlier program carries that program's counts and tags: the tags go on
+    // from where it stopped and the counters start from zero again, so that neither a stale tag nor a
+    // stale count can pass for a new one.  (No rank may still be running a program on these arenas.)
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpy(&p->tag_next, shard->counters + TAG_SLOT, sizeof(p->tag_next), cudaMemcpyDeviceToHost);
+    if (p->tag_next == 0) p->tag_next = 1;
+    if (e == cudaSuccess) e = cudaMemset(shard->counters, 0, TAG_SLOT * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemset(shard->counters + PEER_COUNTER_OFFSET, 0, (COUNTER_WORDS - PEER_COUNTER_OFFSET) * sizeof(unsigned long long));
   } else {
-    if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_counters, phases.size() * sizeof(unsigned long long));
-    if (e == cudaSuccess) e = cudaMemset(p->d_counters, 0, phases.size() * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_counters, COUNTER_WORDS * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemset(p->d_counters, 0, COUNTER_WORDS * sizeof(unsigned long long));
   }
   if (e == cudaSuccess) e = cudaMemcpy(p->d_entries, entries.data(), entries.size() * sizeof(ProgEntry), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(p->d_phases, phases.data(), phases.size() * sizeof(ProgPhase), cudaMemcpyHostToDevice);
@@ -700,38 +959,32 @@ static cudaError_t program_build(const std::vector<ProgEntry>& entries_in, const
   return cudaSuccess;
 }
 
-cudaError_t program_create(const std::vector<ProgEntry>& entries, const std::vector<int>& phase_of,
-                           int sm_count, Program** out, std::string* msg) {
-  return program_build(entries, phase_of, sm_count, nullptr, nullptr, out, msg);
-}
-
-cudaError_t program_create_sharded(const std::vector<ProgEntry>& entries, const std::vector<int>& phase_of,
-                                   int sm_count, unsigned long long* counters, const PeerTable& peers,
-                                   Program** out, std::string* msg) {
-  return program_build(entries, phase_of, sm_count, counters, &peers, out, msg);
-}
-
 void program_destroy(Program* p) {
   if (!p) return;
   if (p->d_entries) cudaFree(p->d_entries);
   if (p->d_phases) cudaFree(p->d_phases);
   if (p->d_maps) cudaFree(p->d_maps);
   if (p->d_counters && p->own_counters) cudaFree(p->d_counters);
+  if (p->d_tagged) cudaFree(p->d_tagged);
   if (p->d_peers) cudaFree(p->d_peers);
   delete p;
 }
 
-cudaError_t program_run(Program* p, cudaStream_t stream, int* err_flag, uint64_t* launches) {
+cudaError_t program_run(Program* p, cudaStream_t stream, int* err_flag, int poll_limit, uint64_t* launches) {
   cudaError_t e;
   const int mt = p->max_tokens;
-  if (mt == 1) e = prog_launch<1>(p, stream, err_flag);
-  else if (mt == 2) e = prog_launch<2>(p, stream, err_flag);
-  else if (mt <= 4) e = prog_launch<4>(p, stream, err_flag);
-  else e = prog_launch<8>(p, stream, err_flag);
+#define LLR_RUN(MT) (p->flow ? prog_launch<MT, true>(p, stream, err_flag, poll_limit) : prog_launch<MT, false>(p, stream, err_flag, poll_limit))
+  if (mt == 1) e = LLR_RUN(1);
+  else if (mt == 2) e = LLR_RUN(2);
+  else if (mt <= 4) e = LLR_RUN(4);
+  else e = LLR_RUN(8);
+#undef LLR_RUN
   if (e == cudaSuccess && launches) ++*launches;
   return e;
 }
 
+int program_counter_phases(const Program* p) { return p->counter_phases; }
+int program_grid(const Program* p) { return p->grid; }
 int program_phases(const Program* p) { return p->n_phases; }
 int program_entries(const Program* p) { return p->n_entries; }
 

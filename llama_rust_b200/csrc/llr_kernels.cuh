@@ -67,40 +67,72 @@ bool gemv_mma_hostout_ok(const MatView& m, int64_t tokens);
 cudaError_t launch_gemv_mma_hostout(const MatView& m, const float* x, float* y, int64_t tokens, const HostOut& ho,
                                     cudaStream_t stream, int sm_count, int* err_flag, uint64_t* launches);
 
-// One matrix product of a program (llr_gemv_stream.cu).  tile_begin / n_tiles are filled in
-// by program_create.
+// One matrix product of a program (llr_gemv_stream.cu).  The caller fills the first block and the
+// operation fields; tile_begin / n_tiles and everything about tagged buffers are filled in by
+// program_create.
+//
+// Tagged buffers.  A result that a later entry of the same program reads is also written as 8-byte
+// pairs {f32 bits, tag}, tag = tag_base of the run + producing phase.  A consumer loads pairs and
+// spins (bounded) until every tag is the expected one: the value is its own arrival signal, so no
+// counter, fence or poll separates a phase from the next.
+enum XOp : int {
+  XOP_NONE = 0,     // x as it is
+  XOP_RMSNORM = 1,  // x * (1 / sqrt(mean(x^2) + eps)) * x2[c]   (x2: norm weights, plain f32, may be null)
+  XOP_SWIGLU = 2,   // silu(x) * x2[c]                            (x2: the `up` vector)
+};
 struct ProgEntry {
   const uint8_t* w;
-  const float* x;
-  float* y;
+  const float* x;     // input, plain f32 (ignored by the kernel when xt is set)
+  float* y;           // result, plain f32 (this rank's slice)
   int64_t row_bytes;
   int rows, cols, dtype, tokens;
   int tile_begin, n_tiles;
   int64_t y_ld;  // floats between consecutive activation rows of y (0: rows); larger when y is a slice of a wider vector
+  // ---- 64 bytes
+  const void* xt;     // tagged input (pairs), or null
+  const void* x2;     // second operand of x_op: plain f32, or pairs when x2_phase >= 0
+  const void* resid;  // added to the finished result, indexed like y: plain f32, or pairs when resid_phase >= 0; may be null
+  void* yt;           // tagged copy of the result (this rank's slice), or null when no entry reads it
+  int x_op;
+  float eps;
+  int x_phase, x2_phase, resid_phase;  // phase that writes the tagged source (-1: plain memory, ready at launch)
+  int pad[3];
 };
+static_assert(sizeof(ProgEntry) == 128, "entries are copied as sixteen 8-byte words");
 // Row-sharded programs across GPUs: where the other ranks keep their copies of the results
-// and of the phase counters.  peer y address = local y address + y_delta[g] bytes.
+// and of the phase counters.  peer address = local address + delta[g] bytes (arenas have one layout).
 struct PeerTable {
   int n_peers;  // other ranks (world size - 1), at most 7
   int pad;
   unsigned long long* counters[7];
   long long y_delta[7];
 };
+// wait_prev: bit 0 = wait for the previous phase's counter, bit 1 = publish this phase's counter,
+// bit 2 (phase 0 of a sharded program) = wait for the end of the previous run on every rank.
 struct ProgPhase { int first_entry, n_entries, n_tiles, wait_prev; };
 struct Program;
 bool prog_entry_supported(const MatView& m);
-// phase_of[i] is non-decreasing; a change starts a phase that waits for the previous one
+// Placement of a sharded program's buffers: the arena is header | result area of result_bytes |
+// tagged area of 2 * result_bytes; the pair of the float at result offset o lies at tagged offset 2 o.
+struct ShardInfo {
+  unsigned long long* counters;  // arena header
+  PeerTable peers;
+  char* arena;
+  size_t result_bytes;
+  int world, rank;
+};
+// phase_of[i] is non-decreasing.  strict_phases: an input that is not an earlier entry's result makes
+// its phase wait until the previous phase is completely written (counter per phase); otherwise such
+// inputs are read as they are at launch.
 cudaError_t program_create(const std::vector<ProgEntry>& entries, const std::vector<int>& phase_of,
-                           int sm_count, Program** out, std::string* msg);
-// Same, for one rank of a row-sharded program: `counters` (one per phase, zeroed, in memory the
-// peers can write) replaces the program's own counter array, `peers` says where the others are.
-cudaError_t program_create_sharded(const std::vector<ProgEntry>& entries, const std::vector<int>& phase_of,
-                                   int sm_count, unsigned long long* counters, const PeerTable& peers,
-                                   Program** out, std::string* msg);
+                           int sm_count, bool strict_phases, const ShardInfo* shard, Program** out, std::string* msg);
 void program_destroy(Program* p);
-cudaError_t program_run(Program* p, cudaStream_t stream, int* err_flag, uint64_t* launches);
+// poll_limit: iterations a device-side wait for another CTA's or rank's data may take before it gives up
+cudaError_t program_run(Program* p, cudaStream_t stream, int* err_flag, int poll_limit, uint64_t* launches);
 int program_phases(const Program* p);
 int program_entries(const Program* p);
+int program_counter_phases(const Program* p);
+int program_grid(const Program* p);  // phases that synchronise through a counter
 
 // dequant -> shared memory -> tcgen05/TMEM chunk GEMM (bf16 operands, f32 accumulate) for
 // Q4_K / Q8_0 / Q5_0 / Q5_1 with many activation rows; see llr_gemm_tc.cu.

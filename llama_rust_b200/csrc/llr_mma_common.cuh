@@ -12,6 +12,7 @@
 // 2^24 (relative 2^-25), everything before it is exact.
 #pragma once
 #include "llr_formats.cuh"
+#include "llr_kernels.cuh"
 
 namespace llr {
 namespace mma {
@@ -89,6 +90,10 @@ __device__ __forceinline__ float4 ld_x_keep(const float4* p, uint64_t policy) {
   asm volatile("ld.global.cg.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p), "l"(policy) : "memory");
   return v;
+}
+// 16 bytes global -> shared, asynchronous (cp.async.commit_group / wait_group complete it); both addresses 16-byte aligned
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -324,37 +329,222 @@ __device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* ro
 }
 
 
+// ---- where activations come from ---------------------------------------------------------
+// Plain f32 memory that is ready when the launch starts, or tagged pairs {f32 bits, tag} that an
+// earlier phase of the same launch writes (on this GPU or, in a row-sharded program, on another):
+// a pair whose tag is the expected one carries a finished value, so loading it IS the wait.
+struct XSrc {
+  const float* x;     // plain input (used when xt is null)
+  const uint2* xt;    // tagged input
+  const void* x2;     // XOP_RMSNORM: norm weights (plain, may be null); XOP_SWIGLU: `up`, plain or tagged
+  uint32_t tag, tag2; // expected tags of xt / x2
+  int op;             // XOP_*
+  int x2_tagged;
+};
+// State of a warp's bounded waits on tagged data.  Once a wait has run out anywhere in the launch
+// (this warp: dead; another CTA: the abort word holds this run's epoch) later waits return at once,
+// so a launch that lost a producer finishes in about its normal time.
+struct WaitCtx {
+  int* err;
+  unsigned long long* abort_word;
+  unsigned long long epoch;
+  int limit;
+  bool dead;
+};
+template <bool SYS> __device__ __forceinline__ void ld_pairs2(const void* p, unsigned long long& a, unsigned long long& b) {
+  if (SYS) asm volatile("ld.relaxed.sys.global.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+  else asm volatile("ld.relaxed.gpu.global.v2.b64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+template <bool SYS> __device__ __forceinline__ unsigned long long ld_pair(const void* p) {
+  unsigned long long a;
+  if (SYS) asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+  else asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(a) : "l"(p) : "memory");
+  return a;
+}
+template <bool SYS> __device__ __forceinline__ void st_pair(void* p, float v, uint32_t tag) {
+  const unsigned long long a = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+  if (SYS) asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
+  else asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(a) : "memory");
+}
+// A wait on tagged data ran out, or another CTA's did: record it.  Returns true when the caller should stop waiting.
+__device__ __forceinline__ bool wait_step(int& polls, WaitCtx& wc) {
+  ++polls;
+  if ((polls & 15) == 0 && ld_pair<false>(wc.abort_word) == wc.epoch) { wc.dead = true; return true; }
+  if (polls > wc.limit) {
+    wc.dead = true;
+    *(volatile unsigned long long*)wc.abort_word = wc.epoch;
+    report_error(wc.err, 2);
+    return true;
+  }
+  __nanosleep(polls < 8 ? 32 : 128);
+  return false;
+}
+// One pair, polled until its tag arrives (the reducer's residual).
+template <bool SYS> __device__ __forceinline__ void poll_pair(const void* p, uint32_t want, WaitCtx& wc) {
+  int polls = 0;
+  while ((uint32_t)(ld_pair<SYS>(p) >> 32) != want)
+    if (wait_step(polls, wc)) return;
+}
+// Eight consecutive values per lane for NJ jobs at once (element offsets off[], inactive jobs
+// skipped) from tagged pairs: all loads of all jobs are in flight before any is used.  A lane whose
+// pairs do not all carry the expected tag yet loads them again after a short sleep, on its own (a
+// lane's eight values are neighbours in one result tile and arrive together; lanes of different
+// tiles need not wait for each other's round trips), until they do or the wait limit is reached.
+template <bool SYS, int NJ>
+__device__ __forceinline__ void load_tagged(const uint2* base, uint32_t want, const int64_t (&off)[NJ], const bool (&act)[NJ],
+                                            float (&v)[NJ][8], WaitCtx& wc) {
+  int polls = 0;
+  for (;;) {
+    bool late = false;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+      if (act[j]) {
+        unsigned long long a[8];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) ld_pairs2<SYS>(base + off[j] + 2 * q, a[2 * q], a[2 * q + 1]);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          v[j][q] = __uint_as_float((uint32_t)a[q]);
+          late = late || (uint32_t)(a[q] >> 32) != want;
+        }
+      }
+    if (!late || wc.dead || wait_step(polls, wc)) break;
+  }
+  __syncwarp();
+  wc.dead = __any_sync(~0u, wc.dead);
+}
+template <int NJ>
+__device__ __forceinline__ void load_plain(const float* base, const int64_t (&off)[NJ], const bool (&act)[NJ],
+                                           float (&v)[NJ][8], uint64_t keep) {
+#pragma unroll
+  for (int j = 0; j < NJ; ++j)
+    if (act[j]) {
+      const float4 pa = ld_x_keep((const float4*)(base + off[j]), keep), pb = ld_x_keep((const float4*)(base + off[j]) + 1, keep);
+      v[j][0] = pa.x; v[j][1] = pa.y; v[j][2] = pa.z; v[j][3] = pa.w;
+      v[j][4] = pb.x; v[j][5] = pb.y; v[j][6] = pb.z; v[j][7] = pb.w;
+    }
+}
+// The activations of NJ jobs with the entry's element-wise operation applied (XOP_SWIGLU; the
+// normalisation of XOP_RMSNORM is applied by the caller, which needs the row's sum of squares first).
+template <bool SYS, int NJ>
+__device__ __forceinline__ void fetch_jobs(const XSrc& s, const int64_t (&off)[NJ], const bool (&act)[NJ],
+                                           float (&v)[NJ][8], WaitCtx& wc, uint64_t keep) {
+  if (s.xt) load_tagged<SYS, NJ>(s.xt, s.tag, off, act, v, wc);
+  else load_plain<NJ>(s.x, off, act, v, keep);
+  if (s.op != XOP_SWIGLU) return;
+  // silu(g) * u as the reference computes it: g / (1 + exp(-g)), then the product (decode.rs:11826, :2984)
+#pragma unroll
+  for (int j = 0; j < NJ; ++j)
+    if (act[j]) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[j][q] = __fdiv_rn(v[j][q], 1.0f + expf(-v[j][q]));
+    }
+  float u[NJ][8];
+  if (s.x2_tagged) load_tagged<SYS, NJ>((const uint2*)s.x2, s.tag2, off, act, u, wc);
+  else load_plain<NJ>((const float*)s.x2, off, act, u, keep);
+#pragma unroll
+  for (int j = 0; j < NJ; ++j)
+    if (act[j]) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[j][q] = __fmul_rn(v[j][q], u[j][q]);
+    }
+}
+
+// Sum of squares of every activation row of an XOP_RMSNORM entry -> 1 / sqrt(mean + eps) per row
+// (rmsnorm_inplace, decode.rs:11498; the reference adds sequentially, here lanes, then warps, add
+// in a fixed order, so the value is reproducible but may differ from the sequential sum in the
+// last bits).  Called by all eight consumer warps; part is float[NWARP][8] and inv float[8] in
+// shared memory.  The second barrier also keeps a warp from writing its next partial sums while
+// another still adds up these.
+template <int MT, bool SYS>
+__device__ __forceinline__ void row_inv_rms(const XSrc& s, int cols, int tokens, float eps, float* part, float* inv,
+                                            int warp, int lane, WaitCtx& wc, uint64_t keep) {
+  const int nblk = cols >> 8;
+  float ss[MT];
+#pragma unroll
+  for (int k = 0; k < MT; ++k) ss[k] = 0.f;
+  XSrc raw = s;
+  raw.op = XOP_NONE;
+  for (int b0 = warp; b0 < nblk; b0 += 2 * NWARP)
+#pragma unroll
+    for (int k = 0; k < MT; ++k) {
+      if (k >= tokens) break;
+      const int64_t off[2] = {(int64_t)k * cols + b0 * 256 + 8 * lane, (int64_t)k * cols + (b0 + NWARP) * 256 + 8 * lane};
+      const bool act[2] = {true, b0 + NWARP < nblk};
+      float v[2][8];
+      fetch_jobs<SYS, 2>(raw, off, act, v, wc, keep);
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        if (act[j]) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) ss[k] = fmaf(v[j][q], v[j][q], ss[k]);
+        }
+    }
+  float* mine = part + warp * 8;
+#pragma unroll
+  for (int k = 0; k < MT; ++k) {
+    float t = ss[k];
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) t += __shfl_xor_sync(~0u, t, m);
+    if (lane == 0) mine[k] = t;
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(NWARP * 32) : "memory");
+  if (lane < tokens) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) t += part[w * 8 + lane];
+    const float rms = sqrtf(__fadd_rn(__fdiv_rn(t, (float)(cols <= 65535 ? cols : 1)), eps));
+    if (warp == 0) inv[lane] = rms > 0.f ? __fdiv_rn(1.0f, rms) : 0.f;
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(NWARP * 32) : "memory");
+}
+
 // Activations of one span (nblk256 blocks of 256 columns starting at column col0, `tokens`
 // activation rows) -> four int8 digit planes per activation row, the f32 sums of x per 32
-// columns (Q4_K mins) and 2^-e per block.  Loads are L2-coherent (the activations may have been
-// produced by an earlier phase of the same launch) and kept in L2 (policy `keep`).
+// columns (Q4_K mins) and 2^-e per block.  Plain loads are L2-coherent and kept in L2 (policy
+// `keep`); tagged loads wait for their values (see XSrc).
 // Warp w of the eight consumer warps splits the blocks b = w (mod 8) of every activation row, and
 // those are exactly the blocks whose planes, sums and scales it reads in the block routines: no
 // other warp depends on what it writes here, so a __syncwarp() is all the caller needs.
-template <int MT>
-__device__ __forceinline__ void split_activations(const float* __restrict__ X, int cols, int col0,
+template <int MT, bool SYS, bool FLOW>
+__device__ __forceinline__ void split_activations(const XSrc& src, int cols, int col0,
                                                   int nblk256, int tokens, uint8_t* dig, float* sxf,
-                                                  float* xsi, int warp, int lane, uint64_t keep) {
+                                                  float* xsi, const float* inv, int warp, int lane, WaitCtx& wc, uint64_t keep) {
   // two jobs per pass: both loads are in flight before either is used.  One activation row: blocks
   // b0 and b0 + 8; several: rows tok0 and tok0 + 1 of block b0.
   for (int b0 = warp; b0 < nblk256; b0 += (MT == 1 ? 2 * NWARP : NWARP))
   for (int tok0 = 0; tok0 < tokens; tok0 += (MT == 1 ? 1 : 2)) {
-   float4 pa[2], pb[2];
+   float vv[2][8];
+   int64_t off[2];
+   bool act[2];
 #pragma unroll
    for (int u = 0; u < 2; ++u) {
     const int jb = MT == 1 ? b0 + u * NWARP : b0, jt = MT == 1 ? 0 : tok0 + u;
-    if (MT == 1 ? jb < nblk256 : jt < tokens) {
-      const float4* xp = (const float4*)(X + (int64_t)jt * cols + col0 + jb * 256 + 8 * lane);
-      pa[u] = ld_x_keep(xp, keep);
-      pb[u] = ld_x_keep(xp + 1, keep);
-    }
+    act[u] = MT == 1 ? jb < nblk256 : jt < tokens;
+    off[u] = (int64_t)jt * cols + col0 + jb * 256 + 8 * lane;
    }
+   if (FLOW) fetch_jobs<SYS, 2>(src, off, act, vv, wc, keep);
+   else load_plain<2>(src.x, off, act, vv, keep);
 #pragma unroll
    for (int u = 0; u < 2; ++u) {
     const int b = MT == 1 ? b0 + u * NWARP : b0, tok = MT == 1 ? 0 : tok0 + u;
-    if (MT == 1 ? b >= nblk256 : tok >= tokens) break;
-    const float4 va = pa[u], vb = pb[u];
-    const float v[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+    if (!act[u]) break;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = vv[u][j];
+    if (FLOW && src.op == XOP_RMSNORM) {  // (x * inv) * w, two roundings as in the reference
+      const float r = inv[tok];
+      if (src.x2) {
+        const float4 wa = __ldg((const float4*)((const float*)src.x2 + col0 + b * 256 + 8 * lane));
+        const float4 wb = __ldg((const float4*)((const float*)src.x2 + col0 + b * 256 + 8 * lane) + 1);
+        const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(__fmul_rn(v[j], r), wv[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(v[j], r);
+      }
+    }
     // Largest magnitude of the block as a bit pattern: for non-negative floats the unsigned order of
     // the bits is the numeric order, infinities and NaNs sort above every finite value, and one
     // redux.sync replaces a five-step shuffle reduction on the latency-critical start of a phase.

@@ -20,6 +20,7 @@ DTYPES = {"F16": F16, "BF16": BF16, "F32": F32, "Q5_0": Q5_0, "Q5_1": Q5_1, "Q4_
           "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K}
 OK, ERR_INVALID, ERR_UNALIGNED, ERR_DTYPE, ERR_OVERFLOW, ERR_FOREIGN, ERR_CUDA, ERR_OOM, ERR_CONFIG = range(9)
 PATH_AUTO, PATH_GENERIC, PATH_STAGED, PATH_MMA, PATH_TC = 0, 1, 2, 3, 4
+XOP_NONE, XOP_RMSNORM, XOP_SWIGLU = 0, 1, 2
 
 _cdll = None
 
@@ -87,6 +88,12 @@ class Program:
 
     def run(self, stream: int = 0) -> None:
         self._exec._check(lib().llr_program_run(self._exec._h, self._h, stream))
+
+    def info(self) -> dict:
+        """entries, phases, and how many phases synchronise through a counter instead of tagged results."""
+        a, b, c, d = C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint32()
+        self._exec._check(lib().llr_program_info(self._h, C.byref(a), C.byref(b), C.byref(c), C.byref(d)))
+        return {"entries": a.value, "phases": b.value, "counter_phases": c.value, "ctas": d.value}
 
     def free(self) -> None:
         if self._h:
@@ -183,6 +190,28 @@ class Executor:
         h = C.c_void_p()
         self._check(lib().llr_program_create(self._h, arr, len(entries), C.byref(h)))
         return Program(self, h.value, len(entries))
+
+    def program_ops(self, ops, shard=None) -> Program:
+        """ops: iterable of dicts with keys matrix, x, y, tokens, phase and optionally x2, resid, y_ld, x_op, eps
+        (llr_program_op).  shard: None, or (arena, arena_bytes, world, rank, peer_arenas) for one rank of a
+        row-sharded program."""
+        ops = list(ops)
+        arr = (_lib.ProgramOp * len(ops))()
+        for i, o in enumerate(ops):
+            arr[i] = _lib.ProgramOp(o["matrix"]._h, o["x"], o.get("x2") or None, o.get("resid") or None, o["y"],
+                                    int(o.get("y_ld", 0)), o["tokens"], o["phase"], int(o.get("x_op", 0)),
+                                    float(o.get("eps", 0.0)))
+        h = C.c_void_p()
+        sh = None
+        if shard is not None:
+            arena, arena_bytes, world, rank, peer_arenas = shard
+            peers = (C.c_void_p * world)(*[int(p) if p else None for p in peer_arenas])
+            sh = C.byref(_lib.ProgramShard(arena, arena_bytes, world, rank, peers))
+        self._check(lib().llr_program_create_ops(self._h, arr, len(ops), sh, C.byref(h)))
+        return Program(self, h.value, len(ops))
+
+    def set_wait_limit(self, polls: int) -> None:
+        self._check(lib().llr_exec_set_wait_limit(self._h, polls))
 
     # -- row-sharded programs across GPUs (llr_shared_*, llr_program_create_sharded) ----
     def shared_alloc(self, nbytes: int) -> tuple[int, bytes]:

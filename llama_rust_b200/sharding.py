@@ -137,44 +137,58 @@ class ExpertParallelFFN:
 
 def arena_layout(row_counts: Sequence[int], tokens: int = 1) -> tuple[list[int], int]:
     """Byte offsets of the full-width result buffers inside a rank's arena (behind the library's
-    header, 256-byte aligned) and the arena size.  Identical on every rank."""
+    header, 256-byte aligned) and the arena size: header | results | twice as much for the tagged
+    copies of the results (see llr_program_create_sharded).  Identical on every rank."""
     from ._lib import ARENA_HEADER_BYTES
     offs, cur = [], ARENA_HEADER_BYTES
     for rows in row_counts:
         offs.append(cur)
         cur += (4 * rows * tokens + 255) // 256 * 256
-    return offs, cur
+    return offs, ARENA_HEADER_BYTES + 3 * (cur - ARENA_HEADER_BYTES)
 
 
 class ShardedDecodeProgram:
     """One decode step of row-sharded products as a single launch per rank.
 
-    specs: list of (shard_matrix, x, full_rows, phase) in execution order; shard_matrix is this
-    rank's resident row slice (rows = full_rows / world); x is a device address, or a callable
-    taking the arena's base address (for an input that is an earlier result: arena + its offset
-    from arena_layout).  Result i lives full width in every
-    rank's arena at `self.y_ptr(i)`; after `run()` + a device synchronize on EVERY rank and a host
-    barrier it holds the complete vector on every rank."""
+    specs: list of (shard_matrix, x, full_rows, phase) or dicts with those keys plus the optional
+    x2, resid, x_op, eps of llr_program_op, in execution order; shard_matrix is this rank's resident
+    row slice (rows = full_rows / world); x (x2, resid) is a device address, or a callable taking the
+    arena's base address (for an input that is an earlier result: arena + its offset from
+    arena_layout).  Tuples create a program with strict phases, dicts one whose inputs are either
+    results of the program or ready at launch.  Result i lives full width in every rank's arena at
+    `self.y_ptr(i)`; after `run()` + a device synchronize on EVERY rank and a host barrier it holds
+    the complete vector on every rank."""
 
     def __init__(self, ex, specs, tokens: int = 1, group=None):
         self.ex, self.group = ex, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        self.offsets, self.arena_bytes = arena_layout([s[2] for s in specs], tokens)
+        as_ops = len(specs) > 0 and isinstance(specs[0], dict)
+        if not as_ops:
+            specs = [dict(matrix=m, x=x, full_rows=r, phase=p) for m, x, r, p in specs]
+        self.offsets, self.arena_bytes = arena_layout([s["full_rows"] for s in specs], tokens)
         self.arena, handle = ex.shared_alloc(self.arena_bytes)
         handles = [None] * self.world
         dist.all_gather_object(handles, handle, group=group)
         self.peers = [None if g == self.rank else ex.shared_open(handles[g]) for g in range(self.world)]
-        entries, y_ld = [], []
-        for (mat, x_ptr, full_rows, phase), off in zip(specs, self.offsets):
+
+        def addr(v):
+            return v(self.arena) if callable(v) else v
+        ops = []
+        for s, off in zip(specs, self.offsets):
+            mat, full_rows = s["matrix"], s["full_rows"]
             r0, r1 = row_range(full_rows, self.world, self.rank)
             if r1 - r0 != mat.rows:
                 raise ValueError(f"shard has {mat.rows} rows, rank {self.rank} of {self.world} owns {r1 - r0} of {full_rows}")
-            if callable(x_ptr):
-                x_ptr = x_ptr(self.arena)
-            entries.append((mat, x_ptr, self.arena + off + 4 * r0, tokens, phase))
-            y_ld.append(full_rows)
-        self.program = ex.sharded_program(entries, y_ld, self.arena, self.arena_bytes, self.world, self.rank, self.peers)
-        dist.barrier(group=group)  # every rank has opened every arena before anybody runs
+            ops.append(dict(matrix=mat, x=addr(s["x"]), x2=addr(s.get("x2")), resid=addr(s.get("resid")),
+                            y=self.arena + off + 4 * r0, y_ld=full_rows, tokens=tokens, phase=s["phase"],
+                            x_op=s.get("x_op", 0), eps=s.get("eps", 0.0)))
+        if as_ops:
+            self.program = ex.program_ops(ops, (self.arena, self.arena_bytes, self.world, self.rank, self.peers))
+        else:
+            self.program = ex.sharded_program([(o["matrix"], o["x"], o["y"], tokens, o["phase"]) for o in ops],
+                                              [o["y_ld"] for o in ops], self.arena, self.arena_bytes, self.world,
+                                              self.rank, self.peers)
+        dist.barrier(group=group)  # every rank has opened every arena and created its program before anybody runs
 
     def y_ptr(self, i: int) -> int:
         return self.arena + self.offsets[i]

@@ -301,6 +301,20 @@ def moe_ffn(n_used: int, norm_w: bool, router_kind: int, router, expert_kind: in
     return out, ids, w
 
 
+def rmsnorm(x, w, eps: float) -> np.ndarray:
+    """rmsnorm_inplace (langtax/src/decode.rs:11498) on a copy of one activation row."""
+    out = np.array(x, dtype=np.float32).reshape(-1).copy()
+    wv = _f32(w)
+    lib.orc_rmsnorm(_p(out), _p(wv), out.size, eps)
+    return out
+
+
+def silu(x) -> np.ndarray:
+    """silu_inplace (decode.rs:11826), element by element."""
+    v = _f32(x)
+    return np.array([lib.orc_silu(float(a)) for a in v], dtype=np.float32)
+
+
 def ref_q8_gemv_binary() -> str | None:
     """Path of the reference's own q8_gemv.c compiled unmodified, if it was built."""
     p = os.path.join(_HERE, "_ref", "q8_gemv_ref")

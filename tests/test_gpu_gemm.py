@@ -104,7 +104,7 @@ def test_operand_format_follows_weight_range(ex, orc):
 
 @pytest.mark.parametrize("name,rows,cols", [("Q4_K", 14336, 4096), ("Q8_0", 4096, 14336), ("Q5_0", 4096, 4096),
                                             ("Q5_1", 4096, 4096)])
-@pytest.mark.parametrize("tokens", [64, 1024])
+@pytest.mark.parametrize("tokens", [64, 256, 1024])
 def test_config4_full_size_shapes_on_sampled_rows(ex, orc, name, rows, cols, tokens):
     """BASELINE config 4 at its full sizes (Q8_0 4096x14336 runs split along K).  The device
     computes the whole product; the CPU f32 row kernels are run on a sample of the weight rows
@@ -131,4 +131,37 @@ def test_config4_full_size_shapes_on_sampled_rows(ex, orc, name, rows, cols, tok
     assert rel_l2 <= 4e-3, f"{name} {rows}x{cols} M={tokens}: relative L2 error {rel_l2:.3e}"
     rms_terms = _bounds(kind, len(sel), cols, wsel, x, tokens, orc)
     assert np.all(np.abs(got - cpu) <= 6 * 2.0 ** -8 * rms_terms + 1e-6), f"{name} M={tokens}: element outside the bound"
+    print(f"config4 {name} {rows}x{cols} M={tokens}: relative L2 error {rel_l2:.2e}, max |gpu-cpu|/(1+|cpu|) = "
+          f"{(np.abs(got - cpu) / (1 + np.abs(cpu))).max():.2e}")
     m.free()
+
+
+def test_crate_facing_matmul_reaches_the_binary16_error_level(orc):
+    """llr_matmul (the call the crate makes) uploads on a cache miss; the operand choice of the tensor-core GEMM
+    must be made there as it is in llr_matrix_upload, so that 64 activation rows of a matrix whose weights fit
+    binary16 get binary16 operands (relative L2 error about 3e-4) and not bfloat16 ones (2.3e-3), on the miss
+    and on the hit."""
+    from llama_rust_b200 import Executor
+    kind, rows, cols, tokens = ALL["Q4_K"], 256, 2048, 64
+    rng = np.random.default_rng(91)
+    w = random_packed(rng, kind, rows, cols)
+    x = rng.standard_normal(tokens * cols).astype(np.float32)
+    cpu = orc.gemm(kind, cols, tokens, w, x, rows, simd=True)
+    e = Executor(0)
+    for attempt in ("miss", "hit"):
+        y = np.full(rows * tokens, np.nan, np.float32)
+        e.matmul(kind, rows, cols, tokens, w, x, y)
+        rel = np.linalg.norm(y.reshape(tokens, rows) - cpu) / np.linalg.norm(cpu)
+        assert rel <= 8e-4, f"cache {attempt}: relative L2 error {rel:.3e}"
+    c = e.counters()
+    assert c["cache_misses"] == 1 and c["cache_hits"] == 1
+    # a decode-sized first call must leave the matrix examined as well
+    w2 = random_packed(rng, kind, rows, cols)
+    y1 = np.empty(rows, np.float32)
+    e.matmul(kind, rows, cols, 1, w2, x[:cols], y1)
+    cpu2 = orc.gemm(kind, cols, tokens, w2, x, rows, simd=True)
+    y = np.empty(rows * tokens, np.float32)
+    e.matmul(kind, rows, cols, tokens, w2, x, y)
+    rel = np.linalg.norm(y.reshape(tokens, rows) - cpu2) / np.linalg.norm(cpu2)
+    assert rel <= 8e-4, f"after a decode-sized miss: relative L2 error {rel:.3e}"
+    e.close()

@@ -98,8 +98,36 @@ def test_llama3_8b_shape_centered_greedy_identity_against_cpu_golden():
     prompt = lw.prompt_ids(g["n_prompt"], cfg["n_vocab"], g["prompt_seed"])
     ids, margin, _ = lw.run_gpu(cfg, g["n_prompt"] + g["n_gen"], ex, mats, embd_mat, prompt, g["n_gen"])
     ref = np.array(g["ids"])
-    n = lw.compared_prefix(ref, g["top2_margin"], g["logit_scale"])
-    assert n >= 16, (n, g["min_margin"], g["logit_scale"])
-    assert np.array_equal(ids[:n], ref[:n]), f"first difference at {int(np.argmax(ids != ref))} of {n} decidable tokens"
-    print(f"config 3 centered: {n} decidable tokens of {g['n_gen']} identical; whole sequence identical: {bool(np.array_equal(ids, ref))}")
+    # every one of the 128 tokens, the two near-ties of the reference included (smallest top-2 margin 2.76 at a
+    # logit scale of 5716: 4.8e-4 relative, still far above the 1e-5 the products differ by)
+    assert np.array_equal(ids, ref), f"first difference at {int(np.argmax(ids != ref))} (margin there {g['top2_margin'][int(np.argmax(ids != ref))]})"
+    ex.close()
+
+
+def test_llama3_8b_shape_centered_greedy_tokens_with_tensor_core_prefill():
+    """The same run with the automatic path: the 512-token prompt goes through the tcgen05 GEMM (16-bit operands,
+    relative L2 error about 3e-4 per product), the decode steps through the f32-faithful kernels.  Identity with the
+    CPU tokens is not promised on this path; what is asserted is that the first differing token, if any, falls on
+    a step the reference itself decides narrowly (top-2 margin under 2 % of the logit scale).  The outcome is printed."""
+    if not os.path.exists(GOLDEN_CENTERED):
+        pytest.skip("tests/golden/config3_centered_golden.json has not been generated")
+    from llama_rust_b200 import Executor
+    g = json.load(open(GOLDEN_CENTERED))
+    cfg = lw.LLAMA3_8B
+    tl = lw.tensor_list(cfg)
+    weights, embd = lw.centered_weights(cfg, g["base_seed"])
+    ex = Executor(0)
+    ex.set_path(0)
+    mats = [ex.upload(dt, rows, cols, w) for (name, dt, rows, cols), w in zip(tl, weights)]
+    embd_mat = ex.upload(lw.Q4_K, cfg["n_vocab"], cfg["n_embd"], embd)
+    del weights, embd
+    prompt = lw.prompt_ids(g["n_prompt"], cfg["n_vocab"], g["prompt_seed"])
+    ids, margin, _ = lw.run_gpu(cfg, g["n_prompt"] + g["n_gen"], ex, mats, embd_mat, prompt, g["n_gen"])
+    ref = np.array(g["ids"])
+    same = ids == ref
+    first = int(np.argmin(same)) if not same.all() else -1
+    print(f"config 3 centered, tensor-core prefill: {'all ' + str(len(ref)) if first < 0 else 'first ' + str(first)} tokens identical"
+          + ("" if first < 0 else f"; reference margin at the first difference {g['top2_margin'][first]:.3g} of scale {g['logit_scale']:.4g}"))
+    if first >= 0:
+        assert g["top2_margin"][first] < 2e-2 * g["logit_scale"], (first, g["top2_margin"][first])
     ex.close()

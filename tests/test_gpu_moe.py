@@ -120,3 +120,32 @@ def test_config5_full_size_layer(orc):
             assert np.all(np.isfinite(out))
             err = float(np.abs(out - ref_out).max())
             assert err <= tol * scale, f"path {path}: max err {err:.3e} vs scale {scale:.3g}"
+
+
+def test_config5_full_size_layer_512_tokens_on_sampled_tokens(orc):
+    """BASELINE config 5 with 512 tokens (1024 routed rows, about 128 per expert: the wide grouped tiles).  The
+    device runs the whole layer; a token's output depends on that token alone, so the CPU walk of the layer is run
+    on every eighth token (64 tokens) and compared with the device's rows for those tokens: routing identical, the
+    f32-faithful path within 3e-5 of the output scale, the grouped tensor-core path within 2e-2."""
+    from llama_rust_b200 import Executor, synth
+    n_expert, n_used, n_embd, n_ff, tokens = 8, 2, 4096, 14336, 512
+    with Executor(0) as ex:
+        mats = {k: [ex.synth(Q4_K, r, c, synth.tensor_seed(5, f"config5.{k}.{e}")) for e in range(n_expert)]
+                for k, (r, c) in {"gate": (n_ff, n_embd), "up": (n_ff, n_embd), "down": (n_embd, n_ff)}.items()}
+        packs = {k: [ex.download(m) for m in v] for k, v in mats.items()}
+        router_w = (synth.activations(n_expert * n_embd, synth.tensor_seed(5, "config5.router")) * np.float32(0.05)).reshape(n_expert, n_embd)
+        router = ex.upload(F32, n_expert, n_embd, router_w.view(np.uint8).reshape(-1))
+        x = synth.activations(tokens * n_embd, synth.tensor_seed(5, "config5.x512")).reshape(tokens, n_embd)
+        sel = np.arange(0, tokens, 8)
+        ref_out, ref_ids, ref_w = orc.moe_ffn(n_used, True, F32, router_w.view(np.uint8).reshape(-1), Q4_K, packs["gate"],
+                                              packs["up"], packs["down"], n_embd, n_ff, np.ascontiguousarray(x[sel]))
+        scale = max(1.0, float(np.abs(ref_out).max()))
+        for path, tol in ((3, 3e-5), (0, 2e-2)):
+            ex.set_path(path)
+            out, ids, w = ex.moe_ffn(router, mats["gate"], mats["up"], mats["down"], n_used, True, x)
+            assert np.all(np.isfinite(out))
+            assert np.array_equal(ids[sel], ref_ids), "routing decisions differ"
+            assert np.allclose(w[sel], ref_w, rtol=1e-5, atol=1e-6)
+            err = float(np.abs(out[sel] - ref_out).max())
+            assert err <= tol * scale, f"path {path}: max err {err:.3e} vs scale {scale:.3g}"
+            print(f"config5 T=512 path {path}: max err {err:.3e} of scale {scale:.3g}; rows per expert {np.bincount(ids.reshape(-1), minlength=n_expert).tolist()}")

@@ -278,6 +278,32 @@ def test_config2_decode_shapes(ex, orc, name, rows, cols):
     m.free()
 
 
+@pytest.mark.parametrize("name,rows,cols", [("Q4_K", 14336, 4096), ("Q4_K", 4096, 14336), ("Q6_K", 128256, 4096)])
+def test_config2_full_row_counts_on_sampled_rows(ex, orc, name, rows, cols):
+    """BASELINE config 2 at its true row counts (gate/up, down, lm_head), M = 1, 2, 4, 8.  The device computes the
+    whole product; the CPU row kernels run on a sample of the weight rows (the first and last 128 and 256 spread
+    over the matrix).  Every output must be finite; the sampled ones are held to the full parity bar.  The
+    per-element figures are printed for the record (pytest -rP shows them)."""
+    from llama_rust_b200 import row_bytes, synth
+    kind = ALL[name]
+    m = ex.synth(kind, rows, cols, synth.tensor_seed(2, f"config2.full.{name}.{rows}x{cols}"))
+    w = ex.download(m)
+    rng = np.random.default_rng(rows + cols)
+    sel = np.unique(np.concatenate([np.arange(128), np.arange(rows - 128, rows), rng.integers(0, rows, 256)]))
+    rb = row_bytes(kind, cols)
+    wsel = np.ascontiguousarray(w.reshape(rows, rb)[sel]).reshape(-1)
+    for tokens in (1, 2, 4, 8):
+        x = synth.activations(tokens * cols, synth.tensor_seed(2, f"x.full.{tokens}"))
+        y = np.full(rows * tokens, np.nan, np.float32)
+        ex.gemm_resident(m, tokens, x, y)
+        assert np.all(np.isfinite(y))
+        cpu, exact, abs_sum = gemv_references(kind, len(sel), cols, wsel, x, tokens)
+        got = np.ascontiguousarray(y.reshape(tokens, rows)[:, sel])
+        per_elem, vs_exact = check_gemv(got, cpu, exact, abs_sum, cols, f"{name} {rows}x{cols} M={tokens}")
+        print(f"config2 {name} {rows}x{cols} M={tokens}: max |gpu-cpu|/(1+|cpu|) = {per_elem:.2e}, max |gpu-exact|/(1+|exact|) = {vs_exact:.2e}")
+    m.free()
+
+
 def test_gemv_is_linear_and_deterministic(ex):
     """Size-independent properties on a BASELINE-size matrix (gate/up 14336x4096 Q4_K)."""
     from llama_rust_b200 import synth
