@@ -333,6 +333,52 @@ typedef struct llr_moe_layer {
 int llr_moe_ffn(llr_exec* exec, const llr_moe_layer* layer, size_t tokens, const float* x, size_t x_len,
                 float* out, size_t out_len, int32_t* sel_ids, float* sel_w);
 
+/* ---- device-resident Llama walk ------------------------------------------------------
+ * The per-token walk of the plain llama architecture with everything on the device
+ * [langtax/src/decode.rs: Llama::forward_layers :2737-3097 -- rmsnorm_inplace :11498, the
+ * q/k/v products, rope :11578 (adjacent-pair rotation), store_kv :12059 into a dense
+ * [layer][kv_head][position][head_dim] f32 cache, attend_query :11126 with grouped-query
+ * heads, attn_output, residual, rmsnorm, silu(gate)*up :2972-2996, ffn_down, residual; last
+ * token's logits :3058-3079; greedy argmax sample.rs:293].  It stands where
+ * Session::{prefill, decode} stand: the reference runs the element-wise steps on the host
+ * between two executor calls (225 host round trips per token); here a generated token
+ * never leaves the device, llr_session_decode enqueues all steps and synchronizes once.
+ * Matrix products go through the executor's kernels (llr_exec_set_path applies).
+ * Sums the reference adds sequentially (sum of squares, scores, softmax denominator) are
+ * added in a fixed tree order: logits agree with the host walk to rounding, not bit for bit.
+ * Norm weights are host f32 vectors of n_embd (NULL: all ones).  output == NULL: tied to
+ * token_embd [decode.rs:2069-2072].  The model's matrices must outlive the session. */
+typedef struct llr_llama_config {
+  uint32_t n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab, n_ctx;
+  float rms_eps;   /* llama.attention.layer_norm_rms_epsilon, default 1e-5 [decode.rs:1958] */
+  float rope_base; /* llama.rope.freq_base, default 10000 [decode.rs:2053] */
+} llr_llama_config;
+typedef struct llr_llama_layer {
+  const llr_matrix *attn_q, *attn_k, *attn_v, *attn_output, *ffn_gate, *ffn_up, *ffn_down;
+  const float *attn_norm, *ffn_norm;
+} llr_llama_layer;
+typedef struct llr_llama_model {
+  llr_llama_config cfg;
+  const llr_matrix* token_embd;
+  const llr_matrix* output;
+  const float* output_norm;
+  const llr_llama_layer* layers; /* cfg.n_layer of them */
+} llr_llama_model;
+typedef struct llr_session llr_session;
+int llr_session_create(llr_exec* exec, const llr_llama_model* model, llr_session** out);
+/* Appends n tokens at the session's position (in chunks of up to 512 rows through the batched
+ * products) and leaves the logits of the last one in the session; last_logits (optional, host,
+ * n_vocab floats) receives them. */
+int llr_session_prefill(llr_session* session, const int32_t* tokens, size_t n, float* last_logits);
+/* Greedy decode: n_gen times { token = argmax(logits); append token -> logits }.  out_ids receives
+ * the n_gen tokens, out_margin (optional) each step's top-2 logit margin. */
+int llr_session_decode(llr_session* session, size_t n_gen, int32_t* out_ids, float* out_margin);
+/* Copies the current logits (n_vocab floats) to the host. */
+int llr_session_logits(llr_session* session, float* logits, size_t n);
+int llr_session_position(const llr_session* session, size_t* position);
+int llr_session_reset(llr_session* session);
+int llr_session_free(llr_session* session);
+
 /* Dequantize rows [row0, row0+n_rows) of a resident matrix to f32 on the
  * device and copy them to out (n_rows*cols floats, host).  Bit-exact
  * counterpart of dequant_<t>_row [quant.rs:7511, 7533, 7734, 7884, 7918, 8046,

@@ -21,6 +21,8 @@ SYMBOLS = [
     "llr_program_run", "llr_program_free", "llr_gemm_device_noalloc", "llr_moe_ffn",
     "llr_shared_alloc", "llr_shared_open", "llr_shared_close", "llr_shared_free",
     "llr_program_create_sharded", "llr_program_create_ops", "llr_program_info", "llr_exec_set_wait_limit",
+    "llr_session_create", "llr_session_prefill", "llr_session_decode", "llr_session_logits", "llr_session_position",
+    "llr_session_reset", "llr_session_free",
 ]
 ARENA_HEADER_BYTES = 65536
 
@@ -45,6 +47,21 @@ class ProgramOp(C.Structure):
 class ProgramShard(C.Structure):
     _fields_ = [("arena", C.c_void_p), ("arena_bytes", C.c_size_t), ("world", C.c_uint32), ("rank", C.c_uint32),
                 ("peer_arenas", C.POINTER(C.c_void_p))]
+
+
+class LlamaConfig(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff", "n_vocab", "n_ctx")] + \
+               [("rms_eps", C.c_float), ("rope_base", C.c_float)]
+
+
+class LlamaLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down",
+                                          "attn_norm", "ffn_norm")]
+
+
+class LlamaModel(C.Structure):
+    _fields_ = [("cfg", LlamaConfig), ("token_embd", C.c_void_p), ("output", C.c_void_p), ("output_norm", C.c_void_p),
+                ("layers", C.POINTER(LlamaLayer))]
 
 
 class MoeLayer(C.Structure):
@@ -97,6 +114,13 @@ def load() -> C.CDLL:
     lib.llr_program_create_ops.argtypes = [vp, C.POINTER(ProgramOp), sz, C.POINTER(ProgramShard), C.POINTER(vp)]
     lib.llr_program_info.argtypes = [vp, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]
     lib.llr_exec_set_wait_limit.argtypes = [vp, C.c_uint32]
+    lib.llr_session_create.argtypes = [vp, C.POINTER(LlamaModel), C.POINTER(vp)]
+    lib.llr_session_prefill.argtypes = [vp, vp, sz, vp]
+    lib.llr_session_decode.argtypes = [vp, sz, vp, vp]
+    lib.llr_session_logits.argtypes = [vp, vp, sz]
+    lib.llr_session_position.argtypes = [vp, C.POINTER(sz)]
+    lib.llr_session_reset.argtypes = [vp]
+    lib.llr_session_free.argtypes = [vp]
     for s in SYMBOLS:
         if s != "llr_exec_last_error":
             getattr(lib, s).restype = C.c_int

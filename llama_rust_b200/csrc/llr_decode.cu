@@ -1,0 +1,349 @@
+// Element-wise and attention kernels of the device-resident Llama walk: what stands between the matrix
+// products of Llama::forward_layers (langtax/src/decode.rs:2737-3097) -- rmsnorm_inplace :11498, rope :11578
+// (adjacent-pair rotation), store_kv :12059, attend_query :11126 with grouped-query heads, silu :11826,
+// the residual adds -- and the greedy argmax of sample.rs:293.  The host walk of the reference runs these on
+// the CPU between two executor calls; here a decode step never leaves the device.
+//
+// Arithmetic follows the reference's formulas; sums that the reference adds sequentially (sum of squares,
+// attention scores, softmax denominator, weighted values) are added in a fixed tree / block order here, so
+// results are reproducible from run to run and differ from the CPU walk in the last bits only.
+#include <cuda_runtime.h>
+#include <math_constants.h>
+
+#include "llr_kernels.cuh"
+
+namespace llr {
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(~0u, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(~0u, v, o));
+  return v;
+}
+// block-wide sum / max through shared memory (blockDim.x a multiple of 32, at most 1024); every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < nw; ++w) t += sh[w];  // fixed order
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* sh) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  float t = -CUDART_INF_F;
+  for (int w = 0; w < nw; ++w) t = fmaxf(t, sh[w]);
+  return t;
+}
+
+// one block per activation row
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add, const float* __restrict__ w, float* __restrict__ y,
+               int n, float eps) {
+  __shared__ float sh[32];
+  float* xr = x + (int64_t)blockIdx.x * n;
+  const float* ar = add ? add + (int64_t)blockIdx.x * n : nullptr;
+  float* yr = y + (int64_t)blockIdx.x * n;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = xr[i];
+    if (ar) { v = __fadd_rn(ar[i], v); xr[i] = v; }  // proj + residual (decode.rs:2938, :3050)
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, sh);
+  const float rms = sqrtf(__fadd_rn(__fdiv_rn(ss, (float)(n <= 65535 ? n : 1)), eps));
+  const float inv = rms > 0.f ? __fdiv_rn(1.0f, rms) : 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float t = __fmul_rn(xr[i], inv);
+    yr[i] = w ? __fmul_rn(t, w[i]) : t;
+  }
+}
+
+// grid (token, head of q and k together): one thread per rotated pair; then the k and v rows go to the cache
+__global__ void __launch_bounds__(128)
+rope_store_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v, float* __restrict__ cache_k,
+                  float* __restrict__ cache_v, const int* __restrict__ pos_dev, int layer, WalkShape w) {
+  const int t = blockIdx.x, h = blockIdx.y;  // h < n_head: a q head, else a k head
+  const int pos = *pos_dev + t;
+  const int hd = w.head_dim;
+  const bool is_q = h < w.n_head;
+  const int hk = h - w.n_head;
+  float* vec = is_q ? q + ((int64_t)t * w.n_head + h) * hd : k + ((int64_t)t * w.n_head_kv + hk) * hd;
+  const float theta_scale = w.theta_scale;  // base^(-2/n_rot), computed once on the host in f32 as the reference does
+  for (int p = threadIdx.x; 2 * p + 1 < hd; p += blockDim.x) {
+    float theta = (float)(pos <= 65535 ? pos : 65535);
+    for (int i = 0; i < p; ++i) theta *= theta_scale;  // the reference advances theta multiplicatively in f32
+    const float c = cosf(theta), s = sinf(theta);
+    const float a = vec[2 * p], b = vec[2 * p + 1];
+    vec[2 * p] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+    vec[2 * p + 1] = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+  }
+  if (is_q) return;
+  __syncthreads();
+  // dense cache [layer][kv_head][t][hd] (store_kv, decode.rs:12059)
+  const int64_t off = (((int64_t)layer * w.n_head_kv + hk) * w.n_ctx + pos) * hd;
+  const float* vv = v + ((int64_t)t * w.n_head_kv + hk) * hd;
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    cache_k[off + i] = vec[i];
+    cache_v[off + i] = vv[i];
+  }
+}
+
+// Attention of one token: grid (kv head, position split, token).  A block handles the query heads that share its kv
+// head over its slice of the positions and writes, per query head, the slice's maximum score, the sum of exp(score -
+// max) and the exp-weighted sum of value rows; attention_combine_kernel merges the slices (the usual two-pass softmax,
+// rearranged so that K and V are read once per kv head and by many SMs).
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_MAX_GQA = 8;
+__global__ void __launch_bounds__(ATT_THREADS)
+attention_partial_kernel(const float* __restrict__ q, const float* __restrict__ cache_k, const float* __restrict__ cache_v,
+                         float* __restrict__ part, const int* __restrict__ pos_dev, int layer, int n_split, WalkShape w) {
+  extern __shared__ float sm[];  // q[gqa][hd] | scores[gqa][chunk] | red[32]
+  const int hkv = blockIdx.x, split = blockIdx.y, t = blockIdx.z;
+  const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
+  const int seq = *pos_dev + t + 1;
+  const int chunk = (seq + n_split - 1) / n_split;
+  const int s0 = split * chunk, s1 = min(seq, s0 + chunk);
+  const int max_chunk = (w.n_ctx + n_split - 1) / n_split;
+  float* sq = sm;
+  float* sc = sq + gqa * hd;
+  float* red = sc + gqa * max_chunk;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = ATT_THREADS / 32;
+  const float scale = 1.0f / sqrtf((float)hd);
+  for (int i = threadIdx.x; i < gqa * hd; i += ATT_THREADS)
+    sq[i] = q[((int64_t)t * w.n_head + hkv * gqa) * hd + i];
+  __syncthreads();
+  const float* kbase = cache_k + ((int64_t)layer * w.n_head_kv + hkv) * w.n_ctx * hd;
+  const float* vbase = cache_v + ((int64_t)layer * w.n_head_kv + hkv) * w.n_ctx * hd;
+  // scores: one warp per position, all query heads of the group against one read of the K row
+  for (int s = s0 + warp; s < s1; s += nw) {
+    float acc[ATT_MAX_GQA];
+#pragma unroll
+    for (int g = 0; g < ATT_MAX_GQA; ++g) acc[g] = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+      const float kv = kbase[(int64_t)s * hd + i];
+#pragma unroll
+      for (int g = 0; g < ATT_MAX_GQA; ++g)
+        if (g < gqa) acc[g] = fmaf(sq[g * hd + i], kv, acc[g]);
+    }
+#pragma unroll
+    for (int g = 0; g < ATT_MAX_GQA; ++g)
+      if (g < gqa) {
+        const float d = warp_sum(acc[g]);
+        if (lane == 0) sc[g * max_chunk + (s - s0)] = __fmul_rn(d, scale);
+      }
+  }
+  __syncthreads();
+  float* out = part + (((int64_t)t * w.n_head_kv + hkv) * n_split + split) * gqa * (hd + 2);
+  for (int g = 0; g < gqa; ++g) {
+    float m = -CUDART_INF_F;
+    for (int s = threadIdx.x; s < s1 - s0; s += ATT_THREADS) m = fmaxf(m, sc[g * max_chunk + s]);
+    m = block_max(m, red);
+    float l = 0.f;
+    for (int s = threadIdx.x; s < s1 - s0; s += ATT_THREADS) {
+      const float e = expf(sc[g * max_chunk + s] - m);
+      sc[g * max_chunk + s] = e;
+      l += e;
+    }
+    l = block_sum(l, red);
+    if (threadIdx.x == 0) { out[g * (hd + 2) + hd] = m; out[g * (hd + 2) + hd + 1] = l; }
+  }
+  __syncthreads();
+  // weighted values: thread i owns dimension i (hd <= ATT_THREADS), positions in ascending order
+  for (int i = threadIdx.x; i < hd; i += ATT_THREADS) {
+    float acc[ATT_MAX_GQA];
+#pragma unroll
+    for (int g = 0; g < ATT_MAX_GQA; ++g) acc[g] = 0.f;
+    for (int s = s0; s < s1; ++s) {
+      const float vv = vbase[(int64_t)s * hd + i];
+#pragma unroll
+      for (int g = 0; g < ATT_MAX_GQA; ++g)
+        if (g < gqa) acc[g] = fmaf(sc[g * max_chunk + (s - s0)], vv, acc[g]);
+    }
+#pragma unroll
+    for (int g = 0; g < ATT_MAX_GQA; ++g)
+      if (g < gqa) out[g * (hd + 2) + i] = acc[g];
+  }
+}
+
+// grid (query head, token): merges the position slices in ascending order
+__global__ void __launch_bounds__(128)
+attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, const int* __restrict__ pos_dev,
+                         int n_split, WalkShape w) {
+  const int hq = blockIdx.x, t = blockIdx.y;
+  const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
+  const int hkv = hq / gqa, g = hq % gqa;
+  const int seq = *pos_dev + t + 1;
+  const int chunk = (seq + n_split - 1) / n_split;
+  const float* base = part + ((int64_t)t * w.n_head_kv + hkv) * n_split * gqa * (hd + 2) + g * (hd + 2);
+  float m = -CUDART_INF_F;
+  for (int sp = 0; sp < n_split && sp * chunk < seq; ++sp) m = fmaxf(m, base[(int64_t)sp * gqa * (hd + 2) + hd]);
+  float l = 0.f;
+  for (int sp = 0; sp < n_split && sp * chunk < seq; ++sp) {
+    const float* p = base + (int64_t)sp * gqa * (hd + 2);
+    l = fmaf(p[hd + 1], expf(p[hd] - m), l);
+  }
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    float acc = 0.f;
+    for (int sp = 0; sp < n_split && sp * chunk < seq; ++sp) {
+      const float* p = base + (int64_t)sp * gqa * (hd + 2);
+      acc = fmaf(p[i], expf(p[hd] - m), acc);
+    }
+    out[((int64_t)t * w.n_head + hq) * hd + i] = l > 0.f ? __fdiv_rn(acc, l) : 0.f;
+  }
+}
+
+__global__ void swiglu_kernel(float* __restrict__ g, const float* __restrict__ u, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float a = g[i];
+    g[i] = __fmul_rn(__fdiv_rn(a, 1.0f + expf(-a)), u[i]);  // silu(gate) * up (decode.rs:11826, :2984)
+  }
+}
+__global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    x[i] = __fadd_rn(y[i], x[i]);
+}
+
+// one block: index of the first strict maximum (sample.rs:293: `v > best` scanning upwards, so ties go to the
+// lower index), its margin over the largest other value, and the position counter advanced for the next step
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float* __restrict__ logits, int n, int* __restrict__ out_id, float* __restrict__ out_margin,
+              int* __restrict__ pos_dev, int advance) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ int s_best;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (n > 0) {
+    float best = -CUDART_INF_F;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float v = logits[i];
+      if (v > best) { best = v; bi = i; }  // ascending i per thread: the first of equal values stays
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(~0u, best, o);
+      const int oi = __shfl_xor_sync(~0u, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+      best = lane < nw ? sv[lane] : -CUDART_INF_F;
+      bi = lane < nw ? si[lane] : 0x7fffffff;
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(~0u, best, o);
+        const int oi = __shfl_xor_sync(~0u, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      if (lane == 0) s_best = bi == 0x7fffffff ? 0 : bi;  // all NaN or -inf: index 0, as the reference's scan leaves it
+    }
+    __syncthreads();
+    const int win = s_best;
+    if (out_margin) {
+      float second = -CUDART_INF_F;
+      for (int i = threadIdx.x; i < n; i += blockDim.x)
+        if (i != win) second = fmaxf(second, logits[i]);
+      second = warp_max(second);
+      __syncthreads();
+      if (lane == 0) sv[warp] = second;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float m = -CUDART_INF_F;
+        for (int w = 0; w < nw; ++w) m = fmaxf(m, sv[w]);
+        *out_margin = logits[win] - m;
+      }
+    }
+    if (threadIdx.x == 0) *out_id = win;
+  }
+  if (threadIdx.x == 0 && pos_dev) *pos_dev += advance;
+}
+
+int attention_splits(int tokens, const WalkShape& w) {
+  // enough blocks to occupy the device when one token attends (decode); a chunk of prompt tokens brings its own
+  int splits = tokens >= 16 ? 1 : 148 / (w.n_head_kv > 0 ? w.n_head_kv : 1);
+  if (splits < 1) splits = 1;
+  if (splits > 16) splits = 16;
+  return splits;
+}
+
+}  // namespace
+
+cudaError_t launch_rmsnorm(float* x, const float* add, const float* w, float* y, int tokens, int n, float eps,
+                           cudaStream_t s, uint64_t* launches) {
+  if (tokens <= 0) return cudaSuccess;
+  rmsnorm_kernel<<<tokens, 256, 0, s>>>(x, add, w, y, n, eps);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rope_store(float* q, float* k, const float* v, float* cache_k, float* cache_v, const int* pos_dev,
+                              int tokens, int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches) {
+  if (tokens <= 0) return cudaSuccess;
+  rope_store_kernel<<<dim3(tokens, w.n_head + w.n_head_kv), 128, 0, s>>>(q, k, v, cache_k, cache_v, pos_dev, layer, w);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+size_t attention_scratch_floats(int tokens, const WalkShape& w) {
+  return (size_t)tokens * w.n_head_kv * attention_splits(tokens, w) * (w.n_head / w.n_head_kv) * (w.head_dim + 2);
+}
+
+cudaError_t launch_attention(const float* q, const float* cache_k, const float* cache_v, float* out, float* scratch,
+                             const int* pos_dev, int tokens, int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches) {
+  if (tokens <= 0) return cudaSuccess;
+  const int gqa = w.n_head / w.n_head_kv;
+  if (gqa < 1 || gqa > ATT_MAX_GQA || w.n_head % w.n_head_kv != 0 || w.head_dim > 1024) return cudaErrorInvalidValue;
+  const int splits = attention_splits(tokens, w);
+  const int max_chunk = (w.n_ctx + splits - 1) / splits;
+  const size_t smem = ((size_t)gqa * w.head_dim + (size_t)gqa * max_chunk + 32) * sizeof(float);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = smem;
+  }
+  attention_partial_kernel<<<dim3(w.n_head_kv, splits, tokens), ATT_THREADS, smem, s>>>(q, cache_k, cache_v, scratch, pos_dev,
+                                                                                      layer, splits, w);
+  attention_combine_kernel<<<dim3(w.n_head, tokens), 128, 0, s>>>(scratch, out, pos_dev, splits, w);
+  if (launches) *launches += 2;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches) {
+  if (n <= 0) return cudaSuccess;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  swiglu_kernel<<<(unsigned)blocks, 256, 0, s>>>(g, u, n);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_add(float* x, const float* y, int64_t n, cudaStream_t s, uint64_t* launches) {
+  if (n <= 0) return cudaSuccess;
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  add_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, y, n);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_advance(const float* logits, int n, int* out_id, float* out_margin, int* pos_dev, int advance,
+                                  cudaStream_t s, uint64_t* launches) {
+  argmax_kernel<<<1, 1024, 0, s>>>(logits, n, out_id, out_margin, pos_dev, advance);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+}  // namespace llr

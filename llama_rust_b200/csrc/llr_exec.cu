@@ -1228,6 +1228,251 @@ int llr_program_free(llr_program* p) {
   return LLR_OK;
 }
 
+// ---------------------------------------------------------------- device-resident Llama walk
+struct llr_session {
+  llr_exec* owner = nullptr;
+  llr_llama_config cfg{};
+  WalkShape shape{};
+  const llr_matrix* embd = nullptr;
+  const llr_matrix* output = nullptr;
+  std::vector<llr_llama_layer> layers;
+  std::vector<float*> attn_norm, ffn_norm;  // device copies (null: all ones)
+  float* out_norm = nullptr;
+  size_t max_batch = 0, position = 0;
+  bool have_logits = false;
+  // device buffers
+  float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *proj = nullptr,
+        *gate = nullptr, *up = nullptr, *logits = nullptr, *cache_k = nullptr, *cache_v = nullptr, *att_scratch = nullptr,
+        *margins = nullptr;
+  int *ids = nullptr, *pos_dev = nullptr;
+  size_t ids_cap = 0;
+};
+
+namespace {
+
+void session_release(llr_session* s) {
+  for (float* p : s->attn_norm) if (p) cudaFree(p);
+  for (float* p : s->ffn_norm) if (p) cudaFree(p);
+  float* bufs[] = {s->out_norm, s->x, s->xn, s->q, s->k, s->v, s->attn, s->proj, s->gate, s->up, s->logits,
+                   s->cache_k, s->cache_v, s->att_scratch, s->margins};
+  for (float* p : bufs) if (p) cudaFree(p);
+  if (s->ids) cudaFree(s->ids);
+  if (s->pos_dev) cudaFree(s->pos_dev);
+  cudaGetLastError();
+}
+
+cudaError_t session_matmul(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x, float* y) {
+  void* scratch = nullptr;
+  cudaError_t ce = ensure_scratch(e, m, tokens, &scratch);
+  if (ce != cudaSuccess) return ce;
+  return launch_matmul(view_of(m), x, y, (int64_t)tokens, e->stream, e->path, e->sm_count, e->err_flag, scratch, &e->ctr.launches);
+}
+
+// One forward pass over `n` tokens whose ids lie at ids_dev (device) starting at the session's device-side position;
+// with_logits: the last token's logits, then argmax into *next_id (and the margin) and the position advanced by n.
+cudaError_t session_forward(llr_session* s, const int* ids_dev, size_t n, bool with_logits, int* next_id, float* margin) {
+  llr_exec* e = s->owner;
+  const llr_llama_config& c = s->cfg;
+  const size_t E = c.n_embd, QW = (size_t)c.n_head * c.head_dim, FF = c.n_ff;
+  cudaStream_t st = e->stream;
+  uint64_t* L = &e->ctr.launches;
+  cudaError_t ce = launch_dequant_indexed(view_of(s->embd), ids_dev, (int64_t)n, s->x, st, L);
+  const float* pending = nullptr;  // ffn_down result of the previous layer, not yet added to the residual stream
+  for (size_t li = 0; li < c.n_layer && ce == cudaSuccess; ++li) {
+    const llr_llama_layer& W = s->layers[li];
+    if ((ce = launch_rmsnorm(s->x, pending, s->attn_norm[li], s->xn, (int)n, (int)E, c.rms_eps, st, L)) != cudaSuccess) break;
+    if ((ce = session_matmul(e, W.attn_q, n, s->xn, s->q)) != cudaSuccess) break;
+    if ((ce = session_matmul(e, W.attn_k, n, s->xn, s->k)) != cudaSuccess) break;
+    if ((ce = session_matmul(e, W.attn_v, n, s->xn, s->v)) != cudaSuccess) break;
+    if ((ce = launch_rope_store(s->q, s->k, s->v, s->cache_k, s->cache_v, s->pos_dev, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
+    if ((ce = launch_attention(s->q, s->cache_k, s->cache_v, s->attn, s->att_scratch, s->pos_dev, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
+    if ((ce = session_matmul(e, W.attn_output, n, s->attn, s->proj)) != cudaSuccess) break;
+    if ((ce = launch_rmsnorm(s->x, s->proj, s->ffn_norm[li], s->xn, (int)n, (int)E, c.rms_eps, st, L)) != cudaSuccess) break;
+    if ((ce = session_matmul(e, W.ffn_gate, n, s->xn, s->gate)) != cudaSuccess) break;
+    if ((ce = session_matmul(e, W.ffn_up, n, s->xn, s->up)) != cudaSuccess) break;
+    if ((ce = launch_swiglu(s->gate, s->up, (int64_t)(n * FF), st, L)) != cudaSuccess) break;
+    if ((ce = session_matmul(e, W.ffn_down, n, s->gate, s->proj)) != cudaSuccess) break;
+    pending = s->proj;
+  }
+  (void)QW;
+  if (ce != cudaSuccess) return ce;
+  if (with_logits) {
+    // LogitsKind::Last (decode.rs:3058-3079): the last row only
+    float* xl = s->x + (n - 1) * E;
+    if ((ce = launch_rmsnorm(xl, pending ? pending + (n - 1) * E : nullptr, s->out_norm, s->xn, 1, (int)E, c.rms_eps, st, L)) != cudaSuccess) return ce;
+    if ((ce = session_matmul(e, s->output, 1, s->xn, s->logits)) != cudaSuccess) return ce;
+    return launch_argmax_advance(s->logits, next_id ? (int)c.n_vocab : 0, next_id, margin, s->pos_dev, (int)n, st, L);
+  }
+  return launch_argmax_advance(nullptr, 0, nullptr, nullptr, s->pos_dev, (int)n, st, L);
+}
+
+}  // namespace
+
+int llr_session_create(llr_exec* e, const llr_llama_model* m, llr_session** out) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!out) return fail(e, LLR_ERR_INVALID, "null output pointer");
+  *out = nullptr;
+  if (!m || !m->layers || !m->token_embd) return fail(e, LLR_ERR_INVALID, "null model");
+  const llr_llama_config& c = m->cfg;
+  if (c.n_layer == 0 || c.n_embd == 0 || c.n_head == 0 || c.n_head_kv == 0 || c.head_dim == 0 || c.n_ff == 0 || c.n_vocab == 0 ||
+      c.n_ctx == 0 || c.n_head % c.n_head_kv != 0 || c.n_head / c.n_head_kv > 8 || c.head_dim % 2 != 0 || c.head_dim > 1024 ||
+      c.n_embd % 8 != 0 || c.n_ctx > (1u << 20) || !(c.rms_eps >= 0.0f) || !(c.rope_base > 0.0f))
+    return fail(e, LLR_ERR_INVALID, "llama configuration out of range (grouped-query ratio at most 8, even head_dim, n_embd % 8 == 0)");
+  const size_t E = c.n_embd, QW = (size_t)c.n_head * c.head_dim, KVW = (size_t)c.n_head_kv * c.head_dim, FF = c.n_ff, V = c.n_vocab;
+  auto shape_ok = [&](const llr_matrix* w, size_t rows, size_t cols) {
+    return w && w->owner == e && (size_t)w->rows == rows && (size_t)w->cols == cols;
+  };
+  const llr_matrix* output = m->output ? m->output : m->token_embd;
+  if (!shape_ok(m->token_embd, V, E) || !shape_ok(output, V, E))
+    return fail(e, LLR_ERR_INVALID, "token_embd / output must be n_vocab x n_embd matrices of this executor");
+  for (uint32_t li = 0; li < c.n_layer; ++li) {
+    const llr_llama_layer& W = m->layers[li];
+    if (!shape_ok(W.attn_q, QW, E) || !shape_ok(W.attn_k, KVW, E) || !shape_ok(W.attn_v, KVW, E) || !shape_ok(W.attn_output, E, QW) ||
+        !shape_ok(W.ffn_gate, FF, E) || !shape_ok(W.ffn_up, FF, E) || !shape_ok(W.ffn_down, E, FF))
+      return fail(e, LLR_ERR_INVALID, "blk." + std::to_string(li) + ": matrix shapes do not match the configuration (or another executor owns them)");
+  }
+  DeviceGuard guard(e->device);
+  llr_session* s = new (std::nothrow) llr_session();
+  if (!s) return fail(e, LLR_ERR_OOM, "host allocation failed");
+  s->owner = e;
+  s->cfg = c;
+  s->embd = m->token_embd;
+  s->output = output;
+  s->layers.assign(m->layers, m->layers + c.n_layer);
+  const float n_rot = (float)(uint16_t)c.head_dim;
+  s->shape = WalkShape{(int)c.n_embd, (int)c.n_head, (int)c.n_head_kv, (int)c.head_dim, (int)c.n_ff, (int)c.n_ctx, c.rms_eps, c.rope_base,
+                       std::pow(c.rope_base, -2.0f / n_rot)};  // decode.rs:11578: theta_scale in f32
+  s->max_batch = c.n_ctx < 512 ? c.n_ctx : 512;
+  const size_t B = s->max_batch;
+  cudaError_t ce = cudaSuccess;
+  auto alloc = [&](float** p, size_t n) { if (ce == cudaSuccess) ce = cudaMalloc((void**)p, n * sizeof(float)); };
+  auto norm = [&](const float* host, float** dev) {
+    *dev = nullptr;
+    if (!host || ce != cudaSuccess) return;
+    ce = cudaMalloc((void**)dev, E * sizeof(float));
+    if (ce == cudaSuccess) ce = cudaMemcpy(*dev, host, E * sizeof(float), cudaMemcpyHostToDevice);
+  };
+  s->attn_norm.assign(c.n_layer, nullptr);
+  s->ffn_norm.assign(c.n_layer, nullptr);
+  for (uint32_t li = 0; li < c.n_layer; ++li) { norm(m->layers[li].attn_norm, &s->attn_norm[li]); norm(m->layers[li].ffn_norm, &s->ffn_norm[li]); }
+  norm(m->output_norm, &s->out_norm);
+  alloc(&s->x, B * E); alloc(&s->xn, B * E); alloc(&s->q, B * QW); alloc(&s->k, B * KVW); alloc(&s->v, B * KVW);
+  alloc(&s->attn, B * QW); alloc(&s->proj, B * E); alloc(&s->gate, B * FF); alloc(&s->up, B * FF); alloc(&s->logits, V);
+  const size_t cache = (size_t)c.n_layer * c.n_head_kv * c.n_ctx * c.head_dim;
+  alloc(&s->cache_k, cache); alloc(&s->cache_v, cache);
+  size_t sc = attention_scratch_floats((int)B, s->shape), sc1 = attention_scratch_floats(1, s->shape), sc15 = attention_scratch_floats(15, s->shape);
+  if (sc1 > sc) sc = sc1;
+  if (sc15 > sc) sc = sc15;
+  alloc(&s->att_scratch, sc);
+  if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->pos_dev, sizeof(int));
+  if (ce == cudaSuccess) ce = cudaMemset(s->pos_dev, 0, sizeof(int));
+  if (ce != cudaSuccess) {
+    session_release(s);
+    delete s;
+    return fail_cuda(e, ce, "session buffers");
+  }
+  *out = s;
+  return LLR_OK;
+}
+
+int llr_session_free(llr_session* s) {
+  if (!s) return LLR_OK;
+  if (s->owner) {
+    DeviceGuard guard(s->owner->device);
+    cudaStreamSynchronize(s->owner->stream);
+    session_release(s);
+  }
+  delete s;
+  return LLR_OK;
+}
+
+int llr_session_reset(llr_session* s) {
+  if (!s || !s->owner) return LLR_ERR_INVALID;
+  DeviceGuard guard(s->owner->device);
+  cudaError_t ce = cudaMemsetAsync(s->pos_dev, 0, sizeof(int), s->owner->stream);
+  if (ce != cudaSuccess) return fail_cuda(s->owner, ce, "session reset");
+  s->position = 0;
+  s->have_logits = false;
+  return LLR_OK;
+}
+
+int llr_session_position(const llr_session* s, size_t* position) {
+  if (!s || !position) return LLR_ERR_INVALID;
+  *position = s->position;
+  return LLR_OK;
+}
+
+static int session_ids(llr_session* s, size_t n) {
+  if (n <= s->ids_cap) return LLR_OK;
+  if (s->ids) cudaFree(s->ids);
+  if (s->margins) cudaFree(s->margins);
+  s->ids = nullptr; s->margins = nullptr; s->ids_cap = 0;
+  cudaError_t ce = cudaMalloc((void**)&s->ids, n * sizeof(int));
+  if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->margins, n * sizeof(float));
+  if (ce != cudaSuccess) return fail_cuda(s->owner, ce, "token buffer");
+  s->ids_cap = n;
+  return LLR_OK;
+}
+
+int llr_session_prefill(llr_session* s, const int32_t* tokens, size_t n, float* last_logits) {
+  if (!s || !s->owner) return LLR_ERR_INVALID;
+  llr_exec* e = s->owner;
+  if (!tokens || n == 0) return fail(e, LLR_ERR_INVALID, "prefill needs at least one token");
+  if (s->position + n > s->cfg.n_ctx) return fail(e, LLR_ERR_INVALID, "the sequence would exceed the session's context length");
+  for (size_t i = 0; i < n; ++i)
+    if (tokens[i] < 0 || (uint32_t)tokens[i] >= s->cfg.n_vocab) return fail(e, LLR_ERR_INVALID, "token id out of range");
+  DeviceGuard guard(e->device);
+  int rc = session_ids(s, n > 1 ? n : 1);
+  if (rc) return rc;
+  cudaError_t ce = cudaMemcpyAsync(s->ids, tokens, n * sizeof(int), cudaMemcpyHostToDevice, e->stream);
+  for (size_t t0 = 0; t0 < n && ce == cudaSuccess; t0 += s->max_batch) {
+    const size_t m = n - t0 < s->max_batch ? n - t0 : s->max_batch;
+    ce = session_forward(s, s->ids + t0, m, t0 + m == n, nullptr, nullptr);
+  }
+  if (ce == cudaSuccess && last_logits)
+    ce = cudaMemcpyAsync(last_logits, s->logits, s->cfg.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "prefill");
+  if (take_device_error(e) != 0) return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations");
+  s->position += n;
+  s->have_logits = true;
+  return LLR_OK;
+}
+
+int llr_session_decode(llr_session* s, size_t n_gen, int32_t* out_ids, float* out_margin) {
+  if (!s || !s->owner) return LLR_ERR_INVALID;
+  llr_exec* e = s->owner;
+  if (!out_ids || n_gen == 0) return fail(e, LLR_ERR_INVALID, "decode needs a token count and an output buffer");
+  if (!s->have_logits) return fail(e, LLR_ERR_INVALID, "decode needs logits: prefill at least one token first");
+  if (s->position + n_gen > s->cfg.n_ctx) return fail(e, LLR_ERR_INVALID, "the sequence would exceed the session's context length");
+  DeviceGuard guard(e->device);
+  int rc = session_ids(s, n_gen);
+  if (rc) return rc;
+  // token i = argmax of the current logits, written to ids[i] on the device; the forward pass of step i reads it there
+  cudaError_t ce = launch_argmax_advance(s->logits, (int)s->cfg.n_vocab, s->ids, s->margins, nullptr, 0, e->stream, &e->ctr.launches);
+  for (size_t i = 0; i < n_gen && ce == cudaSuccess; ++i)
+    ce = session_forward(s, s->ids + i, 1, true, i + 1 < n_gen ? s->ids + i + 1 : nullptr, i + 1 < n_gen ? s->margins + i + 1 : nullptr);
+  if (ce == cudaSuccess) ce = cudaMemcpyAsync(out_ids, s->ids, n_gen * sizeof(int), cudaMemcpyDeviceToHost, e->stream);
+  if (ce == cudaSuccess && out_margin) ce = cudaMemcpyAsync(out_margin, s->margins, n_gen * sizeof(float), cudaMemcpyDeviceToHost, e->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "decode");
+  if (take_device_error(e) != 0) return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations");
+  s->position += n_gen;
+  e->ctr.d2h_bytes += n_gen * sizeof(int);
+  return LLR_OK;
+}
+
+int llr_session_logits(llr_session* s, float* logits, size_t n) {
+  if (!s || !s->owner) return LLR_ERR_INVALID;
+  llr_exec* e = s->owner;
+  if (!logits || n != s->cfg.n_vocab || !s->have_logits) return fail(e, LLR_ERR_INVALID, "logits buffer does not match n_vocab, or no token has been run");
+  DeviceGuard guard(e->device);
+  cudaError_t ce = cudaMemcpyAsync(logits, s->logits, n * sizeof(float), cudaMemcpyDeviceToHost, e->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "logits download");
+  return LLR_OK;
+}
+
 int llr_dequant_rows(llr_exec* e, const llr_matrix* m, size_t row0, size_t n_rows, float* out,
                      size_t out_len) {
   if (!e) return LLR_ERR_INVALID;

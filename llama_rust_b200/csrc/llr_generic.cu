@@ -88,6 +88,34 @@ dequant_kernel(const uint8_t* __restrict__ W, int64_t row_bytes, int64_t cols, i
   }
 }
 
+// Rows picked by an index list in device memory (token embeddings): out[i] = dequantized row ids[i];
+// an index outside the matrix yields zeros.
+template <int DT>
+__global__ void __launch_bounds__(256)
+dequant_indexed_kernel(const uint8_t* __restrict__ W, int64_t row_bytes, int64_t rows, int64_t cols,
+                       const int* __restrict__ ids, int64_t n, float* __restrict__ out) {
+  constexpr int UPB = units_per_block(DT);
+  constexpr int BE = block_elems(DT);
+  const int64_t n_units = (cols + 7) / 8;
+  const int64_t total = n_units * n;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / n_units, u = i % n_units;
+    const int64_t src = ids[r];
+    float w[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int valid = BE == 1 ? (int)min((int64_t)8, cols - 8 * u) : 8;
+    if (src >= 0 && src < rows) {
+      const uint8_t* wrow = W + src * row_bytes;
+      if constexpr (BE == 1) decode8<DT>(wrow + u * unit_bytes_elem(DT), 0, valid, w);
+      else decode8<DT>(wrow + (u / UPB) * block_bytes(DT), (int)(u % UPB), 8, w);
+    }
+    float* o = out + r * cols + 8 * u;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < valid) o[j] = w[j];
+  }
+}
+
 }  // namespace
 
 #define LLR_DISPATCH_DTYPE(dt, CALL)                         \
@@ -118,6 +146,18 @@ cudaError_t launch_gemv_generic(const MatView& m, const float* x, float* y, int6
                                     y + t0 * m.rows, nt)));
     if (launches) ++*launches;
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dequant_indexed(const MatView& m, const int* ids_dev, int64_t n, float* out,
+                                   cudaStream_t stream, uint64_t* launches) {
+  if (n <= 0) return cudaSuccess;
+  const int64_t total = ((m.cols + 7) / 8) * n;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  LLR_DISPATCH_DTYPE(m.dtype, (dequant_indexed_kernel<DT><<<(unsigned)blocks, 256, 0, stream>>>(
+                                  m.w, m.row_bytes, m.rows, m.cols, ids_dev, n, out)));
+  if (launches) ++*launches;
   return cudaGetLastError();
 }
 

@@ -184,6 +184,31 @@ cudaError_t launch_scatter_combine(const float* y, const int* rows_of_tok, const
 cudaError_t launch_dequant(const MatView& m, int64_t row0, int64_t n_rows, float* out,
                            cudaStream_t stream, uint64_t* launches);
 
+// out[i*cols + c] = dequantized W[ids[i], c] with ids in device memory (token embeddings)
+cudaError_t launch_dequant_indexed(const MatView& m, const int* ids_dev, int64_t n, float* out,
+                                   cudaStream_t stream, uint64_t* launches);
+
+// ---- element-wise and attention kernels of the device-resident Llama walk (llr_decode.cu) ----
+struct WalkShape { int n_embd, n_head, n_head_kv, head_dim, n_ff, n_ctx; float rms_eps, rope_base, theta_scale; };
+// y[t] = (x[t] * 1/sqrt(mean(x[t]^2) + eps)) * w; with `add` non-null first x[t] += add[t] (written back: the new
+// residual stream).  w may be null (all ones).
+cudaError_t launch_rmsnorm(float* x, const float* add, const float* w, float* y, int tokens, int n, float eps,
+                           cudaStream_t s, uint64_t* launches);
+// RoPE (adjacent pairs) on q and k at positions pos0 + t, then k and v into the cache rows of those positions.
+// The position base is read from device memory (pos_dev) so that a captured or pre-enqueued step sees the current value.
+cudaError_t launch_rope_store(float* q, float* k, const float* v, float* cache_k, float* cache_v, const int* pos_dev,
+                              int tokens, int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches);
+// out[t][hq] = softmax(q[t][hq] . K[0..pos0+t] / sqrt(hd)) V, grouped-query heads; scratch holds the partial results of
+// the position splits (attention_scratch_floats)
+size_t attention_scratch_floats(int tokens, const WalkShape& w);
+cudaError_t launch_attention(const float* q, const float* cache_k, const float* cache_v, float* out, float* scratch,
+                             const int* pos_dev, int tokens, int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches);
+cudaError_t launch_swiglu(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches);
+cudaError_t launch_add(float* x, const float* y, int64_t n, cudaStream_t s, uint64_t* launches);
+// first index of the strict maximum of logits[0..n) -> *out_id (device; n == 0: no argmax), and *pos_dev += advance
+cudaError_t launch_argmax_advance(const float* logits, int n, int* out_id, float* out_margin, int* pos_dev, int advance,
+                                  cudaStream_t s, uint64_t* launches);
+
 // Seeded synthetic packed blocks (see llama_rust_b200/synth.py for the recipe).
 cudaError_t launch_synth(int dtype, int64_t rows, int64_t cols, uint64_t seed, uint8_t* w,
                          cudaStream_t stream, uint64_t* launches);

@@ -107,6 +107,77 @@ class Program:
             pass
 
 
+class Session:
+    """The device-resident Llama walk (llr_session_*): stands where the reference's ``Session`` stands
+    (prefill / decode), with the element-wise steps, the KV cache and the greedy argmax on the device."""
+
+    def __init__(self, executor: "Executor", cfg: dict, token_embd: Matrix, layers, output: Matrix | None = None,
+                 output_norm=None):
+        """cfg: n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab, n_ctx (+ rms_eps, rope_base);
+        layers: per layer a dict attn_q, attn_k, attn_v, attn_output, ffn_gate, ffn_up, ffn_down (Matrix) and
+        optionally attn_norm, ffn_norm (float32 arrays of n_embd; absent: all ones)."""
+        self._exec = executor
+        self._keep = []  # host arrays the C call reads during creation
+        c = _lib.LlamaConfig(*(int(cfg[k]) for k in ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff",
+                                                     "n_vocab", "n_ctx")),
+                             float(cfg.get("rms_eps", 1e-5)), float(cfg.get("rope_base", 10000.0)))
+        arr = (_lib.LlamaLayer * len(layers))()
+
+        def norm(v):
+            if v is None:
+                return None
+            a = np.ascontiguousarray(v, np.float32)
+            self._keep.append(a)
+            return a.ctypes.data
+        for i, L in enumerate(layers):
+            arr[i] = _lib.LlamaLayer(*(L[k]._h for k in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up",
+                                                         "ffn_down")), norm(L.get("attn_norm")), norm(L.get("ffn_norm")))
+        model = _lib.LlamaModel(c, token_embd._h, output._h if output is not None else None, norm(output_norm), arr)
+        h = C.c_void_p()
+        executor._check(lib().llr_session_create(executor._h, C.byref(model), C.byref(h)))
+        self._h = h.value
+        self.n_vocab = int(cfg["n_vocab"])
+        self._keep = []
+
+    def prefill(self, tokens, want_logits: bool = False):
+        t = np.ascontiguousarray(tokens, np.int32)
+        out = np.empty(self.n_vocab, np.float32) if want_logits else None
+        self._exec._check(lib().llr_session_prefill(self._h, t.ctypes.data, t.size, out.ctypes.data if want_logits else None))
+        return out
+
+    def decode(self, n_gen: int):
+        """Greedy tokens and each step's top-2 logit margin."""
+        ids = np.empty(n_gen, np.int32)
+        margin = np.empty(n_gen, np.float32)
+        self._exec._check(lib().llr_session_decode(self._h, n_gen, ids.ctypes.data, margin.ctypes.data))
+        return ids, margin
+
+    def logits(self) -> np.ndarray:
+        out = np.empty(self.n_vocab, np.float32)
+        self._exec._check(lib().llr_session_logits(self._h, out.ctypes.data, out.size))
+        return out
+
+    @property
+    def position(self) -> int:
+        p = C.c_size_t()
+        lib().llr_session_position(self._h, C.byref(p))
+        return p.value
+
+    def reset(self) -> None:
+        self._exec._check(lib().llr_session_reset(self._h))
+
+    def free(self) -> None:
+        if self._h:
+            lib().llr_session_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class Executor:
     """One device, one stream, scratch reuse and weight residency (CudaGemv, gpu.rs:139)."""
 
