@@ -213,6 +213,33 @@ def timed(stream, fn, reps):
     return e0.elapsed_time(e1) / reps
 
 
+def session_leg(ex, mats, specs_all):
+    """BASELINE config 3 as one sequence on the device-resident walk (llr_session_*): 512 random prompt tokens, then
+    128 greedy tokens.  Wall time through the C ABI with host token ids in and out; prefill with the automatic kernel
+    choice (tensor-core GEMM for the 512-row chunk), decode with the f32-faithful decode kernels."""
+    from llama_rust_b200 import Session, synth
+    cfg = dict(n_layer=N_LAYER, n_embd=D_MODEL, n_head=32, n_head_kv=8, head_dim=128, n_ff=D_FF, n_vocab=VOCAB, n_ctx=640)
+    embd = ex.synth(Q4_K, VOCAB, D_MODEL, synth.tensor_seed(0, "token_embd.weight"))
+    layers = [{t: mats[f"blk.{li}.{t}.weight"] for t, *_ in LAYER} for li in range(N_LAYER)]
+    s = Session(ex, cfg, embd, layers, output=mats["output.weight"])
+    prompt = (synth.words(7, 0, 512) % np.uint64(VOCAB)).astype(np.int32)
+    s.prefill(prompt[:8])  # warm-up of both phases
+    s.decode(4)
+    s.reset()
+    t0 = time.perf_counter()
+    s.prefill(prompt)
+    t1 = time.perf_counter()
+    ids, _ = s.decode(128)
+    t2 = time.perf_counter()
+    out = {"prefill_ms_512_tokens": (t1 - t0) * 1e3, "prefill_tok_s": 512 / (t1 - t0), "decode_ms_per_token": (t2 - t1) / 128 * 1e3,
+           "decode_tok_s": 128 / (t2 - t1), "distinct_tokens": int(len(set(ids.tolist()))),
+           "what": "llr_session_prefill + llr_session_decode: embedding, RMSNorm, RoPE, KV cache, attention, SwiGLU, argmax and the "
+                   "225 products per token on the device; one host synchronization per call"}
+    s.free()
+    embd.free()
+    return out
+
+
 def config_legs(ex, stream, peak_hbm, peaks):
     """Driver-visible numbers for BASELINE configs 1, 4 and 5 on one GPU (device time, CUDA events):
     config 1 the single Q8_0 product, config 4 the chunk GEMM (tensor-core path, 16-bit operands) for
@@ -569,6 +596,7 @@ def run_ours(args):
     if not args.no_configs and args.mode == "program":
         if world == 1:
             configs = config_legs(ex, stream, peak, peaks)
+            configs["config3_device_resident_walk"] = session_leg(ex, mats, specs_all)
         else:
             sustained = peaks.get("bf16_tflops_sustained", 1354.7)
             configs = {"config5_moe_layer_striped": moe_leg(ex, None, rank, world, peak, sustained)}

@@ -219,7 +219,10 @@ __global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, i
 // lower index), its margin over the largest other value, and the position counter advanced for the next step
 __global__ void __launch_bounds__(1024)
 argmax_kernel(const float* __restrict__ logits, int n, int* __restrict__ out_id, float* __restrict__ out_margin,
-              int* __restrict__ pos_dev, int advance) {
+              int* __restrict__ pos_dev, int advance, int* __restrict__ count_dev) {
+  // with count_dev: out_id[0] is the slot the next step reads its token from, and the token and its margin are also
+  // appended at out_id[1 + *count_dev] / out_margin[*count_dev]: every step of a generation is then the same launch
+  const int slot = count_dev ? *count_dev : 0;
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ int s_best;
@@ -261,10 +264,13 @@ argmax_kernel(const float* __restrict__ logits, int n, int* __restrict__ out_id,
       if (threadIdx.x == 0) {
         float m = -CUDART_INF_F;
         for (int w = 0; w < nw; ++w) m = fmaxf(m, sv[w]);
-        *out_margin = logits[win] - m;
+        out_margin[slot] = logits[win] - m;
       }
     }
-    if (threadIdx.x == 0) *out_id = win;
+    if (threadIdx.x == 0) {
+      out_id[0] = win;
+      if (count_dev) { out_id[1 + slot] = win; *count_dev = slot + 1; }
+    }
   }
   if (threadIdx.x == 0 && pos_dev) *pos_dev += advance;
 }
@@ -340,8 +346,8 @@ cudaError_t launch_add(float* x, const float* y, int64_t n, cudaStream_t s, uint
 }
 
 cudaError_t launch_argmax_advance(const float* logits, int n, int* out_id, float* out_margin, int* pos_dev, int advance,
-                                  cudaStream_t s, uint64_t* launches) {
-  argmax_kernel<<<1, 1024, 0, s>>>(logits, n, out_id, out_margin, pos_dev, advance);
+                                  int* count_dev, cudaStream_t s, uint64_t* launches) {
+  argmax_kernel<<<1, 1024, 0, s>>>(logits, n, out_id, out_margin, pos_dev, advance, count_dev);
   if (launches) ++*launches;
   return cudaGetLastError();
 }

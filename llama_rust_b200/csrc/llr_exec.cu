@@ -1244,8 +1244,12 @@ struct llr_session {
   float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *proj = nullptr,
         *gate = nullptr, *up = nullptr, *logits = nullptr, *cache_k = nullptr, *cache_v = nullptr, *att_scratch = nullptr,
         *margins = nullptr;
-  int *ids = nullptr, *pos_dev = nullptr;
+  int *ids = nullptr, *pos_dev = nullptr;  // ids[0]: the token the next step reads; ids[1..]: prompt chunk or generated tokens
   size_t ids_cap = 0;
+  int* count_dev = nullptr;  // tokens generated by the current llr_session_decode call
+  cudaGraphExec_t step_graph = nullptr;  // one decode step, captured once per kernel path
+  int step_graph_path = -1, step_kernels = 0;
+  bool use_graph = true;
 };
 
 namespace {
@@ -1258,6 +1262,8 @@ void session_release(llr_session* s) {
   for (float* p : bufs) if (p) cudaFree(p);
   if (s->ids) cudaFree(s->ids);
   if (s->pos_dev) cudaFree(s->pos_dev);
+  if (s->count_dev) cudaFree(s->count_dev);
+  if (s->step_graph) cudaGraphExecDestroy(s->step_graph);
   cudaGetLastError();
 }
 
@@ -1270,7 +1276,7 @@ cudaError_t session_matmul(llr_exec* e, const llr_matrix* m, size_t tokens, cons
 
 // One forward pass over `n` tokens whose ids lie at ids_dev (device) starting at the session's device-side position;
 // with_logits: the last token's logits, then argmax into *next_id (and the margin) and the position advanced by n.
-cudaError_t session_forward(llr_session* s, const int* ids_dev, size_t n, bool with_logits, int* next_id, float* margin) {
+cudaError_t session_forward(llr_session* s, const int* ids_dev, size_t n, bool with_logits, bool generate) {
   llr_exec* e = s->owner;
   const llr_llama_config& c = s->cfg;
   const size_t E = c.n_embd, QW = (size_t)c.n_head * c.head_dim, FF = c.n_ff;
@@ -1301,9 +1307,11 @@ cudaError_t session_forward(llr_session* s, const int* ids_dev, size_t n, bool w
     float* xl = s->x + (n - 1) * E;
     if ((ce = launch_rmsnorm(xl, pending ? pending + (n - 1) * E : nullptr, s->out_norm, s->xn, 1, (int)E, c.rms_eps, st, L)) != cudaSuccess) return ce;
     if ((ce = session_matmul(e, s->output, 1, s->xn, s->logits)) != cudaSuccess) return ce;
-    return launch_argmax_advance(s->logits, next_id ? (int)c.n_vocab : 0, next_id, margin, s->pos_dev, (int)n, st, L);
+    // generation: the winner goes to ids[0] (read by the next step) and to the history
+    return launch_argmax_advance(s->logits, generate ? (int)c.n_vocab : 0, s->ids, s->margins, s->pos_dev, (int)n,
+                                 generate ? s->count_dev : nullptr, st, L);
   }
-  return launch_argmax_advance(nullptr, 0, nullptr, nullptr, s->pos_dev, (int)n, st, L);
+  return launch_argmax_advance(nullptr, 0, nullptr, nullptr, s->pos_dev, (int)n, nullptr, st, L);
 }
 
 }  // namespace
@@ -1366,6 +1374,8 @@ int llr_session_create(llr_exec* e, const llr_llama_model* m, llr_session** out)
   alloc(&s->att_scratch, sc);
   if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->pos_dev, sizeof(int));
   if (ce == cudaSuccess) ce = cudaMemset(s->pos_dev, 0, sizeof(int));
+  if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->count_dev, sizeof(int));
+  if (const char* g = std::getenv("LLR_SESSION_GRAPH")) s->use_graph = std::strcmp(g, "0") != 0;
   if (ce != cudaSuccess) {
     session_release(s);
     delete s;
@@ -1407,8 +1417,8 @@ static int session_ids(llr_session* s, size_t n) {
   if (s->ids) cudaFree(s->ids);
   if (s->margins) cudaFree(s->margins);
   s->ids = nullptr; s->margins = nullptr; s->ids_cap = 0;
-  cudaError_t ce = cudaMalloc((void**)&s->ids, n * sizeof(int));
-  if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->margins, n * sizeof(float));
+  cudaError_t ce = cudaMalloc((void**)&s->ids, (n + 2) * sizeof(int));
+  if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->margins, (n + 2) * sizeof(float));
   if (ce != cudaSuccess) return fail_cuda(s->owner, ce, "token buffer");
   s->ids_cap = n;
   return LLR_OK;
@@ -1424,10 +1434,10 @@ int llr_session_prefill(llr_session* s, const int32_t* tokens, size_t n, float* 
   DeviceGuard guard(e->device);
   int rc = session_ids(s, n > 1 ? n : 1);
   if (rc) return rc;
-  cudaError_t ce = cudaMemcpyAsync(s->ids, tokens, n * sizeof(int), cudaMemcpyHostToDevice, e->stream);
+  cudaError_t ce = cudaMemcpyAsync(s->ids + 1, tokens, n * sizeof(int), cudaMemcpyHostToDevice, e->stream);
   for (size_t t0 = 0; t0 < n && ce == cudaSuccess; t0 += s->max_batch) {
     const size_t m = n - t0 < s->max_batch ? n - t0 : s->max_batch;
-    ce = session_forward(s, s->ids + t0, m, t0 + m == n, nullptr, nullptr);
+    ce = session_forward(s, s->ids + 1 + t0, m, t0 + m == n, false);
   }
   if (ce == cudaSuccess && last_logits)
     ce = cudaMemcpyAsync(last_logits, s->logits, s->cfg.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream);
@@ -1446,13 +1456,51 @@ int llr_session_decode(llr_session* s, size_t n_gen, int32_t* out_ids, float* ou
   if (!s->have_logits) return fail(e, LLR_ERR_INVALID, "decode needs logits: prefill at least one token first");
   if (s->position + n_gen > s->cfg.n_ctx) return fail(e, LLR_ERR_INVALID, "the sequence would exceed the session's context length");
   DeviceGuard guard(e->device);
-  int rc = session_ids(s, n_gen);
+  int rc = session_ids(s, n_gen + 1);
   if (rc) return rc;
-  // token i = argmax of the current logits, written to ids[i] on the device; the forward pass of step i reads it there
-  cudaError_t ce = launch_argmax_advance(s->logits, (int)s->cfg.n_vocab, s->ids, s->margins, nullptr, 0, e->stream, &e->ctr.launches);
-  for (size_t i = 0; i < n_gen && ce == cudaSuccess; ++i)
-    ce = session_forward(s, s->ids + i, 1, true, i + 1 < n_gen ? s->ids + i + 1 : nullptr, i + 1 < n_gen ? s->margins + i + 1 : nullptr);
-  if (ce == cudaSuccess) ce = cudaMemcpyAsync(out_ids, s->ids, n_gen * sizeof(int), cudaMemcpyDeviceToHost, e->stream);
+  // Token 0 = argmax of the current logits.  Every step then reads its token from ids[0], runs the walk, and its
+  // argmax writes the next token to ids[0] and appends it to the history ids[1..]; the position and the count live on
+  // the device too.  So all steps are the same sequence of launches: the second one is captured into a graph, which
+  // the remaining steps replay (several hundred launches per token otherwise cost more host time than device time).
+  cudaError_t ce = cudaMemsetAsync(s->count_dev, 0, sizeof(int), e->stream);
+  if (ce == cudaSuccess)
+    ce = launch_argmax_advance(s->logits, (int)s->cfg.n_vocab, s->ids, s->margins, nullptr, 0, s->count_dev, e->stream, &e->ctr.launches);
+  size_t done = 0;
+  if (ce == cudaSuccess) { ce = session_forward(s, s->ids, 1, true, true); ++done; }  // also initialises per-kernel launch state before any capture
+  if (ce == cudaSuccess && s->use_graph && n_gen > 2 && (!s->step_graph || s->step_graph_path != e->path)) {
+    if (s->step_graph) { cudaGraphExecDestroy(s->step_graph); s->step_graph = nullptr; }
+    cudaGraph_t graph = nullptr;
+    const uint64_t launches_before = e->ctr.launches;
+    ce = cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal);
+    if (ce == cudaSuccess) {
+      const cudaError_t fe = session_forward(s, s->ids, 1, true, true);
+      ce = cudaStreamEndCapture(e->stream, &graph);
+      if (fe != cudaSuccess) ce = fe;
+    }
+    const uint64_t captured = e->ctr.launches - launches_before;
+    e->ctr.launches = launches_before;  // captured, not launched
+    if (ce == cudaSuccess) ce = cudaGraphInstantiate(&s->step_graph, graph, 0);
+    if (graph) cudaGraphDestroy(graph);
+    if (ce != cudaSuccess) {  // fall back to plain launches
+      cudaGetLastError();
+      if (s->step_graph) { cudaGraphExecDestroy(s->step_graph); s->step_graph = nullptr; }
+      s->use_graph = false;
+      ce = cudaSuccess;
+    } else {
+      s->step_graph_path = e->path;
+      s->step_kernels = (int)captured;
+    }
+  }
+  for (; done < n_gen && ce == cudaSuccess; ++done) {
+    if (s->use_graph && s->step_graph && s->step_graph_path == e->path) {
+      ce = cudaGraphLaunch(s->step_graph, e->stream);
+      e->ctr.launches += (uint64_t)s->step_kernels;
+    } else {
+      ce = session_forward(s, s->ids, 1, true, true);
+    }
+  }
+  // the last step's argmax produced one token more than asked for: it is the next call's token 0 again
+  if (ce == cudaSuccess) ce = cudaMemcpyAsync(out_ids, s->ids + 1, n_gen * sizeof(int), cudaMemcpyDeviceToHost, e->stream);
   if (ce == cudaSuccess && out_margin) ce = cudaMemcpyAsync(out_margin, s->margins, n_gen * sizeof(float), cudaMemcpyDeviceToHost, e->stream);
   if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
   if (ce != cudaSuccess) return fail_cuda(e, ce, "decode");

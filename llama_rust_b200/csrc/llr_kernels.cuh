@@ -206,8 +206,10 @@ cudaError_t launch_attention(const float* q, const float* cache_k, const float* 
 cudaError_t launch_swiglu(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_add(float* x, const float* y, int64_t n, cudaStream_t s, uint64_t* launches);
 // first index of the strict maximum of logits[0..n) -> *out_id (device; n == 0: no argmax), and *pos_dev += advance
+// With count_dev the token also goes to out_id[1 + *count_dev], its margin to out_margin[*count_dev], and the
+// count grows by one (a generation loop whose steps are identical launches).
 cudaError_t launch_argmax_advance(const float* logits, int n, int* out_id, float* out_margin, int* pos_dev, int advance,
-                                  cudaStream_t s, uint64_t* launches);
+                                  int* count_dev, cudaStream_t s, uint64_t* launches);
 
 // Seeded synthetic packed blocks (see llama_rust_b200/synth.py for the recipe).
 cudaError_t launch_synth(int dtype, int64_t rows, int64_t cols, uint64_t seed, uint8_t* w,
