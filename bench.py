@@ -299,8 +299,9 @@ def config_legs(ex, stream, peak_hbm, peaks):
 
 def moe_leg(ex, group, rank, world, peak_hbm, sustained):
     """Routed-expert layer of BASELINE config 5 (8 experts, top-2, 4096 / 14336, Q4_K experts, F32 router) through
-    the host-buffer entry point with pinned buffers: wall ms per layer call.  world > 1: experts striped e % world,
-    partial outputs summed over the ranks; the result is compared bit for bit with the single-device layer."""
+    the host-buffer entry point with pinned buffers: wall ms per layer call.  world > 1: experts striped e % world, tokens
+    sharded, routed rows exchanged with all-to-all; every rank compares its tokens' outputs bit for bit with the
+    single-device layer."""
     import torch
     from llama_rust_b200 import DTYPES
     n_exp, d_model, d_ff = 8, 4096, 14336
@@ -313,30 +314,54 @@ def moe_leg(ex, group, rank, world, peak_hbm, sustained):
     res = {}
     layer = None
     if world > 1:
-        from llama_rust_b200.sharding import StripedExperts
-        layer = StripedExperts(ex, router, gate, up, down, 2, True, group=group)
+        from llama_rust_b200.sharding import ExpertParallelLayer, home_rank
+        keep = [home_rank(e, world) == rank for e in range(n_exp)]
+        route, experts = ExpertParallelLayer.cuda_backend(ex, router, [m if k else None for m, k in zip(gate, keep)],
+                                                          [m if k else None for m, k in zip(up, keep)],
+                                                          [m if k else None for m, k in zip(down, keep)], 2, True)
+        layer = ExpertParallelLayer(n_exp, 2, route, experts, group=group)
     for tokens in (64, 512):
-        x = torch.from_numpy(np.random.default_rng(tokens).standard_normal((tokens, d_model)).astype(np.float32)).pin_memory().numpy()
+        xs = np.random.default_rng(tokens).standard_normal((tokens, d_model)).astype(np.float32)
+        x = torch.from_numpy(xs).pin_memory().numpy()
         out = torch.empty(tokens, d_model).pin_memory().numpy()
-        call = (lambda: layer(x, device=f"cuda:{torch.cuda.current_device()}")) if layer else \
-               (lambda: ex.moe_ffn(router, gate, up, down, 2, True, x, out))
+        if layer is not None:
+            # tokens sharded over the ranks: device tensors in, device tensors out, routed rows over NCCL all-to-all
+            lo, hi = tokens * rank // world, tokens * (rank + 1) // world
+            xl = torch.from_numpy(np.ascontiguousarray(xs[lo:hi])).cuda()
+            call = lambda: layer(xl)  # noqa: E731
+        else:
+            call = lambda: ex.moe_ffn(router, gate, up, down, 2, True, x, out)  # noqa: E731
         for _ in range(2):
             call()
         n = 5
         if world > 1:
             import torch.distributed as dist
+            torch.cuda.synchronize()
             dist.barrier()
         t0 = time.perf_counter()
         for _ in range(n):
             r = call()
+        torch.cuda.synchronize()
         ms = (time.perf_counter() - t0) / n * 1e3
+        if world > 1:
+            tt = torch.tensor([ms], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
         flops = 2.0 * tokens * 2 * 3 * d_model * d_ff
         nbytes = n_exp * 3 * d_ff * 144 * (d_model // 256)
         floor_ms = max(nbytes / world / (peak_hbm * 1e9), flops / world / (sustained * 1e12)) * 1e3
         rec = {"ms_per_layer_call": ms, "TFLOP_per_s": flops / ms / 1e9, "roofline_ms": floor_ms, "frac_of_roofline": floor_ms / ms}
         if world > 1:
-            full = ex.moe_ffn(router, gate, up, down, 2, True, x)[0]
-            rec["bit_identical_to_single_device"] = bool(np.array_equal(np.asarray(r[0]), full))
+            # untimed check with the f32-faithful products, whose rows do not depend on their batch: same bits as the
+            # single-device layer on this rank's tokens (the automatic choice picks kernels by the number of rows)
+            ex.set_path(3)
+            full = ex.moe_ffn(router, gate, up, down, 2, True, xs[lo:hi])[0]
+            chk = layer(xl)[0].cpu().numpy()
+            ex.set_path(0)
+            same = torch.tensor([1 if np.array_equal(chk, full) else 0], device="cuda")
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            rec["bit_identical_to_single_device"] = bool(same.item())
+            rec["layout"] = f"tokens/{world} per rank on the device, experts e % {world}, routed rows exchanged with NCCL all-to-all"
         res[f"tokens_{tokens}"] = rec
     for m in gate + up + down + [router]:
         m.free()

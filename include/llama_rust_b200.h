@@ -313,8 +313,9 @@ int llr_program_create_sharded(llr_exec* exec, const llr_program_entry* entries,
  * top-k with ties to the lower id, weights optionally divided by max(sum, 2^-14))
  * -> grouped_routed_ffn :10006 (experts in ascending id: gather rows, gate and up
  * products, silu(g)*u, down product) -> scatter_expert_rows :10263 (out[t] += y*w)].
- * Here the routing runs on the host exactly as there, everything else on the
- * device.  router: n_expert x n_embd; gate[e], up[e]: n_ff x n_embd; down[e]:
+ * Everything runs on the device (the routing in the reference's order of operations:
+ * sequential softmax sum, ties to the lower id); only the per-expert row counts visit
+ * the host, which sizes the expert launches with them.  router: n_expert x n_embd; gate[e], up[e]: n_ff x n_embd; down[e]:
  * n_embd x n_ff (the ExpertParts of expertvm/src/store.rs:13-20, resident).
  * x: tokens*n_embd floats, out: tokens*n_embd floats (host).  sel_ids / sel_w
  * (tokens*n_used each, may be null) receive the routing decision.
@@ -332,6 +333,19 @@ typedef struct llr_moe_layer {
 } llr_moe_layer;
 int llr_moe_ffn(llr_exec* exec, const llr_moe_layer* layer, size_t tokens, const float* x, size_t x_len,
                 float* out, size_t out_len, int32_t* sel_ids, float* sel_w);
+/* The two device-pointer halves of the layer, for expert parallelism with an exchange of routed rows between
+ * ranks [the north star's all-to-all of token rows; expertvm/src/place.rs:71-75 gives the owner of an expert]:
+ * llr_moe_route_device: router product, softmax, top-k and router weights for `tokens` rows at x_dev;
+ *   ids_dev / w_dev receive tokens * n_used entries in top-k order (only layer->router, n_expert, n_used and
+ *   norm_w are read).  Enqueued on the executor's stream, no synchronization.
+ * llr_moe_experts_device: gate/up products, silu(g)*u and the down product over packed rows that are already
+ *   grouped by expert in ascending expert id: counts[e] rows for expert e (host array of n_expert entries;
+ *   experts that are not resident here must have count 0), rows_dev and y_dev sum(counts) x n_embd floats.
+ *   The caller multiplies by the router weights and adds a token's rows in ascending expert id. */
+int llr_moe_route_device(llr_exec* exec, const llr_moe_layer* layer, size_t tokens, const float* x_dev,
+                         int32_t* ids_dev, float* w_dev);
+int llr_moe_experts_device(llr_exec* exec, const llr_moe_layer* layer, const uint32_t* counts,
+                           const float* rows_dev, float* y_dev);
 
 /* ---- device-resident Llama walk ------------------------------------------------------
  * The per-token walk of the plain llama architecture with everything on the device

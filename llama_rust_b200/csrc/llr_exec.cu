@@ -798,141 +798,100 @@ cudaError_t matmul_dev(llr_exec* e, const llr_matrix* m, size_t tokens, const fl
 
 }  // namespace
 
-int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float* x, size_t x_len, float* out,
-                size_t out_len, int32_t* sel_ids, float* sel_w) {
-  if (!e) return LLR_ERR_INVALID;
-  if (!L || !L->router || !L->gate || !L->up || !L->down || L->n_expert == 0 || L->n_used == 0 ||
+namespace {
+
+// Shapes and residency of a routed-expert layer, checked once per call.
+struct MoeShape {
+  size_t n_embd = 0, n_ff = 0, n_exp = 0, n_used = 0;
+  std::vector<unsigned char> local;  // expert resident on this executor
+  bool any_remote = false;
+};
+
+int moe_check_layer(llr_exec* e, const llr_moe_layer* L, bool need_router, MoeShape* S) {
+  if (!L || (need_router && !L->router) || !L->gate || !L->up || !L->down || L->n_expert == 0 || L->n_used == 0 ||
       L->n_used > L->n_expert || L->n_expert > 4096)
     return fail(e, LLR_ERR_INVALID, "expert_used_count");
-  int rc = check_matrix(e, L->router);
-  if (rc) return rc;
-  const size_t n_embd = (size_t)L->router->cols, n_exp = L->n_expert, n_used = L->n_used;
-  if ((size_t)L->router->rows != n_exp || n_embd % 4 != 0) return fail(e, LLR_ERR_INVALID, "ffn_gate_inp shape");
+  int rc;
+  S->n_exp = L->n_expert;
+  S->n_used = L->n_used;
+  if (need_router) {
+    if ((rc = check_matrix(e, L->router))) return rc;
+    S->n_embd = (size_t)L->router->cols;
+    if ((size_t)L->router->rows != S->n_exp || S->n_embd % 4 != 0) return fail(e, LLR_ERR_INVALID, "ffn_gate_inp shape");
+  }
   // An expert whose three matrices are all null lives on another rank (experts striped over GPUs):
   // it takes part in the routing, its rows are not computed here and contribute zero to `out`.
-  size_t n_ff = 0;
-  bool any_remote = false;
-  std::vector<char> local(n_exp, 1);
-  for (size_t i = 0; i < n_exp; ++i) {
-    if (!L->gate[i] && !L->up[i] && !L->down[i]) { local[i] = 0; any_remote = true; continue; }
+  S->local.assign(S->n_exp, 1);
+  for (size_t i = 0; i < S->n_exp; ++i) {
+    if (!L->gate[i] && !L->up[i] && !L->down[i]) { S->local[i] = 0; S->any_remote = true; continue; }
     if ((rc = check_matrix(e, L->gate[i])) || (rc = check_matrix(e, L->up[i])) || (rc = check_matrix(e, L->down[i]))) return rc;
-    if (n_ff == 0) n_ff = (size_t)L->gate[i]->rows;
-    if ((size_t)L->gate[i]->rows != n_ff || (size_t)L->gate[i]->cols != n_embd || (size_t)L->up[i]->rows != n_ff ||
-        (size_t)L->up[i]->cols != n_embd || (size_t)L->down[i]->rows != n_embd || (size_t)L->down[i]->cols != n_ff)
+    if (S->n_ff == 0) S->n_ff = (size_t)L->gate[i]->rows;
+    if (S->n_embd == 0) S->n_embd = (size_t)L->gate[i]->cols;
+    if ((size_t)L->gate[i]->rows != S->n_ff || (size_t)L->gate[i]->cols != S->n_embd || (size_t)L->up[i]->rows != S->n_ff ||
+        (size_t)L->up[i]->cols != S->n_embd || (size_t)L->down[i]->rows != S->n_embd || (size_t)L->down[i]->cols != S->n_ff)
       return fail(e, LLR_ERR_INVALID, "expert matrix shapes do not match the layer");
   }
-  if (n_ff == 0) return fail(e, LLR_ERR_INVALID, "no expert of the layer is resident on this executor");
-  size_t nx = 0;
-  if (tokens == 0 || !mul_ok(tokens, n_embd, &nx) || x_len != nx || out_len != nx || !x || !out || tokens > (1u << 24))
-    return fail(e, LLR_ERR_INVALID, "matrix dimensions must be positive and token-aligned");
-  DeviceGuard guard(e->device);
-  const size_t n_rows = tokens * n_used;
-  // device workspace, one block: x | logits | packed x | g | u | y | out | int tables | weights
-  const size_t f_x = nx, f_logits = tokens * n_exp, f_pack = n_rows * n_embd, f_g = n_rows * n_ff, f_y = n_rows * n_embd;
-  // grouped tensor-core path: 16-bit copies of the packed activations and of silu(g)*u, one scale per row, descriptors
-  const size_t f_x16 = (f_pack + f_g) / 2 + 2 * n_rows + 512, f_desc = gemm_tc_group_desc_bytes((int)(2 * n_exp)) / 4 + 64;
-  const size_t floats = f_x + f_logits + f_pack + 2 * f_g + f_y + nx + n_rows /*w*/ + 2 * n_rows /*int tables*/ + 64 + f_x16 + f_desc;
-  cudaError_t ce;
-  if ((ce = grow_device(&e->dev_moe, &e->dev_moe_cap, floats)) != cudaSuccess) return fail_cuda(e, ce, "expert workspace");
-  float* d_x = e->dev_moe;
-  float* d_logits = d_x + f_x;
-  float* d_pack = d_logits + ((f_logits + 3) & ~(size_t)3);
-  float* d_g = d_pack + f_pack;
-  float* d_u = d_g + f_g;
-  float* d_y = d_u + f_g;
-  float* d_out = d_y + f_y;
-  float* d_w = d_out + nx;
-  int* d_tok_of_row = (int*)(d_w + n_rows);
-  int* d_rows_of_tok = d_tok_of_row + n_rows;
+  if (S->n_ff == 0) return fail(e, LLR_ERR_INVALID, "no expert of the layer is resident on this executor");
+  return LLR_OK;
+}
+
+// Device workspace of the expert products for n_rows packed rows, carved from one block.
+struct MoeBuffers {
+  float *g, *u, *y;        // gate / up results (n_rows x n_ff), down results (n_rows x n_embd)
+  float* pack;             // packed f32 rows (n_rows x n_embd) when the rows have to be gathered first
+  char *x16a, *x16b;       // 16-bit operand copies for the grouped tensor-core launches
+  float *sa, *sb;          // their per-row scales
+  void* desc;              // descriptors of a grouped launch
+};
+size_t moe_buffer_floats(const MoeShape& S, size_t n_rows) {
+  const size_t f_pack = n_rows * S.n_embd, f_g = n_rows * S.n_ff;
+  return f_pack + 2 * f_g + f_pack + (f_pack + f_g) / 2 + 2 * n_rows + 1024 + gemm_tc_group_desc_bytes((int)(2 * S.n_exp)) / 4 + 64;
+}
+MoeBuffers moe_carve(float* base, const MoeShape& S, size_t n_rows) {
   auto align256 = [](void* p) { return (char*)(((uintptr_t)p + 255) & ~(uintptr_t)255); };
-  char* d_x16a = align256(d_rows_of_tok + n_rows);           // n_rows x n_embd, 16-bit
-  char* d_x16b = align256(d_x16a + n_rows * n_embd * 2);     // n_rows x n_ff, 16-bit
-  float* d_sa = (float*)align256(d_x16b + n_rows * n_ff * 2);
-  float* d_sb = d_sa + n_rows;
-  void* d_desc = align256(d_sb + n_rows);
-  if ((ce = cudaMemcpyAsync(d_x, x, nx * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess) return fail_cuda(e, ce, "activation upload");
-  // router product (decode.rs:9977), then routing on the host as the reference does
-  if (L->router->dtype == DT_F32 && ((uintptr_t)L->router->dev & 15) == 0)
-    ce = launch_router_logits((const float*)L->router->dev, d_x, d_logits, (int)tokens, (int)n_exp, (int)n_embd, e->stream,
-                              &e->ctr.launches);
-  else
-    ce = matmul_dev(e, L->router, tokens, d_x, d_logits, PATH_MMA);
-  if (ce != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
-  std::vector<float> logits(tokens * n_exp);
-  if ((ce = cudaMemcpyAsync(logits.data(), d_logits, logits.size() * 4, cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
-      (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)
-    return fail_cuda(e, ce, "router download");
-  std::vector<int32_t> ids(n_rows);
-  std::vector<float> wts(n_rows);
-  std::vector<std::vector<int>> buckets(n_exp);
-  std::vector<char> used(n_exp);
-  for (size_t t = 0; t < tokens; ++t) {
-    float* row = logits.data() + t * n_exp;
-    float mx = -INFINITY;  // softmax, decode.rs:12021
-    for (size_t i = 0; i < n_exp; ++i) mx = std::fmax(mx, row[i]);
-    float sum = 0.0f;
-    for (size_t i = 0; i < n_exp; ++i) { row[i] = std::exp(row[i] - mx); sum += row[i]; }
-    if (sum > 0.0f) for (size_t i = 0; i < n_exp; ++i) row[i] /= sum;
-    std::fill(used.begin(), used.end(), 0);
-    float wsum = 0.0f;
-    for (size_t j = 0; j < n_used; ++j) {  // top-k: descending value, ties to the lower index (:11363)
-      int best = -1;
-      for (size_t i = 0; i < n_exp; ++i)
-        if (!used[i] && (best < 0 || row[i] > row[best])) best = (int)i;
-      used[(size_t)best] = 1;
-      ids[t * n_used + j] = best;
-      wts[t * n_used + j] = row[best];
-      wsum += row[best];
-    }
-    if (L->norm_w) {  // fill_router_weights :11392, clamp 2^-14 :321
-      if (wsum < 1.0f / 16384.0f) wsum = 1.0f / 16384.0f;
-      for (size_t j = 0; j < n_used; ++j) wts[t * n_used + j] /= wsum;
-    }
-    for (size_t j = 0; j < n_used; ++j) buckets[(size_t)ids[t * n_used + j]].push_back((int)t);
-  }
-  // packed rows: experts ascending, tokens ascending inside an expert (grouped_routed_ffn :10006)
-  std::vector<int> tok_of_row(n_rows), rows_of_tok(n_rows, 0), fill(tokens, 0), first_row(n_exp + 1, 0);
-  std::vector<float> w_of_tok(n_rows, 0.0f);
-  size_t r = 0;
-  for (size_t ex = 0; ex < n_exp; ++ex) {
-    first_row[ex] = (int)r;
-    for (int t : buckets[ex]) {
-      tok_of_row[r] = t;
-      float w = 0.0f;
-      for (size_t j = 0; j < n_used; ++j)
-        if ((size_t)ids[(size_t)t * n_used + j] == ex) { w = wts[(size_t)t * n_used + j]; break; }
-      const int slot = fill[(size_t)t]++;  // ascending expert id = the reference's accumulation order
-      rows_of_tok[(size_t)t * n_used + slot] = (int)r;
-      w_of_tok[(size_t)t * n_used + slot] = local[ex] ? w : 0.0f;
-      ++r;
-    }
-  }
-  first_row[n_exp] = (int)r;
-  if ((ce = cudaMemcpyAsync(d_tok_of_row, tok_of_row.data(), n_rows * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess ||
-      (ce = cudaMemcpyAsync(d_rows_of_tok, rows_of_tok.data(), n_rows * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess ||
-      (ce = cudaMemcpyAsync(d_w, w_of_tok.data(), n_rows * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess ||
-      (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)  // the host vectors go out of scope later, but keep it simple
-    return fail_cuda(e, ce, "routing upload");
-  if (any_remote && (ce = cudaMemsetAsync(d_y, 0, f_y * 4, e->stream)) != cudaSuccess)  // rows nobody computes here
-    return fail_cuda(e, ce, "expert workspace");
+  MoeBuffers B;
+  B.pack = base;
+  B.g = B.pack + n_rows * S.n_embd;
+  B.u = B.g + n_rows * S.n_ff;
+  B.y = B.u + n_rows * S.n_ff;
+  B.x16a = align256(B.y + n_rows * S.n_embd);
+  B.x16b = align256(B.x16a + n_rows * S.n_embd * 2);
+  B.sa = (float*)align256(B.x16b + n_rows * S.n_ff * 2);
+  B.sb = B.sa + n_rows;
+  B.desc = align256(B.sb + n_rows);
+  return B;
+}
+
+// The expert products over packed rows (grouped_routed_ffn decode.rs:10006-10290 without the scatter): rows
+// [first_row[ex], first_row[ex+1]) belong to expert ex.  The rows are x[tok_of_row[r]] when tok_of_row is given
+// (device), else x itself is the packed matrix.  Results: B.y, packed the same way; rows of experts that are not
+// resident here are zero.
+cudaError_t moe_run_experts(llr_exec* e, const llr_moe_layer* L, const MoeShape& S, const std::vector<int>& first_row,
+                            const float* d_x, const int* d_tok_of_row, const MoeBuffers& B) {
+  const size_t n_exp = S.n_exp, n_embd = S.n_embd, n_ff = S.n_ff;
+  const size_t n_rows = (size_t)first_row[n_exp];
+  cudaError_t ce = cudaSuccess;
+  if (n_rows == 0) return ce;
+  if (S.any_remote && (ce = cudaMemsetAsync(B.y, 0, n_rows * n_embd * 4, e->stream)) != cudaSuccess) return ce;  // rows nobody computes here
   {  // size the GEMM staging buffer once, for the busiest expert's widest product: growing it between
      // launches would free and reallocate, which synchronizes the device
     size_t busiest = 0, most = 0;
     for (size_t ex = 0; ex < n_exp; ++ex)
-      if (local[ex] && (size_t)(first_row[ex + 1] - first_row[ex]) > most) { most = (size_t)(first_row[ex + 1] - first_row[ex]); busiest = ex; }
+      if (S.local[ex] && (size_t)(first_row[ex + 1] - first_row[ex]) > most) { most = (size_t)(first_row[ex + 1] - first_row[ex]); busiest = ex; }
     void* unused = nullptr;
     if (most > 0 && ((ce = ensure_scratch(e, L->down[busiest], most, &unused)) != cudaSuccess ||
                      (ce = ensure_scratch(e, L->gate[busiest], most, &unused)) != cudaSuccess))
-      return fail_cuda(e, ce, "kernel scratch");
+      return ce;
+    if (most == 0) return cudaSuccess;  // nothing routed to a resident expert
   }
   // Grouped tensor-core path (automatic choice, 64 routed rows or more, formats the GEMM takes): the tiles of
   // all experts' gate and up products in one launch, silu(g)*u, all down products in one launch.
   bool grouped = e->path == PATH_AUTO && n_rows >= 64;
   int f16a = 1, f16b = 1;
   size_t first_local = 0;
-  while (!local[first_local]) ++first_local;
+  while (!S.local[first_local]) ++first_local;
   for (size_t ex = 0; ex < n_exp && grouped; ++ex) {
-    if (!local[ex]) continue;
+    if (!S.local[ex]) continue;
     const MatView vg = view_of(L->gate[ex]), vu = view_of(L->up[ex]), vd = view_of(L->down[ex]);
     grouped = gemm_tc_supported(vg, 16) && gemm_tc_supported(vu, 16) && gemm_tc_supported(vd, 16) &&
               vg.dtype == view_of(L->gate[first_local]).dtype && vu.dtype == vg.dtype &&
@@ -940,52 +899,116 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
     if (vg.f16_ok != 1 || vu.f16_ok != 1) f16a = 0;
     if (vd.f16_ok != 1) f16b = 0;
   }
-  bool any_local_rows = false;
-  for (size_t ex = 0; ex < n_exp; ++ex) any_local_rows = any_local_rows || (local[ex] && first_row[ex + 1] > first_row[ex]);
-  if (!any_local_rows) grouped = false;  // nothing routed to a resident expert: the loops below do nothing either
-  // the grouped path gathers and converts in one kernel and never needs the packed f32 rows
-  if (!grouped && (ce = launch_gather_rows(d_x, d_tok_of_row, d_pack, (int)n_rows, (int)n_embd, e->stream, &e->ctr.launches)) != cudaSuccess)
-    return fail_cuda(e, ce, "kernel launch");
+  const float* rows_f32 = d_x;  // packed f32 rows for the per-expert path
+  if (!grouped && d_tok_of_row) {
+    if ((ce = launch_gather_rows(d_x, d_tok_of_row, B.pack, (int)n_rows, (int)n_embd, e->stream, &e->ctr.launches)) != cudaSuccess) return ce;
+    rows_f32 = B.pack;
+  }
   if (grouped) {
     std::vector<GemmGroupSpec> specs;
     for (size_t ex = 0; ex < n_exp; ++ex) {
       const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
-      if (n == 0 || !local[ex]) continue;
-      specs.push_back(GemmGroupSpec{view_of(L->gate[ex]), d_x16a + r0 * n_embd * 2, d_sa + r0, d_g + r0 * n_ff, (int)n});
-      specs.push_back(GemmGroupSpec{view_of(L->up[ex]), d_x16a + r0 * n_embd * 2, d_sa + r0, d_u + r0 * n_ff, (int)n});
+      if (n == 0 || !S.local[ex]) continue;
+      specs.push_back(GemmGroupSpec{view_of(L->gate[ex]), B.x16a + r0 * n_embd * 2, B.sa + r0, B.g + r0 * n_ff, (int)n});
+      specs.push_back(GemmGroupSpec{view_of(L->up[ex]), B.x16a + r0 * n_embd * 2, B.sa + r0, B.u + r0 * n_ff, (int)n});
     }
-    if ((ce = tc_convert_expert_rows(d_x, d_tok_of_row, (int64_t)n_rows, (int)n_embd, f16a != 0, d_x16a, d_sa, e->stream,
-                                     &e->ctr.launches)) != cudaSuccess ||
-        (ce = launch_gemm_tc_grouped(specs.data(), (int)specs.size(), f16a != 0, d_desc, e->stream, e->err_flag, &e->ctr.launches)) != cudaSuccess ||
-        (ce = launch_silu_mul(d_g, d_u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess)
-      return fail_cuda(e, ce, "kernel launch");
+    // the gather of the routed rows is part of the 16-bit conversion
+    if (d_tok_of_row) ce = tc_convert_expert_rows(d_x, d_tok_of_row, (int64_t)n_rows, (int)n_embd, f16a != 0, B.x16a, B.sa, e->stream, &e->ctr.launches);
+    else ce = tc_convert_activations(d_x, (int64_t)n_rows, (int)n_embd, f16a != 0, B.x16a, B.sa, e->stream, &e->ctr.launches);
+    if (ce != cudaSuccess ||
+        (ce = launch_gemm_tc_grouped(specs.data(), (int)specs.size(), f16a != 0, B.desc, e->stream, e->err_flag, &e->ctr.launches)) != cudaSuccess ||
+        (ce = launch_silu_mul(B.g, B.u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess)
+      return ce;
     specs.clear();
     for (size_t ex = 0; ex < n_exp; ++ex) {
       const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
-      if (n == 0 || !local[ex]) continue;
-      specs.push_back(GemmGroupSpec{view_of(L->down[ex]), d_x16b + r0 * n_ff * 2, d_sb + r0, d_y + r0 * n_embd, (int)n});
+      if (n == 0 || !S.local[ex]) continue;
+      specs.push_back(GemmGroupSpec{view_of(L->down[ex]), B.x16b + r0 * n_ff * 2, B.sb + r0, B.y + r0 * n_embd, (int)n});
     }
     // the descriptor buffer is reused: stream order puts this copy after the first grouped launch
-    if ((ce = tc_convert_activations(d_g, (int64_t)n_rows, (int)n_ff, f16b != 0, d_x16b, d_sb, e->stream, &e->ctr.launches)) != cudaSuccess ||
-        (ce = launch_gemm_tc_grouped(specs.data(), (int)specs.size(), f16b != 0, d_desc, e->stream, e->err_flag, &e->ctr.launches)) != cudaSuccess)
-      return fail_cuda(e, ce, "kernel launch");
+    if ((ce = tc_convert_activations(B.g, (int64_t)n_rows, (int)n_ff, f16b != 0, B.x16b, B.sb, e->stream, &e->ctr.launches)) != cudaSuccess ||
+        (ce = launch_gemm_tc_grouped(specs.data(), (int)specs.size(), f16b != 0, B.desc, e->stream, e->err_flag, &e->ctr.launches)) != cudaSuccess)
+      return ce;
+    return cudaSuccess;
   }
-  for (size_t ex = 0; ex < n_exp && !grouped; ++ex) {
+  for (size_t ex = 0; ex < n_exp; ++ex) {
     const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
-    if (n == 0 || !local[ex]) continue;
-    if ((ce = matmul_dev(e, L->gate[ex], n, d_pack + r0 * n_embd, d_g + r0 * n_ff, expert_path(e, n))) != cudaSuccess ||
-        (ce = matmul_dev(e, L->up[ex], n, d_pack + r0 * n_embd, d_u + r0 * n_ff, expert_path(e, n))) != cudaSuccess)
-      return fail_cuda(e, ce, "kernel launch");
+    if (n == 0 || !S.local[ex]) continue;
+    if ((ce = matmul_dev(e, L->gate[ex], n, rows_f32 + r0 * n_embd, B.g + r0 * n_ff, expert_path(e, n))) != cudaSuccess ||
+        (ce = matmul_dev(e, L->up[ex], n, rows_f32 + r0 * n_embd, B.u + r0 * n_ff, expert_path(e, n))) != cudaSuccess)
+      return ce;
   }
-  if (!grouped && any_local_rows && (ce = launch_silu_mul(d_g, d_u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess)
+  if ((ce = launch_silu_mul(B.g, B.u, (int64_t)(n_rows * n_ff), e->stream, &e->ctr.launches)) != cudaSuccess) return ce;
+  for (size_t ex = 0; ex < n_exp; ++ex) {
+    const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
+    if (n == 0 || !S.local[ex]) continue;
+    if ((ce = matmul_dev(e, L->down[ex], n, B.g + r0 * n_ff, B.y + r0 * n_embd, expert_path(e, n))) != cudaSuccess) return ce;
+  }
+  return cudaSuccess;
+}
+
+// Router product and routing on the device: ids / wts (tokens x n_used, top-k order) in device memory.
+cudaError_t moe_route(llr_exec* e, const llr_moe_layer* L, const MoeShape& S, size_t tokens, const float* d_x, float* d_logits,
+                      int* d_ids, float* d_wts) {
+  cudaError_t ce;
+  // router product (decode.rs:9977)
+  if (L->router->dtype == DT_F32 && ((uintptr_t)L->router->dev & 15) == 0)
+    ce = launch_router_logits((const float*)L->router->dev, d_x, d_logits, (int)tokens, (int)S.n_exp, (int)S.n_embd, e->stream,
+                              &e->ctr.launches);
+  else
+    ce = matmul_dev(e, L->router, tokens, d_x, d_logits, PATH_MMA);
+  if (ce != cudaSuccess) return ce;
+  return launch_route(d_logits, (int)tokens, (int)S.n_exp, (int)S.n_used, (int)L->norm_w, d_ids, d_wts, e->stream, &e->ctr.launches);
+}
+
+}  // namespace
+
+int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float* x, size_t x_len, float* out,
+                size_t out_len, int32_t* sel_ids, float* sel_w) {
+  if (!e) return LLR_ERR_INVALID;
+  MoeShape S;
+  int rc = moe_check_layer(e, L, true, &S);
+  if (rc) return rc;
+  const size_t n_embd = S.n_embd, n_exp = S.n_exp, n_used = S.n_used;
+  size_t nx = 0;
+  if (tokens == 0 || !mul_ok(tokens, n_embd, &nx) || x_len != nx || out_len != nx || !x || !out || tokens > (1u << 24))
+    return fail(e, LLR_ERR_INVALID, "matrix dimensions must be positive and token-aligned");
+  DeviceGuard guard(e->device);
+  const size_t n_rows = tokens * n_used;
+  // device workspace, one block: x | logits | out | routing tables | expert buffers
+  const size_t f_logits = (tokens * n_exp + 3) & ~(size_t)3;
+  const size_t f_tables = 6 * n_rows + tokens + n_exp + 64;  // ids, wts, tok_of_row, rows_of_tok, w_of_tok, fill, first_row, local
+  const size_t floats = nx + f_logits + nx + f_tables + moe_buffer_floats(S, n_rows) + 256;
+  cudaError_t ce;
+  if ((ce = grow_device(&e->dev_moe, &e->dev_moe_cap, floats)) != cudaSuccess) return fail_cuda(e, ce, "expert workspace");
+  float* d_x = e->dev_moe;
+  float* d_logits = d_x + nx;
+  float* d_out = d_logits + f_logits;
+  int* d_ids = (int*)(d_out + nx);
+  float* d_wts = (float*)(d_ids + n_rows);
+  int* d_tok_of_row = (int*)(d_wts + n_rows);
+  int* d_rows_of_tok = d_tok_of_row + n_rows;
+  float* d_w = (float*)(d_rows_of_tok + n_rows);
+  int* d_fill = (int*)(d_w + n_rows);
+  int* d_first_row = d_fill + tokens;
+  unsigned char* d_local = (unsigned char*)(d_first_row + n_exp + 1);
+  float* d_expert = (float*)(((uintptr_t)(d_local + n_exp) + 255) & ~(uintptr_t)255);
+  const MoeBuffers B = moe_carve(d_expert, S, n_rows);
+  if ((ce = cudaMemcpyAsync(d_x, x, nx * 4, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess ||
+      (ce = cudaMemcpyAsync(d_local, S.local.data(), n_exp, cudaMemcpyHostToDevice, e->stream)) != cudaSuccess)
+    return fail_cuda(e, ce, "activation upload");
+  // Routing stays on the device: softmax, top-k and the router weights per token, then the packed row order of the
+  // grouped products.  Only the per-expert row counts come back to the host, which needs them to size the launches.
+  if ((ce = moe_route(e, L, S, tokens, d_x, d_logits, d_ids, d_wts)) != cudaSuccess ||
+      (ce = launch_bucket(d_ids, d_wts, d_local, (int)tokens, (int)n_exp, (int)n_used, d_first_row, d_tok_of_row, d_rows_of_tok, d_w,
+                          d_fill, e->stream, &e->ctr.launches)) != cudaSuccess)
     return fail_cuda(e, ce, "kernel launch");
-  for (size_t ex = 0; ex < n_exp && !grouped; ++ex) {
-    const size_t r0 = (size_t)first_row[ex], n = (size_t)first_row[ex + 1] - r0;
-    if (n == 0 || !local[ex]) continue;
-    if ((ce = matmul_dev(e, L->down[ex], n, d_g + r0 * n_ff, d_y + r0 * n_embd, expert_path(e, n))) != cudaSuccess)
-      return fail_cuda(e, ce, "kernel launch");
-  }
-  if ((ce = launch_scatter_combine(d_y, d_rows_of_tok, d_w, d_out, (int)tokens, (int)n_used, (int)n_embd, e->stream,
+  std::vector<int> first_row(n_exp + 1, 0);
+  if ((ce = cudaMemcpyAsync(first_row.data(), d_first_row, (n_exp + 1) * sizeof(int), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
+      (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)
+    return fail_cuda(e, ce, "routing counts");
+  if ((ce = moe_run_experts(e, L, S, first_row, d_x, d_tok_of_row, B)) != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
+  if ((ce = launch_scatter_combine(B.y, d_rows_of_tok, d_w, d_out, (int)tokens, (int)n_used, (int)n_embd, e->stream,
                                    &e->ctr.launches)) != cudaSuccess)
     return fail_cuda(e, ce, "kernel launch");
   const bool out_pinned = is_pinned_host(e, out);  // a pinned result buffer is written directly
@@ -994,7 +1017,11 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
     if ((ce = grow_pinned(&e->pin_y, &e->pin_y_cap, nx)) != cudaSuccess) return fail_cuda(e, ce, "pinned result staging");
     dst = e->pin_y;
   }
+  std::vector<int32_t> ids(sel_ids ? n_rows : 0);
+  std::vector<float> wts(sel_w ? n_rows : 0);
   if ((ce = cudaMemcpyAsync(dst, d_out, nx * 4, cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
+      (sel_ids && (ce = cudaMemcpyAsync(ids.data(), d_ids, n_rows * 4, cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess) ||
+      (sel_w && (ce = cudaMemcpyAsync(wts.data(), d_wts, n_rows * 4, cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess) ||
       (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)
     return fail_cuda(e, ce, "result download");
   if (take_device_error(e) != 0) {
@@ -1003,8 +1030,56 @@ int llr_moe_ffn(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float*
   if (!out_pinned) std::memcpy(out, e->pin_y, nx * 4);
   if (sel_ids) std::memcpy(sel_ids, ids.data(), n_rows * 4);
   if (sel_w) std::memcpy(sel_w, wts.data(), n_rows * 4);
-  e->ctr.h2d_bytes += nx * 4 + 3 * n_rows * 4;
-  e->ctr.d2h_bytes += nx * 4 + logits.size() * 4;
+  e->ctr.h2d_bytes += nx * 4 + n_exp;
+  e->ctr.d2h_bytes += nx * 4 + (n_exp + 1) * 4 + (sel_ids ? n_rows * 4 : 0) + (sel_w ? n_rows * 4 : 0);
+  return LLR_OK;
+}
+
+// Device-pointer pieces of the layer, for callers that keep tokens on the device and exchange routed rows between
+// ranks themselves (experts striped over GPUs).
+int llr_moe_route_device(llr_exec* e, const llr_moe_layer* L, size_t tokens, const float* x_dev, int32_t* ids_dev, float* w_dev) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!L || !L->router || L->n_expert == 0 || L->n_used == 0 || L->n_used > L->n_expert || L->n_expert > 4096)
+    return fail(e, LLR_ERR_INVALID, "expert_used_count");
+  int rc = check_matrix(e, L->router);
+  if (rc) return rc;
+  MoeShape S;
+  S.n_exp = L->n_expert; S.n_used = L->n_used; S.n_embd = (size_t)L->router->cols;
+  if ((size_t)L->router->rows != S.n_exp || S.n_embd % 4 != 0) return fail(e, LLR_ERR_INVALID, "ffn_gate_inp shape");
+  if (tokens == 0 || tokens > (1u << 24) || !x_dev || !ids_dev || !w_dev || ((uintptr_t)x_dev & 15) != 0)
+    return fail(e, LLR_ERR_INVALID, "matrix dimensions must be positive and token-aligned");
+  DeviceGuard guard(e->device);
+  cudaError_t ce;
+  const size_t f_logits = tokens * S.n_exp;
+  if ((ce = grow_device(&e->dev_y, &e->dev_y_cap, f_logits)) != cudaSuccess) return fail_cuda(e, ce, "router scratch");
+  if ((ce = moe_route(e, L, S, tokens, x_dev, e->dev_y, (int*)ids_dev, w_dev)) != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
+  return LLR_OK;
+}
+
+int llr_moe_experts_device(llr_exec* e, const llr_moe_layer* L, const uint32_t* counts, const float* rows_dev, float* y_dev) {
+  if (!e) return LLR_ERR_INVALID;
+  MoeShape S;
+  int rc = moe_check_layer(e, L, false, &S);
+  if (rc) return rc;
+  if (!counts || !rows_dev || !y_dev || ((uintptr_t)rows_dev & 15) != 0 || ((uintptr_t)y_dev & 15) != 0)
+    return fail(e, LLR_ERR_INVALID, "null or unaligned buffer");
+  std::vector<int> first_row(S.n_exp + 1, 0);
+  size_t total = 0;
+  for (size_t ex = 0; ex < S.n_exp; ++ex) {
+    if (counts[ex] != 0 && !S.local[ex]) return fail(e, LLR_ERR_INVALID, "rows for expert " + std::to_string(ex) + ", which is not resident on this executor");
+    total += counts[ex];
+    if (total > (1u << 24)) return fail(e, LLR_ERR_INVALID, "too many routed rows");
+    first_row[ex + 1] = (int)total;
+  }
+  if (total == 0) return LLR_OK;
+  DeviceGuard guard(e->device);
+  cudaError_t ce;
+  if ((ce = grow_device(&e->dev_moe, &e->dev_moe_cap, moe_buffer_floats(S, total) + 256)) != cudaSuccess) return fail_cuda(e, ce, "expert workspace");
+  const MoeBuffers B = moe_carve((float*)(((uintptr_t)e->dev_moe + 255) & ~(uintptr_t)255), S, total);
+  S.any_remote = false;  // every row given here belongs to a resident expert
+  if ((ce = moe_run_experts(e, L, S, first_row, rows_dev, nullptr, B)) != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
+  if ((ce = cudaMemcpyAsync(y_dev, B.y, total * S.n_embd * 4, cudaMemcpyDeviceToDevice, e->stream)) != cudaSuccess)
+    return fail_cuda(e, ce, "result copy");
   return LLR_OK;
 }
 

@@ -177,6 +177,12 @@ cudaError_t launch_silu_mul(float* g, const float* u, int64_t n, cudaStream_t s,
 // logits[t*n_expert + e] = dot(w[e], x[t]) for an F32 router matrix (n_embd % 4 == 0, 16-byte aligned)
 cudaError_t launch_router_logits(const float* w, const float* x, float* logits, int tokens, int n_expert, int n_embd,
                                  cudaStream_t s, uint64_t* launches);
+// Routing on the device: softmax / top-k / weights per token in place on the logits, then the packed row order
+cudaError_t launch_route(float* logits, int tokens, int n_expert, int n_used, int norm_w, int* ids, float* wts,
+                         cudaStream_t s, uint64_t* launches);
+cudaError_t launch_bucket(const int* ids, const float* wts, const unsigned char* local, int tokens, int n_expert, int n_used,
+                          int* first_row, int* tok_of_row, int* rows_of_tok, float* w_of_tok, int* fill, cudaStream_t s,
+                          uint64_t* launches);
 cudaError_t launch_scatter_combine(const float* y, const int* rows_of_tok, const float* w_of_tok, float* out,
                                    int tokens, int n_used, int n_embd, cudaStream_t s, uint64_t* launches);
 

@@ -78,7 +78,103 @@ __global__ void scatter_combine_kernel(const float* __restrict__ y, const int* _
   }
 }
 
+// Routing of one token per thread, in place on its row of router logits, exactly the reference's sequence
+// (route_softmax_tokens decode.rs:9969: softmax :12021 with a sequential sum, topk_into :11363 with ties to the
+// lower id, fill_router_weights :11392 with the 2^-14 clamp :321).  ids / wts: n_used per token, in top-k order.
+__global__ void route_kernel(float* __restrict__ logits, int tokens, int n_expert, int n_used, int norm_w,
+                             int* __restrict__ ids, float* __restrict__ wts) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  float* row = logits + (int64_t)t * n_expert;
+  float mx = -INFINITY;
+  for (int i = 0; i < n_expert; ++i) mx = fmaxf(mx, row[i]);
+  float sum = 0.0f;
+  for (int i = 0; i < n_expert; ++i) { const float e = expf(row[i] - mx); row[i] = e; sum = __fadd_rn(sum, e); }
+  if (sum > 0.0f) for (int i = 0; i < n_expert; ++i) row[i] = __fdiv_rn(row[i], sum);
+  float wsum = 0.0f;
+  for (int j = 0; j < n_used; ++j) {
+    int best = -1;
+    float bv = 0.0f;
+    for (int i = 0; i < n_expert; ++i) {
+      const float v = row[i];
+      if (v == -1.0f) continue;  // taken (probabilities are never negative)
+      if (best < 0 || v > bv) { best = i; bv = v; }
+    }
+    ids[t * n_used + j] = best;
+    wts[t * n_used + j] = bv;
+    wsum = __fadd_rn(wsum, bv);
+    row[best] = -1.0f;
+  }
+  if (norm_w) {
+    if (wsum < 1.0f / 16384.0f) wsum = 1.0f / 16384.0f;
+    for (int j = 0; j < n_used; ++j) wts[t * n_used + j] = __fdiv_rn(wts[t * n_used + j], wsum);
+  }
+}
+
+// Packed row order of the grouped FFN (grouped_routed_ffn decode.rs:10006): experts ascending, tokens ascending
+// inside an expert.  One block; deterministic (prefix sums, no atomics).  first_row[e] = first packed row of expert e
+// (n_expert + 1 entries), tok_of_row[r] = token of packed row r, rows_of_tok / w_of_tok[t*n_used + slot] = row and router
+// weight of token t's slot-th expert in ascending expert id (the accumulation order of scatter_expert_rows :10263);
+// the weight of an expert that is not resident here (local[e] == 0) is zero.  fill: tokens ints of scratch.
+__global__ void __launch_bounds__(1024)
+bucket_kernel(const int* __restrict__ ids, const float* __restrict__ wts, const unsigned char* __restrict__ local, int tokens,
+              int n_expert, int n_used, int* __restrict__ first_row, int* __restrict__ tok_of_row, int* __restrict__ rows_of_tok,
+              float* __restrict__ w_of_tok, int* __restrict__ fill) {
+  __shared__ int warp_tot[32];
+  __shared__ int s_base;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int t = threadIdx.x; t < tokens; t += blockDim.x) fill[t] = 0;
+  if (threadIdx.x == 0) s_base = 0;
+  __syncthreads();
+  for (int e = 0; e < n_expert; ++e) {
+    if (threadIdx.x == 0) first_row[e] = s_base;
+    for (int t0 = 0; t0 < tokens; t0 += blockDim.x) {
+      const int t = t0 + threadIdx.x;
+      int slot_j = -1;
+      if (t < tokens)
+        for (int j = 0; j < n_used; ++j)
+          if (ids[t * n_used + j] == e) { slot_j = j; break; }
+      const unsigned mask = __ballot_sync(~0u, slot_j >= 0);
+      if (lane == 0) warp_tot[warp] = __popc(mask);
+      __syncthreads();
+      int before = 0;
+      for (int w = 0; w < warp; ++w) before += warp_tot[w];
+      int total = 0;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += warp_tot[w];
+      const int base = s_base;
+      if (slot_j >= 0) {
+        const int r = base + before + __popc(mask & ((1u << lane) - 1u));
+        tok_of_row[r] = t;
+        const int slot = fill[t]++;
+        rows_of_tok[t * n_used + slot] = r;
+        w_of_tok[t * n_used + slot] = local[e] ? wts[t * n_used + slot_j] : 0.0f;
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) s_base = base + total;
+      __syncthreads();
+    }
+  }
+  if (threadIdx.x == 0) first_row[n_expert] = s_base;
+}
+
 }  // namespace
+
+cudaError_t launch_route(float* logits, int tokens, int n_expert, int n_used, int norm_w, int* ids, float* wts,
+                         cudaStream_t s, uint64_t* launches) {
+  if (tokens <= 0) return cudaSuccess;
+  route_kernel<<<(tokens + 127) / 128, 128, 0, s>>>(logits, tokens, n_expert, n_used, norm_w, ids, wts);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bucket(const int* ids, const float* wts, const unsigned char* local, int tokens, int n_expert, int n_used,
+                          int* first_row, int* tok_of_row, int* rows_of_tok, float* w_of_tok, int* fill, cudaStream_t s,
+                          uint64_t* launches) {
+  if (tokens <= 0) return cudaSuccess;
+  bucket_kernel<<<1, 1024, 0, s>>>(ids, wts, local, tokens, n_expert, n_used, first_row, tok_of_row, rows_of_tok, w_of_tok, fill);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
 
 cudaError_t launch_gather_rows(const float* x, const int* tok_of_row, float* packed, int n_rows, int n_embd,
                                cudaStream_t s, uint64_t* launches) {

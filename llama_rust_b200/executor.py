@@ -332,6 +332,24 @@ class Executor:
                                       out.size, ids.ctypes.data, w.ctypes.data))
         return out, ids, w
 
+    def _moe_layer(self, router, gate, up, down, n_used, norm_w):
+        n_expert = len(gate)
+        arrs = [(C.c_void_p * n_expert)(*[None if m is None else m._h for m in lst]) for lst in (gate, up, down)]
+        return _lib.MoeLayer(n_expert, n_used, int(norm_w), router._h if router is not None else None, arrs[0], arrs[1], arrs[2]), arrs
+
+    def moe_route_device(self, router: Matrix, n_expert: int, n_used: int, norm_w: bool, tokens: int, x_ptr: int, ids_ptr: int,
+                         w_ptr: int) -> None:
+        """Routing of `tokens` rows at x_ptr on the device (llr_moe_route_device); ids / weights go to device memory."""
+        none = [None] * n_expert
+        layer, keep = self._moe_layer(router, none, none, none, n_used, norm_w)
+        self._check(lib().llr_moe_route_device(self._h, C.byref(layer), tokens, x_ptr, ids_ptr, w_ptr))
+
+    def moe_experts_device(self, gate, up, down, counts, rows_ptr: int, y_ptr: int) -> None:
+        """Expert products over packed rows grouped by expert (llr_moe_experts_device); counts[e] rows for expert e."""
+        layer, keep = self._moe_layer(None, gate, up, down, 1, False)
+        cnt = (C.c_uint32 * len(gate))(*[int(c) for c in counts])
+        self._check(lib().llr_moe_experts_device(self._h, C.byref(layer), cnt, rows_ptr, y_ptr))
+
     def dequant_rows(self, m: Matrix, row0: int = 0, n_rows: int | None = None) -> np.ndarray:
         n = m.rows - row0 if n_rows is None else n_rows
         out = np.empty((n, m.cols), np.float32)

@@ -7,10 +7,10 @@ The reference has no multi-device execution (its only notions are simulated:
   matrix is a contiguous byte range (langtax/src/decode.rs:10876-10879, `quant_mat_rows`
   :9680-9713), so rank g holds rows [g*R/G, (g+1)*R/G) of every matrix, activations are
   replicated, and the exchange is an all-gather of M x R/G result slices.
-* Routed experts stripe as `e % G`; token rows travel to the expert's rank and back with
-  all-to-all, and a token's output is summed over its experts in ascending expert id
-  (the reference's accumulation order, decode.rs:10006-10290), so results do not depend
-  on G.
+* Routed experts stripe as `e % G` and tokens are sharded over the ranks; routed rows travel
+  to the expert's rank and back with all-to-all (`ExpertParallelLayer`), and a token's output
+  is summed over its experts in ascending expert id (the reference's accumulation order,
+  decode.rs:10006-10290), so results do not depend on G.
 
 The compute is a callable, so the same code runs on NCCL with the CUDA executor and on
 gloo with any CPU stand-in (that is how the host logic is tested without GPUs).
@@ -63,76 +63,6 @@ class RowShardedMatmul:
         gathered = torch.empty(self.world * tokens, self.local_rows, dtype=y_local.dtype, device=y_local.device)
         dist.all_gather_into_tensor(gathered, y_local.contiguous(), group=self.group)
         return gathered.view(self.world, tokens, self.local_rows).permute(1, 0, 2).reshape(tokens, self.rows)
-
-
-class ExpertParallelFFN:
-    """Routed-expert FFN with experts striped over ranks.
-
-    `route(x) -> (ids[T, k], w[T, k])` is replicated (every rank routes every token);
-    `expert_ffn(e, rows[n, d]) -> rows[n, d]` runs one local expert on a packed batch.
-    Tokens are replicated too (the usual data layout after attention), so the dispatch
-    all-to-all only moves the rows a rank does NOT own... every rank could gather its own
-    rows locally; the exchange that cannot be avoided is the combine: each rank returns the
-    expert outputs of its experts for all tokens, and every rank sums a token's k rows in
-    ascending expert id.
-    """
-
-    def __init__(self, n_expert: int, route, expert_ffn, group=None):
-        self.n_expert, self.route, self.expert_ffn, self.group = n_expert, route, expert_ffn, group
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
-
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        ids, w = self.route(x)
-        tokens, k = ids.shape
-        d = x.shape[1]
-        # rows in (expert ascending, token ascending) order, as grouped_routed_ffn builds them
-        flat_e = ids.reshape(-1)
-        flat_t = torch.arange(tokens, device=x.device).repeat_interleave(k)
-        order = torch.argsort(flat_e * tokens + flat_t, stable=True)
-        e_sorted, t_sorted = flat_e[order], flat_t[order]
-        counts = torch.bincount(e_sorted, minlength=self.n_expert)
-        starts = torch.cumsum(counts, 0) - counts
-        y_rows = torch.zeros(tokens * k, d, dtype=x.dtype, device=x.device)
-        # per-rank row counts are known everywhere (routing is replicated): all-to-all sizes
-        per_rank = [int(sum(int(counts[e]) for e in range(self.n_expert) if home_rank(e, self.world) == r))
-                    for r in range(self.world)]
-        mine = []
-        for e in range(self.n_expert):
-            if home_rank(e, self.world) != self.rank or int(counts[e]) == 0:
-                continue
-            s, n = int(starts[e]), int(counts[e])
-            out = self.expert_ffn(e, x[t_sorted[s:s + n]])
-            mine.append((s, out))
-        send = torch.cat([o for _, o in mine]) if mine else torch.zeros(0, d, dtype=x.dtype, device=x.device)
-        # every rank needs every row: all-gather of ragged blocks via all_to_all_single with
-        # identical payload to each peer (the combine step of expert parallelism)
-        recv = torch.empty(sum(per_rank), d, dtype=x.dtype, device=x.device)
-        dist.all_to_all_single(recv, send.repeat(self.world, 1), output_split_sizes=per_rank,
-                               input_split_sizes=[send.shape[0]] * self.world, group=self.group)
-        # place the received blocks: rank r's block lists its experts ascending
-        off = 0
-        for r in range(self.world):
-            for e in range(self.n_expert):
-                if home_rank(e, self.world) != r or int(counts[e]) == 0:
-                    continue
-                s, n = int(starts[e]), int(counts[e])
-                y_rows[s:s + n] = recv[off:off + n]
-                off += n
-        # combine: ascending expert id per token, starting from zero
-        out = torch.zeros_like(x)
-        w_sorted = w.reshape(-1)[order]
-        # slot j of token t = its j-th expert in ascending id
-        slot = torch.zeros(tokens, dtype=torch.long, device=x.device)
-        rows_of_tok = torch.zeros(tokens, k, dtype=torch.long, device=x.device)
-        for i in range(tokens * k):  # routing tables are tiny (T*k entries)
-            t = int(t_sorted[i])
-            rows_of_tok[t, int(slot[t])] = i
-            slot[t] += 1
-        for j in range(k):
-            idx = rows_of_tok[:, j]
-            out = out + y_rows[idx] * w_sorted[idx].unsqueeze(1)
-        return out
 
 
 def arena_layout(row_counts: Sequence[int], tokens: int = 1) -> tuple[list[int], int]:
@@ -209,37 +139,119 @@ class ShardedDecodeProgram:
             self.ex.shared_free(self.arena)
 
 
-class StripedExperts:
-    """Routed-expert FFN layer with the experts striped over the ranks (expert e on rank e % G,
-    expertvm/src/place.rs:71-75), on the CUDA executor.  Every rank routes every token (the router
-    is replicated) and runs llr_moe_ffn with only its own experts resident; the exchange step is one
-    sum of the ranks' partial outputs (NCCL all-reduce, or gloo).  With two experts per token at most
-    two terms of that sum are non-zero for any element, so the result is bit-identical to the
-    single-device layer whatever order the collective adds in."""
+def plan_dispatch(ids, n_expert: int, world: int):
+    """Host side of the token-row exchange.  ids: [T, k] expert ids of this rank's tokens (numpy).  Rows travel to the
+    rank that owns their expert (home_rank) ordered by (destination, expert, token), which is also the order they come
+    back in.  Returns (src_token[n_rows], src_slot[n_rows], send_counts[world], expert_counts[n_expert])."""
+    ids = np.asarray(ids)
+    tokens, k = ids.shape
+    flat_e = ids.reshape(-1).astype(np.int64)
+    flat_t = np.repeat(np.arange(tokens, dtype=np.int64), k)
+    flat_j = np.tile(np.arange(k, dtype=np.int64), tokens)
+    dest = flat_e % world
+    order = np.lexsort((flat_t, flat_e, dest))  # by destination, then expert, then token
+    send_counts = np.bincount(dest, minlength=world).astype(np.int64)
+    expert_counts = np.bincount(flat_e, minlength=n_expert).astype(np.int64)
+    return flat_t[order], flat_j[order], send_counts, expert_counts
 
-    def __init__(self, ex, router, gate, up, down, n_used: int, norm_w: bool, group=None):
-        self.ex, self.router, self.n_used, self.norm_w, self.group = ex, router, n_used, norm_w, group
+
+def plan_regroup(counts_all, rank: int, world: int):
+    """counts_all[src, e]: rows rank src sends for expert e.  The rows this rank receives lie [src][expert][token];
+    the expert products want them [expert][src][token].  Returns (perm, rows_per_expert[n_expert]) with
+    grouped = received[perm] (and received = grouped[inverse of perm])."""
+    counts_all = np.asarray(counts_all, np.int64)
+    n_expert = counts_all.shape[1]
+    mine = [e for e in range(n_expert) if home_rank(e, world) == rank]
+    start = {}
+    off = 0
+    for src in range(world):
+        for e in mine:
+            start[(src, e)] = off
+            off += int(counts_all[src, e])
+    perm = []
+    per_expert = np.zeros(n_expert, np.int64)
+    for e in mine:
+        for src in range(world):
+            n = int(counts_all[src, e])
+            perm.extend(range(start[(src, e)], start[(src, e)] + n))
+            per_expert[e] += n
+    return np.asarray(perm, np.int64), per_expert
+
+
+class ExpertParallelLayer:
+    """Routed-expert FFN layer with the experts striped over the ranks (expert e on rank e % G, expertvm/src/place.rs:
+    71-75) and the TOKENS sharded too: every rank routes its own tokens, sends each routed row to the rank that owns
+    its expert (all-to-all), runs its experts on what it received, sends the results back (all-to-all) and adds a token's
+    rows in ascending expert id (the accumulation order of scatter_expert_rows, decode.rs:10263).  A row's expert output
+    does not depend on which other rows share its batch, so the layer's output is bit-identical to the single-device
+    layer on the same tokens.
+
+    route(x) -> (ids[T, k] int32, w[T, k] float32) and experts(counts[n_expert], rows[n, d]) -> y[n, d] are callables on
+    torch tensors of the group's device type (`cuda_backend` builds them for the CUDA executor); the exchange is
+    torch.distributed all_to_all_single, i.e. NCCL over NVLink for CUDA tensors."""
+
+    def __init__(self, n_expert: int, n_used: int, route, experts, group=None):
+        self.n_expert, self.n_used, self.route, self.experts, self.group = n_expert, n_used, route, experts, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        keep = [home_rank(e, self.world) == self.rank for e in range(len(gate))]
-        self.gate = [m if k else None for m, k in zip(gate, keep)]
-        self.up = [m if k else None for m, k in zip(up, keep)]
-        self.down = [m if k else None for m, k in zip(down, keep)]
 
-    def __call__(self, x, device=None):
-        """x: [tokens, n_embd] float32 numpy array (host).  Returns (out, ids, weights) as numpy arrays
-        (out is a view of a pinned buffer that the next call reuses)."""
-        shape = tuple(np.asarray(x).reshape(-1, self.router.cols).shape)
-        if getattr(self, "_pin", None) is None or tuple(self._pin.shape) != shape:
-            self._pin = torch.empty(shape, dtype=torch.float32)
-            if device is not None:
-                self._pin = self._pin.pin_memory()  # the executor writes its partial sums straight into it
-        partial, ids, w = self.ex.moe_ffn(self.router, self.gate, self.up, self.down, self.n_used, self.norm_w, x,
-                                          out=self._pin.numpy())
-        if device is None:
-            dist.all_reduce(self._pin, op=dist.ReduceOp.SUM, group=self.group)
-        else:
-            t = self._pin.to(device, non_blocking=True)
-            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
-            self._pin.copy_(t, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-        return self._pin.numpy(), ids, w
+    @staticmethod
+    def cuda_backend(ex, router, gate, up, down, n_used: int, norm_w: bool):
+        """(route, experts) over the CUDA executor; gate/up/down hold None for experts that live on other ranks."""
+        n_expert = len(gate)
+
+        def route(x):
+            ids = torch.empty(x.shape[0], n_used, dtype=torch.int32, device=x.device)
+            w = torch.empty(x.shape[0], n_used, dtype=torch.float32, device=x.device)
+            torch.cuda.current_stream().synchronize()  # x is ready before the executor's stream reads it
+            ex.moe_route_device(router, n_expert, n_used, norm_w, x.shape[0], x.data_ptr(), ids.data_ptr(), w.data_ptr())
+            ex.synchronize()
+            return ids, w
+
+        def experts(counts, rows):
+            y = torch.empty_like(rows)
+            if rows.shape[0]:
+                torch.cuda.current_stream().synchronize()
+                ex.moe_experts_device(gate, up, down, counts, rows.data_ptr(), y.data_ptr())
+                ex.synchronize()
+            return y
+        return route, experts
+
+    def __call__(self, x: torch.Tensor):
+        """x: this rank's tokens [T, n_embd] (float32, contiguous).  Returns (out[T, n_embd], ids, w)."""
+        dev = x.device
+        ids, w = self.route(x)
+        src_t, src_j, send_counts, expert_counts = plan_dispatch(ids.cpu().numpy(), self.n_expert, self.world)
+        # who sends how many rows for which expert: one small all-gather
+        mine = torch.tensor(expert_counts, dtype=torch.int64, device=dev)
+        gathered = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(gathered, mine, group=self.group)
+        counts_all = torch.stack(gathered).cpu().numpy()
+        recv_counts = [int(sum(counts_all[src, e] for e in range(self.n_expert) if home_rank(e, self.world) == self.rank))
+                       for src in range(self.world)]
+        t_idx = torch.from_numpy(src_t).to(dev)
+        send = x.index_select(0, t_idx).contiguous()
+        recv = torch.empty(sum(recv_counts), x.shape[1], dtype=x.dtype, device=dev)
+        dist.all_to_all_single(recv, send, output_split_sizes=recv_counts, input_split_sizes=[int(c) for c in send_counts],
+                               group=self.group)
+        perm, per_expert = plan_regroup(counts_all, self.rank, self.world)
+        perm_t = torch.from_numpy(perm).to(dev)
+        y_grouped = self.experts(per_expert, recv.index_select(0, perm_t).contiguous())
+        y_recv = torch.empty_like(recv)
+        y_recv.index_copy_(0, perm_t, y_grouped)
+        back = torch.empty_like(send)
+        dist.all_to_all_single(back, y_recv, output_split_sizes=[int(c) for c in send_counts], input_split_sizes=recv_counts,
+                               group=self.group)
+        # combine: a token's rows in ascending expert id, each multiplied by its router weight, added from zero
+        tokens = x.shape[0]
+        row_of = np.empty((tokens, self.n_used), np.int64)
+        row_of[src_t, src_j] = np.arange(src_t.size)
+        ids_np = ids.cpu().numpy()
+        slot_order = np.argsort(ids_np, axis=1, kind="stable")  # slots by ascending expert id
+        out = torch.zeros_like(x)
+        for s in range(self.n_used):
+            j = slot_order[:, s]
+            rows = torch.from_numpy(row_of[np.arange(tokens), j]).to(dev)
+            wj = w.gather(1, torch.from_numpy(j).to(dev).unsqueeze(1))
+            term = back.index_select(0, rows) * wj  # product rounded, then added: no fused multiply-add
+            out = out + term
+        return out, ids, w

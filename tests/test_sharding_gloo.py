@@ -1,6 +1,7 @@
 """Host logic of the sharding layer on CPU: two gloo ranks, the oracle standing in for the
 device executor.  Row-sharded products must reproduce the unsharded result bit for bit
-(rows are independent), and the expert-parallel FFN must match the single-process MoE walk."""
+(rows are independent), and the expert-parallel layer (tokens sharded, routed rows exchanged with
+all-to-all) must match the single-process MoE walk."""
 import os
 import socket
 
@@ -75,31 +76,66 @@ def test_row_ranges_cover_baseline_shapes():
     assert [sharding.home_rank(e, 4) for e in range(8)] == [0, 1, 2, 3, 0, 1, 2, 3]  # place.rs:71-75
 
 
-def _moe_rank(rank, world, n_used, router_w, gate, up, down, n_embd, n_ff, x, ids, wts):
+def _moe_rank(rank, world, n_used, gate, up, down, n_embd, n_ff, x, ids, wts):
+    """One rank of the expert-parallel layer on CPU tensors: the oracle stands in for the device executor."""
     from llama_rust_b200 import sharding
     from oracle import pyoracle as orc
+    tokens = x.shape[0]
+    lo, hi = tokens * rank // world, tokens * (rank + 1) // world  # this rank's tokens
 
-    def expert(e, rows):
-        n = rows.shape[0]
-        r = rows.numpy()
-        g = orc.gemm(Q4_K, n_embd, n, gate[e], r, n_ff, simd=True, threads=1)
-        u = orc.gemm(Q4_K, n_embd, n, up[e], r, n_ff, simd=True, threads=1)
-        a = np.array([orc.lib.orc_silu(float(v)) for v in g.ravel()], np.float32).reshape(g.shape) * u
-        return torch.from_numpy(orc.gemm(Q4_K, n_ff, n, down[e], a, n_embd, simd=True, threads=1))
+    def route(xt):
+        return torch.from_numpy(ids[lo:hi].astype(np.int32)), torch.from_numpy(wts[lo:hi])
 
-    ffn = sharding.ExpertParallelFFN(len(gate), lambda xt: (torch.from_numpy(ids).long(), torch.from_numpy(wts)), expert)
-    return ffn(torch.from_numpy(x)).numpy()
+    def experts(counts, rows):
+        out, r0 = [], 0
+        for e, n in enumerate(counts):
+            n = int(n)
+            if n == 0:
+                continue
+            assert sharding.home_rank(e, world) == rank  # only rows of this rank's experts arrive
+            r = rows[r0:r0 + n].numpy()
+            g = orc.gemm(Q4_K, n_embd, n, gate[e], r, n_ff, simd=True, threads=1)
+            u = orc.gemm(Q4_K, n_embd, n, up[e], r, n_ff, simd=True, threads=1)
+            a = np.array([orc.lib.orc_silu(float(v)) for v in g.ravel()], np.float32).reshape(g.shape) * u
+            out.append(torch.from_numpy(orc.gemm(Q4_K, n_ff, n, down[e], a, n_embd, simd=True, threads=1)))
+            r0 += n
+        return torch.cat(out) if out else torch.zeros(0, n_embd)
+
+    layer = sharding.ExpertParallelLayer(len(gate), n_used, route, experts)
+    out, _, _ = layer(torch.from_numpy(np.ascontiguousarray(x[lo:hi])))
+    return lo, hi, out.numpy()
 
 
-def test_expert_parallel_ffn_matches_single_process_walk(orc):
+@pytest.mark.parametrize("tokens", [7, 12])
+def test_expert_parallel_layer_matches_single_process_walk(orc, tokens):
+    """Tokens sharded over two ranks, experts striped e % 2, routed rows exchanged with all-to-all (gloo): every rank's
+    outputs for its own tokens are bit-identical to the single-process layer."""
     rng = np.random.default_rng(5)
-    n_expert, n_used, n_embd, n_ff, tokens = 4, 2, 256, 256, 7
+    n_expert, n_used, n_embd, n_ff = 4, 2, 256, 256
     router_w = (rng.standard_normal((n_expert, n_embd)) * 0.05).astype(np.float32)
     gate = [random_packed(rng, Q4_K, n_ff, n_embd) for _ in range(n_expert)]
     up = [random_packed(rng, Q4_K, n_ff, n_embd) for _ in range(n_expert)]
     down = [random_packed(rng, Q4_K, n_embd, n_ff) for _ in range(n_expert)]
     x = rng.standard_normal((tokens, n_embd)).astype(np.float32)
     ref, ids, wts = orc.moe_ffn(n_used, True, F32, router_w.view(np.uint8), Q4_K, gate, up, down, n_embd, n_ff, x)
-    for out in _run(2, _moe_rank, n_used, router_w, gate, up, down, n_embd, n_ff, x, ids, wts):
-        # same products, same ascending-expert accumulation: identical bits for any number of ranks
-        assert np.array_equal(out.view(np.uint32), ref.view(np.uint32))
+    for lo, hi, out in _run(2, _moe_rank, n_used, gate, up, down, n_embd, n_ff, x, ids, wts):
+        # same products per row, same ascending-expert accumulation: identical bits for any number of ranks
+        assert np.array_equal(out.view(np.uint32), ref[lo:hi].view(np.uint32))
+
+
+def test_dispatch_plans_are_consistent():
+    from llama_rust_b200 import sharding
+    rng = np.random.default_rng(9)
+    n_expert, k, world = 8, 2, 4
+    per_rank = []
+    for r in range(world):
+        tokens = 5 + r
+        ids = np.stack([rng.permutation(n_expert)[:k] for _ in range(tokens)])
+        per_rank.append((ids, *sharding.plan_dispatch(ids, n_expert, world)))
+    counts_all = np.stack([p[4] for p in per_rank])
+    for r, (ids, src_t, src_j, send_counts, expert_counts) in enumerate(per_rank):
+        assert send_counts.sum() == ids.size and np.array_equal(ids[src_t, src_j] % world, np.repeat(np.arange(world), send_counts))
+        perm, per_expert = sharding.plan_regroup(counts_all, r, world)
+        mine = [e for e in range(n_expert) if e % world == r]
+        assert sorted(perm.tolist()) == list(range(int(counts_all[:, mine].sum())))
+        assert per_expert.sum() == perm.size and all(per_expert[e] == 0 for e in range(n_expert) if e % world != r)
