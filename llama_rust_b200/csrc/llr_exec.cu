@@ -436,6 +436,8 @@ cudaError_t launch_matmul(const MatView& m, const float* x, float* y, int64_t to
   if (path == PATH_TC) path = PATH_AUTO;
   if ((path == PATH_AUTO || path == PATH_MMA) && x_aligned && err_flag && gemv_mma_supported(m))
     return launch_gemv_mma(m, x, y, tokens, stream, sm_count, err_flag, launches);
+  if (path == PATH_AUTO && x_aligned && gemv_rows_supported(m) && tokens <= 32)
+    return launch_gemv_rows(m, x, y, tokens, stream, sm_count, launches);
   if (path != PATH_GENERIC && x_aligned && gemv_staged_supported(m))
     return launch_gemv_staged(m, x, y, tokens, stream, sm_count, launches);
   return launch_gemv_generic(m, x, y, tokens, stream, launches);

@@ -79,7 +79,8 @@ constexpr int CW = NWARP;                 // consumer warps
 constexpr int NTHREADS = (CW + 2) * 32;   // + producer + reducer
 constexpr int NRB = 4;                    // reduction buffers
 constexpr int MAX_CHUNK = Lay<DT_Q4_K, 1>::CHUNK;
-static_assert(Lay<DT_Q6_K, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q8_0, 1>::CHUNK <= MAX_CHUNK, "ring stage");
+static_assert(Lay<DT_Q6_K, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q8_0, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q4_0, 1>::CHUNK <= MAX_CHUNK &&
+              Lay<DT_Q5_0, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q5_1, 1>::CHUNK <= MAX_CHUNK, "ring stage");
 // Sharded programs keep two counter arrays in the arena header: [0, 4096) this rank's CTAs per
 // phase, [4096, 8192) arrivals of the peers per phase.
 constexpr int PEER_COUNTER_OFFSET = 4096;
@@ -108,6 +109,9 @@ constexpr int Q4K_STAGE_BLOCKS = Fmt<DT_Q4_K>::KSEG / 256;
 __device__ __forceinline__ Geom geom_of(int dtype) {
   if (dtype == DT_Q4_K) return {Fmt<DT_Q4_K>::KSEG, Lay<DT_Q4_K, 1>::SEGB, Lay<DT_Q4_K, 1>::RS, Q4K_STAGE_BLOCKS * 16 * 144};
   if (dtype == DT_Q6_K) return {Fmt<DT_Q6_K>::KSEG, Lay<DT_Q6_K, 1>::SEGB, Lay<DT_Q6_K, 1>::RS, 16 * Lay<DT_Q6_K, 1>::SEGB};
+  if (dtype == DT_Q4_0) return {Fmt<DT_Q4_0>::KSEG, Lay<DT_Q4_0, 1>::SEGB, Lay<DT_Q4_0, 1>::RS, 0};
+  if (dtype == DT_Q5_0) return {Fmt<DT_Q5_0>::KSEG, Lay<DT_Q5_0, 1>::SEGB, Lay<DT_Q5_0, 1>::RS, 0};
+  if (dtype == DT_Q5_1) return {Fmt<DT_Q5_1>::KSEG, Lay<DT_Q5_1, 1>::SEGB, Lay<DT_Q5_1, 1>::RS, 0};
   return {Fmt<DT_Q8_0>::KSEG, Lay<DT_Q8_0, 1>::SEGB, Lay<DT_Q8_0, 1>::RS, 0};
 }
 static_assert(Lay<DT_Q6_K, 1>::RS == Lay<DT_Q6_K, 1>::SEGB, "Q6_K rows lie densely in a stage");
@@ -517,6 +521,21 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
             } else if (dtype == DT_Q6_K) {
               for (int b = warp; b < (seg_cols >> 8); b += CW)
                 block_q6k<MT>(rowA, rowB, b, sub * (gm.kseg / 256) + b, dig, xsi, g, t, acc);
+            } else if (DTFIX == DT_Q4_0) {  // the nibble formats run as single products only (never inside programs)
+              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW)
+#pragma unroll 2
+                for (int i = 0; i < 8; ++i)
+                  block_q40<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, xsi, g, t, acc);
+            } else if (DTFIX == DT_Q5_0) {
+              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW)
+#pragma unroll 2
+                for (int i = 0; i < 8; ++i)
+                  block_q50<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xsi, g, t, acc);
+            } else if (DTFIX == DT_Q5_1) {
+              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW)
+#pragma unroll 2
+                for (int i = 0; i < 8; ++i)
+                  block_q51<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xsi, g, t, acc);
             } else {
               for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW)  // the eight blocks of 256 columns b8
 #pragma unroll 2
@@ -530,7 +549,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           const int rb = j % NRB;
           if (ok && !mbar_wait(&rempty[rb], (uint32_t)(((j / NRB) & 1) ^ 1))) { ok = false; if (lane == 0) report_error(err, 1); }
           float* myred = red + (rb * CW + warp) * 16 * MT;
-          if ((DTFIX >= 0 ? DTFIX : E.dtype) == DT_Q4_K) {
+          if ((DTFIX >= 0 ? DTFIX : E.dtype) == DT_Q4_K || DTFIX == DT_Q5_1) {
 #pragma unroll
             for (int k = 0; k < MT; ++k)
 #pragma unroll
@@ -685,7 +704,8 @@ cudaError_t launch_single(const MatView& m, const float* x, float* y, int tokens
 }  // namespace
 
 bool gemv_mma_supported(const MatView& m) {
-  if (m.dtype != DT_Q4_K && m.dtype != DT_Q6_K && m.dtype != DT_Q8_0) return false;
+  if (m.dtype != DT_Q4_K && m.dtype != DT_Q6_K && m.dtype != DT_Q8_0 && m.dtype != DT_Q4_0 && m.dtype != DT_Q5_0 && m.dtype != DT_Q5_1)
+    return false;
   if (m.rows <= 0 || m.cols <= 0 || m.rows > (1 << 30) || m.cols > (1 << 30)) return false;
   if (((uintptr_t)m.w & 15) != 0 || m.row_bytes % 16 != 0) return false;
   if (m.cols % 256 != 0) return false;
@@ -708,6 +728,9 @@ static cudaError_t launch_passes(const MatView& m, const float* x, float* y, int
                : launch_single<8, D>(m, xp, yp, nt, stream, sm_count, err, ho))
     if (m.dtype == DT_Q4_K) e = LLR_LAUNCH_DT(DT_Q4_K);
     else if (m.dtype == DT_Q6_K) e = LLR_LAUNCH_DT(DT_Q6_K);
+    else if (m.dtype == DT_Q4_0) e = LLR_LAUNCH_DT(DT_Q4_0);
+    else if (m.dtype == DT_Q5_0) e = LLR_LAUNCH_DT(DT_Q5_0);
+    else if (m.dtype == DT_Q5_1) e = LLR_LAUNCH_DT(DT_Q5_1);
     else e = LLR_LAUNCH_DT(DT_Q8_0);
 #undef LLR_LAUNCH_DT
     if (e != cudaSuccess) return e;
@@ -744,7 +767,9 @@ struct Program {
   bool own_counters = true;
 };
 
-bool prog_entry_supported(const MatView& m) { return gemv_mma_supported(m); }
+bool prog_entry_supported(const MatView& m) {
+  return (m.dtype == DT_Q4_K || m.dtype == DT_Q6_K || m.dtype == DT_Q8_0) && gemv_mma_supported(m);
+}
 
 template <int MT, bool FLOW>
 static cudaError_t prog_prepare(int sm_count, int* grid, bool sharded) {

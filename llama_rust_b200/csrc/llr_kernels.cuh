@@ -47,6 +47,11 @@ bool gemv_staged_supported(const MatView& m);
 cudaError_t launch_gemv_staged(const MatView& m, const float* x, float* y, int64_t tokens,
                                cudaStream_t stream, int sm_count, uint64_t* launches);
 
+// Streaming decode GEMV for the element formats F32 / F16 / BF16 (tokens <= 8 per pass); see llr_gemv_rows.cu.
+bool gemv_rows_supported(const MatView& m);
+cudaError_t launch_gemv_rows(const MatView& m, const float* x, float* y, int64_t tokens, cudaStream_t stream, int sm_count,
+                             uint64_t* launches);
+
 // Integer tensor-core decode GEMV for Q4_K / Q6_K / Q8_0 (tokens <= 8 per pass); see
 // llr_gemv_stream.cu.  Launched with programmatic stream serialization.
 bool gemv_mma_supported(const MatView& m);

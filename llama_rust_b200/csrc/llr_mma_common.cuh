@@ -40,6 +40,9 @@ template <int DT> struct Fmt;
 template <> struct Fmt<DT_Q4_K> { static constexpr int KSEG = 4096, BB = 144, BE = 256; };
 template <> struct Fmt<DT_Q6_K> { static constexpr int KSEG = 2048, BB = 210, BE = 256; };
 template <> struct Fmt<DT_Q8_0> { static constexpr int KSEG = 2048, BB = 34, BE = 32; };
+template <> struct Fmt<DT_Q4_0> { static constexpr int KSEG = 2048, BB = 18, BE = 32; };
+template <> struct Fmt<DT_Q5_0> { static constexpr int KSEG = 2048, BB = 22, BE = 32; };
+template <> struct Fmt<DT_Q5_1> { static constexpr int KSEG = 2048, BB = 24, BE = 32; };
 
 template <int DT, int MT> struct Lay {
   using F = Fmt<DT>;
@@ -47,7 +50,7 @@ template <int DT, int MT> struct Lay {
   static constexpr int SEGB = F::KSEG / F::BE * F::BB;          // bytes of one row segment
   // row stride mod 128: 32 spreads the 8-byte fragment reads of eight rows over all banks,
   // 16 does the same for the 4-byte reads of Q6_K
-  static constexpr int RMOD = DT == DT_Q6_K ? 16 : 32;
+  static constexpr int RMOD = (DT == DT_Q6_K || DT == DT_Q4_0 || DT == DT_Q5_0 || DT == DT_Q5_1) ? 16 : 32;
   static constexpr int RS = SEGB + (RMOD + 128 - SEGB % 128) % 128;
   static constexpr int CHUNK = 16 * RS;
   static_assert(RS % 16 == 0 && RS % 128 == RMOD, "row stride");
@@ -328,6 +331,107 @@ __device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* ro
   else block_q80_par<MT, true>(rowA + b * 34, rowB + b * 34, c32, dig, xsi, g, t, acc);
 }
 
+
+// ---- Q4_0 / Q5_0 / Q5_1: 32-column blocks whose codes are nibbles (plus a fifth bit in a 32-bit mask) --------
+// Word t of the 16 quant bytes holds elements 4t..4t+3 in its low nibbles and 16+4t..16+4t+3 in its high nibbles:
+// one 32-bit load per row gives thread t both of its k-slices of the A fragment, and the B fragment takes the digit
+// bytes of the same elements (a sum over k does not care about the order of k as long as A and B agree).
+// Signed codes become int8 without a subtraction: (code << s) ^ 0x80 is 2^s * (code - 2^(7-s)), i.e. 16 (q - 8) for
+// Q4_0 and 8 (code - 16) for Q5_0; the power of two goes into the final scale.  Q5_1 codes are an unsigned operand
+// and its offset m multiplies the f32 sum of the block's activations, like the mins of Q4_K.
+// four bits -> the low bit of four bytes
+__device__ __forceinline__ uint32_t spread4(uint32_t x) { return ((x & 15u) * 0x00204081u) & 0x01010101u; }
+
+template <int MT, bool ODD>
+__device__ __forceinline__ void block_q40_par(const uint8_t* pA, const uint8_t* pB, int c32, const uint8_t* dig,
+                                              const float* xsi, int g, int t, AccT<MT>& acc) {
+  constexpr int NT = (MT + 1) / 2;
+  const uint32_t wA = lds32_par<ODD>(pA + 2 + 4 * t), wB = lds32_par<ODD>(pB + 2 + 4 * t);
+  constexpr uint32_t MH = 0xf0f0f0f0u, SG = 0x80808080u;
+  const uint32_t a0 = ((wA << 4) & MH) ^ SG, a2 = (wA & MH) ^ SG, a1 = ((wB << 4) & MH) ^ SG, a3 = (wB & MH) ^ SG;
+  const float dA = h2f(*(const uint16_t*)pA), dB = h2f(*(const uint16_t*)pB);
+  const float pw0 = (t & 1) ? 4096.f : 0.0625f, pw1 = pw0 * 256.f;  // 256^digit / 16
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const uint8_t* dp = plane_of<MT>(dig, nt, g) + c32 * 32 + 4 * t;
+    int c[4];
+    mma_k32(c, a0, a1, a2, a3, *(const uint32_t*)dp, *(const uint32_t*)(dp + 16));
+    const int tok = 2 * nt + (t >> 1);
+    const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + (c32 >> 3)] : 0.f;
+    acc.y[nt][0] = fmaf((float)c[0], dA * xs * pw0, acc.y[nt][0]);
+    acc.y[nt][1] = fmaf((float)c[1], dA * xs * pw1, acc.y[nt][1]);
+    acc.y[nt][2] = fmaf((float)c[2], dB * xs * pw0, acc.y[nt][2]);
+    acc.y[nt][3] = fmaf((float)c[3], dB * xs * pw1, acc.y[nt][3]);
+  }
+}
+template <int MT>
+__device__ __forceinline__ void block_q40(const uint8_t* rowA, const uint8_t* rowB, int b, int c32, const uint8_t* dig,
+                                          const float* xsi, int g, int t, AccT<MT>& acc) {
+  // 18-byte blocks in a 16-byte aligned row piece: the quants of an even block start 2 bytes off a word boundary
+  if (b & 1) block_q40_par<MT, false>(rowA + b * 18, rowB + b * 18, c32, dig, xsi, g, t, acc);
+  else block_q40_par<MT, true>(rowA + b * 18, rowB + b * 18, c32, dig, xsi, g, t, acc);
+}
+
+// HDR: bytes before the fifth-bit mask (2: Q5_0, 4: Q5_1)
+template <int MT, bool ODD, bool Q51>
+__device__ __forceinline__ void block_q5_par(const uint8_t* pA, const uint8_t* pB, int c32, const uint8_t* dig,
+                                             const float* sxf, const float* xsi, int g, int t, AccT<MT>& acc) {
+  constexpr int NT = (MT + 1) / 2;
+  constexpr int HDR = Q51 ? 4 : 2;
+  const uint32_t hA = lds32_par<ODD>(pA + HDR), hB = lds32_par<ODD>(pB + HDR);
+  const uint32_t wA = lds32_par<ODD>(pA + HDR + 4 + 4 * t), wB = lds32_par<ODD>(pB + HDR + 4 + 4 * t);
+  uint32_t a0, a1, a2, a3;
+  if (Q51) {  // codes 0..31 as they are
+    constexpr uint32_t M4 = 0x0f0f0f0fu;
+    a0 = (wA & M4) | (spread4(hA >> (4 * t)) << 4);
+    a2 = ((wA >> 4) & M4) | (spread4(hA >> (16 + 4 * t)) << 4);
+    a1 = (wB & M4) | (spread4(hB >> (4 * t)) << 4);
+    a3 = ((wB >> 4) & M4) | (spread4(hB >> (16 + 4 * t)) << 4);
+  } else {    // 8 (code - 16)
+    constexpr uint32_t M5 = 0x78787878u, SG = 0x80808080u;
+    a0 = (((wA << 3) & M5) | (spread4(hA >> (4 * t)) << 7)) ^ SG;
+    a2 = (((wA >> 1) & M5) | (spread4(hA >> (16 + 4 * t)) << 7)) ^ SG;
+    a1 = (((wB << 3) & M5) | (spread4(hB >> (4 * t)) << 7)) ^ SG;
+    a3 = (((wB >> 1) & M5) | (spread4(hB >> (16 + 4 * t)) << 7)) ^ SG;
+  }
+  const float dA = h2f(*(const uint16_t*)pA), dB = h2f(*(const uint16_t*)pB);
+  const float pw0 = Q51 ? ((t & 1) ? 65536.f : 1.f) : ((t & 1) ? 8192.f : 0.125f), pw1 = pw0 * 256.f;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const uint8_t* dp = plane_of<MT>(dig, nt, g) + c32 * 32 + 4 * t;
+    int c[4];
+    if (Q51) mma_k32_us(c, a0, a1, a2, a3, *(const uint32_t*)dp, *(const uint32_t*)(dp + 16));
+    else mma_k32(c, a0, a1, a2, a3, *(const uint32_t*)dp, *(const uint32_t*)(dp + 16));
+    const int tok = 2 * nt + (t >> 1);
+    const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + (c32 >> 3)] : 0.f;
+    acc.y[nt][0] = fmaf((float)c[0], dA * xs * pw0, acc.y[nt][0]);
+    acc.y[nt][1] = fmaf((float)c[1], dA * xs * pw1, acc.y[nt][1]);
+    acc.y[nt][2] = fmaf((float)c[2], dB * xs * pw0, acc.y[nt][2]);
+    acc.y[nt][3] = fmaf((float)c[3], dB * xs * pw1, acc.y[nt][3]);
+  }
+  if (Q51 && t == (c32 & 3)) {
+    // the offset: m * sum of the block's activations, kept negative so that the tile's `sum - mn` adds it; one of the
+    // four threads that see this block does it (the four are summed when the tile is handed over)
+    const float mA = h2f(*(const uint16_t*)(pA + 2)), mB = h2f(*(const uint16_t*)(pB + 2));
+#pragma unroll
+    for (int k = 0; k < MT; ++k) {
+      const float sx = sxf[k * (Sp<MT>::SPAN / 32) + c32];
+      acc.mn[0][k] = fmaf(-mA, sx, acc.mn[0][k]);
+      acc.mn[1][k] = fmaf(-mB, sx, acc.mn[1][k]);
+    }
+  }
+}
+template <int MT>
+__device__ __forceinline__ void block_q50(const uint8_t* rowA, const uint8_t* rowB, int b, int c32, const uint8_t* dig,
+                                          const float* sxf, const float* xsi, int g, int t, AccT<MT>& acc) {
+  if (b & 1) block_q5_par<MT, false, false>(rowA + b * 22, rowB + b * 22, c32, dig, sxf, xsi, g, t, acc);
+  else block_q5_par<MT, true, false>(rowA + b * 22, rowB + b * 22, c32, dig, sxf, xsi, g, t, acc);
+}
+template <int MT>
+__device__ __forceinline__ void block_q51(const uint8_t* rowA, const uint8_t* rowB, int b, int c32, const uint8_t* dig,
+                                          const float* sxf, const float* xsi, int g, int t, AccT<MT>& acc) {
+  block_q5_par<MT, false, true>(rowA + b * 24, rowB + b * 24, c32, dig, sxf, xsi, g, t, acc);  // 24-byte blocks stay word aligned
+}
 
 // ---- where activations come from ---------------------------------------------------------
 // Plain f32 memory that is ready when the launch starts, or tagged pairs {f32 bits, tag} that an

@@ -218,7 +218,7 @@ def test_gemv_matches_cpu_row_kernels(ex, orc, name, path):
     ex.set_path(0)
 
 
-@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0"])
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0", "Q4_0", "Q5_0", "Q5_1"])
 def test_tensor_core_gemv_handles_awkward_activations(ex, orc, name):
     """Outliers, tiny values, zero blocks and a non-finite activation through the digit split."""
     kind = ALL[name]
