@@ -379,7 +379,13 @@ typedef struct llr_llama_model {
   const llr_llama_layer* layers; /* cfg.n_layer of them */
 } llr_llama_model;
 typedef struct llr_session llr_session;
+/* One sequence, a KV pool that holds n_ctx positions. */
 int llr_session_create(llr_exec* exec, const llr_llama_model* model, llr_session** out);
+/* n_seq sequences over one paged KV pool [langtax/src/kv_page.rs:395-437]: kv_blocks blocks (0: enough for every sequence
+ * to reach n_ctx) of block_tokens positions each; a sequence takes blocks from the pool as it grows and gives them back
+ * when it is reset.  The single-sequence calls below act on sequence 0. */
+int llr_session_create_paged(llr_exec* exec, const llr_llama_model* model, size_t n_seq, size_t kv_blocks,
+                             size_t block_tokens, llr_session** out);
 /* Appends n tokens at the session's position (in chunks of up to 512 rows through the batched
  * products) and leaves the logits of the last one in the session; last_logits (optional, host,
  * n_vocab floats) receives them. */
@@ -392,6 +398,18 @@ int llr_session_logits(llr_session* session, float* logits, size_t n);
 int llr_session_position(const llr_session* session, size_t* position);
 int llr_session_reset(llr_session* session);
 int llr_session_free(llr_session* session);
+/* A ragged batch over several sequences in one pass [Engine::try_compute_batch langtax/src/engine.rs:1215-1274 ->
+ * prefill_batch decode.rs:2579]: group g appends counts[g] tokens (tokens holds the groups one after the other) to
+ * sequence seq_ids[g]; each sequence at most once per batch; at most 512 rows in all.  The groups are flattened in
+ * ascending sequence id into one activation matrix, so every matrix product of the step runs once over all rows, while
+ * attention and the KV cache go by each row's own sequence and position.  last_logits (optional, n_groups x n_vocab,
+ * host) and next_ids (optional, n_groups, host) receive each group's last-row logits and their greedy argmax, in the
+ * caller's group order.  A row's results do not depend on which other rows share its batch when the f32-faithful
+ * products run (llr_exec_set_path(3)). */
+int llr_session_batch(llr_session* session, size_t n_groups, const uint32_t* seq_ids, const uint32_t* counts,
+                      const int32_t* tokens, float* last_logits, int32_t* next_ids);
+int llr_session_seq_position(const llr_session* session, size_t seq, size_t* position);
+int llr_session_seq_reset(llr_session* session, size_t seq);
 
 /* Dequantize rows [row0, row0+n_rows) of a resident matrix to f32 on the
  * device and copy them to out (n_rows*cols floats, host).  Bit-exact

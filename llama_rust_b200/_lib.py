@@ -22,7 +22,8 @@ SYMBOLS = [
     "llr_shared_alloc", "llr_shared_open", "llr_shared_close", "llr_shared_free",
     "llr_program_create_sharded", "llr_program_create_ops", "llr_program_info", "llr_exec_set_wait_limit",
     "llr_session_create", "llr_session_prefill", "llr_session_decode", "llr_session_logits", "llr_session_position",
-    "llr_session_reset", "llr_session_free", "llr_moe_route_device", "llr_moe_experts_device",
+    "llr_session_reset", "llr_session_free", "llr_session_create_paged", "llr_session_batch", "llr_session_seq_position",
+    "llr_session_seq_reset", "llr_moe_route_device", "llr_moe_experts_device",
 ]
 ARENA_HEADER_BYTES = 65536
 
@@ -117,6 +118,10 @@ def load() -> C.CDLL:
     lib.llr_moe_route_device.argtypes = [vp, C.POINTER(MoeLayer), sz, vp, vp, vp]
     lib.llr_moe_experts_device.argtypes = [vp, C.POINTER(MoeLayer), C.POINTER(C.c_uint32), vp, vp]
     lib.llr_session_create.argtypes = [vp, C.POINTER(LlamaModel), C.POINTER(vp)]
+    lib.llr_session_create_paged.argtypes = [vp, C.POINTER(LlamaModel), sz, sz, sz, C.POINTER(vp)]
+    lib.llr_session_batch.argtypes = [vp, sz, vp, vp, vp, vp, vp]
+    lib.llr_session_seq_position.argtypes = [vp, sz, C.POINTER(sz)]
+    lib.llr_session_seq_reset.argtypes = [vp, sz]
     lib.llr_session_prefill.argtypes = [vp, vp, sz, vp]
     lib.llr_session_decode.argtypes = [vp, sz, vp, vp]
     lib.llr_session_logits.argtypes = [vp, vp, sz]

@@ -47,6 +47,14 @@ __device__ __forceinline__ float block_max(float v, float* sh) {
   return t;
 }
 
+__device__ __forceinline__ int row_position(const RowMap& r, int t) { return r.row_pos ? r.row_pos[t] : *r.pos_dev + t; }
+__device__ __forceinline__ int row_sequence(const RowMap& r, int t) { return r.row_seq ? r.row_seq[t] : 0; }
+// first float of the head vector of (sequence, layer, kv head, position) in a paged cache
+__device__ __forceinline__ int64_t kv_offset(const KvView& kv, int seq, int layer, int head, int pos, int n_head_kv, int hd) {
+  const int b = kv.table[(int64_t)seq * kv.max_blocks + pos / kv.block_tokens];
+  return ((((int64_t)b * kv.n_layer + layer) * n_head_kv + head) * kv.block_tokens + pos % kv.block_tokens) * hd;
+}
+
 // one block per activation row
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add, const float* __restrict__ w, float* __restrict__ y,
@@ -72,10 +80,10 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add, const float
 
 // grid (token, head of q and k together): one thread per rotated pair; then the k and v rows go to the cache
 __global__ void __launch_bounds__(128)
-rope_store_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v, float* __restrict__ cache_k,
-                  float* __restrict__ cache_v, const int* __restrict__ pos_dev, int layer, WalkShape w) {
+rope_store_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v, KvView kv, RowMap rows, int layer,
+                  WalkShape w) {
   const int t = blockIdx.x, h = blockIdx.y;  // h < n_head: a q head, else a k head
-  const int pos = *pos_dev + t;
+  const int pos = row_position(rows, t);
   const int hd = w.head_dim;
   const bool is_q = h < w.n_head;
   const int hk = h - w.n_head;
@@ -91,31 +99,34 @@ rope_store_kernel(float* __restrict__ q, float* __restrict__ k, const float* __r
   }
   if (is_q) return;
   __syncthreads();
-  // dense cache [layer][kv_head][t][hd] (store_kv, decode.rs:12059)
-  const int64_t off = (((int64_t)layer * w.n_head_kv + hk) * w.n_ctx + pos) * hd;
+  // store_kv (decode.rs:12059) into the row's sequence, paged
+  const int64_t off = kv_offset(kv, row_sequence(rows, t), layer, hk, pos, w.n_head_kv, hd);
   const float* vv = v + ((int64_t)t * w.n_head_kv + hk) * hd;
   for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-    cache_k[off + i] = vec[i];
-    cache_v[off + i] = vv[i];
+    kv.k[off + i] = vec[i];
+    kv.v[off + i] = vv[i];
   }
 }
 
-// Attention of one token: grid (kv head, position split, token).  A block handles the query heads that share its kv
+// Attention of one token: grid (kv head, position slice, token).  A block handles the query heads that share its kv
 // head over its slice of the positions and writes, per query head, the slice's maximum score, the sum of exp(score -
 // max) and the exp-weighted sum of value rows; attention_combine_kernel merges the slices (the usual two-pass softmax,
-// rearranged so that K and V are read once per kv head and by many SMs).
+// rearranged so that K and V are read once per kv head and by many SMs).  Slices have a fixed length in positions
+// (attention_chunk), whatever the batch: a row's result depends on its own sequence only, never on what shares its batch.
 constexpr int ATT_THREADS = 256;
 constexpr int ATT_MAX_GQA = 8;
 __global__ void __launch_bounds__(ATT_THREADS)
-attention_partial_kernel(const float* __restrict__ q, const float* __restrict__ cache_k, const float* __restrict__ cache_v,
-                         float* __restrict__ part, const int* __restrict__ pos_dev, int layer, int n_split, WalkShape w) {
+attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restrict__ part, RowMap rows, int layer, int chunk,
+                         WalkShape w) {
   extern __shared__ float sm[];  // q[gqa][hd] | scores[gqa][chunk] | red[32]
   const int hkv = blockIdx.x, split = blockIdx.y, t = blockIdx.z;
   const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
-  const int seq = *pos_dev + t + 1;
-  const int chunk = (seq + n_split - 1) / n_split;
+  const int seq = row_position(rows, t) + 1;  // positions this row attends to
+  const int sid = row_sequence(rows, t);
+  const int n_split = (int)gridDim.y;
   const int s0 = split * chunk, s1 = min(seq, s0 + chunk);
-  const int max_chunk = (w.n_ctx + n_split - 1) / n_split;
+  if (s0 >= seq) return;  // this row's sequence ends before the slice
+  const int max_chunk = chunk;
   float* sq = sm;
   float* sc = sq + gqa * hd;
   float* red = sc + gqa * max_chunk;
@@ -124,18 +135,17 @@ attention_partial_kernel(const float* __restrict__ q, const float* __restrict__ 
   for (int i = threadIdx.x; i < gqa * hd; i += ATT_THREADS)
     sq[i] = q[((int64_t)t * w.n_head + hkv * gqa) * hd + i];
   __syncthreads();
-  const float* kbase = cache_k + ((int64_t)layer * w.n_head_kv + hkv) * w.n_ctx * hd;
-  const float* vbase = cache_v + ((int64_t)layer * w.n_head_kv + hkv) * w.n_ctx * hd;
   // scores: one warp per position, all query heads of the group against one read of the K row
   for (int s = s0 + warp; s < s1; s += nw) {
     float acc[ATT_MAX_GQA];
 #pragma unroll
     for (int g = 0; g < ATT_MAX_GQA; ++g) acc[g] = 0.f;
+    const float* krow = kv.k + kv_offset(kv, sid, layer, hkv, s, w.n_head_kv, hd);
     for (int i = lane; i < hd; i += 32) {
-      const float kv = kbase[(int64_t)s * hd + i];
+      const float kv_i = krow[i];
 #pragma unroll
       for (int g = 0; g < ATT_MAX_GQA; ++g)
-        if (g < gqa) acc[g] = fmaf(sq[g * hd + i], kv, acc[g]);
+        if (g < gqa) acc[g] = fmaf(sq[g * hd + i], kv_i, acc[g]);
     }
 #pragma unroll
     for (int g = 0; g < ATT_MAX_GQA; ++g)
@@ -160,32 +170,50 @@ attention_partial_kernel(const float* __restrict__ q, const float* __restrict__ 
     if (threadIdx.x == 0) { out[g * (hd + 2) + hd] = m; out[g * (hd + 2) + hd + 1] = l; }
   }
   __syncthreads();
-  // weighted values: thread i owns dimension i (hd <= ATT_THREADS), positions in ascending order
-  for (int i = threadIdx.x; i < hd; i += ATT_THREADS) {
-    float acc[ATT_MAX_GQA];
+  // weighted values: thread (i, grp) owns dimension i for every P-th run of eight positions of the slice
+  // (P = ATT_THREADS / hd thread groups); the groups' sums are added in group order through shared memory
+  const int P = ATT_THREADS / hd > 0 ? ATT_THREADS / hd : 1;
+  float acc[ATT_MAX_GQA];
 #pragma unroll
-    for (int g = 0; g < ATT_MAX_GQA; ++g) acc[g] = 0.f;
-    for (int s = s0; s < s1; ++s) {
-      const float vv = vbase[(int64_t)s * hd + i];
+  for (int g = 0; g < ATT_MAX_GQA; ++g) acc[g] = 0.f;
+  const int i = threadIdx.x % hd, grp = threadIdx.x / hd;
+  if (grp < P) {
+    // runs of eight positions go to the groups in turn: the split does not depend on the KV block size
+    const int bs = kv.block_tokens;
+    for (int sb = s0 + 8 * grp; sb < s1; sb += 8 * P) {
+      const int se = min(s1, sb + 8);
+      const float* vrow = nullptr;
+      for (int s = sb; s < se; ++s, vrow += hd) {
+        if (s == sb || s % bs == 0) vrow = kv.v + kv_offset(kv, sid, layer, hkv, s, w.n_head_kv, hd) + i;  // a block's rows are contiguous
+        const float vv = *vrow;
 #pragma unroll
-      for (int g = 0; g < ATT_MAX_GQA; ++g)
-        if (g < gqa) acc[g] = fmaf(sc[g * max_chunk + (s - s0)], vv, acc[g]);
+        for (int g = 0; g < ATT_MAX_GQA; ++g)
+          if (g < gqa) acc[g] = fmaf(sc[g * max_chunk + (s - s0)], vv, acc[g]);
+      }
     }
+  }
+  __syncthreads();  // the scores are no longer needed: their space takes the groups' partial sums
+  float* vsum = sc;  // [P][gqa][hd], fits: P * hd <= ATT_THREADS and gqa * max_chunk >= ... checked at launch
+  if (grp < P)
 #pragma unroll
     for (int g = 0; g < ATT_MAX_GQA; ++g)
-      if (g < gqa) out[g * (hd + 2) + i] = acc[g];
+      if (g < gqa) vsum[(grp * gqa + g) * hd + i] = acc[g];
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < gqa * hd; idx += ATT_THREADS) {
+    float v = 0.f;
+    for (int p = 0; p < P; ++p) v += vsum[p * gqa * hd + idx];
+    out[(idx / hd) * (hd + 2) + idx % hd] = v;
   }
 }
 
 // grid (query head, token): merges the position slices in ascending order
 __global__ void __launch_bounds__(128)
-attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, const int* __restrict__ pos_dev,
-                         int n_split, WalkShape w) {
+attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, RowMap rows, int chunk, WalkShape w) {
   const int hq = blockIdx.x, t = blockIdx.y;
   const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
   const int hkv = hq / gqa, g = hq % gqa;
-  const int seq = *pos_dev + t + 1;
-  const int chunk = (seq + n_split - 1) / n_split;
+  const int seq = row_position(rows, t) + 1;
+  const int n_split = (w.n_ctx + chunk - 1) / chunk;
   const float* base = part + ((int64_t)t * w.n_head_kv + hkv) * n_split * gqa * (hd + 2) + g * (hd + 2);
   float m = -CUDART_INF_F;
   for (int sp = 0; sp < n_split && sp * chunk < seq; ++sp) m = fmaxf(m, base[(int64_t)sp * gqa * (hd + 2) + hd]);
@@ -223,6 +251,9 @@ argmax_kernel(const float* __restrict__ logits, int n, int* __restrict__ out_id,
   // with count_dev: out_id[0] is the slot the next step reads its token from, and the token and its margin are also
   // appended at out_id[1 + *count_dev] / out_margin[*count_dev]: every step of a generation is then the same launch
   const int slot = count_dev ? *count_dev : 0;
+  logits += (int64_t)blockIdx.x * n;  // one block per row of logits (a single row unless launch_argmax_rows)
+  out_id += blockIdx.x;
+  if (out_margin) out_margin += blockIdx.x;
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ int s_best;
@@ -275,12 +306,14 @@ argmax_kernel(const float* __restrict__ logits, int n, int* __restrict__ out_id,
   if (threadIdx.x == 0 && pos_dev) *pos_dev += advance;
 }
 
-int attention_splits(int tokens, const WalkShape& w) {
-  // enough blocks to occupy the device when one token attends (decode); a chunk of prompt tokens brings its own
-  int splits = tokens >= 16 ? 1 : 148 / (w.n_head_kv > 0 ? w.n_head_kv : 1);
-  if (splits < 1) splits = 1;
-  if (splits > 16) splits = 16;
-  return splits;
+// positions per attention slice: 32, or a thirty-second of the context when that is longer
+int attention_chunk(const WalkShape& w) {
+  const int c = (w.n_ctx + 31) / 32;
+  return c > 32 ? c : 32;
+}
+int attention_splits(const WalkShape& w) {
+  const int c = attention_chunk(w);
+  return (w.n_ctx + c - 1) / c;
 }
 
 }  // namespace
@@ -293,26 +326,28 @@ cudaError_t launch_rmsnorm(float* x, const float* add, const float* w, float* y,
   return cudaGetLastError();
 }
 
-cudaError_t launch_rope_store(float* q, float* k, const float* v, float* cache_k, float* cache_v, const int* pos_dev,
-                              int tokens, int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches) {
+cudaError_t launch_rope_store(float* q, float* k, const float* v, const KvView& kv, const RowMap& rows, int tokens, int layer,
+                              const WalkShape& w, cudaStream_t s, uint64_t* launches) {
   if (tokens <= 0) return cudaSuccess;
-  rope_store_kernel<<<dim3(tokens, w.n_head + w.n_head_kv), 128, 0, s>>>(q, k, v, cache_k, cache_v, pos_dev, layer, w);
+  rope_store_kernel<<<dim3(tokens, w.n_head + w.n_head_kv), 128, 0, s>>>(q, k, v, kv, rows, layer, w);
   if (launches) ++*launches;
   return cudaGetLastError();
 }
 
 size_t attention_scratch_floats(int tokens, const WalkShape& w) {
-  return (size_t)tokens * w.n_head_kv * attention_splits(tokens, w) * (w.n_head / w.n_head_kv) * (w.head_dim + 2);
+  return (size_t)tokens * w.n_head_kv * attention_splits(w) * (w.n_head / w.n_head_kv) * (w.head_dim + 2);
 }
 
-cudaError_t launch_attention(const float* q, const float* cache_k, const float* cache_v, float* out, float* scratch,
-                             const int* pos_dev, int tokens, int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches) {
+cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float* scratch, const RowMap& rows, int tokens,
+                             int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches) {
   if (tokens <= 0) return cudaSuccess;
   const int gqa = w.n_head / w.n_head_kv;
-  if (gqa < 1 || gqa > ATT_MAX_GQA || w.n_head % w.n_head_kv != 0 || w.head_dim > 1024) return cudaErrorInvalidValue;
-  const int splits = attention_splits(tokens, w);
-  const int max_chunk = (w.n_ctx + splits - 1) / splits;
-  const size_t smem = ((size_t)gqa * w.head_dim + (size_t)gqa * max_chunk + 32) * sizeof(float);
+  if (gqa < 1 || gqa > ATT_MAX_GQA || w.n_head % w.n_head_kv != 0 || w.head_dim > ATT_THREADS) return cudaErrorInvalidValue;
+  const int splits = attention_splits(w);
+  const int max_chunk = attention_chunk(w);
+  const size_t groups = ATT_THREADS / w.head_dim > 0 ? ATT_THREADS / w.head_dim : 1;
+  const size_t score_floats = (size_t)gqa * max_chunk > groups * gqa * w.head_dim ? (size_t)gqa * max_chunk : groups * gqa * w.head_dim;
+  const size_t smem = ((size_t)gqa * w.head_dim + score_floats + 32) * sizeof(float);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
@@ -320,9 +355,8 @@ cudaError_t launch_attention(const float* q, const float* cache_k, const float* 
     if (e != cudaSuccess) return e;
     configured = smem;
   }
-  attention_partial_kernel<<<dim3(w.n_head_kv, splits, tokens), ATT_THREADS, smem, s>>>(q, cache_k, cache_v, scratch, pos_dev,
-                                                                                      layer, splits, w);
-  attention_combine_kernel<<<dim3(w.n_head, tokens), 128, 0, s>>>(scratch, out, pos_dev, splits, w);
+  attention_partial_kernel<<<dim3(w.n_head_kv, splits, tokens), ATT_THREADS, smem, s>>>(q, kv, scratch, rows, layer, max_chunk, w);
+  attention_combine_kernel<<<dim3(w.n_head, tokens), 128, 0, s>>>(scratch, out, rows, max_chunk, w);
   if (launches) *launches += 2;
   return cudaGetLastError();
 }
@@ -341,6 +375,14 @@ cudaError_t launch_add(float* x, const float* y, int64_t n, cudaStream_t s, uint
   int64_t blocks = (n + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   add_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, y, n);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_rows(const float* logits, int n_rows, int n, int* out_id, float* out_margin, cudaStream_t s,
+                               uint64_t* launches) {
+  if (n_rows <= 0) return cudaSuccess;
+  argmax_kernel<<<n_rows, 1024, 0, s>>>(logits, n, out_id, out_margin, nullptr, 0, nullptr);
   if (launches) ++*launches;
   return cudaGetLastError();
 }

@@ -1315,15 +1315,22 @@ struct llr_session {
   std::vector<llr_llama_layer> layers;
   std::vector<float*> attn_norm, ffn_norm;  // device copies (null: all ones)
   float* out_norm = nullptr;
-  size_t max_batch = 0, position = 0;
-  bool have_logits = false;
+  size_t max_batch = 0;
+  // sequences and their paged KV (kv_page.rs): blocks of block_tokens positions, a table of block ids per sequence
+  size_t n_seq = 1, block_tokens = 16, max_blocks = 0, n_blocks = 0;
+  std::vector<size_t> position;             // tokens appended per sequence
+  std::vector<std::vector<int>> seq_blocks; // block ids per sequence, in order
+  std::vector<int> free_blocks;
+  std::vector<char> have_logits;            // sequence 0: logits in `logits` belong to it
   // device buffers
   float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *proj = nullptr,
         *gate = nullptr, *up = nullptr, *logits = nullptr, *cache_k = nullptr, *cache_v = nullptr, *att_scratch = nullptr,
-        *margins = nullptr;
+        *margins = nullptr, *last_x = nullptr;
+  size_t logits_rows = 1;
   int *ids = nullptr, *pos_dev = nullptr;  // ids[0]: the token the next step reads; ids[1..]: prompt chunk or generated tokens
   size_t ids_cap = 0;
   int* count_dev = nullptr;  // tokens generated by the current llr_session_decode call
+  int *table_dev = nullptr, *row_pos = nullptr, *row_seq = nullptr, *last_rows = nullptr;
   cudaGraphExec_t step_graph = nullptr;  // one decode step, captured once per kernel path
   int step_graph_path = -1, step_kernels = 0;
   bool use_graph = true;
@@ -1335,11 +1342,10 @@ void session_release(llr_session* s) {
   for (float* p : s->attn_norm) if (p) cudaFree(p);
   for (float* p : s->ffn_norm) if (p) cudaFree(p);
   float* bufs[] = {s->out_norm, s->x, s->xn, s->q, s->k, s->v, s->attn, s->proj, s->gate, s->up, s->logits,
-                   s->cache_k, s->cache_v, s->att_scratch, s->margins};
+                   s->cache_k, s->cache_v, s->att_scratch, s->margins, s->last_x};
   for (float* p : bufs) if (p) cudaFree(p);
-  if (s->ids) cudaFree(s->ids);
-  if (s->pos_dev) cudaFree(s->pos_dev);
-  if (s->count_dev) cudaFree(s->count_dev);
+  int* ibufs[] = {s->ids, s->pos_dev, s->count_dev, s->table_dev, s->row_pos, s->row_seq, s->last_rows};
+  for (int* p : ibufs) if (p) cudaFree(p);
   if (s->step_graph) cudaGraphExecDestroy(s->step_graph);
   cudaGetLastError();
 }
@@ -1351,14 +1357,37 @@ cudaError_t session_matmul(llr_exec* e, const llr_matrix* m, size_t tokens, cons
   return launch_matmul(view_of(m), x, y, (int64_t)tokens, e->stream, e->path, e->sm_count, e->err_flag, scratch, &e->ctr.launches);
 }
 
-// One forward pass over `n` tokens whose ids lie at ids_dev (device) starting at the session's device-side position;
-// with_logits: the last token's logits, then argmax into *next_id (and the margin) and the position advanced by n.
-cudaError_t session_forward(llr_session* s, const int* ids_dev, size_t n, bool with_logits, bool generate) {
+KvView session_kv(const llr_session* s) {
+  return KvView{s->cache_k, s->cache_v, s->table_dev, (int)s->block_tokens, (int)s->max_blocks, (int)s->cfg.n_layer};
+}
+
+// Blocks for positions [0, upto) of a sequence; new table entries go to the device on the executor's stream.
+int session_reserve(llr_session* s, size_t seq, size_t upto) {
+  llr_exec* e = s->owner;
+  const size_t need = (upto + s->block_tokens - 1) / s->block_tokens;
+  std::vector<int>& mine = s->seq_blocks[seq];
+  const size_t had = mine.size();
+  if (need <= had) return LLR_OK;
+  if (need - had > s->free_blocks.size())
+    return fail(e, LLR_ERR_OOM, "the session's KV pool has no free block left (" + std::to_string(s->n_blocks) + " blocks of " +
+                                    std::to_string(s->block_tokens) + " positions)");
+  while (mine.size() < need) { mine.push_back(s->free_blocks.back()); s->free_blocks.pop_back(); }
+  cudaError_t ce = cudaMemcpyAsync(s->table_dev + seq * s->max_blocks + had, mine.data() + had, (need - had) * sizeof(int),
+                                   cudaMemcpyHostToDevice, e->stream);
+  if (ce != cudaSuccess) return fail_cuda(e, ce, "block table upload");
+  // the host vector may grow again before the copy has run: pageable copies of this size are staged by the driver at call time
+  return LLR_OK;
+}
+
+// The layers over n rows whose token ids lie at ids_dev; rows stand where `rows` says.  Leaves the residual stream in
+// s->x and the last ffn_down result, not yet added, in s->proj (returned through *pending).
+cudaError_t session_layers(llr_session* s, const int* ids_dev, size_t n, const RowMap& rows, const float** pending_out) {
   llr_exec* e = s->owner;
   const llr_llama_config& c = s->cfg;
-  const size_t E = c.n_embd, QW = (size_t)c.n_head * c.head_dim, FF = c.n_ff;
+  const size_t E = c.n_embd, FF = c.n_ff;
   cudaStream_t st = e->stream;
   uint64_t* L = &e->ctr.launches;
+  const KvView kv = session_kv(s);
   cudaError_t ce = launch_dequant_indexed(view_of(s->embd), ids_dev, (int64_t)n, s->x, st, L);
   const float* pending = nullptr;  // ffn_down result of the previous layer, not yet added to the residual stream
   for (size_t li = 0; li < c.n_layer && ce == cudaSuccess; ++li) {
@@ -1367,8 +1396,8 @@ cudaError_t session_forward(llr_session* s, const int* ids_dev, size_t n, bool w
     if ((ce = session_matmul(e, W.attn_q, n, s->xn, s->q)) != cudaSuccess) break;
     if ((ce = session_matmul(e, W.attn_k, n, s->xn, s->k)) != cudaSuccess) break;
     if ((ce = session_matmul(e, W.attn_v, n, s->xn, s->v)) != cudaSuccess) break;
-    if ((ce = launch_rope_store(s->q, s->k, s->v, s->cache_k, s->cache_v, s->pos_dev, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
-    if ((ce = launch_attention(s->q, s->cache_k, s->cache_v, s->attn, s->att_scratch, s->pos_dev, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
+    if ((ce = launch_rope_store(s->q, s->k, s->v, kv, rows, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
+    if ((ce = launch_attention(s->q, kv, s->attn, s->att_scratch, rows, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
     if ((ce = session_matmul(e, W.attn_output, n, s->attn, s->proj)) != cudaSuccess) break;
     if ((ce = launch_rmsnorm(s->x, s->proj, s->ffn_norm[li], s->xn, (int)n, (int)E, c.rms_eps, st, L)) != cudaSuccess) break;
     if ((ce = session_matmul(e, W.ffn_gate, n, s->xn, s->gate)) != cudaSuccess) break;
@@ -1377,7 +1406,20 @@ cudaError_t session_forward(llr_session* s, const int* ids_dev, size_t n, bool w
     if ((ce = session_matmul(e, W.ffn_down, n, s->gate, s->proj)) != cudaSuccess) break;
     pending = s->proj;
   }
-  (void)QW;
+  *pending_out = pending;
+  return ce;
+}
+
+// One forward pass of sequence 0 over `n` tokens at its device-side position; with_logits: the last token's logits, then
+// (generate) argmax into ids[0] and the history, and the position advanced by n.
+cudaError_t session_forward(llr_session* s, const int* ids_dev, size_t n, bool with_logits, bool generate) {
+  llr_exec* e = s->owner;
+  const llr_llama_config& c = s->cfg;
+  const size_t E = c.n_embd;
+  cudaStream_t st = e->stream;
+  uint64_t* L = &e->ctr.launches;
+  const float* pending = nullptr;
+  cudaError_t ce = session_layers(s, ids_dev, n, RowMap{s->pos_dev, nullptr, nullptr}, &pending);
   if (ce != cudaSuccess) return ce;
   if (with_logits) {
     // LogitsKind::Last (decode.rs:3058-3079): the last row only
@@ -1391,18 +1433,32 @@ cudaError_t session_forward(llr_session* s, const int* ids_dev, size_t n, bool w
   return launch_argmax_advance(nullptr, 0, nullptr, nullptr, s->pos_dev, (int)n, nullptr, st, L);
 }
 
-}  // namespace
+int session_ids(llr_session* s, size_t n) {
+  if (n <= s->ids_cap) return LLR_OK;
+  cudaStreamSynchronize(s->owner->stream);
+  if (s->ids) cudaFree(s->ids);
+  if (s->margins) cudaFree(s->margins);
+  s->ids = nullptr; s->margins = nullptr; s->ids_cap = 0;
+  cudaError_t ce = cudaMalloc((void**)&s->ids, (n + 2) * sizeof(int));
+  if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->margins, (n + 2) * sizeof(float));
+  if (ce != cudaSuccess) return fail_cuda(s->owner, ce, "token buffer");
+  s->ids_cap = n;
+  if (s->step_graph) { cudaGraphExecDestroy(s->step_graph); s->step_graph = nullptr; }  // the captured step addresses the old buffers
+  return LLR_OK;
+}
 
-int llr_session_create(llr_exec* e, const llr_llama_model* m, llr_session** out) {
+int session_create(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t kv_blocks, size_t block_tokens, llr_session** out) {
   if (!e) return LLR_ERR_INVALID;
   if (!out) return fail(e, LLR_ERR_INVALID, "null output pointer");
   *out = nullptr;
   if (!m || !m->layers || !m->token_embd) return fail(e, LLR_ERR_INVALID, "null model");
   const llr_llama_config& c = m->cfg;
   if (c.n_layer == 0 || c.n_embd == 0 || c.n_head == 0 || c.n_head_kv == 0 || c.head_dim == 0 || c.n_ff == 0 || c.n_vocab == 0 ||
-      c.n_ctx == 0 || c.n_head % c.n_head_kv != 0 || c.n_head / c.n_head_kv > 8 || c.head_dim % 2 != 0 || c.head_dim > 1024 ||
+      c.n_ctx == 0 || c.n_head % c.n_head_kv != 0 || c.n_head / c.n_head_kv > 8 || c.head_dim % 2 != 0 || c.head_dim > 256 ||
       c.n_embd % 8 != 0 || c.n_ctx > (1u << 20) || !(c.rms_eps >= 0.0f) || !(c.rope_base > 0.0f))
-    return fail(e, LLR_ERR_INVALID, "llama configuration out of range (grouped-query ratio at most 8, even head_dim, n_embd % 8 == 0)");
+    return fail(e, LLR_ERR_INVALID, "llama configuration out of range (grouped-query ratio at most 8, even head_dim up to 256, n_embd % 8 == 0)");
+  if (n_seq == 0 || n_seq > 4096 || block_tokens == 0 || block_tokens > c.n_ctx)
+    return fail(e, LLR_ERR_INVALID, "a session holds 1..4096 sequences and KV blocks of 1..n_ctx positions");
   const size_t E = c.n_embd, QW = (size_t)c.n_head * c.head_dim, KVW = (size_t)c.n_head_kv * c.head_dim, FF = c.n_ff, V = c.n_vocab;
   auto shape_ok = [&](const llr_matrix* w, size_t rows, size_t cols) {
     return w && w->owner == e && (size_t)w->rows == rows && (size_t)w->cols == cols;
@@ -1427,10 +1483,20 @@ int llr_session_create(llr_exec* e, const llr_llama_model* m, llr_session** out)
   const float n_rot = (float)(uint16_t)c.head_dim;
   s->shape = WalkShape{(int)c.n_embd, (int)c.n_head, (int)c.n_head_kv, (int)c.head_dim, (int)c.n_ff, (int)c.n_ctx, c.rms_eps, c.rope_base,
                        std::pow(c.rope_base, -2.0f / n_rot)};  // decode.rs:11578: theta_scale in f32
-  s->max_batch = c.n_ctx < 512 ? c.n_ctx : 512;
+  s->max_batch = c.n_ctx * n_seq < 512 ? c.n_ctx * n_seq : 512;
+  s->n_seq = n_seq;
+  s->block_tokens = block_tokens;
+  s->max_blocks = (c.n_ctx + block_tokens - 1) / block_tokens;
+  s->n_blocks = kv_blocks ? kv_blocks : s->max_blocks * n_seq;
+  s->position.assign(n_seq, 0);
+  s->seq_blocks.assign(n_seq, {});
+  s->have_logits.assign(n_seq, 0);
+  for (size_t b = s->n_blocks; b-- > 0;) s->free_blocks.push_back((int)b);
+  s->logits_rows = n_seq;
   const size_t B = s->max_batch;
   cudaError_t ce = cudaSuccess;
   auto alloc = [&](float** p, size_t n) { if (ce == cudaSuccess) ce = cudaMalloc((void**)p, n * sizeof(float)); };
+  auto ialloc = [&](int** p, size_t n) { if (ce == cudaSuccess) ce = cudaMalloc((void**)p, n * sizeof(int)); };
   auto norm = [&](const float* host, float** dev) {
     *dev = nullptr;
     if (!host || ce != cudaSuccess) return;
@@ -1442,16 +1508,15 @@ int llr_session_create(llr_exec* e, const llr_llama_model* m, llr_session** out)
   for (uint32_t li = 0; li < c.n_layer; ++li) { norm(m->layers[li].attn_norm, &s->attn_norm[li]); norm(m->layers[li].ffn_norm, &s->ffn_norm[li]); }
   norm(m->output_norm, &s->out_norm);
   alloc(&s->x, B * E); alloc(&s->xn, B * E); alloc(&s->q, B * QW); alloc(&s->k, B * KVW); alloc(&s->v, B * KVW);
-  alloc(&s->attn, B * QW); alloc(&s->proj, B * E); alloc(&s->gate, B * FF); alloc(&s->up, B * FF); alloc(&s->logits, V);
-  const size_t cache = (size_t)c.n_layer * c.n_head_kv * c.n_ctx * c.head_dim;
-  alloc(&s->cache_k, cache); alloc(&s->cache_v, cache);
-  size_t sc = attention_scratch_floats((int)B, s->shape), sc1 = attention_scratch_floats(1, s->shape), sc15 = attention_scratch_floats(15, s->shape);
-  if (sc1 > sc) sc = sc1;
-  if (sc15 > sc) sc = sc15;
-  alloc(&s->att_scratch, sc);
-  if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->pos_dev, sizeof(int));
+  alloc(&s->attn, B * QW); alloc(&s->proj, B * E); alloc(&s->gate, B * FF); alloc(&s->up, B * FF);
+  alloc(&s->logits, s->logits_rows * V); alloc(&s->last_x, n_seq * E);
+  const size_t pool = s->n_blocks * c.n_layer * c.n_head_kv * block_tokens * c.head_dim;
+  alloc(&s->cache_k, pool); alloc(&s->cache_v, pool);
+  alloc(&s->att_scratch, attention_scratch_floats((int)B, s->shape));
+  ialloc(&s->pos_dev, 1); ialloc(&s->count_dev, 1);
+  ialloc(&s->table_dev, n_seq * s->max_blocks); ialloc(&s->row_pos, B); ialloc(&s->row_seq, B); ialloc(&s->last_rows, n_seq);
   if (ce == cudaSuccess) ce = cudaMemset(s->pos_dev, 0, sizeof(int));
-  if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->count_dev, sizeof(int));
+  if (ce == cudaSuccess) ce = cudaMemset(s->table_dev, 0, n_seq * s->max_blocks * sizeof(int));
   if (const char* g = std::getenv("LLR_SESSION_GRAPH")) s->use_graph = std::strcmp(g, "0") != 0;
   if (ce != cudaSuccess) {
     session_release(s);
@@ -1460,6 +1525,15 @@ int llr_session_create(llr_exec* e, const llr_llama_model* m, llr_session** out)
   }
   *out = s;
   return LLR_OK;
+}
+
+}  // namespace
+
+int llr_session_create(llr_exec* e, const llr_llama_model* m, llr_session** out) { return session_create(e, m, 1, 0, 16, out); }
+
+int llr_session_create_paged(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t kv_blocks, size_t block_tokens,
+                             llr_session** out) {
+  return session_create(e, m, n_seq, kv_blocks, block_tokens, out);
 }
 
 int llr_session_free(llr_session* s) {
@@ -1473,31 +1547,39 @@ int llr_session_free(llr_session* s) {
   return LLR_OK;
 }
 
+int llr_session_seq_reset(llr_session* s, size_t seq) {
+  if (!s || !s->owner) return LLR_ERR_INVALID;
+  if (seq >= s->n_seq) return fail(s->owner, LLR_ERR_INVALID, "sequence index out of range");
+  DeviceGuard guard(s->owner->device);
+  if (seq == 0) {
+    cudaError_t ce = cudaMemsetAsync(s->pos_dev, 0, sizeof(int), s->owner->stream);
+    if (ce != cudaSuccess) return fail_cuda(s->owner, ce, "session reset");
+  }
+  for (int b : s->seq_blocks[seq]) s->free_blocks.push_back(b);  // its blocks go back to the pool
+  s->seq_blocks[seq].clear();
+  s->position[seq] = 0;
+  s->have_logits[seq] = 0;
+  return LLR_OK;
+}
+
 int llr_session_reset(llr_session* s) {
   if (!s || !s->owner) return LLR_ERR_INVALID;
-  DeviceGuard guard(s->owner->device);
-  cudaError_t ce = cudaMemsetAsync(s->pos_dev, 0, sizeof(int), s->owner->stream);
-  if (ce != cudaSuccess) return fail_cuda(s->owner, ce, "session reset");
-  s->position = 0;
-  s->have_logits = false;
+  for (size_t q = 0; q < s->n_seq; ++q) {
+    int rc = llr_session_seq_reset(s, q);
+    if (rc) return rc;
+  }
   return LLR_OK;
 }
 
 int llr_session_position(const llr_session* s, size_t* position) {
   if (!s || !position) return LLR_ERR_INVALID;
-  *position = s->position;
+  *position = s->position[0];
   return LLR_OK;
 }
 
-static int session_ids(llr_session* s, size_t n) {
-  if (n <= s->ids_cap) return LLR_OK;
-  if (s->ids) cudaFree(s->ids);
-  if (s->margins) cudaFree(s->margins);
-  s->ids = nullptr; s->margins = nullptr; s->ids_cap = 0;
-  cudaError_t ce = cudaMalloc((void**)&s->ids, (n + 2) * sizeof(int));
-  if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->margins, (n + 2) * sizeof(float));
-  if (ce != cudaSuccess) return fail_cuda(s->owner, ce, "token buffer");
-  s->ids_cap = n;
+int llr_session_seq_position(const llr_session* s, size_t seq, size_t* position) {
+  if (!s || !position || seq >= s->n_seq) return LLR_ERR_INVALID;
+  *position = s->position[seq];
   return LLR_OK;
 }
 
@@ -1505,12 +1587,13 @@ int llr_session_prefill(llr_session* s, const int32_t* tokens, size_t n, float* 
   if (!s || !s->owner) return LLR_ERR_INVALID;
   llr_exec* e = s->owner;
   if (!tokens || n == 0) return fail(e, LLR_ERR_INVALID, "prefill needs at least one token");
-  if (s->position + n > s->cfg.n_ctx) return fail(e, LLR_ERR_INVALID, "the sequence would exceed the session's context length");
+  if (s->position[0] + n > s->cfg.n_ctx) return fail(e, LLR_ERR_INVALID, "the sequence would exceed the session's context length");
   for (size_t i = 0; i < n; ++i)
     if (tokens[i] < 0 || (uint32_t)tokens[i] >= s->cfg.n_vocab) return fail(e, LLR_ERR_INVALID, "token id out of range");
   DeviceGuard guard(e->device);
   int rc = session_ids(s, n > 1 ? n : 1);
   if (rc) return rc;
+  if ((rc = session_reserve(s, 0, s->position[0] + n))) return rc;
   cudaError_t ce = cudaMemcpyAsync(s->ids + 1, tokens, n * sizeof(int), cudaMemcpyHostToDevice, e->stream);
   for (size_t t0 = 0; t0 < n && ce == cudaSuccess; t0 += s->max_batch) {
     const size_t m = n - t0 < s->max_batch ? n - t0 : s->max_batch;
@@ -1521,8 +1604,8 @@ int llr_session_prefill(llr_session* s, const int32_t* tokens, size_t n, float* 
   if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
   if (ce != cudaSuccess) return fail_cuda(e, ce, "prefill");
   if (take_device_error(e) != 0) return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations");
-  s->position += n;
-  s->have_logits = true;
+  s->position[0] += n;
+  s->have_logits[0] = 1;
   return LLR_OK;
 }
 
@@ -1530,11 +1613,12 @@ int llr_session_decode(llr_session* s, size_t n_gen, int32_t* out_ids, float* ou
   if (!s || !s->owner) return LLR_ERR_INVALID;
   llr_exec* e = s->owner;
   if (!out_ids || n_gen == 0) return fail(e, LLR_ERR_INVALID, "decode needs a token count and an output buffer");
-  if (!s->have_logits) return fail(e, LLR_ERR_INVALID, "decode needs logits: prefill at least one token first");
-  if (s->position + n_gen > s->cfg.n_ctx) return fail(e, LLR_ERR_INVALID, "the sequence would exceed the session's context length");
+  if (!s->have_logits[0]) return fail(e, LLR_ERR_INVALID, "decode needs logits: prefill at least one token first");
+  if (s->position[0] + n_gen > s->cfg.n_ctx) return fail(e, LLR_ERR_INVALID, "the sequence would exceed the session's context length");
   DeviceGuard guard(e->device);
   int rc = session_ids(s, n_gen + 1);
   if (rc) return rc;
+  if ((rc = session_reserve(s, 0, s->position[0] + n_gen))) return rc;  // every block the steps below will write
   // Token 0 = argmax of the current logits.  Every step then reads its token from ids[0], runs the walk, and its
   // argmax writes the next token to ids[0] and appends it to the history ids[1..]; the position and the count live on
   // the device too.  So all steps are the same sequence of launches: the second one is captured into a graph, which
@@ -1582,7 +1666,7 @@ int llr_session_decode(llr_session* s, size_t n_gen, int32_t* out_ids, float* ou
   if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
   if (ce != cudaSuccess) return fail_cuda(e, ce, "decode");
   if (take_device_error(e) != 0) return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations");
-  s->position += n_gen;
+  s->position[0] += n_gen;
   e->ctr.d2h_bytes += n_gen * sizeof(int);
   return LLR_OK;
 }
@@ -1590,11 +1674,101 @@ int llr_session_decode(llr_session* s, size_t n_gen, int32_t* out_ids, float* ou
 int llr_session_logits(llr_session* s, float* logits, size_t n) {
   if (!s || !s->owner) return LLR_ERR_INVALID;
   llr_exec* e = s->owner;
-  if (!logits || n != s->cfg.n_vocab || !s->have_logits) return fail(e, LLR_ERR_INVALID, "logits buffer does not match n_vocab, or no token has been run");
+  if (!logits || n != s->cfg.n_vocab || !s->have_logits[0]) return fail(e, LLR_ERR_INVALID, "logits buffer does not match n_vocab, or no token has been run");
   DeviceGuard guard(e->device);
   cudaError_t ce = cudaMemcpyAsync(logits, s->logits, n * sizeof(float), cudaMemcpyDeviceToHost, e->stream);
   if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
   if (ce != cudaSuccess) return fail_cuda(e, ce, "logits download");
+  return LLR_OK;
+}
+
+// A ragged batch: group g appends counts[g] tokens to sequence seq_ids[g].  The groups are flattened, in ascending sequence
+// id, into one activation matrix of sum(counts) rows, so that every matrix product of the step runs once over all of them
+// (Engine::try_compute_batch, engine.rs:1215-1274 -> prefill_batch decode.rs:2579); attention and the KV cache go by
+// each row's own sequence and position.  last_logits (optional, n_groups x n_vocab, in the caller's group order) and
+// next_ids (optional, n_groups) receive each group's last-row logits and their greedy argmax.
+int llr_session_batch(llr_session* s, size_t n_groups, const uint32_t* seq_ids, const uint32_t* counts, const int32_t* tokens,
+                      float* last_logits, int32_t* next_ids) {
+  if (!s || !s->owner) return LLR_ERR_INVALID;
+  llr_exec* e = s->owner;
+  if (n_groups == 0 || n_groups > s->n_seq || !seq_ids || !counts || !tokens) return fail(e, LLR_ERR_INVALID, "a batch needs 1..n_seq groups");
+  const llr_llama_config& c = s->cfg;
+  const size_t E = c.n_embd, V = c.n_vocab;
+  size_t total = 0;
+  std::vector<size_t> first(n_groups);
+  std::vector<char> seen(s->n_seq, 0);
+  for (size_t g = 0; g < n_groups; ++g) {
+    if (seq_ids[g] >= s->n_seq || seen[seq_ids[g]]) return fail(e, LLR_ERR_INVALID, "sequence index out of range or used twice in one batch");
+    seen[seq_ids[g]] = 1;
+    if (counts[g] == 0) return fail(e, LLR_ERR_INVALID, "an empty group");
+    if (s->position[seq_ids[g]] + counts[g] > c.n_ctx) return fail(e, LLR_ERR_INVALID, "a sequence would exceed the session's context length");
+    first[g] = total;
+    total += counts[g];
+  }
+  if (total > s->max_batch) return fail(e, LLR_ERR_INVALID, "the batch has more rows than the session's chunk size (" + std::to_string(s->max_batch) + ")");
+  for (size_t i = 0; i < total; ++i)
+    if (tokens[i] < 0 || (uint32_t)tokens[i] >= c.n_vocab) return fail(e, LLR_ERR_INVALID, "token id out of range");
+  DeviceGuard guard(e->device);
+  int rc = session_ids(s, total);
+  if (rc) return rc;
+  // flatten in ascending sequence id (the engine sorts its jobs by slot)
+  std::vector<size_t> order(n_groups);
+  for (size_t g = 0; g < n_groups; ++g) order[g] = g;
+  std::sort(order.begin(), order.end(), [&](size_t a, size_t b) { return seq_ids[a] < seq_ids[b]; });
+  std::vector<int> ids(total), rpos(total), rseq(total), last(n_groups);
+  size_t r = 0;
+  for (size_t oi = 0; oi < n_groups; ++oi) {
+    const size_t g = order[oi], q = seq_ids[g];
+    if ((rc = session_reserve(s, q, s->position[q] + counts[g]))) return rc;
+    for (size_t i = 0; i < counts[g]; ++i, ++r) {
+      ids[r] = tokens[first[g] + i];
+      rpos[r] = (int)(s->position[q] + i);
+      rseq[r] = (int)q;
+    }
+    last[oi] = (int)r - 1;
+  }
+  cudaStream_t st = e->stream;
+  uint64_t* L = &e->ctr.launches;
+  cudaError_t ce;
+  if ((ce = cudaMemcpyAsync(s->ids + 1, ids.data(), total * sizeof(int), cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+      (ce = cudaMemcpyAsync(s->row_pos, rpos.data(), total * sizeof(int), cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+      (ce = cudaMemcpyAsync(s->row_seq, rseq.data(), total * sizeof(int), cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+      (ce = cudaMemcpyAsync(s->last_rows, last.data(), n_groups * sizeof(int), cudaMemcpyHostToDevice, st)) != cudaSuccess)
+    return fail_cuda(e, ce, "batch upload");
+  const float* pending = nullptr;
+  if ((ce = session_layers(s, s->ids + 1, total, RowMap{nullptr, s->row_pos, s->row_seq}, &pending)) != cudaSuccess)
+    return fail_cuda(e, ce, "kernel launch");
+  // each group's last row: residual add, output norm, logits (LogitsKind::Last per sequence)
+  if (pending && (ce = launch_add(s->x, pending, (int64_t)(total * E), st, L)) != cudaSuccess) return fail_cuda(e, ce, "kernel launch");
+  if ((ce = launch_gather_rows(s->x, s->last_rows, s->last_x, (int)n_groups, (int)E, st, L)) != cudaSuccess ||
+      (ce = launch_rmsnorm(s->last_x, nullptr, s->out_norm, s->last_x, (int)n_groups, (int)E, c.rms_eps, st, L)) != cudaSuccess ||
+      (ce = session_matmul(e, s->output, n_groups, s->last_x, s->logits)) != cudaSuccess)
+    return fail_cuda(e, ce, "kernel launch");
+  std::vector<int> win(n_groups);
+  if (next_ids) {
+    if ((ce = launch_argmax_rows(s->logits, (int)n_groups, (int)V, s->ids, nullptr, st, L)) != cudaSuccess ||
+        (ce = cudaMemcpyAsync(win.data(), s->ids, n_groups * sizeof(int), cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+      return fail_cuda(e, ce, "argmax");
+  }
+  std::vector<float> lg(last_logits ? n_groups * V : 0);
+  if (last_logits && (ce = cudaMemcpyAsync(lg.data(), s->logits, n_groups * V * sizeof(float), cudaMemcpyDeviceToHost, st)) != cudaSuccess)
+    return fail_cuda(e, ce, "logits download");
+  if ((ce = cudaStreamSynchronize(st)) != cudaSuccess) return fail_cuda(e, ce, "batch");
+  if (take_device_error(e) != 0) return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations");
+  for (size_t oi = 0; oi < n_groups; ++oi) {  // results back in the caller's group order
+    const size_t g = order[oi];
+    if (next_ids) next_ids[g] = win[oi];
+    if (last_logits) std::memcpy(last_logits + g * V, lg.data() + oi * V, V * sizeof(float));
+    s->position[seq_ids[g]] += counts[g];
+    s->have_logits[seq_ids[g]] = 0;  // the single-sequence decode loop keeps its own logits
+  }
+  // sequence 0's device-side position follows what was appended to it here
+  if (seen[0]) {
+    const int p0 = (int)s->position[0];
+    if ((ce = cudaMemcpyAsync(s->pos_dev, &p0, sizeof(int), cudaMemcpyHostToDevice, st)) != cudaSuccess ||
+        (ce = cudaStreamSynchronize(st)) != cudaSuccess)
+      return fail_cuda(e, ce, "position upload");
+  }
   return LLR_OK;
 }
 

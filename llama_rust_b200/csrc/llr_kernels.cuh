@@ -205,15 +205,31 @@ struct WalkShape { int n_embd, n_head, n_head_kv, head_dim, n_ff, n_ctx; float r
 // residual stream).  w may be null (all ones).
 cudaError_t launch_rmsnorm(float* x, const float* add, const float* w, float* y, int tokens, int n, float eps,
                            cudaStream_t s, uint64_t* launches);
-// RoPE (adjacent pairs) on q and k at positions pos0 + t, then k and v into the cache rows of those positions.
-// The position base is read from device memory (pos_dev) so that a captured or pre-enqueued step sees the current value.
-cudaError_t launch_rope_store(float* q, float* k, const float* v, float* cache_k, float* cache_v, const int* pos_dev,
-                              int tokens, int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches);
-// out[t][hq] = softmax(q[t][hq] . K[0..pos0+t] / sqrt(hd)) V, grouped-query heads; scratch holds the partial results of
-// the position splits (attention_scratch_floats)
+// Paged KV cache as the kernels see it (langtax/src/kv_page.rs:395-437: a head vector of block b lies at
+// (((b * n_layers + layer) * n_head_kv + head) * block_tokens + t % block_tokens) * head_dim, b = table[t / block_tokens]).
+// table holds max_blocks entries per sequence.
+struct KvView {
+  float* k;
+  float* v;
+  const int* table;
+  int block_tokens, max_blocks, n_layer;
+};
+// Where the rows of a batch stand: row t belongs to sequence row_seq[t] at position row_pos[t]; with null arrays all
+// rows belong to sequence 0 at positions *pos_dev + t (the position counter lives in device memory so that a captured
+// or pre-enqueued step sees the current value).
+struct RowMap {
+  const int* pos_dev;
+  const int* row_pos;
+  const int* row_seq;
+};
+// RoPE (adjacent pairs) on q and k at each row's position, then k and v into the cache.
+cudaError_t launch_rope_store(float* q, float* k, const float* v, const KvView& kv, const RowMap& rows, int tokens, int layer,
+                              const WalkShape& w, cudaStream_t s, uint64_t* launches);
+// out[t][hq] = softmax(q[t][hq] . K[0..pos(t)] / sqrt(hd)) V over row t's own sequence, grouped-query heads; scratch holds
+// the partial results of the position splits (attention_scratch_floats)
 size_t attention_scratch_floats(int tokens, const WalkShape& w);
-cudaError_t launch_attention(const float* q, const float* cache_k, const float* cache_v, float* out, float* scratch,
-                             const int* pos_dev, int tokens, int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches);
+cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float* scratch, const RowMap& rows, int tokens,
+                             int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_swiglu(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_add(float* x, const float* y, int64_t n, cudaStream_t s, uint64_t* launches);
 // first index of the strict maximum of logits[0..n) -> *out_id (device; n == 0: no argmax), and *pos_dev += advance
@@ -221,6 +237,9 @@ cudaError_t launch_add(float* x, const float* y, int64_t n, cudaStream_t s, uint
 // count grows by one (a generation loop whose steps are identical launches).
 cudaError_t launch_argmax_advance(const float* logits, int n, int* out_id, float* out_margin, int* pos_dev, int advance,
                                   int* count_dev, cudaStream_t s, uint64_t* launches);
+// one argmax per row of logits[n_rows][n] -> out_id[row], out_margin[row] (optional)
+cudaError_t launch_argmax_rows(const float* logits, int n_rows, int n, int* out_id, float* out_margin, cudaStream_t s,
+                               uint64_t* launches);
 
 // Seeded synthetic packed blocks (see llama_rust_b200/synth.py for the recipe).
 cudaError_t launch_synth(int dtype, int64_t rows, int64_t cols, uint64_t seed, uint8_t* w,

@@ -112,7 +112,7 @@ class Session:
     (prefill / decode), with the element-wise steps, the KV cache and the greedy argmax on the device."""
 
     def __init__(self, executor: "Executor", cfg: dict, token_embd: Matrix, layers, output: Matrix | None = None,
-                 output_norm=None):
+                 output_norm=None, n_seq: int = 1, kv_blocks: int = 0, block_tokens: int = 16):
         """cfg: n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab, n_ctx (+ rms_eps, rope_base);
         layers: per layer a dict attn_q, attn_k, attn_v, attn_output, ffn_gate, ffn_up, ffn_down (Matrix) and
         optionally attn_norm, ffn_norm (float32 arrays of n_embd; absent: all ones)."""
@@ -134,8 +134,9 @@ class Session:
                                                          "ffn_down")), norm(L.get("attn_norm")), norm(L.get("ffn_norm")))
         model = _lib.LlamaModel(c, token_embd._h, output._h if output is not None else None, norm(output_norm), arr)
         h = C.c_void_p()
-        executor._check(lib().llr_session_create(executor._h, C.byref(model), C.byref(h)))
+        executor._check(lib().llr_session_create_paged(executor._h, C.byref(model), n_seq, kv_blocks, block_tokens, C.byref(h)))
         self._h = h.value
+        self.n_seq = n_seq
         self.n_vocab = int(cfg["n_vocab"])
         self._keep = []
 
@@ -151,6 +152,26 @@ class Session:
         margin = np.empty(n_gen, np.float32)
         self._exec._check(lib().llr_session_decode(self._h, n_gen, ids.ctypes.data, margin.ctypes.data))
         return ids, margin
+
+    def batch(self, groups, want_logits: bool = False):
+        """groups: list of (sequence index, token ids): one ragged batch over several sequences (llr_session_batch).
+        Returns (next_ids[n_groups], logits[n_groups, n_vocab] or None), in the order of `groups`."""
+        seqs = np.array([g[0] for g in groups], np.uint32)
+        counts = np.array([len(g[1]) for g in groups], np.uint32)
+        toks = np.ascontiguousarray(np.concatenate([np.asarray(g[1], np.int32) for g in groups]), np.int32)
+        nxt = np.empty(len(groups), np.int32)
+        lg = np.empty((len(groups), self.n_vocab), np.float32) if want_logits else None
+        self._exec._check(lib().llr_session_batch(self._h, len(groups), seqs.ctypes.data, counts.ctypes.data, toks.ctypes.data,
+                                                  lg.ctypes.data if want_logits else None, nxt.ctypes.data))
+        return nxt, lg
+
+    def seq_position(self, seq: int) -> int:
+        p = C.c_size_t()
+        self._exec._check(lib().llr_session_seq_position(self._h, seq, C.byref(p)))
+        return p.value
+
+    def seq_reset(self, seq: int) -> None:
+        self._exec._check(lib().llr_session_seq_reset(self._h, seq))
 
     def logits(self) -> np.ndarray:
         out = np.empty(self.n_vocab, np.float32)

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 GOLDEN_CENTERED = os.path.join(os.path.dirname(__file__), "golden", "config3_centered_golden.json")
 
 
-def _session(ex, cfg, n_ctx, mats, embd_mat, norms=None):
+def _session(ex, cfg, n_ctx, mats, embd_mat, norms=None, **kw):
     from llama_rust_b200 import Session
     layers = []
     for li in range(cfg["n_layer"]):
@@ -23,7 +23,7 @@ def _session(ex, cfg, n_ctx, mats, embd_mat, norms=None):
         if norms is not None:
             L["attn_norm"], L["ffn_norm"] = norms[li]
         layers.append(L)
-    return Session(ex, dict(cfg, n_ctx=n_ctx), embd_mat, layers, output=mats[7 * cfg["n_layer"]])
+    return Session(ex, dict(cfg, n_ctx=n_ctx), embd_mat, layers, output=mats[7 * cfg["n_layer"]], **kw)
 
 
 def test_small_model_tokens_and_logits_match_the_cpu_walk(orc):
@@ -61,6 +61,67 @@ def test_small_model_tokens_and_logits_match_the_cpu_walk(orc):
     s.prefill(prompt[10:])
     ids3, _ = s.decode(8)
     assert np.array_equal(ids3, ids[:8])
+    s.free()
+    ex.close()
+
+
+def test_ragged_batch_over_several_sequences_equals_running_them_one_by_one(orc):
+    """Engine-style batches (engine.rs:1215-1274): ragged groups of prompt chunks and single decode tokens of three
+    sequences flattened into one activation matrix per step, against the same sequences run alone in a one-sequence
+    session.  With the f32-faithful products a row does not depend on its batch: logits must be the same bits.  The KV
+    pool is paged (blocks of 4 positions, fewer blocks than three full contexts) and blocks return on reset."""
+    from llama_rust_b200 import Executor, NativeCudaError
+    cfg = dict(n_layer=2, n_embd=512, n_head=8, n_head_kv=2, head_dim=64, n_ff=1024, n_vocab=1000)
+    n_ctx = 48
+    tl = lw.tensor_list(cfg)
+    weights, embd = lw.centered_weights(cfg, 21)
+    ex = Executor(0)
+    ex.set_path(3)
+    mats = [ex.upload(dt, rows, cols, w) for (name, dt, rows, cols), w in zip(tl, weights)]
+    embd_mat = ex.upload(lw.Q4_K, cfg["n_vocab"], cfg["n_embd"], embd)
+    prompts = [lw.prompt_ids(n, cfg["n_vocab"], 50 + n) for n in (11, 5, 17)]
+    # reference: each sequence alone, prompt in one piece, then greedy tokens one by one with their logits
+    alone = _session(ex, cfg, n_ctx, mats, embd_mat)
+    want = []
+    for p in prompts:
+        alone.reset()
+        lg = [alone.prefill(p, want_logits=True)]
+        toks = []
+        for _ in range(3):
+            t = int(np.argmax(lg[-1]))
+            toks.append(t)
+            lg.append(alone.prefill([t], want_logits=True))
+        want.append((toks, lg))
+    alone.free()
+    s = _session(ex, cfg, n_ctx, mats, embd_mat, n_seq=3, kv_blocks=24, block_tokens=4)  # 24 blocks x 4 = 96 positions < 3 x 48
+    # step 1: ragged prompt chunks (sequence 2's prompt arrives in two chunks; groups given out of order)
+    nxt, lg = s.batch([(2, prompts[2][:9]), (0, prompts[0]), (1, prompts[1])], want_logits=True)
+    assert np.array_equal(lg[1].view(np.uint32), want[0][1][0].view(np.uint32))
+    assert np.array_equal(lg[2].view(np.uint32), want[1][1][0].view(np.uint32))
+    assert nxt[1] == want[0][0][0] and nxt[2] == want[1][0][0]
+    # step 2: sequences 0 and 1 decode one token each while sequence 2 takes the rest of its prompt
+    nxt, lg = s.batch([(0, [want[0][0][0]]), (1, [want[1][0][0]]), (2, prompts[2][9:])], want_logits=True)
+    assert np.array_equal(lg[0].view(np.uint32), want[0][1][1].view(np.uint32))
+    assert np.array_equal(lg[1].view(np.uint32), want[1][1][1].view(np.uint32))
+    assert np.array_equal(lg[2].view(np.uint32), want[2][1][0].view(np.uint32))
+    assert [int(v) for v in nxt] == [want[0][0][1], want[1][0][1], want[2][0][0]]
+    # step 3: all three decode
+    nxt, lg = s.batch([(q, [want[q][0][1 if q < 2 else 0]]) for q in range(3)], want_logits=True)
+    for q in range(3):
+        assert np.array_equal(lg[q].view(np.uint32), want[q][1][2 if q < 2 else 1].view(np.uint32)), q
+    assert [s.seq_position(q) for q in range(3)] == [13, 7, 18]
+    # the pool is bounded: 13 + 7 + 18 positions hold 4 + 2 + 5 = 11 of the 24 blocks
+    s.batch([(0, list(range(35)))])              # sequence 0 to its full context: 12 blocks, 5 left
+    with pytest.raises(NativeCudaError) as err:
+        s.batch([(1, list(range(41)))])          # sequence 1 would need 10 more
+    assert err.value.code == 7 and s.seq_position(1) == 7
+    s.seq_reset(0)                               # its 12 blocks return to the pool
+    s.batch([(1, list(range(41)))])
+    assert s.seq_position(1) == 48 and s.seq_position(0) == 0
+    with pytest.raises(NativeCudaError):
+        s.batch([(1, [1])])                      # beyond the context length
+    with pytest.raises(NativeCudaError):
+        s.batch([(0, [1]), (0, [2])])            # a sequence twice in one batch
     s.free()
     ex.close()
 
