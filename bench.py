@@ -707,6 +707,55 @@ def check_sharded(ex, sharded, offs, shape_of, xin, phase_of, M, world, rank, sp
             "how": "first layers of the sharded program vs the same products unsharded on each rank's own GPU, all rows, uint32 compare"}
 
 
+def run_case(args):
+    """One small case for profiling (the full sweep holds 5 GB): prints one JSON line.
+      --case gemv    --dtype D --rows R --cols C --m M --reps N --copies K [--path P]   device-pointer products round-robin over K matrices
+      --case moe     --tokens T --reps N                                               the routed-expert layer of BASELINE config 5
+      --case session --prompt P --gen G [--layers L]                                   the device-resident walk on an 8B-shaped model of L layers"""
+    import torch
+    from llama_rust_b200 import DTYPES, Executor, row_bytes as lib_row_bytes, synth
+    ex = Executor(0)
+    if args.path is not None:
+        ex.set_path(args.path)
+    stream = torch.cuda.Stream()
+    sptr = stream.cuda_stream
+    if args.case == "gemv":
+        dt = DTYPES[args.dtype]
+        mats = [ex.synth(dt, args.rows, args.cols, 1000 + i) for i in range(args.copies)]
+        x = torch.randn(args.m, args.cols, device="cuda")
+        y = torch.empty(args.m, args.rows, device="cuda")
+        it = [0]
+
+        def one():
+            ex.matmul_device(mats[it[0] % args.copies], args.m, x.data_ptr(), y.data_ptr(), sptr)
+            it[0] += 1
+        timed(stream, one, min(args.reps, 3))
+        ms = timed(stream, one, args.reps)
+        nbytes = args.rows * lib_row_bytes(dt, args.cols) + 4 * args.m * (args.cols + args.rows)
+        out = {"case": "gemv", "dtype": args.dtype, "rows": args.rows, "cols": args.cols, "m": args.m, "us_per_launch": ms * 1e3,
+               "algorithmic_bytes": nbytes, "GB_per_s": nbytes / ms / 1e6, "TFLOP_per_s": 2.0 * args.m * args.rows * args.cols / ms / 1e9,
+               "launches": ex.counters()["launches"]}
+    elif args.case == "moe":
+        peak, _ = load_peaks()
+        out = {"case": "moe", **moe_leg(ex, None, 0, 1, peak, 1354.7)}
+    else:
+        cfg = dict(n_layer=args.layers, n_embd=D_MODEL, n_head=32, n_head_kv=8, head_dim=128, n_ff=D_FF, n_vocab=VOCAB, n_ctx=args.prompt + args.gen + 8)
+        from llama_rust_b200 import Session
+        embd = ex.synth(Q4_K, VOCAB, D_MODEL, 1)
+        layers = [{t: ex.synth(dt, r, c, 10 * li + j) for j, (t, dt, r, c) in enumerate(LAYER)} for li in range(args.layers)]
+        head = ex.synth(Q6_K, VOCAB, D_MODEL, 2)
+        s = Session(ex, cfg, embd, layers, output=head)
+        prompt = (synth.words(7, 0, args.prompt) % np.uint64(VOCAB)).astype(np.int32)
+        t0 = time.perf_counter()
+        s.prefill(prompt)
+        t1 = time.perf_counter()
+        ids, _ = s.decode(args.gen)
+        t2 = time.perf_counter()
+        out = {"case": "session", "layers": args.layers, "prefill_ms": (t1 - t0) * 1e3, "decode_ms_per_token": (t2 - t1) / args.gen * 1e3,
+               "launches": ex.counters()["launches"]}
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -718,7 +767,20 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip the legs for BASELINE configs 1, 4 and 5")
     ap.add_argument("--mode", default="program", choices=["program", "calls"],
                     help="program: the sweep as one persistent launch; calls: one launch per matmul")
+    ap.add_argument("--case", default=None, choices=["gemv", "moe", "session"], help="run one small case instead of the sweep (for profiling)")
+    ap.add_argument("--dtype", default="Q4_K")
+    ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--cols", type=int, default=4096)
+    ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--copies", type=int, default=6)
+    ap.add_argument("--path", type=int, default=None, help="kernel path of llr_exec_set_path")
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--prompt", type=int, default=64)
+    ap.add_argument("--gen", type=int, default=4)
+    ap.add_argument("--layers", type=int, default=4)
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -55,26 +55,54 @@ __device__ __forceinline__ int64_t kv_offset(const KvView& kv, int seq, int laye
   return ((((int64_t)b * kv.n_layer + layer) * n_head_kv + head) * kv.block_tokens + pos % kv.block_tokens) * hd;
 }
 
-// one block per activation row
-__global__ void __launch_bounds__(256)
+// one block per activation row; a row of up to 4096 values stays in registers between the two passes
+constexpr int NORM_THREADS = 1024;
+__global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add, const float* __restrict__ w, float* __restrict__ y,
                int n, float eps) {
   __shared__ float sh[32];
   float* xr = x + (int64_t)blockIdx.x * n;
   const float* ar = add ? add + (int64_t)blockIdx.x * n : nullptr;
   float* yr = y + (int64_t)blockIdx.x * n;
+  const bool in_regs = n <= 4 * NORM_THREADS && n % 4 == 0;
+  float4 keep = make_float4(0.f, 0.f, 0.f, 0.f);
   float ss = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    float v = xr[i];
-    if (ar) { v = __fadd_rn(ar[i], v); xr[i] = v; }  // proj + residual (decode.rs:2938, :3050)
-    ss = fmaf(v, v, ss);
+  if (in_regs) {
+    const int i = 4 * threadIdx.x;
+    if (i < n) {
+      keep = *(const float4*)(xr + i);
+      if (ar) {  // proj + residual (decode.rs:2938, :3050), written back: the new residual stream
+        const float4 a = *(const float4*)(ar + i);
+        keep.x = __fadd_rn(a.x, keep.x); keep.y = __fadd_rn(a.y, keep.y); keep.z = __fadd_rn(a.z, keep.z); keep.w = __fadd_rn(a.w, keep.w);
+        *(float4*)(xr + i) = keep;
+      }
+      ss = fmaf(keep.x, keep.x, fmaf(keep.y, keep.y, fmaf(keep.z, keep.z, keep.w * keep.w)));
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float v = xr[i];
+      if (ar) { v = __fadd_rn(ar[i], v); xr[i] = v; }
+      ss = fmaf(v, v, ss);
+    }
   }
   ss = block_sum(ss, sh);
   const float rms = sqrtf(__fadd_rn(__fdiv_rn(ss, (float)(n <= 65535 ? n : 1)), eps));
   const float inv = rms > 0.f ? __fdiv_rn(1.0f, rms) : 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float t = __fmul_rn(xr[i], inv);
-    yr[i] = w ? __fmul_rn(t, w[i]) : t;
+  if (in_regs) {
+    const int i = 4 * threadIdx.x;
+    if (i < n) {
+      float4 o = make_float4(__fmul_rn(keep.x, inv), __fmul_rn(keep.y, inv), __fmul_rn(keep.z, inv), __fmul_rn(keep.w, inv));
+      if (w) {
+        const float4 ww = *(const float4*)(w + i);
+        o.x = __fmul_rn(o.x, ww.x); o.y = __fmul_rn(o.y, ww.y); o.z = __fmul_rn(o.z, ww.z); o.w = __fmul_rn(o.w, ww.w);
+      }
+      *(float4*)(yr + i) = o;
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float t = __fmul_rn(xr[i], inv);
+      yr[i] = w ? __fmul_rn(t, w[i]) : t;
+    }
   }
 }
 
@@ -156,18 +184,19 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
   }
   __syncthreads();
   float* out = part + (((int64_t)t * w.n_head_kv + hkv) * n_split + split) * gqa * (hd + 2);
-  for (int g = 0; g < gqa; ++g) {
+  // per query head: the slice's maximum and the sum of exp(score - max); one warp per head, lanes add in a fixed tree
+  for (int g = warp; g < gqa; g += nw) {
     float m = -CUDART_INF_F;
-    for (int s = threadIdx.x; s < s1 - s0; s += ATT_THREADS) m = fmaxf(m, sc[g * max_chunk + s]);
-    m = block_max(m, red);
+    for (int s = lane; s < s1 - s0; s += 32) m = fmaxf(m, sc[g * max_chunk + s]);
+    m = warp_max(m);
     float l = 0.f;
-    for (int s = threadIdx.x; s < s1 - s0; s += ATT_THREADS) {
+    for (int s = lane; s < s1 - s0; s += 32) {
       const float e = expf(sc[g * max_chunk + s] - m);
       sc[g * max_chunk + s] = e;
       l += e;
     }
-    l = block_sum(l, red);
-    if (threadIdx.x == 0) { out[g * (hd + 2) + hd] = m; out[g * (hd + 2) + hd + 1] = l; }
+    l = warp_sum(l);
+    if (lane == 0) { out[g * (hd + 2) + hd] = m; out[g * (hd + 2) + hd + 1] = l; }
   }
   __syncthreads();
   // weighted values: thread (i, grp) owns dimension i for every P-th run of eight positions of the slice
@@ -206,28 +235,33 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
   }
 }
 
-// grid (query head, token): merges the position slices in ascending order
+// grid (query head, token): merges the position slices (at most 32): the first warp turns the slices' maxima into
+// weights exp(m_slice - m) and the denominator, then every thread adds its dimension over the slices in ascending order
 __global__ void __launch_bounds__(128)
 attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, RowMap rows, int chunk, WalkShape w) {
+  __shared__ float s_e[32];
+  __shared__ float s_l;
   const int hq = blockIdx.x, t = blockIdx.y;
   const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
   const int hkv = hq / gqa, g = hq % gqa;
   const int seq = row_position(rows, t) + 1;
-  const int n_split = (w.n_ctx + chunk - 1) / chunk;
+  const int n_split = (w.n_ctx + chunk - 1) / chunk, used = min(n_split, (seq + chunk - 1) / chunk);
   const float* base = part + ((int64_t)t * w.n_head_kv + hkv) * n_split * gqa * (hd + 2) + g * (hd + 2);
-  float m = -CUDART_INF_F;
-  for (int sp = 0; sp < n_split && sp * chunk < seq; ++sp) m = fmaxf(m, base[(int64_t)sp * gqa * (hd + 2) + hd]);
-  float l = 0.f;
-  for (int sp = 0; sp < n_split && sp * chunk < seq; ++sp) {
-    const float* p = base + (int64_t)sp * gqa * (hd + 2);
-    l = fmaf(p[hd + 1], expf(p[hd] - m), l);
+  const int64_t stride = (int64_t)gqa * (hd + 2);
+  if (threadIdx.x < 32) {
+    const int sp = threadIdx.x;
+    const float ms = sp < used ? base[sp * stride + hd] : -CUDART_INF_F;
+    const float m = warp_max(ms);
+    const float e = sp < used ? expf(ms - m) : 0.f;
+    const float l = warp_sum(sp < used ? base[sp * stride + hd + 1] * e : 0.f);
+    s_e[sp] = e;
+    if (sp == 0) s_l = l;
   }
+  __syncthreads();
+  const float l = s_l;
   for (int i = threadIdx.x; i < hd; i += blockDim.x) {
     float acc = 0.f;
-    for (int sp = 0; sp < n_split && sp * chunk < seq; ++sp) {
-      const float* p = base + (int64_t)sp * gqa * (hd + 2);
-      acc = fmaf(p[i], expf(p[hd] - m), acc);
-    }
+    for (int sp = 0; sp < used; ++sp) acc = fmaf(base[sp * stride + i], s_e[sp], acc);
     out[((int64_t)t * w.n_head + hq) * hd + i] = l > 0.f ? __fdiv_rn(acc, l) : 0.f;
   }
 }
@@ -306,6 +340,67 @@ argmax_kernel(const float* __restrict__ logits, int n, int* __restrict__ out_id,
   if (threadIdx.x == 0 && pos_dev) *pos_dev += advance;
 }
 
+// Two-stage argmax of one long row (a vocabulary): ARG_BLOCKS blocks each reduce a contiguous range to (best value, its
+// first index, largest other value of the range); one block merges the ranges in ascending order, so the first of equal
+// maxima still wins (sample.rs:293), and applies the bookkeeping of argmax_kernel.
+constexpr int ARG_BLOCKS = 128;
+__global__ void __launch_bounds__(256)
+argmax_part_kernel(const float* __restrict__ logits, int n, float* __restrict__ pbest, int* __restrict__ pidx, float* __restrict__ psecond) {
+  __shared__ float sv[8], s2[8];
+  __shared__ int si[8];
+  const int per = (n + gridDim.x - 1) / gridDim.x;
+  const int lo = blockIdx.x * per, hi = min(n, lo + per);
+  float best = -CUDART_INF_F, second = -CUDART_INF_F;
+  int bi = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = logits[i];
+    if (v > best) { second = best; best = v; bi = i; }
+    else second = fmaxf(second, v);
+  }
+  // merge (best, index, second) of two disjoint sets: the larger best wins, ties to the lower index; the loser's best
+  // and both seconds compete for second place
+  auto merge = [](float& b, int& i, float& s, float ob, int oi, float os) {
+    const bool other = ob > b || (ob == b && oi < i);
+    const float loser = other ? b : ob;
+    s = fmaxf(fmaxf(s, os), loser);
+    if (other) { b = ob; i = oi; }
+  };
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(~0u, best, o), os = __shfl_xor_sync(~0u, second, o);
+    const int oi = __shfl_xor_sync(~0u, bi, o);
+    merge(best, bi, second, ob, oi, os);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = best; si[warp] = bi; s2[warp] = second; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) merge(best, bi, second, sv[w], si[w], s2[w]);
+    pbest[blockIdx.x] = best; pidx[blockIdx.x] = bi; psecond[blockIdx.x] = second;
+  }
+}
+__global__ void __launch_bounds__(ARG_BLOCKS)
+argmax_merge_kernel(const float* __restrict__ pbest, const int* __restrict__ pidx, const float* __restrict__ psecond, int parts,
+                    int* __restrict__ out_id, float* __restrict__ out_margin, int* __restrict__ pos_dev, int advance,
+                    int* __restrict__ count_dev) {
+  if (threadIdx.x != 0) return;  // a hundred-odd triples: one thread, ascending order
+  float best = -CUDART_INF_F, second = -CUDART_INF_F;
+  int bi = 0x7fffffff;
+  for (int p = 0; p < parts; ++p) {
+    const float ob = pbest[p], os = psecond[p];
+    const int oi = pidx[p];
+    const bool other = ob > best || (ob == best && oi < bi);
+    const float loser = other ? best : ob;
+    second = fmaxf(fmaxf(second, os), loser);
+    if (other) { best = ob; bi = oi; }
+  }
+  const int win = bi == 0x7fffffff ? 0 : bi;
+  const int slot = count_dev ? *count_dev : 0;
+  out_id[0] = win;
+  if (out_margin) out_margin[slot] = best - second;
+  if (count_dev) { out_id[1 + slot] = win; *count_dev = slot + 1; }
+  if (pos_dev) *pos_dev += advance;
+}
+
 // positions per attention slice: 32, or a thirty-second of the context when that is longer
 int attention_chunk(const WalkShape& w) {
   const int c = (w.n_ctx + 31) / 32;
@@ -321,7 +416,7 @@ int attention_splits(const WalkShape& w) {
 cudaError_t launch_rmsnorm(float* x, const float* add, const float* w, float* y, int tokens, int n, float eps,
                            cudaStream_t s, uint64_t* launches) {
   if (tokens <= 0) return cudaSuccess;
-  rmsnorm_kernel<<<tokens, 256, 0, s>>>(x, add, w, y, n, eps);
+  rmsnorm_kernel<<<tokens, NORM_THREADS, 0, s>>>(x, add, w, y, n, eps);
   if (launches) ++*launches;
   return cudaGetLastError();
 }
@@ -388,7 +483,14 @@ cudaError_t launch_argmax_rows(const float* logits, int n_rows, int n, int* out_
 }
 
 cudaError_t launch_argmax_advance(const float* logits, int n, int* out_id, float* out_margin, int* pos_dev, int advance,
-                                  int* count_dev, cudaStream_t s, uint64_t* launches) {
+                                  int* count_dev, float* part, cudaStream_t s, uint64_t* launches) {
+  if (n >= 16384 && part) {  // a vocabulary: spread the scan over the device (part: 3 * ARG_BLOCKS words of scratch)
+    argmax_part_kernel<<<ARG_BLOCKS, 256, 0, s>>>(logits, n, part, (int*)(part + ARG_BLOCKS), part + 2 * ARG_BLOCKS);
+    argmax_merge_kernel<<<1, ARG_BLOCKS, 0, s>>>(part, (const int*)(part + ARG_BLOCKS), part + 2 * ARG_BLOCKS, ARG_BLOCKS, out_id,
+                                                 out_margin, pos_dev, advance, count_dev);
+    if (launches) *launches += 2;
+    return cudaGetLastError();
+  }
   argmax_kernel<<<1, 1024, 0, s>>>(logits, n, out_id, out_margin, pos_dev, advance, count_dev);
   if (launches) ++*launches;
   return cudaGetLastError();

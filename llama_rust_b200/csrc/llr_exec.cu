@@ -1325,12 +1325,14 @@ struct llr_session {
   // device buffers
   float *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *proj = nullptr,
         *gate = nullptr, *up = nullptr, *logits = nullptr, *cache_k = nullptr, *cache_v = nullptr, *att_scratch = nullptr,
-        *margins = nullptr, *last_x = nullptr;
+        *margins = nullptr, *last_x = nullptr, *arg_part = nullptr;
   size_t logits_rows = 1;
   int *ids = nullptr, *pos_dev = nullptr;  // ids[0]: the token the next step reads; ids[1..]: prompt chunk or generated tokens
   size_t ids_cap = 0;
   int* count_dev = nullptr;  // tokens generated by the current llr_session_decode call
   int *table_dev = nullptr, *row_pos = nullptr, *row_seq = nullptr, *last_rows = nullptr;
+  // decode steps (one row): the independent products of a layer as one launch each -- {q, k, v} and {gate, up}
+  std::vector<llr::Program*> qkv_prog, gateup_prog;
   cudaGraphExec_t step_graph = nullptr;  // one decode step, captured once per kernel path
   int step_graph_path = -1, step_kernels = 0;
   bool use_graph = true;
@@ -1342,11 +1344,13 @@ void session_release(llr_session* s) {
   for (float* p : s->attn_norm) if (p) cudaFree(p);
   for (float* p : s->ffn_norm) if (p) cudaFree(p);
   float* bufs[] = {s->out_norm, s->x, s->xn, s->q, s->k, s->v, s->attn, s->proj, s->gate, s->up, s->logits,
-                   s->cache_k, s->cache_v, s->att_scratch, s->margins, s->last_x};
+                   s->cache_k, s->cache_v, s->att_scratch, s->margins, s->last_x, s->arg_part};
   for (float* p : bufs) if (p) cudaFree(p);
   int* ibufs[] = {s->ids, s->pos_dev, s->count_dev, s->table_dev, s->row_pos, s->row_seq, s->last_rows};
   for (int* p : ibufs) if (p) cudaFree(p);
   if (s->step_graph) cudaGraphExecDestroy(s->step_graph);
+  for (llr::Program* p : s->qkv_prog) program_destroy(p);
+  for (llr::Program* p : s->gateup_prog) program_destroy(p);
   cudaGetLastError();
 }
 
@@ -1393,15 +1397,24 @@ cudaError_t session_layers(llr_session* s, const int* ids_dev, size_t n, const R
   for (size_t li = 0; li < c.n_layer && ce == cudaSuccess; ++li) {
     const llr_llama_layer& W = s->layers[li];
     if ((ce = launch_rmsnorm(s->x, pending, s->attn_norm[li], s->xn, (int)n, (int)E, c.rms_eps, st, L)) != cudaSuccess) break;
-    if ((ce = session_matmul(e, W.attn_q, n, s->xn, s->q)) != cudaSuccess) break;
-    if ((ce = session_matmul(e, W.attn_k, n, s->xn, s->k)) != cudaSuccess) break;
-    if ((ce = session_matmul(e, W.attn_v, n, s->xn, s->v)) != cudaSuccess) break;
+    const bool one_row_programs = n == 1 && (e->path == PATH_AUTO || e->path == PATH_MMA);
+    if (one_row_programs && s->qkv_prog[li]) {
+      if ((ce = program_run(s->qkv_prog[li], st, e->err_flag, e->poll_limit, L)) != cudaSuccess) break;
+    } else {
+      if ((ce = session_matmul(e, W.attn_q, n, s->xn, s->q)) != cudaSuccess) break;
+      if ((ce = session_matmul(e, W.attn_k, n, s->xn, s->k)) != cudaSuccess) break;
+      if ((ce = session_matmul(e, W.attn_v, n, s->xn, s->v)) != cudaSuccess) break;
+    }
     if ((ce = launch_rope_store(s->q, s->k, s->v, kv, rows, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
     if ((ce = launch_attention(s->q, kv, s->attn, s->att_scratch, rows, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
     if ((ce = session_matmul(e, W.attn_output, n, s->attn, s->proj)) != cudaSuccess) break;
     if ((ce = launch_rmsnorm(s->x, s->proj, s->ffn_norm[li], s->xn, (int)n, (int)E, c.rms_eps, st, L)) != cudaSuccess) break;
-    if ((ce = session_matmul(e, W.ffn_gate, n, s->xn, s->gate)) != cudaSuccess) break;
-    if ((ce = session_matmul(e, W.ffn_up, n, s->xn, s->up)) != cudaSuccess) break;
+    if (one_row_programs && s->gateup_prog[li]) {
+      if ((ce = program_run(s->gateup_prog[li], st, e->err_flag, e->poll_limit, L)) != cudaSuccess) break;
+    } else {
+      if ((ce = session_matmul(e, W.ffn_gate, n, s->xn, s->gate)) != cudaSuccess) break;
+      if ((ce = session_matmul(e, W.ffn_up, n, s->xn, s->up)) != cudaSuccess) break;
+    }
     if ((ce = launch_swiglu(s->gate, s->up, (int64_t)(n * FF), st, L)) != cudaSuccess) break;
     if ((ce = session_matmul(e, W.ffn_down, n, s->gate, s->proj)) != cudaSuccess) break;
     pending = s->proj;
@@ -1428,9 +1441,9 @@ cudaError_t session_forward(llr_session* s, const int* ids_dev, size_t n, bool w
     if ((ce = session_matmul(e, s->output, 1, s->xn, s->logits)) != cudaSuccess) return ce;
     // generation: the winner goes to ids[0] (read by the next step) and to the history
     return launch_argmax_advance(s->logits, generate ? (int)c.n_vocab : 0, s->ids, s->margins, s->pos_dev, (int)n,
-                                 generate ? s->count_dev : nullptr, st, L);
+                                 generate ? s->count_dev : nullptr, s->arg_part, st, L);
   }
-  return launch_argmax_advance(nullptr, 0, nullptr, nullptr, s->pos_dev, (int)n, nullptr, st, L);
+  return launch_argmax_advance(nullptr, 0, nullptr, nullptr, s->pos_dev, (int)n, nullptr, nullptr, st, L);
 }
 
 int session_ids(llr_session* s, size_t n) {
@@ -1509,7 +1522,7 @@ int session_create(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t k
   norm(m->output_norm, &s->out_norm);
   alloc(&s->x, B * E); alloc(&s->xn, B * E); alloc(&s->q, B * QW); alloc(&s->k, B * KVW); alloc(&s->v, B * KVW);
   alloc(&s->attn, B * QW); alloc(&s->proj, B * E); alloc(&s->gate, B * FF); alloc(&s->up, B * FF);
-  alloc(&s->logits, s->logits_rows * V); alloc(&s->last_x, n_seq * E);
+  alloc(&s->logits, s->logits_rows * V); alloc(&s->last_x, n_seq * E); alloc(&s->arg_part, 512);
   const size_t pool = s->n_blocks * c.n_layer * c.n_head_kv * block_tokens * c.head_dim;
   alloc(&s->cache_k, pool); alloc(&s->cache_v, pool);
   alloc(&s->att_scratch, attention_scratch_floats((int)B, s->shape));
@@ -1518,6 +1531,30 @@ int session_create(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t k
   if (ce == cudaSuccess) ce = cudaMemset(s->pos_dev, 0, sizeof(int));
   if (ce == cudaSuccess) ce = cudaMemset(s->table_dev, 0, n_seq * s->max_blocks * sizeof(int));
   if (const char* g = std::getenv("LLR_SESSION_GRAPH")) s->use_graph = std::strcmp(g, "0") != 0;
+  // One launch for the products of a layer that share their input, where the streaming decode kernel takes all of them
+  s->qkv_prog.assign(c.n_layer, nullptr);
+  s->gateup_prog.assign(c.n_layer, nullptr);
+  auto group = [&](std::initializer_list<std::pair<const llr_matrix*, float*>> items, llr::Program** slot) {
+    std::vector<ProgEntry> pe;
+    std::vector<int> phase;
+    for (const auto& it : items) {
+      const MatView v = view_of(it.first);
+      if (!prog_entry_supported(v)) return;
+      ProgEntry E{};
+      E.w = v.w; E.x = s->xn; E.y = it.second; E.row_bytes = v.row_bytes;
+      E.rows = (int)v.rows; E.cols = (int)v.cols; E.dtype = v.dtype; E.tokens = 1; E.y_ld = v.rows;
+      E.x_phase = E.x2_phase = E.resid_phase = -1;
+      pe.push_back(E);
+      phase.push_back(0);
+    }
+    std::string msg;
+    if (ce == cudaSuccess && program_create(pe, phase, e->sm_count, false, nullptr, slot, &msg) != cudaSuccess) { *slot = nullptr; cudaGetLastError(); }
+  };
+  for (uint32_t li = 0; li < c.n_layer && ce == cudaSuccess; ++li) {
+    const llr_llama_layer& W = s->layers[li];
+    group({{W.attn_q, s->q}, {W.attn_k, s->k}, {W.attn_v, s->v}}, &s->qkv_prog[li]);
+    group({{W.ffn_gate, s->gate}, {W.ffn_up, s->up}}, &s->gateup_prog[li]);
+  }
   if (ce != cudaSuccess) {
     session_release(s);
     delete s;
@@ -1625,7 +1662,7 @@ int llr_session_decode(llr_session* s, size_t n_gen, int32_t* out_ids, float* ou
   // the remaining steps replay (several hundred launches per token otherwise cost more host time than device time).
   cudaError_t ce = cudaMemsetAsync(s->count_dev, 0, sizeof(int), e->stream);
   if (ce == cudaSuccess)
-    ce = launch_argmax_advance(s->logits, (int)s->cfg.n_vocab, s->ids, s->margins, nullptr, 0, s->count_dev, e->stream, &e->ctr.launches);
+    ce = launch_argmax_advance(s->logits, (int)s->cfg.n_vocab, s->ids, s->margins, nullptr, 0, s->count_dev, s->arg_part, e->stream, &e->ctr.launches);
   size_t done = 0;
   if (ce == cudaSuccess) { ce = session_forward(s, s->ids, 1, true, true); ++done; }  // also initialises per-kernel launch state before any capture
   if (ce == cudaSuccess && s->use_graph && n_gen > 2 && (!s->step_graph || s->step_graph_path != e->path)) {

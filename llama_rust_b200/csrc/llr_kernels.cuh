@@ -235,8 +235,9 @@ cudaError_t launch_add(float* x, const float* y, int64_t n, cudaStream_t s, uint
 // first index of the strict maximum of logits[0..n) -> *out_id (device; n == 0: no argmax), and *pos_dev += advance
 // With count_dev the token also goes to out_id[1 + *count_dev], its margin to out_margin[*count_dev], and the
 // count grows by one (a generation loop whose steps are identical launches).
+// part: 384 words of device scratch (a long row is scanned by many blocks), or null
 cudaError_t launch_argmax_advance(const float* logits, int n, int* out_id, float* out_margin, int* pos_dev, int advance,
-                                  int* count_dev, cudaStream_t s, uint64_t* launches);
+                                  int* count_dev, float* part, cudaStream_t s, uint64_t* launches);
 // one argmax per row of logits[n_rows][n] -> out_id[row], out_margin[row] (optional)
 cudaError_t launch_argmax_rows(const float* logits, int n_rows, int n, int* out_id, float* out_margin, cudaStream_t s,
                                uint64_t* launches);
