@@ -136,13 +136,36 @@ int llr_gemm_resident(llr_exec* exec, const llr_matrix* matrix, size_t tokens, c
  * the reference is never needed.  Weights are looked up in a device residency
  * cache keyed by (dtype, rows, cols, length, 128-bit content hash), so the
  * same bytes at another address hit and changed bytes at the same address miss
- * [native_cuda_parity.rs:181-187].  The budget is LLAMA_CUDA_CACHE_BYTES
+ * [native_cuda_parity.rs:181-187].  The reference compares every byte on a hit
+ * [native_gpu.rs:96-98]; here two different matrices with equal shape, length and
+ * fingerprint would be taken for one (no such pair is known; the hash is not
+ * cryptographic).  LLAMA_CUDA_CACHE_VERIFY=1 compares all bytes on the device on
+ * every hit and restores the exact guarantee at the price of an upload per call.  The budget is LLAMA_CUDA_CACHE_BYTES
  * ("auto" or unset: free - max(free/4, 512 MiB); a decimal byte count; 0
  * disables residency but not execution) [native_gpu.rs:5-9, 34-40] and counts
  * packed bytes only.  rows == 0 is a successful no-op [quant.rs:6743]. */
 int llr_matmul(llr_exec* exec, uint8_t dtype, size_t rows, size_t cols, size_t tokens,
                const void* packed, size_t packed_len, const float* x, size_t x_len, float* y,
                size_t y_len);
+
+/* llr_matmul for weights the caller can name: (key_hi, key_lo) is a stable identity of the packed bytes -- the blob
+ * range QuantMat.start..end of an immutable model file [langtax/src/decode.rs:476-485], or (layer, expert, part) of an
+ * expert store [ExpertKey, expertvm/src/store.rs:13-20] -- and replaces the content fingerprint: a hit reads nothing
+ * but the key.  The caller guarantees that one key always names the same bytes.  Keyed and fingerprinted entries
+ * share the budget and never match each other. */
+int llr_matmul_keyed(llr_exec* exec, uint64_t key_hi, uint64_t key_lo, uint8_t dtype, size_t rows, size_t cols,
+                     size_t tokens, const void* packed, size_t packed_len, const float* x, size_t x_len, float* y,
+                     size_t y_len);
+/* Keeps the resident matrix of a key out of eviction (pinned != 0) or releases it again (0)
+ * [pin_hot / unpin_all of the expert store as Engine::pin_predicted uses them, langtax/src/engine.rs:916-950].
+ * Pinned bytes still count against the budget. */
+int llr_exec_pin_key(llr_exec* exec, uint64_t key_hi, uint64_t key_lo, int pinned);
+/* Move an expert's weights to the device that computes, or leave them and ship activations: the byte-volume rule
+ * of plan_placement [expertvm/src/planner.rs:332-349]; returns LLR_PLACE_*. */
+#define LLR_PLACE_MOVE_WEIGHTS 0
+#define LLR_PLACE_DISPATCH_ACTIVATIONS 1
+int llr_plan_placement(uint64_t expert_bytes, uint64_t activation_bytes, uint64_t fan_in, uint64_t reuse,
+                       uint64_t link_bps);
 
 /* Device-pointer form of llr_gemm_resident: x_dev and y_dev are device
  * buffers of tokens*cols and tokens*rows floats; the work is enqueued on

@@ -23,7 +23,8 @@ SYMBOLS = [
     "llr_program_create_sharded", "llr_program_create_ops", "llr_program_info", "llr_exec_set_wait_limit",
     "llr_session_create", "llr_session_prefill", "llr_session_decode", "llr_session_logits", "llr_session_position",
     "llr_session_reset", "llr_session_free", "llr_session_create_paged", "llr_session_batch", "llr_session_seq_position",
-    "llr_session_seq_reset", "llr_moe_route_device", "llr_moe_experts_device",
+    "llr_session_seq_reset", "llr_moe_route_device", "llr_moe_experts_device", "llr_matmul_keyed",
+    "llr_exec_pin_key", "llr_plan_placement",
 ]
 ARENA_HEADER_BYTES = 65536
 
@@ -97,6 +98,10 @@ def load() -> C.CDLL:
     lib.llr_gemm_resident.argtypes = [vp, vp, sz, vp, sz, vp, sz]
     lib.llr_matmul.argtypes = [vp, u8, sz, sz, sz, vp, sz, vp, sz, vp, sz]
     lib.llr_matmul_device.argtypes = [vp, vp, sz, vp, vp, vp]
+    u64 = C.c_uint64
+    lib.llr_matmul_keyed.argtypes = [vp, u64, u64, u8, sz, sz, sz, vp, sz, vp, sz, vp, sz]
+    lib.llr_exec_pin_key.argtypes = [vp, u64, u64, C.c_int]
+    lib.llr_plan_placement.argtypes = [u64, u64, u64, u64, u64]
     lib.llr_exec_synchronize.argtypes = [vp]
     lib.llr_dequant_rows.argtypes = [vp, vp, sz, sz, vp, sz]
     lib.llr_matrix_synth.argtypes = [vp, u8, sz, sz, C.c_uint64, C.POINTER(vp)]

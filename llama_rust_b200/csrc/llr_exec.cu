@@ -53,29 +53,30 @@ inline uint64_t fmix(uint64_t k) {
   return k;
 }
 
-// 128-bit content fingerprint of the packed bytes: four independent
-// multiply-rotate lanes over 32-byte strides, folded with the length.
+// 128-bit content fingerprint of the packed bytes: four multiply-rotate lanes over 32-byte strides; every round folds
+// each lane into its neighbour, so a change in any word reaches all four lanes (independent lanes would let two inputs
+// that differ in the words of one lane collide with 64-bit strength only), then the length and a final avalanche.
 Hash128 content_hash(const uint8_t* p, size_t n) {
   uint64_t l0 = 0x9E3779B97F4A7C15ull, l1 = 0xC2B2AE3D27D4EB4Full, l2 = 0x165667B19E3779F9ull,
            l3 = 0x27D4EB2F165667C5ull;
+  auto round = [&](const uint64_t (&w)[4]) {
+    l0 = rotl((l0 ^ w[0]) * 0x9FB21C651E98DF25ull, 29) + l3;
+    l1 = rotl((l1 ^ w[1]) * 0xD6E8FEB86659FD93ull, 31) + l0;
+    l2 = rotl((l2 ^ w[2]) * 0xA0761D6478BD642Full, 27) + l1;
+    l3 = rotl((l3 ^ w[3]) * 0xE7037ED1A0B428DBull, 33) + l2;
+  };
   size_t i = 0;
   for (; i + 32 <= n; i += 32) {
     uint64_t w[4];
     std::memcpy(w, p + i, 32);
-    l0 = rotl((l0 ^ w[0]) * 0x9FB21C651E98DF25ull, 29);
-    l1 = rotl((l1 ^ w[1]) * 0xD6E8FEB86659FD93ull, 31);
-    l2 = rotl((l2 ^ w[2]) * 0xA0761D6478BD642Full, 27);
-    l3 = rotl((l3 ^ w[3]) * 0xE7037ED1A0B428DBull, 33);
+    round(w);
   }
-  uint8_t tail[32] = {0};
   if (i < n) {
+    uint8_t tail[32] = {0};
     std::memcpy(tail, p + i, n - i);
     uint64_t w[4];
     std::memcpy(w, tail, 32);
-    l0 = rotl((l0 ^ w[0]) * 0x9FB21C651E98DF25ull, 29);
-    l1 = rotl((l1 ^ w[1]) * 0xD6E8FEB86659FD93ull, 31);
-    l2 = rotl((l2 ^ w[2]) * 0xA0761D6478BD642Full, 27);
-    l3 = rotl((l3 ^ w[3]) * 0xE7037ED1A0B428DBull, 33);
+    round(w);
   }
   Hash128 h;
   h.a = fmix(l0 ^ rotl(l1, 17) ^ (uint64_t)n) + fmix(l2 + 0x52DCE729ull);
@@ -87,7 +88,9 @@ struct CacheEntry {
   int dtype;
   int64_t rows, cols;
   size_t len;
-  Hash128 hash;
+  Hash128 hash;   // content fingerprint, or the caller's key when keyed
+  bool keyed;     // identity is a caller-supplied stable key (llr_matmul_keyed), not the content
+  bool pinned;    // never evicted to make room (llr_exec_pin_key)
   llr_matrix* mat;
 };
 
@@ -127,6 +130,9 @@ struct llr_exec {
   int ticket = 0;
   bool host_delivery = true;
   unsigned int* bound_dev = nullptr;  // result word of the weight range check
+  unsigned int* done_count_base = nullptr;
+  bool verify_hits = false;  // LLAMA_CUDA_CACHE_VERIFY: compare all bytes on a fingerprint hit
+  unsigned int* bound_word() { return done_count_base + 1; }
   // activation / result staging
   float* pin_x = nullptr; size_t pin_x_cap = 0;
   float* pin_y = nullptr;
@@ -492,8 +498,10 @@ int llr_exec_create(int device, llr_exec** out) {
   if (ce == cudaSuccess && (ce = cudaMalloc((void**)&e->done_count, 2 * sizeof(unsigned int))) == cudaSuccess) {
     ce = cudaMemset(e->done_count, 0, 2 * sizeof(unsigned int));
     e->bound_dev = e->done_count + 1;
+    e->done_count_base = e->done_count;
   }
   if (const char* bf = std::getenv("LLR_GEMM_BF16")) { if (std::strcmp(bf, "0") != 0) e->bound_dev = nullptr; }  // keep bfloat16 operands
+  if (const char* vh = std::getenv("LLAMA_CUDA_CACHE_VERIFY")) e->verify_hits = std::strcmp(vh, "0") != 0;
   if (const char* hd = std::getenv("LLR_HOST_DELIVERY")) e->host_delivery = std::strcmp(hd, "0") != 0;
   if (ce != cudaSuccess) {
     if (err_host) cudaFreeHost(err_host);
@@ -653,9 +661,8 @@ int llr_gemv_resident(llr_exec* e, const llr_matrix* m, const float* x, size_t x
   return run_host(e, m, 1, x, y);
 }
 
-int llr_matmul(llr_exec* e, uint8_t dtype, size_t rows, size_t cols, size_t tokens,
-               const void* packed, size_t packed_len, const float* x, size_t x_len, float* y,
-               size_t y_len) {
+static int matmul_cached(llr_exec* e, const Hash128* key, uint8_t dtype, size_t rows, size_t cols, size_t tokens,
+                         const void* packed, size_t packed_len, const float* x, size_t x_len, float* y, size_t y_len) {
   if (!e) return LLR_ERR_INVALID;
   // native_matmul, quant.rs:6698-6745
   if (tokens == 0 || cols == 0 || y_len % tokens != 0)
@@ -679,20 +686,37 @@ int llr_matmul(llr_exec* e, uint8_t dtype, size_t rows, size_t cols, size_t toke
   DeviceGuard guard(e->device);
   if ((rc = resolve_limit(e)) != LLR_OK) return rc;
 
-  const Hash128 h = content_hash((const uint8_t*)packed, packed_len);
+  // Identity: the caller's stable key when given (immutable model weights: nothing is read but the key), else a
+  // 128-bit fingerprint of all packed bytes.  The reference compares every byte on a hit (native_gpu.rs:96-98);
+  // LLAMA_CUDA_CACHE_VERIFY=1 restores that guarantee for fingerprint hits: the caller's bytes are uploaded beside the
+  // resident copy and compared on the device, and a difference is treated as a miss.
+  const bool keyed = key != nullptr;
+  const Hash128 h = keyed ? *key : content_hash((const uint8_t*)packed, packed_len);
   for (auto it = e->cache.begin(); it != e->cache.end(); ++it) {
-    if (it->dtype == dtype && it->rows == (int64_t)rows && it->cols == (int64_t)cols &&
+    if (it->keyed == keyed && it->dtype == dtype && it->rows == (int64_t)rows && it->cols == (int64_t)cols &&
         it->len == packed_len && it->hash == h) {
+      if (!keyed && e->verify_hits) {
+        int differ = 0;
+        cudaError_t ve = grow_device(&e->dev_s, &e->dev_s_cap, packed_len + 256);
+        if (ve == cudaSuccess) ve = cudaMemcpyAsync(e->dev_s, packed, packed_len, cudaMemcpyHostToDevice, e->stream);
+        if (ve == cudaSuccess) ve = launch_bytes_differ(e->dev_s, it->mat->dev, packed_len, (int*)e->bound_word(), e->stream, &e->ctr.launches);
+        if (ve == cudaSuccess) ve = cudaMemcpyAsync(&differ, e->bound_word(), sizeof(int), cudaMemcpyDeviceToHost, e->stream);
+        if (ve == cudaSuccess) ve = cudaStreamSynchronize(e->stream);
+        if (ve != cudaSuccess) return fail_cuda(e, ve, "residency verification");
+        if (differ) { drop_entry(e, it); break; }  // a fingerprint collision: the resident copy is not this matrix
+      }
       e->cache.splice(e->cache.end(), e->cache, it);  // most recently used
       ++e->ctr.cache_hits;
-      return run_host(e, it->mat, tokens, x, y);
+      return run_host(e, e->cache.back().mat, tokens, x, y);
     }
   }
   ++e->ctr.cache_misses;
-  // native_gpu.rs:42-44, 178-185: evict oldest entries until the newcomer fits
-  while (!e->cache.empty() &&
-         (expect > e->limit || e->ctr.resident_bytes > e->limit - expect))
-    drop_entry(e, e->cache.begin());
+  // native_gpu.rs:42-44, 178-185: evict the oldest entries (pinned ones stay) until the newcomer fits
+  for (auto it = e->cache.begin(); it != e->cache.end() && (expect > e->limit || e->ctr.resident_bytes > e->limit - expect);) {
+    if (it->pinned) { ++it; continue; }
+    auto victim = it++;
+    drop_entry(e, victim);
+  }
   llr_matrix* m = nullptr;
   if ((rc = alloc_matrix(e, dtype, rows, cols, rb, expect, &m)) != LLR_OK) return rc;
   cudaError_t ce = cudaMemcpyAsync(m->dev, packed, expect, cudaMemcpyHostToDevice, e->stream);
@@ -717,14 +741,48 @@ int llr_matmul(llr_exec* e, uint8_t dtype, size_t rows, size_t cols, size_t toke
     finish_range_check(m, bound, true);
   }
   if (rc != LLR_OK) { cudaStreamSynchronize(e->stream); cudaGetLastError(); release_matrix(e, m); return rc; }
-  // oversized matrices run once and are released (native_gpu.rs:199-211)
-  if (expect <= e->limit) {
-    e->cache.push_back(CacheEntry{dtype, (int64_t)rows, (int64_t)cols, packed_len, h, m});
+  // matrices that do not fit the budget (beside what is pinned) run once and are released (native_gpu.rs:199-211)
+  if (expect <= e->limit && e->ctr.resident_bytes <= e->limit - expect) {
+    e->cache.push_back(CacheEntry{dtype, (int64_t)rows, (int64_t)cols, packed_len, h, keyed, false, m});
     e->ctr.resident_bytes += expect;
   } else {
     release_matrix(e, m);
   }
   return LLR_OK;
+}
+
+int llr_matmul(llr_exec* e, uint8_t dtype, size_t rows, size_t cols, size_t tokens, const void* packed, size_t packed_len,
+               const float* x, size_t x_len, float* y, size_t y_len) {
+  return matmul_cached(e, nullptr, dtype, rows, cols, tokens, packed, packed_len, x, x_len, y, y_len);
+}
+
+int llr_matmul_keyed(llr_exec* e, uint64_t key_hi, uint64_t key_lo, uint8_t dtype, size_t rows, size_t cols, size_t tokens,
+                     const void* packed, size_t packed_len, const float* x, size_t x_len, float* y, size_t y_len) {
+  const Hash128 key{key_hi, key_lo};
+  return matmul_cached(e, &key, dtype, rows, cols, tokens, packed, packed_len, x, x_len, y, y_len);
+}
+
+int llr_exec_pin_key(llr_exec* e, uint64_t key_hi, uint64_t key_lo, int pinned) {
+  if (!e) return LLR_ERR_INVALID;
+  const Hash128 key{key_hi, key_lo};
+  bool found = false;
+  for (auto& ent : e->cache)
+    if (ent.keyed && ent.hash == key) { ent.pinned = pinned != 0; found = true; }
+  if (!found) return fail(e, LLR_ERR_INVALID, "no resident matrix carries this key");
+  return LLR_OK;
+}
+
+// plan_placement (expertvm/src/planner.rs:332-349): move the expert's weights once, or ship activations on every use.
+int llr_plan_placement(uint64_t expert_bytes, uint64_t activation_bytes, uint64_t fan_in, uint64_t reuse, uint64_t link_bps) {
+  // nanoseconds to carry bytes at bps, floored, saturating at 2^64-1 (gpu-sim/src/profile.rs:718-727)
+  auto ns_for_bytes = [](uint64_t bytes, uint64_t bps) -> uint64_t {
+    if (bps == 0) return UINT64_MAX;
+    const unsigned __int128 n = (unsigned __int128)bytes * 1000000000ull / bps;
+    return n > (unsigned __int128)UINT64_MAX ? UINT64_MAX : (uint64_t)n;
+  };
+  auto sat_mul = [](uint64_t a, uint64_t b) { return a != 0 && b > UINT64_MAX / a ? UINT64_MAX : a * b; };
+  const uint64_t dispatch = sat_mul(sat_mul(activation_bytes, fan_in ? fan_in : 1), reuse ? reuse : 1);
+  return ns_for_bytes(expert_bytes, link_bps) <= ns_for_bytes(dispatch, link_bps) ? LLR_PLACE_MOVE_WEIGHTS : LLR_PLACE_DISPATCH_ACTIVATIONS;
 }
 
 int llr_matmul_device(llr_exec* e, const llr_matrix* m, size_t tokens, const float* x_dev,

@@ -116,7 +116,31 @@ dequant_indexed_kernel(const uint8_t* __restrict__ W, int64_t row_bytes, int64_t
   }
 }
 
+// *flag = 1 when the two byte ranges differ anywhere (both 16-byte aligned; n bytes), else 0
+__global__ void bytes_differ_kernel(const uint8_t* __restrict__ a, const uint8_t* __restrict__ b, size_t n, int* __restrict__ flag) {
+  const size_t n16 = n / 16;
+  bool diff = false;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 x = ((const uint4*)a)[i], y = ((const uint4*)b)[i];
+    diff = diff || x.x != y.x || x.y != y.y || x.z != y.z || x.w != y.w;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (size_t i = n16 * 16; i < n; ++i) diff = diff || a[i] != b[i];
+  if (diff) *flag = 1;
+}
+
 }  // namespace
+
+cudaError_t launch_bytes_differ(const void* a, const void* b, size_t n, int* flag_dev, cudaStream_t stream, uint64_t* launches) {
+  cudaError_t e = cudaMemsetAsync(flag_dev, 0, sizeof(int), stream);
+  if (e != cudaSuccess) return e;
+  size_t blocks = (n / 16 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks == 0) blocks = 1;
+  bytes_differ_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const uint8_t*)a, (const uint8_t*)b, n, flag_dev);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
 
 #define LLR_DISPATCH_DTYPE(dt, CALL)                         \
   switch (dt) {                                              \

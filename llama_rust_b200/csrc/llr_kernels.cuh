@@ -242,6 +242,9 @@ cudaError_t launch_argmax_advance(const float* logits, int n, int* out_id, float
 cudaError_t launch_argmax_rows(const float* logits, int n_rows, int n, int* out_id, float* out_margin, cudaStream_t s,
                                uint64_t* launches);
 
+// *flag_dev = 1 when the two device byte ranges differ (both 16-byte aligned), else 0
+cudaError_t launch_bytes_differ(const void* a, const void* b, size_t n, int* flag_dev, cudaStream_t stream, uint64_t* launches);
+
 // Seeded synthetic packed blocks (see llama_rust_b200/synth.py for the recipe).
 cudaError_t launch_synth(int dtype, int64_t rows, int64_t cols, uint64_t seed, uint8_t* w,
                          cudaStream_t stream, uint64_t* launches);

@@ -199,6 +199,14 @@ class Session:
             pass
 
 
+MOVE_WEIGHTS, DISPATCH_ACTIVATIONS = 0, 1
+
+
+def plan_placement(expert_bytes: int, activation_bytes: int, fan_in: int, reuse: int, link_bps: int) -> int:
+    """Move an expert's weights once or ship activations on every use (expertvm/src/planner.rs:332-349)."""
+    return lib().llr_plan_placement(expert_bytes, activation_bytes, fan_in, reuse, link_bps)
+
+
 class Executor:
     """One device, one stream, scratch reuse and weight residency (CudaGemv, gpu.rs:139)."""
 
@@ -269,6 +277,18 @@ class Executor:
         assert y.dtype == np.float32 and y.flags.c_contiguous
         self._check(lib().llr_matmul(self._h, dtype, rows, cols, tokens, w.ctypes.data, w.size,
                                      xv.ctypes.data, xv.size, y.ctypes.data, y.size))
+
+    def matmul_keyed(self, key, dtype: int, rows: int, cols: int, tokens: int, packed, x, y: np.ndarray) -> None:
+        """matmul for weights with a stable identity: key = (hi, lo), e.g. the blob range of an immutable model file
+        (QuantMat.start..end, langtax/src/decode.rs:476-485).  A hit reads nothing but the key."""
+        w, xv = _as_u8(packed), _as_f32(x)
+        assert y.dtype == np.float32 and y.flags.c_contiguous
+        self._check(lib().llr_matmul_keyed(self._h, key[0], key[1], dtype, rows, cols, tokens, w.ctypes.data, w.size,
+                                           xv.ctypes.data, xv.size, y.ctypes.data, y.size))
+
+    def pin_key(self, key, pinned: bool = True) -> None:
+        """Keeps the keyed matrix out of eviction (pin_hot of the expert store, langtax/src/engine.rs:916-950)."""
+        self._check(lib().llr_exec_pin_key(self._h, key[0], key[1], int(pinned)))
 
     def matmul_device(self, m: Matrix, tokens: int, x_ptr: int, y_ptr: int, stream: int = 0) -> None:
         self._check(lib().llr_matmul_device(self._h, m._h, tokens, x_ptr, y_ptr, stream))

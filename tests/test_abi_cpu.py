@@ -87,3 +87,14 @@ def test_host_synth_is_deterministic_and_well_formed(orc):
     x = synth.activations(4096, 3)
     assert abs(float(x.mean())) < 0.1 and 0.9 < float(x.std()) < 1.1
     assert synth.tensor_seed(0, "blk.0.attn_q.weight") != synth.tensor_seed(0, "blk.1.attn_q.weight")
+
+
+def test_plan_placement_follows_the_byte_volume_rule():  # expertvm/src/tests.rs:441-454, planner.rs:332-349
+    from llama_rust_b200 import DISPATCH_ACTIVATIONS, MOVE_WEIGHTS, plan_placement
+    expert, act, pcie = 188 << 20, 4096, 32 * 1_000_000_000
+    assert plan_placement(expert, act, 1, 1, pcie) == DISPATCH_ACTIVATIONS
+    assert plan_placement(expert, act, 1, 64_000, pcie) == MOVE_WEIGHTS
+    assert plan_placement(expert, act, 0, 0, pcie) == DISPATCH_ACTIVATIONS      # zero fan-in and reuse count as one
+    assert plan_placement(4096, 4096, 1, 1, pcie) == MOVE_WEIGHTS               # a tie moves the weights
+    assert plan_placement(expert, act, 1, 1, 0) == MOVE_WEIGHTS                 # no link: both infinite, tie
+    assert plan_placement(1 << 40, 1 << 40, 1 << 40, 1 << 40, 1) == MOVE_WEIGHTS  # saturating products

@@ -371,6 +371,60 @@ def test_residency_is_content_addressed_and_bounded(monkeypatch, orc):
     e.close()
 
 
+def test_keyed_residency_pins_and_verified_hits(monkeypatch, orc):
+    """A caller key replaces the fingerprint (a hit reads only the key), pinned entries outlive eviction, and
+    LLAMA_CUDA_CACHE_VERIFY=1 compares all bytes on a fingerprint hit (native_gpu.rs:96-98)."""
+    from llama_rust_b200 import Executor
+    rng = np.random.default_rng(6)
+    w = [random_packed(rng, Q8_0, 64, 256) for _ in range(4)]
+    x = rng.standard_normal(256).astype(np.float32)
+    want = [orc.gemv(Q8_0, 256, wi, x, 64) for wi in w]
+    monkeypatch.setenv("LLAMA_CUDA_CACHE_BYTES", str(2 * 17408))
+    e = Executor(0)
+    y = np.empty(64, np.float32)
+    e.matmul_keyed((1, 100), Q8_0, 64, 256, 1, w[0], x, y)
+    check_kernel(y, want[0], "keyed miss")
+    e.matmul_keyed((1, 100), Q8_0, 64, 256, 1, w[1], x, y)  # the key decides, not the bytes: still matrix 0
+    check_kernel(y, want[0], "keyed hit")
+    c = e.counters()
+    assert (c["cache_misses"], c["cache_hits"], c["uploads"]) == (1, 1, 1)
+    e.matmul(Q8_0, 64, 256, 1, w[0], x, y)                   # a fingerprinted entry never matches a keyed one
+    assert e.counters()["cache_misses"] == 2
+    e.pin_key((1, 100))
+    e.matmul(Q8_0, 64, 256, 1, w[2], x, y)                   # evicts the fingerprinted w[0], not the pinned key
+    e.matmul(Q8_0, 64, 256, 1, w[3], x, y)                   # evicts w[2]
+    c = e.counters()
+    assert c["evictions"] == 2 and c["resident_bytes"] == 2 * 17408
+    e.matmul_keyed((1, 100), Q8_0, 64, 256, 1, w[0], x, y)
+    assert e.counters()["cache_hits"] == 2
+    check_kernel(y, want[0], "pinned survives")
+    e.pin_key((1, 100), False)
+    e.matmul(Q8_0, 64, 256, 1, w[2], x, y)
+    e.matmul(Q8_0, 64, 256, 1, w[1], x, y)                   # now the key goes too
+    e.matmul_keyed((1, 100), Q8_0, 64, 256, 1, w[0], x, y)
+    assert e.counters()["cache_hits"] == 2
+    with pytest.raises(Exception):
+        e.pin_key((9, 9))
+    e.close()
+    # with both slots pinned a third matrix runs once without residency
+    e = Executor(0)
+    e.matmul_keyed((1, 1), Q8_0, 64, 256, 1, w[0], x, y); e.pin_key((1, 1))
+    e.matmul_keyed((1, 2), Q8_0, 64, 256, 1, w[1], x, y); e.pin_key((1, 2))
+    e.matmul(Q8_0, 64, 256, 1, w[2], x, y)
+    check_kernel(y, want[2], "beside pinned")
+    c = e.counters()
+    assert c["evictions"] == 0 and c["resident_bytes"] == 2 * 17408
+    e.close()
+    monkeypatch.setenv("LLAMA_CUDA_CACHE_VERIFY", "1")
+    e = Executor(0)
+    for i in (0, 0, 1, 0):
+        e.matmul(Q8_0, 64, 256, 1, w[i].copy(), x, y)
+        check_kernel(y, want[i], "verified")
+    c = e.counters()
+    assert (c["cache_misses"], c["cache_hits"]) == (2, 2)
+    e.close()
+
+
 def test_pinned_and_pageable_buffers_give_the_same_bits():
     """Decode-sized host-pointer calls deliver the result from the kernel into the caller's pinned
     buffer (or a pinned staging buffer for pageable memory) and signal completion through a mapped
