@@ -77,6 +77,50 @@ def arena_layout(row_counts: Sequence[int], tokens: int = 1) -> tuple[list[int],
     return offs, ARENA_HEADER_BYTES + 3 * (cur - ARENA_HEADER_BYTES)
 
 
+class RankLeft(RuntimeError):
+    """A peer announced that it leaves, or did not reach the step in time; nothing was launched."""
+
+    def __init__(self, step: int, left: list[int], missing: list[int]):
+        super().__init__(f"step {step}: ranks {left} left, ranks {missing} did not arrive")
+        self.step, self.left, self.missing = step, left, missing
+
+
+class StepGate:
+    """Host-side agreement of all ranks before each launch of a kernel that waits on its peers.
+
+    The sharded program's CTAs spin (bounded) on values that peer GPUs store, so a launch must not start unless every
+    peer launches the same step.  Each rank posts `step` to a key-value store (torch.distributed's TCPStore or any
+    object with set/check) and polls until every rank has posted it; a rank that leaves between steps posts a
+    departure mark first, which the others see before their next launch.  A rank that is silent for `timeout_s`
+    counts as missing.  Either way `enter` raises RankLeft and the caller still owns a usable executor: no kernel
+    of the step ran on this rank."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 5.0, poll_s: float = 0.002, name: str = "gate"):
+        self.store, self.rank, self.world = store, rank, world
+        self.timeout_s, self.poll_s, self.name = timeout_s, poll_s, name
+
+    def _key(self, what, rank):
+        return f"{self.name}/{what}/{rank}"
+
+    def enter(self, step: int) -> None:
+        import time
+        self.store.set(self._key(step, self.rank), b"1")
+        others = [g for g in range(self.world) if g != self.rank]
+        deadline = time.monotonic() + self.timeout_s
+        while True:
+            waiting = [g for g in others if not self.store.check([self._key(step, g)])]
+            if not waiting:
+                return
+            left = [g for g in waiting if self.store.check([self._key("left", g)])]
+            if left or time.monotonic() > deadline:
+                raise RankLeft(step, left, [g for g in waiting if g not in left])
+            time.sleep(self.poll_s)
+
+    def leave(self) -> None:
+        """Call between steps, with none of this rank's kernels in flight."""
+        self.store.set(self._key("left", self.rank), b"1")
+
+
 class ShardedDecodeProgram:
     """One decode step of row-sharded products as a single launch per rank.
 
@@ -123,7 +167,10 @@ class ShardedDecodeProgram:
     def y_ptr(self, i: int) -> int:
         return self.arena + self.offsets[i]
 
-    def run(self, stream: int = 0) -> None:
+    def run(self, stream: int = 0, gate: StepGate | None = None, step: int = 0) -> None:
+        """With a gate, the launch happens only after every rank has reached `step` (else RankLeft, nothing launched)."""
+        if gate is not None:
+            gate.enter(step)
         self.program.run(stream)
 
     def close(self) -> None:

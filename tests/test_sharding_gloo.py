@@ -139,3 +139,39 @@ def test_dispatch_plans_are_consistent():
         mine = [e for e in range(n_expert) if e % world == r]
         assert sorted(perm.tolist()) == list(range(int(counts_all[:, mine].sum())))
         assert per_expert.sum() == perm.size and all(per_expert[e] == 0 for e in range(n_expert) if e % world != r)
+
+
+def _gate_rank(rank, world, port, leave_after, silent):
+    """Steps of a two-rank job whose rank 1 leaves between steps (announced, or silently)."""
+    import datetime
+    from llama_rust_b200.sharding import RankLeft, StepGate
+    store = dist.TCPStore("127.0.0.1", port, world, rank == 0, timeout=datetime.timedelta(seconds=30))
+    gate = StepGate(store, rank, world, timeout_s=1.0)
+    launched = []
+    out = None
+    for step in range(6):
+        if rank == 1 and step == leave_after:
+            if not silent:
+                gate.leave()
+            break
+        try:
+            gate.enter(step)
+        except RankLeft as e:
+            out = (e.step, e.left, e.missing)
+            break
+        launched.append(step)   # the launch of the peer-waiting kernel would stand here
+    if rank == 0:
+        store.set("done", b"1")
+    else:
+        store.wait(["done"])     # the store's host outlives its clients
+    return launched, out
+
+
+@pytest.mark.parametrize("silent", [False, True])
+def test_a_rank_that_leaves_between_steps_is_seen_before_the_next_launch(silent):
+    port = _free_port()
+    res = _run(2, _gate_rank, port, 3, silent)
+    assert res[1] == ([0, 1, 2], None)
+    launched, err = res[0]
+    assert launched == [0, 1, 2]                      # no step is launched that the peer does not launch too
+    assert err == ((3, [], [1]) if silent else (3, [1], []))
