@@ -50,6 +50,15 @@ extern "C" {
 #define LLR_ERR_CUDA 6      /* CUDA runtime failure; see llr_exec_last_error                       */
 #define LLR_ERR_OOM 7       /* device allocation failed after dropping cached weights              */
 #define LLR_ERR_CONFIG 8    /* malformed LLAMA_CUDA_CACHE_BYTES   [native_gpu.rs:20-32]            */
+/* GGUF parse errors [GgufError, langtax/src/gguf.rs:338-370] */
+#define LLR_GGUF_MAGIC 20        /* "not a GGUF file"                 */
+#define LLR_GGUF_VERSION 21      /* "unsupported GGUF version {v}"    */
+#define LLR_GGUF_TRUNCATED 22    /* "truncated GGUF"                  */
+#define LLR_GGUF_UTF8 23         /* "non-utf8 GGUF string"            */
+#define LLR_GGUF_TYPE 24         /* "unsupported ggml type {t}"       */
+#define LLR_GGUF_REMOVED_TYPE 25 /* "ggml-removed type {t}"           */
+#define LLR_GGUF_KV_TYPE 26      /* "unsupported GGUF kv type {t}"    */
+#define LLR_GGUF_SHAPE 27        /* "invalid GGUF tensor shape"       */
 
 typedef struct llr_exec llr_exec;     /* opaque executor: device, stream, scratch, residency */
 typedef struct llr_matrix llr_matrix; /* opaque resident packed matrix, tied to its executor  */
@@ -166,6 +175,51 @@ int llr_exec_pin_key(llr_exec* exec, uint64_t key_hi, uint64_t key_lo, int pinne
 #define LLR_PLACE_DISPATCH_ACTIVATIONS 1
 int llr_plan_placement(uint64_t expert_bytes, uint64_t activation_bytes, uint64_t fan_in, uint64_t reuse,
                        uint64_t link_bps);
+
+/* ---- model files ---------------------------------------------------------------------------------------------
+ * GGUF v3 reader [load_gguf / parse_gguf, langtax/src/gguf.rs:700-806] and the step from a tensor's blob range to a
+ * resident packed matrix [QuantMat, quant_mat, quant_mat_rows: langtax/src/decode.rs:476-485, :9612-9713].
+ * llr_gguf_open maps the file read-only; llr_gguf_open_bytes parses an image the caller keeps alive.  Both return
+ * the object even on a parse error (for llr_gguf_last_error); release it with llr_gguf_close. */
+typedef struct llr_gguf llr_gguf;
+typedef struct {
+  const char* name;    /* valid until llr_gguf_close                                              */
+  int32_t ggml_type;   /* ggml type id as stored in the file                                      */
+  int32_t dtype;       /* LLR_DTYPE_* of the executor, or -1 when it has no kernel for the type   */
+  uint32_t n_dims;     /* 1..4                                                                    */
+  uint64_t shape[4];   /* GGUF order, innermost (columns) first; unused entries are 1             */
+  uint64_t start, end; /* byte range of the payload in the file [Tensor::blob_range, gguf.rs:435] */
+} llr_gguf_tensor;
+int llr_gguf_open(const char* path, llr_gguf** out);
+int llr_gguf_open_bytes(const void* bytes, size_t len, llr_gguf** out);
+void llr_gguf_close(llr_gguf* g);
+const char* llr_gguf_last_error(const llr_gguf* g);
+int llr_gguf_info(const llr_gguf* g, size_t* n_tensors, size_t* alignment, size_t* file_bytes);
+int llr_gguf_tensor_at(const llr_gguf* g, size_t index, llr_gguf_tensor* out); /* file order [Gguf::tensors] */
+int llr_gguf_find(const llr_gguf* g, const char* name, llr_gguf_tensor* out);  /* first of that name [Gguf::tensor] */
+/* Copies bytes [start, start + len) of the file image to out (small host-side tensors such as norm weights). */
+int llr_gguf_read(const llr_gguf* g, uint64_t start, size_t len, void* out);
+/* Typed metadata readers: LLR_ERR_INVALID when the key is absent or holds another type [gguf.rs:571-628]. */
+int llr_gguf_kv_u32(const llr_gguf* g, const char* key, uint32_t* out);
+int llr_gguf_kv_f32(const llr_gguf* g, const char* key, float* out);
+int llr_gguf_kv_bool(const llr_gguf* g, const char* key, int* out);
+int llr_gguf_kv_string(const llr_gguf* g, const char* key, const char** out, size_t* len);
+int llr_gguf_kv_i32s(const llr_gguf* g, const char* key, int32_t* out, size_t cap, size_t* n);
+int llr_gguf_kv_type(const llr_gguf* g, const char* key, int* type, int* elem_type, size_t* n_items);
+/* Any scalar value as raw bits (integers extended to 64 bits, floats as their IEEE bits) with its gguf type. */
+int llr_gguf_kv_bits(const llr_gguf* g, const char* key, uint64_t* bits, int* type);
+/* Rows [first_row, first_row + n_rows) (n_rows 0: all rows) of part `part` (0 for a 2-D weight, the expert for a
+ * 3-D *_exps tensor) as a resident matrix: the bytes go from the file image to the device packed. */
+int llr_gguf_upload(llr_exec* exec, llr_gguf* g, const char* name, size_t part, size_t first_row, size_t n_rows,
+                    llr_matrix** out);
+/* The same range through llr_matmul_keyed, the key being (this open file, byte offset): the crate-facing product
+ * for weights that live in a model file; after the first call nothing of the weights is read on the host. */
+int llr_gguf_matmul(llr_exec* exec, llr_gguf* g, const char* name, size_t part, size_t first_row, size_t n_rows,
+                    size_t tokens, const float* x, size_t x_len, float* y, size_t y_len);
+/* The key llr_gguf_matmul uses for that range, e.g. for llr_exec_pin_key.  key_hi counts open files from 1;
+ * callers that make keys of their own keep them apart by setting the top bit of key_hi. */
+int llr_gguf_key(llr_gguf* g, const char* name, size_t part, size_t first_row, size_t n_rows, uint64_t* key_hi,
+                 uint64_t* key_lo);
 
 /* Device-pointer form of llr_gemm_resident: x_dev and y_dev are device
  * buffers of tokens*cols and tokens*rows floats; the work is enqueued on

@@ -24,7 +24,10 @@ SYMBOLS = [
     "llr_session_create", "llr_session_prefill", "llr_session_decode", "llr_session_logits", "llr_session_position",
     "llr_session_reset", "llr_session_free", "llr_session_create_paged", "llr_session_batch", "llr_session_seq_position",
     "llr_session_seq_reset", "llr_moe_route_device", "llr_moe_experts_device", "llr_matmul_keyed",
-    "llr_exec_pin_key", "llr_plan_placement",
+    "llr_exec_pin_key", "llr_plan_placement", "llr_gguf_open", "llr_gguf_open_bytes", "llr_gguf_close",
+    "llr_gguf_last_error", "llr_gguf_info", "llr_gguf_tensor_at", "llr_gguf_find", "llr_gguf_read", "llr_gguf_kv_u32",
+    "llr_gguf_kv_f32", "llr_gguf_kv_bits", "llr_gguf_kv_bool", "llr_gguf_kv_string", "llr_gguf_kv_i32s", "llr_gguf_kv_type",
+    "llr_gguf_upload", "llr_gguf_matmul", "llr_gguf_key",
 ]
 ARENA_HEADER_BYTES = 65536
 
@@ -33,6 +36,11 @@ class Counters(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "launches", "uploads", "upload_bytes", "resident_bytes", "cache_limit", "cache_hits",
         "cache_misses", "evictions", "h2d_bytes", "d2h_bytes")]
+
+
+class GgufTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("ggml_type", C.c_int32), ("dtype", C.c_int32), ("n_dims", C.c_uint32),
+                ("shape", C.c_uint64 * 4), ("start", C.c_uint64), ("end", C.c_uint64)]
 
 
 class ProgramEntry(C.Structure):
@@ -102,6 +110,25 @@ def load() -> C.CDLL:
     lib.llr_matmul_keyed.argtypes = [vp, u64, u64, u8, sz, sz, sz, vp, sz, vp, sz, vp, sz]
     lib.llr_exec_pin_key.argtypes = [vp, u64, u64, C.c_int]
     lib.llr_plan_placement.argtypes = [u64, u64, u64, u64, u64]
+    cp = C.c_char_p
+    lib.llr_gguf_open.argtypes = [cp, C.POINTER(vp)]
+    lib.llr_gguf_open_bytes.argtypes = [vp, sz, C.POINTER(vp)]
+    lib.llr_gguf_close.argtypes = [vp]
+    lib.llr_gguf_last_error.argtypes = [vp]
+    lib.llr_gguf_info.argtypes = [vp, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz)]
+    lib.llr_gguf_tensor_at.argtypes = [vp, sz, C.POINTER(GgufTensor)]
+    lib.llr_gguf_find.argtypes = [vp, cp, C.POINTER(GgufTensor)]
+    lib.llr_gguf_read.argtypes = [vp, u64, sz, vp]
+    lib.llr_gguf_kv_u32.argtypes = [vp, cp, C.POINTER(C.c_uint32)]
+    lib.llr_gguf_kv_f32.argtypes = [vp, cp, C.POINTER(C.c_float)]
+    lib.llr_gguf_kv_bits.argtypes = [vp, cp, C.POINTER(u64), C.POINTER(C.c_int)]
+    lib.llr_gguf_kv_bool.argtypes = [vp, cp, C.POINTER(C.c_int)]
+    lib.llr_gguf_kv_string.argtypes = [vp, cp, C.POINTER(cp), C.POINTER(sz)]
+    lib.llr_gguf_kv_i32s.argtypes = [vp, cp, vp, sz, C.POINTER(sz)]
+    lib.llr_gguf_kv_type.argtypes = [vp, cp, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(sz)]
+    lib.llr_gguf_upload.argtypes = [vp, vp, cp, sz, sz, sz, C.POINTER(vp)]
+    lib.llr_gguf_matmul.argtypes = [vp, vp, cp, sz, sz, sz, sz, vp, sz, vp, sz]
+    lib.llr_gguf_key.argtypes = [vp, vp, cp, sz, sz, sz, C.POINTER(u64), C.POINTER(u64)]
     lib.llr_exec_synchronize.argtypes = [vp]
     lib.llr_dequant_rows.argtypes = [vp, vp, sz, sz, vp, sz]
     lib.llr_matrix_synth.argtypes = [vp, u8, sz, sz, C.c_uint64, C.POINTER(vp)]
@@ -134,6 +161,8 @@ def load() -> C.CDLL:
     lib.llr_session_reset.argtypes = [vp]
     lib.llr_session_free.argtypes = [vp]
     for s in SYMBOLS:
-        if s != "llr_exec_last_error":
+        if s not in ("llr_exec_last_error", "llr_gguf_last_error", "llr_gguf_close"):
             getattr(lib, s).restype = C.c_int
+    lib.llr_gguf_last_error.restype = C.c_char_p
+    lib.llr_gguf_close.restype = None
     return lib
