@@ -128,7 +128,7 @@ def load() -> C.CDLL:
     lib.llr_gguf_kv_type.argtypes = [vp, cp, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(sz)]
     lib.llr_gguf_upload.argtypes = [vp, vp, cp, sz, sz, sz, C.POINTER(vp)]
     lib.llr_gguf_matmul.argtypes = [vp, vp, cp, sz, sz, sz, sz, vp, sz, vp, sz]
-    lib.llr_gguf_key.argtypes = [vp, vp, cp, sz, sz, sz, C.POINTER(u64), C.POINTER(u64)]
+    lib.llr_gguf_key.argtypes = [vp, cp, sz, sz, sz, C.POINTER(u64), C.POINTER(u64)]
     lib.llr_exec_synchronize.argtypes = [vp]
     lib.llr_dequant_rows.argtypes = [vp, vp, sz, sz, vp, sz]
     lib.llr_matrix_synth.argtypes = [vp, u8, sz, sz, C.c_uint64, C.POINTER(vp)]
