@@ -3,8 +3,8 @@
 // 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
 //
 // What it computes: gemm_<t>_f32 (langtax/src/quant.rs:6282, 6366, 6380, 6478 ->
-// gemm_f32_x :6760), y[t*rows + r] = sum_c W[r,c] x[t*cols + c], for Q4_K, Q8_0,
-// Q5_0 and Q5_1.  Operands are 16-bit (binary16 when the matrix's weights fit its range,
+// gemm_f32_x :6760; gemm_q6_k_f32 :6296), y[t*rows + r] = sum_c W[r,c] x[t*cols + c], for Q4_K, Q6_K,
+// Q8_0, Q5_0 and Q5_1.  Operands are 16-bit (binary16 when the matrix's weights fit its range,
 // bfloat16 otherwise; see dequant_sub_h), products are exact, accumulation is f32 in
 // tensor memory: this is the tensor-core path with the looser, separately stated tolerance
 // (tests/test_gpu_gemm.py); the f32-faithful path for any number of rows stays the
@@ -73,6 +73,10 @@ template <> struct Pk<DT_Q4_K> { static constexpr int RB = 144, PITCH = 144; };
 template <> struct Pk<DT_Q8_0> { static constexpr int RB = 272, PITCH = 272; };
 template <> struct Pk<DT_Q5_0> { static constexpr int RB = 176, PITCH = 176; };
 template <> struct Pk<DT_Q5_1> { static constexpr int RB = 192, PITCH = 208; };
+// Q6_K blocks are 210 bytes: the block of macro-step ms starts at 210*ms, which is a multiple of 16 bytes only
+// for every eighth step.  The copy starts at the 16-byte boundary below (TMA needs that) and is 240 bytes wide
+// (14 bytes of lead at most + 210, rounded up to an odd number of 16-byte chunks); the decoder adds the lead back.
+template <> struct Pk<DT_Q6_K> { static constexpr int RB = 210, PITCH = 240; };
 
 // Rings: A-operand stages in tensor memory (NA), activation tiles in shared memory (NB, 128 KB),
 // packed bytes in shared memory (NPK macro-steps, whatever is left, at most 6).
@@ -211,10 +215,69 @@ __device__ __forceinline__ void emit4r(uint32_t w, uint32_t mask, uint32_t magic
   o1 = pack_bf16(fmaf(f.y, a, nb), fmaf(g.y, a, nb));
 }
 
-// SB < 0: the sub-block index is the run-time value rsb (formats whose code does not depend on it)
+// 32 bytes at byte offset off (even, the same for all threads of the CTA) of a row in the packed ring, as eight
+// words: three aligned 16-byte loads, then a shift by whole words (four cases, uniform branch) and by a half word.
+__device__ __forceinline__ void lds_32_at(uint32_t prow, int off, uint32_t (&q)[8]) {
+  uint32_t w[12];
+  lds_chunks<3>(prow + (uint32_t)(off & ~15), w);
+  const uint32_t hs = (uint32_t)(off & 2) * 8u;
+  switch ((off & 15) >> 2) {
+    case 0:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[i] = __funnelshift_r(w[i], w[i + 1], hs);
+      break;
+    case 1:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[i] = __funnelshift_r(w[i + 1], w[i + 2], hs);
+      break;
+    case 2:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[i] = __funnelshift_r(w[i + 2], w[i + 3], hs);
+      break;
+    default:
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[i] = __funnelshift_r(w[i + 3], w[i + 4], hs);
+      break;
+  }
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t p) {
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(p));
+  return v;
+}
+// Q6_K sub-block sb (32 columns) of the block that starts `lead` bytes into the ring row: the six-bit codes
+// c = ql nibble | two qh bits << 4 of columns 4i..4i+3 in the bytes of c[i], the two signed scales (columns 0..15,
+// 16..31) and d.  Layout of dequant_q6_k_row (langtax/src/quant.rs): per 128 columns, ql bytes 64n + 32(j & 1) + l
+// give nibble j >> 1, qh bytes 32n + l give bits 2j.., scales 8n + 2j + l / 16.
+__device__ __forceinline__ void q6k_codes(uint32_t prow, int lead, int sb, uint32_t (&c)[8], float& d, int& s0, int& s1) {
+  const int n = sb >> 2, j = sb & 3;
+  uint32_t ql[8], qh[8];
+  lds_32_at(prow, lead + 64 * n + 32 * (j & 1), ql);
+  lds_32_at(prow, lead + 128 + 32 * n, qh);
+  const uint32_t sc = lds_u16(prow + (uint32_t)(lead + 192 + 8 * n + 2 * j));
+  d = h2f(lds_u16(prow + (uint32_t)(lead + 208)));
+  s0 = (int)(int8_t)(sc & 255u);
+  s1 = (int)(int8_t)(sc >> 8);
+  const int nsh = 4 * (j >> 1), hsh = 2 * j;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) c[i] = ((ql[i] >> nsh) & 0x0f0f0f0fu) | (((qh[i] >> hsh) & 0x03030303u) << 4);
+}
+
+// SB < 0: the sub-block index is the run-time value rsb (formats whose code does not depend on it);
+// lead: bytes between the start of the ring row and the block (Q6_K only)
 template <int DT, int SB>
-__device__ __forceinline__ void dequant_sub(uint32_t prow, uint32_t (&out)[16], int rsb = 0) {
-  if constexpr (DT == DT_Q4_K) {
+__device__ __forceinline__ void dequant_sub(uint32_t prow, uint32_t (&out)[16], int rsb = 0, int lead = 0) {
+  if constexpr (DT == DT_Q6_K) {
+    uint32_t c[8];
+    float d;
+    int s0, s1;
+    q6k_codes(prow, lead, SB < 0 ? rsb : SB, c, d, s0, s1);
+    const float a0 = d * (float)s0, a1 = d * (float)s1;  // w = d * scale * (c - 32), magic 1024: nb = -1056 a
+#pragma unroll
+    for (int i = 0; i < 4; ++i) emit4<0x00ff00ffu, 0x64006400u>(c[i], a0, -1056.0f * a0, out[2 * i], out[2 * i + 1]);
+#pragma unroll
+    for (int i = 4; i < 8; ++i) emit4<0x00ff00ffu, 0x64006400u>(c[i], a1, -1056.0f * a1, out[2 * i], out[2 * i + 1]);
+  } else if constexpr (DT == DT_Q4_K) {
     // SB enters only through shift counts, masks and an address: one code path for all eight
     // sub-blocks keeps the dequant loop inside the instruction cache.
     const int sb = SB < 0 ? rsb : SB;
@@ -298,8 +361,19 @@ __device__ __forceinline__ void emit4h(uint32_t w, __half2 off, __half2 a, __hal
 }
 
 template <int DT, int SB>
-__device__ __forceinline__ void dequant_sub_h(uint32_t prow, uint32_t (&out)[16], int rsb = 0) {
-  if constexpr (DT == DT_Q4_K) {
+__device__ __forceinline__ void dequant_sub_h(uint32_t prow, uint32_t (&out)[16], int rsb = 0, int lead = 0) {
+  if constexpr (DT == DT_Q6_K) {
+    uint32_t c[8];
+    float d;
+    int s0, s1;
+    q6k_codes(prow, lead, SB < 0 ? rsb : SB, c, d, s0, s1);
+    const __half2 a0 = __float2half2_rn(d * (float)s0), a1 = __float2half2_rn(d * (float)s1);
+    const __half2 off = __float2half2_rn(1056.f), zero = __float2half2_rn(0.f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) emit4h<0x00ff00ffu, 0x64006400u>(c[i], off, a0, zero, out[2 * i], out[2 * i + 1]);
+#pragma unroll
+    for (int i = 4; i < 8; ++i) emit4h<0x00ff00ffu, 0x64006400u>(c[i], off, a1, zero, out[2 * i], out[2 * i + 1]);
+  } else if constexpr (DT == DT_Q4_K) {
     const int sb = SB < 0 ? rsb : SB;
     uint32_t hdr[4], q[8];
     lds_chunks<1>(prow, hdr);
@@ -409,9 +483,13 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
     const int r = tid & 127, h = (tid >> 7) & 1, g = tid >> 8;
     // this thread's A-operand words: lane = row (the warp's lane quarter is warp % 4), 16 columns per half
     const uint32_t a_dst0 = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(NMMA * BN + 16 * h);
+    int lead = 0;  // Q6_K: where the block starts in the ring row (set per macro-step)
     auto decode = [&](auto KQ, uint32_t prow, uint32_t (&out)[16]) {
       constexpr int kq = decltype(KQ)::value;
-      if constexpr (F16) {
+      if constexpr (DT == DT_Q6_K) {
+        if constexpr (F16) dequant_sub_h<DT, -1>(prow, out, 2 * kq + h, lead);
+        else dequant_sub<DT, -1>(prow, out, 2 * kq + h, lead);
+      } else if constexpr (F16) {
         if constexpr (DT == DT_Q4_K) dequant_sub_h<DT, -1>(prow, out, 2 * kq + h);
         else if (h == 0) dequant_sub_h<DT, 2 * kq>(prow, out);
         else dequant_sub_h<DT, 2 * kq + 1>(prow, out);
@@ -436,6 +514,7 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
       const int ps = ms % NPK;
       if (ok && !bar_wait(&pk_full[ps], (uint32_t)((ms / NPK) & 1))) { ok = false; report_error(err, 3); }
       const uint32_t prow = s32(sP) + ps * L::P_STAGE + r * PITCH;
+      if constexpr (DT == DT_Q6_K) lead = ((ms_begin + ms) * RB) & 15;
       uint32_t o0[16], o1[16];
       if (g == 0) {
         decode(std::integral_constant<int, 0>{}, prow, o0);
@@ -504,10 +583,11 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
         const int ps = ms % NPK;
         if (ok && !bar_wait(&pk_empty[ps], (uint32_t)(((ms / NPK) & 1) ^ 1))) { ok = false; report_error(err, 3); }
         bar_expect(&pk_full[ps], BM * PITCH);
-        // x in 32-bit elements; x*4 = ms*RB is a multiple of 16 bytes.  Rows past the end read as zero.
+        // x in 32-bit elements; x*4 = ms*RB rounded down to a multiple of 16 bytes (only Q6_K's 210 needs the
+        // rounding).  Rows past the end and words past a row's end read as zero.
         asm volatile(
             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-            ::"r"(s32(sP + ps * L::P_STAGE)), "l"(wmap_p), "r"((ms_begin + ms) * (RB / 4)), "r"(row0), "r"(s32(&pk_full[ps])) : "memory");
+            ::"r"(s32(sP + ps * L::P_STAGE)), "l"(wmap_p), "r"((((ms_begin + ms) * RB) & ~15) / 4), "r"(row0), "r"(s32(&pk_full[ps])) : "memory");
       }
     }
   } else if (warp == W_ACT) {
@@ -722,13 +802,14 @@ __global__ void expert_rows_16bit_kernel(const float* __restrict__ x, const int*
 // 0x7f800000 or more.
 template <int DT>
 __global__ void weight_bound_kernel(const uint8_t* __restrict__ W, int64_t n_blocks, unsigned int* __restrict__ out) {
-  constexpr int BB = DT == DT_Q4_K ? 144 : DT == DT_Q8_0 ? 34 : DT == DT_Q5_0 ? 22 : 24;
+  constexpr int BB = DT == DT_Q4_K ? 144 : DT == DT_Q6_K ? 210 : DT == DT_Q8_0 ? 34 : DT == DT_Q5_0 ? 22 : 24;
   float m = 0.f;
   for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks; b += (int64_t)gridDim.x * blockDim.x) {
     const uint16_t* hp = (const uint16_t*)(W + b * BB);
-    const float d = fabsf(__half2float(__ushort_as_half(hp[0])));
+    const float d = fabsf(__half2float(__ushort_as_half(hp[DT == DT_Q6_K ? 104 : 0])));  // Q6_K keeps d behind the quants
     float bound;
-    if (DT == DT_Q4_K) bound = d * (63.f * 15.f) + fabsf(__half2float(__ushort_as_half(hp[1]))) * 63.f;
+    if (DT == DT_Q6_K) bound = d * (128.f * 32.f);  // |scale| <= 128, |c - 32| <= 32
+    else if (DT == DT_Q4_K) bound = d * (63.f * 15.f) + fabsf(__half2float(__ushort_as_half(hp[1]))) * 63.f;
     else if (DT == DT_Q8_0) bound = d * 128.f;
     else if (DT == DT_Q5_0) bound = d * 16.f;
     else bound = d * 31.f + fabsf(__half2float(__ushort_as_half(hp[1])));
@@ -798,7 +879,8 @@ cudaError_t launch_dt(const MatView& m, const void* xb, const float* xscale, flo
 }  // namespace
 
 bool gemm_tc_supported(const MatView& m, int64_t tokens) {
-  if (m.dtype != DT_Q4_K && m.dtype != DT_Q8_0 && m.dtype != DT_Q5_0 && m.dtype != DT_Q5_1) return false;
+  if (m.dtype != DT_Q4_K && m.dtype != DT_Q6_K && m.dtype != DT_Q8_0 && m.dtype != DT_Q5_0 && m.dtype != DT_Q5_1) return false;
+  if (m.dtype == DT_Q6_K && m.cols % 2048 != 0) return false;  // the tensor map wants rows a multiple of 16 bytes apart: 8 x 210
   if (tokens < 16 || tokens > (1 << 24) || m.rows <= 0 || m.rows > (1 << 30)) return false;
   if (m.cols % MACRO != 0 || m.cols <= 0 || m.cols > (1 << 30)) return false;
   return ((uintptr_t)m.w & 15) == 0;
@@ -825,13 +907,14 @@ size_t gemm_tc_scratch_bytes(const MatView& m, int64_t tokens) {
 }
 
 cudaError_t launch_weight_bound(const MatView& m, unsigned int* out_dev, cudaStream_t stream, uint64_t* launches) {
-  const int64_t nb = m.rows * (m.cols / (m.dtype == DT_Q4_K ? 256 : 32));
+  const int64_t nb = m.rows * (m.cols / (m.dtype == DT_Q4_K || m.dtype == DT_Q6_K ? 256 : 32));
   int64_t blocks = (nb + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   cudaError_t e = cudaMemsetAsync(out_dev, 0, sizeof(unsigned int), stream);
   if (e != cudaSuccess) return e;
   switch (m.dtype) {
     case DT_Q4_K: weight_bound_kernel<DT_Q4_K><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
+    case DT_Q6_K: weight_bound_kernel<DT_Q6_K><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
     case DT_Q8_0: weight_bound_kernel<DT_Q8_0><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
     case DT_Q5_0: weight_bound_kernel<DT_Q5_0><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
     case DT_Q5_1: weight_bound_kernel<DT_Q5_1><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
@@ -873,6 +956,7 @@ cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t t
                        : launch_dt<D, false>(m, scratch, nullptr, dst, (int)tokens, splits, stream, err_flag))
   switch (m.dtype) {
     case DT_Q4_K: e = LLR_TC(DT_Q4_K); break;
+    case DT_Q6_K: e = LLR_TC(DT_Q6_K); break;
     case DT_Q8_0: e = LLR_TC(DT_Q8_0); break;
     case DT_Q5_0: e = LLR_TC(DT_Q5_0); break;
     case DT_Q5_1: e = LLR_TC(DT_Q5_1); break;
@@ -996,6 +1080,7 @@ cudaError_t launch_gemm_tc_grouped(const GemmGroupSpec* specs, int n, bool f16, 
   cudaError_t e;
   switch (specs[0].m.dtype) {
     case DT_Q4_K: e = launch_grouped_dt<DT_Q4_K>(specs, n, f16, desc_dev, stream, err_flag); break;
+    case DT_Q6_K: e = launch_grouped_dt<DT_Q6_K>(specs, n, f16, desc_dev, stream, err_flag); break;
     case DT_Q8_0: e = launch_grouped_dt<DT_Q8_0>(specs, n, f16, desc_dev, stream, err_flag); break;
     case DT_Q5_0: e = launch_grouped_dt<DT_Q5_0>(specs, n, f16, desc_dev, stream, err_flag); break;
     case DT_Q5_1: e = launch_grouped_dt<DT_Q5_1>(specs, n, f16, desc_dev, stream, err_flag); break;
