@@ -8,7 +8,7 @@
  *
  * Conventions shared by all entry points (reference behaviour in brackets):
  *  - dtype tags are the reference's `GemmKind as u8` [langtax/src/quant.rs:6645]:
- *    F16=0 BF16=1 F32=2 Q5_0=6 Q5_1=7 Q4_0=12 Q8_0=13 Q4_K=17 Q6_K=19.  Any
+ *    F16=0 BF16=1 F32=2 Q4_1=5 Q5_0=6 Q5_1=7 Q4_0=12 Q8_0=13 Q4_K=17 Q5_K=18 Q6_K=19.  Any
  *    other tag is LLR_ERR_DTYPE; there is no CPU fallback [README.md:29-31].
  *  - activations and results are token-major f32: x[t*cols + c], y[t*rows + r]
  *    [quant.rs:6264-6267].
@@ -34,11 +34,13 @@ extern "C" {
 #define LLR_DTYPE_F16 0
 #define LLR_DTYPE_BF16 1
 #define LLR_DTYPE_F32 2
+#define LLR_DTYPE_Q4_1 5
 #define LLR_DTYPE_Q5_0 6
 #define LLR_DTYPE_Q5_1 7
 #define LLR_DTYPE_Q4_0 12
 #define LLR_DTYPE_Q8_0 13
 #define LLR_DTYPE_Q4_K 17
+#define LLR_DTYPE_Q5_K 18
 #define LLR_DTYPE_Q6_K 19
 
 #define LLR_OK 0

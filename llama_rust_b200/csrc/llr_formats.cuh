@@ -2,7 +2,7 @@
 //
 // Layouts follow langtax/src/quant.rs:86-163 (constants) and the packers at
 // :4342 (Q8_0), :4581 (Q4_0), :4639 (Q5_0), :4680 (Q5_1), :4977 (Q4_K),
-// :5712 (Q6_K).  `decode8` yields eight consecutive weights of a row with the
+// :5712 (Q6_K), :4611 (Q4_1), :5019 (Q5_K).  `decode8` yields eight consecutive weights of a row with the
 // reference's arithmetic, rounding by rounding (dequant_<t>_row,
 // quant.rs:7511-8853): products and sums are issued with __fmul_rn / __fsub_rn
 // / __fadd_rn so the compiler can never contract them into an FMA.
@@ -13,14 +13,14 @@
 namespace llr {
 
 enum : int {
-  DT_F16 = 0, DT_BF16 = 1, DT_F32 = 2, DT_Q5_0 = 6, DT_Q5_1 = 7,
-  DT_Q4_0 = 12, DT_Q8_0 = 13, DT_Q4_K = 17, DT_Q6_K = 19
+  DT_F16 = 0, DT_BF16 = 1, DT_F32 = 2, DT_Q4_1 = 5, DT_Q5_0 = 6, DT_Q5_1 = 7,
+  DT_Q4_0 = 12, DT_Q8_0 = 13, DT_Q4_K = 17, DT_Q5_K = 18, DT_Q6_K = 19
 };
 
 __host__ __device__ constexpr int block_elems(int dt) {
   return (dt == DT_F16 || dt == DT_BF16 || dt == DT_F32) ? 1
-         : (dt == DT_Q5_0 || dt == DT_Q5_1 || dt == DT_Q4_0 || dt == DT_Q8_0) ? 32
-         : (dt == DT_Q4_K || dt == DT_Q6_K) ? 256 : 0;
+         : (dt == DT_Q5_0 || dt == DT_Q5_1 || dt == DT_Q4_0 || dt == DT_Q4_1 || dt == DT_Q8_0) ? 32
+         : (dt == DT_Q4_K || dt == DT_Q5_K || dt == DT_Q6_K) ? 256 : 0;
 }
 
 __host__ __device__ constexpr int block_bytes(int dt) {
@@ -29,8 +29,10 @@ __host__ __device__ constexpr int block_bytes(int dt) {
          : dt == DT_Q5_0 ? 22
          : dt == DT_Q5_1 ? 24
          : dt == DT_Q4_0 ? 18
+         : dt == DT_Q4_1 ? 20
          : dt == DT_Q8_0 ? 34
          : dt == DT_Q4_K ? 144
+         : dt == DT_Q5_K ? 176
          : dt == DT_Q6_K ? 210 : 0;
 }
 
@@ -98,6 +100,32 @@ __device__ __forceinline__ void decode8(const uint8_t* __restrict__ blk, int u, 
     for (int j = 0; j < 8; ++j) {
       const int nib = hi ? (q[j] >> 4) : (q[j] & 15);
       w[j] = __fmul_rn((float)(nib - 8), d);
+    }
+  } else if constexpr (DT == DT_Q4_1) {  // dequant_q4_1_row, quant.rs:7703: q*d rounded, then + m
+    const float d = f16_bits_to_f32(ld16(blk));
+    const float m = f16_bits_to_f32(ld16(blk + 2));
+    const int hi = u >= 2;
+    const uint8_t* q = blk + 4 + 8 * (u & 1);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int nib = hi ? (q[j] >> 4) : (q[j] & 15);
+      w[j] = __fadd_rn(__fmul_rn((float)nib, d), m);
+    }
+  } else if constexpr (DT == DT_Q5_K) {  // dequant_q5_k_row, quant.rs:8133: a = d*sc, b = dmin*m, a*q - b
+    const float d = f16_bits_to_f32(ld16(blk));
+    const float dmin = f16_bits_to_f32(ld16(blk + 2));
+    const int g = u >> 3, v = u & 7, hi = v >= 4, l0 = 8 * (v & 3);
+    int sc, mn;
+    scale_min_k4(blk + 4, 2 * g + hi, &sc, &mn);
+    const float a = __fmul_rn(d, (float)sc);
+    const float b = __fmul_rn(dmin, (float)mn);
+    const uint8_t* q = blk + 48 + g * 32 + l0;
+    const uint8_t* qh = blk + 16 + l0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int nib = hi ? (q[j] >> 4) : (q[j] & 15);
+      const int code = nib + (((qh[j] >> (2 * g + hi)) & 1) << 4);
+      w[j] = __fsub_rn(__fmul_rn(a, (float)code), b);
     }
   } else if constexpr (DT == DT_Q5_0 || DT == DT_Q5_1) {
     constexpr int HDR = DT == DT_Q5_0 ? 2 : 4;

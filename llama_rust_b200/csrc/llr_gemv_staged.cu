@@ -108,6 +108,39 @@ __device__ __forceinline__ void unit_dot(const uint8_t* blk, int u, const float 
 #pragma unroll
     for (int k = 0; k < 4; ++k) { q[k] = byte_f32(v.x, k) - 8.0f; q[4 + k] = byte_f32(v.y, k) - 8.0f; }
     fold<MT, false>(q, x, d, 0.0f, acc);
+  } else if constexpr (DT == DT_Q4_1) {
+    const float d = f16_bits_to_f32(lds16(blk));
+    const float m = f16_bits_to_f32(lds16(blk + 2));
+    uint2 v = lds8_a2(blk + 4 + 8 * (u & 1));
+    if (u >= 2) { v.x >>= 4; v.y >>= 4; }
+    v.x &= 0x0f0f0f0fu; v.y &= 0x0f0f0f0fu;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { q[k] = byte_f32(v.x, k); q[4 + k] = byte_f32(v.y, k); }
+    fold<MT, true>(q, x, d, m, acc);
+  } else if constexpr (DT == DT_Q5_K) {
+    // blocks are 16-byte aligned in the row (176 = 11 x 16) and the window keeps that alignment
+    const uint4 h = *(const uint4*)blk;  // d | dmin<<16, then the 12 scale bytes
+    const float d = f16_bits_to_f32(h.x & 0xffffu);
+    const float dmin = f16_bits_to_f32(h.x >> 16);
+    const int g = u >> 3, v8 = u & 7, hi = v8 >= 4, sub = 2 * g + hi, l0 = 8 * (v8 & 3);
+    uint32_t sc, mn;
+    if (sub < 4) {
+      sc = (h.y >> (8 * sub)) & 63u;
+      mn = (h.z >> (8 * sub)) & 63u;
+    } else {
+      const int jj = sub - 4;
+      const uint32_t hb = (h.w >> (8 * jj)) & 255u;
+      sc = (hb & 15u) | (((h.y >> (8 * jj + 6)) & 3u) << 4);
+      mn = (hb >> 4) | (((h.z >> (8 * jj + 6)) & 3u) << 4);
+    }
+    uint2 v = *(const uint2*)(blk + 48 + g * 32 + l0);
+    const uint2 hbits = *(const uint2*)(blk + 16 + l0);
+    if (hi) { v.x >>= 4; v.y >>= 4; }
+    v.x = (v.x & 0x0f0f0f0fu) | (((hbits.x >> sub) & 0x01010101u) << 4);
+    v.y = (v.y & 0x0f0f0f0fu) | (((hbits.y >> sub) & 0x01010101u) << 4);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { q[k] = byte_f32(v.x, k); q[4 + k] = byte_f32(v.y, k); }
+    fold<MT, true>(q, x, d * (float)sc, -(dmin * (float)mn), acc);
   } else if constexpr (DT == DT_Q5_0 || DT == DT_Q5_1) {
     constexpr int HDR = DT == DT_Q5_0 ? 2 : 4;
     const float d = f16_bits_to_f32(lds16(blk));
@@ -333,6 +366,8 @@ cudaError_t launch_gemv_staged(const MatView& m, const float* x, float* y, int64
       case DT_BF16: e = launch_mt<DT_BF16>(m, xp, yp, nt, stream, sm_count); break;
       case DT_F32: e = launch_mt<DT_F32>(m, xp, yp, nt, stream, sm_count); break;
       case DT_Q5_0: e = launch_mt<DT_Q5_0>(m, xp, yp, nt, stream, sm_count); break;
+      case DT_Q4_1: e = launch_mt<DT_Q4_1>(m, xp, yp, nt, stream, sm_count); break;
+      case DT_Q5_K: e = launch_mt<DT_Q5_K>(m, xp, yp, nt, stream, sm_count); break;
       case DT_Q5_1: e = launch_mt<DT_Q5_1>(m, xp, yp, nt, stream, sm_count); break;
       case DT_Q4_0: e = launch_mt<DT_Q4_0>(m, xp, yp, nt, stream, sm_count); break;
       case DT_Q8_0: e = launch_mt<DT_Q8_0>(m, xp, yp, nt, stream, sm_count); break;

@@ -147,6 +147,8 @@ cudaError_t launch_bytes_differ(const void* a, const void* b, size_t n, int* fla
     case DT_F16: { constexpr int DT = DT_F16; CALL; } break;   \
     case DT_BF16: { constexpr int DT = DT_BF16; CALL; } break; \
     case DT_F32: { constexpr int DT = DT_F32; CALL; } break;   \
+    case DT_Q4_1: { constexpr int DT = DT_Q4_1; CALL; } break; \
+    case DT_Q5_K: { constexpr int DT = DT_Q5_K; CALL; } break; \
     case DT_Q5_0: { constexpr int DT = DT_Q5_0; CALL; } break; \
     case DT_Q5_1: { constexpr int DT = DT_Q5_1; CALL; } break; \
     case DT_Q4_0: { constexpr int DT = DT_Q4_0; CALL; } break; \

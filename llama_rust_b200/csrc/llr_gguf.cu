@@ -30,9 +30,9 @@ struct Layout { int id; int block_bytes; int block_elems; int llr_dtype; };
 // ggml type id, bytes per block, elements per block (gguf.rs:248-283, quant.rs:86-183), executor tag or -1
 constexpr Layout kLayouts[] = {
     {0, 4, 1, LLR_DTYPE_F32},   {1, 2, 1, LLR_DTYPE_F16},    {30, 2, 1, LLR_DTYPE_BF16},  {2, 18, 32, LLR_DTYPE_Q4_0},
-    {3, 20, 32, -1},            {6, 22, 32, LLR_DTYPE_Q5_0}, {7, 24, 32, LLR_DTYPE_Q5_1}, {8, 34, 32, LLR_DTYPE_Q8_0},
+    {3, 20, 32, LLR_DTYPE_Q4_1},          {6, 22, 32, LLR_DTYPE_Q5_0}, {7, 24, 32, LLR_DTYPE_Q5_1}, {8, 34, 32, LLR_DTYPE_Q8_0},
     {9, 36, 32, -1},            {10, 84, 256, -1},           {11, 110, 256, -1},          {12, 144, 256, LLR_DTYPE_Q4_K},
-    {13, 176, 256, -1},         {14, 210, 256, LLR_DTYPE_Q6_K}, {15, 292, 256, -1},       {16, 66, 256, -1},
+    {13, 176, 256, LLR_DTYPE_Q5_K},       {14, 210, 256, LLR_DTYPE_Q6_K}, {15, 292, 256, -1},       {16, 66, 256, -1},
     {17, 74, 256, -1},          {18, 98, 256, -1},           {19, 50, 256, -1},           {20, 18, 32, -1},
     {21, 110, 256, -1},         {22, 82, 256, -1},           {23, 136, 256, -1},          {29, 56, 256, -1},
     {34, 54, 256, -1},          {35, 66, 256, -1},           {39, 17, 32, -1},            {40, 36, 64, -1},

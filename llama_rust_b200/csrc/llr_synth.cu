@@ -64,8 +64,8 @@ __device__ inline void put16(uint8_t* dst, uint16_t v) {
 }
 
 __host__ __device__ constexpr int words_per_block(int dt) {
-  return dt == DT_Q8_0 ? 7 : dt == DT_Q4_0 ? 5 : dt == DT_Q5_0 ? 6 : dt == DT_Q5_1 ? 9
-         : dt == DT_Q4_K ? 24 : dt == DT_Q6_K ? 29 : 3;
+  return dt == DT_Q8_0 ? 7 : dt == DT_Q4_0 ? 5 : dt == DT_Q5_0 ? 6 : dt == DT_Q5_1 ? 9 : dt == DT_Q4_1 ? 8
+         : dt == DT_Q4_K ? 24 : dt == DT_Q5_K ? 28 : dt == DT_Q6_K ? 29 : 3;
 }
 
 template <int DT>
@@ -94,6 +94,16 @@ __global__ void synth_kernel(uint8_t* __restrict__ w, int64_t n_blocks, uint64_t
       put_words(o + 8, seed, i0 + 1, 16);
       put16(o, scale16(seed, i0 + 3));
       put16(o + 2, scale16(seed, i0 + 6));
+    } else if constexpr (DT == DT_Q4_1) {
+      put_words(o + 4, seed, i0, 16);
+      put16(o, scale16(seed, i0 + 2));
+      put16(o + 2, scale16(seed, i0 + 5));
+    } else if constexpr (DT == DT_Q5_K) {
+      put_words(o + 48, seed, i0, 128);
+      put_words(o + 16, seed, i0 + 16, 32);
+      put_words(o + 4, seed, i0 + 20, 12);
+      put16(o, scale16(seed, i0 + 22));
+      put16(o + 2, scale16(seed, i0 + 25));
     } else if constexpr (DT == DT_Q4_K) {
       put_words(o + 16, seed, i0, 128);
       put_words(o + 4, seed, i0 + 16, 12);
@@ -133,7 +143,7 @@ cudaError_t launch_synth(int dtype, int64_t rows, int64_t cols, uint64_t seed, u
 #define LLR_SYNTH_CASE(D) case D: synth_kernel<D><<<(unsigned)blocks, 256, 0, stream>>>(w, n_blocks, seed); break;
     LLR_SYNTH_CASE(DT_F16) LLR_SYNTH_CASE(DT_BF16) LLR_SYNTH_CASE(DT_F32) LLR_SYNTH_CASE(DT_Q5_0)
     LLR_SYNTH_CASE(DT_Q5_1) LLR_SYNTH_CASE(DT_Q4_0) LLR_SYNTH_CASE(DT_Q8_0) LLR_SYNTH_CASE(DT_Q4_K)
-    LLR_SYNTH_CASE(DT_Q6_K)
+    LLR_SYNTH_CASE(DT_Q6_K) LLR_SYNTH_CASE(DT_Q4_1) LLR_SYNTH_CASE(DT_Q5_K)
 #undef LLR_SYNTH_CASE
     default: return cudaErrorInvalidValue;
   }

@@ -16,8 +16,9 @@ import numpy as np
 from . import _lib
 
 F16, BF16, F32, Q5_0, Q5_1, Q4_0, Q8_0, Q4_K, Q6_K = 0, 1, 2, 6, 7, 12, 13, 17, 19
+Q4_1, Q5_K = 5, 18
 DTYPES = {"F16": F16, "BF16": BF16, "F32": F32, "Q5_0": Q5_0, "Q5_1": Q5_1, "Q4_0": Q4_0,
-          "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K}
+          "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K, "Q4_1": Q4_1, "Q5_K": Q5_K}
 OK, ERR_INVALID, ERR_UNALIGNED, ERR_DTYPE, ERR_OVERFLOW, ERR_FOREIGN, ERR_CUDA, ERR_OOM, ERR_CONFIG = range(9)
 PATH_AUTO, PATH_GENERIC, PATH_STAGED, PATH_MMA, PATH_TC = 0, 1, 2, 3, 4
 XOP_NONE, XOP_RMSNORM, XOP_SWIGLU = 0, 1, 2

@@ -17,21 +17,22 @@ correctly rounded IEEE arithmetic, so there is no libm in the way:
 Words consumed per block (in this order): Q8_0 7 (4 quants, 3 scale); Q4_0 5
 (2, 3); Q5_0 6 (1 qh [low 4 bytes], 2 quants, 3 d); Q5_1 9 (Q5_0 + 3 for m);
 Q4_K 24 (16 quants, 2 scale bytes [12 bytes], 3 d, 3 dmin); Q6_K 29 (16 ql, 8 qh,
-2 scales, 3 d); element formats 3 per element.
+2 scales, 3 d); Q4_1 8 (2 quants, 3 d, 3 m); Q5_K 28 (16 quants, 4 qh, 2 scale bytes
+[12 bytes], 3 d, 3 dmin); element formats 3 per element.
 """
 from __future__ import annotations
 
 import numpy as np
 
-from .executor import BF16, F16, F32, Q4_0, Q4_K, Q5_0, Q5_1, Q6_K, Q8_0
+from .executor import BF16, F16, F32, Q4_0, Q4_1, Q4_K, Q5_0, Q5_1, Q5_K, Q6_K, Q8_0
 
 _GAMMA = np.uint64(0x9E3779B97F4A7C15)
 _M1 = np.uint64(0xBF58476D1CE4E5B9)
 _M2 = np.uint64(0x94D049BB133111EB)
 
-BLOCK_ELEMS = {F16: 1, BF16: 1, F32: 1, Q5_0: 32, Q5_1: 32, Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256}
-BLOCK_BYTES = {F16: 2, BF16: 2, F32: 4, Q5_0: 22, Q5_1: 24, Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210}
-WORDS_PER_BLOCK = {Q8_0: 7, Q4_0: 5, Q5_0: 6, Q5_1: 9, Q4_K: 24, Q6_K: 29, F16: 3, BF16: 3, F32: 3}
+BLOCK_ELEMS = {F16: 1, BF16: 1, F32: 1, Q5_0: 32, Q5_1: 32, Q4_0: 32, Q4_1: 32, Q8_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256}
+BLOCK_BYTES = {F16: 2, BF16: 2, F32: 4, Q5_0: 22, Q5_1: 24, Q4_0: 18, Q4_1: 20, Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210}
+WORDS_PER_BLOCK = {Q8_0: 7, Q4_0: 5, Q5_0: 6, Q5_1: 9, Q4_1: 8, Q4_K: 24, Q5_K: 28, Q6_K: 29, F16: 3, BF16: 3, F32: 3}
 
 
 def tensor_seed(base: int, name: str) -> int:
@@ -118,6 +119,16 @@ def packed_blocks(dtype: int, first_block: int, n_blocks: int, seed: int) -> np.
         out[:, 8:24] = _bytes_of(w, 1, 16)
         _put16(out, 0, _scale16(w, 3))
         _put16(out, 2, _scale16(w, 6))
+    elif dtype == Q4_1:
+        out[:, 4:20] = _bytes_of(w, 0, 16)
+        _put16(out, 0, _scale16(w, 2))
+        _put16(out, 2, _scale16(w, 5))
+    elif dtype == Q5_K:
+        out[:, 48:176] = _bytes_of(w, 0, 128)
+        out[:, 16:48] = _bytes_of(w, 16, 32)
+        out[:, 4:16] = _bytes_of(w, 20, 12)
+        _put16(out, 0, _scale16(w, 22))
+        _put16(out, 2, _scale16(w, 25))
     elif dtype == Q4_K:
         out[:, 16:144] = _bytes_of(w, 0, 128)
         out[:, 4:16] = _bytes_of(w, 16, 12)

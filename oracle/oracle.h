@@ -12,7 +12,7 @@
  * reproduces the reference's in-tree known-answer tests (tests/test_oracle_*).
  *
  * dtype tags are the reference's `GemmKind as u8` (langtax/src/quant.rs:6645):
- * F16=0 BF16=1 F32=2 Q5_0=6 Q5_1=7 Q4_0=12 Q8_0=13 Q4_K=17 Q6_K=19.
+ * F16=0 BF16=1 F32=2 Q4_1=5 Q5_0=6 Q5_1=7 Q4_0=12 Q8_0=13 Q4_K=17 Q5_K=18 Q6_K=19.
  */
 #ifndef LLR_ORACLE_H
 #define LLR_ORACLE_H
@@ -24,8 +24,8 @@ extern "C" {
 #endif
 
 enum {
-  ORC_F16 = 0, ORC_BF16 = 1, ORC_F32 = 2, ORC_Q5_0 = 6, ORC_Q5_1 = 7,
-  ORC_Q4_0 = 12, ORC_Q8_0 = 13, ORC_Q4_K = 17, ORC_Q6_K = 19
+  ORC_F16 = 0, ORC_BF16 = 1, ORC_F32 = 2, ORC_Q4_1 = 5, ORC_Q5_0 = 6, ORC_Q5_1 = 7,
+  ORC_Q4_0 = 12, ORC_Q8_0 = 13, ORC_Q4_K = 17, ORC_Q5_K = 18, ORC_Q6_K = 19
 };
 
 /* error codes (0 = ok) mirroring QuantError variants, quant.rs:4120-4160 */
@@ -33,7 +33,7 @@ enum {
   ORC_OK = 0,
   ORC_ERR_UNALIGNED_COLS = 1, /* QuantError::UnalignedCols */
   ORC_ERR_SIZE = 2,           /* QuantError::Size */
-  ORC_ERR_DTYPE = 3,          /* tag outside the nine above */
+  ORC_ERR_DTYPE = 3,          /* tag outside the eleven above */
   ORC_ERR_OVERFLOW = 4
 };
 
@@ -56,6 +56,9 @@ void orc_pack_q5_1_block(float d, float m, const uint8_t q5[32], uint8_t out[24]
 void orc_pack_q4_k_block(float d, float dmin, const uint8_t sc[8], const uint8_t mn[8],
                          const uint8_t q4[256], uint8_t out[144]);
 void orc_pack_q6_k_block(float d, const int8_t sc[16], const int8_t q[256], uint8_t out[210]);
+void orc_pack_q4_1_block(float d, float m, const uint8_t q4[32], uint8_t out[20]);            /* quant.rs:4611 */
+void orc_pack_q5_k_block(float d, float dmin, const uint8_t sc[8], const uint8_t mn[8],
+                         const uint8_t q5[256], uint8_t out[176]);                              /* quant.rs:5019 */
 void orc_pack_f16(const float* v, int64_t n, uint8_t* out);
 void orc_pack_bf16(const float* v, int64_t n, uint8_t* out);
 

@@ -78,8 +78,8 @@ uint16_t orc_f32_to_bf16(float f) {
 int orc_block_elems(int kind) {
   switch (kind) {
     case ORC_F16: case ORC_BF16: case ORC_F32: return 1;
-    case ORC_Q5_0: case ORC_Q5_1: case ORC_Q4_0: case ORC_Q8_0: return 32;
-    case ORC_Q4_K: case ORC_Q6_K: return 256;
+    case ORC_Q5_0: case ORC_Q5_1: case ORC_Q4_0: case ORC_Q4_1: case ORC_Q8_0: return 32;
+    case ORC_Q4_K: case ORC_Q5_K: case ORC_Q6_K: return 256;
     default: return 0;
   }
 }
@@ -92,8 +92,10 @@ int orc_block_bytes(int kind) {
     case ORC_Q5_0: return 22;
     case ORC_Q5_1: return 24;
     case ORC_Q4_0: return 18;
+    case ORC_Q4_1: return 20;
     case ORC_Q8_0: return 34;
     case ORC_Q4_K: return 144;
+    case ORC_Q5_K: return 176;
     case ORC_Q6_K: return 210;
     default: return 0;
   }
@@ -171,6 +173,31 @@ void orc_pack_q4_k_block(float d, float dmin, const uint8_t sc[8], const uint8_t
     for (int l = 0; l < 32; ++l)
       out[16 + g * 32 + l] =
           (uint8_t)((q4[g * 64 + l] & 0x0f) | ((q4[g * 64 + 32 + l] & 0x0f) << 4));
+}
+
+// quant.rs:4611-4634: lo nibble is element j, hi nibble element j+16
+void orc_pack_q4_1_block(float d, float m, const uint8_t q4[32], uint8_t out[20]) {
+  st16(out, orc_f32_to_f16(d));
+  st16(out + 2, orc_f32_to_f16(m));
+  for (int j = 0; j < 16; ++j) out[4 + j] = (uint8_t)((q4[j] & 0x0f) | ((q4[j + 16] & 0x0f) << 4));
+}
+
+// quant.rs:5019-5072: the Q4_K header, then qh (bit 2g / 2g+1 of byte l: fifth bit of elements 64g+l / 64g+32+l),
+// then the nibbles
+void orc_pack_q5_k_block(float d, float dmin, const uint8_t sc[8], const uint8_t mn[8],
+                         const uint8_t q5[256], uint8_t out[176]) {
+  uint8_t head[144];
+  uint8_t zero[256] = {0};
+  orc_pack_q4_k_block(d, dmin, sc, mn, zero, head);
+  std::memset(out, 0, 176);
+  std::memcpy(out, head, 16);
+  for (int g = 0; g < 4; ++g)
+    for (int l = 0; l < 32; ++l) {
+      const uint8_t l5 = q5[g * 64 + l] & 31, h5 = q5[g * 64 + 32 + l] & 31;
+      out[48 + g * 32 + l] = (uint8_t)((l5 & 0x0f) | ((h5 & 0x0f) << 4));
+      if (l5 > 15) out[16 + l] |= (uint8_t)(1u << (2 * g));
+      if (h5 > 15) out[16 + l] |= (uint8_t)(2u << (2 * g));
+    }
 }
 
 // quant.rs:5712-5748
@@ -269,6 +296,43 @@ void dequant_block(int kind, const uint8_t* wb, float* out) {
         const float p1 = (float)c1 * d;
         out[j] = p0 + m;
         out[j + 16] = p1 + m;
+      }
+      break;
+    }
+    case ORC_Q4_1: {  // :7703  q*d rounded, then + m rounded
+      const float d = orc_f16_to_f32(ld16(wb));
+      const float m = orc_f16_to_f32(ld16(wb + 2));
+      for (int j = 0; j < 16; ++j) {
+        const uint8_t p = wb[4 + j];
+        const float p0 = (float)(p & 0x0f) * d;
+        const float p1 = (float)(p >> 4) * d;
+        out[j] = p0 + m;
+        out[j + 16] = p1 + m;
+      }
+      break;
+    }
+    case ORC_Q5_K: {  // :8133  a=d*sc, b=dmin*m, w = a*q5 - b
+      const float d = orc_f16_to_f32(ld16(wb));
+      const float dmin = orc_f16_to_f32(ld16(wb + 2));
+      const uint8_t* scales = wb + 4;
+      const uint8_t* qh = wb + 16;
+      const uint8_t* qs = wb + 48;
+      for (int g = 0; g < 4; ++g) {
+        uint8_t sc0, m0, sc1, m1;
+        scale_min_k4(scales, 2 * g, &sc0, &m0);
+        scale_min_k4(scales, 2 * g + 1, &sc1, &m1);
+        const float a0 = d * (float)sc0, b0 = dmin * (float)m0;
+        const float a1 = d * (float)sc1, b1 = dmin * (float)m1;
+        const uint8_t u1 = (uint8_t)(1u << (2 * g)), u2 = (uint8_t)(2u << (2 * g));
+        for (int l = 0; l < 32; ++l) {
+          const uint8_t p = qs[g * 32 + l];
+          const float q0 = (float)((p & 0x0f) + ((qh[l] & u1) ? 16 : 0));  // q5_from_nibble, :5756
+          const float q1 = (float)((p >> 4) + ((qh[l] & u2) ? 16 : 0));
+          const float t0 = a0 * q0;
+          const float t1 = a1 * q1;
+          out[g * 64 + l] = t0 - b0;
+          out[g * 64 + 32 + l] = t1 - b1;
+        }
       }
       break;
     }
@@ -374,6 +438,49 @@ void dot_block(int kind, const uint8_t* wb, const float* x, float& sum) {
         const float w1 = p1 + m;
         sum += w0 * x[j];
         sum += w1 * x[j + 16];
+      }
+      break;
+    }
+    case ORC_Q4_1: {  // :9125  element j then j+16, per nibble byte
+      const float d = orc_f16_to_f32(ld16(wb));
+      const float m = orc_f16_to_f32(ld16(wb + 2));
+      for (int j = 0; j < 16; ++j) {
+        const uint8_t p = wb[4 + j];
+        const float p0 = (float)(p & 0x0f) * d;
+        const float w0 = p0 + m;
+        sum += w0 * x[j];
+        const float p1 = (float)(p >> 4) * d;
+        const float w1 = p1 + m;
+        sum += w1 * x[j + 16];
+      }
+      break;
+    }
+    case ORC_Q5_K: {  // :9469  per l: element l of the low half, then of the high half
+      const float d = orc_f16_to_f32(ld16(wb));
+      const float dmin = orc_f16_to_f32(ld16(wb + 2));
+      const uint8_t* scales = wb + 4;
+      const uint8_t* qh = wb + 16;
+      const uint8_t* qs = wb + 48;
+      for (int g = 0; g < 4; ++g) {
+        uint8_t sc0, m0, sc1, m1;
+        scale_min_k4(scales, 2 * g, &sc0, &m0);
+        scale_min_k4(scales, 2 * g + 1, &sc1, &m1);
+        const float a0 = d * (float)sc0, b0 = dmin * (float)m0;
+        const float a1 = d * (float)sc1, b1 = dmin * (float)m1;
+        const uint8_t u1 = (uint8_t)(1u << (2 * g)), u2 = (uint8_t)(2u << (2 * g));
+        const float* xlo = x + g * 64;
+        const float* xhi = xlo + 32;
+        for (int l = 0; l < 32; ++l) {
+          const uint8_t p = qs[g * 32 + l];
+          const float q0 = (float)((p & 0x0f) + ((qh[l] & u1) ? 16 : 0));
+          const float q1 = (float)((p >> 4) + ((qh[l] & u2) ? 16 : 0));
+          const float t0 = a0 * q0;
+          const float w0 = t0 - b0;
+          sum += w0 * xlo[l];
+          const float t1 = a1 * q1;
+          const float w1 = t1 - b1;
+          sum += w1 * xhi[l];
+        }
       }
       break;
     }

@@ -18,8 +18,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 
 F16, BF16, F32, Q5_0, Q5_1, Q4_0, Q8_0, Q4_K, Q6_K = 0, 1, 2, 6, 7, 12, 13, 17, 19
+Q4_1, Q5_K = 5, 18
 KINDS = {"F16": F16, "BF16": BF16, "F32": F32, "Q5_0": Q5_0, "Q5_1": Q5_1,
-         "Q4_0": Q4_0, "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K}
+         "Q4_0": Q4_0, "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K, "Q4_1": Q4_1, "Q5_K": Q5_K}
 OK, ERR_UNALIGNED_COLS, ERR_SIZE, ERR_DTYPE, ERR_OVERFLOW = 0, 1, 2, 3, 4
 
 
@@ -73,6 +74,10 @@ def _load() -> C.CDLL:
     lib.orc_pack_q5_0_block.argtypes = [C.c_float, u8p, u8p]
     lib.orc_pack_q5_1_block.restype = None
     lib.orc_pack_q5_1_block.argtypes = [C.c_float, C.c_float, u8p, u8p]
+    lib.orc_pack_q4_1_block.restype = None
+    lib.orc_pack_q4_1_block.argtypes = [C.c_float, C.c_float, u8p, u8p]
+    lib.orc_pack_q5_k_block.restype = None
+    lib.orc_pack_q5_k_block.argtypes = [C.c_float, C.c_float, u8p, u8p, u8p, u8p]
     lib.orc_pack_q4_k_block.restype = None
     lib.orc_pack_q4_k_block.argtypes = [C.c_float, C.c_float, u8p, u8p, u8p, u8p]
     lib.orc_pack_q6_k_block.restype = None
@@ -186,6 +191,24 @@ def pack_q4_k_block(d: float, dmin: float, scales, mins, q4) -> np.ndarray:
     assert sc.size == 8 and mn.size == 8 and q.size == 256
     out = np.zeros(144, np.uint8)
     lib.orc_pack_q4_k_block(d, dmin, _p(sc), _p(mn), _p(q), _p(out))
+    return out
+
+
+def pack_q4_1_block(d: float, m: float, q4) -> np.ndarray:
+    q = np.ascontiguousarray(q4, dtype=np.uint8)
+    assert q.size == 32
+    out = np.zeros(20, np.uint8)
+    lib.orc_pack_q4_1_block(d, m, _p(q), _p(out))
+    return out
+
+
+def pack_q5_k_block(d: float, dmin: float, scales, mins, q5) -> np.ndarray:
+    sc = np.ascontiguousarray(scales, dtype=np.uint8)
+    mn = np.ascontiguousarray(mins, dtype=np.uint8)
+    q = np.ascontiguousarray(q5, dtype=np.uint8)
+    assert sc.size == 8 and mn.size == 8 and q.size == 256
+    out = np.zeros(176, np.uint8)
+    lib.orc_pack_q5_k_block(d, dmin, _p(sc), _p(mn), _p(q), _p(out))
     return out
 
 

@@ -6,8 +6,9 @@ import numpy as np
 from oracle import pyoracle as orc
 
 F16, BF16, F32, Q5_0, Q5_1, Q4_0, Q8_0, Q4_K, Q6_K = 0, 1, 2, 6, 7, 12, 13, 17, 19
+Q4_1, Q5_K = 5, 18
 ALL = {"F32": F32, "F16": F16, "BF16": BF16, "Q4_0": Q4_0, "Q5_0": Q5_0, "Q5_1": Q5_1,
-       "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K}
+       "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K, "Q4_1": Q4_1, "Q5_K": Q5_K}
 
 
 def values(row: int, cols: int) -> np.ndarray:
@@ -118,7 +119,7 @@ def random_packed(rng, kind, rows, cols, scale_mode="normal"):
             h = f32_to_f16_trunc((np.abs(rng.standard_normal(nb)) * 0.01).astype(np.float32))
         raw[:, col] = h & 0xFF
         raw[:, col + 1] = h >> 8
-    for col in {Q8_0: [0], Q4_0: [0], Q5_0: [0], Q5_1: [0, 2], Q4_K: [0, 2], Q6_K: [208]}[kind]:
+    for col in {Q8_0: [0], Q4_0: [0], Q5_0: [0], Q5_1: [0, 2], Q4_K: [0, 2], Q6_K: [208], Q4_1: [0, 2], Q5_K: [0, 2]}[kind]:
         put(col)
     if kind == Q8_0:  # codes uniform in [-127, 127]
         q = raw[:, 2:].view(np.int8)

@@ -37,7 +37,7 @@ def test_library_exports_every_declared_symbol(lib):
 
 def test_row_bytes_matches_reference_table(lib, orc):
     from llama_rust_b200 import executor as ex
-    for kind in (0, 1, 2, 6, 7, 12, 13, 17, 19):
+    for kind in (0, 1, 2, 5, 6, 7, 12, 13, 17, 18, 19):
         for cols in (0, 256, 4096, 14336):
             assert ex.row_bytes(kind, cols) == orc.row_bytes(kind, cols)
     # BASELINE shapes (quant.rs:86-163)
@@ -47,7 +47,8 @@ def test_row_bytes_matches_reference_table(lib, orc):
     with pytest.raises(ex.NativeCudaError) as e:
         ex.row_bytes(13, 33)
     assert e.value.code == ex.ERR_UNALIGNED
-    for bad in (3, 4, 5, 8, 14, 18, 20, 255):  # the other GemmKind tags are out of scope
+    assert ex.row_bytes(5, 4096) == 2560 and ex.row_bytes(18, 4096) == 2816
+    for bad in (3, 4, 8, 14, 16, 20, 255):  # the other GemmKind tags are out of scope
         with pytest.raises(ex.NativeCudaError) as e:
             ex.row_bytes(bad, 256)
         assert e.value.code == ex.ERR_DTYPE

@@ -23,7 +23,7 @@ def test_tensors_parts_and_row_ranges_upload_packed(orc):
     exps = random_packed(rng, Q4_K, parts * rows, cols)
     tensors = [(n, GGML_OF[dt], (cols, rows), w.tobytes()) for n, (dt, w) in mats.items()]
     tensors.append(("blk.0.ffn_up_exps.weight", 12, (cols, rows, parts), exps.tobytes()))
-    tensors.append(("w_q41", 3, (cols, rows), bytes(rows * cols // 32 * 20)))
+    tensors.append(("w_q2k", 10, (cols, rows), bytes(rows * cols // 256 * 84)))
     g = GgufFile(gf.write_gguf(gf.DEFAULT_KV, tensors))
     ex = Executor(0)
     x = rng.standard_normal(cols).astype(np.float32)

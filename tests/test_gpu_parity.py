@@ -114,7 +114,7 @@ def test_overflowing_shape_is_rejected_without_touching_output(q):  # parity.rs:
 def test_unsupported_dtype_tag_is_an_error_not_a_fallback(q):
     out = np.array([123.5], np.float32)
     with pytest.raises(q.QuantError) as e:
-        q.native_matmul(18, 256, 1, np.zeros(176, np.uint8), np.zeros(256, np.float32), out)  # Q5_K tag
+        q.native_matmul(3, 256, 1, np.zeros(84, np.uint8), np.zeros(256, np.float32), out)  # Q2_K tag
     assert e.value.code == 3 and out[0] == 123.5
 
 

@@ -113,6 +113,67 @@ def test_pack_q5_0_layout_known_answer(orc):  # quant.rs:10907-10926
     assert row[0] == 0.75 and row[16] == 3.0 and row[7] == -2.25 and row[23] == -0.25
 
 
+def test_pack_q4_1_known_answer(orc):  # quant.rs:10796-10828, gguf.rs:1506-1523
+    qs = np.zeros(32, np.uint8)
+    qs[0], qs[16], qs[7], qs[23] = 3, 12, 7, 15
+    w = orc.pack_q4_1_block(0.25, 0.05, qs)
+    assert w.size == 20 and w[4] == 0xC3 and w[11] == 0xF7
+    m = np.float32(orc.f16_to_f32(int(w[2]) | int(w[3]) << 8))      # 0.05 truncated to binary16
+    assert abs(float(m) - 0.05) < 2e-5 and float(m) <= 0.05
+    x = np.zeros(32, np.float32)
+    x[0], x[16], x[7], x[23] = 2, 4, 1, 3
+    row = orc.dequant_row(orc.Q4_1, 32, w)
+    want = np.full(32, m, np.float32)
+    for i, q in ((0, 3), (16, 12), (7, 7), (23, 15)):
+        want[i] = np.float32(np.float32(q * 0.25) + m)
+    assert np.array_equal(row.view(np.uint32), want.view(np.uint32))
+    y = orc.gemv(orc.Q4_1, 32, w, x, 1)[0]
+    assert abs(y - 27.0) / 28.0 < 1e-5                               # (3/4+m)2 + (3+m)4 + (7/4+m) + (15/4+m)3 with m = 0.05
+    acc = np.float32(0.0)
+    for j in range(16):                                              # element j then j+16, one running sum
+        acc = np.float32(acc + np.float32(row[j] * x[j]))
+        acc = np.float32(acc + np.float32(row[j + 16] * x[j + 16]))
+    assert acc.view(np.uint32) == np.float32(y).view(np.uint32)
+    # gemm == repeated gemv, token-major (quant.rs:10831-10880)
+    w2 = np.concatenate([orc.pack_q4_1_block(0.25, 0.05, np.where(np.arange(32) == 0, 3 + r, np.where(np.arange(32) == 16, 12 + r,
+                                                                   np.where(np.arange(32) == 7, 7, 0))).astype(np.uint8)) for r in range(2)])
+    xk = np.zeros((3, 32), np.float32)
+    xk[:, 0] = [1, 2, 3]
+    xk[:, 16] = 2
+    yk = orc.gemm(orc.Q4_1, 32, 3, w2, xk, 2)
+    for t in range(3):
+        assert np.array_equal(yk[t], orc.gemv(orc.Q4_1, 32, w2, xk[t], 2))
+
+
+def test_pack_q5_k_known_answer(orc):  # quant.rs:12078-12111, gguf.rs:1714-1731
+    qs = np.zeros(256, np.uint8)
+    qs[0], qs[32], qs[64], qs[128] = 3, 17, 20, 21
+    w = orc.pack_q5_k_block(0.25, 0.05, [2, 1, 3, 1, 4, 1, 1, 1], [1, 0, 0, 0, 2, 0, 0, 0], qs)
+    assert w.size == 176
+    assert w[16] & 0b00010111 == 0b00010110      # qh[0]: bit 1 (q=17), bit 2 (q=20), bit 4 (q=21); bit 0 clear (q=3)
+    assert np.array_equal(w[:16], orc.pack_q4_k_block(0.25, 0.05, [2, 1, 3, 1, 4, 1, 1, 1], [1, 0, 0, 0, 2, 0, 0, 0],
+                                                      np.zeros(256, np.uint8))[:16])
+    dmin = np.float32(orc.f16_to_f32(int(w[2]) | int(w[3]) << 8))
+    x = np.zeros(256, np.float32)
+    x[0], x[32], x[64], x[128] = 2, 4, 1, 3
+    row = orc.dequant_row(orc.Q5_K, 256, w)
+    assert row[0] == np.float32(np.float32(0.5 * 3) - dmin) and row[32] == 4.25 and row[64] == 15.0
+    assert row[128] == np.float32(np.float32(21.0) - np.float32(dmin * 2))
+    y = orc.gemv(orc.Q5_K, 256, w, x, 1)[0]
+    assert abs(y - 97.6) / 98.6 < 1e-5            # 1.45*2 + 4.25*4 + 15 + 20.9*3
+    acc = np.float32(0.0)
+    for g in range(4):                            # per l: low half element, then high half element
+        for l in range(32):
+            for e in (64 * g + l, 64 * g + 32 + l):
+                acc = np.float32(acc + np.float32(row[e] * x[e]))
+    assert acc.view(np.uint32) == np.float32(y).view(np.uint32)
+    # a one-block GGUF payload of the reference's own test: scales all 1, mins 0, d = 1 (gguf.rs:1714-1718)
+    qs = np.zeros(256, np.uint8)
+    qs[0], qs[32] = 3, 17
+    w = orc.pack_q5_k_block(1.0, 0.0, [1] * 8, [0] * 8, qs)
+    assert orc.dequant_row(orc.Q5_K, 256, w)[[0, 32, 1]].tolist() == [3.0, 17.0, 0.0]
+
+
 def test_pack_q6_k_one_nonzero(orc):  # quant.rs:10321-10340
     qs = np.zeros(256, np.int8)
     qs[0], qs[32] = 1, 2
