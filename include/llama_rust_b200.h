@@ -489,6 +489,10 @@ int llr_session_batch(llr_session* session, size_t n_groups, const uint32_t* seq
                       const int32_t* tokens, float* last_logits, int32_t* next_ids);
 int llr_session_seq_position(const llr_session* session, size_t seq, size_t* position);
 int llr_session_seq_reset(llr_session* session, size_t seq);
+/* Keeps the first n_keep positions of a sequence's cache and forgets the rest (their blocks return to the pool):
+ * the device half of prompt reuse [KvCache::prompt keeps the longest common prefix and recomputes the remainder,
+ * langtax/tests/native_cuda_parity.rs:243-256]. */
+int llr_session_seq_truncate(llr_session* session, size_t seq, size_t n_keep);
 
 /* Dequantize rows [row0, row0+n_rows) of a resident matrix to f32 on the
  * device and copy them to out (n_rows*cols floats, host).  Bit-exact

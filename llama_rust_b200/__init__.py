@@ -9,6 +9,8 @@ from .executor import (BF16, DTYPES, F16, F32, Q4_0, Q4_1, Q4_K, Q5_0, Q5_1, Q5_
                        NativeCudaError, Session, XOP_NONE, XOP_RMSNORM, XOP_SWIGLU, row_bytes, plan_placement,
                        MOVE_WEIGHTS, DISPATCH_ACTIVATIONS)
 
-__all__ = ["Executor", "Matrix", "Session", "NativeCudaError", "row_bytes", "DTYPES", "F16", "BF16", "F32",
+from .engine import Engine, EngineCfg
+
+__all__ = ["Engine", "EngineCfg", "Executor", "Matrix", "Session", "NativeCudaError", "row_bytes", "DTYPES", "F16", "BF16", "F32",
            "Q5_0", "Q5_1", "Q4_0", "Q4_1", "Q5_K", "Q8_0", "Q4_K", "Q6_K", "XOP_NONE", "XOP_RMSNORM", "XOP_SWIGLU", "plan_placement",
            "MOVE_WEIGHTS", "DISPATCH_ACTIVATIONS"]

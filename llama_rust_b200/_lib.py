@@ -23,7 +23,7 @@ SYMBOLS = [
     "llr_program_create_sharded", "llr_program_create_ops", "llr_program_info", "llr_exec_set_wait_limit",
     "llr_session_create", "llr_session_prefill", "llr_session_decode", "llr_session_logits", "llr_session_position",
     "llr_session_reset", "llr_session_free", "llr_session_create_paged", "llr_session_batch", "llr_session_seq_position",
-    "llr_session_seq_reset", "llr_moe_route_device", "llr_moe_experts_device", "llr_matmul_keyed",
+    "llr_session_seq_reset", "llr_session_seq_truncate", "llr_moe_route_device", "llr_moe_experts_device", "llr_matmul_keyed",
     "llr_exec_pin_key", "llr_plan_placement", "llr_gguf_open", "llr_gguf_open_bytes", "llr_gguf_close",
     "llr_gguf_last_error", "llr_gguf_info", "llr_gguf_tensor_at", "llr_gguf_find", "llr_gguf_read", "llr_gguf_kv_u32",
     "llr_gguf_kv_f32", "llr_gguf_kv_bits", "llr_gguf_kv_bool", "llr_gguf_kv_string", "llr_gguf_kv_i32s", "llr_gguf_kv_type",
@@ -154,6 +154,7 @@ def load() -> C.CDLL:
     lib.llr_session_batch.argtypes = [vp, sz, vp, vp, vp, vp, vp]
     lib.llr_session_seq_position.argtypes = [vp, sz, C.POINTER(sz)]
     lib.llr_session_seq_reset.argtypes = [vp, sz]
+    lib.llr_session_seq_truncate.argtypes = [vp, sz, sz]
     lib.llr_session_prefill.argtypes = [vp, vp, sz, vp]
     lib.llr_session_decode.argtypes = [vp, sz, vp, vp]
     lib.llr_session_logits.argtypes = [vp, vp, sz]

@@ -1657,6 +1657,28 @@ int llr_session_seq_reset(llr_session* s, size_t seq) {
   return LLR_OK;
 }
 
+int llr_session_seq_truncate(llr_session* s, size_t seq, size_t n_keep) {
+  if (!s || !s->owner) return LLR_ERR_INVALID;
+  llr_exec* e = s->owner;
+  if (seq >= s->n_seq) return fail(e, LLR_ERR_INVALID, "sequence index out of range");
+  if (n_keep > s->position[seq]) return fail(e, LLR_ERR_INVALID, "a sequence cannot be truncated beyond its position");
+  if (n_keep == s->position[seq]) return LLR_OK;
+  DeviceGuard guard(e->device);
+  if (seq == 0) {  // sequence 0 keeps its position on the device too (graph replay advances it there)
+    const int p = (int)n_keep;
+    cudaError_t ce = cudaMemcpyAsync(s->pos_dev, &p, sizeof(int), cudaMemcpyHostToDevice, e->stream);
+    if (ce != cudaSuccess) return fail_cuda(e, ce, "session truncate");
+  }
+  // Blocks wholly behind the kept prefix go back to the pool; work already queued on the stream that reads them
+  // runs before anything that could write them again.
+  const size_t keep_blocks = (n_keep + s->block_tokens - 1) / s->block_tokens;
+  std::vector<int>& mine = s->seq_blocks[seq];
+  while (mine.size() > keep_blocks) { s->free_blocks.push_back(mine.back()); mine.pop_back(); }
+  s->position[seq] = n_keep;
+  s->have_logits[seq] = 0;
+  return LLR_OK;
+}
+
 int llr_session_reset(llr_session* s) {
   if (!s || !s->owner) return LLR_ERR_INVALID;
   for (size_t q = 0; q < s->n_seq; ++q) {

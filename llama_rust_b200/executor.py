@@ -140,11 +140,13 @@ class Session:
         self.n_seq = n_seq
         self.n_vocab = int(cfg["n_vocab"])
         self._keep = []
+        self._ids = [[] for _ in range(n_seq)]  # token ids whose keys and values each sequence's cache holds
 
     def prefill(self, tokens, want_logits: bool = False):
         t = np.ascontiguousarray(tokens, np.int32)
         out = np.empty(self.n_vocab, np.float32) if want_logits else None
         self._exec._check(lib().llr_session_prefill(self._h, t.ctypes.data, t.size, out.ctypes.data if want_logits else None))
+        self._ids[0].extend(int(v) for v in t)
         return out
 
     def decode(self, n_gen: int):
@@ -152,6 +154,7 @@ class Session:
         ids = np.empty(n_gen, np.int32)
         margin = np.empty(n_gen, np.float32)
         self._exec._check(lib().llr_session_decode(self._h, n_gen, ids.ctypes.data, margin.ctypes.data))
+        self._ids[0].extend(int(v) for v in ids)
         return ids, margin
 
     def batch(self, groups, want_logits: bool = False):
@@ -164,7 +167,39 @@ class Session:
         lg = np.empty((len(groups), self.n_vocab), np.float32) if want_logits else None
         self._exec._check(lib().llr_session_batch(self._h, len(groups), seqs.ctypes.data, counts.ctypes.data, toks.ctypes.data,
                                                   lg.ctypes.data if want_logits else None, nxt.ctypes.data))
+        for q, t in groups:
+            self._ids[q].extend(int(v) for v in t)
         return nxt, lg
+
+    def cached_ids(self, seq: int = 0) -> list:
+        return list(self._ids[seq])
+
+    def seq_truncate(self, seq: int, n_keep: int) -> None:
+        self._exec._check(lib().llr_session_seq_truncate(self._h, seq, n_keep))
+        del self._ids[seq][n_keep:]
+
+    def prompt_suffix(self, tokens, seq: int = 0, max_suffix: int = 0):
+        """KvCache::prompt_suffix (langtax/src/decode.rs:1155-1195): keeps the longest common prefix of `tokens` and the
+        cached ids, rewinds the cache to it and returns the tokens still to forward, at most max_suffix of them (0: all).
+        When the whole prompt is cached the last token is forwarded again, so that its logits exist."""
+        tokens = [int(v) for v in tokens]
+        if not tokens:
+            raise ValueError("prefill tokens")
+        have = self._ids[seq]
+        lcp = 0
+        while lcp < len(have) and lcp < len(tokens) and have[lcp] == tokens[lcp]:
+            lcp += 1
+        keep = len(tokens) - 1 if lcp == len(tokens) else lcp
+        self.seq_truncate(seq, keep)
+        rest = tokens[keep:]
+        return rest[:max_suffix] if max_suffix else rest
+
+    def prompt(self, tokens, seq: int = 0):
+        """Session::prompt: the logits after `tokens` as a full prompt, re-using what the cache already holds of it."""
+        rest = self.prompt_suffix(tokens, seq)
+        if self.n_seq == 1 and seq == 0:
+            return self.prefill(rest, want_logits=True)
+        return self.batch([(seq, rest)], want_logits=True)[1][0]
 
     def seq_position(self, seq: int) -> int:
         p = C.c_size_t()
@@ -173,6 +208,7 @@ class Session:
 
     def seq_reset(self, seq: int) -> None:
         self._exec._check(lib().llr_session_seq_reset(self._h, seq))
+        self._ids[seq] = []
 
     def logits(self) -> np.ndarray:
         out = np.empty(self.n_vocab, np.float32)
@@ -187,6 +223,7 @@ class Session:
 
     def reset(self) -> None:
         self._exec._check(lib().llr_session_reset(self._h))
+        self._ids = [[] for _ in range(self.n_seq)]
 
     def free(self) -> None:
         if self._h:

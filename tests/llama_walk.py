@@ -63,13 +63,14 @@ def _generate(c, cb, tensors_ptr, kinds_ptr, embd_kind, embd_ptr, embd_cb, promp
     return ids, margin, logits
 
 
-def run_cpu(cfg, n_ctx, weights, embd, prompt, n_gen, threads=0, want_logits=False):
-    """weights: packed numpy arrays in tensor_list order; embd: packed token_embd (Q4_K)."""
+def run_cpu(cfg, n_ctx, weights, embd, prompt, n_gen, threads=0, want_logits=False, kinds=None, embd_kind=Q4_K):
+    """weights: packed numpy arrays in tensor_list order; embd: packed token_embd (Q4_K unless embd_kind says otherwise);
+    kinds: dtype of each tensor when it is not tensor_list's mix."""
     c = make_cfg(cfg, n_ctx)
     tl = tensor_list(cfg)
     ptrs = (C.c_void_p * len(tl))(*[w.ctypes.data for w in weights])
-    kinds = (C.c_int * len(tl))(*[t[1] for t in tl])
-    return _generate(c, None, ptrs, kinds, Q4_K, embd.ctypes.data, None, prompt, n_gen, threads, want_logits)
+    kinds = (C.c_int * len(tl))(*(kinds if kinds is not None else [t[1] for t in tl]))
+    return _generate(c, None, ptrs, kinds, embd_kind, embd.ctypes.data, None, prompt, n_gen, threads, want_logits)
 
 
 def run_gpu(cfg, n_ctx, ex, mats, embd_mat, prompt, n_gen, want_logits=False):
