@@ -8,6 +8,8 @@
 // attention scores, softmax denominator, weighted values) are added in a fixed tree / block order here, so
 // results are reproducible from run to run and differ from the CPU walk in the last bits only.
 #include <cuda_runtime.h>
+
+#include <cstdlib>
 #include <math_constants.h>
 
 #include "llr_kernels.cuh"
@@ -55,11 +57,21 @@ __device__ __forceinline__ int64_t kv_offset(const KvView& kv, int seq, int laye
   return ((((int64_t)b * kv.n_layer + layer) * n_head_kv + head) * kv.block_tokens + pos % kv.block_tokens) * hd;
 }
 
+// The element-wise kernels of the walk are launched with programmatic stream serialization: a kernel may be placed on
+// the SMs while its predecessor still runs, so its launch latency overlaps the predecessor's execution.  Each kernel
+// therefore waits for its predecessor (and everything before it) before it reads anything, and lets its successor be
+// placed right away; the matrix kernels that follow use that to prefetch weights.
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // one block per activation row; a row of up to 4096 values stays in registers between the two passes
 constexpr int NORM_THREADS = 1024;
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add, const float* __restrict__ w, float* __restrict__ y,
                int n, float eps) {
+  pdl_enter();
   __shared__ float sh[32];
   float* xr = x + (int64_t)blockIdx.x * n;
   const float* ar = add ? add + (int64_t)blockIdx.x * n : nullptr;
@@ -110,6 +122,7 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add, const float
 __global__ void __launch_bounds__(128)
 rope_store_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v, KvView kv, RowMap rows, int layer,
                   WalkShape w) {
+  pdl_enter();
   const int t = blockIdx.x, h = blockIdx.y;  // h < n_head: a q head, else a k head
   const int pos = row_position(rows, t);
   const int hd = w.head_dim;
@@ -146,6 +159,7 @@ constexpr int ATT_MAX_GQA = 8;
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restrict__ part, RowMap rows, int layer, int chunk,
                          WalkShape w) {
+  pdl_enter();
   extern __shared__ float sm[];  // q[gqa][hd] | scores[gqa][chunk] | red[32]
   const int hkv = blockIdx.x, split = blockIdx.y, t = blockIdx.z;
   const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
@@ -163,24 +177,53 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
   for (int i = threadIdx.x; i < gqa * hd; i += ATT_THREADS)
     sq[i] = q[((int64_t)t * w.n_head + hkv * gqa) * hd + i];
   __syncthreads();
-  // scores: one warp per position, all query heads of the group against one read of the K row
-  for (int s = s0 + warp; s < s1; s += nw) {
-    float acc[ATT_MAX_GQA];
+  // scores: one warp per position, all query heads of the group against one read of the K row.  Four positions are in
+  // flight per warp (their K rows are fetched before any of them is used): the loop is bound by memory latency, not
+  // by arithmetic.  Each position's sum is formed exactly as if it were alone: columns in ascending order per lane.
+  constexpr int SP = 4;
+  for (int sbase = s0 + warp; sbase < s1; sbase += nw * SP) {
+    float acc[SP][ATT_MAX_GQA];
+    const float* krow[SP];
 #pragma unroll
-    for (int g = 0; g < ATT_MAX_GQA; ++g) acc[g] = 0.f;
-    const float* krow = kv.k + kv_offset(kv, sid, layer, hkv, s, w.n_head_kv, hd);
-    for (int i = lane; i < hd; i += 32) {
-      const float kv_i = krow[i];
+    for (int j = 0; j < SP; ++j) {
+      const int sj = sbase + j * nw;
+      krow[j] = sj < s1 ? kv.k + kv_offset(kv, sid, layer, hkv, sj, w.n_head_kv, hd) : nullptr;
 #pragma unroll
-      for (int g = 0; g < ATT_MAX_GQA; ++g)
-        if (g < gqa) acc[g] = fmaf(sq[g * hd + i], kv_i, acc[g]);
+      for (int g = 0; g < ATT_MAX_GQA; ++g) acc[j][g] = 0.f;
+    }
+    for (int i0 = 0; i0 < hd; i0 += 128) {
+      float kvv[SP][4];
+#pragma unroll
+      for (int j = 0; j < SP; ++j)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + lane + 32 * u;
+          kvv[j][u] = (krow[j] && i < hd) ? krow[j][i] : 0.f;
+        }
+#pragma unroll
+      for (int j = 0; j < SP; ++j)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + lane + 32 * u;
+          if (krow[j] && i < hd) {
+#pragma unroll
+            for (int g = 0; g < ATT_MAX_GQA; ++g)
+              if (g < gqa) acc[j][g] = fmaf(sq[g * hd + i], kvv[j][u], acc[j][g]);
+          }
+        }
     }
 #pragma unroll
-    for (int g = 0; g < ATT_MAX_GQA; ++g)
-      if (g < gqa) {
-        const float d = warp_sum(acc[g]);
-        if (lane == 0) sc[g * max_chunk + (s - s0)] = __fmul_rn(d, scale);
+    for (int j = 0; j < SP; ++j) {
+      const int sj = sbase + j * nw;
+      if (sj < s1) {  // warp-uniform
+#pragma unroll
+        for (int g = 0; g < ATT_MAX_GQA; ++g)
+          if (g < gqa) {
+            const float d = warp_sum(acc[j][g]);
+            if (lane == 0) sc[g * max_chunk + (sj - s0)] = __fmul_rn(d, scale);
+          }
       }
+    }
   }
   __syncthreads();
   float* out = part + (((int64_t)t * w.n_head_kv + hkv) * n_split + split) * gqa * (hd + 2);
@@ -207,18 +250,20 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
   for (int g = 0; g < ATT_MAX_GQA; ++g) acc[g] = 0.f;
   const int i = threadIdx.x % hd, grp = threadIdx.x / hd;
   if (grp < P) {
-    // runs of eight positions go to the groups in turn: the split does not depend on the KV block size
-    const int bs = kv.block_tokens;
+    // runs of eight positions go to the groups in turn: the split does not depend on the KV block size.  The eight
+    // value rows of a run are fetched before the first is used; the sums are formed in ascending position order.
     for (int sb = s0 + 8 * grp; sb < s1; sb += 8 * P) {
-      const int se = min(s1, sb + 8);
-      const float* vrow = nullptr;
-      for (int s = sb; s < se; ++s, vrow += hd) {
-        if (s == sb || s % bs == 0) vrow = kv.v + kv_offset(kv, sid, layer, hkv, s, w.n_head_kv, hd) + i;  // a block's rows are contiguous
-        const float vv = *vrow;
+      float vv[8];
 #pragma unroll
-        for (int g = 0; g < ATT_MAX_GQA; ++g)
-          if (g < gqa) acc[g] = fmaf(sc[g * max_chunk + (s - s0)], vv, acc[g]);
-      }
+      for (int j = 0; j < 8; ++j)
+        vv[j] = sb + j < s1 ? kv.v[kv_offset(kv, sid, layer, hkv, sb + j, w.n_head_kv, hd) + i] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (sb + j < s1) {
+#pragma unroll
+          for (int g = 0; g < ATT_MAX_GQA; ++g)
+            if (g < gqa) acc[g] = fmaf(sc[g * max_chunk + (sb + j - s0)], vv[j], acc[g]);
+        }
     }
   }
   __syncthreads();  // the scores are no longer needed: their space takes the groups' partial sums
@@ -239,6 +284,7 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
 // weights exp(m_slice - m) and the denominator, then every thread adds its dimension over the slices in ascending order
 __global__ void __launch_bounds__(128)
 attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, RowMap rows, int chunk, WalkShape w) {
+  pdl_enter();
   __shared__ float s_e[32];
   __shared__ float s_l;
   const int hq = blockIdx.x, t = blockIdx.y;
@@ -267,12 +313,14 @@ attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out
 }
 
 __global__ void swiglu_kernel(float* __restrict__ g, const float* __restrict__ u, int64_t n) {
+  pdl_enter();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
     const float a = g[i];
     g[i] = __fmul_rn(__fdiv_rn(a, 1.0f + expf(-a)), u[i]);  // silu(gate) * up (decode.rs:11826, :2984)
   }
 }
 __global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, int64_t n) {
+  pdl_enter();
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
     x[i] = __fadd_rn(y[i], x[i]);
 }
@@ -282,6 +330,7 @@ __global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, i
 __global__ void __launch_bounds__(1024)
 argmax_kernel(const float* __restrict__ logits, int n, int* __restrict__ out_id, float* __restrict__ out_margin,
               int* __restrict__ pos_dev, int advance, int* __restrict__ count_dev) {
+  pdl_enter();
   // with count_dev: out_id[0] is the slot the next step reads its token from, and the token and its margin are also
   // appended at out_id[1 + *count_dev] / out_margin[*count_dev]: every step of a generation is then the same launch
   const int slot = count_dev ? *count_dev : 0;
@@ -346,6 +395,7 @@ argmax_kernel(const float* __restrict__ logits, int n, int* __restrict__ out_id,
 constexpr int ARG_BLOCKS = 128;
 __global__ void __launch_bounds__(256)
 argmax_part_kernel(const float* __restrict__ logits, int n, float* __restrict__ pbest, int* __restrict__ pidx, float* __restrict__ psecond) {
+  pdl_enter();
   __shared__ float sv[8], s2[8];
   __shared__ int si[8];
   const int per = (n + gridDim.x - 1) / gridDim.x;
@@ -382,6 +432,7 @@ __global__ void __launch_bounds__(ARG_BLOCKS)
 argmax_merge_kernel(const float* __restrict__ pbest, const int* __restrict__ pidx, const float* __restrict__ psecond, int parts,
                     int* __restrict__ out_id, float* __restrict__ out_margin, int* __restrict__ pos_dev, int advance,
                     int* __restrict__ count_dev) {
+  pdl_enter();
   if (threadIdx.x != 0) return;  // a hundred-odd triples: one thread, ascending order
   float best = -CUDART_INF_F, second = -CUDART_INF_F;
   int bi = 0x7fffffff;
@@ -411,22 +462,40 @@ int attention_splits(const WalkShape& w) {
   return (w.n_ctx + c - 1) / c;
 }
 
+// LLR_WALK_PDL=0 launches these kernels in plain stream order
+bool walk_pdl() {
+  static const bool on = [] { const char* v = std::getenv("LLR_WALK_PDL"); return !(v && v[0] == '0'); }();
+  return on;
+}
+template <typename... P, typename... A>
+cudaError_t launch_walk(void (*kern)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, A... args) {
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cfg.attrs = &attr;
+  cfg.numAttrs = walk_pdl() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<P>(args)...);
+}
+
 }  // namespace
 
 cudaError_t launch_rmsnorm(float* x, const float* add, const float* w, float* y, int tokens, int n, float eps,
                            cudaStream_t s, uint64_t* launches) {
   if (tokens <= 0) return cudaSuccess;
-  rmsnorm_kernel<<<tokens, NORM_THREADS, 0, s>>>(x, add, w, y, n, eps);
   if (launches) ++*launches;
-  return cudaGetLastError();
+  return launch_walk(rmsnorm_kernel, dim3(tokens), dim3(NORM_THREADS), 0, s, x, add, w, y, n, eps);
 }
 
 cudaError_t launch_rope_store(float* q, float* k, const float* v, const KvView& kv, const RowMap& rows, int tokens, int layer,
                               const WalkShape& w, cudaStream_t s, uint64_t* launches) {
   if (tokens <= 0) return cudaSuccess;
-  rope_store_kernel<<<dim3(tokens, w.n_head + w.n_head_kv), 128, 0, s>>>(q, k, v, kv, rows, layer, w);
   if (launches) ++*launches;
-  return cudaGetLastError();
+  return launch_walk(rope_store_kernel, dim3(tokens, w.n_head + w.n_head_kv), dim3(128), 0, s, q, k, v, kv, rows, layer, w);
 }
 
 size_t attention_scratch_floats(int tokens, const WalkShape& w) {
@@ -450,50 +519,47 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
     if (e != cudaSuccess) return e;
     configured = smem;
   }
-  attention_partial_kernel<<<dim3(w.n_head_kv, splits, tokens), ATT_THREADS, smem, s>>>(q, kv, scratch, rows, layer, max_chunk, w);
-  attention_combine_kernel<<<dim3(w.n_head, tokens), 128, 0, s>>>(scratch, out, rows, max_chunk, w);
   if (launches) *launches += 2;
-  return cudaGetLastError();
+  cudaError_t e = launch_walk(attention_partial_kernel, dim3(w.n_head_kv, splits, tokens), dim3(ATT_THREADS), smem, s, q, kv, scratch, rows, layer,
+                              max_chunk, w);
+  if (e != cudaSuccess) return e;
+  return launch_walk(attention_combine_kernel, dim3(w.n_head, tokens), dim3(128), 0, s, (const float*)scratch, out, rows, max_chunk, w);
 }
 
 cudaError_t launch_swiglu(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches) {
   if (n <= 0) return cudaSuccess;
   int64_t blocks = (n + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  swiglu_kernel<<<(unsigned)blocks, 256, 0, s>>>(g, u, n);
   if (launches) ++*launches;
-  return cudaGetLastError();
+  return launch_walk(swiglu_kernel, dim3((unsigned)blocks), dim3(256), 0, s, g, u, n);
 }
 
 cudaError_t launch_add(float* x, const float* y, int64_t n, cudaStream_t s, uint64_t* launches) {
   if (n <= 0) return cudaSuccess;
   int64_t blocks = (n + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  add_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, y, n);
   if (launches) ++*launches;
-  return cudaGetLastError();
+  return launch_walk(add_kernel, dim3((unsigned)blocks), dim3(256), 0, s, x, y, n);
 }
 
 cudaError_t launch_argmax_rows(const float* logits, int n_rows, int n, int* out_id, float* out_margin, cudaStream_t s,
                                uint64_t* launches) {
   if (n_rows <= 0) return cudaSuccess;
-  argmax_kernel<<<n_rows, 1024, 0, s>>>(logits, n, out_id, out_margin, nullptr, 0, nullptr);
   if (launches) ++*launches;
-  return cudaGetLastError();
+  return launch_walk(argmax_kernel, dim3(n_rows), dim3(1024), 0, s, logits, n, out_id, out_margin, (int*)nullptr, 0, (int*)nullptr);
 }
 
 cudaError_t launch_argmax_advance(const float* logits, int n, int* out_id, float* out_margin, int* pos_dev, int advance,
                                   int* count_dev, float* part, cudaStream_t s, uint64_t* launches) {
   if (n >= 16384 && part) {  // a vocabulary: spread the scan over the device (part: 3 * ARG_BLOCKS words of scratch)
-    argmax_part_kernel<<<ARG_BLOCKS, 256, 0, s>>>(logits, n, part, (int*)(part + ARG_BLOCKS), part + 2 * ARG_BLOCKS);
-    argmax_merge_kernel<<<1, ARG_BLOCKS, 0, s>>>(part, (const int*)(part + ARG_BLOCKS), part + 2 * ARG_BLOCKS, ARG_BLOCKS, out_id,
-                                                 out_margin, pos_dev, advance, count_dev);
     if (launches) *launches += 2;
-    return cudaGetLastError();
+    cudaError_t e = launch_walk(argmax_part_kernel, dim3(ARG_BLOCKS), dim3(256), 0, s, logits, n, part, (int*)(part + ARG_BLOCKS), part + 2 * ARG_BLOCKS);
+    if (e != cudaSuccess) return e;
+    return launch_walk(argmax_merge_kernel, dim3(1), dim3(ARG_BLOCKS), 0, s, (const float*)part, (const int*)(part + ARG_BLOCKS),
+                       (const float*)(part + 2 * ARG_BLOCKS), (int)ARG_BLOCKS, out_id, out_margin, pos_dev, advance, count_dev);
   }
-  argmax_kernel<<<1, 1024, 0, s>>>(logits, n, out_id, out_margin, pos_dev, advance, count_dev);
   if (launches) ++*launches;
-  return cudaGetLastError();
+  return launch_walk(argmax_kernel, dim3(1), dim3(1024), 0, s, logits, n, out_id, out_margin, pos_dev, advance, count_dev);
 }
 
 }  // namespace llr
