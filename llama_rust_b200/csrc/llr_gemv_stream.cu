@@ -78,6 +78,7 @@ using namespace mma;
 constexpr int CW = NWARP;                 // consumer warps
 constexpr int NTHREADS = (CW + 2) * 32;   // + producer + reducer
 constexpr int NRB = 4;                    // reduction buffers
+constexpr int PART_COLS = 4096;           // columns between two hand-offs of partial sums to the reducer
 constexpr int MAX_CHUNK = Lay<DT_Q4_K, 1>::CHUNK;
 static_assert(Lay<DT_Q6_K, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q8_0, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q4_0, 1>::CHUNK <= MAX_CHUNK &&
               Lay<DT_Q5_0, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q5_1, 1>::CHUNK <= MAX_CHUNK, "ring stage");
@@ -299,19 +300,29 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
         if (!entry_range(E, lo, hi, &t0, &t1)) continue;
         const int n_span = (E.cols + SPAN - 1) / SPAN;
         for (int span = 0; span < n_span; ++span) {
-          for (int tile = t0; tile < t1; ++tile, ++j) {
+          const int n_part = (min(SPAN, E.cols - span * SPAN) + PART_COLS - 1) / PART_COLS;
+          float carry[(16 * MT + 31) / 32];
+          for (int tile = t0; tile < t1; ++tile)
+          for (int part = 0; part < n_part; ++part, ++j) {
             const int rb = j % NRB;
             if (ok && !mbar_wait(&rfull[rb], (uint32_t)((j / NRB) & 1))) { ok = false; if (lane == 0) report_error(err, 1); }
             const float* rp0 = red + rb * CW * 16 * MT;
-            for (int idx = lane; idx < 16 * MT; idx += 32) {
+#pragma unroll
+            for (int slot = 0; slot < (16 * MT + 31) / 32; ++slot) {
+              const int idx = lane + 32 * slot;
+              if (idx >= 16 * MT) break;
               const int r = idx / MT, k = idx % MT, row = tile * 16 + r;
+              const bool valid = row < E.rows && k < E.tokens;
+              const int64_t at = (int64_t)k * E.y_ld + row;
+              float* yp = E.y + at;
               float v = 0.f;
 #pragma unroll
               for (int w = 0; w < CW; ++w) v += rp0[w * 16 * MT + idx];
-              if (row < E.rows && k < E.tokens) {
-                const int64_t at = (int64_t)k * E.y_ld + row;
-                float* yp = E.y + at;
-                if (span != 0) v += *yp;
+              // y = ((P0 + P1) + P2) + ...: the parts of a span are chained in a register, the spans through y
+              if (part != 0) v += carry[slot];
+              else if (span != 0 && valid) v += *yp;
+              if (part != n_part - 1) { carry[slot] = v; continue; }
+              if (valid) {
                 if (span != n_span - 1) { *yp = v; continue; }
                 if (FLOW && E.resid) {  // residual add: result + residual, as the walk adds them (decode.rs:2938, :3050)
                   if (E.resid_phase >= 0) {
@@ -498,14 +509,20 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           __syncwarp();
         }
         const int nsub = (span_cols + gm.kseg - 1) / gm.kseg;
-        for (int tile = t0; tile < t1; ++tile, ++j) {
+        // Partial sums go to the reducer every PART_COLS columns, whatever the span: a row's result is then formed
+        // the same way for one activation row (whose span is twice as long) as inside a batch.
+        const int part_mask = PART_COLS / gm.kseg - 1;  // stages per part minus one: 0 or 1
+        for (int tile = t0; tile < t1; ++tile) {
           AccT<MT> acc;
+          auto clear = [&] {
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
+            for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc.y[nt][i] = 0.f;
+              for (int i = 0; i < 4; ++i) acc.y[nt][i] = 0.f;
 #pragma unroll
-          for (int k = 0; k < MT; ++k) acc.mn[0][k] = acc.mn[1][k] = 0.f;
+            for (int k = 0; k < MT; ++k) acc.mn[0][k] = acc.mn[1][k] = 0.f;
+          };
+          clear();
           for (int sub = 0; sub < nsub; ++sub, ++c) {
             const int stage = c % NST;
             if (ok && !mbar_wait(&full[stage], (uint32_t)((c / NST) & 1))) { ok = false; if (lane == 0) report_error(err, 1); }
@@ -544,8 +561,8 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[stage]);  // this warp no longer reads the stage
-          }
-          // ---- hand this warp's partial sums of the tile to the reducer ----
+            if ((sub & part_mask) != part_mask && sub != nsub - 1) continue;
+          // ---- hand this warp's partial sums of the part to the reducer ----
           const int rb = j % NRB;
           if (ok && !mbar_wait(&rempty[rb], (uint32_t)(((j / NRB) & 1) ^ 1))) { ok = false; if (lane == 0) report_error(err, 1); }
           float* myred = red + (rb * CW + warp) * 16 * MT;
@@ -578,6 +595,9 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&rfull[rb]);
+          ++j;
+          clear();
+          }
         }
       }
     }

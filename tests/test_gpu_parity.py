@@ -334,6 +334,29 @@ def test_device_generator_matches_host_generator(ex, name):
     m.free()
 
 
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0", "Q4_0", "Q5_1"])
+def test_a_row_of_activations_gives_the_same_bits_alone_and_inside_a_batch(ex, name):
+    """The f32-faithful kernels hand their partial sums over every 4096 columns whatever the number of activation
+    rows, so one activation row alone (its digit planes span 8192 columns) and the same row inside a batch of 2..8 give
+    identical bits, also for rows longer than 4096 columns (ffn_down: 14336).  Engine batches and expert buckets rely
+    on it."""
+    from llama_rust_b200 import synth
+    kind = ALL[name]
+    ex.set_path(3)
+    for rows, cols in ((64, 14336), (48, 8192), (32, 6144)):
+        m = ex.synth(kind, rows, cols, synth.tensor_seed(9, f"{name}.{rows}.{cols}"))
+        x = synth.activations(8 * cols, 77).reshape(8, cols)
+        alone = np.empty((8, rows), np.float32)
+        for t in range(8):
+            ex.gemv_resident(m, x[t], alone[t])
+        for batch in (2, 3, 8):
+            y = np.empty(batch * rows, np.float32)
+            ex.gemm_resident(m, batch, x[:batch], y)
+            assert np.array_equal(y.reshape(batch, rows).view(np.uint32), alone[:batch].view(np.uint32)), (name, cols, batch)
+        m.free()
+    ex.set_path(0)
+
+
 # ---- residency -----------------------------------------------------------------------
 def test_residency_is_content_addressed_and_bounded(monkeypatch, orc):
     from llama_rust_b200 import Executor
