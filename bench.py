@@ -581,6 +581,8 @@ def run_ours(args):
             prog.run(sptr)
             assert rt.cudaMemcpyAsync(hyb.data_ptr(), logits_dev, 4 * hyb.numel(), 2, sptr) == 0
             stream.synchronize()
+        barrier()  # rank 0 has just stopped its clock sampler: the ranks enter the exchange of the next launch together
+        ex.synchronize()  # raises if a bounded device-side wait gave up in anything above
         for _ in range(2):
             e2e_prog_step()
         barrier()

@@ -120,11 +120,23 @@ static_assert(Lay<DT_Q6_K, 1>::RS == Lay<DT_Q6_K, 1>::SEGB, "Q6_K rows lie dense
 __device__ __forceinline__ void mbar_arrive(uint64_t* b) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
 }
-// bounded wait; false when it gave up
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity) {
+// Bounded wait on a barrier of this CTA; false when it gave up.  Inside a program another warp of the CTA may itself
+// be waiting (bounded by the executor's poll limit) for another CTA or another GPU, and that wait can legitimately
+// outlast SPIN_LIMIT: with an abort word this wait therefore gives up when the run's abort word is raised (some wait
+// of the run ran out) and otherwise only after a hard bound far beyond any poll limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, const unsigned long long* abort_word = nullptr,
+                                          unsigned long long epoch = 0) {
   int spins = 0;
-  while (!mbar_try_wait(b, parity))
-    if (++spins > SPIN_LIMIT) return false;
+  while (!mbar_try_wait(b, parity)) {
+    ++spins;
+    if (!abort_word) {
+      if (spins > SPIN_LIMIT) return false;
+    } else if ((spins & 0xffff) == 0) {
+      unsigned long long a;
+      asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(a) : "l"(abort_word) : "memory");
+      if (a == epoch || spins > 256 * SPIN_LIMIT / 4) return false;
+    }
+  }
   return true;
 }
 // Q4_K stages lie [block][row][144 bytes]: rows 144 bytes apart are 16 bytes apart modulo
@@ -214,6 +226,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
   float* red = (float*)(smem + L::RED);
   uint64_t* full = (uint64_t*)(smem + L::BAR);
   uint64_t* empty = full + NST;
+  const unsigned long long* abort_word = PROGRAM && counters ? counters + ABORT_SLOT : nullptr;
   uint64_t* rfull = empty + NST;
   uint64_t* rempty = rfull + NRB;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -255,7 +268,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
             for (int tile = t0; tile < t1; ++tile) {
               for (int sub = 0; sub < nsub; ++sub, ++c) {
                 const int stage = c % NST;
-                if (ok && !mbar_wait(&empty[stage], (uint32_t)(((c / NST) & 1) ^ 1))) { ok = false; report_error(err, 1); }
+                if (ok && !mbar_wait(&empty[stage], (uint32_t)(((c / NST) & 1) ^ 1), abort_word, epoch)) { ok = false; report_error(err, 1); }
                 uint8_t* dst = ring + stage * MAX_CHUNK;
                 const int seg = span * (SPAN / gm.kseg) + sub;
                 if (gm.box_bytes) {
@@ -305,7 +318,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           for (int tile = t0; tile < t1; ++tile)
           for (int part = 0; part < n_part; ++part, ++j) {
             const int rb = j % NRB;
-            if (ok && !mbar_wait(&rfull[rb], (uint32_t)((j / NRB) & 1))) { ok = false; if (lane == 0) report_error(err, 1); }
+            if (ok && !mbar_wait(&rfull[rb], (uint32_t)((j / NRB) & 1), abort_word, epoch)) { ok = false; if (lane == 0) report_error(err, 1); }
             const float* rp0 = red + rb * CW * 16 * MT;
 #pragma unroll
             for (int slot = 0; slot < (16 * MT + 31) / 32; ++slot) {
@@ -525,7 +538,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           clear();
           for (int sub = 0; sub < nsub; ++sub, ++c) {
             const int stage = c % NST;
-            if (ok && !mbar_wait(&full[stage], (uint32_t)((c / NST) & 1))) { ok = false; if (lane == 0) report_error(err, 1); }
+            if (ok && !mbar_wait(&full[stage], (uint32_t)((c / NST) & 1), abort_word, epoch)) { ok = false; if (lane == 0) report_error(err, 1); }
             const uint8_t* chunk = ring + stage * MAX_CHUNK;
             const uint8_t* rowA = chunk + g * gm.rs;
             const uint8_t* rowB = chunk + (g + 8) * gm.rs;
@@ -564,7 +577,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
             if ((sub & part_mask) != part_mask && sub != nsub - 1) continue;
           // ---- hand this warp's partial sums of the part to the reducer ----
           const int rb = j % NRB;
-          if (ok && !mbar_wait(&rempty[rb], (uint32_t)(((j / NRB) & 1) ^ 1))) { ok = false; if (lane == 0) report_error(err, 1); }
+          if (ok && !mbar_wait(&rempty[rb], (uint32_t)(((j / NRB) & 1) ^ 1), abort_word, epoch)) { ok = false; if (lane == 0) report_error(err, 1); }
           float* myred = red + (rb * CW + warp) * 16 * MT;
           if ((DTFIX >= 0 ? DTFIX : E.dtype) == DT_Q4_K || DTFIX == DT_Q5_1) {
 #pragma unroll
