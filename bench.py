@@ -297,7 +297,7 @@ def config_legs(ex, stream, peak_hbm, peaks):
     return out
 
 
-def moe_leg(ex, group, rank, world, peak_hbm, sustained):
+def moe_leg(ex, group, rank, world, peak_hbm, sustained, token_counts=(64, 512)):
     """Routed-expert layer of BASELINE config 5 (8 experts, top-2, 4096 / 14336, Q4_K experts, F32 router) through
     the host-buffer entry point with pinned buffers: wall ms per layer call.  world > 1: experts striped e % world, tokens
     sharded, routed rows exchanged with all-to-all; every rank compares its tokens' outputs bit for bit with the
@@ -320,7 +320,7 @@ def moe_leg(ex, group, rank, world, peak_hbm, sustained):
                                                           [m if k else None for m, k in zip(up, keep)],
                                                           [m if k else None for m, k in zip(down, keep)], 2, True)
         layer = ExpertParallelLayer(n_exp, 2, route, experts, group=group)
-    for tokens in (64, 512):
+    for tokens in token_counts:
         xs = np.random.default_rng(tokens).standard_normal((tokens, d_model)).astype(np.float32)
         x = torch.from_numpy(xs).pin_memory().numpy()
         out = torch.empty(tokens, d_model).pin_memory().numpy()
@@ -712,7 +712,7 @@ def check_sharded(ex, sharded, offs, shape_of, xin, phase_of, M, world, rank, sp
 def run_case(args):
     """One small case for profiling (the full sweep holds 5 GB): prints one JSON line.
       --case gemv    --dtype D --rows R --cols C --m M --reps N --copies K [--path P]   device-pointer products round-robin over K matrices
-      --case moe     --tokens T --reps N                                               the routed-expert layer of BASELINE config 5
+      --case moe     --tokens T                                                        the routed-expert layer of BASELINE config 5 (2 warm-up + 5 timed calls)
       --case session --prompt P --gen G [--layers L]                                   the device-resident walk on an 8B-shaped model of L layers"""
     import torch
     from llama_rust_b200 import DTYPES, Executor, row_bytes as lib_row_bytes, synth
@@ -739,7 +739,7 @@ def run_case(args):
                "launches": ex.counters()["launches"]}
     elif args.case == "moe":
         peak, _ = load_peaks()
-        out = {"case": "moe", **moe_leg(ex, None, 0, 1, peak, 1354.7)}
+        out = {"case": "moe", **moe_leg(ex, None, 0, 1, peak, 1354.7, token_counts=(args.tokens,))}
     else:
         cfg = dict(n_layer=args.layers, n_embd=D_MODEL, n_head=32, n_head_kv=8, head_dim=128, n_ff=D_FF, n_vocab=VOCAB, n_ctx=args.prompt + args.gen + 8)
         from llama_rust_b200 import Session
