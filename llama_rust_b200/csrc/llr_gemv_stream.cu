@@ -57,19 +57,6 @@
 
 #define LLR_ARENA_HEADER_BYTES_INTERNAL 65536  // LLR_ARENA_HEADER_BYTES of the public header
 
-#ifdef LLR_TRACE
-// Debug build only: clock64 stamps of CTAs 0 and 150, [cta][phase][event].
-__device__ long long g_trace[2][1024][8];
-__device__ unsigned long long g_trace_all[304][132][4];  // [cta][phase][event 0 phase start, 2 dependency met, 4 consumer done, 5 published], globaltimer ns
-__device__ __forceinline__ unsigned long long gtimer() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define LLR_STAMP(ev) do { if (PROGRAM && lane == 0 && (warp == 0 || warp == CW + 1) && ph < 132) { \
-    if ((bid == 0 || bid == 150)) g_trace[bid != 0][ph][ev] = clock64(); \
-    if (bid < 304 && (ev == 0 || ev == 2 || ev == 4 || ev == 5)) g_trace_all[bid][ph][ev == 0 ? 0 : ev == 2 ? 1 : ev == 4 ? 2 : 3] = gtimer(); } } while (0)
-extern "C" int llr_debug_trace(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)); }
-extern "C" int llr_debug_trace_all(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_trace_all, sizeof(g_trace_all)); }
-#else
-#define LLR_STAMP(ev) do {} while (0)
-#endif
 
 namespace llr {
 namespace {
@@ -394,7 +381,6 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
             asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(counters + ph), "l"(1ull) : "memory");
         }
       }
-      LLR_STAMP(5);
     }
     if (HOSTOUT) {
       // this CTA's stores to host memory are performed; the CTA that counts last tells the host
@@ -440,12 +426,10 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
   static_assert(ENT_CACHE * sizeof(ProgEntry) == 32 * 16, "one 16-byte chunk per lane");
   if (PROGRAM && warp == 0) prefetch_phase(0, 0);
   for (int ph = 0; ph < wk.n_phases; ++ph) {
-    LLR_STAMP(0);
     if (PROGRAM) {
       if (warp == 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
       consumer_sync();  // publish the descriptor and the cached entries of this phase
     }
-    LLR_STAMP(1);
     const ProgPhase P = PROGRAM ? s_phase[ph & 1] : wk.phases[ph];
     // everybody is in phase ph now: the buffers of phase ph - 1 are free for phase ph + 1
     if (PROGRAM && warp == 0 && ph + 1 < wk.n_phases) prefetch_phase(ph + 1, P.first_entry + P.n_entries);
@@ -501,7 +485,6 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
             consumer_sync();
             waited = true;
           }
-          LLR_STAMP(2);
           // the planes a warp overwrites are the ones it alone reads (see split_activations)
           __syncwarp();
           // the 1/rms of the row belongs to the whole row: computed when its first span is split
@@ -517,7 +500,6 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           }
           dead = prepare_activations<MT, PEERS, FLOW>(src, E.cols, E.tokens, FLOW ? E.eps : 0.f, span, nblk256, need_rms, dig, sxf, xsi,
                                                 s_part, s_inv, WaitCtx{err, PROGRAM ? counters + ABORT_SLOT : nullptr, epoch, wk.poll_limit, dead});
-          LLR_STAMP(3);
           if (lane == 0) s_key[warp] = SplitKey{xkey, FLOW ? E.x2 : nullptr, E.cols, span, E.tokens, FLOW ? E.x_op : 0, ph, 0};
           __syncwarp();
         }
@@ -614,7 +596,6 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
         }
       }
     }
-    LLR_STAMP(4);
   }
 }
 

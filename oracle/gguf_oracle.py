@@ -4,7 +4,7 @@ Follows langtax/src/gguf.rs: `parse_gguf` (:714-806), `read_kv_value` (:925-950)
 (`GgmlType::from_i32` :165-204, `is_ggml_removed_type_id` :117-119, `layout` :248-283) and the block sizes of
 langtax/src/quant.rs:86-183.  Errors carry the name of the reference's GgufError variant (:338-370).
 
-Parity pin: the reference holds no byte-level golden GGUF file; its own tests build files with `write_gguf`
+Parity unpinned: the reference holds no byte-level golden GGUF file; its own tests build files with `write_gguf`
 (:640-712) and read them back.  The files of tests/gguf_files.py follow that writer's layout rule for rule (header,
 metadata, tensor table, payloads aligned to `general.alignment` relative to the aligned end of the table), and the
 hand-assembled image in tests/test_gguf_cpu.py pins the byte layout independently of both."""
