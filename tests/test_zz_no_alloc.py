@@ -41,6 +41,25 @@ def test_noalloc_gemm_matches_regular_entry_point_twice():
             # CPU reference is asserted in tests/test_gpu_gemm.py)
             assert torch.equal(y_new, y_ref), f"dtype {dtype} call {call}"
         m.free()
+    # the call path allocates nothing: free device memory is the same after two more calls of a new, larger shape
+    m = ex.synth(Q4_K, 512, 4096, 13)
+    x = torch.randn(300, 4096, device="cuda")
+    y = torch.empty(300, 512, device="cuda")
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    for _ in range(2):
+        assert L.llr_gemm_device_noalloc(ex._h, m._h, 300, x.data_ptr(), y.data_ptr(), None) == 0
+    ex.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0
+    m.free()
+    # columns that are not a multiple of 256 are rejected
+    odd = ex.synth(Q8_0, 128, 2048 + 32, 14)
+    xo = torch.zeros(64, 2048 + 32, device="cuda")
+    yo = torch.full((64, 128), 7.0, device="cuda")
+    assert L.llr_gemm_device_noalloc(ex._h, odd._h, 64, xo.data_ptr(), yo.data_ptr(), None) == 1
+    ex.synchronize()
+    assert bool((yo == 7.0).all())
+    odd.free()
     # beyond the built-in staging area: a clear error, nothing launched, output untouched
     big = ex.synth(Q4_K, 128, 16384, 5)
     tokens = 1100  # 1100 * 16384 * 2 = 36 MB > 32 MiB
