@@ -26,15 +26,24 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   return v;
 }
 
-// eight consecutive weights starting at element index c of the row
-template <int DT> __device__ __forceinline__ void load8(const uint8_t* row, int64_t c, float (&w)[8]) {
+// The raw 16-byte pieces that hold eight consecutive weights starting at element index c of the row: kept as they
+// come (32 bytes for F32, 16 for the 2-byte formats) and widened only when they are used, so that the pieces in
+// flight cost a quarter of the registers their f32 values would and four CTAs fit an SM.
+template <int DT> struct Raw8 { uint4 a, b; };
+template <int DT> __device__ __forceinline__ void fetch8(const uint8_t* row, int64_t c, Raw8<DT>& r) {
   if constexpr (DT == DT_F32) {
-    const uint4 a = ld_stream16(row + 4 * c), b = ld_stream16(row + 4 * c + 16);
-    w[0] = __uint_as_float(a.x); w[1] = __uint_as_float(a.y); w[2] = __uint_as_float(a.z); w[3] = __uint_as_float(a.w);
-    w[4] = __uint_as_float(b.x); w[5] = __uint_as_float(b.y); w[6] = __uint_as_float(b.z); w[7] = __uint_as_float(b.w);
+    r.a = ld_stream16(row + 4 * c);
+    r.b = ld_stream16(row + 4 * c + 16);
   } else {
-    const uint4 v = ld_stream16(row + 2 * c);
-    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    r.a = ld_stream16(row + 2 * c);
+  }
+}
+template <int DT> __device__ __forceinline__ void widen8(const Raw8<DT>& r, float (&w)[8]) {
+  if constexpr (DT == DT_F32) {
+    w[0] = __uint_as_float(r.a.x); w[1] = __uint_as_float(r.a.y); w[2] = __uint_as_float(r.a.z); w[3] = __uint_as_float(r.a.w);
+    w[4] = __uint_as_float(r.b.x); w[5] = __uint_as_float(r.b.y); w[6] = __uint_as_float(r.b.z); w[7] = __uint_as_float(r.b.w);
+  } else {
+    const uint32_t u[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       if constexpr (DT == DT_F16) {
@@ -50,7 +59,7 @@ template <int DT> __device__ __forceinline__ void load8(const uint8_t* row, int6
 }
 
 template <int DT, int MT>
-__global__ void __launch_bounds__(ROW_WARPS * 32)
+__global__ void __launch_bounds__(ROW_WARPS * 32, (DT == DT_F32 || MT > 2) ? 2 : 4)
 gemv_rows_kernel(const uint8_t* __restrict__ W, int64_t row_bytes, int64_t rows, int64_t cols,
                  const float* __restrict__ X, float* __restrict__ Y, int tokens) {
   const int lane = threadIdx.x & 31;
@@ -63,22 +72,24 @@ gemv_rows_kernel(const uint8_t* __restrict__ W, int64_t row_bytes, int64_t rows,
     for (int t = 0; t < MT; ++t) acc[t] = 0.f;
     constexpr int UNROLL = Unroll<DT>::N;
     for (int64_t c0 = 8 * lane; c0 < cols; c0 += 256 * UNROLL) {
-      float w[UNROLL][8];
+      Raw8<DT> raw[UNROLL];
 #pragma unroll
       for (int i = 0; i < UNROLL; ++i)
-        if (c0 + 256 * i < cols) load8<DT>(wr, c0 + 256 * i, w[i]);
+        if (c0 + 256 * i < cols) fetch8<DT>(wr, c0 + 256 * i, raw[i]);
 #pragma unroll
       for (int i = 0; i < UNROLL; ++i) {
         const int64_t c = c0 + 256 * i;
         if (c < cols) {
+          float w[8];
+          widen8<DT>(raw[i], w);
 #pragma unroll
           for (int t = 0; t < MT; ++t)
             if (t < tokens) {
               const float4* xp = (const float4*)(X + (int64_t)t * cols + c);
               const float4 a = __ldg(xp), b = __ldg(xp + 1);
               float s = acc[t];
-              s = fmaf(w[i][0], a.x, s); s = fmaf(w[i][1], a.y, s); s = fmaf(w[i][2], a.z, s); s = fmaf(w[i][3], a.w, s);
-              s = fmaf(w[i][4], b.x, s); s = fmaf(w[i][5], b.y, s); s = fmaf(w[i][6], b.z, s); s = fmaf(w[i][7], b.w, s);
+              s = fmaf(w[0], a.x, s); s = fmaf(w[1], a.y, s); s = fmaf(w[2], a.z, s); s = fmaf(w[3], a.w, s);
+              s = fmaf(w[4], b.x, s); s = fmaf(w[5], b.y, s); s = fmaf(w[6], b.z, s); s = fmaf(w[7], b.w, s);
               acc[t] = s;
             }
         }
@@ -97,7 +108,7 @@ gemv_rows_kernel(const uint8_t* __restrict__ W, int64_t row_bytes, int64_t rows,
 template <int DT, int MT>
 cudaError_t launch_rows(const MatView& m, const float* x, float* y, int tokens, cudaStream_t stream, int sm_count) {
   int64_t grid = (m.rows + ROW_WARPS - 1) / ROW_WARPS;
-  const int64_t cap = (int64_t)sm_count * 8;  // eight CTAs of 256 threads per SM
+  const int64_t cap = (int64_t)sm_count * 8;  // two waves of the four CTAs of 256 threads an SM holds
   if (grid > cap) grid = cap;
   gemv_rows_kernel<DT, MT><<<(unsigned)grid, ROW_WARPS * 32, 0, stream>>>(m.w, m.row_bytes, m.rows, m.cols, x, y, tokens);
   return cudaGetLastError();

@@ -308,7 +308,7 @@ __device__ __forceinline__ void block_q80_par(const uint8_t* pA, const uint8_t* 
     wB = make_uint2(__funnelshift_r(b0, b1, 16), __funnelshift_r(b1, b2, 16));
   }
   const float dA = h2f(*(const uint16_t*)pA), dB = h2f(*(const uint16_t*)pB);
-  const float pw0 = (t & 1) ? 65536.f : 1.f, pw1 = pw0 * 256.f;
+  const float pw0 = (t & 1) ? 65536.f : 1.f;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const uint2 bd = *(const uint2*)(plane_of<MT>(dig, nt, g) + c32 * 32 + 8 * t);
@@ -316,10 +316,10 @@ __device__ __forceinline__ void block_q80_par(const uint8_t* pA, const uint8_t* 
     mma_k32(c, wA.x, wB.x, wA.y, wB.y, bd.x, bd.y);
     const int tok = 2 * nt + (t >> 1);
     const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + (c32 >> 3)] : 0.f;
-    acc.y[nt][0] = fmaf((float)c[0], dA * xs * pw0, acc.y[nt][0]);
-    acc.y[nt][1] = fmaf((float)c[1], dA * xs * pw1, acc.y[nt][1]);
-    acc.y[nt][2] = fmaf((float)c[2], dB * xs * pw0, acc.y[nt][2]);
-    acc.y[nt][3] = fmaf((float)c[3], dB * xs * pw1, acc.y[nt][3]);
+    // the two digits a thread holds are joined as integers (|sum| < 2^20 each, so c0 + 256 c1 fits 32 bits): one
+    // conversion and one FMA per row instead of two; the conversion rounds to 24 bits, relative 2^-25 of the pair
+    acc.y[nt][0] = fmaf((float)(c[0] + 256 * c[1]), dA * xs * pw0, acc.y[nt][0]);
+    acc.y[nt][2] = fmaf((float)(c[2] + 256 * c[3]), dB * xs * pw0, acc.y[nt][2]);
   }
 }
 // block b of the row pieces rowA / rowB (row pieces start 16-byte aligned)
@@ -350,7 +350,7 @@ __device__ __forceinline__ void block_q40_par(const uint8_t* pA, const uint8_t* 
   constexpr uint32_t MH = 0xf0f0f0f0u, SG = 0x80808080u;
   const uint32_t a0 = ((wA << 4) & MH) ^ SG, a2 = (wA & MH) ^ SG, a1 = ((wB << 4) & MH) ^ SG, a3 = (wB & MH) ^ SG;
   const float dA = h2f(*(const uint16_t*)pA), dB = h2f(*(const uint16_t*)pB);
-  const float pw0 = (t & 1) ? 4096.f : 0.0625f, pw1 = pw0 * 256.f;  // 256^digit / 16
+  const float pw0 = (t & 1) ? 4096.f : 0.0625f;  // 256^digit / 16
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const uint8_t* dp = plane_of<MT>(dig, nt, g) + c32 * 32 + 4 * t;
@@ -358,10 +358,10 @@ __device__ __forceinline__ void block_q40_par(const uint8_t* pA, const uint8_t* 
     mma_k32(c, a0, a1, a2, a3, *(const uint32_t*)dp, *(const uint32_t*)(dp + 16));
     const int tok = 2 * nt + (t >> 1);
     const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + (c32 >> 3)] : 0.f;
-    acc.y[nt][0] = fmaf((float)c[0], dA * xs * pw0, acc.y[nt][0]);
-    acc.y[nt][1] = fmaf((float)c[1], dA * xs * pw1, acc.y[nt][1]);
-    acc.y[nt][2] = fmaf((float)c[2], dB * xs * pw0, acc.y[nt][2]);
-    acc.y[nt][3] = fmaf((float)c[3], dB * xs * pw1, acc.y[nt][3]);
+    // the two digits a thread holds are joined as integers (|sum| < 2^20 each, so c0 + 256 c1 fits 32 bits): one
+    // conversion and one FMA per row instead of two; the conversion rounds to 24 bits, relative 2^-25 of the pair
+    acc.y[nt][0] = fmaf((float)(c[0] + 256 * c[1]), dA * xs * pw0, acc.y[nt][0]);
+    acc.y[nt][2] = fmaf((float)(c[2] + 256 * c[3]), dB * xs * pw0, acc.y[nt][2]);
   }
 }
 template <int MT>
@@ -395,7 +395,7 @@ __device__ __forceinline__ void block_q5_par(const uint8_t* pA, const uint8_t* p
     a3 = (((wB >> 1) & M5) | (spread4(hB >> (16 + 4 * t)) << 7)) ^ SG;
   }
   const float dA = h2f(*(const uint16_t*)pA), dB = h2f(*(const uint16_t*)pB);
-  const float pw0 = Q51 ? ((t & 1) ? 65536.f : 1.f) : ((t & 1) ? 8192.f : 0.125f), pw1 = pw0 * 256.f;
+  const float pw0 = Q51 ? ((t & 1) ? 65536.f : 1.f) : ((t & 1) ? 8192.f : 0.125f);
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const uint8_t* dp = plane_of<MT>(dig, nt, g) + c32 * 32 + 4 * t;
@@ -404,10 +404,10 @@ __device__ __forceinline__ void block_q5_par(const uint8_t* pA, const uint8_t* p
     else mma_k32(c, a0, a1, a2, a3, *(const uint32_t*)dp, *(const uint32_t*)(dp + 16));
     const int tok = 2 * nt + (t >> 1);
     const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + (c32 >> 3)] : 0.f;
-    acc.y[nt][0] = fmaf((float)c[0], dA * xs * pw0, acc.y[nt][0]);
-    acc.y[nt][1] = fmaf((float)c[1], dA * xs * pw1, acc.y[nt][1]);
-    acc.y[nt][2] = fmaf((float)c[2], dB * xs * pw0, acc.y[nt][2]);
-    acc.y[nt][3] = fmaf((float)c[3], dB * xs * pw1, acc.y[nt][3]);
+    // the two digits a thread holds are joined as integers (|sum| < 2^20 each, so c0 + 256 c1 fits 32 bits): one
+    // conversion and one FMA per row instead of two; the conversion rounds to 24 bits, relative 2^-25 of the pair
+    acc.y[nt][0] = fmaf((float)(c[0] + 256 * c[1]), dA * xs * pw0, acc.y[nt][0]);
+    acc.y[nt][2] = fmaf((float)(c[2] + 256 * c[3]), dB * xs * pw0, acc.y[nt][2]);
   }
   if (Q51 && t == (c32 & 3)) {
     // the offset: m * sum of the block's activations, kept negative so that the tile's `sum - mn` adds it; one of the
