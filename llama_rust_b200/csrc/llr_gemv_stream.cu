@@ -534,25 +534,37 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
               for (int b = warp; b < (seg_cols >> 8); b += CW)
                 block_q6k<MT>(rowA, rowB, b, sub * (gm.kseg / 256) + b, dig, xsi, g, t, acc);
             } else if (DTFIX == DT_Q4_0) {  // the nibble formats run as single products only (never inside programs)
-              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW)
-#pragma unroll 2
+              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
+                float xw[NT];
+                group_scales<MT>(xsi, sub * (gm.kseg / 256) + b8, t, (t & 1) ? 4096.f : 0.0625f, xw);
+#pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  block_q40<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, xsi, g, t, acc);
+                  block_q40<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, xw, g, t, acc);
+              }
             } else if (DTFIX == DT_Q5_0) {
-              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW)
-#pragma unroll 2
+              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
+                float xw[NT];
+                group_scales<MT>(xsi, sub * (gm.kseg / 256) + b8, t, (t & 1) ? 8192.f : 0.125f, xw);
+#pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  block_q50<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xsi, g, t, acc);
+                  block_q50<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xw, g, t, acc);
+              }
             } else if (DTFIX == DT_Q5_1) {
-              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW)
-#pragma unroll 2
+              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
+                float xw[NT];
+                group_scales<MT>(xsi, sub * (gm.kseg / 256) + b8, t, (t & 1) ? 65536.f : 1.f, xw);
+#pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  block_q51<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xsi, g, t, acc);
+                  block_q51<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xw, g, t, acc);
+              }
             } else {
-              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW)  // the eight blocks of 256 columns b8
-#pragma unroll 2
+              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
+                float xw[NT];
+                group_scales<MT>(xsi, sub * (gm.kseg / 256) + b8, t, (t & 1) ? 65536.f : 1.f, xw);
+#pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  block_q80<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, xsi, g, t, acc);
+                  block_q80<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, xw, g, t, acc);
+              }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[stage]);  // this warp no longer reads the stage

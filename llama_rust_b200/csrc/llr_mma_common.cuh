@@ -290,11 +290,23 @@ __device__ __forceinline__ void block_q6k(const uint8_t* rowA, const uint8_t* ro
   else block_q6k_par<MT, false>(rowA + b * 210, rowB + b * 210, cb, dig, xsi, g, t, acc);
 }
 
+// For the 32-column formats: per pair of activation rows, the scale of this thread's row in the 256-column group c256
+// times `pw`, the weight of the lower of the two digits the thread holds (a power of two, so the order of the
+// products does not matter).  Computed once per group of eight blocks.
+template <int MT>
+__device__ __forceinline__ void group_scales(const float* xsi, int c256, int t, float pw, float (&xw)[(MT + 1) / 2]) {
+#pragma unroll
+  for (int nt = 0; nt < (MT + 1) / 2; ++nt) {
+    const int tok = 2 * nt + (t >> 1);
+    xw[nt] = (tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + c256] : 0.f) * pw;
+  }
+}
+
 // One Q8_0 block (32 columns): the int8 quants are the A fragment as they lie.  Blocks are 34
 // bytes long: the quants of an even block start 2 bytes off a word boundary (OFF).
 template <int MT, bool OFF>
 __device__ __forceinline__ void block_q80_par(const uint8_t* pA, const uint8_t* pB, int c32,
-                                              const uint8_t* dig, const float* xsi, int g, int t,
+                                              const uint8_t* dig, const float (&xw)[(MT + 1) / 2], int g, int t,
                                               Acc<DT_Q8_0, MT>& acc) {
   constexpr int NT = (MT + 1) / 2;
   uint2 wA, wB;
@@ -308,27 +320,24 @@ __device__ __forceinline__ void block_q80_par(const uint8_t* pA, const uint8_t* 
     wB = make_uint2(__funnelshift_r(b0, b1, 16), __funnelshift_r(b1, b2, 16));
   }
   const float dA = h2f(*(const uint16_t*)pA), dB = h2f(*(const uint16_t*)pB);
-  const float pw0 = (t & 1) ? 65536.f : 1.f;
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const uint2 bd = *(const uint2*)(plane_of<MT>(dig, nt, g) + c32 * 32 + 8 * t);
     int c[4];
     mma_k32(c, wA.x, wB.x, wA.y, wB.y, bd.x, bd.y);
-    const int tok = 2 * nt + (t >> 1);
-    const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + (c32 >> 3)] : 0.f;
     // the two digits a thread holds are joined as integers (|sum| < 2^20 each, so c0 + 256 c1 fits 32 bits): one
     // conversion and one FMA per row instead of two; the conversion rounds to 24 bits, relative 2^-25 of the pair
-    acc.y[nt][0] = fmaf((float)(c[0] + 256 * c[1]), dA * xs * pw0, acc.y[nt][0]);
-    acc.y[nt][2] = fmaf((float)(c[2] + 256 * c[3]), dB * xs * pw0, acc.y[nt][2]);
+    acc.y[nt][0] = fmaf((float)(c[0] + 256 * c[1]), dA * xw[nt], acc.y[nt][0]);
+    acc.y[nt][2] = fmaf((float)(c[2] + 256 * c[3]), dB * xw[nt], acc.y[nt][2]);
   }
 }
 // block b of the row pieces rowA / rowB (row pieces start 16-byte aligned)
 template <int MT>
 __device__ __forceinline__ void block_q80(const uint8_t* rowA, const uint8_t* rowB, int b, int c32,
-                                          const uint8_t* dig, const float* xsi, int g, int t,
+                                          const uint8_t* dig, const float (&xw)[(MT + 1) / 2], int g, int t,
                                           Acc<DT_Q8_0, MT>& acc) {
-  if (b & 1) block_q80_par<MT, false>(rowA + b * 34, rowB + b * 34, c32, dig, xsi, g, t, acc);
-  else block_q80_par<MT, true>(rowA + b * 34, rowB + b * 34, c32, dig, xsi, g, t, acc);
+  if (b & 1) block_q80_par<MT, false>(rowA + b * 34, rowB + b * 34, c32, dig, xw, g, t, acc);
+  else block_q80_par<MT, true>(rowA + b * 34, rowB + b * 34, c32, dig, xw, g, t, acc);
 }
 
 
@@ -344,38 +353,35 @@ __device__ __forceinline__ uint32_t spread4(uint32_t x) { return ((x & 15u) * 0x
 
 template <int MT, bool ODD>
 __device__ __forceinline__ void block_q40_par(const uint8_t* pA, const uint8_t* pB, int c32, const uint8_t* dig,
-                                              const float* xsi, int g, int t, AccT<MT>& acc) {
+                                              const float (&xw)[(MT + 1) / 2], int g, int t, AccT<MT>& acc) {
   constexpr int NT = (MT + 1) / 2;
   const uint32_t wA = lds32_par<ODD>(pA + 2 + 4 * t), wB = lds32_par<ODD>(pB + 2 + 4 * t);
   constexpr uint32_t MH = 0xf0f0f0f0u, SG = 0x80808080u;
   const uint32_t a0 = ((wA << 4) & MH) ^ SG, a2 = (wA & MH) ^ SG, a1 = ((wB << 4) & MH) ^ SG, a3 = (wB & MH) ^ SG;
   const float dA = h2f(*(const uint16_t*)pA), dB = h2f(*(const uint16_t*)pB);
-  const float pw0 = (t & 1) ? 4096.f : 0.0625f;  // 256^digit / 16
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const uint8_t* dp = plane_of<MT>(dig, nt, g) + c32 * 32 + 4 * t;
     int c[4];
     mma_k32(c, a0, a1, a2, a3, *(const uint32_t*)dp, *(const uint32_t*)(dp + 16));
-    const int tok = 2 * nt + (t >> 1);
-    const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + (c32 >> 3)] : 0.f;
     // the two digits a thread holds are joined as integers (|sum| < 2^20 each, so c0 + 256 c1 fits 32 bits): one
     // conversion and one FMA per row instead of two; the conversion rounds to 24 bits, relative 2^-25 of the pair
-    acc.y[nt][0] = fmaf((float)(c[0] + 256 * c[1]), dA * xs * pw0, acc.y[nt][0]);
-    acc.y[nt][2] = fmaf((float)(c[2] + 256 * c[3]), dB * xs * pw0, acc.y[nt][2]);
+    acc.y[nt][0] = fmaf((float)(c[0] + 256 * c[1]), dA * xw[nt], acc.y[nt][0]);
+    acc.y[nt][2] = fmaf((float)(c[2] + 256 * c[3]), dB * xw[nt], acc.y[nt][2]);
   }
 }
 template <int MT>
 __device__ __forceinline__ void block_q40(const uint8_t* rowA, const uint8_t* rowB, int b, int c32, const uint8_t* dig,
-                                          const float* xsi, int g, int t, AccT<MT>& acc) {
+                                          const float (&xw)[(MT + 1) / 2], int g, int t, AccT<MT>& acc) {
   // 18-byte blocks in a 16-byte aligned row piece: the quants of an even block start 2 bytes off a word boundary
-  if (b & 1) block_q40_par<MT, false>(rowA + b * 18, rowB + b * 18, c32, dig, xsi, g, t, acc);
-  else block_q40_par<MT, true>(rowA + b * 18, rowB + b * 18, c32, dig, xsi, g, t, acc);
+  if (b & 1) block_q40_par<MT, false>(rowA + b * 18, rowB + b * 18, c32, dig, xw, g, t, acc);
+  else block_q40_par<MT, true>(rowA + b * 18, rowB + b * 18, c32, dig, xw, g, t, acc);
 }
 
 // HDR: bytes before the fifth-bit mask (2: Q5_0, 4: Q5_1)
 template <int MT, bool ODD, bool Q51>
 __device__ __forceinline__ void block_q5_par(const uint8_t* pA, const uint8_t* pB, int c32, const uint8_t* dig,
-                                             const float* sxf, const float* xsi, int g, int t, AccT<MT>& acc) {
+                                             const float* sxf, const float (&xw)[(MT + 1) / 2], int g, int t, AccT<MT>& acc) {
   constexpr int NT = (MT + 1) / 2;
   constexpr int HDR = Q51 ? 4 : 2;
   const uint32_t hA = lds32_par<ODD>(pA + HDR), hB = lds32_par<ODD>(pB + HDR);
@@ -395,19 +401,16 @@ __device__ __forceinline__ void block_q5_par(const uint8_t* pA, const uint8_t* p
     a3 = (((wB >> 1) & M5) | (spread4(hB >> (16 + 4 * t)) << 7)) ^ SG;
   }
   const float dA = h2f(*(const uint16_t*)pA), dB = h2f(*(const uint16_t*)pB);
-  const float pw0 = Q51 ? ((t & 1) ? 65536.f : 1.f) : ((t & 1) ? 8192.f : 0.125f);
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const uint8_t* dp = plane_of<MT>(dig, nt, g) + c32 * 32 + 4 * t;
     int c[4];
     if (Q51) mma_k32_us(c, a0, a1, a2, a3, *(const uint32_t*)dp, *(const uint32_t*)(dp + 16));
     else mma_k32(c, a0, a1, a2, a3, *(const uint32_t*)dp, *(const uint32_t*)(dp + 16));
-    const int tok = 2 * nt + (t >> 1);
-    const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + (c32 >> 3)] : 0.f;
     // the two digits a thread holds are joined as integers (|sum| < 2^20 each, so c0 + 256 c1 fits 32 bits): one
     // conversion and one FMA per row instead of two; the conversion rounds to 24 bits, relative 2^-25 of the pair
-    acc.y[nt][0] = fmaf((float)(c[0] + 256 * c[1]), dA * xs * pw0, acc.y[nt][0]);
-    acc.y[nt][2] = fmaf((float)(c[2] + 256 * c[3]), dB * xs * pw0, acc.y[nt][2]);
+    acc.y[nt][0] = fmaf((float)(c[0] + 256 * c[1]), dA * xw[nt], acc.y[nt][0]);
+    acc.y[nt][2] = fmaf((float)(c[2] + 256 * c[3]), dB * xw[nt], acc.y[nt][2]);
   }
   if (Q51 && t == (c32 & 3)) {
     // the offset: m * sum of the block's activations, kept negative so that the tile's `sum - mn` adds it; one of the
@@ -423,14 +426,14 @@ __device__ __forceinline__ void block_q5_par(const uint8_t* pA, const uint8_t* p
 }
 template <int MT>
 __device__ __forceinline__ void block_q50(const uint8_t* rowA, const uint8_t* rowB, int b, int c32, const uint8_t* dig,
-                                          const float* sxf, const float* xsi, int g, int t, AccT<MT>& acc) {
-  if (b & 1) block_q5_par<MT, false, false>(rowA + b * 22, rowB + b * 22, c32, dig, sxf, xsi, g, t, acc);
-  else block_q5_par<MT, true, false>(rowA + b * 22, rowB + b * 22, c32, dig, sxf, xsi, g, t, acc);
+                                          const float* sxf, const float (&xw)[(MT + 1) / 2], int g, int t, AccT<MT>& acc) {
+  if (b & 1) block_q5_par<MT, false, false>(rowA + b * 22, rowB + b * 22, c32, dig, sxf, xw, g, t, acc);
+  else block_q5_par<MT, true, false>(rowA + b * 22, rowB + b * 22, c32, dig, sxf, xw, g, t, acc);
 }
 template <int MT>
 __device__ __forceinline__ void block_q51(const uint8_t* rowA, const uint8_t* rowB, int b, int c32, const uint8_t* dig,
-                                          const float* sxf, const float* xsi, int g, int t, AccT<MT>& acc) {
-  block_q5_par<MT, false, true>(rowA + b * 24, rowB + b * 24, c32, dig, sxf, xsi, g, t, acc);  // 24-byte blocks stay word aligned
+                                          const float* sxf, const float (&xw)[(MT + 1) / 2], int g, int t, AccT<MT>& acc) {
+  block_q5_par<MT, false, true>(rowA + b * 24, rowB + b * 24, c32, dig, sxf, xw, g, t, acc);  // 24-byte blocks stay word aligned
 }
 
 // ---- where activations come from ---------------------------------------------------------
