@@ -149,34 +149,41 @@ rope_store_kernel(float* __restrict__ q, float* __restrict__ k, const float* __r
   }
 }
 
-// Attention of one token: grid (kv head, position slice, token).  A block handles the query heads that share its kv
-// head over its slice of the positions and writes, per query head, the slice's maximum score, the sum of exp(score -
-// max) and the exp-weighted sum of value rows; attention_combine_kernel merges the slices (the usual two-pass softmax,
-// rearranged so that K and V are read once per kv head and by many SMs).  Slices have a fixed length in positions
-// (attention_chunk), whatever the batch: a row's result depends on its own sequence only, never on what shares its batch.
+// Attention of one row over one slice of positions.  A block handles the query heads that share a kv head and
+// writes, per query head, the slice's maximum score, the sum of exp(score - max) and the exp-weighted sum of value
+// rows; attention_combine_kernel merges the slices (the usual two-pass softmax, rearranged so that K and V are read
+// once per kv head and by many SMs).  Slices have a fixed length in positions (attention_chunk), whatever the batch: a
+// row's result depends on its own sequence only, never on what shares its batch.
+// `KV` says where the key and value rows of a position lie: in the paged cache (one row per block: decode steps) or
+// in a shared-memory tile that a block fills once for many rows of a prompt chunk.  The arithmetic is this one
+// function either way, so both kernels give the same bits.
 constexpr int ATT_THREADS = 256;
 constexpr int ATT_MAX_GQA = 8;
-__global__ void __launch_bounds__(ATT_THREADS)
-attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restrict__ part, RowMap rows, int layer, int chunk,
-                         WalkShape w) {
-  pdl_enter();
-  extern __shared__ float sm[];  // q[gqa][hd] | scores[gqa][chunk] | red[32]
-  const int hkv = blockIdx.x, split = blockIdx.y, t = blockIdx.z;
-  const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
-  const int seq = row_position(rows, t) + 1;  // positions this row attends to
-  const int sid = row_sequence(rows, t);
-  const int n_split = (int)gridDim.y;
-  const int s0 = split * chunk, s1 = min(seq, s0 + chunk);
-  if (s0 >= seq) return;  // this row's sequence ends before the slice
-  const int max_chunk = chunk;
-  float* sq = sm;
-  float* sc = sq + gqa * hd;
-  float* red = sc + gqa * max_chunk;
+constexpr int ATT_ROWS = 16;       // rows per block of the tiled kernel
+constexpr int ATT_TILE_CHUNK = 64; // longest slice the tiled kernel stages (2 x 64 x head_dim floats)
+
+struct KvGlobal {
+  const KvView& kv;
+  int sid, layer, hkv, n_head_kv, hd;
+  __device__ __forceinline__ const float* k(int s) const { return kv.k + kv_offset(kv, sid, layer, hkv, s, n_head_kv, hd); }
+  __device__ __forceinline__ const float* v(int s) const { return kv.v + kv_offset(kv, sid, layer, hkv, s, n_head_kv, hd); }
+};
+struct KvTile {
+  const float* kt;
+  const float* vt;
+  int s0, hd;
+  __device__ __forceinline__ const float* k(int s) const { return kt + (s - s0) * hd; }
+  __device__ __forceinline__ const float* v(int s) const { return vt + (s - s0) * hd; }
+};
+
+// sq: the row's query heads of this kv head [gqa][hd] in shared memory (filled and synchronized by the caller);
+// sc: [max(gqa * max_chunk, P * gqa * hd)] floats of shared memory; out: the slice's record of this row.
+// Ends with the block's threads past their last read of sq and sc only after the caller's next __syncthreads().
+template <typename KV>
+__device__ __forceinline__ void attend_slice(const KV& src, const float* sq, float* sc, float* out, int s0, int s1, int max_chunk,
+                                             int hd, int gqa) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = ATT_THREADS / 32;
   const float scale = 1.0f / sqrtf((float)hd);
-  for (int i = threadIdx.x; i < gqa * hd; i += ATT_THREADS)
-    sq[i] = q[((int64_t)t * w.n_head + hkv * gqa) * hd + i];
-  __syncthreads();
   // scores: one warp per position, all query heads of the group against one read of the K row.  Four positions are in
   // flight per warp (their K rows are fetched before any of them is used): the loop is bound by memory latency, not
   // by arithmetic.  Each position's sum is formed exactly as if it were alone: columns in ascending order per lane.
@@ -187,7 +194,7 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
 #pragma unroll
     for (int j = 0; j < SP; ++j) {
       const int sj = sbase + j * nw;
-      krow[j] = sj < s1 ? kv.k + kv_offset(kv, sid, layer, hkv, sj, w.n_head_kv, hd) : nullptr;
+      krow[j] = sj < s1 ? src.k(sj) : nullptr;
 #pragma unroll
       for (int g = 0; g < ATT_MAX_GQA; ++g) acc[j][g] = 0.f;
     }
@@ -226,7 +233,6 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
     }
   }
   __syncthreads();
-  float* out = part + (((int64_t)t * w.n_head_kv + hkv) * n_split + split) * gqa * (hd + 2);
   // per query head: the slice's maximum and the sum of exp(score - max); one warp per head, lanes add in a fixed tree
   for (int g = warp; g < gqa; g += nw) {
     float m = -CUDART_INF_F;
@@ -255,8 +261,7 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
     for (int sb = s0 + 8 * grp; sb < s1; sb += 8 * P) {
       float vv[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        vv[j] = sb + j < s1 ? kv.v[kv_offset(kv, sid, layer, hkv, sb + j, w.n_head_kv, hd) + i] : 0.f;
+      for (int j = 0; j < 8; ++j) vv[j] = sb + j < s1 ? src.v(sb + j)[i] : 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         if (sb + j < s1) {
@@ -267,7 +272,7 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
     }
   }
   __syncthreads();  // the scores are no longer needed: their space takes the groups' partial sums
-  float* vsum = sc;  // [P][gqa][hd], fits: P * hd <= ATT_THREADS and gqa * max_chunk >= ... checked at launch
+  float* vsum = sc;  // [P][gqa][hd]
   if (grp < P)
 #pragma unroll
     for (int g = 0; g < ATT_MAX_GQA; ++g)
@@ -277,6 +282,172 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
     float v = 0.f;
     for (int p = 0; p < P; ++p) v += vsum[p * gqa * hd + idx];
     out[(idx / hd) * (hd + 2) + idx % hd] = v;
+  }
+}
+
+// grid (kv head, position slice, token): one row per block, K and V straight from the paged cache (decode steps)
+__global__ void __launch_bounds__(ATT_THREADS)
+attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restrict__ part, RowMap rows, int layer, int chunk,
+                         WalkShape w) {
+  pdl_enter();
+  extern __shared__ float sm[];  // q[gqa][hd] | scores[gqa][chunk] or sums[P][gqa][hd]
+  const int hkv = blockIdx.x, split = blockIdx.y, t = blockIdx.z;
+  const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
+  const int seq = row_position(rows, t) + 1;  // positions this row attends to
+  const int sid = row_sequence(rows, t);
+  const int n_split = (int)gridDim.y;
+  const int s0 = split * chunk, s1 = min(seq, s0 + chunk);
+  if (s0 >= seq) return;  // this row's sequence ends before the slice
+  float* sq = sm;
+  float* sc = sq + gqa * hd;
+  for (int i = threadIdx.x; i < gqa * hd; i += ATT_THREADS)
+    sq[i] = q[((int64_t)t * w.n_head + hkv * gqa) * hd + i];
+  __syncthreads();
+  float* out = part + (((int64_t)t * w.n_head_kv + hkv) * n_split + split) * gqa * (hd + 2);
+  attend_slice(KvGlobal{kv, sid, layer, hkv, w.n_head_kv, hd}, sq, sc, out, s0, s1, chunk, hd, gqa);
+}
+
+// The same slice of one row done by ONE warp, every elementary sum formed in the order attend_slice forms it (a
+// position's score: lanes over the columns, four per lane in ascending order, then the shuffle tree; a head's
+// softmax: lanes over the positions; a dimension's weighted sum: per group of runs of eight positions in ascending
+// order, then the groups in order), so the bits are the same.  sq [gqa][hd] and sc [gqa][max_chunk] are this warp's.
+template <typename KV>
+__device__ __forceinline__ void attend_slice_warp(const KV& src, const float* sq, float* sc, float* out, int s0, int s1, int max_chunk,
+                                                  int hd, int gqa) {
+  const int lane = threadIdx.x & 31;
+  const float scale = 1.0f / sqrtf((float)hd);
+  constexpr int SP = 4;
+  for (int sbase = s0; sbase < s1; sbase += SP) {
+    float acc[SP][ATT_MAX_GQA];
+    const float* krow[SP];
+#pragma unroll
+    for (int j = 0; j < SP; ++j) {
+      krow[j] = sbase + j < s1 ? src.k(sbase + j) : nullptr;
+#pragma unroll
+      for (int g = 0; g < ATT_MAX_GQA; ++g) acc[j][g] = 0.f;
+    }
+    for (int i0 = 0; i0 < hd; i0 += 128) {
+      float kvv[SP][4];
+#pragma unroll
+      for (int j = 0; j < SP; ++j)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + lane + 32 * u;
+          kvv[j][u] = (krow[j] && i < hd) ? krow[j][i] : 0.f;
+        }
+#pragma unroll
+      for (int j = 0; j < SP; ++j)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + lane + 32 * u;
+          if (krow[j] && i < hd) {
+#pragma unroll
+            for (int g = 0; g < ATT_MAX_GQA; ++g)
+              if (g < gqa) acc[j][g] = fmaf(sq[g * hd + i], kvv[j][u], acc[j][g]);
+          }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < SP; ++j)
+      if (sbase + j < s1) {
+#pragma unroll
+        for (int g = 0; g < ATT_MAX_GQA; ++g)
+          if (g < gqa) {
+            const float d = warp_sum(acc[j][g]);
+            if (lane == 0) sc[g * max_chunk + (sbase + j - s0)] = __fmul_rn(d, scale);
+          }
+      }
+  }
+  __syncwarp();
+  for (int g = 0; g < gqa; ++g) {
+    float m = -CUDART_INF_F;
+    for (int s = lane; s < s1 - s0; s += 32) m = fmaxf(m, sc[g * max_chunk + s]);
+    m = warp_max(m);
+    float l = 0.f;
+    for (int s = lane; s < s1 - s0; s += 32) {
+      const float e = expf(sc[g * max_chunk + s] - m);
+      sc[g * max_chunk + s] = e;
+      l += e;
+    }
+    l = warp_sum(l);
+    if (lane == 0) { out[g * (hd + 2) + hd] = m; out[g * (hd + 2) + hd + 1] = l; }
+  }
+  __syncwarp();
+  const int P = ATT_THREADS / hd > 0 ? ATT_THREADS / hd : 1;  // the groups of attend_slice
+  for (int i = lane; i < hd; i += 32) {
+    float total[ATT_MAX_GQA];
+#pragma unroll
+    for (int g = 0; g < ATT_MAX_GQA; ++g) total[g] = 0.f;
+    for (int grp = 0; grp < P; ++grp) {
+      float acc[ATT_MAX_GQA];
+#pragma unroll
+      for (int g = 0; g < ATT_MAX_GQA; ++g) acc[g] = 0.f;
+      for (int sb = s0 + 8 * grp; sb < s1; sb += 8 * P) {
+        float vv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vv[j] = sb + j < s1 ? src.v(sb + j)[i] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (sb + j < s1) {
+#pragma unroll
+            for (int g = 0; g < ATT_MAX_GQA; ++g)
+              if (g < gqa) acc[g] = fmaf(sc[g * max_chunk + (sb + j - s0)], vv[j], acc[g]);
+          }
+      }
+#pragma unroll
+      for (int g = 0; g < ATT_MAX_GQA; ++g) total[g] += acc[g];
+    }
+#pragma unroll
+    for (int g = 0; g < ATT_MAX_GQA; ++g)
+      if (g < gqa) out[g * (hd + 2) + i] = total[g];
+  }
+}
+
+// grid (kv head, position slice, group of ATT_ROWS rows): the rows of a prompt chunk share the slice's key and value
+// rows, which the block stages in shared memory once per run of rows of one sequence; each warp then takes rows of
+// its own, with no block-wide barrier between rows.
+__global__ void __launch_bounds__(ATT_THREADS, 3)
+attention_tile_kernel(const float* __restrict__ q, KvView kv, float* __restrict__ part, RowMap rows, int layer, int chunk,
+                      WalkShape w, int tokens) {
+  pdl_enter();
+  extern __shared__ float sm[];  // k tile [chunk][hd] | v tile [chunk][hd] | per warp: q[gqa][hd], scores[gqa][chunk]
+  const int hkv = blockIdx.x, split = blockIdx.y;
+  const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
+  const int n_split = (int)gridDim.y;
+  const int s0 = split * chunk;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = ATT_THREADS / 32;
+  float* kt = sm;
+  float* vt = kt + chunk * hd;
+  float* sq = vt + chunk * hd + warp * gqa * hd;
+  float* sc = vt + chunk * hd + nw * gqa * hd + warp * gqa * chunk;
+  const int t_begin = blockIdx.z * ATT_ROWS, t_end = min(tokens, t_begin + ATT_ROWS);
+  for (int t = t_begin; t < t_end;) {  // runs of rows of one sequence; everything here is block-uniform
+    const int sid = row_sequence(rows, t);
+    int u = t, need = 0;
+    for (; u < t_end && row_sequence(rows, u) == sid; ++u) need = max(need, min(row_position(rows, u) + 1, s0 + chunk) - s0);
+    if (need > 0) {
+      // positions [s0, s0 + need) lie in blocks the sequence owns: a row's position is below its reserved length
+      __syncthreads();  // the previous run's readers are done with the tile
+      const int vec = hd / 4;
+      for (int idx = threadIdx.x; idx < need * vec; idx += ATT_THREADS) {
+        const int p = idx / vec, c = idx % vec;
+        const int64_t off = kv_offset(kv, sid, layer, hkv, s0 + p, w.n_head_kv, hd);
+        ((float4*)(kt + p * hd))[c] = ((const float4*)(kv.k + off))[c];
+        ((float4*)(vt + p * hd))[c] = ((const float4*)(kv.v + off))[c];
+      }
+      __syncthreads();
+      for (int r = t + warp; r < u; r += nw) {
+        const int seq = row_position(rows, r) + 1;
+        if (s0 >= seq) continue;
+        const int s1 = min(seq, s0 + chunk);
+        for (int i = lane; i < gqa * hd; i += 32) sq[i] = q[((int64_t)r * w.n_head + hkv * gqa) * hd + i];
+        __syncwarp();
+        float* out = part + (((int64_t)r * w.n_head_kv + hkv) * n_split + split) * gqa * (hd + 2);
+        attend_slice_warp(KvTile{kt, vt, s0, hd}, sq, sc, out, s0, s1, chunk, hd, gqa);
+        __syncwarp();
+      }
+    }
+    t = u;
   }
 }
 
@@ -520,8 +691,22 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
     configured = smem;
   }
   if (launches) *launches += 2;
-  cudaError_t e = launch_walk(attention_partial_kernel, dim3(w.n_head_kv, splits, tokens), dim3(ATT_THREADS), smem, s, q, kv, scratch, rows, layer,
-                              max_chunk, w);
+  cudaError_t e;
+  // prompt chunks: rows of a group share the slice's keys and values through a shared-memory tile
+  const size_t tile_smem = (2 * (size_t)max_chunk * w.head_dim + (ATT_THREADS / 32) * ((size_t)gqa * w.head_dim + (size_t)gqa * max_chunk)) * sizeof(float);
+  if (tokens >= 4 && max_chunk <= ATT_TILE_CHUNK && w.head_dim % 4 == 0 && tile_smem <= 200 * 1024) {
+    static size_t tile_configured = 0;
+    if (tile_smem > 48 * 1024 && tile_smem > tile_configured) {
+      e = cudaFuncSetAttribute(attention_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem);
+      if (e != cudaSuccess) return e;
+      tile_configured = tile_smem;
+    }
+    e = launch_walk(attention_tile_kernel, dim3(w.n_head_kv, splits, (tokens + ATT_ROWS - 1) / ATT_ROWS), dim3(ATT_THREADS), tile_smem, s, q,
+                    kv, scratch, rows, layer, max_chunk, w, tokens);
+  } else {
+    e = launch_walk(attention_partial_kernel, dim3(w.n_head_kv, splits, tokens), dim3(ATT_THREADS), smem, s, q, kv, scratch, rows, layer,
+                    max_chunk, w);
+  }
   if (e != cudaSuccess) return e;
   return launch_walk(attention_combine_kernel, dim3(w.n_head, tokens), dim3(128), 0, s, (const float*)scratch, out, rows, max_chunk, w);
 }
