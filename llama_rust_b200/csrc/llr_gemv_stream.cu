@@ -219,7 +219,10 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int bid = blockIdx.x, nb = gridDim.x;
 
-  if (!PROGRAM) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Programmatic dependent launch (single products and one-phase programs are launched that way; elsewhere both
+  // instructions do nothing): the next kernel of the stream may be placed now, and this kernel's producer starts
+  // streaming weights while the kernel before it still runs; what touches activations or results waits below.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tid == 0) {
     for (int s = 0; s < NST; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], CW); }
     for (int s = 0; s < NRB; ++s) { mbar_init(&rfull[s], CW); mbar_init(&rempty[s], 1); }
@@ -283,7 +286,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
     return;
   }
 
-  if (!PROGRAM) asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (warp == CW + 1) {
     // -------------------------------------------------------------- reducer
@@ -829,6 +832,19 @@ static cudaError_t prog_launch(Program* p, cudaStream_t stream, int* err, int po
     void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dm, (void*)&dc, (void*)&run, (void*)&pt, (void*)&err};
     e = cudaLaunchCooperativeKernel((const void*)gemv_sharded_program_kernel<MT, FLOW>, dim3((unsigned)p->grid),
                                     dim3(NTHREADS), args, SLay<MT>::TOTAL, stream);
+  } else if (np == 1 && p->counter_phases == 0) {
+    // one phase: no CTA waits for another, so the launch need not be cooperative and can overlap its predecessor
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p->grid);
+    cfg.blockDim = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = SLay<MT>::TOTAL;
+    cfg.stream = stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kern, de, dp, np, dm, dc, run, err);
   } else {
     void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dm, (void*)&dc, (void*)&run, (void*)&err};
     e = cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)p->grid), dim3(NTHREADS), args,
