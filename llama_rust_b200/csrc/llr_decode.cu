@@ -308,58 +308,51 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
 }
 
 // The same slice of one row done by ONE warp, every elementary sum formed in the order attend_slice forms it (a
-// position's score: lanes over the columns, four per lane in ascending order, then the shuffle tree; a head's
-// softmax: lanes over the positions; a dimension's weighted sum: per group of runs of eight positions in ascending
-// order, then the groups in order), so the bits are the same.  sq [gqa][hd] and sc [gqa][max_chunk] are this warp's.
-template <typename KV>
-__device__ __forceinline__ void attend_slice_warp(const KV& src, const float* sq, float* sc, float* out, int s0, int s1, int max_chunk,
-                                                  int hd, int gqa) {
+// position's score: lanes over the columns in ascending order, then the shuffle tree; a head's softmax: lanes over the
+// positions; a dimension's weighted sum: per group of runs of eight positions in ascending order, then the groups in
+// order), so the bits are the same.  GQA query heads per kv head and P = ATT_THREADS / head_dim groups are template
+// parameters: nothing is predicated, and the loop over the value rows goes over the positions once, each position's
+// weights and value row loaded once for all the dimensions and heads a lane owns (the loop is bound by shared-memory
+// loads).  sq [GQA][hd] and sc [GQA][max_chunk] are this warp's.
+template <int GQA, int P, typename KV>
+__device__ __forceinline__ void attend_slice_warp(const KV& src, const float* sq, float* sc, float* out, int s0, int s1, int max_chunk) {
+  constexpr int HD = ATT_THREADS / P, ND = HD / 32;
   const int lane = threadIdx.x & 31;
-  const float scale = 1.0f / sqrtf((float)hd);
+  const float scale = 1.0f / sqrtf((float)HD);
   constexpr int SP = 4;
   for (int sbase = s0; sbase < s1; sbase += SP) {
-    float acc[SP][ATT_MAX_GQA];
-    const float* krow[SP];
+    float acc[SP][GQA];
+    float kvv[SP][ND];
 #pragma unroll
     for (int j = 0; j < SP; ++j) {
-      krow[j] = sbase + j < s1 ? src.k(sbase + j) : nullptr;
+      const bool live = sbase + j < s1;
+      const float* krow = src.k(live ? sbase + j : s0);
 #pragma unroll
-      for (int g = 0; g < ATT_MAX_GQA; ++g) acc[j][g] = 0.f;
+      for (int u = 0; u < ND; ++u) kvv[j][u] = live ? krow[lane + 32 * u] : 0.f;
+#pragma unroll
+      for (int g = 0; g < GQA; ++g) acc[j][g] = 0.f;
     }
-    for (int i0 = 0; i0 < hd; i0 += 128) {
-      float kvv[SP][4];
 #pragma unroll
-      for (int j = 0; j < SP; ++j)
+    for (int u = 0; u < ND; ++u)
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + lane + 32 * u;
-          kvv[j][u] = (krow[j] && i < hd) ? krow[j][i] : 0.f;
-        }
+      for (int g = 0; g < GQA; ++g) {
+        const float qv = sq[g * HD + lane + 32 * u];
 #pragma unroll
-      for (int j = 0; j < SP; ++j)
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i0 + lane + 32 * u;
-          if (krow[j] && i < hd) {
-#pragma unroll
-            for (int g = 0; g < ATT_MAX_GQA; ++g)
-              if (g < gqa) acc[j][g] = fmaf(sq[g * hd + i], kvv[j][u], acc[j][g]);
-          }
-        }
-    }
+        for (int j = 0; j < SP; ++j) acc[j][g] = fmaf(qv, kvv[j][u], acc[j][g]);
+      }
 #pragma unroll
     for (int j = 0; j < SP; ++j)
       if (sbase + j < s1) {
 #pragma unroll
-        for (int g = 0; g < ATT_MAX_GQA; ++g)
-          if (g < gqa) {
-            const float d = warp_sum(acc[j][g]);
-            if (lane == 0) sc[g * max_chunk + (sbase + j - s0)] = __fmul_rn(d, scale);
-          }
+        for (int g = 0; g < GQA; ++g) {
+          const float d = warp_sum(acc[j][g]);
+          if (lane == 0) sc[g * max_chunk + (sbase + j - s0)] = __fmul_rn(d, scale);
+        }
       }
   }
   __syncwarp();
-  for (int g = 0; g < gqa; ++g) {
+#pragma unroll
+  for (int g = 0; g < GQA; ++g) {
     float m = -CUDART_INF_F;
     for (int s = lane; s < s1 - s0; s += 32) m = fmaxf(m, sc[g * max_chunk + s]);
     m = warp_max(m);
@@ -370,49 +363,58 @@ __device__ __forceinline__ void attend_slice_warp(const KV& src, const float* sq
       l += e;
     }
     l = warp_sum(l);
-    if (lane == 0) { out[g * (hd + 2) + hd] = m; out[g * (hd + 2) + hd + 1] = l; }
+    if (lane == 0) { out[g * (HD + 2) + HD] = m; out[g * (HD + 2) + HD + 1] = l; }
   }
   __syncwarp();
-  const int P = ATT_THREADS / hd > 0 ? ATT_THREADS / hd : 1;  // the groups of attend_slice
-  for (int i = lane; i < hd; i += 32) {
-    float total[ATT_MAX_GQA];
+  float acc[ND][P][GQA];
 #pragma unroll
-    for (int g = 0; g < ATT_MAX_GQA; ++g) total[g] = 0.f;
+  for (int k = 0; k < ND; ++k)
+#pragma unroll
+    for (int grp = 0; grp < P; ++grp)
+#pragma unroll
+      for (int g = 0; g < GQA; ++g) acc[k][grp][g] = 0.f;
+  for (int rb = 0; s0 + 8 * rb < s1; rb += P) {
+#pragma unroll
     for (int grp = 0; grp < P; ++grp) {
-      float acc[ATT_MAX_GQA];
+      const int sb = s0 + 8 * (rb + grp);
 #pragma unroll
-      for (int g = 0; g < ATT_MAX_GQA; ++g) acc[g] = 0.f;
-      for (int sb = s0 + 8 * grp; sb < s1; sb += 8 * P) {
-        float vv[8];
+      for (int j = 0; j < 8; ++j)
+        if (sb + j < s1) {
+          float e[GQA], v[ND];
+          const float* vrow = src.v(sb + j);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) vv[j] = sb + j < s1 ? src.v(sb + j)[i] : 0.f;
+          for (int g = 0; g < GQA; ++g) e[g] = sc[g * max_chunk + (sb + j - s0)];
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          if (sb + j < s1) {
+          for (int k = 0; k < ND; ++k) v[k] = vrow[lane + 32 * k];
 #pragma unroll
-            for (int g = 0; g < ATT_MAX_GQA; ++g)
-              if (g < gqa) acc[g] = fmaf(sc[g * max_chunk + (sb + j - s0)], vv[j], acc[g]);
-          }
-      }
+          for (int k = 0; k < ND; ++k)
 #pragma unroll
-      for (int g = 0; g < ATT_MAX_GQA; ++g) total[g] += acc[g];
+            for (int g = 0; g < GQA; ++g) acc[k][grp][g] = fmaf(e[g], v[k], acc[k][grp][g]);
+        }
     }
-#pragma unroll
-    for (int g = 0; g < ATT_MAX_GQA; ++g)
-      if (g < gqa) out[g * (hd + 2) + i] = total[g];
   }
+#pragma unroll
+  for (int k = 0; k < ND; ++k)
+#pragma unroll
+    for (int g = 0; g < GQA; ++g) {
+      float total = 0.f;
+#pragma unroll
+      for (int grp = 0; grp < P; ++grp) total += acc[k][grp][g];
+      out[g * (HD + 2) + lane + 32 * k] = total;
+    }
 }
 
 // grid (kv head, position slice, group of ATT_ROWS rows): the rows of a prompt chunk share the slice's key and value
 // rows, which the block stages in shared memory once per run of rows of one sequence; each warp then takes rows of
 // its own, with no block-wide barrier between rows.
+template <int GQA, int P>
 __global__ void __launch_bounds__(ATT_THREADS, 3)
 attention_tile_kernel(const float* __restrict__ q, KvView kv, float* __restrict__ part, RowMap rows, int layer, int chunk,
                       WalkShape w, int tokens) {
   pdl_enter();
   extern __shared__ float sm[];  // k tile [chunk][hd] | v tile [chunk][hd] | per warp: q[gqa][hd], scores[gqa][chunk]
+  constexpr int hd = ATT_THREADS / P, gqa = GQA;
   const int hkv = blockIdx.x, split = blockIdx.y;
-  const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
   const int n_split = (int)gridDim.y;
   const int s0 = split * chunk;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = ATT_THREADS / 32;
@@ -421,14 +423,21 @@ attention_tile_kernel(const float* __restrict__ q, KvView kv, float* __restrict_
   float* sq = vt + chunk * hd + warp * gqa * hd;
   float* sc = vt + chunk * hd + nw * gqa * hd + warp * gqa * chunk;
   const int t_begin = blockIdx.z * ATT_ROWS, t_end = min(tokens, t_begin + ATT_ROWS);
+  // sequence and position of the group's rows, fetched in one go (the runs below are found in shared memory)
+  __shared__ int s_seq[ATT_ROWS], s_pos[ATT_ROWS];
+  if (threadIdx.x < ATT_ROWS && t_begin + (int)threadIdx.x < t_end) {
+    s_seq[threadIdx.x] = row_sequence(rows, t_begin + threadIdx.x);
+    s_pos[threadIdx.x] = row_position(rows, t_begin + threadIdx.x);
+  }
+  __syncthreads();
   for (int t = t_begin; t < t_end;) {  // runs of rows of one sequence; everything here is block-uniform
-    const int sid = row_sequence(rows, t);
+    const int sid = s_seq[t - t_begin];
     int u = t, need = 0;
-    for (; u < t_end && row_sequence(rows, u) == sid; ++u) need = max(need, min(row_position(rows, u) + 1, s0 + chunk) - s0);
+    for (; u < t_end && s_seq[u - t_begin] == sid; ++u) need = max(need, min(s_pos[u - t_begin] + 1, s0 + chunk) - s0);
     if (need > 0) {
       // positions [s0, s0 + need) lie in blocks the sequence owns: a row's position is below its reserved length
       __syncthreads();  // the previous run's readers are done with the tile
-      const int vec = hd / 4;
+      constexpr int vec = hd / 4;
       for (int idx = threadIdx.x; idx < need * vec; idx += ATT_THREADS) {
         const int p = idx / vec, c = idx % vec;
         const int64_t off = kv_offset(kv, sid, layer, hkv, s0 + p, w.n_head_kv, hd);
@@ -437,13 +446,13 @@ attention_tile_kernel(const float* __restrict__ q, KvView kv, float* __restrict_
       }
       __syncthreads();
       for (int r = t + warp; r < u; r += nw) {
-        const int seq = row_position(rows, r) + 1;
+        const int seq = s_pos[r - t_begin] + 1;
         if (s0 >= seq) continue;
         const int s1 = min(seq, s0 + chunk);
         for (int i = lane; i < gqa * hd; i += 32) sq[i] = q[((int64_t)r * w.n_head + hkv * gqa) * hd + i];
         __syncwarp();
         float* out = part + (((int64_t)r * w.n_head_kv + hkv) * n_split + split) * gqa * (hd + 2);
-        attend_slice_warp(KvTile{kt, vt, s0, hd}, sq, sc, out, s0, s1, chunk, hd, gqa);
+        attend_slice_warp<GQA, P>(KvTile{kt, vt, s0, hd}, sq, sc, out, s0, s1, chunk);
         __syncwarp();
       }
     }
@@ -694,15 +703,18 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
   cudaError_t e;
   // prompt chunks: rows of a group share the slice's keys and values through a shared-memory tile
   const size_t tile_smem = (2 * (size_t)max_chunk * w.head_dim + (ATT_THREADS / 32) * ((size_t)gqa * w.head_dim + (size_t)gqa * max_chunk)) * sizeof(float);
-  if (tokens >= 4 && max_chunk <= ATT_TILE_CHUNK && w.head_dim % 4 == 0 && tile_smem <= 200 * 1024) {
-    static size_t tile_configured = 0;
-    if (tile_smem > 48 * 1024 && tile_smem > tile_configured) {
-      e = cudaFuncSetAttribute(attention_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem);
+  void (*tile)(const float*, KvView, float*, RowMap, int, int, WalkShape, int) = nullptr;
+#define LLR_TILE(G, PP) if (gqa == G && w.head_dim == ATT_THREADS / PP) tile = attention_tile_kernel<G, PP>;
+  LLR_TILE(1, 1) LLR_TILE(2, 1) LLR_TILE(4, 1) LLR_TILE(1, 2) LLR_TILE(2, 2) LLR_TILE(4, 2) LLR_TILE(8, 2)
+  LLR_TILE(1, 4) LLR_TILE(2, 4) LLR_TILE(4, 4) LLR_TILE(8, 4)
+#undef LLR_TILE
+  if (tile && tokens >= 4 && max_chunk <= ATT_TILE_CHUNK && tile_smem <= 200 * 1024) {
+    if (tile_smem > 48 * 1024) {
+      e = cudaFuncSetAttribute((const void*)tile, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem);
       if (e != cudaSuccess) return e;
-      tile_configured = tile_smem;
     }
-    e = launch_walk(attention_tile_kernel, dim3(w.n_head_kv, splits, (tokens + ATT_ROWS - 1) / ATT_ROWS), dim3(ATT_THREADS), tile_smem, s, q,
-                    kv, scratch, rows, layer, max_chunk, w, tokens);
+    e = launch_walk(tile, dim3(w.n_head_kv, splits, (tokens + ATT_ROWS - 1) / ATT_ROWS), dim3(ATT_THREADS), tile_smem, s, q, kv, scratch,
+                    rows, layer, max_chunk, w, tokens);
   } else {
     e = launch_walk(attention_partial_kernel, dim3(w.n_head_kv, splits, tokens), dim3(ATT_THREADS), smem, s, q, kv, scratch, rows, layer,
                     max_chunk, w);
