@@ -460,36 +460,50 @@ attention_tile_kernel(const float* __restrict__ q, KvView kv, float* __restrict_
   }
 }
 
-// grid (query head, token): merges the position slices (at most 32): the first warp turns the slices' maxima into
-// weights exp(m_slice - m) and the denominator, then every thread adds its dimension over the slices in ascending order
+// grid (query heads / 4, token), one warp per query head: merges the position slices (at most 32).  Lane sp turns
+// slice sp's maximum into the weight exp(m_slice - m); the denominator is the shuffle-tree sum of the weighted slice
+// sums; then every lane adds its dimensions over the slices in ascending order, the weights coming by shuffle.
 __global__ void __launch_bounds__(128)
-attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, RowMap rows, int chunk, WalkShape w) {
+attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, RowMap rows, int chunk, WalkShape w, int heads_per_block) {
   pdl_enter();
-  __shared__ float s_e[32];
-  __shared__ float s_l;
-  const int hq = blockIdx.x, t = blockIdx.y;
+  // heads_per_block 4: one warp per head (many rows: fewer, fuller blocks); 1: the four warps share a head's
+  // dimensions (a decode step has few blocks to fill the device with)
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int hq = heads_per_block == 4 ? blockIdx.x * 4 + warp : blockIdx.x, t = blockIdx.y;
+  if (hq >= w.n_head) return;
+  const int d0 = heads_per_block == 4 ? lane : lane + 32 * warp, dstep = heads_per_block == 4 ? 32 : 128;
   const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
   const int hkv = hq / gqa, g = hq % gqa;
   const int seq = row_position(rows, t) + 1;
   const int n_split = (w.n_ctx + chunk - 1) / chunk, used = min(n_split, (seq + chunk - 1) / chunk);
   const float* base = part + ((int64_t)t * w.n_head_kv + hkv) * n_split * gqa * (hd + 2) + g * (hd + 2);
   const int64_t stride = (int64_t)gqa * (hd + 2);
-  if (threadIdx.x < 32) {
-    const int sp = threadIdx.x;
-    const float ms = sp < used ? base[sp * stride + hd] : -CUDART_INF_F;
-    const float m = warp_max(ms);
-    const float e = sp < used ? expf(ms - m) : 0.f;
-    const float l = warp_sum(sp < used ? base[sp * stride + hd + 1] * e : 0.f);
-    s_e[sp] = e;
-    if (sp == 0) s_l = l;
+  const float ms = lane < used ? base[lane * stride + hd] : -CUDART_INF_F;
+  const float m = warp_max(ms);
+  const float e = lane < used ? expf(ms - m) : 0.f;
+  const float l = warp_sum(lane < used ? base[lane * stride + hd + 1] * e : 0.f);
+  float acc[8];  // head_dim <= 256: up to eight dimensions per lane, all in flight at once
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  for (int sp0 = 0; sp0 < used; sp0 += 4) {  // four slices' records are fetched before the first is used
+    float v[4][8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[j][k] = (sp0 + j < used && d0 + dstep * k < hd) ? base[(sp0 + j) * stride + d0 + dstep * k] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float es = __shfl_sync(0xffffffffu, e, (sp0 + j) & 31);
+      if (sp0 + j < used) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (d0 + dstep * k < hd) acc[k] = fmaf(v[j][k], es, acc[k]);
+      }
+    }
   }
-  __syncthreads();
-  const float l = s_l;
-  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-    float acc = 0.f;
-    for (int sp = 0; sp < used; ++sp) acc = fmaf(base[sp * stride + i], s_e[sp], acc);
-    out[((int64_t)t * w.n_head + hq) * hd + i] = l > 0.f ? __fdiv_rn(acc, l) : 0.f;
-  }
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    if (d0 + dstep * k < hd) out[((int64_t)t * w.n_head + hq) * hd + d0 + dstep * k] = l > 0.f ? __fdiv_rn(acc[k], l) : 0.f;
 }
 
 __global__ void swiglu_kernel(float* __restrict__ g, const float* __restrict__ u, int64_t n) {
@@ -720,7 +734,8 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
                     max_chunk, w);
   }
   if (e != cudaSuccess) return e;
-  return launch_walk(attention_combine_kernel, dim3(w.n_head, tokens), dim3(128), 0, s, (const float*)scratch, out, rows, max_chunk, w);
+  return launch_walk(attention_combine_kernel, dim3(tokens >= 16 ? (w.n_head + 3) / 4 : w.n_head, tokens), dim3(128), 0, s, (const float*)scratch, out, rows,
+                     max_chunk, w, tokens >= 16 ? 4 : 1);
 }
 
 cudaError_t launch_swiglu(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches) {
