@@ -285,10 +285,28 @@ __device__ __forceinline__ void attend_slice(const KV& src, const float* sq, flo
   }
 }
 
-// grid (kv head, position slice, token): one row per block, K and V straight from the paged cache (decode steps)
+// The rotation of rope_store_kernel on n_vec vectors of hd floats in shared memory: one thread per pair
+__device__ __forceinline__ void rope_in_place(float* vecs, int n_vec, int hd, int pos, float theta_scale) {
+  const int half = hd / 2;
+  for (int idx = threadIdx.x; idx < n_vec * half; idx += blockDim.x) {
+    float* vec = vecs + (idx / half) * hd;
+    const int p = idx % half;
+    float theta = (float)(pos <= 65535 ? pos : 65535);
+    for (int i = 0; i < p; ++i) theta *= theta_scale;
+    const float c = cosf(theta), s = sinf(theta);
+    const float a = vec[2 * p], b = vec[2 * p + 1];
+    vec[2 * p] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+    vec[2 * p + 1] = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+  }
+}
+
+// grid (kv head, position slice, token): one row per block, K and V straight from the paged cache (decode steps).
+// With k_new / v_new (a single decode token) the kernel also does what rope_store_kernel does for that token: q is
+// rotated as it is loaded, and the block whose slice holds the token's position rotates the new key, writes it and
+// the new value into the cache and then reads them back like any other position: one launch less per layer.
 __global__ void __launch_bounds__(ATT_THREADS)
 attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restrict__ part, RowMap rows, int layer, int chunk,
-                         WalkShape w) {
+                         WalkShape w, const float* __restrict__ k_new, const float* __restrict__ v_new) {
   pdl_enter();
   extern __shared__ float sm[];  // q[gqa][hd] | scores[gqa][chunk] or sums[P][gqa][hd]
   const int hkv = blockIdx.x, split = blockIdx.y, t = blockIdx.z;
@@ -302,6 +320,22 @@ attention_partial_kernel(const float* __restrict__ q, KvView kv, float* __restri
   float* sc = sq + gqa * hd;
   for (int i = threadIdx.x; i < gqa * hd; i += ATT_THREADS)
     sq[i] = q[((int64_t)t * w.n_head + hkv * gqa) * hd + i];
+  if (k_new) {
+    const bool mine = s1 == seq;  // the slice that holds the token's own position
+    if (mine)
+      for (int i = threadIdx.x; i < hd; i += ATT_THREADS) sc[i] = k_new[((int64_t)t * w.n_head_kv + hkv) * hd + i];
+    __syncthreads();
+    rope_in_place(sq, gqa, hd, seq - 1, w.theta_scale);
+    if (mine) {
+      rope_in_place(sc, 1, hd, seq - 1, w.theta_scale);
+      __syncthreads();
+      const int64_t off = kv_offset(kv, sid, layer, hkv, seq - 1, w.n_head_kv, hd);
+      for (int i = threadIdx.x; i < hd; i += ATT_THREADS) {
+        kv.k[off + i] = sc[i];
+        kv.v[off + i] = v_new[((int64_t)t * w.n_head_kv + hkv) * hd + i];
+      }
+    }
+  }
   __syncthreads();
   float* out = part + (((int64_t)t * w.n_head_kv + hkv) * n_split + split) * gqa * (hd + 2);
   attend_slice(KvGlobal{kv, sid, layer, hkv, w.n_head_kv, hd}, sq, sc, out, s0, s1, chunk, hd, gqa);
@@ -697,7 +731,7 @@ size_t attention_scratch_floats(int tokens, const WalkShape& w) {
 }
 
 cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float* scratch, const RowMap& rows, int tokens,
-                             int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches) {
+                             int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches, const float* k_new, const float* v_new) {
   if (tokens <= 0) return cudaSuccess;
   const int gqa = w.n_head / w.n_head_kv;
   if (gqa < 1 || gqa > ATT_MAX_GQA || w.n_head % w.n_head_kv != 0 || w.head_dim > ATT_THREADS) return cudaErrorInvalidValue;
@@ -731,7 +765,7 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
                     rows, layer, max_chunk, w, tokens);
   } else {
     e = launch_walk(attention_partial_kernel, dim3(w.n_head_kv, splits, tokens), dim3(ATT_THREADS), smem, s, q, kv, scratch, rows, layer,
-                    max_chunk, w);
+                    max_chunk, w, tokens == 1 ? k_new : (const float*)nullptr, tokens == 1 ? v_new : (const float*)nullptr);
   }
   if (e != cudaSuccess) return e;
   return launch_walk(attention_combine_kernel, dim3(tokens >= 16 ? (w.n_head + 3) / 4 : w.n_head, tokens), dim3(128), 0, s, (const float*)scratch, out, rows,

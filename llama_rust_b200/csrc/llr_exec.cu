@@ -1463,8 +1463,12 @@ cudaError_t session_layers(llr_session* s, const int* ids_dev, size_t n, const R
       if ((ce = session_matmul(e, W.attn_k, n, s->xn, s->k)) != cudaSuccess) break;
       if ((ce = session_matmul(e, W.attn_v, n, s->xn, s->v)) != cudaSuccess) break;
     }
-    if ((ce = launch_rope_store(s->q, s->k, s->v, kv, rows, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
-    if ((ce = launch_attention(s->q, kv, s->attn, s->att_scratch, rows, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
+    if (n == 1) {  // a decode token: rotation and cache store happen inside the attention kernel
+      if ((ce = launch_attention(s->q, kv, s->attn, s->att_scratch, rows, 1, (int)li, s->shape, st, L, s->k, s->v)) != cudaSuccess) break;
+    } else {
+      if ((ce = launch_rope_store(s->q, s->k, s->v, kv, rows, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
+      if ((ce = launch_attention(s->q, kv, s->attn, s->att_scratch, rows, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
+    }
     if ((ce = session_matmul(e, W.attn_output, n, s->attn, s->proj)) != cudaSuccess) break;
     if ((ce = launch_rmsnorm(s->x, s->proj, s->ffn_norm[li], s->xn, (int)n, (int)E, c.rms_eps, st, L)) != cudaSuccess) break;
     if (one_row_programs && s->gateup_prog[li]) {
