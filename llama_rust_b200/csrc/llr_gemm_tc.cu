@@ -4,7 +4,7 @@
 //
 // What it computes: gemm_<t>_f32 (langtax/src/quant.rs:6282, 6366, 6380, 6478 ->
 // gemm_f32_x :6760; gemm_q6_k_f32 :6296), y[t*rows + r] = sum_c W[r,c] x[t*cols + c], for Q4_K, Q6_K,
-// Q8_0, Q5_0 and Q5_1.  Operands are 16-bit (binary16 when the matrix's weights fit its range,
+// Q8_0, Q5_0, Q5_1 and Q4_0.  Operands are 16-bit (binary16 when the matrix's weights fit its range,
 // bfloat16 otherwise; see dequant_sub_h), products are exact, accumulation is f32 in
 // tensor memory: this is the tensor-core path with the looser, separately stated tolerance
 // (tests/test_gpu_gemm.py); the f32-faithful path for any number of rows stays the
@@ -72,6 +72,7 @@ template <int DT> struct Pk;
 template <> struct Pk<DT_Q4_K> { static constexpr int RB = 144, PITCH = 144; };
 template <> struct Pk<DT_Q8_0> { static constexpr int RB = 272, PITCH = 272; };
 template <> struct Pk<DT_Q5_0> { static constexpr int RB = 176, PITCH = 176; };
+template <> struct Pk<DT_Q4_0> { static constexpr int RB = 144, PITCH = 144; };
 template <> struct Pk<DT_Q5_1> { static constexpr int RB = 192, PITCH = 208; };
 // Q6_K blocks are 210 bytes: the block of macro-step ms starts at 210*ms, which is a multiple of 16 bytes only
 // for every eighth step.  The copy starts at the 16-byte boundary below (TMA needs that) and is 240 bytes wide
@@ -313,6 +314,27 @@ __device__ __forceinline__ void dequant_sub(uint32_t prow, uint32_t (&out)[16], 
     go(std::integral_constant<int, 2>{}); go(std::integral_constant<int, 3>{});
     go(std::integral_constant<int, 4>{}); go(std::integral_constant<int, 5>{});
     go(std::integral_constant<int, 6>{}); go(std::integral_constant<int, 7>{});
+  } else if constexpr (DT == DT_Q4_0) {
+    // 18-byte blocks: d, then sixteen bytes whose low nibbles are columns 0..15 and high nibbles 16..31; w = (q - 8) d
+    constexpr int C0 = (18 * SB) / 16, OFF = 18 * SB - 16 * C0, NCH = (OFF + 18 + 15) / 16;
+    uint32_t w[4 * NCH + 1];
+    {
+      uint32_t t[4 * NCH];
+      lds_chunks<NCH>(prow + 16 * C0, t);
+#pragma unroll
+      for (int i = 0; i < 4 * NCH; ++i) w[i] = t[i];
+      w[4 * NCH] = 0;
+    }
+    const float d = h2f(h_at<OFF>(w));
+    const float nb = -1032.0f * d;  // (q - 8) * d with the magic 1024; exact
+    auto go = [&](auto I) {
+      constexpr int i = decltype(I)::value;
+      const uint32_t qs = w_at<OFF + 2 + 4 * i>(w);
+      emit4<0x00ff00ffu, 0x64006400u>(qs & 0x0f0f0f0fu, d, nb, out[2 * i], out[2 * i + 1]);
+      emit4<0x00ff00ffu, 0x64006400u>((qs >> 4) & 0x0f0f0f0fu, d, nb, out[8 + 2 * i], out[8 + 2 * i + 1]);
+    };
+    go(std::integral_constant<int, 0>{}); go(std::integral_constant<int, 1>{});
+    go(std::integral_constant<int, 2>{}); go(std::integral_constant<int, 3>{});
   } else {
     constexpr int BB = DT == DT_Q5_0 ? 22 : 24, HDR = DT == DT_Q5_0 ? 2 : 4;
     constexpr int C0 = (BB * SB) / 16, OFF = BB * SB - 16 * C0, NCH = (OFF + BB + 15) / 16;
@@ -406,6 +428,26 @@ __device__ __forceinline__ void dequant_sub_h(uint32_t prow, uint32_t (&out)[16]
     go(std::integral_constant<int, 2>{}); go(std::integral_constant<int, 3>{});
     go(std::integral_constant<int, 4>{}); go(std::integral_constant<int, 5>{});
     go(std::integral_constant<int, 6>{}); go(std::integral_constant<int, 7>{});
+  } else if constexpr (DT == DT_Q4_0) {
+    constexpr int C0 = (18 * SB) / 16, OFF = 18 * SB - 16 * C0, NCH = (OFF + 18 + 15) / 16;
+    uint32_t w[4 * NCH + 1];
+    {
+      uint32_t t[4 * NCH];
+      lds_chunks<NCH>(prow + 16 * C0, t);
+#pragma unroll
+      for (int i = 0; i < 4 * NCH; ++i) w[i] = t[i];
+      w[4 * NCH] = 0;
+    }
+    const uint32_t dh = h_at<OFF>(w);
+    const __half2 d = bits_h2(dh | (dh << 16)), off = __float2half2_rn(1032.f), zero = __float2half2_rn(0.f);
+    auto go = [&](auto I) {
+      constexpr int i = decltype(I)::value;
+      const uint32_t qs = w_at<OFF + 2 + 4 * i>(w);
+      emit4h<0x00ff00ffu, 0x64006400u>(qs & 0x0f0f0f0fu, off, d, zero, out[2 * i], out[2 * i + 1]);
+      emit4h<0x00ff00ffu, 0x64006400u>((qs >> 4) & 0x0f0f0f0fu, off, d, zero, out[8 + 2 * i], out[8 + 2 * i + 1]);
+    };
+    go(std::integral_constant<int, 0>{}); go(std::integral_constant<int, 1>{});
+    go(std::integral_constant<int, 2>{}); go(std::integral_constant<int, 3>{});
   } else {
     constexpr int BB = DT == DT_Q5_0 ? 22 : 24, HDR = DT == DT_Q5_0 ? 2 : 4;
     constexpr int C0 = (BB * SB) / 16, OFF = BB * SB - 16 * C0, NCH = (OFF + BB + 15) / 16;
@@ -802,7 +844,7 @@ __global__ void expert_rows_16bit_kernel(const float* __restrict__ x, const int*
 // 0x7f800000 or more.
 template <int DT>
 __global__ void weight_bound_kernel(const uint8_t* __restrict__ W, int64_t n_blocks, unsigned int* __restrict__ out) {
-  constexpr int BB = DT == DT_Q4_K ? 144 : DT == DT_Q6_K ? 210 : DT == DT_Q8_0 ? 34 : DT == DT_Q5_0 ? 22 : 24;
+  constexpr int BB = DT == DT_Q4_K ? 144 : DT == DT_Q6_K ? 210 : DT == DT_Q8_0 ? 34 : DT == DT_Q5_0 ? 22 : DT == DT_Q4_0 ? 18 : 24;
   float m = 0.f;
   for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks; b += (int64_t)gridDim.x * blockDim.x) {
     const uint16_t* hp = (const uint16_t*)(W + b * BB);
@@ -812,6 +854,7 @@ __global__ void weight_bound_kernel(const uint8_t* __restrict__ W, int64_t n_blo
     else if (DT == DT_Q4_K) bound = d * (63.f * 15.f) + fabsf(__half2float(__ushort_as_half(hp[1]))) * 63.f;
     else if (DT == DT_Q8_0) bound = d * 128.f;
     else if (DT == DT_Q5_0) bound = d * 16.f;
+    else if (DT == DT_Q4_0) bound = d * 8.f;
     else bound = d * 31.f + fabsf(__half2float(__ushort_as_half(hp[1])));
     if (!(bound <= 3.4028234e38f)) bound = __uint_as_float(0x7f800000u);
     m = fmaxf(m, bound);
@@ -879,7 +922,7 @@ cudaError_t launch_dt(const MatView& m, const void* xb, const float* xscale, flo
 }  // namespace
 
 bool gemm_tc_supported(const MatView& m, int64_t tokens) {
-  if (m.dtype != DT_Q4_K && m.dtype != DT_Q6_K && m.dtype != DT_Q8_0 && m.dtype != DT_Q5_0 && m.dtype != DT_Q5_1) return false;
+  if (m.dtype != DT_Q4_K && m.dtype != DT_Q6_K && m.dtype != DT_Q8_0 && m.dtype != DT_Q5_0 && m.dtype != DT_Q5_1 && m.dtype != DT_Q4_0) return false;
   if (m.dtype == DT_Q6_K && m.cols % 2048 != 0) return false;  // the tensor map wants rows a multiple of 16 bytes apart: 8 x 210
   if (tokens < 16 || tokens > (1 << 24) || m.rows <= 0 || m.rows > (1 << 30)) return false;
   if (m.cols % MACRO != 0 || m.cols <= 0 || m.cols > (1 << 30)) return false;
@@ -917,6 +960,7 @@ cudaError_t launch_weight_bound(const MatView& m, unsigned int* out_dev, cudaStr
     case DT_Q6_K: weight_bound_kernel<DT_Q6_K><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
     case DT_Q8_0: weight_bound_kernel<DT_Q8_0><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
     case DT_Q5_0: weight_bound_kernel<DT_Q5_0><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
+    case DT_Q4_0: weight_bound_kernel<DT_Q4_0><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
     case DT_Q5_1: weight_bound_kernel<DT_Q5_1><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
     default: return cudaErrorInvalidValue;
   }
@@ -959,6 +1003,7 @@ cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t t
     case DT_Q6_K: e = LLR_TC(DT_Q6_K); break;
     case DT_Q8_0: e = LLR_TC(DT_Q8_0); break;
     case DT_Q5_0: e = LLR_TC(DT_Q5_0); break;
+    case DT_Q4_0: e = LLR_TC(DT_Q4_0); break;
     case DT_Q5_1: e = LLR_TC(DT_Q5_1); break;
     default: return cudaErrorInvalidValue;
   }
@@ -1083,6 +1128,7 @@ cudaError_t launch_gemm_tc_grouped(const GemmGroupSpec* specs, int n, bool f16, 
     case DT_Q6_K: e = launch_grouped_dt<DT_Q6_K>(specs, n, f16, desc_dev, stream, err_flag); break;
     case DT_Q8_0: e = launch_grouped_dt<DT_Q8_0>(specs, n, f16, desc_dev, stream, err_flag); break;
     case DT_Q5_0: e = launch_grouped_dt<DT_Q5_0>(specs, n, f16, desc_dev, stream, err_flag); break;
+    case DT_Q4_0: e = launch_grouped_dt<DT_Q4_0>(specs, n, f16, desc_dev, stream, err_flag); break;
     case DT_Q5_1: e = launch_grouped_dt<DT_Q5_1>(specs, n, f16, desc_dev, stream, err_flag); break;
     default: return cudaErrorInvalidValue;
   }

@@ -70,9 +70,9 @@ def test_noalloc_gemm_matches_regular_entry_point_twice():
     ex.synchronize()
     assert bool((y == 7.0).all())
     # formats the tensor-core GEMM does not take are rejected, not rerouted
-    q40 = ex.synth(12, 128, 2048, 6)  # Q4_0 has no tensor-core routine
-    rc = L.llr_gemm_device_noalloc(ex._h, q40._h, 64, x.data_ptr(), y.data_ptr(), None)
+    f16 = ex.synth(0, 128, 2048, 6)  # F16 weights have no tensor-core routine
+    rc = L.llr_gemm_device_noalloc(ex._h, f16._h, 64, x.data_ptr(), y.data_ptr(), None)
     assert rc == 1
     big.free()
-    q40.free()
+    f16.free()
     ex.close()
