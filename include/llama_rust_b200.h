@@ -98,10 +98,11 @@ int llr_exec_counters(const llr_exec* exec, llr_counters* out);
  * staged kernel, else the shape-agnostic one), 1 = the shape-agnostic byte-load
  * kernel, 2 = the shared-memory staged FMA kernel (falls back to 1 for shapes
  * it cannot take), 3 = the integer tensor-core kernel for any number of
- * activation rows (f32-faithful), 4 = the bf16 tcgen05 GEMM whenever it can take
+ * activation rows (f32-faithful), 4 = the tcgen05 GEMM whenever it can take
  * the call.  Automatic choice: up to 63 activation rows as 3, from 64 rows the
- * bf16 tcgen05 GEMM for Q4_K/Q8_0/Q5_0/Q5_1 (16-bit operands: relative L2 error of a
- * result up to 4e-3 against the f32 row kernels).
+ * tcgen05 GEMM for Q4_K/Q6_K/Q8_0/Q5_0/Q5_1/Q4_0 (16-bit operands, binary16 when
+ * the weights' range allows, else bfloat16: relative L2 error of a result up to
+ * 4e-3 against the f32 row kernels, 3e-4 typical with binary16).
  * Also read once from the environment variable LLR_GEMV_PATH
  * (generic|staged|mma|tc) when the executor is created. */
 int llr_exec_set_path(llr_exec* exec, int path);
@@ -238,8 +239,8 @@ int llr_matmul_device(llr_exec* exec, const llr_matrix* matrix, size_t tokens, c
  * buffer could fail or evict; code inside a region where the implicit device
  * synchronization of cudaMalloc/cudaFree is not acceptable; hosts that hand this
  * library a fixed memory budget up front.  Same tensor-core GEMM as the
- * automatic path takes from 64 activation rows on (Q4_K, Q8_0, Q5_0, Q5_1;
- * cols % 256 == 0; tokens >= 16; 16-bit operands -- binary16 when the matrix's
+ * automatic path takes from 64 activation rows on (Q4_K, Q6_K, Q8_0, Q5_0, Q5_1,
+ * Q4_0; cols % 256 == 0, Q6_K cols % 2048 == 0; tokens >= 16; 16-bit operands -- binary16 when the matrix's
  * weights fit its range, else bfloat16 -- with f32 accumulation), but the
  * 16-bit copy of the activations is staged in a fixed 32 MiB array built into the
  * library (every GPU that loads the library holds it until the process exits)
