@@ -68,7 +68,7 @@ constexpr int NRB = 4;                    // reduction buffers
 constexpr int PART_COLS = 4096;           // columns between two hand-offs of partial sums to the reducer
 constexpr int MAX_CHUNK = Lay<DT_Q4_K, 1>::CHUNK;
 static_assert(Lay<DT_Q6_K, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q8_0, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q4_0, 1>::CHUNK <= MAX_CHUNK &&
-              Lay<DT_Q5_0, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q5_1, 1>::CHUNK <= MAX_CHUNK, "ring stage");
+              Lay<DT_Q5_0, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q5_1, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q4_1, 1>::CHUNK <= MAX_CHUNK, "ring stage");
 // Sharded programs keep two counter arrays in the arena header: [0, 4096) this rank's CTAs per
 // phase, [4096, 8192) arrivals of the peers per phase.
 constexpr int PEER_COUNTER_OFFSET = 4096;
@@ -94,12 +94,16 @@ template <int MT> struct SLay {
 // whatever its size, which capped sixteen 1680-byte row copies per stage at 87 % of the copy peak.
 struct Geom { int kseg, segb, rs, box_bytes; };
 constexpr int Q4K_STAGE_BLOCKS = Fmt<DT_Q4_K>::KSEG / 256;
+constexpr int Q5K_STAGE_BLOCKS = Fmt<DT_Q5_K>::KSEG / 256;   // the 176-byte blocks are laid out like Q4_K's
+static_assert(Q5K_STAGE_BLOCKS * 16 * 176 <= MAX_CHUNK, "ring stage");
 __device__ __forceinline__ Geom geom_of(int dtype) {
   if (dtype == DT_Q4_K) return {Fmt<DT_Q4_K>::KSEG, Lay<DT_Q4_K, 1>::SEGB, Lay<DT_Q4_K, 1>::RS, Q4K_STAGE_BLOCKS * 16 * 144};
   if (dtype == DT_Q6_K) return {Fmt<DT_Q6_K>::KSEG, Lay<DT_Q6_K, 1>::SEGB, Lay<DT_Q6_K, 1>::RS, 16 * Lay<DT_Q6_K, 1>::SEGB};
   if (dtype == DT_Q4_0) return {Fmt<DT_Q4_0>::KSEG, Lay<DT_Q4_0, 1>::SEGB, Lay<DT_Q4_0, 1>::RS, 0};
   if (dtype == DT_Q5_0) return {Fmt<DT_Q5_0>::KSEG, Lay<DT_Q5_0, 1>::SEGB, Lay<DT_Q5_0, 1>::RS, 0};
   if (dtype == DT_Q5_1) return {Fmt<DT_Q5_1>::KSEG, Lay<DT_Q5_1, 1>::SEGB, Lay<DT_Q5_1, 1>::RS, 0};
+  if (dtype == DT_Q4_1) return {Fmt<DT_Q4_1>::KSEG, Lay<DT_Q4_1, 1>::SEGB, Lay<DT_Q4_1, 1>::RS, 0};
+  if (dtype == DT_Q5_K) return {Fmt<DT_Q5_K>::KSEG, Lay<DT_Q5_K, 1>::SEGB, Lay<DT_Q5_K, 1>::RS, Q5K_STAGE_BLOCKS * 16 * 176};
   return {Fmt<DT_Q8_0>::KSEG, Lay<DT_Q8_0, 1>::SEGB, Lay<DT_Q8_0, 1>::RS, 0};
 }
 static_assert(Lay<DT_Q6_K, 1>::RS == Lay<DT_Q6_K, 1>::SEGB, "Q6_K rows lie densely in a stage");
@@ -265,6 +269,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
                   // rows and blocks beyond the matrix are filled with zeros and still counted
                   mbar_expect_tx(&full[stage], (uint32_t)gm.box_bytes);
                   if (dtype == DT_Q4_K) tma_box_3d(dst, map, 0, tile * 16, seg * Q4K_STAGE_BLOCKS, &full[stage], stream_once);
+                  else if (DTFIX == DT_Q5_K) tma_box_3d(dst, map, 0, tile * 16, seg * Q5K_STAGE_BLOCKS, &full[stage], stream_once);
                   else tma_box_2d(dst, map, seg * (Lay<DT_Q6_K, 1>::SEGB / 8), tile * 16, &full[stage], stream_once);
                   continue;
                 }
@@ -533,6 +538,9 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
               // stage layout [block][row][144]; fragment row g is tile row q4k_row(g), see there
               for (int b = warp; b < (seg_cols >> 8); b += CW)
                 block_q4k<MT>(chunk + (b * 16 + q4k_row(g)) * 144, chunk + (b * 16 + q4k_row(g) + 8) * 144, sub * (gm.kseg / 256) + b, dig, sxf, xsi, g, t, acc);
+            } else if (DTFIX == DT_Q5_K) {  // single products only, like the nibble formats below
+              for (int b = warp; b < (seg_cols >> 8); b += CW)
+                block_q4k<MT, true>(chunk + (b * 16 + q4k_row(g)) * 176, chunk + (b * 16 + q4k_row(g) + 8) * 176, sub * (gm.kseg / 256) + b, dig, sxf, xsi, g, t, acc);
             } else if (dtype == DT_Q6_K) {
               for (int b = warp; b < (seg_cols >> 8); b += CW)
                 block_q6k<MT>(rowA, rowB, b, sub * (gm.kseg / 256) + b, dig, xsi, g, t, acc);
@@ -560,6 +568,14 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
                 for (int i = 0; i < 8; ++i)
                   block_q51<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xw, g, t, acc);
               }
+            } else if (DTFIX == DT_Q4_1) {
+              for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
+                float xw[NT];
+                group_scales<MT>(xsi, sub * (gm.kseg / 256) + b8, t, (t & 1) ? 65536.f : 1.f, xw);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  block_q41<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xw, g, t, acc);
+              }
             } else {
               for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
                 float xw[NT];
@@ -576,7 +592,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           const int rb = j % NRB;
           if (ok && !mbar_wait(&rempty[rb], (uint32_t)(((j / NRB) & 1) ^ 1), abort_word, epoch)) { ok = false; if (lane == 0) report_error(err, 1); }
           float* myred = red + (rb * CW + warp) * 16 * MT;
-          if ((DTFIX >= 0 ? DTFIX : E.dtype) == DT_Q4_K || DTFIX == DT_Q5_1) {
+          if ((DTFIX >= 0 ? DTFIX : E.dtype) == DT_Q4_K || DTFIX == DT_Q5_1 || DTFIX == DT_Q4_1 || DTFIX == DT_Q5_K) {
 #pragma unroll
             for (int k = 0; k < MT; ++k)
 #pragma unroll
@@ -598,7 +614,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
 #pragma unroll
               for (int k = 0; k < MT; ++k)
                 if (k == tok) { mA = acc.mn[0][k]; mB = acc.mn[1][k]; }
-              const int gr = (DTFIX >= 0 ? DTFIX : E.dtype) == DT_Q4_K ? q4k_row(g) : g;
+              const int gr = ((DTFIX >= 0 ? DTFIX : E.dtype) == DT_Q4_K || DTFIX == DT_Q5_K) ? q4k_row(g) : g;
               myred[gr * MT + tok] = vA - mA;
               myred[(gr + 8) * MT + tok] = vB - mB;
             }
@@ -672,14 +688,15 @@ gemv_sharded_program_kernel(const ProgEntry* __restrict__ entries, const ProgPha
 // stays zeroed and is never used.
 bool encode_weight_map(const uint8_t* w, int dtype, int64_t rows, int64_t cols, int64_t row_bytes, CUtensorMap* map) {
   memset(map, 0, sizeof(*map));
-  if (dtype != DT_Q4_K && dtype != DT_Q6_K) return true;
+  if (dtype != DT_Q4_K && dtype != DT_Q6_K && dtype != DT_Q5_K) return true;
   EncodeTiledFn enc = tensor_map_encoder();
   if (!enc) return false;
   const cuuint32_t estr[3] = {1, 1, 1};
-  if (dtype == DT_Q4_K) {
-    const cuuint64_t dims[3] = {36, (cuuint64_t)rows, (cuuint64_t)(cols / 256)};
-    const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, 144};
-    const cuuint32_t box[3] = {36, 16, (cuuint32_t)Q4K_STAGE_BLOCKS};
+  if (dtype == DT_Q4_K || dtype == DT_Q5_K) {
+    const cuuint32_t words = dtype == DT_Q4_K ? 36 : 44;
+    const cuuint64_t dims[3] = {words, (cuuint64_t)rows, (cuuint64_t)(cols / 256)};
+    const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, 4 * words};
+    const cuuint32_t box[3] = {words, 16, (cuuint32_t)(dtype == DT_Q4_K ? Q4K_STAGE_BLOCKS : Q5K_STAGE_BLOCKS)};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (void*)w, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
   }
@@ -733,7 +750,8 @@ cudaError_t launch_single(const MatView& m, const float* x, float* y, int tokens
 }  // namespace
 
 bool gemv_mma_supported(const MatView& m) {
-  if (m.dtype != DT_Q4_K && m.dtype != DT_Q6_K && m.dtype != DT_Q8_0 && m.dtype != DT_Q4_0 && m.dtype != DT_Q5_0 && m.dtype != DT_Q5_1)
+  if (m.dtype != DT_Q4_K && m.dtype != DT_Q6_K && m.dtype != DT_Q8_0 && m.dtype != DT_Q4_0 && m.dtype != DT_Q5_0 && m.dtype != DT_Q5_1 &&
+      m.dtype != DT_Q4_1 && m.dtype != DT_Q5_K)
     return false;
   if (m.rows <= 0 || m.cols <= 0 || m.rows > (1 << 30) || m.cols > (1 << 30)) return false;
   if (((uintptr_t)m.w & 15) != 0 || m.row_bytes % 16 != 0) return false;
@@ -760,6 +778,8 @@ static cudaError_t launch_passes(const MatView& m, const float* x, float* y, int
     else if (m.dtype == DT_Q4_0) e = LLR_LAUNCH_DT(DT_Q4_0);
     else if (m.dtype == DT_Q5_0) e = LLR_LAUNCH_DT(DT_Q5_0);
     else if (m.dtype == DT_Q5_1) e = LLR_LAUNCH_DT(DT_Q5_1);
+    else if (m.dtype == DT_Q4_1) e = LLR_LAUNCH_DT(DT_Q4_1);
+    else if (m.dtype == DT_Q5_K) e = LLR_LAUNCH_DT(DT_Q5_K);
     else e = LLR_LAUNCH_DT(DT_Q8_0);
 #undef LLR_LAUNCH_DT
     if (e != cudaSuccess) return e;

@@ -43,6 +43,8 @@ template <> struct Fmt<DT_Q8_0> { static constexpr int KSEG = 2048, BB = 34, BE 
 template <> struct Fmt<DT_Q4_0> { static constexpr int KSEG = 2048, BB = 18, BE = 32; };
 template <> struct Fmt<DT_Q5_0> { static constexpr int KSEG = 2048, BB = 22, BE = 32; };
 template <> struct Fmt<DT_Q5_1> { static constexpr int KSEG = 2048, BB = 24, BE = 32; };
+template <> struct Fmt<DT_Q4_1> { static constexpr int KSEG = 2048, BB = 20, BE = 32; };
+template <> struct Fmt<DT_Q5_K> { static constexpr int KSEG = 2048, BB = 176, BE = 256; };
 
 template <int DT, int MT> struct Lay {
   using F = Fmt<DT>;
@@ -50,7 +52,7 @@ template <int DT, int MT> struct Lay {
   static constexpr int SEGB = F::KSEG / F::BE * F::BB;          // bytes of one row segment
   // row stride mod 128: 32 spreads the 8-byte fragment reads of eight rows over all banks,
   // 16 does the same for the 4-byte reads of Q6_K
-  static constexpr int RMOD = (DT == DT_Q6_K || DT == DT_Q4_0 || DT == DT_Q5_0 || DT == DT_Q5_1) ? 16 : 32;
+  static constexpr int RMOD = (DT == DT_Q6_K || DT == DT_Q4_0 || DT == DT_Q5_0 || DT == DT_Q5_1 || DT == DT_Q4_1) ? 16 : 32;
   static constexpr int RS = SEGB + (RMOD + 128 - SEGB % 128) % 128;
   static constexpr int CHUNK = 16 * RS;
   static_assert(RS % 16 == 0 && RS % 128 == RMOD, "row stride");
@@ -146,11 +148,17 @@ template <int DT, int MT> using Acc = AccT<MT>;
 // Low nibbles are an int8 A operand after one AND.  High nibbles stay where they are: the bytes
 // 16 q are an unsigned A operand, their sums go to a second accumulator, and the 1/16 is part of
 // the final scale (a power of two, so the int -> float rounding is the same).
-template <int MT>
+// K5: the block is a Q5_K one (176 bytes: the same 16-byte header, then 32 bytes whose bit 2G / 2G+1 is the fifth
+// bit of the low / high nibble of quant byte l of group G, then the 128 quant bytes).  Codes 0..31 are built in
+// the low five bits of every byte for both halves, so both sums carry the same weight.
+template <int MT, bool K5 = false>
 __device__ __forceinline__ void block_q4k(const uint8_t* pA, const uint8_t* pB, int cb,
                                           const uint8_t* dig, const float* sxf, const float* xsi,
                                           int g, int t, Acc<DT_Q4_K, MT>& acc) {
   constexpr int NT = (MT + 1) / 2;
+  constexpr int QS = K5 ? 48 : 16;
+  uint2 fA = make_uint2(0u, 0u), fB = make_uint2(0u, 0u);
+  if (K5) { fA = *(const uint2*)(pA + 16 + 8 * t); fB = *(const uint2*)(pB + 16 + 8 * t); }
   const uint4 hA = *(const uint4*)pA, hB = *(const uint4*)pB;
   // 6-bit scales and mins packed four to a word: bytes 0..3 = sub-blocks 0..3 (word 0), 4..7 (word 1)
   const uint32_t scA0 = hA.y & 0x3f3f3f3fu, scA1 = (hA.w & 0x0f0f0f0fu) | ((hA.y >> 2) & 0x30303030u);
@@ -162,9 +170,9 @@ __device__ __forceinline__ void block_q4k(const uint8_t* pA, const uint8_t* pB, 
     for (int i = 0; i < 4; ++i) Tl[nt][i] = Th[nt][i] = 0;
 #pragma unroll
   for (int G = 0; G < 4; ++G) {
-    const uint2 wA = *(const uint2*)(pA + 16 + G * 32 + 8 * t);
-    const uint2 wB = *(const uint2*)(pB + 16 + G * 32 + 8 * t);
-    constexpr uint32_t M4 = 0x0f0f0f0fu, MH = 0xf0f0f0f0u;
+    const uint2 wA = *(const uint2*)(pA + QS + G * 32 + 8 * t);
+    const uint2 wB = *(const uint2*)(pB + QS + G * 32 + 8 * t);
+    constexpr uint32_t M4 = 0x0f0f0f0fu, MH = 0xf0f0f0f0u, B5 = 0x10101010u;
     const uint32_t scAp = G < 2 ? scA0 : scA1, scBp = G < 2 ? scB0 : scB1;
     // byte 2 (G & 1) and the next one, zero-extended: one byte permute each
     const int sAlo = (int)__byte_perm(scAp, 0, 0x4440 + 2 * (G & 1)), sAhi = (int)__byte_perm(scAp, 0, 0x4441 + 2 * (G & 1));
@@ -174,8 +182,17 @@ __device__ __forceinline__ void block_q4k(const uint8_t* pA, const uint8_t* pB, 
       const uint8_t* dp = plane_of<MT>(dig, nt, g) + cb * 256 + G * 64 + 8 * t;
       const uint2 blo = *(const uint2*)dp, bhi = *(const uint2*)(dp + 32);
       int clo[4], chi[4];
-      mma_k32(clo, wA.x & M4, wB.x & M4, wA.y & M4, wB.y & M4, blo.x, blo.y);
-      mma_k32_us(chi, wA.x & MH, wB.x & MH, wA.y & MH, wB.y & MH, bhi.x, bhi.y);
+      if (K5) {
+        // bit 2G of a mask byte moves to bit 4: a shift by 4 - 2G (left for G < 2, right for G = 3)
+        auto fifth = [](uint32_t f, int bit) { return (bit <= 4 ? f << (4 - bit) : f >> (bit - 4)) & B5; };
+        mma_k32(clo, (wA.x & M4) | fifth(fA.x, 2 * G), (wB.x & M4) | fifth(fB.x, 2 * G),
+                (wA.y & M4) | fifth(fA.y, 2 * G), (wB.y & M4) | fifth(fB.y, 2 * G), blo.x, blo.y);
+        mma_k32(chi, ((wA.x >> 4) & M4) | fifth(fA.x, 2 * G + 1), ((wB.x >> 4) & M4) | fifth(fB.x, 2 * G + 1),
+                ((wA.y >> 4) & M4) | fifth(fA.y, 2 * G + 1), ((wB.y >> 4) & M4) | fifth(fB.y, 2 * G + 1), bhi.x, bhi.y);
+      } else {
+        mma_k32(clo, wA.x & M4, wB.x & M4, wA.y & M4, wB.y & M4, blo.x, blo.y);
+        mma_k32_us(chi, wA.x & MH, wB.x & MH, wA.y & MH, wB.y & MH, bhi.x, bhi.y);
+      }
       Tl[nt][0] += sAlo * clo[0]; Th[nt][0] += sAhi * chi[0];
       Tl[nt][1] += sAlo * clo[1]; Th[nt][1] += sAhi * chi[1];
       Tl[nt][2] += sBlo * clo[2]; Th[nt][2] += sBhi * chi[2];
@@ -186,16 +203,17 @@ __device__ __forceinline__ void block_q4k(const uint8_t* pA, const uint8_t* pB, 
   const float dB = h2f(hB.x & 0xffffu), dminB = h2f(hB.x >> 16);
   // columns 2t, 2t+1 of an n-tile are activation row (t >> 1), digits 2(t&1) and 2(t&1)+1;
   // the weights are 256^digit / 16
-  const float pw0 = (t & 1) ? 4096.f : 0.0625f, pw1 = pw0 * 256.f;
+  const float pw0 = K5 ? ((t & 1) ? 65536.f : 1.f) : ((t & 1) ? 4096.f : 0.0625f), pw1 = pw0 * 256.f;
+  constexpr int LW = K5 ? 1 : 16;  // weight of the low-nibble sums relative to the high-nibble ones
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
     const int tok = 2 * nt + (t >> 1);
     const float xs = tok < MT ? xsi[tok * (Sp<MT>::SPAN / 256) + cb] : 0.f;
-    // 16 Tl + Th < 2^31: |Tl| <= 4 * 63 * 32 * 15 * 128 < 2^24 and |Th| <= 16 times that
-    acc.y[nt][0] = fmaf((float)(Tl[nt][0] * 16 + Th[nt][0]), dA * xs * pw0, acc.y[nt][0]);
-    acc.y[nt][1] = fmaf((float)(Tl[nt][1] * 16 + Th[nt][1]), dA * xs * pw1, acc.y[nt][1]);
-    acc.y[nt][2] = fmaf((float)(Tl[nt][2] * 16 + Th[nt][2]), dB * xs * pw0, acc.y[nt][2]);
-    acc.y[nt][3] = fmaf((float)(Tl[nt][3] * 16 + Th[nt][3]), dB * xs * pw1, acc.y[nt][3]);
+    // 16 Tl + Th < 2^31: |Tl| <= 4 * 63 * 32 * 15 * 128 < 2^24 and |Th| <= 16 times that (Q5_K: both < 2^25)
+    acc.y[nt][0] = fmaf((float)(Tl[nt][0] * LW + Th[nt][0]), dA * xs * pw0, acc.y[nt][0]);
+    acc.y[nt][1] = fmaf((float)(Tl[nt][1] * LW + Th[nt][1]), dA * xs * pw1, acc.y[nt][1]);
+    acc.y[nt][2] = fmaf((float)(Tl[nt][2] * LW + Th[nt][2]), dB * xs * pw0, acc.y[nt][2]);
+    acc.y[nt][3] = fmaf((float)(Tl[nt][3] * LW + Th[nt][3]), dB * xs * pw1, acc.y[nt][3]);
   }
   // mins: this thread covers sub-blocks t and t + 4 of both rows.  Byte t of header words 2 and 3
   // of both rows side by side (row g in byte 0, row g+8 in byte 2), so that the 6-bit fields of
@@ -434,6 +452,37 @@ template <int MT>
 __device__ __forceinline__ void block_q51(const uint8_t* rowA, const uint8_t* rowB, int b, int c32, const uint8_t* dig,
                                           const float* sxf, const float (&xw)[(MT + 1) / 2], int g, int t, AccT<MT>& acc) {
   block_q5_par<MT, false, true>(rowA + b * 24, rowB + b * 24, c32, dig, sxf, xw, g, t, acc);  // 24-byte blocks stay word aligned
+}
+
+// Q4_1: 20-byte blocks {d, m, 16 quant bytes}; codes 0..15 as an unsigned operand, the offset like Q5_1's
+template <int MT>
+__device__ __forceinline__ void block_q41(const uint8_t* rowA, const uint8_t* rowB, int b, int c32, const uint8_t* dig,
+                                          const float* sxf, const float (&xw)[(MT + 1) / 2], int g, int t, AccT<MT>& acc) {
+  constexpr int NT = (MT + 1) / 2;
+  const uint8_t* pA = rowA + b * 20;  // 20-byte blocks stay word aligned
+  const uint8_t* pB = rowB + b * 20;
+  const uint32_t wA = *(const uint32_t*)(pA + 4 + 4 * t), wB = *(const uint32_t*)(pB + 4 + 4 * t);
+  constexpr uint32_t M4 = 0x0f0f0f0fu;
+  const uint32_t a0 = wA & M4, a2 = (wA >> 4) & M4, a1 = wB & M4, a3 = (wB >> 4) & M4;
+  const uint32_t hdA = *(const uint32_t*)pA, hdB = *(const uint32_t*)pB;
+  const float dA = h2f(hdA & 0xffffu), dB = h2f(hdB & 0xffffu);
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const uint8_t* dp = plane_of<MT>(dig, nt, g) + c32 * 32 + 4 * t;
+    int c[4];
+    mma_k32(c, a0, a1, a2, a3, *(const uint32_t*)dp, *(const uint32_t*)(dp + 16));
+    acc.y[nt][0] = fmaf((float)(c[0] + 256 * c[1]), dA * xw[nt], acc.y[nt][0]);
+    acc.y[nt][2] = fmaf((float)(c[2] + 256 * c[3]), dB * xw[nt], acc.y[nt][2]);
+  }
+  if (t == (c32 & 3)) {
+    const float mA = h2f(hdA >> 16), mB = h2f(hdB >> 16);
+#pragma unroll
+    for (int k = 0; k < MT; ++k) {
+      const float sx = sxf[k * (Sp<MT>::SPAN / 32) + c32];
+      acc.mn[0][k] = fmaf(-mA, sx, acc.mn[0][k]);
+      acc.mn[1][k] = fmaf(-mB, sx, acc.mn[1][k]);
+    }
+  }
 }
 
 // ---- where activations come from ---------------------------------------------------------

@@ -218,7 +218,7 @@ def test_gemv_matches_cpu_row_kernels(ex, orc, name, path):
     ex.set_path(0)
 
 
-@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0", "Q4_0", "Q5_0", "Q5_1"])
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0", "Q4_0", "Q5_0", "Q5_1", "Q4_1", "Q5_K"])
 def test_tensor_core_gemv_handles_awkward_activations(ex, orc, name):
     """Outliers, tiny values, zero blocks and a non-finite activation through the digit split."""
     kind = ALL[name]
@@ -334,7 +334,7 @@ def test_device_generator_matches_host_generator(ex, name):
     m.free()
 
 
-@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0", "Q4_0", "Q5_1"])
+@pytest.mark.parametrize("name", ["Q4_K", "Q6_K", "Q8_0", "Q4_0", "Q5_1", "Q4_1", "Q5_K"])
 def test_a_row_of_activations_gives_the_same_bits_alone_and_inside_a_batch(ex, name):
     """The f32-faithful kernels hand their partial sums over every 4096 columns whatever the number of activation
     rows, so one activation row alone (its digit planes span 8192 columns) and the same row inside a batch of 2..8 give
