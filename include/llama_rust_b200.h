@@ -100,7 +100,7 @@ int llr_exec_counters(const llr_exec* exec, llr_counters* out);
  * it cannot take), 3 = the integer tensor-core kernel for any number of
  * activation rows (f32-faithful), 4 = the tcgen05 GEMM whenever it can take
  * the call.  Automatic choice: up to 63 activation rows as 3, from 64 rows the
- * tcgen05 GEMM for Q4_K/Q6_K/Q8_0/Q5_0/Q5_1/Q4_0 (16-bit operands, binary16 when
+ * tcgen05 GEMM for every block-quantized format (16-bit operands, binary16 when
  * the weights' range allows, else bfloat16: relative L2 error of a result up to
  * 4e-3 against the f32 row kernels, 3e-4 typical with binary16).
  * Also read once from the environment variable LLR_GEMV_PATH

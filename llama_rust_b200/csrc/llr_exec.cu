@@ -813,7 +813,7 @@ int llr_gemm_device_noalloc(llr_exec* e, const llr_matrix* m, size_t tokens, con
   const MatView v = view_of(m);
   if (!gemm_tc_supported(v, (int64_t)tokens))
     return fail(e, LLR_ERR_INVALID,
-                "the allocation-free GEMM takes Q4_K, Q8_0, Q5_0 or Q5_1 with cols % 256 == 0 and at least 16 activation rows");
+                "the allocation-free GEMM takes the block-quantized formats with cols % 256 == 0 (Q6_K: % 2048) and at least 16 activation rows");
   size_t need = 0;
   if (!mul_ok(tokens, (size_t)v.cols, &need) || !mul_ok(need, 2, &need) || need > gemm_tc_static_scratch_limit())
     return fail(e, LLR_ERR_INVALID, "tokens * cols * 2 = " + std::to_string(need) + " bytes exceeds the built-in staging area of " +

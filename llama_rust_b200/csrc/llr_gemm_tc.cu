@@ -74,6 +74,8 @@ template <> struct Pk<DT_Q8_0> { static constexpr int RB = 272, PITCH = 272; };
 template <> struct Pk<DT_Q5_0> { static constexpr int RB = 176, PITCH = 176; };
 template <> struct Pk<DT_Q4_0> { static constexpr int RB = 144, PITCH = 144; };
 template <> struct Pk<DT_Q5_1> { static constexpr int RB = 192, PITCH = 208; };
+template <> struct Pk<DT_Q4_1> { static constexpr int RB = 160, PITCH = 176; };
+template <> struct Pk<DT_Q5_K> { static constexpr int RB = 176, PITCH = 176; };
 // Q6_K blocks are 210 bytes: the block of macro-step ms starts at 210*ms, which is a multiple of 16 bytes only
 // for every eighth step.  The copy starts at the 16-byte boundary below (TMA needs that) and is 240 bytes wide
 // (14 bytes of lead at most + 210, rounded up to an odd number of 16-byte chunks); the decoder adds the lead back.
@@ -300,6 +302,48 @@ __device__ __forceinline__ void dequant_sub(uint32_t prow, uint32_t (&out)[16], 
     const float nb = fmaf(hi ? -64.0f : -1024.0f, a, -(dmin * (float)mn));
 #pragma unroll
     for (int i = 0; i < 8; ++i) emit4r(q[i], mask, magic, a, nb, out[2 * i], out[2 * i + 1]);
+  } else if constexpr (DT == DT_Q5_K) {
+    // the Q4_K header, then 32 bytes whose bit sb is the fifth bit of column l of sub-block sb, then the nibbles
+    const int sb = SB < 0 ? rsb : SB;
+    uint32_t hdr[4], q[8], fh[8];
+    lds_chunks<1>(prow, hdr);
+    lds_chunks<2>(prow + 16, fh);
+    lds_chunks<2>(prow + 48 + 32 * (sb >> 1), q);
+    const float d = h2f(hdr[0] & 0xffffu), dmin = h2f(hdr[0] >> 16);
+    const int sh = 8 * (sb & 3);
+    const uint32_t b_lo = (hdr[1] >> sh) & 255u, b_mid = (hdr[2] >> sh) & 255u, b_hi = (hdr[3] >> sh) & 255u;
+    uint32_t sc, mn;
+    if (sb < 4) { sc = b_lo & 63u; mn = b_mid & 63u; }
+    else { sc = (b_hi & 15u) | ((b_lo >> 6) << 4); mn = (b_hi >> 4) | ((b_mid >> 6) << 4); }
+    const float a = d * (float)sc;
+    const float nb = fmaf(-1024.0f, a, -(dmin * (float)mn));
+    const int nsh = 4 * (sb & 1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t c = ((q[i] >> nsh) & 0x0f0f0f0fu) | (((fh[i] >> sb) & 0x01010101u) << 4);
+      emit4<0x00ff00ffu, 0x64006400u>(c, a, nb, out[2 * i], out[2 * i + 1]);
+    }
+  } else if constexpr (DT == DT_Q4_1) {
+    // 20-byte blocks: d, m, sixteen bytes whose low nibbles are columns 0..15 and high nibbles 16..31; w = q d + m
+    constexpr int C0 = (20 * SB) / 16, OFF = 20 * SB - 16 * C0, NCH = (OFF + 20 + 15) / 16;
+    uint32_t w[4 * NCH + 1];
+    {
+      uint32_t t[4 * NCH];
+      lds_chunks<NCH>(prow + 16 * C0, t);
+#pragma unroll
+      for (int i = 0; i < 4 * NCH; ++i) w[i] = t[i];
+      w[4 * NCH] = 0;
+    }
+    const float d = h2f(h_at<OFF>(w));
+    const float nb = fmaf(-1024.0f, d, h2f(h_at<OFF + 2>(w)));
+    auto go = [&](auto I) {
+      constexpr int i = decltype(I)::value;
+      const uint32_t qs = w_at<OFF + 4 + 4 * i>(w);
+      emit4<0x00ff00ffu, 0x64006400u>(qs & 0x0f0f0f0fu, d, nb, out[2 * i], out[2 * i + 1]);
+      emit4<0x00ff00ffu, 0x64006400u>((qs >> 4) & 0x0f0f0f0fu, d, nb, out[8 + 2 * i], out[8 + 2 * i + 1]);
+    };
+    go(std::integral_constant<int, 0>{}); go(std::integral_constant<int, 1>{});
+    go(std::integral_constant<int, 2>{}); go(std::integral_constant<int, 3>{});
   } else if constexpr (DT == DT_Q8_0) {
     constexpr int C0 = (34 * SB) / 16, OFF = 34 * SB - 16 * C0;
     uint32_t w[12];
@@ -414,6 +458,46 @@ __device__ __forceinline__ void dequant_sub_h(uint32_t prow, uint32_t (&out)[16]
 #pragma unroll
       for (int i = 0; i < 8; ++i) emit4h<0x000f000fu, 0x64006400u>(q[i], __float2half2_rn(1024.f), a, nb, out[2 * i], out[2 * i + 1]);
     }
+  } else if constexpr (DT == DT_Q5_K) {
+    const int sb = SB < 0 ? rsb : SB;
+    uint32_t hdr[4], q[8], fh[8];
+    lds_chunks<1>(prow, hdr);
+    lds_chunks<2>(prow + 16, fh);
+    lds_chunks<2>(prow + 48 + 32 * (sb >> 1), q);
+    const float d = h2f(hdr[0] & 0xffffu), dmin = h2f(hdr[0] >> 16);
+    const int sh = 8 * (sb & 3);
+    const uint32_t b_lo = (hdr[1] >> sh) & 255u, b_mid = (hdr[2] >> sh) & 255u, b_hi = (hdr[3] >> sh) & 255u;
+    uint32_t sc, mn;
+    if (sb < 4) { sc = b_lo & 63u; mn = b_mid & 63u; }
+    else { sc = (b_hi & 15u) | ((b_lo >> 6) << 4); mn = (b_hi >> 4) | ((b_mid >> 6) << 4); }
+    const __half2 a = __float2half2_rn(d * (float)sc), nb = __float2half2_rn(-(dmin * (float)mn));
+    const __half2 off = __float2half2_rn(1024.f);
+    const int nsh = 4 * (sb & 1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t c = ((q[i] >> nsh) & 0x0f0f0f0fu) | (((fh[i] >> sb) & 0x01010101u) << 4);
+      emit4h<0x00ff00ffu, 0x64006400u>(c, off, a, nb, out[2 * i], out[2 * i + 1]);
+    }
+  } else if constexpr (DT == DT_Q4_1) {
+    constexpr int C0 = (20 * SB) / 16, OFF = 20 * SB - 16 * C0, NCH = (OFF + 20 + 15) / 16;
+    uint32_t w[4 * NCH + 1];
+    {
+      uint32_t t[4 * NCH];
+      lds_chunks<NCH>(prow + 16 * C0, t);
+#pragma unroll
+      for (int i = 0; i < 4 * NCH; ++i) w[i] = t[i];
+      w[4 * NCH] = 0;
+    }
+    const uint32_t dh = h_at<OFF>(w), mh = h_at<OFF + 2>(w);
+    const __half2 d = bits_h2(dh | (dh << 16)), off = __float2half2_rn(1024.f), nb = bits_h2(mh | (mh << 16));
+    auto go = [&](auto I) {
+      constexpr int i = decltype(I)::value;
+      const uint32_t qs = w_at<OFF + 4 + 4 * i>(w);
+      emit4h<0x00ff00ffu, 0x64006400u>(qs & 0x0f0f0f0fu, off, d, nb, out[2 * i], out[2 * i + 1]);
+      emit4h<0x00ff00ffu, 0x64006400u>((qs >> 4) & 0x0f0f0f0fu, off, d, nb, out[8 + 2 * i], out[8 + 2 * i + 1]);
+    };
+    go(std::integral_constant<int, 0>{}); go(std::integral_constant<int, 1>{});
+    go(std::integral_constant<int, 2>{}); go(std::integral_constant<int, 3>{});
   } else if constexpr (DT == DT_Q8_0) {
     constexpr int C0 = (34 * SB) / 16, OFF = 34 * SB - 16 * C0;
     uint32_t w[12];
@@ -532,11 +616,11 @@ __device__ __forceinline__ void gemm_tc_tile(const CUtensorMap* wmap_p, const CU
         if constexpr (F16) dequant_sub_h<DT, -1>(prow, out, 2 * kq + h, lead);
         else dequant_sub<DT, -1>(prow, out, 2 * kq + h, lead);
       } else if constexpr (F16) {
-        if constexpr (DT == DT_Q4_K) dequant_sub_h<DT, -1>(prow, out, 2 * kq + h);
+        if constexpr (DT == DT_Q4_K || DT == DT_Q5_K) dequant_sub_h<DT, -1>(prow, out, 2 * kq + h);
         else if (h == 0) dequant_sub_h<DT, 2 * kq>(prow, out);
         else dequant_sub_h<DT, 2 * kq + 1>(prow, out);
       } else {
-        if constexpr (DT == DT_Q4_K) dequant_sub<DT, -1>(prow, out, 2 * kq + h);
+        if constexpr (DT == DT_Q4_K || DT == DT_Q5_K) dequant_sub<DT, -1>(prow, out, 2 * kq + h);
         else if (h == 0) dequant_sub<DT, 2 * kq>(prow, out);
         else dequant_sub<DT, 2 * kq + 1>(prow, out);
       }
@@ -844,7 +928,8 @@ __global__ void expert_rows_16bit_kernel(const float* __restrict__ x, const int*
 // 0x7f800000 or more.
 template <int DT>
 __global__ void weight_bound_kernel(const uint8_t* __restrict__ W, int64_t n_blocks, unsigned int* __restrict__ out) {
-  constexpr int BB = DT == DT_Q4_K ? 144 : DT == DT_Q6_K ? 210 : DT == DT_Q8_0 ? 34 : DT == DT_Q5_0 ? 22 : DT == DT_Q4_0 ? 18 : 24;
+  constexpr int BB = DT == DT_Q4_K ? 144 : DT == DT_Q5_K ? 176 : DT == DT_Q6_K ? 210 : DT == DT_Q8_0 ? 34 : DT == DT_Q5_0 ? 22
+                     : DT == DT_Q4_0 ? 18 : DT == DT_Q4_1 ? 20 : 24;
   float m = 0.f;
   for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b < n_blocks; b += (int64_t)gridDim.x * blockDim.x) {
     const uint16_t* hp = (const uint16_t*)(W + b * BB);
@@ -852,6 +937,8 @@ __global__ void weight_bound_kernel(const uint8_t* __restrict__ W, int64_t n_blo
     float bound;
     if (DT == DT_Q6_K) bound = d * (128.f * 32.f);  // |scale| <= 128, |c - 32| <= 32
     else if (DT == DT_Q4_K) bound = d * (63.f * 15.f) + fabsf(__half2float(__ushort_as_half(hp[1]))) * 63.f;
+    else if (DT == DT_Q5_K) bound = d * (63.f * 31.f) + fabsf(__half2float(__ushort_as_half(hp[1]))) * 63.f;
+    else if (DT == DT_Q4_1) bound = d * 15.f + fabsf(__half2float(__ushort_as_half(hp[1])));
     else if (DT == DT_Q8_0) bound = d * 128.f;
     else if (DT == DT_Q5_0) bound = d * 16.f;
     else if (DT == DT_Q4_0) bound = d * 8.f;
@@ -922,7 +1009,9 @@ cudaError_t launch_dt(const MatView& m, const void* xb, const float* xscale, flo
 }  // namespace
 
 bool gemm_tc_supported(const MatView& m, int64_t tokens) {
-  if (m.dtype != DT_Q4_K && m.dtype != DT_Q6_K && m.dtype != DT_Q8_0 && m.dtype != DT_Q5_0 && m.dtype != DT_Q5_1 && m.dtype != DT_Q4_0) return false;
+  if (m.dtype != DT_Q4_K && m.dtype != DT_Q6_K && m.dtype != DT_Q8_0 && m.dtype != DT_Q5_0 && m.dtype != DT_Q5_1 && m.dtype != DT_Q4_0 &&
+      m.dtype != DT_Q4_1 && m.dtype != DT_Q5_K)
+    return false;
   if (m.dtype == DT_Q6_K && m.cols % 2048 != 0) return false;  // the tensor map wants rows a multiple of 16 bytes apart: 8 x 210
   if (tokens < 16 || tokens > (1 << 24) || m.rows <= 0 || m.rows > (1 << 30)) return false;
   if (m.cols % MACRO != 0 || m.cols <= 0 || m.cols > (1 << 30)) return false;
@@ -950,7 +1039,7 @@ size_t gemm_tc_scratch_bytes(const MatView& m, int64_t tokens) {
 }
 
 cudaError_t launch_weight_bound(const MatView& m, unsigned int* out_dev, cudaStream_t stream, uint64_t* launches) {
-  const int64_t nb = m.rows * (m.cols / (m.dtype == DT_Q4_K || m.dtype == DT_Q6_K ? 256 : 32));
+  const int64_t nb = m.rows * (m.cols / (m.dtype == DT_Q4_K || m.dtype == DT_Q6_K || m.dtype == DT_Q5_K ? 256 : 32));
   int64_t blocks = (nb + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   cudaError_t e = cudaMemsetAsync(out_dev, 0, sizeof(unsigned int), stream);
@@ -962,6 +1051,8 @@ cudaError_t launch_weight_bound(const MatView& m, unsigned int* out_dev, cudaStr
     case DT_Q5_0: weight_bound_kernel<DT_Q5_0><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
     case DT_Q4_0: weight_bound_kernel<DT_Q4_0><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
     case DT_Q5_1: weight_bound_kernel<DT_Q5_1><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
+    case DT_Q4_1: weight_bound_kernel<DT_Q4_1><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
+    case DT_Q5_K: weight_bound_kernel<DT_Q5_K><<<(unsigned)blocks, 256, 0, stream>>>(m.w, nb, out_dev); break;
     default: return cudaErrorInvalidValue;
   }
   if (launches) ++*launches;
@@ -1005,6 +1096,8 @@ cudaError_t launch_gemm_tc(const MatView& m, const float* x, float* y, int64_t t
     case DT_Q5_0: e = LLR_TC(DT_Q5_0); break;
     case DT_Q4_0: e = LLR_TC(DT_Q4_0); break;
     case DT_Q5_1: e = LLR_TC(DT_Q5_1); break;
+    case DT_Q4_1: e = LLR_TC(DT_Q4_1); break;
+    case DT_Q5_K: e = LLR_TC(DT_Q5_K); break;
     default: return cudaErrorInvalidValue;
   }
 #undef LLR_TC
@@ -1130,6 +1223,8 @@ cudaError_t launch_gemm_tc_grouped(const GemmGroupSpec* specs, int n, bool f16, 
     case DT_Q5_0: e = launch_grouped_dt<DT_Q5_0>(specs, n, f16, desc_dev, stream, err_flag); break;
     case DT_Q4_0: e = launch_grouped_dt<DT_Q4_0>(specs, n, f16, desc_dev, stream, err_flag); break;
     case DT_Q5_1: e = launch_grouped_dt<DT_Q5_1>(specs, n, f16, desc_dev, stream, err_flag); break;
+    case DT_Q4_1: e = launch_grouped_dt<DT_Q4_1>(specs, n, f16, desc_dev, stream, err_flag); break;
+    case DT_Q5_K: e = launch_grouped_dt<DT_Q5_K>(specs, n, f16, desc_dev, stream, err_flag); break;
     default: return cudaErrorInvalidValue;
   }
   if (e == cudaSuccess && launches) ++*launches;

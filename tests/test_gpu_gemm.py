@@ -31,7 +31,8 @@ def _bounds(kind, rows, cols, w, x, tokens, orc):
 
 @pytest.mark.parametrize("name,rows,cols", [("Q4_K", 300, 1024), ("Q8_0", 256, 1536), ("Q5_0", 130, 1024),
                                             ("Q5_1", 128, 2048), ("Q4_K", 512, 4096), ("Q6_K", 300, 2048),
-                                            ("Q6_K", 256, 6144), ("Q4_0", 200, 1024), ("Q4_0", 128, 4096)])
+                                            ("Q6_K", 256, 6144), ("Q4_0", 200, 1024), ("Q4_0", 128, 4096),
+                                            ("Q5_K", 300, 1024), ("Q5_K", 128, 4096), ("Q4_1", 200, 1024), ("Q4_1", 128, 4096)])
 @pytest.mark.parametrize("tokens", [64, 100, 256, 300])
 def test_tensor_core_gemm_matches_cpu_f32_reference(ex, orc, name, rows, cols, tokens):
     kind = ALL[name]
@@ -105,7 +106,7 @@ def test_operand_format_follows_weight_range(ex, orc):
 
 @pytest.mark.parametrize("name,rows,cols", [("Q4_K", 14336, 4096), ("Q8_0", 4096, 14336), ("Q5_0", 4096, 4096),
                                             ("Q5_1", 4096, 4096), ("Q6_K", 4096, 14336), ("Q6_K", 1024, 4096),
-                                            ("Q4_0", 4096, 4096)])
+                                            ("Q4_0", 4096, 4096), ("Q5_K", 4096, 4096), ("Q4_1", 4096, 4096)])
 @pytest.mark.parametrize("tokens", [64, 256, 1024])
 def test_config4_full_size_shapes_on_sampled_rows(ex, orc, name, rows, cols, tokens):
     """BASELINE config 4 at its full sizes (Q8_0 4096x14336 runs split along K).  The device
