@@ -239,8 +239,8 @@ int llr_matmul_device(llr_exec* exec, const llr_matrix* matrix, size_t tokens, c
  * buffer could fail or evict; code inside a region where the implicit device
  * synchronization of cudaMalloc/cudaFree is not acceptable; hosts that hand this
  * library a fixed memory budget up front.  Same tensor-core GEMM as the
- * automatic path takes from 64 activation rows on (Q4_K, Q6_K, Q8_0, Q5_0, Q5_1,
- * Q4_0; cols % 256 == 0, Q6_K cols % 2048 == 0; tokens >= 16; 16-bit operands -- binary16 when the matrix's
+ * automatic path takes from 64 activation rows on (every block-quantized format;
+ * cols % 256 == 0, Q6_K cols % 2048 == 0; tokens >= 16; 16-bit operands -- binary16 when the matrix's
  * weights fit its range, else bfloat16 -- with f32 accumulation), but the
  * 16-bit copy of the activations is staged in a fixed 32 MiB array built into the
  * library (every GPU that loads the library holds it until the process exits)
