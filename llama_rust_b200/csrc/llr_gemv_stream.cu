@@ -67,8 +67,7 @@ constexpr int NTHREADS = (CW + 2) * 32;   // + producer + reducer
 constexpr int NRB = 4;                    // reduction buffers
 constexpr int PART_COLS = 4096;           // columns between two hand-offs of partial sums to the reducer
 constexpr int MAX_CHUNK = Lay<DT_Q4_K, 1>::CHUNK;
-static_assert(Lay<DT_Q6_K, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q8_0, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q4_0, 1>::CHUNK <= MAX_CHUNK &&
-              Lay<DT_Q5_0, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q5_1, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q4_1, 1>::CHUNK <= MAX_CHUNK, "ring stage");
+static_assert(Lay<DT_Q6_K, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q8_0, 1>::CHUNK <= MAX_CHUNK, "ring stage");
 // Sharded programs keep two counter arrays in the arena header: [0, 4096) this rank's CTAs per
 // phase, [4096, 8192) arrivals of the peers per phase.
 constexpr int PEER_COUNTER_OFFSET = 4096;
@@ -86,25 +85,33 @@ template <int MT> struct SLay {
 };
 
 // How a stage of 16 rows x kseg columns reaches shared memory.
-//   Q4_K: one 3-D TMA box over (36 words of a block, rows, blocks of the row): the stage is laid
-//         out [block][row][144 bytes], whose fragment reads are conflict-free without padding;
+//   Q4_K, Q5_K, Q4_0, Q4_1, Q5_0, Q5_1: one 3-D TMA box over (words of a 256-column group, rows, groups of
+//         the row): the stage is laid out [group][row][pitch].  A group is one K-quant block or eight 32-column
+//         blocks; its bytes are a multiple of 16, which a box needs.  The pitch is the group's size, except
+//         where that would put the fragment reads of eight rows on the same banks (Q4_1: 160 bytes, Q5_1: 192):
+//         there the box is 16 bytes wider than the tensor's inner extent, and the copy engine fills the rest
+//         with zeros without reading anything.  With the row order of q4k_row() the pitches 144, 176 and 208
+//         spread the 4- and 8-byte fragment reads of a warp over all banks;
 //   Q6_K: one 2-D box over (8-byte words of the row, rows): rows 1680 bytes apart (16 mod 128);
-//   Q8_0: one bulk copy per row into a padded pitch (its 2176-byte pieces exceed a box row).
+//   Q8_0: one bulk copy per row into a padded pitch.
 // One instruction per stage matters: the TMA unit of an SM accepts a bulk copy every ~40 ns
 // whatever its size, which capped sixteen 1680-byte row copies per stage at 87 % of the copy peak.
-struct Geom { int kseg, segb, rs, box_bytes; };
-constexpr int Q4K_STAGE_BLOCKS = Fmt<DT_Q4_K>::KSEG / 256;
-constexpr int Q5K_STAGE_BLOCKS = Fmt<DT_Q5_K>::KSEG / 256;   // the 176-byte blocks are laid out like Q4_K's
-static_assert(Q5K_STAGE_BLOCKS * 16 * 176 <= MAX_CHUNK, "ring stage");
+struct Geom { int kseg, segb, rs, box_bytes, pitch; };
+// words of a 256-column group in memory, and words of a box row in the stage
+__host__ __device__ constexpr int box3_words(int dt) {
+  return dt == DT_Q4_K || dt == DT_Q4_0 ? 36 : dt == DT_Q5_K || dt == DT_Q5_0 ? 44 : dt == DT_Q5_1 ? 48 : dt == DT_Q4_1 ? 40 : 0;
+}
+__host__ __device__ constexpr int box3_pitch_words(int dt) { return dt == DT_Q5_1 ? 52 : dt == DT_Q4_1 ? 44 : box3_words(dt); }
+__host__ __device__ constexpr int box3_kseg(int dt) { return dt == DT_Q4_K || dt == DT_Q4_0 ? 4096 : 2048; }
+static_assert(Fmt<DT_Q4_K>::KSEG == box3_kseg(DT_Q4_K) && Fmt<DT_Q5_K>::KSEG == box3_kseg(DT_Q5_K) && Fmt<DT_Q4_0>::KSEG == box3_kseg(DT_Q4_0) &&
+              Fmt<DT_Q5_0>::KSEG == box3_kseg(DT_Q5_0) && Fmt<DT_Q5_1>::KSEG == box3_kseg(DT_Q5_1) && Fmt<DT_Q4_1>::KSEG == box3_kseg(DT_Q4_1), "stage length");
+__host__ __device__ constexpr int box3_bytes(int dt) { return box3_kseg(dt) / 256 * 16 * box3_pitch_words(dt) * 4; }
+static_assert(box3_bytes(DT_Q4_K) <= MAX_CHUNK && box3_bytes(DT_Q5_K) <= MAX_CHUNK && box3_bytes(DT_Q4_0) <= MAX_CHUNK &&
+              box3_bytes(DT_Q5_0) <= MAX_CHUNK && box3_bytes(DT_Q5_1) <= MAX_CHUNK && box3_bytes(DT_Q4_1) <= MAX_CHUNK, "ring stage");
 __device__ __forceinline__ Geom geom_of(int dtype) {
-  if (dtype == DT_Q4_K) return {Fmt<DT_Q4_K>::KSEG, Lay<DT_Q4_K, 1>::SEGB, Lay<DT_Q4_K, 1>::RS, Q4K_STAGE_BLOCKS * 16 * 144};
-  if (dtype == DT_Q6_K) return {Fmt<DT_Q6_K>::KSEG, Lay<DT_Q6_K, 1>::SEGB, Lay<DT_Q6_K, 1>::RS, 16 * Lay<DT_Q6_K, 1>::SEGB};
-  if (dtype == DT_Q4_0) return {Fmt<DT_Q4_0>::KSEG, Lay<DT_Q4_0, 1>::SEGB, Lay<DT_Q4_0, 1>::RS, 0};
-  if (dtype == DT_Q5_0) return {Fmt<DT_Q5_0>::KSEG, Lay<DT_Q5_0, 1>::SEGB, Lay<DT_Q5_0, 1>::RS, 0};
-  if (dtype == DT_Q5_1) return {Fmt<DT_Q5_1>::KSEG, Lay<DT_Q5_1, 1>::SEGB, Lay<DT_Q5_1, 1>::RS, 0};
-  if (dtype == DT_Q4_1) return {Fmt<DT_Q4_1>::KSEG, Lay<DT_Q4_1, 1>::SEGB, Lay<DT_Q4_1, 1>::RS, 0};
-  if (dtype == DT_Q5_K) return {Fmt<DT_Q5_K>::KSEG, Lay<DT_Q5_K, 1>::SEGB, Lay<DT_Q5_K, 1>::RS, Q5K_STAGE_BLOCKS * 16 * 176};
-  return {Fmt<DT_Q8_0>::KSEG, Lay<DT_Q8_0, 1>::SEGB, Lay<DT_Q8_0, 1>::RS, 0};
+  if (box3_words(dtype)) return {box3_kseg(dtype), 0, 0, box3_bytes(dtype), 4 * box3_pitch_words(dtype)};
+  if (dtype == DT_Q6_K) return {Fmt<DT_Q6_K>::KSEG, Lay<DT_Q6_K, 1>::SEGB, Lay<DT_Q6_K, 1>::RS, 16 * Lay<DT_Q6_K, 1>::SEGB, 0};
+  return {Fmt<DT_Q8_0>::KSEG, Lay<DT_Q8_0, 1>::SEGB, Lay<DT_Q8_0, 1>::RS, 0, 0};
 }
 static_assert(Lay<DT_Q6_K, 1>::RS == Lay<DT_Q6_K, 1>::SEGB, "Q6_K rows lie densely in a stage");
 
@@ -268,8 +275,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
                 if (gm.box_bytes) {
                   // rows and blocks beyond the matrix are filled with zeros and still counted
                   mbar_expect_tx(&full[stage], (uint32_t)gm.box_bytes);
-                  if (dtype == DT_Q4_K) tma_box_3d(dst, map, 0, tile * 16, seg * Q4K_STAGE_BLOCKS, &full[stage], stream_once);
-                  else if (DTFIX == DT_Q5_K) tma_box_3d(dst, map, 0, tile * 16, seg * Q5K_STAGE_BLOCKS, &full[stage], stream_once);
+                  if (dtype != DT_Q6_K) tma_box_3d(dst, map, 0, tile * 16, seg * (gm.kseg / 256), &full[stage], stream_once);
                   else tma_box_2d(dst, map, seg * (Lay<DT_Q6_K, 1>::SEGB / 8), tile * 16, &full[stage], stream_once);
                   continue;
                 }
@@ -548,33 +554,37 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
               for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
                 float xw[NT];
                 group_scales<MT>(xsi, sub * (gm.kseg / 256) + b8, t, (t & 1) ? 4096.f : 0.0625f, xw);
+                const uint8_t* grpA = chunk + (b8 * 16 + q4k_row(g)) * gm.pitch;  // stage layout [group][row][pitch]
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  block_q40<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, xw, g, t, acc);
+                  block_q40<MT>(grpA, grpA + 8 * gm.pitch, i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, xw, g, t, acc);
               }
             } else if (DTFIX == DT_Q5_0) {
               for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
                 float xw[NT];
                 group_scales<MT>(xsi, sub * (gm.kseg / 256) + b8, t, (t & 1) ? 8192.f : 0.125f, xw);
+                const uint8_t* grpA = chunk + (b8 * 16 + q4k_row(g)) * gm.pitch;  // stage layout [group][row][pitch]
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  block_q50<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xw, g, t, acc);
+                  block_q50<MT>(grpA, grpA + 8 * gm.pitch, i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xw, g, t, acc);
               }
             } else if (DTFIX == DT_Q5_1) {
               for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
                 float xw[NT];
                 group_scales<MT>(xsi, sub * (gm.kseg / 256) + b8, t, (t & 1) ? 65536.f : 1.f, xw);
+                const uint8_t* grpA = chunk + (b8 * 16 + q4k_row(g)) * gm.pitch;  // stage layout [group][row][pitch]
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  block_q51<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xw, g, t, acc);
+                  block_q51<MT>(grpA, grpA + 8 * gm.pitch, i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xw, g, t, acc);
               }
             } else if (DTFIX == DT_Q4_1) {
               for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
                 float xw[NT];
                 group_scales<MT>(xsi, sub * (gm.kseg / 256) + b8, t, (t & 1) ? 65536.f : 1.f, xw);
+                const uint8_t* grpA = chunk + (b8 * 16 + q4k_row(g)) * gm.pitch;  // stage layout [group][row][pitch]
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  block_q41<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xw, g, t, acc);
+                  block_q41<MT>(grpA, grpA + 8 * gm.pitch, i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, sxf, xw, g, t, acc);
               }
             } else {
               for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
@@ -614,7 +624,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
 #pragma unroll
               for (int k = 0; k < MT; ++k)
                 if (k == tok) { mA = acc.mn[0][k]; mB = acc.mn[1][k]; }
-              const int gr = ((DTFIX >= 0 ? DTFIX : E.dtype) == DT_Q4_K || DTFIX == DT_Q5_K) ? q4k_row(g) : g;
+              const int gr = box3_words(DTFIX >= 0 ? DTFIX : E.dtype) ? q4k_row(g) : g;  // box stages hold the rows in that order
               myred[gr * MT + tok] = vA - mA;
               myred[(gr + 8) * MT + tok] = vB - mB;
             }
@@ -688,15 +698,16 @@ gemv_sharded_program_kernel(const ProgEntry* __restrict__ entries, const ProgPha
 // stays zeroed and is never used.
 bool encode_weight_map(const uint8_t* w, int dtype, int64_t rows, int64_t cols, int64_t row_bytes, CUtensorMap* map) {
   memset(map, 0, sizeof(*map));
-  if (dtype != DT_Q4_K && dtype != DT_Q6_K && dtype != DT_Q5_K) return true;
+  if (!box3_words(dtype) && dtype != DT_Q6_K) return true;
   EncodeTiledFn enc = tensor_map_encoder();
   if (!enc) return false;
   const cuuint32_t estr[3] = {1, 1, 1};
-  if (dtype == DT_Q4_K || dtype == DT_Q5_K) {
-    const cuuint32_t words = dtype == DT_Q4_K ? 36 : 44;
+  if (box3_words(dtype)) {
+    // a box row wider than the group (Q4_1, Q5_1) ends outside the tensor's inner extent: filled with zeros, not read
+    const cuuint32_t words = (cuuint32_t)box3_words(dtype);
     const cuuint64_t dims[3] = {words, (cuuint64_t)rows, (cuuint64_t)(cols / 256)};
     const cuuint64_t strides[2] = {(cuuint64_t)row_bytes, 4 * words};
-    const cuuint32_t box[3] = {words, 16, (cuuint32_t)(dtype == DT_Q4_K ? Q4K_STAGE_BLOCKS : Q5K_STAGE_BLOCKS)};
+    const cuuint32_t box[3] = {(cuuint32_t)box3_pitch_words(dtype), 16, (cuuint32_t)(box3_kseg(dtype) / 256)};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, (void*)w, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
   }

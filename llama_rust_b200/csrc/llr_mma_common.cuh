@@ -40,7 +40,7 @@ template <int DT> struct Fmt;
 template <> struct Fmt<DT_Q4_K> { static constexpr int KSEG = 4096, BB = 144, BE = 256; };
 template <> struct Fmt<DT_Q6_K> { static constexpr int KSEG = 2048, BB = 210, BE = 256; };
 template <> struct Fmt<DT_Q8_0> { static constexpr int KSEG = 2048, BB = 34, BE = 32; };
-template <> struct Fmt<DT_Q4_0> { static constexpr int KSEG = 2048, BB = 18, BE = 32; };
+template <> struct Fmt<DT_Q4_0> { static constexpr int KSEG = 4096, BB = 18, BE = 32; };
 template <> struct Fmt<DT_Q5_0> { static constexpr int KSEG = 2048, BB = 22, BE = 32; };
 template <> struct Fmt<DT_Q5_1> { static constexpr int KSEG = 2048, BB = 24, BE = 32; };
 template <> struct Fmt<DT_Q4_1> { static constexpr int KSEG = 2048, BB = 20, BE = 32; };
