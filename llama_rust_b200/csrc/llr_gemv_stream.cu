@@ -67,7 +67,7 @@ constexpr int NTHREADS = (CW + 2) * 32;   // + producer + reducer
 constexpr int NRB = 4;                    // reduction buffers
 constexpr int PART_COLS = 4096;           // columns between two hand-offs of partial sums to the reducer
 constexpr int MAX_CHUNK = Lay<DT_Q4_K, 1>::CHUNK;
-static_assert(Lay<DT_Q6_K, 1>::CHUNK <= MAX_CHUNK && Lay<DT_Q8_0, 1>::CHUNK <= MAX_CHUNK, "ring stage");
+static_assert(Lay<DT_Q6_K, 1>::CHUNK <= MAX_CHUNK, "ring stage");
 // Sharded programs keep two counter arrays in the arena header: [0, 4096) this rank's CTAs per
 // phase, [4096, 8192) arrivals of the peers per phase.
 constexpr int PEER_COUNTER_OFFSET = 4096;
@@ -85,33 +85,32 @@ template <int MT> struct SLay {
 };
 
 // How a stage of 16 rows x kseg columns reaches shared memory.
-//   Q4_K, Q5_K, Q4_0, Q4_1, Q5_0, Q5_1: one 3-D TMA box over (words of a 256-column group, rows, groups of
+//   Q4_K, Q5_K, Q8_0, Q4_0, Q4_1, Q5_0, Q5_1: one 3-D TMA box over (words of a 256-column group, rows, groups of
 //         the row): the stage is laid out [group][row][pitch].  A group is one K-quant block or eight 32-column
 //         blocks; its bytes are a multiple of 16, which a box needs.  The pitch is the group's size, except
 //         where that would put the fragment reads of eight rows on the same banks (Q4_1: 160 bytes, Q5_1: 192):
 //         there the box is 16 bytes wider than the tensor's inner extent, and the copy engine fills the rest
 //         with zeros without reading anything.  With the row order of q4k_row() the pitches 144, 176 and 208
 //         spread the 4- and 8-byte fragment reads of a warp over all banks;
-//   Q6_K: one 2-D box over (8-byte words of the row, rows): rows 1680 bytes apart (16 mod 128);
-//   Q8_0: one bulk copy per row into a padded pitch.
+//   Q6_K: one 2-D box over (8-byte words of the row, rows): rows 1680 bytes apart (16 mod 128).
 // One instruction per stage matters: the TMA unit of an SM accepts a bulk copy every ~40 ns
-// whatever its size, which capped sixteen 1680-byte row copies per stage at 87 % of the copy peak.
+// whatever its size: sixteen row copies per stage capped Q6_K at 87 % of the copy peak and held the 32-column
+// formats at 3.0-3.4 TB/s.
 struct Geom { int kseg, segb, rs, box_bytes, pitch; };
 // words of a 256-column group in memory, and words of a box row in the stage
 __host__ __device__ constexpr int box3_words(int dt) {
-  return dt == DT_Q4_K || dt == DT_Q4_0 ? 36 : dt == DT_Q5_K || dt == DT_Q5_0 ? 44 : dt == DT_Q5_1 ? 48 : dt == DT_Q4_1 ? 40 : 0;
+  return dt == DT_Q4_K || dt == DT_Q4_0 ? 36 : dt == DT_Q5_K || dt == DT_Q5_0 ? 44 : dt == DT_Q5_1 ? 48 : dt == DT_Q4_1 ? 40 : dt == DT_Q8_0 ? 68 : 0;
 }
 __host__ __device__ constexpr int box3_pitch_words(int dt) { return dt == DT_Q5_1 ? 52 : dt == DT_Q4_1 ? 44 : box3_words(dt); }
 __host__ __device__ constexpr int box3_kseg(int dt) { return dt == DT_Q4_K || dt == DT_Q4_0 ? 4096 : 2048; }
 static_assert(Fmt<DT_Q4_K>::KSEG == box3_kseg(DT_Q4_K) && Fmt<DT_Q5_K>::KSEG == box3_kseg(DT_Q5_K) && Fmt<DT_Q4_0>::KSEG == box3_kseg(DT_Q4_0) &&
-              Fmt<DT_Q5_0>::KSEG == box3_kseg(DT_Q5_0) && Fmt<DT_Q5_1>::KSEG == box3_kseg(DT_Q5_1) && Fmt<DT_Q4_1>::KSEG == box3_kseg(DT_Q4_1), "stage length");
+              Fmt<DT_Q5_0>::KSEG == box3_kseg(DT_Q5_0) && Fmt<DT_Q8_0>::KSEG == box3_kseg(DT_Q8_0) && Fmt<DT_Q5_1>::KSEG == box3_kseg(DT_Q5_1) && Fmt<DT_Q4_1>::KSEG == box3_kseg(DT_Q4_1), "stage length");
 __host__ __device__ constexpr int box3_bytes(int dt) { return box3_kseg(dt) / 256 * 16 * box3_pitch_words(dt) * 4; }
 static_assert(box3_bytes(DT_Q4_K) <= MAX_CHUNK && box3_bytes(DT_Q5_K) <= MAX_CHUNK && box3_bytes(DT_Q4_0) <= MAX_CHUNK &&
-              box3_bytes(DT_Q5_0) <= MAX_CHUNK && box3_bytes(DT_Q5_1) <= MAX_CHUNK && box3_bytes(DT_Q4_1) <= MAX_CHUNK, "ring stage");
+              box3_bytes(DT_Q5_0) <= MAX_CHUNK && box3_bytes(DT_Q8_0) <= MAX_CHUNK && box3_bytes(DT_Q5_1) <= MAX_CHUNK && box3_bytes(DT_Q4_1) <= MAX_CHUNK, "ring stage");
 __device__ __forceinline__ Geom geom_of(int dtype) {
   if (box3_words(dtype)) return {box3_kseg(dtype), 0, 0, box3_bytes(dtype), 4 * box3_pitch_words(dtype)};
-  if (dtype == DT_Q6_K) return {Fmt<DT_Q6_K>::KSEG, Lay<DT_Q6_K, 1>::SEGB, Lay<DT_Q6_K, 1>::RS, 16 * Lay<DT_Q6_K, 1>::SEGB, 0};
-  return {Fmt<DT_Q8_0>::KSEG, Lay<DT_Q8_0, 1>::SEGB, Lay<DT_Q8_0, 1>::RS, 0, 0};
+  return {Fmt<DT_Q6_K>::KSEG, Lay<DT_Q6_K, 1>::SEGB, Lay<DT_Q6_K, 1>::RS, 16 * Lay<DT_Q6_K, 1>::SEGB, 0};
 }
 static_assert(Lay<DT_Q6_K, 1>::RS == Lay<DT_Q6_K, 1>::SEGB, "Q6_K rows lie densely in a stage");
 
@@ -259,9 +258,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           const int dtype = DTFIX >= 0 ? DTFIX : E.dtype;
           const Geom gm = geom_of(dtype);
           const CUtensorMap* map = wk.maps + (PROGRAM ? P.first_entry + ei : 0);
-          const int cols = E.cols, rows = E.rows;
-          const int64_t row_bytes = E.row_bytes;
-          const uint8_t* w = E.w;
+          const int cols = E.cols;
           const int n_span = (cols + SPAN - 1) / SPAN;
           for (int span = 0; span < n_span; ++span) {
             const int span_cols = min(SPAN, cols - span * SPAN);
@@ -272,22 +269,10 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
                 if (ok && !mbar_wait(&empty[stage], (uint32_t)(((c / NST) & 1) ^ 1), abort_word, epoch)) { ok = false; report_error(err, 1); }
                 uint8_t* dst = ring + stage * MAX_CHUNK;
                 const int seg = span * (SPAN / gm.kseg) + sub;
-                if (gm.box_bytes) {
-                  // rows and blocks beyond the matrix are filled with zeros and still counted
-                  mbar_expect_tx(&full[stage], (uint32_t)gm.box_bytes);
-                  if (dtype != DT_Q6_K) tma_box_3d(dst, map, 0, tile * 16, seg * (gm.kseg / 256), &full[stage], stream_once);
-                  else tma_box_2d(dst, map, seg * (Lay<DT_Q6_K, 1>::SEGB / 8), tile * 16, &full[stage], stream_once);
-                  continue;
-                }
-                const int64_t seg_off = (int64_t)seg * gm.segb;
-                const int64_t left = row_bytes - seg_off;
-                const uint32_t bytes = (uint32_t)(left < gm.segb ? left : gm.segb);
-                mbar_expect_tx(&full[stage], 16 * bytes);
-                const uint8_t* src = w + (int64_t)(tile * 16) * row_bytes + seg_off;
-                const int last = rows - 1 - tile * 16;  // rows beyond the matrix refetch the last one
-#pragma unroll 4
-                for (int r = 0; r < 16; ++r)
-                  bulk_g2s_hint(dst + r * gm.rs, src + (int64_t)min(r, last) * row_bytes, bytes, &full[stage], stream_once);
+                // rows and groups beyond the matrix are filled with zeros and still counted
+                mbar_expect_tx(&full[stage], (uint32_t)gm.box_bytes);
+                if (dtype != DT_Q6_K) tma_box_3d(dst, map, 0, tile * 16, seg * (gm.kseg / 256), &full[stage], stream_once);
+                else tma_box_2d(dst, map, seg * (Lay<DT_Q6_K, 1>::SEGB / 8), tile * 16, &full[stage], stream_once);
               }
             }
           }
@@ -590,9 +575,10 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
               for (int b8 = warp; b8 < (seg_cols >> 8); b8 += CW) {
                 float xw[NT];
                 group_scales<MT>(xsi, sub * (gm.kseg / 256) + b8, t, (t & 1) ? 65536.f : 1.f, xw);
+                const uint8_t* grpA = chunk + (b8 * 16 + q4k_row(g)) * gm.pitch;
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                  block_q80<MT>(rowA, rowB, b8 * 8 + i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, xw, g, t, acc);
+                  block_q80<MT>(grpA, grpA + 8 * gm.pitch, i, sub * (gm.kseg / 32) + b8 * 8 + i, dig, xw, g, t, acc);
               }
             }
             __syncwarp();
@@ -694,8 +680,7 @@ gemv_sharded_program_kernel(const ProgEntry* __restrict__ entries, const ProgPha
   stream_body<MT, true, -1, true, false, FLOW>(wk, counters, run.epoch, err);
 }
 
-// Tensor map of one matrix for the stage loads (see Geom).  Q8_0 is copied row by row: its map
-// stays zeroed and is never used.
+// Tensor map of one matrix for the stage loads (see Geom).
 bool encode_weight_map(const uint8_t* w, int dtype, int64_t rows, int64_t cols, int64_t row_bytes, CUtensorMap* map) {
   memset(map, 0, sizeof(*map));
   if (!box3_words(dtype) && dtype != DT_Q6_K) return true;
