@@ -427,6 +427,40 @@ int llr_moe_route_device(llr_exec* exec, const llr_moe_layer* layer, size_t toke
 int llr_moe_experts_device(llr_exec* exec, const llr_moe_layer* layer, const uint32_t* counts,
                            const float* rows_dev, float* y_dev);
 
+/* Expert parallelism with the exchange inside the library: experts striped over the ranks (expert e on rank
+ * e % world, expertvm/src/place.rs:71-75), tokens sharded over the ranks, routed rows and their results moved
+ * between GPUs by peer stores from the kernels that gather and scatter them [the north star's all-to-all of token
+ * rows; grouped_routed_ffn decode.rs:10006, scatter_expert_rows :10263].  One process per GPU (or several
+ * executors of one process); no collective call, no host hop for rows; one small device-to-host copy of row counts
+ * per run sizes the expert launches.
+ *   arena: llr_moe_ep_arena_bytes(...) bytes of zeroed device memory per rank that the peers can write
+ *   (llr_shared_alloc / llr_shared_open); peer_arenas[g] is rank g's arena as mapped in this process (the entry of
+ *   this rank itself is ignored; may be NULL when world is 1).  layer: as llr_moe_ffn, with NULL gate/up/down for
+ *   every expert e with e % world != rank.  max_tokens bounds the tokens of this rank per run.
+ * A run is three calls, which llr_moe_ep_run makes in order:
+ *   llr_moe_ep_dispatch  routes this rank's tokens (x_dev: tokens x n_embd floats on the device) and stores each
+ *                        routed row into its expert's owner; enqueued, no synchronization;
+ *   llr_moe_ep_serve     waits on the device, bounded by llr_exec_set_wait_limit, until every rank's rows for this
+ *                        rank's experts have arrived, runs the experts on them and stores the results back into the
+ *                        senders; synchronizes the stream once (row counts);
+ *   llr_moe_ep_combine   waits (bounded) for the results of every owner and adds a token's rows times their router
+ *                        weights in ascending expert id into out_dev; ids_dev / w_dev (tokens * n_used, may be NULL)
+ *                        receive the routing decision; enqueued, no synchronization (llr_exec_synchronize ends the run).
+ * Every rank makes the same sequence of runs (a rank with no tokens of its own still passes at least one).  Ranks must
+ * reach a wait within the wait limit of each other, else the run fails with LLR_ERR_CUDA and the layer object has to be
+ * re-created on every rank.  Several ranks driven from ONE thread (executors on one or several GPUs) call dispatch
+ * on every rank first, then serve on every rank, then combine: no wait then ever spins.  With the f32-faithful
+ * kernels (llr_exec_set_path(exec, 3)) the output is bit-identical to llr_moe_ffn on the same tokens. */
+typedef struct llr_moe_ep llr_moe_ep;
+size_t llr_moe_ep_arena_bytes(uint32_t n_expert, uint32_t n_used, size_t n_embd, uint32_t world, size_t max_tokens);
+int llr_moe_ep_create(llr_exec* exec, const llr_moe_layer* layer, uint32_t world, uint32_t rank, size_t max_tokens,
+                      void* arena, size_t arena_bytes, void* const* peer_arenas, llr_moe_ep** out);
+int llr_moe_ep_dispatch(llr_moe_ep* ep, size_t tokens, const float* x_dev);
+int llr_moe_ep_serve(llr_moe_ep* ep);
+int llr_moe_ep_combine(llr_moe_ep* ep, float* out_dev, int32_t* ids_dev, float* w_dev);
+int llr_moe_ep_run(llr_moe_ep* ep, size_t tokens, const float* x_dev, float* out_dev, int32_t* ids_dev, float* w_dev);
+int llr_moe_ep_free(llr_moe_ep* ep);
+
 /* ---- device-resident Llama walk ------------------------------------------------------
  * The per-token walk of the plain llama architecture with everything on the device
  * [langtax/src/decode.rs: Llama::forward_layers :2737-3097 -- rmsnorm_inplace :11498, the

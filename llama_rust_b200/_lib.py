@@ -27,7 +27,8 @@ SYMBOLS = [
     "llr_exec_pin_key", "llr_plan_placement", "llr_gguf_open", "llr_gguf_open_bytes", "llr_gguf_close",
     "llr_gguf_last_error", "llr_gguf_info", "llr_gguf_tensor_at", "llr_gguf_find", "llr_gguf_read", "llr_gguf_kv_u32",
     "llr_gguf_kv_f32", "llr_gguf_kv_bits", "llr_gguf_kv_bool", "llr_gguf_kv_string", "llr_gguf_kv_i32s", "llr_gguf_kv_type",
-    "llr_gguf_upload", "llr_gguf_matmul", "llr_gguf_key",
+    "llr_gguf_upload", "llr_gguf_matmul", "llr_gguf_key", "llr_moe_ep_arena_bytes", "llr_moe_ep_create", "llr_moe_ep_dispatch",
+    "llr_moe_ep_serve", "llr_moe_ep_combine", "llr_moe_ep_run", "llr_moe_ep_free",
 ]
 ARENA_HEADER_BYTES = 65536
 
@@ -149,6 +150,14 @@ def load() -> C.CDLL:
     lib.llr_exec_set_wait_limit.argtypes = [vp, C.c_uint32]
     lib.llr_moe_route_device.argtypes = [vp, C.POINTER(MoeLayer), sz, vp, vp, vp]
     lib.llr_moe_experts_device.argtypes = [vp, C.POINTER(MoeLayer), C.POINTER(C.c_uint32), vp, vp]
+    lib.llr_moe_ep_arena_bytes.argtypes = [C.c_uint32, C.c_uint32, sz, C.c_uint32, sz]
+    lib.llr_moe_ep_arena_bytes.restype = sz
+    lib.llr_moe_ep_create.argtypes = [vp, C.POINTER(MoeLayer), C.c_uint32, C.c_uint32, sz, vp, sz, C.POINTER(vp), C.POINTER(vp)]
+    lib.llr_moe_ep_dispatch.argtypes = [vp, sz, vp]
+    lib.llr_moe_ep_serve.argtypes = [vp]
+    lib.llr_moe_ep_combine.argtypes = [vp, vp, vp, vp]
+    lib.llr_moe_ep_run.argtypes = [vp, sz, vp, vp, vp, vp]
+    lib.llr_moe_ep_free.argtypes = [vp]
     lib.llr_session_create.argtypes = [vp, C.POINTER(LlamaModel), C.POINTER(vp)]
     lib.llr_session_create_paged.argtypes = [vp, C.POINTER(LlamaModel), sz, sz, sz, C.POINTER(vp)]
     lib.llr_session_batch.argtypes = [vp, sz, vp, vp, vp, vp, vp]

@@ -17,6 +17,7 @@
 #include <atomic>
 #include <cstring>
 #include <list>
+#include <memory>
 #include <new>
 #include <string>
 #include <unordered_set>
@@ -1141,6 +1142,210 @@ int llr_moe_experts_device(llr_exec* e, const llr_moe_layer* L, const uint32_t* 
   if ((ce = cudaMemcpyAsync(y_dev, B.y, total * S.n_embd * 4, cudaMemcpyDeviceToDevice, e->stream)) != cudaSuccess)
     return fail_cuda(e, ce, "result copy");
   return LLR_OK;
+}
+
+// ---- expert parallelism over peer stores (kernels: llr_moe_ep.cu) ----------------------------------------
+struct llr_moe_ep {
+  llr_exec* owner = nullptr;
+  MoeShape S;
+  llr_moe_layer layer{};
+  std::vector<const llr_matrix*> gate, up, down;
+  EpLayout L{};
+  EpPeers peers{};
+  unsigned long long epoch = 0, dispatch_total = 0, return_total = 0;
+  size_t tokens = 0;  // of the run in flight
+  int stage = 0;      // 0 idle, 1 dispatched, 2 served
+  char* tables = nullptr;  // one device block: everything below except rows
+  float* d_logits = nullptr; int* d_ids = nullptr; float* d_wts = nullptr; int* d_tok_of_row = nullptr;
+  int* d_rows_of_tok = nullptr; float* d_w = nullptr; int* d_fill = nullptr; int* d_first_row = nullptr;
+  unsigned char* d_local = nullptr; int* d_seg_first = nullptr; int* d_ret_src = nullptr; int* d_ret_tag = nullptr;
+  float* d_rows = nullptr; size_t rows_cap = 0;  // gathered rows of this rank's experts
+  int* h_cnt = nullptr;  // pinned: counts [local expert][sender], then the segment starts
+};
+
+size_t llr_moe_ep_arena_bytes(uint32_t n_expert, uint32_t n_used, size_t n_embd, uint32_t world, size_t max_tokens) {
+  if (n_expert == 0 || n_used == 0 || n_used > n_expert || n_expert > 4096 || n_embd == 0 || n_embd % 4 != 0 || n_embd > (1u << 20) ||
+      world == 0 || world > (uint32_t)EP_MAX_WORLD || max_tokens == 0 || max_tokens > (1u << 20))
+    return 0;
+  return ep_layout((int)n_expert, (int)n_used, (int)n_embd, (int)world, 0, (int)max_tokens).total;
+}
+
+int llr_moe_ep_free(llr_moe_ep* ep) {
+  if (!ep) return LLR_OK;
+  DeviceGuard guard(ep->owner->device);
+  cudaStreamSynchronize(ep->owner->stream);
+  if (ep->tables) cudaFree(ep->tables);
+  if (ep->d_rows) cudaFree(ep->d_rows);
+  if (ep->h_cnt) cudaFreeHost(ep->h_cnt);
+  delete ep;
+  return LLR_OK;
+}
+
+int llr_moe_ep_create(llr_exec* e, const llr_moe_layer* L, uint32_t world, uint32_t rank, size_t max_tokens, void* arena,
+                      size_t arena_bytes, void* const* peer_arenas, llr_moe_ep** out) {
+  if (!e) return LLR_ERR_INVALID;
+  if (!out) return fail(e, LLR_ERR_INVALID, "null output");
+  *out = nullptr;
+  MoeShape S;
+  int rc = moe_check_layer(e, L, true, &S);
+  if (rc) return rc;
+  if (world == 0 || world > (uint32_t)EP_MAX_WORLD || rank >= world || max_tokens == 0 || max_tokens > (1u << 20) || !arena ||
+      ((uintptr_t)arena & 255) != 0 || (world > 1 && !peer_arenas))
+    return fail(e, LLR_ERR_INVALID, "expert-parallel layer: world 1..8, rank < world, max_tokens 1..2^20, a 256-byte aligned arena");
+  for (size_t ex = 0; ex < S.n_exp; ++ex)
+    if ((S.local[ex] != 0) != (ex % world == rank))
+      return fail(e, LLR_ERR_INVALID, "expert " + std::to_string(ex) + ": rank e % world holds an expert's matrices and every other rank passes NULL for it");
+  const EpLayout lay = ep_layout((int)S.n_exp, (int)S.n_used, (int)S.n_embd, (int)world, (int)rank, (int)max_tokens);
+  if (arena_bytes < lay.total)
+    return fail(e, LLR_ERR_INVALID, "the arena holds " + std::to_string(arena_bytes) + " bytes, llr_moe_ep_arena_bytes asks for " + std::to_string(lay.total));
+  std::unique_ptr<llr_moe_ep> ep(new llr_moe_ep);
+  ep->owner = e;
+  ep->S = S;
+  ep->S.any_remote = false;  // the rows this rank computes all belong to its own experts
+  ep->gate.assign(L->gate, L->gate + S.n_exp);
+  ep->up.assign(L->up, L->up + S.n_exp);
+  ep->down.assign(L->down, L->down + S.n_exp);
+  ep->layer = *L;
+  ep->layer.gate = ep->gate.data(); ep->layer.up = ep->up.data(); ep->layer.down = ep->down.data();
+  ep->L = lay;
+  for (uint32_t g = 0; g < world; ++g) {
+    ep->peers.arena[g] = g == rank ? (char*)arena : (char*)peer_arenas[g];
+    if (!ep->peers.arena[g] || ((uintptr_t)ep->peers.arena[g] & 255) != 0) return fail(e, LLR_ERR_INVALID, "peer arena " + std::to_string(g));
+  }
+  DeviceGuard guard(e->device);
+  const size_t T = max_tokens, n_rows = T * S.n_used, n_seg = (size_t)lay.e_loc * world, max_gather = n_seg * T;
+  auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  size_t at = 0;
+  auto take = [&](size_t bytes) { const size_t o = at; at = up256(at + bytes); return o; };
+  const size_t o_logits = take(T * S.n_exp * 4), o_ids = take(n_rows * 4), o_wts = take(n_rows * 4), o_tor = take(n_rows * 4),
+               o_rot = take(n_rows * 4), o_w = take(n_rows * 4), o_fill = take(T * 4), o_first = take((S.n_exp + 1) * 4),
+               o_local = take(S.n_exp), o_seg = take((n_seg + 1) * 4), o_rsrc = take(max_gather * 4), o_rtag = take(max_gather * 4);
+  cudaError_t ce;
+  if ((ce = cudaMalloc((void**)&ep->tables, at)) != cudaSuccess) return fail_cuda(e, ce, "expert-parallel tables");
+  char* tb = ep->tables;
+  ep->d_logits = (float*)(tb + o_logits); ep->d_ids = (int*)(tb + o_ids); ep->d_wts = (float*)(tb + o_wts);
+  ep->d_tok_of_row = (int*)(tb + o_tor); ep->d_rows_of_tok = (int*)(tb + o_rot); ep->d_w = (float*)(tb + o_w);
+  ep->d_fill = (int*)(tb + o_fill); ep->d_first_row = (int*)(tb + o_first); ep->d_local = (unsigned char*)(tb + o_local);
+  ep->d_seg_first = (int*)(tb + o_seg); ep->d_ret_src = (int*)(tb + o_rsrc); ep->d_ret_tag = (int*)(tb + o_rtag);
+  if ((ce = cudaMallocHost((void**)&ep->h_cnt, (2 * n_seg + 2) * sizeof(int))) != cudaSuccess) {
+    llr_moe_ep_free(ep.release());
+    return fail_cuda(e, ce, "expert-parallel tables");
+  }
+  // every selected expert's weight counts: the rows of experts that live elsewhere come back from their owners
+  if ((ce = cudaMemsetAsync(ep->d_local, 1, S.n_exp, e->stream)) != cudaSuccess || (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess) {
+    llr_moe_ep_free(ep.release());
+    return fail_cuda(e, ce, "expert-parallel tables");
+  }
+  *out = ep.release();
+  return LLR_OK;
+}
+
+int llr_moe_ep_dispatch(llr_moe_ep* ep, size_t tokens, const float* x_dev) {
+  if (!ep) return LLR_ERR_INVALID;
+  llr_exec* e = ep->owner;
+  if (ep->stage != 0) return fail(e, LLR_ERR_INVALID, "expert-parallel layer: the previous run has not been combined");
+  if (tokens == 0 || tokens > (size_t)ep->L.t_max || !x_dev || ((uintptr_t)x_dev & 15) != 0)
+    return fail(e, LLR_ERR_INVALID, "expert-parallel layer: 1..max_tokens rows at a 16-byte aligned device address");
+  DeviceGuard guard(e->device);
+  const MoeShape& S = ep->S;
+  cudaError_t ce;
+  if ((ce = moe_route(e, &ep->layer, S, tokens, x_dev, ep->d_logits, ep->d_ids, ep->d_wts)) != cudaSuccess ||
+      (ce = launch_bucket(ep->d_ids, ep->d_wts, ep->d_local, (int)tokens, (int)S.n_exp, (int)S.n_used, ep->d_first_row, ep->d_tok_of_row,
+                          ep->d_rows_of_tok, ep->d_w, ep->d_fill, e->stream, &e->ctr.launches)) != cudaSuccess)
+    return fail_cuda(e, ce, "kernel launch");
+  const size_t n_rows = tokens * S.n_used;
+  ++ep->epoch;
+  ep->dispatch_total += n_rows;
+  if ((ce = launch_ep_dispatch(x_dev, ep->d_tok_of_row, ep->d_first_row, (int)n_rows, ep->peers, ep->L, (int)(ep->epoch & 1), ep->epoch,
+                               ep->dispatch_total, e->stream, &e->ctr.launches)) != cudaSuccess)
+    return fail_cuda(e, ce, "kernel launch");
+  ep->tokens = tokens;
+  ep->stage = 1;
+  return LLR_OK;
+}
+
+int llr_moe_ep_serve(llr_moe_ep* ep) {
+  if (!ep) return LLR_ERR_INVALID;
+  llr_exec* e = ep->owner;
+  if (ep->stage != 1) return fail(e, LLR_ERR_INVALID, "expert-parallel layer: serve follows dispatch");
+  DeviceGuard guard(e->device);
+  const EpLayout& L = ep->L;
+  const MoeShape& S = ep->S;
+  const int p = (int)(ep->epoch & 1);
+  const size_t n_seg = (size_t)L.e_loc * L.world;
+  char* mine = ep->peers.arena[L.rank];
+  ep->stage = 0;  // a failure below ends the run
+  cudaError_t ce;
+  if ((ce = launch_ep_wait(((EpHeader*)mine)->flag_in, L.world, ep->epoch, e->poll_limit, e->err_flag, e->stream, &e->ctr.launches)) != cudaSuccess ||
+      (ce = cudaMemcpyAsync(ep->h_cnt, mine + L.cnt_off[p], n_seg * sizeof(int), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
+      (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)
+    return fail_cuda(e, ce, "routed-row counts");
+  if (take_device_error(e) != 0)
+    return fail(e, LLR_ERR_CUDA, "a device-side wait ran out of iterations (a rank did not deliver its routed rows); re-create the expert-parallel layer on every rank");
+  e->ctr.d2h_bytes += n_seg * sizeof(int);
+  // packed order of this rank's experts: expert ascending, sender ascending, arrival position ascending
+  int* seg = ep->h_cnt + n_seg;
+  std::vector<int> first_row(S.n_exp + 1, 0);
+  int total = 0;
+  for (size_t k = 0; k < n_seg; ++k) {
+    const int c = ep->h_cnt[k];
+    if (c < 0 || c > L.t_max) return fail(e, LLR_ERR_CUDA, "expert-parallel layer: a sender's row count is out of range");
+    seg[k] = total;
+    total += c;
+  }
+  seg[n_seg] = total;
+  for (size_t ex = 0; ex < S.n_exp; ++ex) {
+    const size_t le = ex / L.world;
+    first_row[ex + 1] = first_row[ex] + (S.local[ex] ? seg[(le + 1) * L.world] - seg[le * L.world] : 0);
+  }
+  if ((ce = cudaMemcpyAsync(ep->d_seg_first, seg, (n_seg + 1) * sizeof(int), cudaMemcpyHostToDevice, e->stream)) != cudaSuccess)
+    return fail_cuda(e, ce, "segment table");
+  const float* y = nullptr;
+  if (total > 0) {
+    if ((ce = grow_device(&ep->d_rows, &ep->rows_cap, (size_t)total * S.n_embd)) != cudaSuccess ||
+        (ce = grow_device(&e->dev_moe, &e->dev_moe_cap, moe_buffer_floats(S, (size_t)total) + 256)) != cudaSuccess)
+      return fail_cuda(e, ce, "expert workspace");
+    const MoeBuffers B = moe_carve((float*)(((uintptr_t)e->dev_moe + 255) & ~(uintptr_t)255), S, (size_t)total);
+    if ((ce = launch_ep_gather(mine, L, p, ep->d_seg_first, (int)n_seg, total, ep->d_rows, ep->d_ret_src, ep->d_ret_tag, e->stream,
+                               &e->ctr.launches)) != cudaSuccess ||
+        (ce = moe_run_experts(e, &ep->layer, S, first_row, ep->d_rows, nullptr, B)) != cudaSuccess)
+      return fail_cuda(e, ce, "kernel launch");
+    y = B.y;
+  }
+  ep->return_total += (unsigned long long)total;
+  if ((ce = launch_ep_return(y, ep->d_ret_src, ep->d_ret_tag, total, ep->peers, L, p, ep->epoch, ep->return_total, e->stream,
+                             &e->ctr.launches)) != cudaSuccess)
+    return fail_cuda(e, ce, "kernel launch");
+  ep->stage = 2;
+  return LLR_OK;
+}
+
+int llr_moe_ep_combine(llr_moe_ep* ep, float* out_dev, int32_t* ids_dev, float* w_dev) {
+  if (!ep) return LLR_ERR_INVALID;
+  llr_exec* e = ep->owner;
+  if (ep->stage != 2) return fail(e, LLR_ERR_INVALID, "expert-parallel layer: combine follows serve");
+  if (!out_dev || ((uintptr_t)out_dev & 15) != 0) return fail(e, LLR_ERR_INVALID, "null or unaligned buffer");
+  DeviceGuard guard(e->device);
+  const EpLayout& L = ep->L;
+  const int p = (int)(ep->epoch & 1);
+  char* mine = ep->peers.arena[L.rank];
+  const size_t n_rows = ep->tokens * ep->S.n_used;
+  ep->stage = 0;
+  cudaError_t ce;
+  if ((ce = launch_ep_wait(((EpHeader*)mine)->flag_back, L.world, ep->epoch, e->poll_limit, e->err_flag, e->stream, &e->ctr.launches)) != cudaSuccess ||
+      (ce = launch_scatter_combine((const float*)(mine + L.back_off[p]), ep->d_rows_of_tok, ep->d_w, out_dev, (int)ep->tokens, (int)ep->S.n_used,
+                                   (int)ep->S.n_embd, e->stream, &e->ctr.launches)) != cudaSuccess ||
+      (ids_dev && (ce = cudaMemcpyAsync(ids_dev, ep->d_ids, n_rows * 4, cudaMemcpyDeviceToDevice, e->stream)) != cudaSuccess) ||
+      (w_dev && (ce = cudaMemcpyAsync(w_dev, ep->d_wts, n_rows * 4, cudaMemcpyDeviceToDevice, e->stream)) != cudaSuccess))
+    return fail_cuda(e, ce, "kernel launch");
+  return LLR_OK;
+}
+
+int llr_moe_ep_run(llr_moe_ep* ep, size_t tokens, const float* x_dev, float* out_dev, int32_t* ids_dev, float* w_dev) {
+  int rc = llr_moe_ep_dispatch(ep, tokens, x_dev);
+  if (rc == LLR_OK) rc = llr_moe_ep_serve(ep);
+  if (rc == LLR_OK) rc = llr_moe_ep_combine(ep, out_dev, ids_dev, w_dev);
+  return rc;
 }
 
 struct llr_program {

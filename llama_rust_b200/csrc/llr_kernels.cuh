@@ -191,6 +191,32 @@ cudaError_t launch_bucket(const int* ids, const float* wts, const unsigned char*
 cudaError_t launch_scatter_combine(const float* y, const int* rows_of_tok, const float* w_of_tok, float* out,
                                    int tokens, int n_used, int n_embd, cudaStream_t s, uint64_t* launches);
 
+// Expert parallelism over peer stores (llr_moe_ep.cu).  An arena starts with an EpHeader, then twice (runs
+// alternate): counts [local expert][sender], packed row numbers and rows [local expert][sender][t_max], and the
+// return area [t_max * n_used] rows.
+constexpr int EP_MAX_WORLD = 8;
+struct EpHeader {
+  unsigned long long flag_in[EP_MAX_WORLD];    // [sender]: last run whose rows from that sender are complete here
+  unsigned long long flag_back[EP_MAX_WORLD];  // [owner]: last run whose results from that owner are complete here
+  unsigned long long done_dispatch, done_return;  // this rank's CTAs, counted over all runs
+};
+struct EpPeers { char* arena[EP_MAX_WORLD]; };  // every rank's arena as mapped here (entry `rank`: this rank's own)
+struct EpLayout {
+  int n_expert, n_used, n_embd, world, rank, t_max, e_loc;
+  size_t cnt_off[2], tag_off[2], recv_off[2], back_off[2], total;
+};
+EpLayout ep_layout(int n_expert, int n_used, int n_embd, int world, int rank, int t_max);
+cudaError_t launch_ep_dispatch(const float* x, const int* tok_of_row, const int* first_row, int n_rows, const EpPeers& peers,
+                               const EpLayout& L, int parity, unsigned long long epoch, unsigned long long done_target,
+                               cudaStream_t s, uint64_t* launches);
+cudaError_t launch_ep_wait(const unsigned long long* flags, int world, unsigned long long epoch, int poll_limit, int* err,
+                           cudaStream_t s, uint64_t* launches);
+cudaError_t launch_ep_gather(const char* arena, const EpLayout& L, int parity, const int* seg_first, int n_seg, int n_rows,
+                             float* rows, int* ret_src, int* ret_tag, cudaStream_t s, uint64_t* launches);
+cudaError_t launch_ep_return(const float* y, const int* ret_src, const int* ret_tag, int n_rows, const EpPeers& peers,
+                             const EpLayout& L, int parity, unsigned long long epoch, unsigned long long done_target,
+                             cudaStream_t s, uint64_t* launches);
+
 // out[(r-row0)*cols + c] = dequantized W[r,c], bit-exact with the reference.
 cudaError_t launch_dequant(const MatView& m, int64_t row0, int64_t n_rows, float* out,
                            cudaStream_t stream, uint64_t* launches);

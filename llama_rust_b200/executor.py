@@ -245,6 +245,44 @@ def plan_placement(expert_bytes: int, activation_bytes: int, fan_in: int, reuse:
     return lib().llr_plan_placement(expert_bytes, activation_bytes, fan_in, reuse, link_bps)
 
 
+def moe_ep_arena_bytes(n_expert: int, n_used: int, n_embd: int, world: int, max_tokens: int) -> int:
+    """Bytes of peer-writable arena one rank of an expert-parallel layer needs (llr_moe_ep_arena_bytes)."""
+    n = int(lib().llr_moe_ep_arena_bytes(n_expert, n_used, n_embd, world, max_tokens))
+    if n == 0:
+        raise ValueError("expert-parallel layer: invalid shape")
+    return n
+
+
+class MoeEp:
+    """Handle of llr_moe_ep_*: dispatch -> serve -> combine per run (run() makes the three calls); device pointers."""
+
+    def __init__(self, ex: "Executor", h: int):
+        self._ex, self._h = ex, h
+
+    def dispatch(self, tokens: int, x_ptr: int) -> None:
+        self._ex._check(lib().llr_moe_ep_dispatch(self._h, tokens, x_ptr))
+
+    def serve(self) -> None:
+        self._ex._check(lib().llr_moe_ep_serve(self._h))
+
+    def combine(self, out_ptr: int, ids_ptr: int | None = None, w_ptr: int | None = None) -> None:
+        self._ex._check(lib().llr_moe_ep_combine(self._h, out_ptr, ids_ptr, w_ptr))
+
+    def run(self, tokens: int, x_ptr: int, out_ptr: int, ids_ptr: int | None = None, w_ptr: int | None = None) -> None:
+        self._ex._check(lib().llr_moe_ep_run(self._h, tokens, x_ptr, out_ptr, ids_ptr, w_ptr))
+
+    def free(self) -> None:
+        if self._h:
+            lib().llr_moe_ep_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class Executor:
     """One device, one stream, scratch reuse and weight residency (CudaGemv, gpu.rs:139)."""
 
@@ -428,6 +466,16 @@ class Executor:
         layer, keep = self._moe_layer(None, gate, up, down, 1, False)
         cnt = (C.c_uint32 * len(gate))(*[int(c) for c in counts])
         self._check(lib().llr_moe_experts_device(self._h, C.byref(layer), cnt, rows_ptr, y_ptr))
+
+    def moe_ep(self, router: Matrix, gate, up, down, n_used: int, norm_w: bool, world: int, rank: int, max_tokens: int,
+               arena: int, arena_bytes: int, peer_arenas) -> "MoeEp":
+        """Expert-parallel layer with the exchange inside the library (llr_moe_ep_create); gate/up/down hold None for
+        the experts of other ranks, peer_arenas[g] is rank g's arena as mapped here."""
+        layer, keep = self._moe_layer(router, gate, up, down, n_used, norm_w)
+        peers = (C.c_void_p * world)(*[None if g == rank else peer_arenas[g] for g in range(world)])
+        h = C.c_void_p()
+        self._check(lib().llr_moe_ep_create(self._h, C.byref(layer), world, rank, max_tokens, arena, arena_bytes, peers, C.byref(h)))
+        return MoeEp(self, h.value)
 
     def dequant_rows(self, m: Matrix, row0: int = 0, n_rows: int | None = None) -> np.ndarray:
         n = m.rows - row0 if n_rows is None else n_rows

@@ -93,6 +93,77 @@ def test_striped_experts_partials_sum_to_the_single_device_layer(orc):
     ex.close()
 
 
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_expert_parallel_layer_with_peer_stores_on_one_gpu(world):
+    """llr_moe_ep_*: experts striped e % world, tokens sharded, routed rows and results moved by peer stores.  One GPU
+    plays every rank here (one executor per rank, the stages called rank after rank with a synchronize in between, so
+    no wait ever spins); the output of every rank's tokens is bit-identical to the single-device layer on the f32-
+    faithful path.  Three runs with changing token counts go through both halves of the arena; world = 3 leaves
+    rank 2 with two experts and ranks 0 and 1 with three."""
+    import torch
+    from llama_rust_b200 import Executor, NativeCudaError
+    from llama_rust_b200.executor import moe_ep_arena_bytes
+    n_expert, n_used, n_embd, n_ff, t_max = 8, 2, 512, 1024, 48
+    rng = np.random.default_rng(77 + world)
+    router_w = (rng.standard_normal((n_expert, n_embd)) * 0.05).astype(np.float32)
+    ref = Executor(0)
+    ref.set_path(3)
+    full = {k: [ref.synth(Q4_K, r, c, seed + e) for e in range(n_expert)]
+            for k, (r, c, seed) in {"gate": (n_ff, n_embd, 100), "up": (n_ff, n_embd, 200), "down": (n_embd, n_ff, 300)}.items()}
+    ref_router = ref.upload(F32, n_expert, n_embd, router_w.view(np.uint8).reshape(-1))
+    exs = [Executor(0) for _ in range(world)]
+    nbytes = moe_ep_arena_bytes(n_expert, n_used, n_embd, world, t_max)
+    arenas = [ex.shared_alloc(nbytes)[0] for ex in exs]
+    eps, mines, routers = [], [], []
+    for r, ex in enumerate(exs):
+        ex.set_path(3)
+        mine = {k: [ex.synth(Q4_K, m.rows, m.cols, seed + e) if e % world == r else None for e, m in enumerate(full[k])]
+                for k, seed in (("gate", 100), ("up", 200), ("down", 300))}
+        router = ex.upload(F32, n_expert, n_embd, router_w.view(np.uint8).reshape(-1))
+        eps.append(ex.moe_ep(router, mine["gate"], mine["up"], mine["down"], n_used, True, world, r, t_max, arenas[r], nbytes, arenas))
+        mines.append(mine)
+        routers.append(router)
+    for run, counts in enumerate(([5, 48, 17], [48, 1, 30], [9, 9, 9])):
+        counts = counts[:world]
+        xs = [rng.standard_normal((n, n_embd)).astype(np.float32) for n in counts]
+        want, want_ids, want_w = ref.moe_ffn(ref_router, full["gate"], full["up"], full["down"], n_used, True, np.concatenate(xs))
+        x_t = [torch.from_numpy(x).cuda() for x in xs]
+        out_t = [torch.full((n, n_embd), float("nan"), device="cuda") for n in counts]
+        ids_t = [torch.zeros((n, n_used), dtype=torch.int32, device="cuda") for n in counts]
+        w_t = [torch.zeros((n, n_used), dtype=torch.float32, device="cuda") for n in counts]
+        torch.cuda.synchronize()
+        for r in range(world):
+            eps[r].dispatch(counts[r], x_t[r].data_ptr())
+        for ex in exs:
+            ex.synchronize()
+        for r in range(world):
+            eps[r].serve()
+        for ex in exs:
+            ex.synchronize()
+        for r in range(world):
+            eps[r].combine(out_t[r].data_ptr(), ids_t[r].data_ptr(), w_t[r].data_ptr())
+        for ex in exs:
+            ex.synchronize()
+        got = np.concatenate([o.cpu().numpy() for o in out_t])
+        assert np.array_equal(np.concatenate([i.cpu().numpy() for i in ids_t]), want_ids), run
+        assert np.array_equal(np.concatenate([v.cpu().numpy() for v in w_t]).view(np.uint32), want_w.view(np.uint32)), run
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (run, float(np.abs(got - want).max()))
+    # the stages of a run come in order, and a rank holds exactly the experts e % world == rank
+    with pytest.raises(NativeCudaError):
+        eps[0].serve()
+    with pytest.raises(NativeCudaError):
+        eps[0].dispatch(t_max + 1, x_t[0].data_ptr())
+    if world > 1:
+        with pytest.raises(NativeCudaError, match="e % world"):  # rank 0's experts offered as rank 1
+            exs[0].moe_ep(routers[0], mines[0]["gate"], mines[0]["up"], mines[0]["down"], n_used, True, world, 1, t_max, arenas[0], nbytes, arenas)
+    for ep in eps:
+        ep.free()
+    for ex, a in zip(exs, arenas):
+        ex.shared_free(a)
+        ex.close()
+    ref.close()
+
+
 def test_config5_full_size_layer(orc):
     """BASELINE config 5 at its full size: 8 experts, top-2, 4096 / 14336, Q4_K experts generated on
     the device from seeds (792 MB), F32 router, 64 tokens.  One CPU walk of the layer (the
