@@ -300,9 +300,11 @@ def config_legs(ex, stream, peak_hbm, peaks):
 def moe_leg(ex, group, rank, world, peak_hbm, sustained, token_counts=(64, 512)):
     """Routed-expert layer of BASELINE config 5 (8 experts, top-2, 4096 / 14336, Q4_K experts, F32 router) through
     the host-buffer entry point with pinned buffers: wall ms per layer call.  world > 1: experts striped e % world, tokens
-    sharded, routed rows exchanged with all-to-all; every rank compares its tokens' outputs bit for bit with the
+    sharded on the device, routed rows and results exchanged by peer stores inside the library (llr_moe_ep_*); the same
+    layer over NCCL all-to-all is timed beside it; every rank compares its tokens' outputs bit for bit with the
     single-device layer."""
     import torch
+    import torch.distributed as dist
     from llama_rust_b200 import DTYPES
     n_exp, d_model, d_ff = 8, 4096, 14336
     gate = [ex.synth(Q4_K, d_ff, d_model, 100 + e) for e in range(n_exp)]
@@ -312,41 +314,43 @@ def moe_leg(ex, group, rank, world, peak_hbm, sustained, token_counts=(64, 512))
     w = (rng.standard_normal((n_exp, d_model)) * 0.05).astype(np.float32)
     router = ex.upload(DTYPES["F32"], n_exp, d_model, w.view(np.uint8).reshape(-1))
     res = {}
-    layer = None
+    layer = nccl_layer = None
     if world > 1:
-        from llama_rust_b200.sharding import ExpertParallelLayer, home_rank
+        from llama_rust_b200.sharding import ExpertParallelLayer, PeerExpertParallelLayer, home_rank
         keep = [home_rank(e, world) == rank for e in range(n_exp)]
-        route, experts = ExpertParallelLayer.cuda_backend(ex, router, [m if k else None for m, k in zip(gate, keep)],
-                                                          [m if k else None for m, k in zip(up, keep)],
-                                                          [m if k else None for m, k in zip(down, keep)], 2, True)
-        layer = ExpertParallelLayer(n_exp, 2, route, experts, group=group)
-    for tokens in token_counts:
-        xs = np.random.default_rng(tokens).standard_normal((tokens, d_model)).astype(np.float32)
-        x = torch.from_numpy(xs).pin_memory().numpy()
-        out = torch.empty(tokens, d_model).pin_memory().numpy()
-        if layer is not None:
-            # tokens sharded over the ranks: device tensors in, device tensors out, routed rows over NCCL all-to-all
-            lo, hi = tokens * rank // world, tokens * (rank + 1) // world
-            xl = torch.from_numpy(np.ascontiguousarray(xs[lo:hi])).cuda()
-            call = lambda: layer(xl)  # noqa: E731
-        else:
-            call = lambda: ex.moe_ffn(router, gate, up, down, 2, True, x, out)  # noqa: E731
+        mine = [[m if k else None for m, k in zip(lst, keep)] for lst in (gate, up, down)]
+        layer = PeerExpertParallelLayer(ex, router, mine[0], mine[1], mine[2], 2, True, max(token_counts) // world + 1, group=group)
+        route, experts = ExpertParallelLayer.cuda_backend(ex, router, mine[0], mine[1], mine[2], 2, True)
+        nccl_layer = ExpertParallelLayer(n_exp, 2, route, experts, group=group)
+
+    def timed(call, n=5):
         for _ in range(2):
             call()
-        n = 5
         torch.cuda.synchronize()  # also keeps torch's one-time CUDA set-up out of the timed region
         if world > 1:
-            import torch.distributed as dist
             dist.barrier()
         t0 = time.perf_counter()
         for _ in range(n):
-            r = call()
+            call()
         torch.cuda.synchronize()
         ms = (time.perf_counter() - t0) / n * 1e3
         if world > 1:
             tt = torch.tensor([ms], device="cuda")
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             ms = float(tt.item())
+        return ms
+    for tokens in token_counts:
+        xs = np.random.default_rng(tokens).standard_normal((tokens, d_model)).astype(np.float32)
+        x = torch.from_numpy(xs).pin_memory().numpy()
+        out = torch.empty(tokens, d_model).pin_memory().numpy()
+        if layer is not None:
+            # tokens sharded over the ranks: device tensors in, device tensors out
+            lo, hi = tokens * rank // world, tokens * (rank + 1) // world
+            xl = torch.from_numpy(np.ascontiguousarray(xs[lo:hi])).cuda()
+            ms = timed(lambda: layer(xl))
+            ms_nccl = timed(lambda: nccl_layer(xl))
+        else:
+            ms = timed(lambda: ex.moe_ffn(router, gate, up, down, 2, True, x, out))
         flops = 2.0 * tokens * 2 * 3 * d_model * d_ff
         nbytes = n_exp * 3 * d_ff * 144 * (d_model // 256)
         floor_ms = max(nbytes / world / (peak_hbm * 1e9), flops / world / (sustained * 1e12)) * 1e3
@@ -356,13 +360,20 @@ def moe_leg(ex, group, rank, world, peak_hbm, sustained, token_counts=(64, 512))
             # single-device layer on this rank's tokens (the automatic choice picks kernels by the number of rows)
             ex.set_path(3)
             full = ex.moe_ffn(router, gate, up, down, 2, True, xs[lo:hi])[0]
+            dist.barrier()
             chk = layer(xl)[0].cpu().numpy()
+            chk_nccl = nccl_layer(xl)[0].cpu().numpy()
             ex.set_path(0)
-            same = torch.tensor([1 if np.array_equal(chk, full) else 0], device="cuda")
+            same = torch.tensor([1 if np.array_equal(chk, full) and np.array_equal(chk_nccl, full) else 0], device="cuda")
             dist.all_reduce(same, op=dist.ReduceOp.MIN)
             rec["bit_identical_to_single_device"] = bool(same.item())
-            rec["layout"] = f"tokens/{world} per rank on the device, experts e % {world}, routed rows exchanged with NCCL all-to-all"
+            rec["layout"] = (f"tokens/{world} per rank on the device, experts e % {world}, routed rows and results exchanged by peer "
+                             "stores from the library's gather / scatter kernels")
+            rec["same_layer_over_nccl_all_to_all_ms"] = ms_nccl
         res[f"tokens_{tokens}"] = rec
+    if layer is not None:
+        dist.barrier()
+        layer.close()
     for m in gate + up + down + [router]:
         m.free()
     return res

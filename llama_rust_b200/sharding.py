@@ -302,3 +302,44 @@ class ExpertParallelLayer:
             term = back.index_select(0, rows) * wj  # product rounded, then added: no fused multiply-add
             out = out + term
         return out, ids, w
+
+
+class PeerExpertParallelLayer:
+    """The expert-parallel layer with the exchange inside the library (llr_moe_ep_*): same layout as
+    ExpertParallelLayer (expert e on rank e % G, tokens sharded), but routed rows and their results move between the
+    GPUs as peer stores issued by the gather and scatter kernels, with no collective call and no host hop for rows.
+    The process group only carries the memory handles at construction (any backend).  gate/up/down hold None for
+    the experts of other ranks; max_tokens bounds this rank's tokens per call.  Every rank makes the same sequence
+    of calls; a rank must pass at least one token."""
+
+    def __init__(self, ex, router, gate, up, down, n_used: int, norm_w: bool, max_tokens: int, group=None):
+        from .executor import moe_ep_arena_bytes
+        self.ex, self.n_used, self.n_embd = ex, n_used, router.cols
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self.nbytes = moe_ep_arena_bytes(len(gate), n_used, router.cols, world, max_tokens)
+        self.arena, handle = ex.shared_alloc(self.nbytes)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle, group=group)
+        self.peers = [self.arena if g == rank else ex.shared_open(handles[g]) for g in range(world)]
+        self.ep = ex.moe_ep(router, gate, up, down, n_used, norm_w, world, rank, max_tokens, self.arena, self.nbytes, self.peers)
+        self.rank = rank
+        dist.barrier(group=group)  # every rank's layer exists before anybody's first run stores into a peer
+
+    def __call__(self, x: torch.Tensor, synchronize: bool = True):
+        """x: this rank's tokens [T, n_embd] (float32, contiguous, on the executor's GPU).  Returns (out, ids, w)."""
+        tokens = x.shape[0]
+        out = torch.empty_like(x)
+        ids = torch.empty(tokens, self.n_used, dtype=torch.int32, device=x.device)
+        w = torch.empty(tokens, self.n_used, dtype=torch.float32, device=x.device)
+        torch.cuda.current_stream().synchronize()  # x is ready before the executor's stream reads it
+        self.ep.run(tokens, x.data_ptr(), out.data_ptr(), ids.data_ptr(), w.data_ptr())
+        if synchronize:
+            self.ex.synchronize()
+        return out, ids, w
+
+    def close(self) -> None:
+        self.ep.free()
+        for g, p in enumerate(self.peers):
+            if g != self.rank:
+                self.ex.shared_close(p)
+        self.ex.shared_free(self.arena)

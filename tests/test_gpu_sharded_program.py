@@ -163,6 +163,57 @@ def _moe_worker(rank, world, port, ret):
         ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
 
 
+def _moe_ep_worker(rank, world, port, ret):
+    """The expert-parallel layer whose exchange is peer stores inside the library (llr_moe_ep_*)."""
+    try:
+        import torch
+        import torch.distributed as dist
+        from llama_rust_b200 import Executor
+        from llama_rust_b200.sharding import PeerExpertParallelLayer, home_rank
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        torch.cuda.set_device(rank)
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        ex = Executor(rank)
+        F32 = 2
+        n_expert, n_used, n_embd, n_ff = 8, 2, 1024, 2048
+        gate = [ex.synth(Q4_K, n_ff, n_embd, 10 + e) for e in range(n_expert)]
+        up = [ex.synth(Q4_K, n_ff, n_embd, 30 + e) for e in range(n_expert)]
+        down = [ex.synth(Q4_K, n_embd, n_ff, 50 + e) for e in range(n_expert)]
+        rng = np.random.default_rng(3)
+        router = ex.upload(F32, n_expert, n_embd, (rng.standard_normal((n_expert, n_embd)) * 0.05).astype(np.float32).view(np.uint8).reshape(-1))
+        keep = [home_rank(e, world) == rank for e in range(n_expert)]
+        layer = PeerExpertParallelLayer(ex, router, [m if k else None for m, k in zip(gate, keep)],
+                                        [m if k else None for m, k in zip(up, keep)],
+                                        [m if k else None for m, k in zip(down, keep)], n_used, True, 320)
+        ok = "ok"
+        for path, tokens in ((3, 7), (3, 128), (3, 600), (0, 128), (0, 600), (3, 9)):
+            ex.set_path(path)
+            x = rng.standard_normal((tokens, n_embd)).astype(np.float32)      # the same on every rank (same seed)
+            lo, hi = tokens * rank // world, tokens * (rank + 1) // world    # this rank's tokens
+            full, ids, w = ex.moe_ffn(router, gate, up, down, n_used, True, x[lo:hi])  # single-device answer for them
+            dist.barrier()  # ranks enter a run together: the device-side waits are bounded
+            out, ids_s, w_s = layer(torch.from_numpy(np.ascontiguousarray(x[lo:hi])).cuda())
+            got = out.cpu().numpy()
+            if not (np.array_equal(ids_s.cpu().numpy(), ids) and np.array_equal(w_s.cpu().numpy(), w)):
+                ok = f"path {path} tokens={tokens}: routing differs"
+                break
+            if path == 3 and not np.array_equal(got, full):
+                ok = f"path {path} tokens={tokens}: expert-parallel result differs in {int((got != full).sum())} of {got.size} values, max {np.abs(got - full).max()}"
+                break
+            if path == 0 and not np.abs(got - full).max() <= 2e-2 * max(1.0, np.abs(full).max()):
+                ok = f"path {path} tokens={tokens}: outside the tensor-core tolerance, max {np.abs(got - full).max()}"
+                break
+        dist.barrier()
+        layer.close()
+        ex.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        ret[rank] = ok
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        ret[rank] = f"{type(e).__name__}: {e}\n{traceback.format_exc()}"
+
+
 def _spawn(world, target, *args):
     import torch.multiprocessing as mp
     with socket.socket() as s:
@@ -192,3 +243,12 @@ def test_expert_parallel_layer_over_two_gpus_equals_the_single_device_layer():
 def test_expert_parallel_layer_on_one_rank_equals_the_layer_call():
     """The same code path with a group of one rank: no second GPU needed (the all-to-all is then a local copy)."""
     assert _spawn(1, _moe_worker) == {0: "ok"}
+
+
+def test_expert_parallel_layer_with_peer_stores_over_two_gpus():
+    """Tokens sharded, experts striped e % 2, routed rows and results moved by peer stores from the library's own
+    kernels; bit-identical to the single-device layer on the f32-faithful path."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    assert _spawn(2, _moe_ep_worker) == {0: "ok", 1: "ok"}
