@@ -164,6 +164,38 @@ def test_expert_parallel_layer_with_peer_stores_on_one_gpu(world):
     ref.close()
 
 
+def test_expert_parallel_wait_for_an_absent_rank_runs_out_and_the_executor_stays_usable():
+    """A rank whose peer never delivers: the bounded device-side wait of serve() runs out (the flag is simply never
+    set, nothing faults), the call reports LLR_ERR_CUDA with the reason, and the executor serves the next product."""
+    import torch
+    from llama_rust_b200 import Executor, NativeCudaError
+    from llama_rust_b200.executor import moe_ep_arena_bytes
+    n_expert, n_used, n_embd, n_ff, t_max = 4, 2, 256, 512, 8
+    ex = Executor(0)
+    ex.set_wait_limit(2000)  # about a millisecond
+    rng = np.random.default_rng(5)
+    router = ex.upload(F32, n_expert, n_embd, (rng.standard_normal((n_expert, n_embd)) * 0.05).astype(np.float32).view(np.uint8).reshape(-1))
+    mine = {k: [ex.synth(Q4_K, r, c, 7 + e) if e % 2 == 0 else None for e in range(n_expert)]
+            for k, (r, c) in {"gate": (n_ff, n_embd), "up": (n_ff, n_embd), "down": (n_embd, n_ff)}.items()}
+    nbytes = moe_ep_arena_bytes(n_expert, n_used, n_embd, 2, t_max)
+    arena0, arena1 = ex.shared_alloc(nbytes)[0], ex.shared_alloc(nbytes)[0]  # "rank 1" is memory nobody works on
+    ep = ex.moe_ep(router, mine["gate"], mine["up"], mine["down"], n_used, True, 2, 0, t_max, arena0, nbytes, [arena0, arena1])
+    x = torch.from_numpy(rng.standard_normal((t_max, n_embd)).astype(np.float32)).cuda()
+    torch.cuda.synchronize()
+    ep.dispatch(t_max, x.data_ptr())
+    with pytest.raises(NativeCudaError, match="did not deliver"):
+        ep.serve()
+    w = random_packed(rng, Q4_K, 32, 256)
+    m = ex.upload(Q4_K, 32, 256, w)
+    y = np.empty(32, np.float32)
+    ex.gemv_resident(m, np.ones(256, np.float32), y)
+    assert np.all(np.isfinite(y))
+    ep.free()
+    ex.shared_free(arena0)
+    ex.shared_free(arena1)
+    ex.close()
+
+
 def test_config5_full_size_layer(orc):
     """BASELINE config 5 at its full size: 8 experts, top-2, 4096 / 14336, Q4_K experts generated on
     the device from seeds (792 MB), F32 router, 64 tokens.  One CPU walk of the layer (the
