@@ -351,10 +351,26 @@ def moe_leg(ex, group, rank, world, peak_hbm, sustained, token_counts=(64, 512))
             ms_nccl = timed(lambda: nccl_layer(xl))
         else:
             ms = timed(lambda: ex.moe_ffn(router, gate, up, down, 2, True, x, out))
+            # the same layer with the tokens already on the device and the output left there (the expert-parallel entry
+            # points with a world of one rank): what the N > 1 figures, whose tokens live on the device, compare with
+            from llama_rust_b200.executor import moe_ep_arena_bytes
+            nb = moe_ep_arena_bytes(n_exp, 2, d_model, 1, tokens)
+            arena = ex.shared_alloc(nb)[0]
+            ep = ex.moe_ep(router, gate, up, down, 2, True, 1, 0, tokens, arena, nb, [arena])
+            xd, od = torch.from_numpy(xs).cuda(), torch.empty(tokens, d_model, device="cuda")
+
+            def on_device():
+                ep.run(tokens, xd.data_ptr(), od.data_ptr())
+                ex.synchronize()
+            ms_dev = timed(on_device)
+            ep.free()
+            ex.shared_free(arena)
         flops = 2.0 * tokens * 2 * 3 * d_model * d_ff
         nbytes = n_exp * 3 * d_ff * 144 * (d_model // 256)
         floor_ms = max(nbytes / world / (peak_hbm * 1e9), flops / world / (sustained * 1e12)) * 1e3
         rec = {"ms_per_layer_call": ms, "TFLOP_per_s": flops / ms / 1e9, "roofline_ms": floor_ms, "frac_of_roofline": floor_ms / ms}
+        if world == 1:
+            rec["tokens_on_device_ms_per_layer_call"] = ms_dev
         if world > 1:
             # untimed check with the f32-faithful products, whose rows do not depend on their batch: same bits as the
             # single-device layer on this rank's tokens (the automatic choice picks kernels by the number of rows)
