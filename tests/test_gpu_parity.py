@@ -242,6 +242,38 @@ def test_tensor_core_gemv_handles_awkward_activations(ex, orc, name):
     m.free()
 
 
+@pytest.mark.parametrize("name", ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1"])
+def test_tensor_core_gemv_one_nonzero_activation_at_every_column(ex, orc, name):
+    """The reference's single-term idea (simd/tests.rs:755: one non-zero term per position) on the integer tensor-core
+    kernel: with x = 1.7 e_c the result is column c of the dequantized matrix times 1.7, for every column of two
+    256-column groups and for one and three activation rows.  A weight, digit plane or fifth-bit that sits at the wrong
+    place changes a result by the size of a weight; rounding differences stay below 4e-6 of the largest one."""
+    kind = ALL[name]
+    rng = np.random.default_rng(0xD0 + kind)
+    rows, cols = 40, (2048 if name == "Q6_K" else 512)  # the kernel takes Q6_K rows in pieces of 2048 columns
+    w = random_packed(rng, kind, rows, cols)
+    m = ex.upload(kind, rows, cols, w)
+    wf = orc.dequant_matrix(kind, rows, cols, w).astype(np.float64)
+    tol = 4e-6 * np.abs(wf).max() * 1.7
+    ex.set_path(3)
+    for c in range(cols):
+        x = np.zeros((3, cols), np.float32)
+        x[0, c] = 1.7
+        x[2, c] = -0.85
+        x[1, (c * 7 + 3) % cols] = 1.7
+        y1 = np.empty(rows, np.float32)
+        ex.gemv_resident(m, x[0], y1)
+        assert np.abs(y1 - wf[:, c] * 1.7).max() <= tol, (name, c, 1)
+        y3 = np.empty(3 * rows, np.float32)
+        ex.gemm_resident(m, 3, x, y3)
+        y3 = y3.reshape(3, rows)
+        assert np.abs(y3[0] - wf[:, c] * 1.7).max() <= tol, (name, c, 3)
+        assert np.abs(y3[1] - wf[:, (c * 7 + 3) % cols] * 1.7).max() <= tol, (name, c, "row 1")
+        assert np.abs(y3[2] + wf[:, c] * 0.85).max() <= tol, (name, c, "row 2")
+    ex.set_path(0)
+    m.free()
+
+
 def test_config1_q8_0_4096_gemv_seed0(ex, orc):
     """BASELINE config 1: Q8_0 4096x4096, x ~ N(0,1), seed 0, M = 1, every kernel family."""
     from llama_rust_b200 import synth
