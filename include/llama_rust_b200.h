@@ -484,6 +484,17 @@ typedef struct llr_llama_config {
 typedef struct llr_llama_layer {
   const llr_matrix *attn_q, *attn_k, *attn_v, *attn_output, *ffn_gate, *ffn_up, *ffn_down;
   const float *attn_norm, *ffn_norm;
+  /* architecture=llama with routed experts [llama_moe_into decode.rs:10366: softmax over all experts, top-k, SwiGLU
+   * experts, weights normalised with the 2^-14 clamp, no shared expert]: n_expert > 0 replaces the dense FFN of this
+   * layer by the routed layer of llr_moe_ffn (ffn_gate / ffn_up / ffn_down are then not read and may be NULL).
+   * ffn_gate_inp: n_expert x n_embd; the three arrays hold n_expert matrices each (n_ff x n_embd, n_ff x n_embd,
+   * n_embd x n_ff; cfg.n_ff is the experts' width).  The arrays are copied at session creation.  The per-expert row
+   * counts of every layer visit the host, so the steps of such a session are not replayed from a graph. */
+  uint32_t n_expert, n_expert_used;
+  const llr_matrix* ffn_gate_inp;
+  const llr_matrix* const* ffn_gate_exps;
+  const llr_matrix* const* ffn_up_exps;
+  const llr_matrix* const* ffn_down_exps;
 } llr_llama_layer;
 typedef struct llr_llama_model {
   llr_llama_config cfg;

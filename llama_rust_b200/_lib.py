@@ -67,7 +67,10 @@ class LlamaConfig(C.Structure):
 
 class LlamaLayer(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down",
-                                          "attn_norm", "ffn_norm")]
+                                          "attn_norm", "ffn_norm")] + \
+               [("n_expert", C.c_uint32), ("n_expert_used", C.c_uint32), ("ffn_gate_inp", C.c_void_p),
+                ("ffn_gate_exps", C.POINTER(C.c_void_p)), ("ffn_up_exps", C.POINTER(C.c_void_p)),
+                ("ffn_down_exps", C.POINTER(C.c_void_p))]
 
 
 class LlamaModel(C.Structure):

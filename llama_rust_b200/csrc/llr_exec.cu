@@ -1596,6 +1596,17 @@ struct llr_session {
   int *table_dev = nullptr, *row_pos = nullptr, *row_seq = nullptr, *last_rows = nullptr;
   // decode steps (one row): the independent products of a layer as one launch each -- {q, k, v} and {gate, up}
   std::vector<llr::Program*> qkv_prog, gateup_prog;
+  // layers whose FFN is a routed-expert layer (architecture=llama with n_expert > 0): own copies of the matrix arrays
+  struct Moe {
+    std::vector<const llr_matrix*> gate, up, down;
+    llr_moe_layer layer{};
+    MoeShape S;
+  };
+  std::vector<std::unique_ptr<Moe>> moe;  // per layer, null: dense FFN
+  char* moe_tables = nullptr;             // routing tables for max_batch rows, one device block
+  float *moe_logits = nullptr, *moe_wts = nullptr, *moe_w = nullptr;
+  int *moe_ids = nullptr, *moe_tok_of_row = nullptr, *moe_rows_of_tok = nullptr, *moe_fill = nullptr, *moe_first_row = nullptr;
+  unsigned char* moe_local = nullptr;
   cudaGraphExec_t step_graph = nullptr;  // one decode step, captured once per kernel path
   int step_graph_path = -1, step_kernels = 0;
   bool use_graph = true;
@@ -1612,6 +1623,7 @@ void session_release(llr_session* s) {
   int* ibufs[] = {s->ids, s->pos_dev, s->count_dev, s->table_dev, s->row_pos, s->row_seq, s->last_rows};
   for (int* p : ibufs) if (p) cudaFree(p);
   if (s->step_graph) cudaGraphExecDestroy(s->step_graph);
+  if (s->moe_tables) cudaFree(s->moe_tables);
   for (llr::Program* p : s->qkv_prog) program_destroy(p);
   for (llr::Program* p : s->gateup_prog) program_destroy(p);
   cudaGetLastError();
@@ -1646,6 +1658,30 @@ int session_reserve(llr_session* s, size_t seq, size_t upto) {
   return LLR_OK;
 }
 
+// The routed-expert layer of layer li over the n normalised rows in s->xn; the result (not yet added to the residual
+// stream) goes to s->proj.  The per-expert row counts visit the host, which sizes the expert launches with them.
+cudaError_t session_moe_ffn(llr_session* s, size_t li, size_t n) {
+  llr_exec* e = s->owner;
+  llr_session::Moe& M = *s->moe[li];
+  const MoeShape& S = M.S;
+  cudaError_t ce;
+  if ((ce = moe_route(e, &M.layer, S, n, s->xn, s->moe_logits, s->moe_ids, s->moe_wts)) != cudaSuccess ||
+      (ce = launch_bucket(s->moe_ids, s->moe_wts, s->moe_local, (int)n, (int)S.n_exp, (int)S.n_used, s->moe_first_row, s->moe_tok_of_row,
+                          s->moe_rows_of_tok, s->moe_w, s->moe_fill, e->stream, &e->ctr.launches)) != cudaSuccess)
+    return ce;
+  std::vector<int> first_row(S.n_exp + 1, 0);
+  if ((ce = cudaMemcpyAsync(first_row.data(), s->moe_first_row, (S.n_exp + 1) * sizeof(int), cudaMemcpyDeviceToHost, e->stream)) != cudaSuccess ||
+      (ce = cudaStreamSynchronize(e->stream)) != cudaSuccess)
+    return ce;
+  e->ctr.d2h_bytes += (S.n_exp + 1) * sizeof(int);
+  const size_t n_rows = n * S.n_used;
+  if ((ce = grow_device(&e->dev_moe, &e->dev_moe_cap, moe_buffer_floats(S, n_rows) + 256)) != cudaSuccess) return ce;
+  const MoeBuffers B = moe_carve((float*)(((uintptr_t)e->dev_moe + 255) & ~(uintptr_t)255), S, n_rows);
+  if ((ce = moe_run_experts(e, &M.layer, S, first_row, s->xn, s->moe_tok_of_row, B)) != cudaSuccess) return ce;
+  return launch_scatter_combine(B.y, s->moe_rows_of_tok, s->moe_w, s->proj, (int)n, (int)S.n_used, (int)S.n_embd, e->stream,
+                                &e->ctr.launches);
+}
+
 // The layers over n rows whose token ids lie at ids_dev; rows stand where `rows` says.  Leaves the residual stream in
 // s->x and the last ffn_down result, not yet added, in s->proj (returned through *pending).
 cudaError_t session_layers(llr_session* s, const int* ids_dev, size_t n, const RowMap& rows, const float** pending_out) {
@@ -1676,6 +1712,11 @@ cudaError_t session_layers(llr_session* s, const int* ids_dev, size_t n, const R
     }
     if ((ce = session_matmul(e, W.attn_output, n, s->attn, s->proj)) != cudaSuccess) break;
     if ((ce = launch_rmsnorm(s->x, s->proj, s->ffn_norm[li], s->xn, (int)n, (int)E, c.rms_eps, st, L)) != cudaSuccess) break;
+    if (s->moe[li]) {  // routed experts stand where the dense FFN stands (llama_moe_into decode.rs:10366)
+      if ((ce = session_moe_ffn(s, li, n)) != cudaSuccess) break;
+      pending = s->proj;
+      continue;
+    }
     if (one_row_programs && s->gateup_prog[li]) {
       if ((ce = program_run(s->gateup_prog[li], st, e->err_flag, e->poll_limit, L)) != cudaSuccess) break;
     } else {
@@ -1743,13 +1784,21 @@ int session_create(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t k
   auto shape_ok = [&](const llr_matrix* w, size_t rows, size_t cols) {
     return w && w->owner == e && (size_t)w->rows == rows && (size_t)w->cols == cols;
   };
+  size_t max_expert = 0, max_used = 0;  // over the layers with routed experts
   const llr_matrix* output = m->output ? m->output : m->token_embd;
   if (!shape_ok(m->token_embd, V, E) || !shape_ok(output, V, E))
     return fail(e, LLR_ERR_INVALID, "token_embd / output must be n_vocab x n_embd matrices of this executor");
   for (uint32_t li = 0; li < c.n_layer; ++li) {
     const llr_llama_layer& W = m->layers[li];
-    if (!shape_ok(W.attn_q, QW, E) || !shape_ok(W.attn_k, KVW, E) || !shape_ok(W.attn_v, KVW, E) || !shape_ok(W.attn_output, E, QW) ||
-        !shape_ok(W.ffn_gate, FF, E) || !shape_ok(W.ffn_up, FF, E) || !shape_ok(W.ffn_down, E, FF))
+    bool ffn_ok = shape_ok(W.ffn_gate, FF, E) && shape_ok(W.ffn_up, FF, E) && shape_ok(W.ffn_down, E, FF);
+    if (W.n_expert > 0) {
+      ffn_ok = W.n_expert_used > 0 && W.n_expert_used <= W.n_expert && W.n_expert <= 4096 && shape_ok(W.ffn_gate_inp, W.n_expert, E) &&
+               W.ffn_gate_exps && W.ffn_up_exps && W.ffn_down_exps && E % 4 == 0;
+      for (uint32_t ex = 0; ex < W.n_expert && ffn_ok; ++ex)
+        ffn_ok = shape_ok(W.ffn_gate_exps[ex], FF, E) && shape_ok(W.ffn_up_exps[ex], FF, E) && shape_ok(W.ffn_down_exps[ex], E, FF);
+      if (ffn_ok) { max_expert = std::max(max_expert, (size_t)W.n_expert); max_used = std::max(max_used, (size_t)W.n_expert_used); }
+    }
+    if (!shape_ok(W.attn_q, QW, E) || !shape_ok(W.attn_k, KVW, E) || !shape_ok(W.attn_v, KVW, E) || !shape_ok(W.attn_output, E, QW) || !ffn_ok)
       return fail(e, LLR_ERR_INVALID, "blk." + std::to_string(li) + ": matrix shapes do not match the configuration (or another executor owns them)");
   }
   DeviceGuard guard(e->device);
@@ -1760,6 +1809,21 @@ int session_create(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t k
   s->embd = m->token_embd;
   s->output = output;
   s->layers.assign(m->layers, m->layers + c.n_layer);
+  s->moe.resize(c.n_layer);
+  for (uint32_t li = 0; li < c.n_layer; ++li) {
+    const llr_llama_layer& W = m->layers[li];
+    if (W.n_expert == 0) continue;
+    std::unique_ptr<llr_session::Moe> M(new llr_session::Moe);
+    M->gate.assign(W.ffn_gate_exps, W.ffn_gate_exps + W.n_expert);
+    M->up.assign(W.ffn_up_exps, W.ffn_up_exps + W.n_expert);
+    M->down.assign(W.ffn_down_exps, W.ffn_down_exps + W.n_expert);
+    M->layer = llr_moe_layer{W.n_expert, W.n_expert_used, 1u, W.ffn_gate_inp, M->gate.data(), M->up.data(), M->down.data()};
+    M->S.n_embd = E; M->S.n_ff = FF; M->S.n_exp = W.n_expert; M->S.n_used = W.n_expert_used;
+    M->S.local.assign(W.n_expert, 1);
+    s->moe[li] = std::move(M);
+    s->layers[li].ffn_gate_exps = s->layers[li].ffn_up_exps = s->layers[li].ffn_down_exps = nullptr;  // the copies above are the ones used
+    s->use_graph = false;  // every routed layer synchronizes for its row counts
+  }
   const float n_rot = (float)(uint16_t)c.head_dim;
   s->shape = WalkShape{(int)c.n_embd, (int)c.n_head, (int)c.n_head_kv, (int)c.head_dim, (int)c.n_ff, (int)c.n_ctx, c.rms_eps, c.rope_base,
                        std::pow(c.rope_base, -2.0f / n_rot)};  // decode.rs:11578: theta_scale in f32
@@ -1797,7 +1861,24 @@ int session_create(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t k
   ialloc(&s->table_dev, n_seq * s->max_blocks); ialloc(&s->row_pos, B); ialloc(&s->row_seq, B); ialloc(&s->last_rows, n_seq);
   if (ce == cudaSuccess) ce = cudaMemset(s->pos_dev, 0, sizeof(int));
   if (ce == cudaSuccess) ce = cudaMemset(s->table_dev, 0, n_seq * s->max_blocks * sizeof(int));
-  if (const char* g = std::getenv("LLR_SESSION_GRAPH")) s->use_graph = std::strcmp(g, "0") != 0;
+  if (const char* g = std::getenv("LLR_SESSION_GRAPH")) s->use_graph = s->use_graph && std::strcmp(g, "0") != 0;
+  if (max_expert > 0 && ce == cudaSuccess) {
+    const size_t n_rows = B * max_used;
+    auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    size_t at = 0;
+    auto take = [&](size_t bytes) { const size_t o = at; at = up256(at + bytes); return o; };
+    const size_t o_logits = take(B * max_expert * 4), o_ids = take(n_rows * 4), o_wts = take(n_rows * 4), o_tor = take(n_rows * 4),
+                 o_rot = take(n_rows * 4), o_w = take(n_rows * 4), o_fill = take(B * 4), o_first = take((max_expert + 1) * 4),
+                 o_local = take(max_expert);
+    ce = cudaMalloc((void**)&s->moe_tables, at);
+    if (ce == cudaSuccess) {
+      char* tb = s->moe_tables;
+      s->moe_logits = (float*)(tb + o_logits); s->moe_ids = (int*)(tb + o_ids); s->moe_wts = (float*)(tb + o_wts);
+      s->moe_tok_of_row = (int*)(tb + o_tor); s->moe_rows_of_tok = (int*)(tb + o_rot); s->moe_w = (float*)(tb + o_w);
+      s->moe_fill = (int*)(tb + o_fill); s->moe_first_row = (int*)(tb + o_first); s->moe_local = (unsigned char*)(tb + o_local);
+      ce = cudaMemset(s->moe_local, 1, max_expert);
+    }
+  }
   // One launch for the products of a layer that share their input, where the streaming decode kernel takes all of them
   s->qkv_prog.assign(c.n_layer, nullptr);
   s->gateup_prog.assign(c.n_layer, nullptr);
@@ -1820,7 +1901,7 @@ int session_create(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t k
   for (uint32_t li = 0; li < c.n_layer && ce == cudaSuccess; ++li) {
     const llr_llama_layer& W = s->layers[li];
     group({{W.attn_q, s->q}, {W.attn_k, s->k}, {W.attn_v, s->v}}, &s->qkv_prog[li]);
-    group({{W.ffn_gate, s->gate}, {W.ffn_up, s->up}}, &s->gateup_prog[li]);
+    if (!s->moe[li]) group({{W.ffn_gate, s->gate}, {W.ffn_up, s->up}}, &s->gateup_prog[li]);
   }
   if (ce != cudaSuccess) {
     session_release(s);

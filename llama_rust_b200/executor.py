@@ -116,7 +116,9 @@ class Session:
                  output_norm=None, n_seq: int = 1, kv_blocks: int = 0, block_tokens: int = 16):
         """cfg: n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab, n_ctx (+ rms_eps, rope_base);
         layers: per layer a dict attn_q, attn_k, attn_v, attn_output, ffn_gate, ffn_up, ffn_down (Matrix) and
-        optionally attn_norm, ffn_norm (float32 arrays of n_embd; absent: all ones)."""
+        optionally attn_norm, ffn_norm (float32 arrays of n_embd; absent: all ones).  A layer with routed experts
+        (architecture=llama, n_expert > 0) has ffn_gate_inp (Matrix, n_expert x n_embd), ffn_gate_exps, ffn_up_exps,
+        ffn_down_exps (lists of n_expert matrices) and n_expert_used instead of ffn_gate, ffn_up, ffn_down."""
         self._exec = executor
         self._keep = []  # host arrays the C call reads during creation
         c = _lib.LlamaConfig(*(int(cfg[k]) for k in ("n_layer", "n_embd", "n_head", "n_head_kv", "head_dim", "n_ff",
@@ -131,8 +133,15 @@ class Session:
             self._keep.append(a)
             return a.ctypes.data
         for i, L in enumerate(layers):
-            arr[i] = _lib.LlamaLayer(*(L[k]._h for k in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up",
-                                                         "ffn_down")), norm(L.get("attn_norm")), norm(L.get("ffn_norm")))
+            dense = [L[k]._h if L.get(k) is not None else None for k in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate",
+                                                                          "ffn_up", "ffn_down")]
+            arr[i] = _lib.LlamaLayer(*dense, norm(L.get("attn_norm")), norm(L.get("ffn_norm")))
+            if L.get("ffn_gate_inp") is not None:
+                n_expert = len(L["ffn_gate_exps"])
+                exps = [(C.c_void_p * n_expert)(*[m._h for m in L[k]]) for k in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps")]
+                self._keep.extend(exps)
+                arr[i].n_expert, arr[i].n_expert_used, arr[i].ffn_gate_inp = n_expert, int(L["n_expert_used"]), L["ffn_gate_inp"]._h
+                arr[i].ffn_gate_exps, arr[i].ffn_up_exps, arr[i].ffn_down_exps = exps
         model = _lib.LlamaModel(c, token_embd._h, output._h if output is not None else None, norm(output_norm), arr)
         h = C.c_void_p()
         executor._check(lib().llr_session_create_paged(executor._h, C.byref(model), n_seq, kv_blocks, block_tokens, C.byref(h)))

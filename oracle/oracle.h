@@ -137,6 +137,22 @@ int orc_llama_generate(const orc_llama_cfg* c, orc_matmul_cb cb, void* user, con
                        int n_prompt, int n_gen, int32_t* out_ids, float* out_margin, float* last_logits,
                        int threads);
 
+/* The same walk for architecture=llama with n_expert > 0 (llama_moe_into decode.rs:10366): every layer's dense FFN is
+ * the routed-expert layer above with norm_w = 1.  router[layer]; gate / up / down[layer * n_expert + e]; the dense
+ * ffn entries of tensors[] are not read.  moe == NULL: the dense walk. */
+typedef struct orc_llama_moe {
+  int32_t n_expert, n_used, router_kind, expert_kind;
+  const uint8_t* const* router;
+  const uint8_t* const* gate;
+  const uint8_t* const* up;
+  const uint8_t* const* down;
+} orc_llama_moe;
+int orc_llama_generate_moe(const orc_llama_cfg* c, const orc_llama_moe* moe, orc_matmul_cb cb, void* user,
+                           const uint8_t* const* tensors, const int* kinds, int embd_kind, const uint8_t* token_embd,
+                           int (*embd_cb)(void* user, int32_t token, float* row), const int32_t* prompt,
+                           int n_prompt, int n_gen, int32_t* out_ids, float* out_margin, float* last_logits,
+                           int threads);
+
 #ifdef __cplusplus
 }
 #endif

@@ -106,6 +106,17 @@ int orc_llama_generate(const orc_llama_cfg* c, orc_matmul_cb cb, void* user, con
                        int (*embd_cb)(void* user, int32_t token, float* row), const int32_t* prompt,
                        int n_prompt, int n_gen, int32_t* out_ids, float* out_margin, float* last_logits,
                        int threads) {
+  return orc_llama_generate_moe(c, nullptr, cb, user, tensors, kinds, embd_kind, token_embd, embd_cb, prompt, n_prompt, n_gen,
+                                out_ids, out_margin, last_logits, threads);
+}
+
+// The same walk with the dense FFN of every layer replaced by the routed experts of `moe` when it is given
+// (llama_moe_into decode.rs:10366: architecture=llama with n_expert > 0, norm_w = true, no shared expert).
+int orc_llama_generate_moe(const orc_llama_cfg* c, const orc_llama_moe* moe, orc_matmul_cb cb, void* user,
+                           const uint8_t* const* tensors, const int* kinds, int embd_kind, const uint8_t* token_embd,
+                           int (*embd_cb)(void* user, int32_t token, float* row), const int32_t* prompt,
+                           int n_prompt, int n_gen, int32_t* out_ids, float* out_margin, float* last_logits,
+                           int threads) {
   const int64_t E = c->n_embd, H = c->n_head, HKV = c->n_head_kv, HD = c->head_dim, FF = c->n_ff, V = c->n_vocab;
   const int64_t QW = H * HD, KVW = HKV * HD;
   if (n_prompt <= 0 || n_prompt + n_gen > c->n_ctx || H % HKV != 0) return ORC_ERR_SIZE;
@@ -114,6 +125,8 @@ int orc_llama_generate(const orc_llama_cfg* c, orc_matmul_cb cb, void* user, con
       v((size_t)(nmax * KVW)), attn((size_t)(nmax * QW)), proj((size_t)(nmax * E)), gate((size_t)(nmax * FF)),
       up((size_t)(nmax * FF)), ffn((size_t)(nmax * E)), xn((size_t)E), logits((size_t)V), scores((size_t)c->n_ctx);
   std::vector<float> ones((size_t)E, 1.0f);
+  std::vector<int32_t> sel_ids;
+  std::vector<float> sel_w;
   std::vector<float> cache_k((size_t)c->n_layer * HKV * c->n_ctx * HD), cache_v(cache_k.size());
   auto kv_off = [&](int64_t layer, int64_t h, int64_t t) { return ((layer * HKV + h) * c->n_ctx + t) * HD; };
   const int64_t embd_rb = orc_row_bytes(embd_kind, E);
@@ -179,6 +192,15 @@ int orc_llama_generate(const orc_llama_cfg* c, orc_matmul_cb cb, void* user, con
       for (int64_t i = 0; i < n * E; ++i) x[(size_t)i] = proj[(size_t)i] + residual[(size_t)i];
       std::memcpy(residual.data(), x.data(), sizeof(float) * (size_t)(n * E));
       for (int64_t t = 0; t < n; ++t) orc_rmsnorm(x.data() + t * E, ones.data(), E, c->rms_eps);
+      if (moe) {
+        const int64_t NE = moe->n_expert;
+        sel_ids.resize((size_t)(n * moe->n_used));
+        sel_w.resize((size_t)(n * moe->n_used));
+        if ((rc = orc_moe_ffn(moe->n_expert, moe->n_used, 1, moe->router_kind, moe->router[li], orc_row_bytes(moe->router_kind, E) * NE,
+                              moe->expert_kind, moe->gate + li * NE, moe->up + li * NE, moe->down + li * NE, E, FF, n, x.data(),
+                              ffn.data(), sel_ids.data(), sel_w.data(), threads)))
+          return rc;
+      } else {
       if ((rc = walk_matmul(c, cb, user, tensors, kinds, base + 4, FF, E, n, x.data(), gate.data(), threads))) return rc;
       if ((rc = walk_matmul(c, cb, user, tensors, kinds, base + 5, FF, E, n, x.data(), up.data(), threads))) return rc;
       for (int64_t i = 0; i < n * FF; ++i) {
@@ -186,6 +208,7 @@ int orc_llama_generate(const orc_llama_cfg* c, orc_matmul_cb cb, void* user, con
         gate[(size_t)i] = a * up[(size_t)i];
       }
       if ((rc = walk_matmul(c, cb, user, tensors, kinds, base + 6, E, FF, n, gate.data(), ffn.data(), threads))) return rc;
+      }
       for (int64_t i = 0; i < n * E; ++i) x[(size_t)i] = ffn[(size_t)i] + residual[(size_t)i];
     }
     std::memcpy(xn.data(), x.data() + (n - 1) * E, sizeof(float) * (size_t)E);

@@ -24,6 +24,13 @@ orc.lib.orc_llama_generate.argtypes = [C.POINTER(Cfg), C.c_void_p, C.c_void_p, C
                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p,
                                        C.c_void_p, C.c_void_p, C.c_int]
 
+class MoeCfg(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_expert", "n_used", "router_kind", "expert_kind")] + \
+               [(n, C.c_void_p) for n in ("router", "gate", "up", "down")]
+
+
+orc.lib.orc_llama_generate_moe.argtypes = [C.POINTER(Cfg), C.POINTER(MoeCfg)] + orc.lib.orc_llama_generate.argtypes[1:]
+
 LLAMA3_8B = dict(n_layer=32, n_embd=4096, n_head=32, n_head_kv=8, head_dim=128, n_ff=14336, n_vocab=128256)
 
 
@@ -50,27 +57,38 @@ def prompt_ids(n, vocab, seed):
     return (synth.words(seed, 0, n) % np.uint64(vocab)).astype(np.int32)
 
 
-def _generate(c, cb, tensors_ptr, kinds_ptr, embd_kind, embd_ptr, embd_cb, prompt, n_gen, threads, want_logits):
+def _generate(c, cb, tensors_ptr, kinds_ptr, embd_kind, embd_ptr, embd_cb, prompt, n_gen, threads, want_logits, moe=None):
     ids = np.zeros(n_gen, np.int32)
     margin = np.zeros(n_gen, np.float32)
     logits = np.zeros(c.n_vocab, np.float32) if want_logits else None
     p = np.ascontiguousarray(prompt, np.int32)
-    rc = orc.lib.orc_llama_generate(C.byref(c), cb, None, tensors_ptr, kinds_ptr, embd_kind, embd_ptr, embd_cb,
-                                    p.ctypes.data, p.size, n_gen, ids.ctypes.data, margin.ctypes.data,
-                                    logits.ctypes.data if want_logits else None, threads)
+    rc = orc.lib.orc_llama_generate_moe(C.byref(c), C.byref(moe) if moe is not None else None, cb, None, tensors_ptr, kinds_ptr,
+                                        embd_kind, embd_ptr, embd_cb, p.ctypes.data, p.size, n_gen, ids.ctypes.data,
+                                        margin.ctypes.data, logits.ctypes.data if want_logits else None, threads)
     if rc:
         raise RuntimeError(f"walk failed with status {rc}")
     return ids, margin, logits
 
 
-def run_cpu(cfg, n_ctx, weights, embd, prompt, n_gen, threads=0, want_logits=False, kinds=None, embd_kind=Q4_K):
+def run_cpu(cfg, n_ctx, weights, embd, prompt, n_gen, threads=0, want_logits=False, kinds=None, embd_kind=Q4_K, moe=None):
     """weights: packed numpy arrays in tensor_list order; embd: packed token_embd (Q4_K unless embd_kind says otherwise);
-    kinds: dtype of each tensor when it is not tensor_list's mix."""
+    kinds: dtype of each tensor when it is not tensor_list's mix.  moe (architecture=llama with routed experts): a dict
+    n_used, router_kind, expert_kind, router[layer], gate / up / down[layer][expert] of packed arrays; the ffn entries of
+    `weights` are then not read and may be None."""
     c = make_cfg(cfg, n_ctx)
     tl = tensor_list(cfg)
-    ptrs = (C.c_void_p * len(tl))(*[w.ctypes.data for w in weights])
+    ptrs = (C.c_void_p * len(tl))(*[None if w is None else w.ctypes.data for w in weights])
     kinds = (C.c_int * len(tl))(*(kinds if kinds is not None else [t[1] for t in tl]))
-    return _generate(c, None, ptrs, kinds, embd_kind, embd.ctypes.data, None, prompt, n_gen, threads, want_logits)
+    m = None
+    if moe is not None:
+        n_expert = len(moe["gate"][0])
+        flat = {k: (C.c_void_p * (cfg["n_layer"] * n_expert))(*[a.ctypes.data for per_layer in moe[k] for a in per_layer])
+                for k in ("gate", "up", "down")}
+        router = (C.c_void_p * cfg["n_layer"])(*[a.ctypes.data for a in moe["router"]])
+        m = MoeCfg(n_expert, moe["n_used"], moe["router_kind"], moe["expert_kind"], C.cast(router, C.c_void_p),
+                   C.cast(flat["gate"], C.c_void_p), C.cast(flat["up"], C.c_void_p), C.cast(flat["down"], C.c_void_p))
+        m._keep = (flat, router)
+    return _generate(c, None, ptrs, kinds, embd_kind, embd.ctypes.data, None, prompt, n_gen, threads, want_logits, moe=m)
 
 
 def run_gpu(cfg, n_ctx, ex, mats, embd_mat, prompt, n_gen, want_logits=False):

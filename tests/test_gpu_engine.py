@@ -18,6 +18,9 @@ MODELS = {
     "llama-f32": (dict(n_layer=2, n_embd=64, n_head=4, n_head_kv=2, head_dim=16, n_ff=128, n_vocab=48), F32, F32, F32),
     "llama-q4_0": (dict(n_layer=2, n_embd=64, n_head=4, n_head_kv=2, head_dim=16, n_ff=128, n_vocab=48), Q4_0, Q4_0, F32),
     "llama-q4_k": (dict(n_layer=2, n_embd=256, n_head=4, n_head_kv=2, head_dim=64, n_ff=512, n_vocab=48), Q4_K, Q6_K, Q4_K),
+    # architecture=llama with routed experts (llama_moe_into decode.rs:10366): four experts, two per token, F32 router
+    "llama-moe-q4_k": (dict(n_layer=2, n_embd=256, n_head=4, n_head_kv=2, head_dim=64, n_ff=256, n_vocab=48, n_expert=4, n_used=2),
+                       Q4_K, Q6_K, Q4_K),
 }
 
 
@@ -40,7 +43,18 @@ def _model(name):
         embd = rng.standard_normal(cfg["n_vocab"] * cfg["n_embd"]).astype(np.float32).view(np.uint8)
     else:
         embd = lw.center_q4k(random_packed(rng, Q4_K, cfg["n_vocab"], cfg["n_embd"]))
-    return cfg, tl, kinds, weights, embd_kind, embd
+    moe = None
+    if cfg.get("n_expert"):
+        E, FF, NE = cfg["n_embd"], cfg["n_ff"], cfg["n_expert"]
+        moe = dict(n_used=cfg["n_used"], router_kind=F32, expert_kind=Q4_K,
+                   router=[(rng.standard_normal(NE * E) * 0.5).astype(np.float32).view(np.uint8) for _ in range(cfg["n_layer"])],
+                   gate=[[lw.center_q4k(random_packed(rng, Q4_K, FF, E)) for _ in range(NE)] for _ in range(cfg["n_layer"])],
+                   up=[[lw.center_q4k(random_packed(rng, Q4_K, FF, E)) for _ in range(NE)] for _ in range(cfg["n_layer"])],
+                   down=[[lw.center_q4k(random_packed(rng, Q4_K, E, FF)) for _ in range(NE)] for _ in range(cfg["n_layer"])])
+        for i, (n, _, _, _) in enumerate(tl):  # the dense ffn tensors do not exist in such a model
+            if ".ffn_" in n:
+                weights[i] = None
+    return cfg, tl, kinds, weights, embd_kind, embd, moe
 
 
 def _check(actual, expected, what):  # native_cuda_parity.rs:150-158
@@ -50,23 +64,32 @@ def _check(actual, expected, what):  # native_cuda_parity.rs:150-158
 
 def _sessions(ex, name, n_ctx=32, **kw):
     from llama_rust_b200 import Session
-    cfg, tl, kinds, weights, embd_kind, embd = _model(name)
-    mats = [ex.upload(k, r, c, w) for (n, _, r, c), k, w in zip(tl, kinds, weights)]
+    cfg, tl, kinds, weights, embd_kind, embd, moe = _model(name)
+    mats = [None if w is None else ex.upload(k, r, c, w) for (n, _, r, c), k, w in zip(tl, kinds, weights)]
     embd_mat = ex.upload(embd_kind, cfg["n_vocab"], cfg["n_embd"], embd)
     layers = [dict(zip(("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down"), mats[7 * li:7 * li + 7]))
               for li in range(cfg["n_layer"])]
+    if moe is not None:
+        E, FF, NE = cfg["n_embd"], cfg["n_ff"], cfg["n_expert"]
+        for li, L in enumerate(layers):
+            L["n_expert_used"] = moe["n_used"]
+            L["ffn_gate_inp"] = ex.upload(F32, NE, E, moe["router"][li])
+            L["ffn_gate_exps"] = [ex.upload(Q4_K, FF, E, w) for w in moe["gate"][li]]
+            L["ffn_up_exps"] = [ex.upload(Q4_K, FF, E, w) for w in moe["up"][li]]
+            L["ffn_down_exps"] = [ex.upload(Q4_K, E, FF, w) for w in moe["down"][li]]
 
     def make(**kw):
         return Session(ex, dict(cfg, n_ctx=n_ctx), embd_mat, layers, output=mats[-1], **kw)
 
     def cpu_logits(tokens):
         return lw.run_cpu(cfg, n_ctx, weights, embd, np.asarray(tokens, np.int32), 0, want_logits=True, kinds=kinds,
-                          embd_kind=embd_kind)[2]
+                          embd_kind=embd_kind, moe=moe)[2]
 
     def cpu_greedy(tokens, n):
-        ids, margin, _ = lw.run_cpu(cfg, n_ctx, weights, embd, np.asarray(tokens, np.int32), n, kinds=kinds, embd_kind=embd_kind)
+        ids, margin, _ = lw.run_cpu(cfg, n_ctx, weights, embd, np.asarray(tokens, np.int32), n, kinds=kinds, embd_kind=embd_kind,
+                                    moe=moe)
         return ids, margin
-    return make, cpu_logits, cpu_greedy, (mats, embd_mat)
+    return make, cpu_logits, cpu_greedy, (mats, embd_mat, layers)
 
 
 @pytest.mark.parametrize("name", list(MODELS))
