@@ -149,6 +149,7 @@ class Session:
         self.n_seq = n_seq
         self.n_vocab = int(cfg["n_vocab"])
         self._keep = []
+        self._model = (token_embd, output, layers)  # the device reads these matrices for as long as the session lives
         self._ids = [[] for _ in range(n_seq)]  # token ids whose keys and values each sequence's cache holds
 
     def prefill(self, tokens, want_logits: bool = False):

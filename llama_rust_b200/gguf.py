@@ -200,23 +200,38 @@ def llama_config(g: GgufFile, n_ctx: int | None = None) -> dict:
     emb = g.tensor("token_embd.weight")
     if emb is None:
         raise KeyError("token_embd.weight")
-    return dict(n_layer=need("block_count"), n_embd=n_embd, n_head=n_head, n_head_kv=n_head_kv, head_dim=head_dim,
-                n_ff=need("feed_forward_length"), n_vocab=emb.n_rows,
-                n_ctx=n_ctx or g.kv_u32(f"{arch}.context_length") or 2048,
-                rms_eps=g.kv_f32(f"{arch}.attention.layer_norm_rms_epsilon") or 1e-5,
-                rope_base=g.kv_f32(f"{arch}.rope.freq_base") or 10000.0)
+    cfg = dict(n_layer=need("block_count"), n_embd=n_embd, n_head=n_head, n_head_kv=n_head_kv, head_dim=head_dim,
+               n_ff=need("feed_forward_length"), n_vocab=emb.n_rows,
+               n_ctx=n_ctx or g.kv_u32(f"{arch}.context_length") or 2048,
+               rms_eps=g.kv_f32(f"{arch}.attention.layer_norm_rms_epsilon") or 1e-5,
+               rope_base=g.kv_f32(f"{arch}.rope.freq_base") or 10000.0)
+    n_expert = g.kv_u32(f"{arch}.expert_count") or 0
+    if n_expert:  # architecture=llama with routed experts (llama.expert_count / llama.expert_used_count)
+        n_used = g.kv_u32(f"{arch}.expert_used_count") or 0
+        if not 0 < n_used <= n_expert:
+            raise GgufError(27, f"{arch}.expert_used_count")
+        cfg.update(n_expert=n_expert, n_expert_used=n_used)
+    return cfg
 
 
 def load_llama(ex: Executor, g: GgufFile, n_ctx: int | None = None, **session_args) -> Session:
-    """Uploads every weight of a dense Llama-family file packed and returns the device-resident session.  `output.weight`
+    """Uploads every weight of a Llama-family file (dense, or with routed experts) packed and returns the device-resident session.  `output.weight`
     falls back to the token embedding when the file ties them (decode.rs:2069-2072)."""
     cfg = llama_config(g, n_ctx)
     token_embd = g.upload(ex, "token_embd.weight")
     output = g.upload(ex, "output.weight") if g.tensor("output.weight") is not None else None
     layers = []
+    n_expert = cfg.get("n_expert", 0)
     for i in range(cfg["n_layer"]):
-        L = {k: g.upload(ex, f"blk.{i}.{k}.weight") for k in ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate",
-                                                               "ffn_up", "ffn_down")}
+        L = {k: g.upload(ex, f"blk.{i}.{k}.weight") for k in ("attn_q", "attn_k", "attn_v", "attn_output")}
+        if n_expert and g.tensor(f"blk.{i}.ffn_gate_inp.weight") is not None:
+            # routed experts: the router and one resident matrix per expert part of the 3-D *_exps tensors
+            L["ffn_gate_inp"] = g.upload(ex, f"blk.{i}.ffn_gate_inp.weight")
+            L["n_expert_used"] = cfg["n_expert_used"]
+            for k in ("ffn_gate_exps", "ffn_up_exps", "ffn_down_exps"):
+                L[k] = [g.upload(ex, f"blk.{i}.{k}.weight", part=e) for e in range(n_expert)]
+        else:
+            L.update({k: g.upload(ex, f"blk.{i}.{k}.weight") for k in ("ffn_gate", "ffn_up", "ffn_down")})
         L["attn_norm"] = g.f32s(f"blk.{i}.attn_norm.weight")
         L["ffn_norm"] = g.f32s(f"blk.{i}.ffn_norm.weight")
         layers.append(L)

@@ -114,3 +114,59 @@ def test_a_llama_file_loads_into_a_session(orc):
     assert np.array_equal(first.view(np.uint32), want_first.view(np.uint32)) and np.array_equal(ids, want_ids)
     assert len(set(ids.tolist())) > 1
     s.free(); ref.free(); ex.close(); g.close()
+
+
+def test_a_llama_file_with_routed_experts_loads_into_a_session(orc):
+    """architecture=llama with llama.expert_count > 0: the router and the 3-D ffn_*_exps tensors (one expert per slice of the
+    slowest dimension, as the reference's quant_mat takes them, decode.rs:9612) become a session whose logits are those of
+    the session built from the same arrays."""
+    from llama_rust_b200 import Executor, Session
+    from llama_rust_b200.gguf import GgufFile, llama_config, load_llama
+    from helpers import F32, random_packed
+    cfg = dict(n_layer=2, n_embd=256, n_head=4, n_head_kv=2, head_dim=64, n_ff=256, n_vocab=64)
+    NE, NU, E, FF, n_ctx = 4, 2, 256, 256, 32
+    rng = np.random.default_rng(21)
+    tl = [t for t in lw.tensor_list(cfg) if ".ffn_" not in t[0]]
+    dense = [lw.center_q4k(random_packed(rng, Q4_K, r, c)) if dt == Q4_K else random_packed(rng, dt, r, c) for _, dt, r, c in tl]
+    embd = lw.center_q4k(random_packed(rng, Q4_K, 64, E))
+    router = [(rng.standard_normal((NE, E)) * 0.5).astype(np.float32) for _ in range(2)]
+    exps = {k: [[lw.center_q4k(random_packed(rng, Q4_K, r, c)) for _ in range(NE)] for _ in range(2)]
+            for k, (r, c) in (("ffn_gate_exps", (FF, E)), ("ffn_up_exps", (FF, E)), ("ffn_down_exps", (E, FF)))}
+    kv = gf.DEFAULT_KV + [("general.architecture", gf.STRING, "llama"), ("llama.block_count", gf.U32, 2),
+                          ("llama.embedding_length", gf.U32, E), ("llama.feed_forward_length", gf.U32, FF),
+                          ("llama.attention.head_count", gf.U32, 4), ("llama.attention.head_count_kv", gf.U32, 2),
+                          ("llama.expert_count", gf.U32, NE), ("llama.expert_used_count", gf.U32, NU),
+                          ("llama.context_length", gf.U32, n_ctx)]
+    ones = np.ones(E, np.float32)
+    tensors = [("token_embd.weight", 12, (E, 64), embd.tobytes()), ("output_norm.weight", 0, (E,), ones.tobytes())]
+    tensors += [(name, GGML_OF[dt], (c, r), w.tobytes()) for (name, dt, r, c), w in zip(tl, dense)]
+    for i in range(2):
+        tensors += [(f"blk.{i}.attn_norm.weight", 0, (E,), ones.tobytes()), (f"blk.{i}.ffn_norm.weight", 0, (E,), ones.tobytes()),
+                    (f"blk.{i}.ffn_gate_inp.weight", 0, (E, NE), router[i].tobytes())]
+        for k, (r, c) in (("ffn_gate_exps", (FF, E)), ("ffn_up_exps", (FF, E)), ("ffn_down_exps", (E, FF))):
+            tensors.append((f"blk.{i}.{k}.weight", 12, (c, r, NE), b"".join(w.tobytes() for w in exps[k][i])))
+    g = GgufFile(gf.write_gguf(kv, tensors))
+    got = llama_config(g)
+    assert got["n_expert"] == NE and got["n_expert_used"] == NU
+    ex = Executor(0)
+    ex.set_path(3)
+    s = load_llama(ex, g)
+    prompt = [3, 9, 27, 17, 5]
+    first = s.prefill(prompt, want_logits=True)
+    ids, _ = s.decode(6)
+    by_name = {name: ex.upload(dt, r, c, w) for (name, dt, r, c), w in zip(tl, dense)}
+    layers = []
+    for i in range(2):
+        L = {k: by_name[f"blk.{i}.{k}.weight"] for k in ("attn_q", "attn_k", "attn_v", "attn_output")}
+        L["ffn_gate_inp"] = ex.upload(F32, NE, E, router[i].view(np.uint8).reshape(-1))
+        L["n_expert_used"] = NU
+        for k, (r, c) in (("ffn_gate_exps", (FF, E)), ("ffn_up_exps", (FF, E)), ("ffn_down_exps", (E, FF))):
+            L[k] = [ex.upload(Q4_K, r, c, w) for w in exps[k][i]]
+        layers.append(L)
+    embd_mat = ex.upload(Q4_K, 64, E, embd)  # the session reads the model's matrices for as long as it lives
+    ref = Session(ex, dict(cfg, n_ctx=n_ctx), embd_mat, layers, output=by_name["output.weight"], output_norm=ones)
+    want_first = ref.prefill(prompt, want_logits=True)
+    want_ids, _ = ref.decode(6)
+    assert np.all(np.isfinite(first))
+    assert np.array_equal(first.view(np.uint32), want_first.view(np.uint32)) and np.array_equal(ids, want_ids)
+    s.free(); ref.free(); ex.close(); g.close()
