@@ -740,7 +740,8 @@ def run_case(args):
     """One small case for profiling (the full sweep holds 5 GB): prints one JSON line.
       --case gemv    --dtype D --rows R --cols C --m M --reps N --copies K [--path P]   device-pointer products round-robin over K matrices
       --case moe     --tokens T                                                        the routed-expert layer of BASELINE config 5 (2 warm-up + 5 timed calls)
-      --case session --prompt P --gen G [--layers L]                                   the device-resident walk on an 8B-shaped model of L layers"""
+      --case session --prompt P --gen G [--layers L] [--experts E]                     the device-resident walk on an 8B-shaped model of L layers
+                                                                                       (E routed experts per layer, two per token, instead of the dense FFN)"""
     import torch
     from llama_rust_b200 import DTYPES, Executor, row_bytes as lib_row_bytes, synth
     ex = Executor(0)
@@ -772,6 +773,17 @@ def run_case(args):
         from llama_rust_b200 import Session
         embd = ex.synth(Q4_K, VOCAB, D_MODEL, 1)
         layers = [{t: ex.synth(dt, r, c, 10 * li + j) for j, (t, dt, r, c) in enumerate(LAYER)} for li in range(args.layers)]
+        if args.experts:  # config 5's experts in every layer (Mixtral-shaped: routed experts where the dense FFN stands)
+            rng = np.random.default_rng(3)
+            for li, L in enumerate(layers):
+                for t in ("ffn_gate", "ffn_up", "ffn_down"):
+                    L.pop(t).free()
+                L["n_expert_used"] = 2
+                L["ffn_gate_inp"] = ex.upload(DTYPES["F32"], args.experts, D_MODEL,
+                                              (rng.standard_normal((args.experts, D_MODEL)) * 0.05).astype(np.float32).view(np.uint8).reshape(-1))
+                L["ffn_gate_exps"] = [ex.synth(Q4_K, D_FF, D_MODEL, 1000 * li + e) for e in range(args.experts)]
+                L["ffn_up_exps"] = [ex.synth(Q4_K, D_FF, D_MODEL, 1000 * li + 100 + e) for e in range(args.experts)]
+                L["ffn_down_exps"] = [ex.synth(Q4_K, D_MODEL, D_FF, 1000 * li + 200 + e) for e in range(args.experts)]
         head = ex.synth(Q6_K, VOCAB, D_MODEL, 2)
         s = Session(ex, cfg, embd, layers, output=head)
         prompt = (synth.words(7, 0, args.prompt) % np.uint64(VOCAB)).astype(np.int32)
@@ -780,7 +792,7 @@ def run_case(args):
         t1 = time.perf_counter()
         ids, _ = s.decode(args.gen)
         t2 = time.perf_counter()
-        out = {"case": "session", "layers": args.layers, "prefill_ms": (t1 - t0) * 1e3, "decode_ms_per_token": (t2 - t1) / args.gen * 1e3,
+        out = {"case": "session", "layers": args.layers, "experts": args.experts, "prefill_ms": (t1 - t0) * 1e3, "decode_ms_per_token": (t2 - t1) / args.gen * 1e3,
                "launches": ex.counters()["launches"]}
     print(json.dumps(out))
 
@@ -807,6 +819,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=64)
     ap.add_argument("--gen", type=int, default=4)
     ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--experts", type=int, default=0, help="--case session: routed experts per layer (0: dense FFN)")
     args = ap.parse_args()
     if args.case:
         return run_case(args)
