@@ -1708,7 +1708,9 @@ cudaError_t session_layers(llr_session* s, const int* ids_dev, size_t n, const R
       if ((ce = launch_attention(s->q, kv, s->attn, s->att_scratch, rows, 1, (int)li, s->shape, st, L, s->k, s->v)) != cudaSuccess) break;
     } else {
       if ((ce = launch_rope_store(s->q, s->k, s->v, kv, rows, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
-      if ((ce = launch_attention(s->q, kv, s->attn, s->att_scratch, rows, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
+      // the automatic path takes the tensor cores for chunks of 64 rows and more, as it does for the products
+      if ((ce = launch_attention(s->q, kv, s->attn, s->att_scratch, rows, (int)n, (int)li, s->shape, st, L, nullptr, nullptr,
+                                 e->path == PATH_AUTO && n >= TC_MIN_TOKENS)) != cudaSuccess) break;
     }
     if ((ce = session_matmul(e, W.attn_output, n, s->attn, s->proj)) != cudaSuccess) break;
     if ((ce = launch_rmsnorm(s->x, s->proj, s->ffn_norm[li], s->xn, (int)n, (int)E, c.rms_eps, st, L)) != cudaSuccess) break;

@@ -95,6 +95,42 @@ def test_prompt_chunks_and_single_tokens_give_the_same_bits(orc):
     ex.close()
 
 
+@pytest.mark.parametrize("n_head,n_head_kv,head_dim,n_ctx", [(4, 2, 64, 1024), (4, 1, 128, 2048), (8, 1, 64, 2048), (2, 2, 128, 512)])
+def test_prompt_attention_on_tensor_cores_agrees_with_the_f32_kernels(orc, n_head, n_head_kv, head_dim, n_ctx):
+    """Prompt chunks of 64 rows and more run their attention as 3xTF32 MMAs on the automatic path.  With F32 weights the
+    products are the same f32 kernels on both paths, so the logits of the automatic path and of the f32-faithful path
+    differ by the attention kernel alone: they must agree to rounding (1e-5 of the logit scale), for slices of 32 and of
+    64 positions, one to eight query heads per kv head, prompts that are not a multiple of the row tile, a second chunk
+    that starts in the middle of a slice, and against the CPU walk at the model-level tolerance."""
+    from llama_rust_b200 import Executor
+    from helpers import F32
+    cfg = dict(n_layer=2, n_embd=n_head * head_dim, n_head=n_head, n_head_kv=n_head_kv, head_dim=head_dim, n_ff=256, n_vocab=300)
+    rng = np.random.default_rng(n_head * 100 + head_dim + n_ctx)
+    tl = lw.tensor_list(cfg)
+    weights = [(rng.standard_normal(r * c) / np.sqrt(c)).astype(np.float32).view(np.uint8) for _, _, r, c in tl]
+    embd = rng.standard_normal(cfg["n_vocab"] * cfg["n_embd"]).astype(np.float32).view(np.uint8)
+    prompt = lw.prompt_ids(150, cfg["n_vocab"], 5)
+    more = lw.prompt_ids(77, cfg["n_vocab"], 6)
+    logits = {}
+    ex = Executor(0)
+    mats = [ex.upload(F32, r, c, w) for (_, _, r, c), w in zip(tl, weights)]
+    embd_mat = ex.upload(F32, cfg["n_vocab"], cfg["n_embd"], embd)
+    for path in (0, 3):
+        ex.set_path(path)
+        s = _session(ex, cfg, n_ctx, mats, embd_mat)
+        a = s.prefill(prompt, want_logits=True)
+        b = s.prefill(more, want_logits=True)  # positions 150..226: the chunk starts inside a slice
+        logits[path] = (a, b)
+        s.free()
+    cpu = lw.run_cpu(cfg, n_ctx, weights, embd, np.concatenate([prompt, more]), 0, want_logits=True, kinds=[F32] * len(tl), embd_kind=F32)[2]
+    for i in range(2):
+        scale = float(np.abs(logits[3][i]).max())
+        assert np.all(np.isfinite(logits[0][i]))
+        assert np.abs(logits[0][i] - logits[3][i]).max() <= 1e-5 * scale, (i, np.abs(logits[0][i] - logits[3][i]).max(), scale)
+    assert np.abs(logits[0][1] - cpu).max() <= 1e-4 * float(np.abs(cpu).max())
+    ex.close()
+
+
 def test_ragged_batch_over_several_sequences_equals_running_them_one_by_one(orc):
     """Engine-style batches (engine.rs:1215-1274): ragged groups of prompt chunks and single decode tokens of three
     sequences flattened into one activation matrix per step, against the same sequences run alone in a one-sequence
