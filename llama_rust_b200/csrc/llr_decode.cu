@@ -7,6 +7,7 @@
 // Arithmetic follows the reference's formulas; sums that the reference adds sequentially (sum of squares,
 // attention scores, softmax denominator, weighted values) are added in a fixed tree / block order here, so
 // results are reproducible from run to run and differ from the CPU walk in the last bits only.
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdlib>
@@ -495,153 +496,147 @@ attention_tile_kernel(const float* __restrict__ q, KvView kv, float* __restrict_
 }
 
 // ---- prompt chunks of one sequence on the tensor cores -----------------------------------------------------------
-// Same grid and same partial records as the tiled kernel above, for rows of ONE sequence at consecutive positions
-// (llr_session_prefill): a block holds a slice of CH = 8 NT positions of one kv head and ATT_ROWS rows; warp g takes
-// query head hkv * GQA + g.  Scores are Q K^T as m16n8k8 TF32 MMAs with both operands split into a TF32 head and a TF32
-// tail (x = hi + lo; hi*hi + lo*hi + hi*lo keeps ~21 significant bits, f32 accumulation), the exponentials go through
-// shared memory into the A operand of P V, split the same way.  Results agree with the f32 kernels to rounding, not
-// bit for bit: the automatic path uses this kernel from 64 rows on, the f32-faithful path never does.
-__device__ __forceinline__ uint32_t tf32_of(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return r;
+// Same partial records as the tiled kernel above, for rows of ONE sequence at consecutive positions
+// (llr_session_prefill).  A block holds 16 RT rows and one kv head and walks the slices blockIdx.y, blockIdx.y +
+// gridDim.y, ... of CH = 8 NT positions; a warp takes one query head of the group and sixteen of the rows.  Queries, keys, values and the
+// exponentials are rounded to binary16 when they are staged in shared memory (values transposed, so that two
+// consecutive positions of a dimension share a word); scores and weighted sums are m16n8k16 MMAs with f32
+// accumulation, maxima, exponentials and their sums are f32.  This is the attention of the 16-bit tensor-core path:
+// the automatic path uses it from 64 rows on, next to the 16-bit chunk GEMM and with the same kind of tolerance; the
+// f32-faithful path never does.
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *(const uint32_t*)&h;
 }
-__device__ __forceinline__ void tf32_split(float x, uint32_t& hi, uint32_t& lo) {
-  hi = tf32_of(x);
-  lo = tf32_of(x - __uint_as_float(hi));
-}
-__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// c += A B with A (16 x 8, row pointers pa0 = row g, pa1 = row g + 8, already offset by the k-step) and the B fragment values
-__device__ __forceinline__ void mma_3xtf32(float (&c)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4], float b0, float b1) {
-  uint32_t bh0, bl0, bh1, bl1;
-  tf32_split(b0, bh0, bl0);
-  tf32_split(b1, bh1, bl1);
-  mma_tf32(c, al, bh0, bh1);
-  mma_tf32(c, ah, bl0, bl1);
-  mma_tf32(c, ah, bh0, bh1);
-}
 
-template <int GQA, int HD, int NT>
-__global__ void __launch_bounds__(32 * GQA)
-attention_tile_mma_kernel(const float* __restrict__ q, KvView kv, float* __restrict__ part, RowMap rows, int layer, WalkShape w, int tokens) {
+template <int GQA, int HD, int NT, int RT>
+__global__ void __launch_bounds__(32 * GQA * RT)
+attention_tile_mma_kernel(const float* __restrict__ q, KvView kv, float* __restrict__ part, RowMap rows, int layer, WalkShape w, int tokens,
+                          int n_split) {
   pdl_enter();
-  constexpr int CH = 8 * NT, KS = HD + 4, VS = HD + 8, QS = HD + 4, PS = CH + 4;
-  extern __shared__ float sm[];  // k tile [CH][KS] | v tile [CH][VS] | per warp: q [16][QS], later the exponentials [16][PS]
-  float* kt = sm;
-  float* vt = kt + CH * KS;
+  // strides in 32-bit words (two binary16 each); + 4 words spreads the fragment reads of eight rows over all banks
+  constexpr int CH = 8 * NT, KW = HD / 2 + 4, VW = CH / 2 + 4, QW = HD / 2 + 4, PW = CH / 2 + 4, NW = GQA * RT, NTHR = 32 * NW;
+  extern __shared__ uint32_t smw[];  // k [CH][KW] | v transposed [HD][VW] | per warp: q [16][QW] | per warp: exponentials [16][PW]
+  uint32_t* kt = smw;
+  uint32_t* vt = kt + CH * KW;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-  float* qw = vt + CH * VS + warp * 16 * QS;
-  const int hkv = blockIdx.x, split = blockIdx.y, n_split = (int)gridDim.y, s0 = split * CH;
-  const int t_begin = blockIdx.z * ATT_ROWS, n_rows = min(tokens - t_begin, ATT_ROWS);
-  const int p0 = row_position(rows, t_begin);  // row r of the group stands at position p0 + r
-  const int need = min(p0 + n_rows, s0 + CH) - s0;  // positions of the slice any row of the group attends to
-  if (need <= 0) return;
-  const int sid = row_sequence(rows, t_begin);
+  uint32_t* qw = vt + HD * VW + warp * 16 * QW;
+  uint32_t* pw = vt + HD * VW + NW * 16 * QW + warp * 16 * PW;
+  const int hkv = blockIdx.x, head = warp % GQA;  // a warp: one query head of the group, sixteen of the block's 16 RT rows
+  const int b_begin = blockIdx.z * (16 * RT), b_rows = min(tokens - b_begin, 16 * RT);
+  const int last_pos = row_position(rows, b_begin) + b_rows - 1;  // of the block: the slices it walks
+  if ((int)blockIdx.y * CH > last_pos) return;
+  const int t_begin = b_begin + 16 * (warp / GQA), n_rows = max(0, min(tokens - t_begin, 16));
+  const int p0 = row_position(rows, b_begin) + 16 * (warp / GQA);  // row r of the warp stands at position p0 + r
+  const int sid = row_sequence(rows, b_begin);
   constexpr int vec = HD / 4;
-  for (int idx = threadIdx.x; idx < CH * vec; idx += 32 * GQA) {
-    const int p = idx / vec, c = idx % vec;
-    float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
-    if (p < need) {
-      const int64_t off = kv_offset(kv, sid, layer, hkv, s0 + p, w.n_head_kv, HD);
-      kk = ((const float4*)(kv.k + off))[c];
-      vv = ((const float4*)(kv.v + off))[c];
-    }
-    *(float4*)(kt + p * KS + 4 * c) = kk;
-    *(float4*)(vt + p * VS + 4 * c) = vv;
-  }
   for (int idx = lane; idx < 16 * vec; idx += 32) {  // this warp's head of the group's rows; rows past the end are zero
     const int r = idx / vec, c = idx % vec;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < n_rows) v = ((const float4*)(q + ((int64_t)(t_begin + r) * w.n_head + hkv * GQA + warp) * HD))[c];
-    *(float4*)(qw + r * QS + 4 * c) = v;
+    if (r < n_rows) v = ((const float4*)(q + ((int64_t)(t_begin + r) * w.n_head + hkv * GQA + head) * HD))[c];
+    *(uint2*)(qw + r * QW + 2 * c) = make_uint2(pack_h2(v.x, v.y), pack_h2(v.z, v.w));
   }
-  __syncthreads();
-  // ---- scores: rows g and g + 8 of the group against the slice's positions 8 nt + 2t, + 1
-  float sc[NT][4];
+  const float scale = 1.0f / sqrtf((float)HD);
+  for (int split = blockIdx.y; split * CH <= last_pos; split += (int)gridDim.y) {
+    const int s0 = split * CH;
+    // ---- stage the slice: positions no row of the group attends to are zero (their exponentials are zero as well)
+    for (int idx = threadIdx.x; idx < CH * vec; idx += NTHR) {
+      const int p = idx % CH, c = idx / CH;  // consecutive threads take consecutive positions: the transposed stores of v spread over the banks
+      float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+      if (s0 + p <= last_pos) {
+        const int64_t off = kv_offset(kv, sid, layer, hkv, s0 + p, w.n_head_kv, HD);
+        kk = ((const float4*)(kv.k + off))[c];
+        vv = ((const float4*)(kv.v + off))[c];
+      }
+      *(uint2*)(kt + p * KW + 2 * c) = make_uint2(pack_h2(kk.x, kk.y), pack_h2(kk.z, kk.w));
+      __half* vh = (__half*)vt;
+      vh[(4 * c + 0) * (2 * VW) + p] = __float2half_rn(vv.x);
+      vh[(4 * c + 1) * (2 * VW) + p] = __float2half_rn(vv.y);
+      vh[(4 * c + 2) * (2 * VW) + p] = __float2half_rn(vv.z);
+      vh[(4 * c + 3) * (2 * VW) + p] = __float2half_rn(vv.w);
+    }
+    __syncthreads();
+    if (p0 + n_rows - 1 >= s0) {  // warp-uniform: some row of this warp attends to the slice
+    // ---- scores: rows g and g + 8 of the group against the slice's positions 8 nt + 2t, + 1
+    float sc[NT][4];
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
-#pragma unroll 2
-  for (int k0 = 0; k0 < HD; k0 += 8) {
-    uint32_t ah[4], al[4];
-    tf32_split(qw[g * QS + k0 + t], ah[0], al[0]);
-    tf32_split(qw[(g + 8) * QS + k0 + t], ah[1], al[1]);
-    tf32_split(qw[g * QS + k0 + t + 4], ah[2], al[2]);
-    tf32_split(qw[(g + 8) * QS + k0 + t + 4], ah[3], al[3]);
+      for (int i = 0; i < 4; ++i) sc[nt][i] = 0.f;
+#pragma unroll
+    for (int k0 = 0; k0 < HD / 2; k0 += 8) {  // in words: 16 dimensions per step
+      const uint32_t a[4] = {qw[g * QW + k0 + t], qw[(g + 8) * QW + k0 + t], qw[g * QW + k0 + t + 4], qw[(g + 8) * QW + k0 + t + 4]};
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint32_t* kr = kt + (8 * nt + g) * KW + k0 + t;
+        mma_f16(sc[nt], a, kr[0], kr[4]);
+      }
+    }
+    // ---- scale, causal mask, maximum, exponentials (rounded to binary16, as the MMA below reads them) and their sum
+    const int lim0 = p0 + g - s0, lim1 = p0 + g + 8 - s0;  // last slice column rows g / g + 8 attend to
+    float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int col = 8 * nt + 2 * t + j;
+        sc[nt][j] = (g < n_rows && col <= lim0) ? __fmul_rn(sc[nt][j], scale) : -CUDART_INF_F;
+        sc[nt][2 + j] = (g + 8 < n_rows && col <= lim1) ? __fmul_rn(sc[nt][2 + j], scale) : -CUDART_INF_F;
+        m0 = fmaxf(m0, sc[nt][j]);
+        m1 = fmaxf(m1, sc[nt][2 + j]);
+      }
+    m0 = fmaxf(m0, __shfl_xor_sync(~0u, m0, 1)); m0 = fmaxf(m0, __shfl_xor_sync(~0u, m0, 2));
+    m1 = fmaxf(m1, __shfl_xor_sync(~0u, m1, 1)); m1 = fmaxf(m1, __shfl_xor_sync(~0u, m1, 2));
+    float l0 = 0.f, l1 = 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      const float* kr = kt + (8 * nt + g) * KS + k0 + t;
-      mma_3xtf32(sc[nt], ah, al, kr[0], kr[4]);
+      float e[4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        e[j] = sc[nt][j] == -CUDART_INF_F ? 0.f : expf(sc[nt][j] - m0);
+        e[2 + j] = sc[nt][2 + j] == -CUDART_INF_F ? 0.f : expf(sc[nt][2 + j] - m1);
+      }
+      const __half2 h0 = __floats2half2_rn(e[0], e[1]), h1 = __floats2half2_rn(e[2], e[3]);
+      l0 += __low2float(h0) + __high2float(h0);  // the sum of what the weighted sum below uses
+      l1 += __low2float(h1) + __high2float(h1);
+      pw[g * PW + 4 * nt + t] = *(const uint32_t*)&h0;
+      pw[(g + 8) * PW + 4 * nt + t] = *(const uint32_t*)&h1;
     }
-  }
-  // ---- scale, causal mask, maximum, exponentials and their sum per row
-  const float scale = 1.0f / sqrtf((float)HD);
-  const int lim0 = p0 + g - s0, lim1 = p0 + g + 8 - s0;  // last slice column rows g / g + 8 attend to
-  float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F;
+    l0 += __shfl_xor_sync(~0u, l0, 1); l0 += __shfl_xor_sync(~0u, l0, 2);
+    l1 += __shfl_xor_sync(~0u, l1, 1); l1 += __shfl_xor_sync(~0u, l1, 2);
+    __syncwarp();
+    // ---- weighted value rows: dimensions 8 nd + 2t, + 1 of rows g and g + 8
+    float o[HD / 8][4];
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
+    for (int nd = 0; nd < HD / 8; ++nd)
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int col = 8 * nt + 2 * t + j;
-      sc[nt][j] = (g < n_rows && col <= lim0) ? __fmul_rn(sc[nt][j], scale) : -CUDART_INF_F;
-      sc[nt][2 + j] = (g + 8 < n_rows && col <= lim1) ? __fmul_rn(sc[nt][2 + j], scale) : -CUDART_INF_F;
-      m0 = fmaxf(m0, sc[nt][j]);
-      m1 = fmaxf(m1, sc[nt][2 + j]);
+      for (int i = 0; i < 4; ++i) o[nd][i] = 0.f;
+#pragma unroll
+    for (int k0 = 0; k0 < CH / 2; k0 += 8) {  // in words: 16 positions per step
+      const uint32_t a[4] = {pw[g * PW + k0 + t], pw[(g + 8) * PW + k0 + t], pw[g * PW + k0 + t + 4], pw[(g + 8) * PW + k0 + t + 4]};
+#pragma unroll
+      for (int nd = 0; nd < HD / 8; ++nd) {
+        const uint32_t* vr = vt + (8 * nd + g) * VW + k0 + t;
+        mma_f16(o[nd], a, vr[0], vr[4]);
+      }
     }
-  m0 = fmaxf(m0, __shfl_xor_sync(~0u, m0, 1)); m0 = fmaxf(m0, __shfl_xor_sync(~0u, m0, 2));
-  m1 = fmaxf(m1, __shfl_xor_sync(~0u, m1, 1)); m1 = fmaxf(m1, __shfl_xor_sync(~0u, m1, 2));
-  float l0 = 0.f, l1 = 0.f;
-  __syncwarp();  // every lane has read its part of the query rows: the exponentials take their place
+    // ---- the slice's record of each row: HD sums, the maximum, the sum of exponentials (rows the slice lies beyond are not read)
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
+    for (int half = 0; half < 2; ++half) {
+      const int r = g + 8 * half;
+      if (r >= n_rows || p0 + r < s0) continue;
+      float* out = part + ((((int64_t)(t_begin + r) * w.n_head_kv + hkv) * n_split + split) * GQA + head) * (HD + 2);
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const float e0 = sc[nt][j] == -CUDART_INF_F ? 0.f : expf(sc[nt][j] - m0);
-      const float e1 = sc[nt][2 + j] == -CUDART_INF_F ? 0.f : expf(sc[nt][2 + j] - m1);
-      l0 += e0;
-      l1 += e1;
-      qw[g * PS + 8 * nt + 2 * t + j] = e0;
-      qw[(g + 8) * PS + 8 * nt + 2 * t + j] = e1;
+      for (int nd = 0; nd < HD / 8; ++nd) *(float2*)(out + 8 * nd + 2 * t) = make_float2(o[nd][2 * half], o[nd][2 * half + 1]);
+      if (t == 0) { out[HD] = half ? m1 : m0; out[HD + 1] = half ? l1 : l0; }
     }
-  l0 += __shfl_xor_sync(~0u, l0, 1); l0 += __shfl_xor_sync(~0u, l0, 2);
-  l1 += __shfl_xor_sync(~0u, l1, 1); l1 += __shfl_xor_sync(~0u, l1, 2);
-  __syncwarp();
-  // ---- weighted value rows: dimensions 8 nd + 2t, + 1 of rows g and g + 8
-  float o[HD / 8][4];
-#pragma unroll
-  for (int nd = 0; nd < HD / 8; ++nd)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) o[nd][i] = 0.f;
-#pragma unroll
-  for (int k0 = 0; k0 < CH; k0 += 8) {
-    uint32_t ah[4], al[4];
-    tf32_split(qw[g * PS + k0 + t], ah[0], al[0]);
-    tf32_split(qw[(g + 8) * PS + k0 + t], ah[1], al[1]);
-    tf32_split(qw[g * PS + k0 + t + 4], ah[2], al[2]);
-    tf32_split(qw[(g + 8) * PS + k0 + t + 4], ah[3], al[3]);
-#pragma unroll
-    for (int nd = 0; nd < HD / 8; ++nd) {
-      const float* vr = vt + (k0 + t) * VS + 8 * nd + g;
-      mma_3xtf32(o[nd], ah, al, vr[0], vr[4 * VS]);
     }
-  }
-  // ---- the slice's record of each row: HD sums, the maximum, the sum of exponentials (rows the slice lies beyond are not read)
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int r = g + 8 * half;
-    if (r >= n_rows || p0 + r < s0) continue;
-    float* out = part + ((((int64_t)(t_begin + r) * w.n_head_kv + hkv) * n_split + split) * GQA + warp) * (HD + 2);
-#pragma unroll
-    for (int nd = 0; nd < HD / 8; ++nd) {
-      out[8 * nd + 2 * t] = o[nd][2 * half];
-      out[8 * nd + 2 * t + 1] = o[nd][2 * half + 1];
-    }
-    if (t == 0) { out[HD] = half ? m1 : m0; out[HD + 1] = half ? l1 : l0; }
+    __syncthreads();  // every warp is done with the slice before the next one is staged
   }
 }
 
@@ -908,24 +903,27 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
   LLR_TILE(1, 1) LLR_TILE(2, 1) LLR_TILE(4, 1) LLR_TILE(1, 2) LLR_TILE(2, 2) LLR_TILE(4, 2) LLR_TILE(8, 2)
   LLR_TILE(1, 4) LLR_TILE(2, 4) LLR_TILE(4, 4) LLR_TILE(8, 4)
 #undef LLR_TILE
-  // a prompt chunk of one sequence at consecutive positions, when the caller allows 3xTF32 arithmetic: tensor cores
-  void (*mma)(const float*, KvView, float*, RowMap, int, WalkShape, int) = nullptr;
+  // a prompt chunk of one sequence at consecutive positions, when the caller allows 16-bit operands: tensor cores
+  void (*mma)(const float*, KvView, float*, RowMap, int, WalkShape, int, int) = nullptr;
   size_t mma_smem = 0;
+  int mma_rt = 1;
   if (tensor_cores && !rows.row_pos && !rows.row_seq && tokens >= 64 && (max_chunk == 32 || max_chunk == 64) &&
       (w.head_dim == 64 || w.head_dim == 128)) {
-#define LLR_MMA(G, H, N) if (gqa == G && w.head_dim == H && max_chunk == 8 * N) mma = attention_tile_mma_kernel<G, H, N>;
+#define LLR_MMA(G, H, N) if (gqa == G && w.head_dim == H && max_chunk == 8 * N) mma = attention_tile_mma_kernel<G, H, N, (G <= 4 ? 4 : 2)>;
     LLR_MMA(1, 64, 4) LLR_MMA(2, 64, 4) LLR_MMA(4, 64, 4) LLR_MMA(8, 64, 4) LLR_MMA(1, 64, 8) LLR_MMA(2, 64, 8) LLR_MMA(4, 64, 8) LLR_MMA(8, 64, 8)
     LLR_MMA(1, 128, 4) LLR_MMA(2, 128, 4) LLR_MMA(4, 128, 4) LLR_MMA(8, 128, 4) LLR_MMA(1, 128, 8) LLR_MMA(2, 128, 8) LLR_MMA(4, 128, 8) LLR_MMA(8, 128, 8)
 #undef LLR_MMA
-    mma_smem = ((size_t)max_chunk * (2 * w.head_dim + 12) + (size_t)gqa * 16 * (w.head_dim + 4)) * sizeof(float);
+    mma_rt = gqa <= 4 ? 4 : 2;  // sixteen-row tiles per block
+    mma_smem = ((size_t)max_chunk * (w.head_dim / 2 + 4) + (size_t)w.head_dim * (max_chunk / 2 + 4) +
+                (size_t)gqa * mma_rt * 16 * (w.head_dim / 2 + 4 + max_chunk / 2 + 4)) * sizeof(uint32_t);
   }
   if (mma && mma_smem <= 200 * 1024) {
     if (mma_smem > 48 * 1024) {
       e = cudaFuncSetAttribute((const void*)mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_smem);
       if (e != cudaSuccess) return e;
     }
-    e = launch_walk(mma, dim3(w.n_head_kv, splits, (tokens + ATT_ROWS - 1) / ATT_ROWS), dim3(32 * gqa), mma_smem, s, q, kv, scratch, rows,
-                    layer, w, tokens);
+    e = launch_walk(mma, dim3(w.n_head_kv, splits < 4 ? splits : 4, (tokens + 16 * mma_rt - 1) / (16 * mma_rt)), dim3(32 * gqa * mma_rt), mma_smem,
+                    s, q, kv, scratch, rows, layer, w, tokens, splits);
   } else if (tile && tokens >= 4 && max_chunk <= ATT_TILE_CHUNK && tile_smem <= 200 * 1024) {
     if (tile_smem > 48 * 1024) {
       e = cudaFuncSetAttribute((const void*)tile, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem);

@@ -97,11 +97,12 @@ def test_prompt_chunks_and_single_tokens_give_the_same_bits(orc):
 
 @pytest.mark.parametrize("n_head,n_head_kv,head_dim,n_ctx", [(4, 2, 64, 1024), (4, 1, 128, 2048), (8, 1, 64, 2048), (2, 2, 128, 512)])
 def test_prompt_attention_on_tensor_cores_agrees_with_the_f32_kernels(orc, n_head, n_head_kv, head_dim, n_ctx):
-    """Prompt chunks of 64 rows and more run their attention as 3xTF32 MMAs on the automatic path.  With F32 weights the
-    products are the same f32 kernels on both paths, so the logits of the automatic path and of the f32-faithful path
-    differ by the attention kernel alone: they must agree to rounding (1e-5 of the logit scale), for slices of 32 and of
-    64 positions, one to eight query heads per kv head, prompts that are not a multiple of the row tile, a second chunk
-    that starts in the middle of a slice, and against the CPU walk at the model-level tolerance."""
+    """Prompt chunks of 64 rows and more run their attention as binary16 MMAs with f32 accumulation on the automatic path.
+    With F32 weights the products are the same f32 kernels on both paths, so the logits of the automatic path and of the
+    f32-faithful path differ by the attention kernel alone: they must agree within the 16-bit tolerance (1e-3 of the
+    logit scale; a misplaced fragment would change them by the scale itself), for slices of 32 and of 64 positions, one
+    to eight query heads per kv head, prompts that are not a multiple of the row tile, a second chunk that starts in
+    the middle of a slice, and against the CPU walk."""
     from llama_rust_b200 import Executor
     from helpers import F32
     cfg = dict(n_layer=2, n_embd=n_head * head_dim, n_head=n_head, n_head_kv=n_head_kv, head_dim=head_dim, n_ff=256, n_vocab=300)
@@ -126,8 +127,10 @@ def test_prompt_attention_on_tensor_cores_agrees_with_the_f32_kernels(orc, n_hea
     for i in range(2):
         scale = float(np.abs(logits[3][i]).max())
         assert np.all(np.isfinite(logits[0][i]))
-        assert np.abs(logits[0][i] - logits[3][i]).max() <= 1e-5 * scale, (i, np.abs(logits[0][i] - logits[3][i]).max(), scale)
-    assert np.abs(logits[0][1] - cpu).max() <= 1e-4 * float(np.abs(cpu).max())
+        err = float(np.abs(logits[0][i] - logits[3][i]).max())
+        assert 0.0 < err <= 1e-3 * scale, (i, err, scale)  # not zero either: the automatic path took the other kernel
+    assert np.abs(logits[0][1] - cpu).max() <= 1e-3 * float(np.abs(cpu).max())
+    assert np.abs(logits[3][1] - cpu).max() <= 1e-4 * float(np.abs(cpu).max())
     ex.close()
 
 
