@@ -471,7 +471,10 @@ int llr_moe_ep_free(llr_moe_ep* ep);
  * Session::{prefill, decode} stand: the reference runs the element-wise steps on the host
  * between two executor calls (225 host round trips per token); here a generated token
  * never leaves the device, llr_session_decode enqueues all steps and synchronizes once.
- * Matrix products go through the executor's kernels (llr_exec_set_path applies).
+ * Matrix products go through the executor's kernels (llr_exec_set_path applies); on the
+ * automatic path a prompt chunk of 64 rows and more also runs its attention on the tensor
+ * cores with binary16 operands and f32 accumulation (the tolerance of the 16-bit chunk GEMM;
+ * llr_exec_set_path(exec, 3) keeps f32 arithmetic throughout).
  * Sums the reference adds sequentially (sum of squares, scores, softmax denominator) are
  * added in a fixed tree order: logits agree with the host walk to rounding, not bit for bit.
  * Norm weights are host f32 vectors of n_embd (NULL: all ones).  output == NULL: tied to
