@@ -542,6 +542,14 @@ attention_tile_mma_kernel(const float* __restrict__ q, KvView kv, float* __restr
     *(uint2*)(qw + r * QW + 2 * c) = make_uint2(pack_h2(v.x, v.y), pack_h2(v.z, v.w));
   }
   const float scale = 1.0f / sqrtf((float)HD);
+  // The slices a block walks are merged as they come (running maximum, rescaled sums): one record per row, head and
+  // blockIdx.y, at slice index blockIdx.y, instead of one per slice.
+  float run_m0 = -CUDART_INF_F, run_m1 = -CUDART_INF_F, run_l0 = 0.f, run_l1 = 0.f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int nd = 0; nd < HD / 8; ++nd)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[nd][i] = 0.f;
   for (int split = blockIdx.y; split * CH <= last_pos; split += (int)gridDim.y) {
     const int s0 = split * CH;
     // ---- stage the slice: positions no row of the group attends to are zero (their exponentials are zero as well)
@@ -592,6 +600,14 @@ attention_tile_mma_kernel(const float* __restrict__ q, KvView kv, float* __restr
       }
     m0 = fmaxf(m0, __shfl_xor_sync(~0u, m0, 1)); m0 = fmaxf(m0, __shfl_xor_sync(~0u, m0, 2));
     m1 = fmaxf(m1, __shfl_xor_sync(~0u, m1, 1)); m1 = fmaxf(m1, __shfl_xor_sync(~0u, m1, 2));
+    // what the earlier slices left is rescaled to the new maximum (a row that has attended to nothing yet keeps zeros)
+    m0 = fmaxf(m0, run_m0);
+    m1 = fmaxf(m1, run_m1);
+    const float a0 = run_m0 == -CUDART_INF_F ? 0.f : expf(run_m0 - m0), a1 = run_m1 == -CUDART_INF_F ? 0.f : expf(run_m1 - m1);
+    run_m0 = m0;
+    run_m1 = m1;
+#pragma unroll
+    for (int nd = 0; nd < HD / 8; ++nd) { o[nd][0] *= a0; o[nd][1] *= a0; o[nd][2] *= a1; o[nd][3] *= a1; }
     float l0 = 0.f, l1 = 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -609,13 +625,10 @@ attention_tile_mma_kernel(const float* __restrict__ q, KvView kv, float* __restr
     }
     l0 += __shfl_xor_sync(~0u, l0, 1); l0 += __shfl_xor_sync(~0u, l0, 2);
     l1 += __shfl_xor_sync(~0u, l1, 1); l1 += __shfl_xor_sync(~0u, l1, 2);
+    run_l0 = fmaf(run_l0, a0, l0);
+    run_l1 = fmaf(run_l1, a1, l1);
     __syncwarp();
-    // ---- weighted value rows: dimensions 8 nd + 2t, + 1 of rows g and g + 8
-    float o[HD / 8][4];
-#pragma unroll
-    for (int nd = 0; nd < HD / 8; ++nd)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) o[nd][i] = 0.f;
+    // ---- weighted value rows: dimensions 8 nd + 2t, + 1 of rows g and g + 8, added to the rescaled sums
 #pragma unroll
     for (int k0 = 0; k0 < CH / 2; k0 += 8) {  // in words: 16 positions per step
       const uint32_t a[4] = {pw[g * PW + k0 + t], pw[(g + 8) * PW + k0 + t], pw[g * PW + k0 + t + 4], pw[(g + 8) * PW + k0 + t + 4]};
@@ -625,18 +638,19 @@ attention_tile_mma_kernel(const float* __restrict__ q, KvView kv, float* __restr
         mma_f16(o[nd], a, vr[0], vr[4]);
       }
     }
-    // ---- the slice's record of each row: HD sums, the maximum, the sum of exponentials (rows the slice lies beyond are not read)
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int r = g + 8 * half;
-      if (r >= n_rows || p0 + r < s0) continue;
-      float* out = part + ((((int64_t)(t_begin + r) * w.n_head_kv + hkv) * n_split + split) * GQA + head) * (HD + 2);
-#pragma unroll
-      for (int nd = 0; nd < HD / 8; ++nd) *(float2*)(out + 8 * nd + 2 * t) = make_float2(o[nd][2 * half], o[nd][2 * half + 1]);
-      if (t == 0) { out[HD] = half ? m1 : m0; out[HD + 1] = half ? l1 : l0; }
-    }
     }
     __syncthreads();  // every warp is done with the slice before the next one is staged
+  }
+  // ---- one record per row: HD sums, the maximum, the sum of exponentials.  A row whose position lies before this
+  // block's first slice has none, and the merge does not look for one: it reads min(slices of the row, gridDim.y) records.
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = g + 8 * half;
+    if (r >= n_rows || p0 + r < (int)blockIdx.y * CH) continue;
+    float* out = part + ((((int64_t)(t_begin + r) * w.n_head_kv + hkv) * n_split + blockIdx.y) * GQA + head) * (HD + 2);
+#pragma unroll
+    for (int nd = 0; nd < HD / 8; ++nd) *(float2*)(out + 8 * nd + 2 * t) = make_float2(o[nd][2 * half], o[nd][2 * half + 1]);
+    if (t == 0) { out[HD] = half ? run_m1 : run_m0; out[HD + 1] = half ? run_l1 : run_l0; }
   }
 }
 
@@ -644,7 +658,8 @@ attention_tile_mma_kernel(const float* __restrict__ q, KvView kv, float* __restr
 // slice sp's maximum into the weight exp(m_slice - m); the denominator is the shuffle-tree sum of the weighted slice
 // sums; then every lane adds its dimensions over the slices in ascending order, the weights coming by shuffle.
 __global__ void __launch_bounds__(128)
-attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, RowMap rows, int chunk, WalkShape w, int heads_per_block) {
+attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, RowMap rows, int chunk, WalkShape w, int heads_per_block,
+                         int max_records) {
   pdl_enter();
   // heads_per_block 4: one warp per head (many rows: fewer, fuller blocks); 1: the four warps share a head's
   // dimensions (a decode step has few blocks to fill the device with)
@@ -655,7 +670,8 @@ attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out
   const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
   const int hkv = hq / gqa, g = hq % gqa;
   const int seq = row_position(rows, t) + 1;
-  const int n_split = (w.n_ctx + chunk - 1) / chunk, used = min(n_split, (seq + chunk - 1) / chunk);
+  // max_records: the tensor-core kernel leaves one record per walked run of slices, at the first indices
+  const int n_split = (w.n_ctx + chunk - 1) / chunk, used = min(min(n_split, (seq + chunk - 1) / chunk), max_records);
   const float* base = part + ((int64_t)t * w.n_head_kv + hkv) * n_split * gqa * (hd + 2) + g * (hd + 2);
   const int64_t stride = (int64_t)gqa * (hd + 2);
   const float ms = lane < used ? base[lane * stride + hd] : -CUDART_INF_F;
@@ -917,7 +933,9 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
     mma_smem = ((size_t)max_chunk * (w.head_dim / 2 + 4) + (size_t)w.head_dim * (max_chunk / 2 + 4) +
                 (size_t)gqa * mma_rt * 16 * (w.head_dim / 2 + 4 + max_chunk / 2 + 4)) * sizeof(uint32_t);
   }
+  int max_records = splits;
   if (mma && mma_smem <= 200 * 1024) {
+    max_records = splits < 4 ? splits : 4;
     if (mma_smem > 48 * 1024) {
       e = cudaFuncSetAttribute((const void*)mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_smem);
       if (e != cudaSuccess) return e;
@@ -937,7 +955,7 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
   }
   if (e != cudaSuccess) return e;
   return launch_walk(attention_combine_kernel, dim3(tokens >= 16 ? (w.n_head + 3) / 4 : w.n_head, tokens), dim3(128), 0, s, (const float*)scratch, out, rows,
-                     max_chunk, w, tokens >= 16 ? 4 : 1);
+                     max_chunk, w, tokens >= 16 ? 4 : 1, max_records);
 }
 
 cudaError_t launch_swiglu(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches) {
