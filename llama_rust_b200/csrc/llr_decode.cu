@@ -10,6 +10,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <math_constants.h>
 
@@ -659,7 +660,7 @@ attention_tile_mma_kernel(const float* __restrict__ q, KvView kv, float* __restr
 // sums; then every lane adds its dimensions over the slices in ascending order, the weights coming by shuffle.
 __global__ void __launch_bounds__(128)
 attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, RowMap rows, int chunk, WalkShape w, int heads_per_block,
-                         int max_records) {
+                         int max_records, int record_chunk) {
   pdl_enter();
   // heads_per_block 4: one warp per head (many rows: fewer, fuller blocks); 1: the four warps share a head's
   // dimensions (a decode step has few blocks to fill the device with)
@@ -670,8 +671,10 @@ attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out
   const int hd = w.head_dim, gqa = w.n_head / w.n_head_kv;
   const int hkv = hq / gqa, g = hq % gqa;
   const int seq = row_position(rows, t) + 1;
-  // max_records: the tensor-core kernel leaves one record per walked run of slices, at the first indices
-  const int n_split = (w.n_ctx + chunk - 1) / chunk, used = min(min(n_split, (seq + chunk - 1) / chunk), max_records);
+  // chunk: positions per slice of the f32 kernels, which fixes the room a row's records take.  The tensor-core kernel
+  // walks slices of record_chunk positions of its own and leaves one record per walked run of slices, at the first
+  // max_records indices.
+  const int n_split = (w.n_ctx + chunk - 1) / chunk, used = min(min(n_split, (seq + record_chunk - 1) / record_chunk), max_records);
   const float* base = part + ((int64_t)t * w.n_head_kv + hkv) * n_split * gqa * (hd + 2) + g * (hd + 2);
   const int64_t stride = (int64_t)gqa * (hd + 2);
   const float ms = lane < used ? base[lane * stride + hd] : -CUDART_INF_F;
@@ -923,24 +926,27 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
   void (*mma)(const float*, KvView, float*, RowMap, int, WalkShape, int, int) = nullptr;
   size_t mma_smem = 0;
   int mma_rt = 1;
-  if (tensor_cores && !rows.row_pos && !rows.row_seq && tokens >= 64 && (max_chunk == 32 || max_chunk == 64) &&
-      (w.head_dim == 64 || w.head_dim == 128)) {
-#define LLR_MMA(G, H, N) if (gqa == G && w.head_dim == H && max_chunk == 8 * N) mma = attention_tile_mma_kernel<G, H, N, (G <= 4 ? 4 : 2)>;
+  // its slices are its own (64 positions; 32 when the context is short): the records it leaves do not depend on max_chunk
+  const int mma_chunk = w.n_ctx > 1024 ? 64 : 32;
+  if (tensor_cores && !rows.row_pos && !rows.row_seq && tokens >= 64 && (w.head_dim == 64 || w.head_dim == 128)) {
+#define LLR_MMA(G, H, N) if (gqa == G && w.head_dim == H && mma_chunk == 8 * N) mma = attention_tile_mma_kernel<G, H, N, (G <= 4 ? 4 : 2)>;
     LLR_MMA(1, 64, 4) LLR_MMA(2, 64, 4) LLR_MMA(4, 64, 4) LLR_MMA(8, 64, 4) LLR_MMA(1, 64, 8) LLR_MMA(2, 64, 8) LLR_MMA(4, 64, 8) LLR_MMA(8, 64, 8)
     LLR_MMA(1, 128, 4) LLR_MMA(2, 128, 4) LLR_MMA(4, 128, 4) LLR_MMA(8, 128, 4) LLR_MMA(1, 128, 8) LLR_MMA(2, 128, 8) LLR_MMA(4, 128, 8) LLR_MMA(8, 128, 8)
 #undef LLR_MMA
     mma_rt = gqa <= 4 ? 4 : 2;  // sixteen-row tiles per block
-    mma_smem = ((size_t)max_chunk * (w.head_dim / 2 + 4) + (size_t)w.head_dim * (max_chunk / 2 + 4) +
-                (size_t)gqa * mma_rt * 16 * (w.head_dim / 2 + 4 + max_chunk / 2 + 4)) * sizeof(uint32_t);
+    mma_smem = ((size_t)mma_chunk * (w.head_dim / 2 + 4) + (size_t)w.head_dim * (mma_chunk / 2 + 4) +
+                (size_t)gqa * mma_rt * 16 * (w.head_dim / 2 + 4 + mma_chunk / 2 + 4)) * sizeof(uint32_t);
   }
-  int max_records = splits;
+  int max_records = splits, record_chunk = max_chunk;
   if (mma && mma_smem <= 200 * 1024) {
-    max_records = splits < 4 ? splits : 4;
+    const int mma_splits = (w.n_ctx + mma_chunk - 1) / mma_chunk;
+    max_records = std::min(std::min(mma_splits, splits), 4);
+    record_chunk = mma_chunk;
     if (mma_smem > 48 * 1024) {
       e = cudaFuncSetAttribute((const void*)mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_smem);
       if (e != cudaSuccess) return e;
     }
-    e = launch_walk(mma, dim3(w.n_head_kv, splits < 4 ? splits : 4, (tokens + 16 * mma_rt - 1) / (16 * mma_rt)), dim3(32 * gqa * mma_rt), mma_smem,
+    e = launch_walk(mma, dim3(w.n_head_kv, max_records, (tokens + 16 * mma_rt - 1) / (16 * mma_rt)), dim3(32 * gqa * mma_rt), mma_smem,
                     s, q, kv, scratch, rows, layer, w, tokens, splits);
   } else if (tile && tokens >= 4 && max_chunk <= ATT_TILE_CHUNK && tile_smem <= 200 * 1024) {
     if (tile_smem > 48 * 1024) {
@@ -955,7 +961,7 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
   }
   if (e != cudaSuccess) return e;
   return launch_walk(attention_combine_kernel, dim3(tokens >= 16 ? (w.n_head + 3) / 4 : w.n_head, tokens), dim3(128), 0, s, (const float*)scratch, out, rows,
-                     max_chunk, w, tokens >= 16 ? 4 : 1, max_records);
+                     max_chunk, w, tokens >= 16 ? 4 : 1, max_records, record_chunk);
 }
 
 cudaError_t launch_swiglu(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches) {

@@ -95,7 +95,8 @@ def test_prompt_chunks_and_single_tokens_give_the_same_bits(orc):
     ex.close()
 
 
-@pytest.mark.parametrize("n_head,n_head_kv,head_dim,n_ctx", [(4, 2, 64, 1024), (4, 1, 128, 2048), (8, 1, 64, 2048), (2, 2, 128, 512)])
+@pytest.mark.parametrize("n_head,n_head_kv,head_dim,n_ctx", [(4, 2, 64, 1024), (4, 1, 128, 2048), (8, 1, 64, 2048), (2, 2, 128, 512),
+                                                             (4, 2, 128, 4096)])  # 4096: the f32 kernels' slices are 128 positions long
 def test_prompt_attention_on_tensor_cores_agrees_with_the_f32_kernels(orc, n_head, n_head_kv, head_dim, n_ctx):
     """Prompt chunks of 64 rows and more run their attention as binary16 MMAs with f32 accumulation on the automatic path.
     With F32 weights the products are the same f32 kernels on both paths, so the logits of the automatic path and of the
