@@ -769,7 +769,7 @@ def run_case(args):
         peak, _ = load_peaks()
         out = {"case": "moe", **moe_leg(ex, None, 0, 1, peak, 1354.7, token_counts=(args.tokens,))}
     else:
-        cfg = dict(n_layer=args.layers, n_embd=D_MODEL, n_head=32, n_head_kv=8, head_dim=128, n_ff=D_FF, n_vocab=VOCAB, n_ctx=args.prompt + args.gen + 8)
+        cfg = dict(n_layer=args.layers, n_embd=D_MODEL, n_head=32, n_head_kv=8, head_dim=128, n_ff=D_FF, n_vocab=VOCAB, n_ctx=max(args.ctx, args.prompt + args.gen + 8))
         from llama_rust_b200 import Session
         embd = ex.synth(Q4_K, VOCAB, D_MODEL, 1)
         layers = [{t: ex.synth(dt, r, c, 10 * li + j) for j, (t, dt, r, c) in enumerate(LAYER)} for li in range(args.layers)]
@@ -819,6 +819,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=64)
     ap.add_argument("--gen", type=int, default=4)
     ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--ctx", type=int, default=0, help="--case session: context length of the session (default: prompt + gen + 8)")
     ap.add_argument("--experts", type=int, default=0, help="--case session: routed experts per layer (0: dense FFN)")
     args = ap.parse_args()
     if args.case:

@@ -162,7 +162,7 @@ rope_store_kernel(float* __restrict__ q, float* __restrict__ k, const float* __r
 constexpr int ATT_THREADS = 256;
 constexpr int ATT_MAX_GQA = 8;
 constexpr int ATT_ROWS = 16;       // rows per block of the tiled kernel
-constexpr int ATT_TILE_CHUNK = 64; // longest slice the tiled kernel stages (2 x 64 x head_dim floats)
+constexpr int ATT_TILE_CHUNK = 128; // longest slice the tiled kernel stages (2 x 128 x head_dim floats: contexts up to 4096 positions)
 
 struct KvGlobal {
   const KvView& kv;

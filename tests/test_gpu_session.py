@@ -65,26 +65,27 @@ def test_small_model_tokens_and_logits_match_the_cpu_walk(orc):
     ex.close()
 
 
-def test_prompt_chunks_and_single_tokens_give_the_same_bits(orc):
+@pytest.mark.parametrize("n_ctx", [128, 4096])  # slices of 32 positions; of 128, the longest the tiled kernel stages
+def test_prompt_chunks_and_single_tokens_give_the_same_bits(orc, n_ctx):
     """A prompt forwarded as one chunk (rows share each slice's keys and values through a shared-memory tile), in ragged
     pieces, and token by token (one row per block, straight from the paged cache) leaves the same logits, bit for bit:
     both attention kernels run one per-row routine.  Context of 100 positions: several slices per row."""
     from llama_rust_b200 import Executor
     cfg = dict(n_layer=2, n_embd=512, n_head=8, n_head_kv=2, head_dim=64, n_ff=1024, n_vocab=1000)
-    n_ctx = 128
     tl = lw.tensor_list(cfg)
     weights, embd = lw.centered_weights(cfg, 5)
     ex = Executor(0)
     ex.set_path(3)
     mats = [ex.upload(dt, rows, cols, w) for (name, dt, rows, cols), w in zip(tl, weights)]
     embd_mat = ex.upload(lw.Q4_K, cfg["n_vocab"], cfg["n_embd"], embd)
-    prompt = lw.prompt_ids(100, cfg["n_vocab"], 3)
-    s = _session(ex, cfg, n_ctx, mats, embd_mat, n_seq=1, kv_blocks=32, block_tokens=4)
+    n_prompt = 100 if n_ctx == 128 else 300  # 300: rows in the first, second and third slice of 128 positions
+    prompt = lw.prompt_ids(n_prompt, cfg["n_vocab"], 3)
+    s = _session(ex, cfg, n_ctx, mats, embd_mat, n_seq=1, kv_blocks=128, block_tokens=4)
     whole = s.prefill(prompt, want_logits=True)
     s.reset()
-    for piece in (prompt[:3], prompt[3:40], prompt[40:41], prompt[41:99]):
+    for piece in (prompt[:3], prompt[3:40], prompt[40:41], prompt[41:n_prompt - 1]):
         s.prefill(piece)
-    pieces = s.prefill(prompt[99:], want_logits=True)
+    pieces = s.prefill(prompt[n_prompt - 1:], want_logits=True)
     s.reset()
     for t in prompt[:-1]:
         s.prefill([t])
