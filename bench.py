@@ -772,7 +772,8 @@ def run_case(args):
         cfg = dict(n_layer=args.layers, n_embd=D_MODEL, n_head=32, n_head_kv=8, head_dim=128, n_ff=D_FF, n_vocab=VOCAB, n_ctx=max(args.ctx, args.prompt + args.gen + 8))
         from llama_rust_b200 import Session
         embd = ex.synth(Q4_K, VOCAB, D_MODEL, 1)
-        layers = [{t: ex.synth(dt, r, c, 10 * li + j) for j, (t, dt, r, c) in enumerate(LAYER)} for li in range(args.layers)]
+        one = DTYPES[args.dtype] if args.dtype != "Q4_K" else None  # --dtype D: every layer matrix in that format instead of the Q4_K / Q6_K mix
+        layers = [{t: ex.synth(one if one is not None else dt, r, c, 10 * li + j) for j, (t, dt, r, c) in enumerate(LAYER)} for li in range(args.layers)]
         if args.experts:  # config 5's experts in every layer (Mixtral-shaped: routed experts where the dense FFN stands)
             rng = np.random.default_rng(3)
             for li, L in enumerate(layers):

@@ -491,8 +491,10 @@ typedef struct llr_llama_layer {
    * experts, weights normalised with the 2^-14 clamp, no shared expert]: n_expert > 0 replaces the dense FFN of this
    * layer by the routed layer of llr_moe_ffn (ffn_gate / ffn_up / ffn_down are then not read and may be NULL).
    * ffn_gate_inp: n_expert x n_embd; the three arrays hold n_expert matrices each (n_ff x n_embd, n_ff x n_embd,
-   * n_embd x n_ff; cfg.n_ff is the experts' width).  The arrays are copied at session creation.  The per-expert row
-   * counts of every layer visit the host, so the steps of such a session are not replayed from a graph. */
+   * n_embd x n_ff; cfg.n_ff is the experts' width).  The arrays are copied at session creation.  For more than one row
+   * the per-expert row counts of every such layer visit the host (one synchronization per layer); a step of one token
+   * chooses its experts' products on the device (no host round trip, replayed from a graph like a dense step) when every
+   * expert matrix is in a block-quantized format the streaming decode kernel takes and at most 8 experts are used. */
   uint32_t n_expert, n_expert_used;
   const llr_matrix* ffn_gate_inp;
   const llr_matrix* const* ffn_gate_exps;

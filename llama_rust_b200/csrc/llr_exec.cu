@@ -1601,8 +1601,12 @@ struct llr_session {
     std::vector<const llr_matrix*> gate, up, down;
     llr_moe_layer layer{};
     MoeShape S;
+    char* maps = nullptr;  // device: tensor maps of the experts' gate | up | down matrices (n_expert each), for one-token steps
   };
   std::vector<std::unique_ptr<Moe>> moe;  // per layer, null: dense FFN
+  bool has_moe = false, moe_select = false;  // moe_select: every routed layer can choose its experts' products on the device
+  int* moe_sel = nullptr;     // one token's experts in ascending id (8 ints), then their router weights (8 floats)
+  float* moe_y = nullptr;     // the selected experts' down results (8 x n_embd)
   char* moe_tables = nullptr;             // routing tables for max_batch rows, one device block
   float *moe_logits = nullptr, *moe_wts = nullptr, *moe_w = nullptr;
   int *moe_ids = nullptr, *moe_tok_of_row = nullptr, *moe_rows_of_tok = nullptr, *moe_fill = nullptr, *moe_first_row = nullptr;
@@ -1624,6 +1628,9 @@ void session_release(llr_session* s) {
   for (int* p : ibufs) if (p) cudaFree(p);
   if (s->step_graph) cudaGraphExecDestroy(s->step_graph);
   if (s->moe_tables) cudaFree(s->moe_tables);
+  if (s->moe_sel) cudaFree(s->moe_sel);
+  if (s->moe_y) cudaFree(s->moe_y);
+  for (auto& M : s->moe) if (M && M->maps) cudaFree(M->maps);
   for (llr::Program* p : s->qkv_prog) program_destroy(p);
   for (llr::Program* p : s->gateup_prog) program_destroy(p);
   cudaGetLastError();
@@ -1665,6 +1672,29 @@ cudaError_t session_moe_ffn(llr_session* s, size_t li, size_t n) {
   llr_session::Moe& M = *s->moe[li];
   const MoeShape& S = M.S;
   cudaError_t ce;
+  if (n == 1 && s->moe_select && (e->path == PATH_AUTO || e->path == PATH_MMA)) {
+    // One token: its experts are chosen on the device and their products read the weights through the chosen expert's
+    // tensor map, so the step needs no row counts on the host (and can be replayed from a graph).  Same kernels and the
+    // same order of additions as below: the result has the same bits.
+    const size_t U = S.n_used, FF = S.n_ff, E = S.n_embd, NE = S.n_exp;
+    int* sel = s->moe_sel;
+    float* selw = (float*)(s->moe_sel + 8);
+    const MatView vg = view_of(M.gate[0]), vd = view_of(M.down[0]);
+    if ((ce = moe_route(e, &M.layer, S, 1, s->xn, s->moe_logits, s->moe_ids, s->moe_wts)) != cudaSuccess ||
+        (ce = launch_select_sorted(s->moe_ids, s->moe_wts, (int)U, sel, selw, e->stream, &e->ctr.launches)) != cudaSuccess)
+      return ce;
+    for (size_t j = 0; j < U; ++j)
+      if ((ce = launch_gemv_mma_select(vg, M.maps, sel + j, s->xn, s->gate + j * FF, e->stream, e->sm_count, e->err_flag, &e->ctr.launches)) != cudaSuccess ||
+          (ce = launch_gemv_mma_select(vg, M.maps + NE * GEMV_MAP_BYTES, sel + j, s->xn, s->up + j * FF, e->stream, e->sm_count, e->err_flag,
+                                       &e->ctr.launches)) != cudaSuccess)
+        return ce;
+    if ((ce = launch_silu_mul(s->gate, s->up, (int64_t)(U * FF), e->stream, &e->ctr.launches)) != cudaSuccess) return ce;
+    for (size_t j = 0; j < U; ++j)
+      if ((ce = launch_gemv_mma_select(vd, M.maps + 2 * NE * GEMV_MAP_BYTES, sel + j, s->gate + j * FF, s->moe_y + j * E, e->stream, e->sm_count,
+                                       e->err_flag, &e->ctr.launches)) != cudaSuccess)
+        return ce;
+    return launch_combine_one(s->moe_y, selw, s->proj, (int)U, (int)E, e->stream, &e->ctr.launches);
+  }
   if ((ce = moe_route(e, &M.layer, S, n, s->xn, s->moe_logits, s->moe_ids, s->moe_wts)) != cudaSuccess ||
       (ce = launch_bucket(s->moe_ids, s->moe_wts, s->moe_local, (int)n, (int)S.n_exp, (int)S.n_used, s->moe_first_row, s->moe_tok_of_row,
                           s->moe_rows_of_tok, s->moe_w, s->moe_fill, e->stream, &e->ctr.launches)) != cudaSuccess)
@@ -1824,7 +1854,7 @@ int session_create(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t k
     M->S.local.assign(W.n_expert, 1);
     s->moe[li] = std::move(M);
     s->layers[li].ffn_gate_exps = s->layers[li].ffn_up_exps = s->layers[li].ffn_down_exps = nullptr;  // the copies above are the ones used
-    s->use_graph = false;  // every routed layer synchronizes for its row counts
+    s->has_moe = true;
   }
   const float n_rot = (float)(uint16_t)c.head_dim;
   s->shape = WalkShape{(int)c.n_embd, (int)c.n_head, (int)c.n_head_kv, (int)c.head_dim, (int)c.n_ff, (int)c.n_ctx, c.rms_eps, c.rope_base,
@@ -1865,6 +1895,34 @@ int session_create(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t k
   if (ce == cudaSuccess) ce = cudaMemset(s->table_dev, 0, n_seq * s->max_blocks * sizeof(int));
   if (const char* g = std::getenv("LLR_SESSION_GRAPH")) s->use_graph = s->use_graph && std::strcmp(g, "0") != 0;
   if (max_expert > 0 && ce == cudaSuccess) {
+    // One-token steps choose their experts' products on the device when every expert matrix of every routed layer goes
+    // through the streaming decode kernel in one format per kind: tensor maps gate | up | down of all experts per layer.
+    s->moe_select = max_used <= 8 && B >= max_used;
+    for (uint32_t li = 0; li < c.n_layer && s->moe_select; ++li) {
+      if (!s->moe[li]) continue;
+      const llr_session::Moe& M = *s->moe[li];
+      for (size_t ex = 0; ex < M.S.n_exp && s->moe_select; ++ex)
+        s->moe_select = gemv_mma_supported(view_of(M.gate[ex])) && gemv_mma_supported(view_of(M.up[ex])) && gemv_mma_supported(view_of(M.down[ex])) &&
+                        M.gate[ex]->dtype == M.gate[0]->dtype && M.up[ex]->dtype == M.gate[0]->dtype && M.down[ex]->dtype == M.down[0]->dtype;
+    }
+    for (uint32_t li = 0; li < c.n_layer && s->moe_select && ce == cudaSuccess; ++li) {
+      if (!s->moe[li]) continue;
+      llr_session::Moe& M = *s->moe[li];
+      const size_t NE = M.S.n_exp;
+      std::vector<char> host(3 * NE * GEMV_MAP_BYTES);
+      for (size_t ex = 0; ex < NE && ce == cudaSuccess; ++ex) {
+        if ((ce = gemv_mma_encode_map(view_of(M.gate[ex]), host.data() + ex * GEMV_MAP_BYTES)) != cudaSuccess ||
+            (ce = gemv_mma_encode_map(view_of(M.up[ex]), host.data() + (NE + ex) * GEMV_MAP_BYTES)) != cudaSuccess ||
+            (ce = gemv_mma_encode_map(view_of(M.down[ex]), host.data() + (2 * NE + ex) * GEMV_MAP_BYTES)) != cudaSuccess)
+          break;
+      }
+      if (ce == cudaSuccess) ce = cudaMalloc((void**)&M.maps, host.size());
+      if (ce == cudaSuccess) ce = cudaMemcpy(M.maps, host.data(), host.size(), cudaMemcpyHostToDevice);
+    }
+    if (s->moe_select && ce == cudaSuccess) {
+      ce = cudaMalloc((void**)&s->moe_sel, 8 * sizeof(int) + 8 * sizeof(float));
+      if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->moe_y, 8 * E * sizeof(float));
+    }
     const size_t n_rows = B * max_used;
     auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
     size_t at = 0;
@@ -2037,7 +2095,9 @@ int llr_session_decode(llr_session* s, size_t n_gen, int32_t* out_ids, float* ou
     ce = launch_argmax_advance(s->logits, (int)s->cfg.n_vocab, s->ids, s->margins, nullptr, 0, s->count_dev, s->arg_part, e->stream, &e->ctr.launches);
   size_t done = 0;
   if (ce == cudaSuccess) { ce = session_forward(s, s->ids, 1, true, true); ++done; }  // also initialises per-kernel launch state before any capture
-  if (ce == cudaSuccess && s->use_graph && n_gen > 2 && (!s->step_graph || s->step_graph_path != e->path)) {
+  // a step with routed layers is the same sequence of launches only when its experts are chosen on the device
+  const bool graph_ok = s->use_graph && (!s->has_moe || (s->moe_select && (e->path == PATH_AUTO || e->path == PATH_MMA)));
+  if (ce == cudaSuccess && graph_ok && n_gen > 2 && (!s->step_graph || s->step_graph_path != e->path)) {
     if (s->step_graph) { cudaGraphExecDestroy(s->step_graph); s->step_graph = nullptr; }
     cudaGraph_t graph = nullptr;
     const uint64_t launches_before = e->ctr.launches;
@@ -2062,7 +2122,7 @@ int llr_session_decode(llr_session* s, size_t n_gen, int32_t* out_ids, float* ou
     }
   }
   for (; done < n_gen && ce == cudaSuccess; ++done) {
-    if (s->use_graph && s->step_graph && s->step_graph_path == e->path) {
+    if (graph_ok && s->use_graph && s->step_graph && s->step_graph_path == e->path) {
       ce = cudaGraphLaunch(s->step_graph, e->stream);
       e->ctr.launches += (uint64_t)s->step_kernels;
     } else {

@@ -649,6 +649,21 @@ gemv_stream_hostout_kernel(const __grid_constant__ ProgEntry one, const __grid_c
   stream_body<MT, false, DT, false, true>(wk, nullptr, 0ull, err);
 }
 
+// One product with one activation row whose matrix is chosen on the device: maps[*sel] of an array of tensor maps
+// of equally shaped matrices (the experts of a routed layer; the kernels address weights through the map alone).
+// *sel is written by an earlier kernel of the stream, so nothing is fetched before that kernel has finished.
+template <int DT>
+__global__ void __launch_bounds__(NTHREADS, 2)
+gemv_stream_select_kernel(const __grid_constant__ ProgEntry one, const CUtensorMap* __restrict__ maps, const int* __restrict__ sel,
+                          int* __restrict__ err) {
+  __shared__ ProgPhase phase;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x == 0) phase = ProgPhase{0, 1, one.n_tiles, 0};
+  __syncthreads();
+  Work wk{&one, &phase, 1, nullptr, HostOut{}, maps + *sel, 1, 0u, 0};
+  stream_body<1, false, DT>(wk, nullptr, 0ull, err);
+}
+
 // What changes from run to run of a program.
 struct RunArgs {
   unsigned long long epoch;     // runs of this program so far, this one included (what the counters count in)
@@ -787,6 +802,55 @@ static cudaError_t launch_passes(const MatView& m, const float* x, float* y, int
 cudaError_t launch_gemv_mma(const MatView& m, const float* x, float* y, int64_t tokens,
                             cudaStream_t stream, int sm_count, int* err, uint64_t* launches) {
   return launch_passes(m, x, y, tokens, stream, sm_count, err, launches, nullptr);
+}
+
+cudaError_t gemv_mma_encode_map(const MatView& m, void* map_out) {
+  static_assert(sizeof(CUtensorMap) == GEMV_MAP_BYTES, "tensor map size");
+  if (!gemv_mma_supported(m)) return cudaErrorInvalidValue;
+  return encode_weight_map(m.w, m.dtype, m.rows, m.cols, m.row_bytes, (CUtensorMap*)map_out) ? cudaSuccess : cudaErrorNotSupported;
+}
+
+template <int DT>
+static cudaError_t launch_select(const MatView& shape, const void* maps_dev, const int* sel_dev, const float* x, float* y,
+                                 cudaStream_t stream, int sm_count, int* err) {
+  constexpr int smem = SLay<1>::TOTAL;
+  static int bps = 0;
+  if (bps == 0) {
+    cudaError_t e = occupancy(gemv_stream_select_kernel<DT>, smem, &bps);
+    if (e != cudaSuccess) return e;
+  }
+  ProgEntry E{nullptr, x, y, shape.row_bytes, (int)shape.rows, (int)shape.cols, shape.dtype, 1, 0, (int)((shape.rows + 15) / 16), shape.rows};
+  int grid = sm_count * bps;
+  if (grid > E.n_tiles) grid = E.n_tiles;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(NTHREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemv_stream_select_kernel<DT>, E, (const CUtensorMap*)maps_dev, sel_dev, err);
+}
+
+cudaError_t launch_gemv_mma_select(const MatView& shape, const void* maps_dev, const int* sel_dev, const float* x, float* y,
+                                   cudaStream_t stream, int sm_count, int* err, uint64_t* launches) {
+  if (!gemv_mma_supported(shape)) return cudaErrorInvalidValue;
+  cudaError_t e;
+  switch (shape.dtype) {
+    case DT_Q4_K: e = launch_select<DT_Q4_K>(shape, maps_dev, sel_dev, x, y, stream, sm_count, err); break;
+    case DT_Q5_K: e = launch_select<DT_Q5_K>(shape, maps_dev, sel_dev, x, y, stream, sm_count, err); break;
+    case DT_Q6_K: e = launch_select<DT_Q6_K>(shape, maps_dev, sel_dev, x, y, stream, sm_count, err); break;
+    case DT_Q8_0: e = launch_select<DT_Q8_0>(shape, maps_dev, sel_dev, x, y, stream, sm_count, err); break;
+    case DT_Q4_0: e = launch_select<DT_Q4_0>(shape, maps_dev, sel_dev, x, y, stream, sm_count, err); break;
+    case DT_Q4_1: e = launch_select<DT_Q4_1>(shape, maps_dev, sel_dev, x, y, stream, sm_count, err); break;
+    case DT_Q5_0: e = launch_select<DT_Q5_0>(shape, maps_dev, sel_dev, x, y, stream, sm_count, err); break;
+    default: e = launch_select<DT_Q5_1>(shape, maps_dev, sel_dev, x, y, stream, sm_count, err); break;
+  }
+  if (e == cudaSuccess && launches) ++*launches;
+  return e;
 }
 
 bool gemv_mma_hostout_ok(const MatView& m, int64_t tokens) { return tokens >= 1 && tokens <= 8 && gemv_mma_supported(m); }

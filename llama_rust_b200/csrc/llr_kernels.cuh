@@ -68,6 +68,13 @@ struct HostOut {
   unsigned int* count;
   int ticket;
 };
+// One product with ONE activation row whose matrix a kernel earlier in the stream chooses: the weights are addressed
+// through maps_dev[*sel_dev], an array (device memory) of GEMV_MAP_BYTES-byte tensor maps that gemv_mma_encode_map filled
+// for matrices of one shape and format (`shape`: any of them).  No host round trip between the choice and the product.
+constexpr int GEMV_MAP_BYTES = 128;
+cudaError_t gemv_mma_encode_map(const MatView& m, void* map_out);
+cudaError_t launch_gemv_mma_select(const MatView& shape, const void* maps_dev, const int* sel_dev, const float* x, float* y,
+                                   cudaStream_t stream, int sm_count, int* err_flag, uint64_t* launches);
 bool gemv_mma_hostout_ok(const MatView& m, int64_t tokens);
 cudaError_t launch_gemv_mma_hostout(const MatView& m, const float* x, float* y, int64_t tokens, const HostOut& ho,
                                     cudaStream_t stream, int sm_count, int* err_flag, uint64_t* launches);
@@ -190,6 +197,9 @@ cudaError_t launch_bucket(const int* ids, const float* wts, const unsigned char*
                           uint64_t* launches);
 cudaError_t launch_scatter_combine(const float* y, const int* rows_of_tok, const float* w_of_tok, float* out,
                                    int tokens, int n_used, int n_embd, cudaStream_t s, uint64_t* launches);
+// One token without a host round trip: its selection sorted by expert id (n_used <= 8), and the combine of its experts' rows
+cudaError_t launch_select_sorted(const int* ids, const float* wts, int n_used, int* sel, float* selw, cudaStream_t s, uint64_t* launches);
+cudaError_t launch_combine_one(const float* y, const float* selw, float* out, int n_used, int n_embd, cudaStream_t s, uint64_t* launches);
 
 // Expert parallelism over peer stores (llr_moe_ep.cu).  An arena starts with an EpHeader, then twice (runs
 // alternate): counts [local expert][sender], packed row numbers and rows [local expert][sender][t_max], and the

@@ -157,7 +157,49 @@ bucket_kernel(const int* __restrict__ ids, const float* __restrict__ wts, const 
   if (threadIdx.x == 0) first_row[n_expert] = s_base;
 }
 
+// One token's selection in ascending expert id (the order scatter_expert_rows :10263 adds in), for the products whose
+// matrix is chosen on the device.  n_used <= 8; one thread.
+__global__ void select_sorted_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int n_used, int* __restrict__ sel,
+                                     float* __restrict__ selw) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x != 0) return;
+  int id[8];
+  float w[8];
+  for (int j = 0; j < n_used; ++j) { id[j] = ids[j]; w[j] = wts[j]; }
+  for (int a = 1; a < n_used; ++a)  // insertion sort: ids of one token are distinct
+    for (int b = a; b > 0 && id[b - 1] > id[b]; --b) {
+      const int ti = id[b]; id[b] = id[b - 1]; id[b - 1] = ti;
+      const float tw = w[b]; w[b] = w[b - 1]; w[b - 1] = tw;
+    }
+  for (int j = 0; j < n_used; ++j) { sel[j] = id[j]; selw[j] = w[j]; }
+}
+
+// out[c] = sum over the selected experts, in the order given, of y[j][c] * w[j]: product rounded, then added, from zero
+// (what scatter_combine_kernel does for a packed batch)
+__global__ void combine_one_kernel(const float* __restrict__ y, const float* __restrict__ selw, float* __restrict__ out, int n_used,
+                                   int n_embd) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < n_embd; c += gridDim.x * blockDim.x) {
+    float acc = 0.0f;
+    for (int j = 0; j < n_used; ++j) acc = __fadd_rn(acc, __fmul_rn(y[(int64_t)j * n_embd + c], selw[j]));
+    out[c] = acc;
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_select_sorted(const int* ids, const float* wts, int n_used, int* sel, float* selw, cudaStream_t s, uint64_t* launches) {
+  if (n_used < 1 || n_used > 8) return cudaErrorInvalidValue;
+  select_sorted_kernel<<<1, 32, 0, s>>>(ids, wts, n_used, sel, selw);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_one(const float* y, const float* selw, float* out, int n_used, int n_embd, cudaStream_t s, uint64_t* launches) {
+  combine_one_kernel<<<(n_embd + 255) / 256, 256, 0, s>>>(y, selw, out, n_used, n_embd);
+  if (launches) ++*launches;
+  return cudaGetLastError();
+}
 
 cudaError_t launch_route(float* logits, int tokens, int n_expert, int n_used, int norm_w, int* ids, float* wts,
                          cudaStream_t s, uint64_t* launches) {

@@ -169,4 +169,13 @@ def test_a_llama_file_with_routed_experts_loads_into_a_session(orc):
     want_ids, _ = ref.decode(6)
     assert np.all(np.isfinite(first))
     assert np.array_equal(first.view(np.uint32), want_first.view(np.uint32)) and np.array_equal(ids, want_ids)
+    # token by token a step chooses its experts' products on the device (no row counts on the host); the prompt as one
+    # chunk goes through the packed rows: the same bits either way
+    ref.reset()
+    for tok in prompt[:-1]:
+        ref.prefill([tok])
+    single = ref.prefill(prompt[-1:], want_logits=True)
+    assert np.array_equal(single.view(np.uint32), want_first.view(np.uint32))
+    ids_again, _ = ref.decode(6)
+    assert np.array_equal(ids_again, want_ids)
     s.free(); ref.free(); ex.close(); g.close()
