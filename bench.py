@@ -242,7 +242,7 @@ def session_leg(ex, mats, specs_all):
 
 def config_legs(ex, stream, peak_hbm, peaks):
     """Driver-visible numbers for BASELINE configs 1, 4 and 5 on one GPU (device time, CUDA events):
-    config 1 the single Q8_0 product, config 4 the chunk GEMM (tensor-core path, 16-bit operands) for
+    config 1 the single Q8_0 product, every format's decode kernel on one large matrix, config 4 the chunk GEMM (tensor-core path, 16-bit operands) for
     four formats at three batch sizes, config 5 the routed-expert layer at 64 and 512 tokens."""
     import torch
     from llama_rust_b200 import DTYPES
@@ -267,6 +267,27 @@ def config_legs(ex, stream, peak_hbm, peaks):
                                        "algorithmic_bytes": nbytes, "launch": "one PDL launch per product, 8 distinct matrices"}
     for m in mats:
         m.free()
+    # every format's decode kernel on one large matrix (65536 x 4096, one activation row, 4 distinct matrices round-robin:
+    # 0.6-4.3 GB, far beyond L2): what a format's kernel sustains when the launch is long enough to stream
+    from llama_rust_b200 import row_bytes as lib_row_bytes
+    fm = {}
+    for name in ("Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "F16", "BF16", "F32"):
+        dt, rows, cols = DTYPES[name], 65536, 4096
+        mats = [ex.synth(dt, rows, cols, 700 + i) for i in range(4)]
+        x = torch.randn(cols, device="cuda")
+        y = torch.empty(rows, device="cuda")
+        it = [0]
+
+        def one():
+            ex.matmul_device(mats[it[0] % 4], 1, x.data_ptr(), y.data_ptr(), sptr)
+            it[0] += 1
+        timed(stream, one, 4)
+        ms = timed(stream, one, 24)
+        nbytes = rows * lib_row_bytes(dt, cols) + 4 * (rows + cols)
+        fm[name] = {"us_per_product": ms * 1e3, "GB_per_s": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peak_hbm}
+        for m in mats:
+            m.free()
+    out["decode_formats_65536x4096_m1"] = fm
     # config 4
     burst, sustained = peaks.get("bf16_tflops", 1619.1), peaks.get("bf16_tflops_sustained", 1354.7)
     c4 = {}
