@@ -897,7 +897,7 @@ size_t attention_scratch_floats(int tokens, const WalkShape& w) {
 
 cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float* scratch, const RowMap& rows, int tokens,
                              int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches, const float* k_new, const float* v_new,
-                             bool tensor_cores) {
+                             bool tensor_cores, bool one_sequence) {
   if (tokens <= 0) return cudaSuccess;
   const int gqa = w.n_head / w.n_head_kv;
   if (gqa < 1 || gqa > ATT_MAX_GQA || w.n_head % w.n_head_kv != 0 || w.head_dim > ATT_THREADS) return cudaErrorInvalidValue;
@@ -928,7 +928,7 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
   int mma_rt = 1;
   // its slices are its own (64 positions; 32 when the context is short): the records it leaves do not depend on max_chunk
   const int mma_chunk = w.n_ctx > 1024 ? 64 : 32;
-  if (tensor_cores && !rows.row_pos && !rows.row_seq && tokens >= 64 && (w.head_dim == 64 || w.head_dim == 128)) {
+  if (tensor_cores && (one_sequence || (!rows.row_pos && !rows.row_seq)) && tokens >= 64 && (w.head_dim == 64 || w.head_dim == 128)) {
 #define LLR_MMA(G, H, N) if (gqa == G && w.head_dim == H && mma_chunk == 8 * N) mma = attention_tile_mma_kernel<G, H, N, (G <= 4 ? 4 : 2)>;
     LLR_MMA(1, 64, 4) LLR_MMA(2, 64, 4) LLR_MMA(4, 64, 4) LLR_MMA(8, 64, 4) LLR_MMA(1, 64, 8) LLR_MMA(2, 64, 8) LLR_MMA(4, 64, 8) LLR_MMA(8, 64, 8)
     LLR_MMA(1, 128, 4) LLR_MMA(2, 128, 4) LLR_MMA(4, 128, 4) LLR_MMA(8, 128, 4) LLR_MMA(1, 128, 8) LLR_MMA(2, 128, 8) LLR_MMA(4, 128, 8) LLR_MMA(8, 128, 8)

@@ -1604,6 +1604,7 @@ struct llr_session {
     char* maps = nullptr;  // device: tensor maps of the experts' gate | up | down matrices (n_expert each), for one-token steps
   };
   std::vector<std::unique_ptr<Moe>> moe;  // per layer, null: dense FFN
+  std::vector<std::pair<size_t, size_t>> batch_groups;  // llr_session_batch: (first row, rows) of each group of the batch in flight
   bool has_moe = false, moe_select = false;  // moe_select: every routed layer can choose its experts' products on the device
   int* moe_sel = nullptr;     // one token's experts in ascending id (8 ints), then their router weights (8 floats)
   float* moe_y = nullptr;     // the selected experts' down results (8 x n_embd)
@@ -1738,9 +1739,32 @@ cudaError_t session_layers(llr_session* s, const int* ids_dev, size_t n, const R
       if ((ce = launch_attention(s->q, kv, s->attn, s->att_scratch, rows, 1, (int)li, s->shape, st, L, s->k, s->v)) != cudaSuccess) break;
     } else {
       if ((ce = launch_rope_store(s->q, s->k, s->v, kv, rows, (int)n, (int)li, s->shape, st, L)) != cudaSuccess) break;
-      // the automatic path takes the tensor cores for chunks of 64 rows and more, as it does for the products
-      if ((ce = launch_attention(s->q, kv, s->attn, s->att_scratch, rows, (int)n, (int)li, s->shape, st, L, nullptr, nullptr,
-                                 e->path == PATH_AUTO && n >= TC_MIN_TOKENS)) != cudaSuccess) break;
+      // the automatic path takes the tensor cores for chunks of 64 rows and more of one sequence, as it does for the products
+      const bool tc = e->path == PATH_AUTO && n >= TC_MIN_TOKENS;
+      bool big_group = false;
+      if (tc && rows.row_seq)
+        for (const auto& gr : s->batch_groups) big_group = big_group || gr.second >= (size_t)TC_MIN_TOKENS;
+      if (big_group) {
+        // a ragged batch: every group of 64 rows and more on its own (tensor cores), the runs of smaller groups between them together
+        const size_t q_row = (size_t)c.n_head * c.head_dim, rec_row = attention_scratch_floats(1, s->shape);
+        auto part = [&](size_t t0, size_t len, bool one) {
+          return launch_attention(s->q + t0 * q_row, kv, s->attn + t0 * q_row, s->att_scratch + t0 * rec_row,
+                                  RowMap{nullptr, rows.row_pos + t0, rows.row_seq + t0}, (int)len, (int)li, s->shape, st, L, nullptr, nullptr, one, one);
+        };
+        size_t run0 = 0, at = 0;
+        for (const auto& gr : s->batch_groups) {
+          if (gr.second >= (size_t)TC_MIN_TOKENS) {
+            if (at > run0 && (ce = part(run0, at - run0, false)) != cudaSuccess) break;
+            if ((ce = part(gr.first, gr.second, true)) != cudaSuccess) break;
+            run0 = gr.first + gr.second;
+          }
+          at = gr.first + gr.second;
+        }
+        if (ce == cudaSuccess && at > run0) ce = part(run0, at - run0, false);
+        if (ce != cudaSuccess) break;
+      } else if ((ce = launch_attention(s->q, kv, s->attn, s->att_scratch, rows, (int)n, (int)li, s->shape, st, L, nullptr, nullptr, tc)) != cudaSuccess) {
+        break;
+      }
     }
     if ((ce = session_matmul(e, W.attn_output, n, s->attn, s->proj)) != cudaSuccess) break;
     if ((ce = launch_rmsnorm(s->x, s->proj, s->ffn_norm[li], s->xn, (int)n, (int)E, c.rms_eps, st, L)) != cudaSuccess) break;
@@ -2186,9 +2210,11 @@ int llr_session_batch(llr_session* s, size_t n_groups, const uint32_t* seq_ids, 
   std::sort(order.begin(), order.end(), [&](size_t a, size_t b) { return seq_ids[a] < seq_ids[b]; });
   std::vector<int> ids(total), rpos(total), rseq(total), last(n_groups);
   size_t r = 0;
+  s->batch_groups.clear();
   for (size_t oi = 0; oi < n_groups; ++oi) {
     const size_t g = order[oi], q = seq_ids[g];
     if ((rc = session_reserve(s, q, s->position[q] + counts[g]))) return rc;
+    s->batch_groups.emplace_back(r, (size_t)counts[g]);
     for (size_t i = 0; i < counts[g]; ++i, ++r) {
       ids[r] = tokens[first[g] + i];
       rpos[r] = (int)(s->position[q] + i);

@@ -267,7 +267,8 @@ size_t attention_scratch_floats(int tokens, const WalkShape& w);
 cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float* scratch, const RowMap& rows, int tokens,
                              int layer, const WalkShape& w, cudaStream_t s, uint64_t* launches,
                              const float* k_new = nullptr, const float* v_new = nullptr,  // k_new / v_new: one decode token whose rotation and cache store the attention kernel does itself
-                             bool tensor_cores = false);  // a prompt chunk of one sequence may run as binary16 MMAs with f32 accumulation (the tolerance of the 16-bit chunk GEMM)
+                             bool tensor_cores = false,  // a prompt chunk of one sequence may run as binary16 MMAs with f32 accumulation (the tolerance of the 16-bit chunk GEMM)
+                             bool one_sequence = false);  // the caller vouches that the rows are one sequence at consecutive positions (rows given per row)
 cudaError_t launch_swiglu(float* g, const float* u, int64_t n, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_add(float* x, const float* y, int64_t n, cudaStream_t s, uint64_t* launches);
 // first index of the strict maximum of logits[0..n) -> *out_id (device; n == 0: no argmax), and *pos_dev += advance

@@ -197,6 +197,43 @@ def test_ragged_batch_over_several_sequences_equals_running_them_one_by_one(orc)
     ex.close()
 
 
+def test_ragged_batch_with_long_groups_takes_the_tensor_cores_per_group(orc):
+    """On the automatic path every group of 64 rows and more of a ragged batch runs its attention on the tensor cores (one
+    sequence at consecutive positions), the runs of shorter groups between them keep the f32 kernels.  F32 weights: the
+    products are the same on both paths, so short groups must give the bits of the f32-faithful path and long groups
+    must agree with it within the 16-bit tolerance (and differ from it: the other kernel did run)."""
+    from llama_rust_b200 import Executor
+    from helpers import F32
+    cfg = dict(n_layer=2, n_embd=256, n_head=4, n_head_kv=2, head_dim=64, n_ff=256, n_vocab=300)
+    rng = np.random.default_rng(71)
+    tl = lw.tensor_list(cfg)
+    weights = [(rng.standard_normal(r * c) / np.sqrt(c)).astype(np.float32).view(np.uint8) for _, _, r, c in tl]
+    embd = rng.standard_normal(cfg["n_vocab"] * cfg["n_embd"]).astype(np.float32).view(np.uint8)
+    ex = Executor(0)
+    mats = [ex.upload(F32, r, c, w) for (_, _, r, c), w in zip(tl, weights)]
+    embd_mat = ex.upload(F32, cfg["n_vocab"], cfg["n_embd"], embd)
+    groups1 = [(0, lw.prompt_ids(3, 300, 1)), (1, lw.prompt_ids(100, 300, 2)), (2, lw.prompt_ids(5, 300, 3)), (3, lw.prompt_ids(1, 300, 4)),
+               (4, lw.prompt_ids(70, 300, 5))]
+    groups2 = [(1, lw.prompt_ids(90, 300, 6)), (0, lw.prompt_ids(2, 300, 7)), (4, lw.prompt_ids(64, 300, 8))]  # long groups start mid-slice
+    got = {}
+    for path in (0, 3):
+        ex.set_path(path)
+        s = _session(ex, cfg, 1024, mats, embd_mat, n_seq=5, kv_blocks=0, block_tokens=16)
+        _, lg1 = s.batch(groups1, want_logits=True)
+        _, lg2 = s.batch(groups2, want_logits=True)
+        got[path] = (lg1, lg2)
+        s.free()
+    for step, long_groups in ((0, (1, 4)), (1, (0, 2))):
+        for gi in range(len(got[0][step])):
+            a, b = got[0][step][gi], got[3][step][gi]
+            if gi in long_groups:
+                err = float(np.abs(a - b).max())
+                assert 0.0 < err <= 1e-3 * float(np.abs(b).max()), (step, gi, err)
+            else:
+                assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), (step, gi)
+    ex.close()
+
+
 def test_session_validates_its_model_and_calls():
     from llama_rust_b200 import Executor, NativeCudaError, Session
     cfg = dict(n_layer=1, n_embd=256, n_head=4, n_head_kv=2, head_dim=64, n_ff=512, n_vocab=300)
