@@ -458,7 +458,9 @@ attention_tile_kernel(const float* __restrict__ q, KvView kv, float* __restrict_
   float* vt = kt + chunk * hd;
   float* sq = vt + chunk * hd + warp * gqa * hd;
   float* sc = vt + chunk * hd + nw * gqa * hd + warp * gqa * chunk;
-  const int t_begin = blockIdx.z * ATT_ROWS, t_end = min(tokens, t_begin + ATT_ROWS);
+  // the last rows first: in a prompt chunk they attend to the most slices, the blocks of the first rows (which leave at once for
+  // the slices beyond them) then fill the tail
+  const int t_begin = ((int)gridDim.z - 1 - (int)blockIdx.z) * ATT_ROWS, t_end = min(tokens, t_begin + ATT_ROWS);
   // sequence and position of the group's rows, fetched in one go (the runs below are found in shared memory)
   __shared__ int s_seq[ATT_ROWS], s_pos[ATT_ROWS];
   if (threadIdx.x < ATT_ROWS && t_begin + (int)threadIdx.x < t_end) {
@@ -529,7 +531,8 @@ attention_tile_mma_kernel(const float* __restrict__ q, KvView kv, float* __restr
   uint32_t* qw = vt + HD * VW + warp * 16 * QW;
   uint32_t* pw = vt + HD * VW + NW * 16 * QW + warp * 16 * PW;
   const int hkv = blockIdx.x, head = warp % GQA;  // a warp: one query head of the group, sixteen of the block's 16 RT rows
-  const int b_begin = blockIdx.z * (16 * RT), b_rows = min(tokens - b_begin, 16 * RT);
+  // the last rows first: they attend to the most positions, and the short blocks of the first rows then fill the tail
+  const int b_begin = ((int)gridDim.z - 1 - (int)blockIdx.z) * (16 * RT), b_rows = min(tokens - b_begin, 16 * RT);
   const int last_pos = row_position(rows, b_begin) + b_rows - 1;  // of the block: the slices it walks
   if ((int)blockIdx.y * CH > last_pos) return;
   const int t_begin = b_begin + 16 * (warp / GQA), n_rows = max(0, min(tokens - t_begin, 16));
