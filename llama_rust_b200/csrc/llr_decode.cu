@@ -120,34 +120,42 @@ rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ add, const float
   }
 }
 
-// grid (token, head of q and k together): one thread per rotated pair; then the k and v rows go to the cache
-__global__ void __launch_bounds__(128)
+// One block per token: the cosine and sine of every pair's angle once (all heads of a token turn by the same
+// angles), then the rotation of every q and k head, then the k and v rows into the cache.
+__global__ void __launch_bounds__(256)
 rope_store_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v, KvView kv, RowMap rows, int layer,
                   WalkShape w) {
   pdl_enter();
-  const int t = blockIdx.x, h = blockIdx.y;  // h < n_head: a q head, else a k head
+  __shared__ float s_cos[128], s_sin[128];  // head_dim <= 256
+  const int t = blockIdx.x;
   const int pos = row_position(rows, t);
-  const int hd = w.head_dim;
-  const bool is_q = h < w.n_head;
-  const int hk = h - w.n_head;
-  float* vec = is_q ? q + ((int64_t)t * w.n_head + h) * hd : k + ((int64_t)t * w.n_head_kv + hk) * hd;
+  const int hd = w.head_dim, half = hd / 2;
   const float theta_scale = w.theta_scale;  // base^(-2/n_rot), computed once on the host in f32 as the reference does
-  for (int p = threadIdx.x; 2 * p + 1 < hd; p += blockDim.x) {
+  for (int p = threadIdx.x; p < half; p += blockDim.x) {
     float theta = (float)(pos <= 65535 ? pos : 65535);
     for (int i = 0; i < p; ++i) theta *= theta_scale;  // the reference advances theta multiplicatively in f32
-    const float c = cosf(theta), s = sinf(theta);
-    const float a = vec[2 * p], b = vec[2 * p + 1];
-    vec[2 * p] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
-    vec[2 * p + 1] = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+    s_cos[p] = cosf(theta);
+    s_sin[p] = sinf(theta);
   }
-  if (is_q) return;
   __syncthreads();
+  float* qrow = q + (int64_t)t * w.n_head * hd;
+  float* krow = k + (int64_t)t * w.n_head_kv * hd;
+  for (int idx = threadIdx.x; idx < (w.n_head + w.n_head_kv) * half; idx += blockDim.x) {
+    const int h = idx / half, p = idx % half;
+    float* vec = h < w.n_head ? qrow + h * hd : krow + (h - w.n_head) * hd;
+    const float c = s_cos[p], s = s_sin[p];
+    const float2 ab = *(const float2*)(vec + 2 * p);
+    *(float2*)(vec + 2 * p) = make_float2(__fsub_rn(__fmul_rn(ab.x, c), __fmul_rn(ab.y, s)), __fadd_rn(__fmul_rn(ab.x, s), __fmul_rn(ab.y, c)));
+  }
+  __syncthreads();  // the rotated keys are read back below by other threads of the block
   // store_kv (decode.rs:12059) into the row's sequence, paged
-  const int64_t off = kv_offset(kv, row_sequence(rows, t), layer, hk, pos, w.n_head_kv, hd);
-  const float* vv = v + ((int64_t)t * w.n_head_kv + hk) * hd;
-  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-    kv.k[off + i] = vec[i];
-    kv.v[off + i] = vv[i];
+  const int sid = row_sequence(rows, t);
+  const float* vrow = v + (int64_t)t * w.n_head_kv * hd;
+  for (int idx = threadIdx.x; idx < w.n_head_kv * hd; idx += blockDim.x) {
+    const int hk = idx / hd, i = idx % hd;
+    const int64_t off = kv_offset(kv, sid, layer, hk, pos, w.n_head_kv, hd);
+    kv.k[off + i] = krow[idx];
+    kv.v[off + i] = vrow[idx];
   }
 }
 
@@ -891,7 +899,7 @@ cudaError_t launch_rope_store(float* q, float* k, const float* v, const KvView& 
                               const WalkShape& w, cudaStream_t s, uint64_t* launches) {
   if (tokens <= 0) return cudaSuccess;
   if (launches) ++*launches;
-  return launch_walk(rope_store_kernel, dim3(tokens, w.n_head + w.n_head_kv), dim3(128), 0, s, q, k, v, kv, rows, layer, w);
+  return launch_walk(rope_store_kernel, dim3(tokens), dim3(256), 0, s, q, k, v, kv, rows, layer, w);
 }
 
 size_t attention_scratch_floats(int tokens, const WalkShape& w) {
