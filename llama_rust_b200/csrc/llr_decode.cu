@@ -716,11 +716,17 @@ attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out
     if (d0 + dstep * k < hd) out[((int64_t)t * w.n_head + hq) * hd + d0 + dstep * k] = l > 0.f ? __fdiv_rn(acc[k], l) : 0.f;
 }
 
+__device__ __forceinline__ float swiglu_of(float a, float b) { return __fmul_rn(__fdiv_rn(a, 1.0f + expf(-a)), b); }  // silu(gate) * up (decode.rs:11826, :2984)
 __global__ void swiglu_kernel(float* __restrict__ g, const float* __restrict__ u, int64_t n) {
   pdl_enter();
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    const float a = g[i];
-    g[i] = __fmul_rn(__fdiv_rn(a, 1.0f + expf(-a)), u[i]);  // silu(gate) * up (decode.rs:11826, :2984)
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) g[i] = swiglu_of(g[i], u[i]);
+}
+// the same, four elements per thread and step (n4 = n / 4; g and u 16-byte aligned)
+__global__ void swiglu4_kernel(float4* __restrict__ g, const float4* __restrict__ u, int64_t n4) {
+  pdl_enter();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    const float4 a = g[i], b = u[i];
+    g[i] = make_float4(swiglu_of(a.x, b.x), swiglu_of(a.y, b.y), swiglu_of(a.z, b.z), swiglu_of(a.w, b.w));
   }
 }
 __global__ void add_kernel(float* __restrict__ x, const float* __restrict__ y, int64_t n) {
@@ -980,6 +986,11 @@ cudaError_t launch_swiglu(float* g, const float* u, int64_t n, cudaStream_t s, u
   int64_t blocks = (n + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (launches) ++*launches;
+  if (n % 4 == 0 && (((uintptr_t)g | (uintptr_t)u) & 15) == 0) {
+    int64_t b4 = (n / 4 + 255) / 256;
+    if (b4 > 148 * 8) b4 = 148 * 8;
+    return launch_walk(swiglu4_kernel, dim3((unsigned)b4), dim3(256), 0, s, (float4*)g, (const float4*)u, n / 4);
+  }
   return launch_walk(swiglu_kernel, dim3((unsigned)blocks), dim3(256), 0, s, g, u, n);
 }
 
