@@ -99,3 +99,19 @@ def test_plan_placement_follows_the_byte_volume_rule():  # expertvm/src/tests.rs
     assert plan_placement(4096, 4096, 1, 1, pcie) == MOVE_WEIGHTS               # a tie moves the weights
     assert plan_placement(expert, act, 1, 1, 0) == MOVE_WEIGHTS                 # no link: both infinite, tie
     assert plan_placement(1 << 40, 1 << 40, 1 << 40, 1 << 40, 1) == MOVE_WEIGHTS  # saturating products
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 on its own (what a cgo / bindgen / cbindgen consumer sees)."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    header = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "llama_rust_b200.h")
+    src = tmp_path / "use_header.c"
+    src.write_text(f'#include "{header}"\nint main(void) {{ llr_exec* e = 0; llr_moe_ep* p = 0; (void)e; (void)p; '
+                   'return sizeof(llr_llama_layer) + sizeof(llr_moe_layer) + sizeof(llr_gguf_tensor) > 0 ? 0 : 1; }\n')
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-c", str(src), "-o", str(tmp_path / "use_header.o")],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
