@@ -115,3 +115,36 @@ def test_header_is_plain_c(tmp_path):
     r = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-c", str(src), "-o", str(tmp_path / "use_header.o")],
                        capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
+
+
+def test_ctypes_structures_have_the_layout_of_the_header(tmp_path):
+    """Every structure that crosses the boundary by value or by pointer: size and the offset of every field as the C
+    compiler lays the header's declaration out, against the ctypes mirror the tests and the bench call through."""
+    import shutil
+    import subprocess
+    from llama_rust_b200 import _lib
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    pairs = {"llr_counters": _lib.Counters, "llr_gguf_tensor": _lib.GgufTensor, "llr_program_entry": _lib.ProgramEntry,
+             "llr_program_op": _lib.ProgramOp, "llr_program_shard": _lib.ProgramShard, "llr_llama_config": _lib.LlamaConfig,
+             "llr_llama_layer": _lib.LlamaLayer, "llr_llama_model": _lib.LlamaModel, "llr_moe_layer": _lib.MoeLayer}
+    header = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include", "llama_rust_b200.h")
+    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{header}"', 'int main(void) {']
+    for cname, st in pairs.items():
+        lines.append(f'  printf("{cname} %zu", sizeof({cname}));')
+        for fname, *_ in st._fields_:
+            lines.append(f'  printf(" %zu", offsetof({cname}, {fname}));')
+        lines.append('  printf("\\n");')
+    lines += ['  return 0;', '}']
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines) + "\n")
+    exe = tmp_path / "layout"
+    r = subprocess.run([gcc, "-std=c99", str(src), "-o", str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr  # a field the mirror names and the header does not fails here
+    out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split("\n")
+    for line in filter(None, out):
+        cname, size, *offs = line.split()
+        st = pairs[cname]
+        assert int(size) == C.sizeof(st), (cname, size, C.sizeof(st))
+        assert [int(o) for o in offs] == [getattr(st, f[0]).offset for f in st._fields_], cname
