@@ -191,3 +191,26 @@ def test_open_from_a_path_maps_the_file(tmp_path):
         assert g.read(t.start, t.end).tobytes() == payload["w_q4k"]
     with pytest.raises(GgufError):
         GgufFile(str(tmp_path / "absent.gguf"))
+
+
+def test_llama_hyper_parameters_of_dense_and_routed_expert_files():
+    """`llama_config` (decode.rs:1905-1930, 7461-7515): the walk's hyper-parameters from `<arch>.*` metadata, with the
+    reference's defaults (kv heads = heads, head_dim = n_embd / heads, eps 1e-5, base 10000), the vocabulary from the
+    embedding's rows, and the expert counts of architecture=llama files with routed experts (llama_moe_into :10366)."""
+    from llama_rust_b200.gguf import GgufError, GgufFile, llama_config
+    base = gf.DEFAULT_KV + [("general.architecture", gf.STRING, "llama"), ("llama.block_count", gf.U32, 3),
+                            ("llama.embedding_length", gf.U32, 64), ("llama.feed_forward_length", gf.U32, 128),
+                            ("llama.attention.head_count", gf.U32, 4)]
+    embd = [("token_embd.weight", 0, (64, 10), np.zeros(640, np.float32).tobytes())]
+    cfg = llama_config(GgufFile(gf.write_gguf(base, embd)))
+    assert cfg == dict(n_layer=3, n_embd=64, n_head=4, n_head_kv=4, head_dim=16, n_ff=128, n_vocab=10, n_ctx=2048, rms_eps=1e-5,
+                       rope_base=10000.0)
+    moe = base + [("llama.attention.head_count_kv", gf.U32, 2), ("llama.expert_count", gf.U32, 8), ("llama.expert_used_count", gf.U32, 2),
+                  ("llama.context_length", gf.U32, 512)]
+    cfg = llama_config(GgufFile(gf.write_gguf(moe, embd)), n_ctx=100)
+    assert (cfg["n_head_kv"], cfg["n_expert"], cfg["n_expert_used"], cfg["n_ctx"]) == (2, 8, 2, 100)
+    assert llama_config(GgufFile(gf.write_gguf(moe, embd)))["n_ctx"] == 512
+    with pytest.raises(GgufError):  # more experts used than there are
+        llama_config(GgufFile(gf.write_gguf(base + [("llama.expert_count", gf.U32, 2), ("llama.expert_used_count", gf.U32, 3)], embd)))
+    with pytest.raises(GgufError):  # a required key is missing
+        llama_config(GgufFile(gf.write_gguf(base[:-1], embd)))
