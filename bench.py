@@ -19,7 +19,10 @@ one copy out per step; at N > 1 this is `e2e`);
 `roofline` is the kernel the timed region consists of (the persistent program
 kernel; the Q4_K single-product launches are reported beside it) against the
 measured HBM peak; `cpu_baseline` is the CPU oracle (AVX2 row kernels, reference threading)
-on a bounded sample of the same sweep.
+on a bounded sample of the same sweep.  `configs` holds the other BASELINE configurations (1: the
+single Q8_0 product; every format's decode kernel on one large matrix; 4: the chunk GEMM; 5: the
+routed-expert layer, at N > 1 expert-parallel over peer stores beside the NCCL all-to-all form;
+3: the walk on the device).  `--case gemv|moe|session` runs one small case for profiling.
 """
 from __future__ import annotations
 
