@@ -1596,6 +1596,9 @@ struct llr_session {
   int *table_dev = nullptr, *row_pos = nullptr, *row_seq = nullptr, *last_rows = nullptr;
   // decode steps (one row): the independent products of a layer as one launch each -- {q, k, v} and {gate, up}
   std::vector<llr::Program*> qkv_prog, gateup_prog;
+  // routed layers, one token: the chosen experts' {gate, up} products as one launch and their down products as another
+  // (select programs over Moe::maps and moe_sel); null where a format is outside the programs' and the products run one by one
+  std::vector<llr::Program*> moe_gateup_prog, moe_down_prog;
   // layers whose FFN is a routed-expert layer (architecture=llama with n_expert > 0): own copies of the matrix arrays
   struct Moe {
     std::vector<const llr_matrix*> gate, up, down;
@@ -1634,6 +1637,8 @@ void session_release(llr_session* s) {
   for (auto& M : s->moe) if (M && M->maps) cudaFree(M->maps);
   for (llr::Program* p : s->qkv_prog) program_destroy(p);
   for (llr::Program* p : s->gateup_prog) program_destroy(p);
+  for (llr::Program* p : s->moe_gateup_prog) program_destroy(p);
+  for (llr::Program* p : s->moe_down_prog) program_destroy(p);
   cudaGetLastError();
 }
 
@@ -1684,16 +1689,26 @@ cudaError_t session_moe_ffn(llr_session* s, size_t li, size_t n) {
     if ((ce = moe_route(e, &M.layer, S, 1, s->xn, s->moe_logits, s->moe_ids, s->moe_wts)) != cudaSuccess ||
         (ce = launch_select_sorted(s->moe_ids, s->moe_wts, (int)U, sel, selw, e->stream, &e->ctr.launches)) != cudaSuccess)
       return ce;
-    for (size_t j = 0; j < U; ++j)
-      if ((ce = launch_gemv_mma_select(vg, M.maps, sel + j, s->xn, s->gate + j * FF, e->stream, e->sm_count, e->err_flag, &e->ctr.launches)) != cudaSuccess ||
-          (ce = launch_gemv_mma_select(vg, M.maps + NE * GEMV_MAP_BYTES, sel + j, s->xn, s->up + j * FF, e->stream, e->sm_count, e->err_flag,
-                                       &e->ctr.launches)) != cudaSuccess)
-        return ce;
+    llr::Program* pgu = s->moe_gateup_prog[li];
+    llr::Program* pdn = s->moe_down_prog[li];
+    if (pgu) {
+      if ((ce = program_run(pgu, e->stream, e->err_flag, e->poll_limit, &e->ctr.launches)) != cudaSuccess) return ce;
+    } else {
+      for (size_t j = 0; j < U; ++j)
+        if ((ce = launch_gemv_mma_select(vg, M.maps, sel + j, s->xn, s->gate + j * FF, e->stream, e->sm_count, e->err_flag, &e->ctr.launches)) != cudaSuccess ||
+            (ce = launch_gemv_mma_select(vg, M.maps + NE * GEMV_MAP_BYTES, sel + j, s->xn, s->up + j * FF, e->stream, e->sm_count, e->err_flag,
+                                         &e->ctr.launches)) != cudaSuccess)
+          return ce;
+    }
     if ((ce = launch_silu_mul(s->gate, s->up, (int64_t)(U * FF), e->stream, &e->ctr.launches)) != cudaSuccess) return ce;
-    for (size_t j = 0; j < U; ++j)
-      if ((ce = launch_gemv_mma_select(vd, M.maps + 2 * NE * GEMV_MAP_BYTES, sel + j, s->gate + j * FF, s->moe_y + j * E, e->stream, e->sm_count,
-                                       e->err_flag, &e->ctr.launches)) != cudaSuccess)
-        return ce;
+    if (pdn) {
+      if ((ce = program_run(pdn, e->stream, e->err_flag, e->poll_limit, &e->ctr.launches)) != cudaSuccess) return ce;
+    } else {
+      for (size_t j = 0; j < U; ++j)
+        if ((ce = launch_gemv_mma_select(vd, M.maps + 2 * NE * GEMV_MAP_BYTES, sel + j, s->gate + j * FF, s->moe_y + j * E, e->stream, e->sm_count,
+                                         e->err_flag, &e->ctr.launches)) != cudaSuccess)
+          return ce;
+    }
     return launch_combine_one(s->moe_y, selw, s->proj, (int)U, (int)E, e->stream, &e->ctr.launches);
   }
   if ((ce = moe_route(e, &M.layer, S, n, s->xn, s->moe_logits, s->moe_ids, s->moe_wts)) != cudaSuccess ||
@@ -1954,7 +1969,7 @@ int session_create(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t k
     const size_t o_logits = take(B * max_expert * 4), o_ids = take(n_rows * 4), o_wts = take(n_rows * 4), o_tor = take(n_rows * 4),
                  o_rot = take(n_rows * 4), o_w = take(n_rows * 4), o_fill = take(B * 4), o_first = take((max_expert + 1) * 4),
                  o_local = take(max_expert);
-    ce = cudaMalloc((void**)&s->moe_tables, at);
+    if (ce == cudaSuccess) ce = cudaMalloc((void**)&s->moe_tables, at);
     if (ce == cudaSuccess) {
       char* tb = s->moe_tables;
       s->moe_logits = (float*)(tb + o_logits); s->moe_ids = (int*)(tb + o_ids); s->moe_wts = (float*)(tb + o_wts);
@@ -1986,6 +2001,37 @@ int session_create(llr_exec* e, const llr_llama_model* m, size_t n_seq, size_t k
     const llr_llama_layer& W = s->layers[li];
     group({{W.attn_q, s->q}, {W.attn_k, s->k}, {W.attn_v, s->v}}, &s->qkv_prog[li]);
     if (!s->moe[li]) group({{W.ffn_gate, s->gate}, {W.ffn_up, s->up}}, &s->gateup_prog[li]);
+  }
+  s->moe_gateup_prog.assign(c.n_layer, nullptr);
+  s->moe_down_prog.assign(c.n_layer, nullptr);
+  for (uint32_t li = 0; li < c.n_layer && ce == cudaSuccess && s->moe_select; ++li) {
+    if (!s->moe[li]) continue;
+    const llr_session::Moe& M = *s->moe[li];
+    const MatView vg = view_of(M.gate[0]), vd = view_of(M.down[0]);
+    // slot j of the step's sorted experts: x, y and the base of its kind's maps
+    auto select_group = [&](const MatView& v, std::initializer_list<std::pair<float*, size_t>> kinds, const float* x, size_t x_step,
+                            size_t y_step, llr::Program** slot) {
+      if (!prog_entry_supported(v)) return;
+      std::vector<ProgEntry> pe;
+      for (size_t j = 0; j < M.S.n_used; ++j)
+        for (const auto& kind : kinds) {
+          ProgEntry E{};
+          E.w = v.w; E.x = x + j * x_step; E.y = kind.first + j * y_step; E.row_bytes = v.row_bytes;
+          E.rows = (int)v.rows; E.cols = (int)v.cols; E.dtype = v.dtype; E.tokens = 1; E.y_ld = v.rows;
+          E.x_phase = E.x2_phase = E.resid_phase = -1;
+          E.sel_slot = (int)j; E.map_base = (int)kind.second;
+          pe.push_back(E);
+        }
+      std::string msg;
+      if (program_create(pe, std::vector<int>(pe.size(), 0), e->sm_count, false, nullptr, slot, &msg) != cudaSuccess ||
+          program_set_select(*slot, M.maps, s->moe_sel) != cudaSuccess) {
+        if (*slot) program_destroy(*slot);
+        *slot = nullptr;
+        cudaGetLastError();
+      }
+    };
+    select_group(vg, {{s->gate, 0}, {s->up, M.S.n_exp}}, s->xn, 0, M.S.n_ff, &s->moe_gateup_prog[li]);
+    select_group(vd, {{s->moe_y, 2 * M.S.n_exp}}, s->gate, M.S.n_ff, E, &s->moe_down_prog[li]);
   }
   if (ce != cudaSuccess) {
     session_release(s);

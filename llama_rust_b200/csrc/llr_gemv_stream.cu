@@ -155,6 +155,7 @@ struct Work {
   int n_entries;           // entries of the program
   uint32_t tag_base;       // tag of phase p in this run = tag_base + p
   int poll_limit;          // bound of the waits on other CTAs' or ranks' data
+  const int* sel;          // select programs: entry E reads its weights through maps[E.map_base + sel[E.sel_slot]]
 };
 // Slots of the counter array beside the per-phase counters ([0, 4095) this rank's CTAs per phase,
 // [4096, 8191) arrivals of the peers per phase).
@@ -209,7 +210,9 @@ struct SplitKey {
 // FLOW: the program may carry results from entry to entry as tagged pairs and apply RMSNorm / SwiGLU /
 // residual adds; compiled out otherwise (the plain split and the per-phase counters need fewer registers
 // around the block routines, which run at the register limit of two CTAs per SM).
-template <int MT, bool PROGRAM, int DTFIX, bool PEERS = false, bool HOSTOUT = false, bool FLOW = false>
+// SELECT: one-phase programs whose entries choose their matrix at run time (see Work::sel); the table is written by an
+// earlier kernel of the stream, so the producer too waits for that kernel before it fetches anything.
+template <int MT, bool PROGRAM, int DTFIX, bool PEERS = false, bool HOSTOUT = false, bool FLOW = false, bool SELECT = false>
 __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* counters,
                                             unsigned long long epoch, int* err) {
   using L = SLay<MT>;
@@ -247,6 +250,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
       int c = 0;
       bool ok = true;
       const uint64_t stream_once = l2_policy_evict_first();
+      if (SELECT) asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int ph = 0; ph < wk.n_phases; ++ph) {
         const ProgPhase P = wk.phases[ph];
         int lo, hi;
@@ -257,7 +261,7 @@ __device__ __forceinline__ void stream_body(const Work wk, unsigned long long* c
           if (!entry_range(E, lo, hi, &t0, &t1)) continue;
           const int dtype = DTFIX >= 0 ? DTFIX : E.dtype;
           const Geom gm = geom_of(dtype);
-          const CUtensorMap* map = wk.maps + (PROGRAM ? P.first_entry + ei : 0);
+          const CUtensorMap* map = SELECT ? wk.maps + E.map_base + wk.sel[E.sel_slot] : wk.maps + (PROGRAM ? P.first_entry + ei : 0);
           const int cols = E.cols;
           const int n_span = (cols + SPAN - 1) / SPAN;
           for (int span = 0; span < n_span; ++span) {
@@ -695,6 +699,16 @@ gemv_sharded_program_kernel(const ProgEntry* __restrict__ entries, const ProgPha
   stream_body<MT, true, -1, true, false, FLOW>(wk, counters, run.epoch, err);
 }
 
+// One phase of one-token products that each pick one of several equally shaped matrices through a device table.
+__global__ void __launch_bounds__(NTHREADS, 2)
+gemv_select_program_kernel(const ProgEntry* __restrict__ entries, const ProgPhase* __restrict__ phases,
+                           const CUtensorMap* __restrict__ maps, const int* __restrict__ sel,
+                           unsigned long long* __restrict__ counters, const RunArgs run, int* __restrict__ err) {
+  Work wk{entries, phases, 1, nullptr, HostOut{}, maps, run.n_entries, run.tag_base, run.poll_limit, sel};
+  if (blockIdx.x == 0 && threadIdx.x == 0) counters[TAG_SLOT] = run.tag_next;
+  stream_body<1, true, -1, false, false, false, true>(wk, counters, run.epoch, err);
+}
+
 // Tensor map of one matrix for the stage loads (see Geom).
 bool encode_weight_map(const uint8_t* w, int dtype, int64_t rows, int64_t cols, int64_t row_bytes, CUtensorMap* map) {
   memset(map, 0, sizeof(*map));
@@ -874,6 +888,8 @@ struct Program {
   unsigned long long tag_next = 1;  // tags are never reused, whatever programs ran on the same buffers before; 0 marks fresh memory
   PeerTable* d_peers = nullptr;   // sharded programs: the peer table, and the counters are not ours
   bool own_counters = true;
+  const CUtensorMap* sel_maps = nullptr;  // select programs (program_set_select): the caller's maps and table, both on the device
+  const int* sel = nullptr;
 };
 
 bool prog_entry_supported(const MatView& m) {
@@ -924,7 +940,8 @@ static cudaError_t prog_launch(Program* p, cudaStream_t stream, int* err, int po
     cfg.stream = stream;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, kern, de, dp, np, dm, dc, run, err);
+    if (MT == 1 && !FLOW && p->sel) e = cudaLaunchKernelEx(&cfg, gemv_select_program_kernel, de, dp, p->sel_maps, p->sel, dc, run, err);
+    else e = cudaLaunchKernelEx(&cfg, kern, de, dp, np, dm, dc, run, err);
   } else {
     void* args[] = {(void*)&de, (void*)&dp, (void*)&np, (void*)&dm, (void*)&dc, (void*)&run, (void*)&err};
     e = cudaLaunchCooperativeKernel((const void*)kern, dim3((unsigned)p->grid), dim3(NTHREADS), args,
@@ -1103,6 +1120,16 @@ cudaError_t program_create(const std::vector<ProgEntry>& entries_in, const std::
     return e;
   }
   *out = p;
+  return cudaSuccess;
+}
+
+cudaError_t program_set_select(Program* p, const void* maps_dev, const int* sel_dev) {
+  if (p->n_phases != 1 || p->counter_phases != 0 || p->flow || p->max_tokens != 1 || p->d_peers) return cudaErrorInvalidValue;
+  int bps = 0;  // the grid stays the plain program's: no CTA waits for another, so residency does not matter
+  cudaError_t e = occupancy(gemv_select_program_kernel, SLay<1>::TOTAL, &bps);
+  if (e != cudaSuccess) return e;
+  p->sel_maps = (const CUtensorMap*)maps_dev;
+  p->sel = sel_dev;
   return cudaSuccess;
 }
 

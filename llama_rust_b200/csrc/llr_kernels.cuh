@@ -108,7 +108,8 @@ struct ProgEntry {
   int x_op;
   float eps;
   int x_phase, x2_phase, resid_phase;  // phase that writes the tagged source (-1: plain memory, ready at launch)
-  int pad[3];
+  int sel_slot, map_base;  // select programs (program_set_select): the matrix is maps[map_base + sel[sel_slot]]
+  int pad;
 };
 static_assert(sizeof(ProgEntry) == 128, "entries are copied as sixteen 8-byte words");
 // Row-sharded programs across GPUs: where the other ranks keep their copies of the results
@@ -139,6 +140,10 @@ struct ShardInfo {
 cudaError_t program_create(const std::vector<ProgEntry>& entries, const std::vector<int>& phase_of,
                            int sm_count, bool strict_phases, const ShardInfo* shard, Program** out, std::string* msg);
 void program_destroy(Program* p);
+// Turns a one-phase, one-token program without operations into a select program: entry E then reads its weights through
+// maps_dev[E.map_base + sel_dev[E.sel_slot]] (tensor maps of gemv_mma_encode_map, matrices shaped like E) instead of
+// E.w.  The table is read on the device when the launch runs, after the kernels before it in the stream.
+cudaError_t program_set_select(Program* p, const void* maps_dev, const int* sel_dev);
 // poll_limit: iterations a device-side wait for another CTA's or rank's data may take before it gives up
 cudaError_t program_run(Program* p, cudaStream_t stream, int* err_flag, int poll_limit, uint64_t* launches);
 int program_phases(const Program* p);
