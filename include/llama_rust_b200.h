@@ -448,7 +448,8 @@ int llr_moe_experts_device(llr_exec* exec, const llr_moe_layer* layer, const uin
  *                        receive the routing decision; enqueued, no synchronization (llr_exec_synchronize ends the run).
  * Every rank makes the same sequence of runs (a rank with no tokens of its own still passes at least one).  Ranks must
  * reach a wait within the wait limit of each other, else the run fails with LLR_ERR_CUDA and the layer object has to be
- * re-created on every rank.  Several ranks driven from ONE thread (executors on one or several GPUs) call dispatch
+ * re-created on every rank, on zeroed arenas: runs are counted from the creation of the layer, in the object and in the
+ * arena alike, so an arena that served a layer before is refused (LLR_ERR_INVALID) until it has been zeroed again.  Several ranks driven from ONE thread (executors on one or several GPUs) call dispatch
  * on every rank first, then serve on every rank, then combine: no wait then ever spins.  With the f32-faithful
  * kernels (llr_exec_set_path(exec, 3)) the output is bit-identical to llr_moe_ffn on the same tokens. */
 typedef struct llr_moe_ep llr_moe_ep;

@@ -1198,6 +1198,18 @@ int llr_moe_ep_create(llr_exec* e, const llr_moe_layer* L, uint32_t world, uint3
   const EpLayout lay = ep_layout((int)S.n_exp, (int)S.n_used, (int)S.n_embd, (int)world, (int)rank, (int)max_tokens);
   if (arena_bytes < lay.total)
     return fail(e, LLR_ERR_INVALID, "the arena holds " + std::to_string(arena_bytes) + " bytes, llr_moe_ep_arena_bytes asks for " + std::to_string(lay.total));
+  DeviceGuard guard(e->device);
+  {
+    // Runs are counted from zero in this object and in the arena alike.  The words below are written by this rank's own
+    // kernels only, so they tell (without racing against peers that already run) whether this arena served a layer
+    // before: its flags would then pass for runs that have not happened yet.
+    EpHeader h;
+    cudaError_t ce = cudaMemcpy(&h, arena, sizeof(h), cudaMemcpyDeviceToHost);
+    if (ce != cudaSuccess) return fail_cuda(e, ce, "expert-parallel arena");
+    if (h.done_dispatch != 0 || h.done_return != 0 || h.flag_in[rank] != 0 || h.flag_back[rank] != 0)
+      return fail(e, LLR_ERR_INVALID, "the arena has served an expert-parallel layer before: free the layer on every rank, zero every arena "
+                                      "(or allocate new ones), and only then create the next layer");
+  }
   std::unique_ptr<llr_moe_ep> ep(new llr_moe_ep);
   ep->owner = e;
   ep->S = S;
@@ -1212,7 +1224,6 @@ int llr_moe_ep_create(llr_exec* e, const llr_moe_layer* L, uint32_t world, uint3
     ep->peers.arena[g] = g == rank ? (char*)arena : (char*)peer_arenas[g];
     if (!ep->peers.arena[g] || ((uintptr_t)ep->peers.arena[g] & 255) != 0) return fail(e, LLR_ERR_INVALID, "peer arena " + std::to_string(g));
   }
-  DeviceGuard guard(e->device);
   const size_t T = max_tokens, n_rows = T * S.n_used, n_seg = (size_t)lay.e_loc * world, max_gather = n_seg * T;
   auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
   size_t at = 0;

@@ -158,6 +158,9 @@ def test_expert_parallel_layer_with_peer_stores_on_one_gpu(world):
             exs[0].moe_ep(routers[0], mines[0]["gate"], mines[0]["up"], mines[0]["down"], n_used, True, world, 1, t_max, arenas[0], nbytes, arenas)
     for ep in eps:
         ep.free()
+    # a second layer on arenas that still carry the first one's run counts would take stale flags for new ones: refused
+    with pytest.raises(NativeCudaError, match="has served"):
+        exs[0].moe_ep(routers[0], mines[0]["gate"], mines[0]["up"], mines[0]["down"], n_used, True, world, 0, t_max, arenas[0], nbytes, arenas)
     for ex, a in zip(exs, arenas):
         ex.shared_free(a)
         ex.close()
