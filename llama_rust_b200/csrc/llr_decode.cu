@@ -924,11 +924,12 @@ cudaError_t launch_attention(const float* q, const KvView& kv, float* out, float
   const size_t score_floats = (size_t)gqa * max_chunk > groups * gqa * w.head_dim ? (size_t)gqa * max_chunk : groups * gqa * w.head_dim;
   const size_t smem = ((size_t)gqa * w.head_dim + score_floats + 32) * sizeof(float);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
+  static PerDevice configured;  // largest size the kernel has been allowed on this device
+  std::atomic<int>& allowed = configured.here();
+  if (smem > 48 * 1024 && (int)smem > allowed.load(std::memory_order_relaxed)) {
     cudaError_t e = cudaFuncSetAttribute(attention_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    configured = smem;
+    allowed.store((int)smem, std::memory_order_relaxed);
   }
   if (launches) *launches += 2;
   cudaError_t e;

@@ -958,11 +958,12 @@ cudaError_t launch_bn(const MatView& m, const CUtensorMap& wmap, const CUtensorM
                       int tokens, int splits, cudaStream_t stream, int* err) {
   auto kern = gemm_tc_kernel<DT, BN, F16>;
   constexpr int smem = GLay<DT, BN>::TOTAL;
-  static bool ready = false;
-  if (!ready) {
+  static PerDevice ready;  // per instantiation
+  std::atomic<int>& slot = ready.here();
+  if (slot.load(std::memory_order_relaxed) == 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    ready = true;
+    slot.store(1, std::memory_order_relaxed);
   }
   // Programmatic dependent launch: the packed-weight pipeline and the dequantization start while the
   // conversion kernel before it is still running; what depends on that kernel waits inside.
@@ -1139,11 +1140,12 @@ template <int DT, int BN, bool F16>
 cudaError_t launch_grouped_bn(const GemmGroup* desc_dev, int n_groups, int tiles, cudaStream_t stream, int* err) {
   auto kern = gemm_tc_grouped_kernel<DT, BN, F16>;
   constexpr int smem = GLay<DT, BN>::TOTAL;
-  static bool ready = false;
-  if (!ready) {
+  static PerDevice ready;  // per instantiation
+  std::atomic<int>& slot = ready.here();
+  if (slot.load(std::memory_order_relaxed) == 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    ready = true;
+    slot.store(1, std::memory_order_relaxed);
   }
   kern<<<(unsigned)tiles, TC_THREADS, smem, stream>>>(desc_dev, n_groups, err);
   return cudaGetLastError();

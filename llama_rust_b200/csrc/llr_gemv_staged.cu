@@ -310,7 +310,9 @@ cudaError_t launch_one(const MatView& m, const float* x, float* y, int tokens, c
                        int sm_count) {
   auto kern = gemv_staged_kernel<DT, MT, R>;
   constexpr size_t smem = (size_t)NW * STAGES * R * Seg<DT>::SROW;
-  static int blocks_per_sm = 0;  // per instantiation
+  static PerDevice cache;  // per instantiation
+  std::atomic<int>& slot = cache.here();
+  int blocks_per_sm = slot.load(std::memory_order_relaxed);
   if (blocks_per_sm == 0) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -318,6 +320,7 @@ cudaError_t launch_one(const MatView& m, const float* x, float* y, int tokens, c
     e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, NW * 32, smem);
     if (e != cudaSuccess) return e;
     blocks_per_sm = n > 0 ? n : 1;
+    slot.store(blocks_per_sm, std::memory_order_relaxed);
   }
   const int64_t n_groups = (m.rows + R - 1) / R;
   int64_t grid = (n_groups + NW - 1) / NW;

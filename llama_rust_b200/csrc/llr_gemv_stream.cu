@@ -747,11 +747,13 @@ template <int MT, int DT>
 cudaError_t launch_single(const MatView& m, const float* x, float* y, int tokens, cudaStream_t stream,
                           int sm_count, int* err, const HostOut* ho) {
   constexpr int smem = SLay<MT>::TOTAL;
-  static int blocks_per_sm = 0, blocks_per_sm_ho = 0;  // per instantiation
-  int& bps = ho ? blocks_per_sm_ho : blocks_per_sm;
+  static PerDevice cache, cache_ho;  // per instantiation
+  std::atomic<int>& slot = (ho ? cache_ho : cache).here();
+  int bps = slot.load(std::memory_order_relaxed);
   if (bps == 0) {
     cudaError_t e = ho ? occupancy(gemv_stream_hostout_kernel<MT, DT>, smem, &bps) : occupancy(gemv_stream_kernel<MT, DT>, smem, &bps);
     if (e != cudaSuccess) return e;
+    slot.store(bps, std::memory_order_relaxed);
   }
   ProgEntry E{m.w, x, y, m.row_bytes, (int)m.rows, (int)m.cols, m.dtype, tokens, 0, (int)((m.rows + 15) / 16), m.rows};
   CUtensorMap map;
@@ -828,10 +830,13 @@ template <int DT>
 static cudaError_t launch_select(const MatView& shape, const void* maps_dev, const int* sel_dev, const float* x, float* y,
                                  cudaStream_t stream, int sm_count, int* err) {
   constexpr int smem = SLay<1>::TOTAL;
-  static int bps = 0;
+  static PerDevice cache;
+  std::atomic<int>& slot = cache.here();
+  int bps = slot.load(std::memory_order_relaxed);
   if (bps == 0) {
     cudaError_t e = occupancy(gemv_stream_select_kernel<DT>, smem, &bps);
     if (e != cudaSuccess) return e;
+    slot.store(bps, std::memory_order_relaxed);
   }
   ProgEntry E{nullptr, x, y, shape.row_bytes, (int)shape.rows, (int)shape.cols, shape.dtype, 1, 0, (int)((shape.rows + 15) / 16), shape.rows};
   int grid = sm_count * bps;

@@ -4,10 +4,23 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <string>
 #include <vector>
 
 namespace llr {
+
+// One-time setup of a kernel, per device: function attributes and occupancy belong to a device's context, and executors
+// of several devices (and threads) may share a process.  here() is the current device's slot; 0 means not set up yet
+// (two threads that both find 0 do the same setup and store the same value).
+struct PerDevice {
+  std::atomic<int> slot[64];
+  std::atomic<int>& here() {
+    int d = 0;
+    cudaGetDevice(&d);
+    return slot[d & 63];
+  }
+};
 
 // A resident packed matrix as the kernels see it.  `w` is 256-byte aligned and
 // the allocation is padded so that 16-byte windows around any row are readable.

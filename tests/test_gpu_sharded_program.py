@@ -252,3 +252,35 @@ def test_expert_parallel_layer_with_peer_stores_over_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     assert _spawn(2, _moe_ep_worker) == {0: "ok", 1: "ok"}
+
+
+def test_one_process_drives_executors_on_two_devices():
+    """Executors of two devices in ONE process (one thread driving several ranks, as the expert-parallel stages allow):
+    kernels are set up per device (shared-memory limits and occupancy belong to a device's context), so the second
+    device runs every kernel family and returns the same bits as the first."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from helpers import random_packed
+    from llama_rust_b200 import Executor
+    rng = np.random.default_rng(2024)
+    cases = []  # path, kind, rows, cols, tokens, packed weights, activations
+    for path, kind, rows, cols, tokens in ((3, Q4_K, 64, 4096, 1), (3, Q6_K, 32, 2048, 3), (3, Q8_0, 48, 2048, 1), (2, Q4_K, 64, 4096, 1),
+                                           (2, Q8_0, 48, 2048, 3), (1, Q6_K, 32, 2048, 1), (0, Q4_K, 128, 4096, 64), (0, Q8_0, 128, 2048, 64)):
+        cases.append((path, kind, rows, cols, tokens, random_packed(rng, kind, rows, cols),
+                      rng.standard_normal(tokens * cols).astype(np.float32)))
+    got = []
+    for dev in (0, 1):
+        with Executor(dev) as ex:
+            mine = []
+            for path, kind, rows, cols, tokens, w, x in cases:
+                ex.set_path(path)
+                m = ex.upload(kind, rows, cols, w)
+                y = np.full(rows * tokens, np.nan, np.float32)
+                ex.gemm_resident(m, tokens, x, y)
+                assert np.all(np.isfinite(y)), (dev, path, kind)
+                mine.append(y)
+                m.free()
+            got.append(mine)
+    for a, b, case in zip(got[0], got[1], cases):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), case[:5]
