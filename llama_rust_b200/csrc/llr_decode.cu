@@ -40,16 +40,6 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
   for (int w = 0; w < nw; ++w) t += sh[w];  // fixed order
   return t;
 }
-__device__ __forceinline__ float block_max(float v, float* sh) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  v = warp_max(v);
-  __syncthreads();
-  if (lane == 0) sh[warp] = v;
-  __syncthreads();
-  float t = -CUDART_INF_F;
-  for (int w = 0; w < nw; ++w) t = fmaxf(t, sh[w]);
-  return t;
-}
 
 __device__ __forceinline__ int row_position(const RowMap& r, int t) { return r.row_pos ? r.row_pos[t] : *r.pos_dev + t; }
 __device__ __forceinline__ int row_sequence(const RowMap& r, int t) { return r.row_seq ? r.row_seq[t] : 0; }

@@ -191,9 +191,6 @@ template <int NCH> __device__ __forceinline__ void lds_chunks(uint32_t p, uint32
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3]) : "r"(p + 16 * i));
 }
-__device__ __forceinline__ void sts128(uint32_t p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
 
 // Four unsigned bytes c0..c3 (each < 1024) -> out[0] = bf16(c0*a+nb), bf16(c1*a+nb); out[1] = c2, c3.
 // MASK/MAGIC pick the bits and the binary16 exponent whose unit in the last place is one
