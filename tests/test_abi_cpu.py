@@ -101,6 +101,27 @@ def test_plan_placement_follows_the_byte_volume_rule():  # expertvm/src/tests.rs
     assert plan_placement(1 << 40, 1 << 40, 1 << 40, 1 << 40, 1) == MOVE_WEIGHTS  # saturating products
 
 
+def test_expert_parallel_arena_size_covers_both_halves_of_the_exchange():
+    """llr_moe_ep_arena_bytes is host arithmetic: per half of the double-buffered arena, one receive slot of n_embd floats
+    (plus a row tag) for every (local expert, sender, position) and one return row per routed row of this rank; shapes the
+    layer cannot take give 0."""
+    from llama_rust_b200.executor import moe_ep_arena_bytes
+    n_expert, n_used, n_embd = 8, 2, 4096
+    for world in (1, 2, 3, 8):
+        e_loc = -(-n_expert // world)
+        for t_max in (1, 48, 512):
+            n = moe_ep_arena_bytes(n_expert, n_used, n_embd, world, t_max)
+            slots = e_loc * world * t_max
+            payload = 2 * (slots * (n_embd + 1) * 4 + t_max * n_used * n_embd * 4 + e_loc * world * 4)
+            assert payload <= n <= payload + 64 * 256, (world, t_max, n, payload)  # tables start on 256-byte boundaries
+            assert n % 256 == 0
+        assert moe_ep_arena_bytes(n_expert, n_used, n_embd, world, 64) > moe_ep_arena_bytes(n_expert, n_used, n_embd, world, 32)
+    for bad in ((0, 2, 4096, 2, 8), (8, 0, 4096, 2, 8), (8, 9, 4096, 2, 8), (8, 2, 0, 2, 8), (8, 2, 4098, 2, 8), (8, 2, 4096, 0, 8),
+                (8, 2, 4096, 9, 8), (8, 2, 4096, 2, 0), (8, 2, 4096, 2, (1 << 20) + 1)):
+        with pytest.raises(ValueError):
+            moe_ep_arena_bytes(*bad)
+
+
 def test_header_is_plain_c(tmp_path):
     """The boundary is a C ABI: the header must compile as C99 on its own (what a cgo / bindgen / cbindgen consumer sees)."""
     import shutil
