@@ -186,12 +186,13 @@ int llr_plan_placement(uint64_t expert_bytes, uint64_t activation_bytes, uint64_
  * the object even on a parse error (for llr_gguf_last_error); release it with llr_gguf_close. */
 typedef struct llr_gguf llr_gguf;
 typedef struct {
-  const char* name;    /* valid until llr_gguf_close                                              */
+  const char* name;    /* valid until llr_gguf_close; name_len bytes of UTF-8 and a terminating NUL */
   int32_t ggml_type;   /* ggml type id as stored in the file                                      */
   int32_t dtype;       /* LLR_DTYPE_* of the executor, or -1 when it has no kernel for the type   */
   uint32_t n_dims;     /* 1..4                                                                    */
   uint64_t shape[4];   /* GGUF order, innermost (columns) first; unused entries are 1             */
   uint64_t start, end; /* byte range of the payload in the file [Tensor::blob_range, gguf.rs:435] */
+  uint64_t name_len;   /* bytes of `name`: a name is any UTF-8 string, NUL bytes included [read_string, gguf.rs:903] */
 } llr_gguf_tensor;
 int llr_gguf_open(const char* path, llr_gguf** out);
 int llr_gguf_open_bytes(const void* bytes, size_t len, llr_gguf** out);
@@ -200,6 +201,7 @@ const char* llr_gguf_last_error(const llr_gguf* g);
 int llr_gguf_info(const llr_gguf* g, size_t* n_tensors, size_t* alignment, size_t* file_bytes);
 int llr_gguf_tensor_at(const llr_gguf* g, size_t index, llr_gguf_tensor* out); /* file order [Gguf::tensors] */
 int llr_gguf_find(const llr_gguf* g, const char* name, llr_gguf_tensor* out);  /* first of that name [Gguf::tensor] */
+/* (names are looked up as C strings: a tensor whose name holds a NUL byte is reached through llr_gguf_tensor_at only) */
 /* Copies bytes [start, start + len) of the file image to out (small host-side tensors such as norm weights). */
 int llr_gguf_read(const llr_gguf* g, uint64_t start, size_t len, void* out);
 /* Typed metadata readers: LLR_ERR_INVALID when the key is absent or holds another type [gguf.rs:571-628]. */

@@ -40,8 +40,8 @@ class Counters(C.Structure):
 
 
 class GgufTensor(C.Structure):
-    _fields_ = [("name", C.c_char_p), ("ggml_type", C.c_int32), ("dtype", C.c_int32), ("n_dims", C.c_uint32),
-                ("shape", C.c_uint64 * 4), ("start", C.c_uint64), ("end", C.c_uint64)]
+    _fields_ = [("name", C.c_void_p), ("ggml_type", C.c_int32), ("dtype", C.c_int32), ("n_dims", C.c_uint32),
+                ("shape", C.c_uint64 * 4), ("start", C.c_uint64), ("end", C.c_uint64), ("name_len", C.c_uint64)]
 
 
 class ProgramEntry(C.Structure):

@@ -256,6 +256,7 @@ void fill(const TensorInfo& t, llr_gguf_tensor* out) {
   for (int d = 0; d < 4; ++d) out->shape[d] = t.shape[d];
   out->start = t.start;
   out->end = t.end;
+  out->name_len = t.name.size();
 }
 
 // The byte range of rows [first_row, first_row + n_rows) of part `part` (decode.rs:9612-9713); n_rows 0 = all rows.

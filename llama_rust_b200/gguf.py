@@ -51,7 +51,7 @@ class TensorInfo:
 
 
 def _info(t: _lib.GgufTensor) -> TensorInfo:
-    return TensorInfo(t.name.decode(), t.ggml_type, t.dtype, tuple(t.shape[:t.n_dims]), t.start, t.end)
+    return TensorInfo(C.string_at(t.name, t.name_len).decode(), t.ggml_type, t.dtype, tuple(t.shape[:t.n_dims]), t.start, t.end)
 
 
 class GgufFile:

@@ -168,16 +168,38 @@ def test_seeded_corruptions_never_disagree_with_the_reference_rules():
     image, _ = _sample_file()
     table_end = min(t[3] for t in go.parse(image)[2])
     rng = np.random.default_rng(5)
-    for _ in range(300):
+    for _ in range(450):
         bad = bytearray(image)
-        for _ in range(int(rng.integers(1, 4))):
-            bad[int(rng.integers(0, table_end))] = int(rng.integers(0, 256))
+        kind = int(rng.integers(0, 3))
+        if kind == 0:  # a few bytes of the tables replaced
+            for _ in range(int(rng.integers(1, 4))):
+                bad[int(rng.integers(0, table_end))] = int(rng.integers(0, 256))
+        elif kind == 1:  # one bit flipped, then the file cut anywhere
+            bad[int(rng.integers(0, table_end))] ^= 1 << int(rng.integers(0, 8))
+            bad = bad[: int(rng.integers(0, len(bad)))]
+        else:  # eight bytes replaced by an extreme count or offset
+            at = int(rng.integers(0, table_end - 8))
+            bad[at:at + 8] = [0, 1, 2 ** 31, 2 ** 32 - 1, 2 ** 63, 2 ** 64 - 1][int(rng.integers(0, 6))].to_bytes(8, "little")
         want, werr = _oracle(bytes(bad))
         if werr is None and sum(len(v[2]) for v in want[1].values() if v[0] == 9) > 10 ** 6:
             continue  # a corrupted count that still fits the file: nothing to learn, much to allocate
         g = _agree(bytes(bad))
         if g is not None:
             g.close()
+
+
+def test_a_tensor_name_with_nul_bytes_crosses_the_boundary_whole():
+    """A name is any UTF-8 string (read_string, gguf.rs:903), NUL bytes included: the record carries its length, and a
+    lookup by C string neither finds such a tensor nor takes it for the prefix before the NUL."""
+    from llama_rust_b200.gguf import GgufFile
+    payload = bytes(range(16))
+    image = gf.write_gguf(gf.DEFAULT_KV, [("a\x00b", 0, (4,), payload), ("a", 0, (4,), payload[::-1])])
+    g = _agree(image)
+    assert [t.name for t in g.tensors()] == ["a\x00b", "a"]
+    t = g.tensor("a")
+    assert t is not None and g.read(t.start, t.end).tobytes() == payload[::-1]
+    g.close()
+    assert isinstance(GgufFile(image), GgufFile)
 
 
 def test_open_from_a_path_maps_the_file(tmp_path):
