@@ -40,7 +40,30 @@ def _agree(image):
     assert g.alignment == alignment and g.blob_len == len(image)
     got = g.tensors()
     assert [(t.name, t.ggml_type, t.shape, t.start, t.end) for t in got] == tensors
+    _same_metadata(g, kv)
     return g
+
+
+def _same_metadata(g, kv):
+    """Every value the restatement read (the last one of a repeated key), through the typed readers of the library."""
+    for key, v in kv.items():
+        if "\x00" in key:
+            continue  # keys are looked up as C strings
+        ty = v[0]
+        if ty == 9:
+            assert g.kv_type(key) == (9, v[1], len(v[2])), key
+            if v[1] == 5:
+                assert g.kv_i32s(key) == [x[1] for x in v[2]], key
+        elif ty == 8:
+            assert g.kv_string(key) == v[1], key
+        elif ty == 7:
+            assert g.kv_bool(key) == v[1], key
+        elif ty in (6, 12):
+            fmt, ifmt = ("<f", "<I") if ty == 6 else ("<d", "<Q")
+            if v[1] == v[1]:  # a NaN's payload is not kept by the restatement's float
+                assert g.kv_bits(key) == (struct.unpack(ifmt, struct.pack(fmt, v[1]))[0], ty), key
+        else:
+            assert g.kv_bits(key) == (v[1] & (2 ** 64 - 1), ty), key
 
 
 def _sample_file():
