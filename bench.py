@@ -2,7 +2,7 @@
 """Benchmark of the quantized matrix-product path on B200.
 
 One "step" is the matmul sweep of one decode token of a Llama-3-8B-shaped model
-in a Q4_K_M-style mix (BASELINE configs 2 and 3): per layer attn_q/attn_k/
+in a Q4_K_M-style mix (benchmark configs 2 and 3): per layer attn_q/attn_k/
 attn_output/ffn_gate/ffn_up as Q4_K and attn_v/ffn_down as Q6_K, 32 layers, plus
 the Q6_K lm_head -- 225 decode GEMVs over 4 875 853 824 packed weight bytes, every
 matrix distinct, so each step streams far more than the 126 MB L2 and no flush
@@ -19,7 +19,7 @@ one copy out per step; at N > 1 this is `e2e`);
 `roofline` is the kernel the timed region consists of (the persistent program
 kernel; the Q4_K single-product launches are reported beside it) against the
 measured HBM peak; `cpu_baseline` is the CPU oracle (AVX2 row kernels, reference threading)
-on a bounded sample of the same sweep.  `configs` holds the other BASELINE configurations (1: the
+on a bounded sample of the same sweep.  `configs` holds the other benchmark configurations (1: the
 single Q8_0 product; every format's decode kernel on one large matrix; 4: the chunk GEMM; 5: the
 routed-expert layer, at N > 1 expert-parallel over peer stores beside the NCCL all-to-all form;
 3: the walk on the device).  `--case gemv|moe|session` runs one small case for profiling.
@@ -217,7 +217,7 @@ def timed(stream, fn, reps):
 
 
 def session_leg(ex, mats, specs_all):
-    """BASELINE config 3 as one sequence on the device-resident walk (llr_session_*): 512 random prompt tokens, then
+    """benchmark config 3 as one sequence on the device-resident walk (llr_session_*): 512 random prompt tokens, then
     128 greedy tokens.  Wall time through the C ABI with host token ids in and out; prefill with the automatic kernel
     choice (tensor-core GEMM for the 512-row chunk), decode with the f32-faithful decode kernels."""
     from llama_rust_b200 import Session, synth
@@ -244,7 +244,7 @@ def session_leg(ex, mats, specs_all):
 
 
 def config_legs(ex, stream, peak_hbm, peaks):
-    """Driver-visible numbers for BASELINE configs 1, 4 and 5 on one GPU (device time, CUDA events):
+    """Driver-visible numbers for benchmark configs 1, 4 and 5 on one GPU (device time, CUDA events):
     config 1 the single Q8_0 product, every format's decode kernel on one large matrix, config 4 the chunk GEMM (tensor-core path, 16-bit operands) for
     four formats at three batch sizes, config 5 the routed-expert layer at 64 and 512 tokens."""
     import torch
@@ -322,7 +322,7 @@ def config_legs(ex, stream, peak_hbm, peaks):
 
 
 def moe_leg(ex, group, rank, world, peak_hbm, sustained, token_counts=(64, 512)):
-    """Routed-expert layer of BASELINE config 5 (8 experts, top-2, 4096 / 14336, Q4_K experts, F32 router) through
+    """Routed-expert layer of benchmark config 5 (8 experts, top-2, 4096 / 14336, Q4_K experts, F32 router) through
     the host-buffer entry point with pinned buffers: wall ms per layer call.  world > 1: experts striped e % world, tokens
     sharded on the device, routed rows and results exchanged by peer stores inside the library (llr_moe_ep_*); the same
     layer over NCCL all-to-all is timed beside it; every rank compares its tokens' outputs bit for bit with the
@@ -774,7 +774,7 @@ def check_sharded(ex, sharded, offs, shape_of, xin, phase_of, M, world, rank, sp
 def run_case(args):
     """One small case for profiling (the full sweep holds 5 GB): prints one JSON line.
       --case gemv    --dtype D --rows R --cols C --m M --reps N --copies K [--path P]   device-pointer products round-robin over K matrices
-      --case moe     --tokens T                                                        the routed-expert layer of BASELINE config 5 (2 warm-up + 5 timed calls)
+      --case moe     --tokens T                                                        the routed-expert layer of benchmark config 5 (2 warm-up + 5 timed calls)
       --case session --prompt P --gen G [--layers L] [--experts E]                     the device-resident walk on an 8B-shaped model of L layers
                                                                                        (E routed experts per layer, two per token, instead of the dense FFN)"""
     import torch
@@ -841,7 +841,7 @@ def main():
     ap.add_argument("--m", type=int, default=1, help="activation rows per matmul (1..8)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
-    ap.add_argument("--no-configs", action="store_true", help="skip the legs for BASELINE configs 1, 4 and 5")
+    ap.add_argument("--no-configs", action="store_true", help="skip the legs for benchmark configs 1, 4 and 5")
     ap.add_argument("--mode", default="program", choices=["program", "calls"],
                     help="program: the sweep as one persistent launch; calls: one launch per matmul")
     ap.add_argument("--case", default=None, choices=["gemv", "moe", "session"], help="run one small case instead of the sweep (for profiling)")

@@ -30,7 +30,7 @@ import torch.distributed as dist
 
 
 def row_range(rows: int, world: int, rank: int) -> tuple[int, int]:
-    """Contiguous, balanced row range of `rank`; exact for every BASELINE shape (rows % 8 == 0)."""
+    """Contiguous, balanced row range of `rank`; exact for every benchmark shape (rows % 8 == 0)."""
     return rows * rank // world, rows * (rank + 1) // world
 
 

@@ -1,4 +1,4 @@
-"""Generates tests/golden/config3_golden.json: the greedy tokens of BASELINE config 3 as the CPU
+"""Generates tests/golden/config3_golden.json: the greedy tokens of benchmark config 3 as the CPU
 oracle (AVX2 restatement of the reference's row kernels + the reference's host walk) produces
 them.  Llama-3-8B-shaped random-init model, Q4_K_M-style mix, weights from the seeded host
 generator (bit-identical to the device generator), 512 uniform-random prompt ids, 128 greedy

@@ -53,7 +53,7 @@ def check_boundary(actual, expected, name):
 
 def check_kernel(actual, cpu, name, tol=1e-5):
     """The reference's CPU-kernel metric, quant.rs:10315: |y - e| / (1 + |e|) < 1e-5.
-    Meaningful for short rows only: at the BASELINE sizes the reference's own scalar
+    Meaningful for short rows only: at the benchmark sizes the reference's own scalar
     and SIMD kernels differ by 1e-4 .. 7e-4 in this metric (see check_gemv)."""
     a = np.asarray(actual, np.float64).ravel()
     e = np.asarray(cpu, np.float64).ravel()
@@ -87,7 +87,7 @@ def check_gemv(actual, cpu, exact, abs_sum, n, name):
     (quant.rs:10315) is returned for the record but not asserted at these sizes: for a
     near-zero output of a long row it measures the f32 summation noise of the CPU kernel
     itself -- the reference's own scalar and AVX2 kernels differ by 1e-4 .. 7e-4 in it on
-    the BASELINE shapes, and its fixtures that use it are a few blocks long."""
+    the benchmark shapes, and its fixtures that use it are a few blocks long."""
     a = np.asarray(actual, np.float64).reshape(np.shape(exact))
     c = np.asarray(cpu, np.float64).reshape(np.shape(exact))
     assert np.all(np.isfinite(a)), name
@@ -102,7 +102,7 @@ def check_gemv(actual, cpu, exact, abs_sum, n, name):
 
 
 def random_packed(rng, kind, rows, cols, scale_mode="normal"):
-    """Uniform random quant bits with |N|*0.01 binary16 scales (BASELINE configs)."""
+    """Uniform random quant bits with |N|*0.01 binary16 scales (benchmark configs)."""
     be, bb = orc.block_elems(kind), orc.block_bytes(kind)
     if be == 1:
         v = (rng.standard_normal(rows * cols) * 0.02).astype(np.float32)

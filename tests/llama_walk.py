@@ -1,4 +1,4 @@
-"""Test harness for BASELINE config 3: the dense Llama walk of the reference (host code in the
+"""Test harness for benchmark config 3: the dense Llama walk of the reference (host code in the
 oracle, langtax/src/decode.rs:2710-3097) driven either by the oracle's CPU matrix products or,
 through callbacks, by the CUDA executor.  The host ops are literally the same code in both
 runs, so any difference in tokens or logits comes from the matrix products alone."""

@@ -40,7 +40,7 @@ def test_row_bytes_matches_reference_table(lib, orc):
     for kind in (0, 1, 2, 5, 6, 7, 12, 13, 17, 18, 19):
         for cols in (0, 256, 4096, 14336):
             assert ex.row_bytes(kind, cols) == orc.row_bytes(kind, cols)
-    # BASELINE shapes (quant.rs:86-163)
+    # benchmark shapes (quant.rs:86-163)
     assert ex.row_bytes(13, 4096) == 4352 and ex.row_bytes(17, 4096) == 2304
     assert ex.row_bytes(17, 14336) == 8064 and ex.row_bytes(19, 4096) == 3360
     assert ex.row_bytes(19, 14336) == 11760 and ex.row_bytes(6, 4096) == 2816 and ex.row_bytes(7, 4096) == 3072

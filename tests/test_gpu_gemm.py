@@ -109,7 +109,7 @@ def test_operand_format_follows_weight_range(ex, orc):
                                             ("Q4_0", 4096, 4096), ("Q5_K", 4096, 4096), ("Q4_1", 4096, 4096)])
 @pytest.mark.parametrize("tokens", [64, 256, 1024])
 def test_config4_full_size_shapes_on_sampled_rows(ex, orc, name, rows, cols, tokens):
-    """BASELINE config 4 at its full sizes (Q8_0 4096x14336 runs split along K).  The device
+    """benchmark config 4 at its full sizes (Q8_0 4096x14336 runs split along K).  The device
     computes the whole product; the CPU f32 row kernels are run on a sample of the weight rows
     (the first and last row tile and 64 rows spread over the matrix), which keeps the CPU side
     to seconds, and the same bounds as above are asserted on those outputs.  Every output is

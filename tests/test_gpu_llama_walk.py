@@ -1,4 +1,4 @@
-"""BASELINE config 3: greedy-token identity of the dense Llama walk, CUDA executor vs CPU
+"""benchmark config 3: greedy-token identity of the dense Llama walk, CUDA executor vs CPU
 reference kernels.  A small model is walked by both sides live; the full Llama-3-8B-shaped
 model (32 layers, 4.9 GB of packed weights, 512-token prompt, 128 greedy tokens) is compared
 with the ids the CPU oracle produced when tests/golden/make_config3.py was run.

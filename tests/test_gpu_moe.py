@@ -200,7 +200,7 @@ def test_expert_parallel_wait_for_an_absent_rank_runs_out_and_the_executor_stays
 
 
 def test_config5_full_size_layer(orc):
-    """BASELINE config 5 at its full size: 8 experts, top-2, 4096 / 14336, Q4_K experts generated on
+    """benchmark config 5 at its full size: 8 experts, top-2, 4096 / 14336, Q4_K experts generated on
     the device from seeds (792 MB), F32 router, 64 tokens.  One CPU walk of the layer (the
     oracle, 4.5e10 FLOP) is compared with the f32-faithful decode path and with the automatic
     choice (grouped tensor-core launches)."""
@@ -229,7 +229,7 @@ def test_config5_full_size_layer(orc):
 
 
 def test_config5_full_size_layer_512_tokens_on_sampled_tokens(orc):
-    """BASELINE config 5 with 512 tokens (1024 routed rows, about 128 per expert: the wide grouped tiles).  The
+    """benchmark config 5 with 512 tokens (1024 routed rows, about 128 per expert: the wide grouped tiles).  The
     device runs the whole layer; a token's output depends on that token alone, so the CPU walk of the layer is run
     on every eighth token (64 tokens) and compared with the device's rows for those tokens: routing identical, the
     f32-faithful path within 3e-5 of the output scale, the grouped tensor-core path within 2e-2."""

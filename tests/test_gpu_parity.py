@@ -275,7 +275,7 @@ def test_tensor_core_gemv_one_nonzero_activation_at_every_column(ex, orc, name):
 
 
 def test_config1_q8_0_4096_gemv_seed0(ex, orc):
-    """BASELINE config 1: Q8_0 4096x4096, x ~ N(0,1), seed 0, M = 1, every kernel family."""
+    """benchmark config 1: Q8_0 4096x4096, x ~ N(0,1), seed 0, M = 1, every kernel family."""
     from llama_rust_b200 import synth
     w = synth.packed_matrix(Q8_0, 4096, 4096, synth.tensor_seed(0, "config1.w"))
     x = synth.activations(4096, synth.tensor_seed(0, "config1.x"))
@@ -295,7 +295,7 @@ def test_config1_q8_0_4096_gemv_seed0(ex, orc):
 @pytest.mark.parametrize("name,rows,cols", [("Q4_K", 4096, 4096), ("Q4_K", 1024, 4096), ("Q4_K", 2048, 14336),
                                             ("Q6_K", 1024, 4096), ("Q6_K", 1024, 14336), ("Q6_K", 4008, 4096)])
 def test_config2_decode_shapes(ex, orc, name, rows, cols):
-    """BASELINE config 2 shapes (row counts trimmed where the CPU oracle would take long), M = 1, 2, 4, 8."""
+    """benchmark config 2 shapes (row counts trimmed where the CPU oracle would take long), M = 1, 2, 4, 8."""
     from llama_rust_b200 import synth
     kind = ALL[name]
     seed = synth.tensor_seed(2, f"config2.{name}.{rows}x{cols}")
@@ -312,7 +312,7 @@ def test_config2_decode_shapes(ex, orc, name, rows, cols):
 
 @pytest.mark.parametrize("name,rows,cols", [("Q4_K", 14336, 4096), ("Q4_K", 4096, 14336), ("Q6_K", 128256, 4096)])
 def test_config2_full_row_counts_on_sampled_rows(ex, orc, name, rows, cols):
-    """BASELINE config 2 at its true row counts (gate/up, down, lm_head), M = 1, 2, 4, 8.  The device computes the
+    """benchmark config 2 at its true row counts (gate/up, down, lm_head), M = 1, 2, 4, 8.  The device computes the
     whole product; the CPU row kernels run on a sample of the weight rows (the first and last 128 and 256 spread
     over the matrix).  Every output must be finite; the sampled ones are held to the full parity bar.  The
     per-element figures are printed for the record (pytest -rP shows them)."""
@@ -337,7 +337,7 @@ def test_config2_full_row_counts_on_sampled_rows(ex, orc, name, rows, cols):
 
 
 def test_gemv_is_linear_and_deterministic(ex):
-    """Size-independent properties on a BASELINE-size matrix (gate/up 14336x4096 Q4_K)."""
+    """Size-independent properties on a benchmark-size matrix (gate/up 14336x4096 Q4_K)."""
     from llama_rust_b200 import synth
     m = ex.synth(Q4_K, 14336, 4096, 7)
     x1, x2 = synth.activations(4096, 1), synth.activations(4096, 2)

@@ -266,7 +266,7 @@ def test_session_validates_its_model_and_calls():
 
 
 def test_llama3_8b_shape_centered_greedy_tokens_on_the_device():
-    """BASELINE config 3 with the whole walk on the device: 512 prompt tokens, 128 greedy tokens, f32-faithful products,
+    """benchmark config 3 with the whole walk on the device: 512 prompt tokens, 128 greedy tokens, f32-faithful products,
     against the CPU tokens of tests/golden.  Asserted up to the first step the CPU walk decides by less than 1e-3 of the
     logit scale (its two near-ties); the outcome for all 128 is printed."""
     if not os.path.exists(GOLDEN_CENTERED):
