@@ -416,7 +416,7 @@ typedef struct llr_moe_layer {
 int llr_moe_ffn(llr_exec* exec, const llr_moe_layer* layer, size_t tokens, const float* x, size_t x_len,
                 float* out, size_t out_len, int32_t* sel_ids, float* sel_w);
 /* The two device-pointer halves of the layer, for expert parallelism with an exchange of routed rows between
- * ranks [the north star's all-to-all of token rows; expertvm/src/place.rs:71-75 gives the owner of an expert]:
+ * ranks [an all-to-all of token rows; expertvm/src/place.rs:71-75 gives the owner of an expert]:
  * llr_moe_route_device: router product, softmax, top-k and router weights for `tokens` rows at x_dev;
  *   ids_dev / w_dev receive tokens * n_used entries in top-k order (only layer->router, n_expert, n_used and
  *   norm_w are read).  Enqueued on the executor's stream, no synchronization.
@@ -431,7 +431,7 @@ int llr_moe_experts_device(llr_exec* exec, const llr_moe_layer* layer, const uin
 
 /* Expert parallelism with the exchange inside the library: experts striped over the ranks (expert e on rank
  * e % world, expertvm/src/place.rs:71-75), tokens sharded over the ranks, routed rows and their results moved
- * between GPUs by peer stores from the kernels that gather and scatter them [the north star's all-to-all of token
+ * between GPUs by peer stores from the kernels that gather and scatter them [the all-to-all of token
  * rows; grouped_routed_ffn decode.rs:10006, scatter_expert_rows :10263].  One process per GPU (or several
  * executors of one process); no collective call, no host hop for rows; one small device-to-host copy of row counts
  * per run sizes the expert launches.
