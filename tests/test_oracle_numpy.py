@@ -105,3 +105,90 @@ def test_vectorized_decoder_on_the_reference_fixture_blocks(orc):
         w = np.concatenate([np.asarray(f.pack_row(r), np.uint8).ravel() for r in range(rows)])
         want = orc.dequant_matrix(f.kind, rows, f.cols, w)
         assert np.array_equal(dequant(f.name, w).reshape(rows, f.cols).view(np.uint32), want.view(np.uint32)), f.name
+
+
+@pytest.mark.parametrize("norm_w", [True, False])
+def test_routed_layer_in_float64_numpy_agrees_with_the_oracle(orc, norm_w):
+    """softmax_routed_layer (decode.rs:9938) written once more in float64 numpy from the reference's text: softmax over
+    all experts, the n_used largest (ties to the lower index, topk_into :11363), weights divided by their clamped sum when
+    norm_w (fill_router_weights :11392), and out = sum_j w_j * down_e(silu(gate_e x) * up_e x).  Same selections as the
+    oracle, weights and outputs within float32 rounding."""
+    from helpers import F32 as KIND_F32, Q4_K
+    rng = np.random.default_rng(31 + int(norm_w))
+    n_expert, n_used, n_embd, n_ff, tokens = 6, 2, 256, 512, 9
+    router = (rng.standard_normal((n_expert, n_embd)) * 0.1).astype(np.float32)
+    packs = {k: [random_packed(rng, Q4_K, r, c) for _ in range(n_expert)]
+             for k, (r, c) in {"gate": (n_ff, n_embd), "up": (n_ff, n_embd), "down": (n_embd, n_ff)}.items()}
+    x = rng.standard_normal((tokens, n_embd)).astype(np.float32)
+    out, ids, w = orc.moe_ffn(n_used, norm_w, KIND_F32, router.view(np.uint8).reshape(-1), Q4_K, packs["gate"], packs["up"],
+                              packs["down"], n_embd, n_ff, x)
+    dense = {k: [orc.dequant_matrix(Q4_K, r, c, p).astype(np.float64) for p in packs[k]]
+             for k, (r, c) in {"gate": (n_ff, n_embd), "up": (n_ff, n_embd), "down": (n_embd, n_ff)}.items()}
+    for t in range(tokens):
+        logits = router.astype(np.float64) @ x[t].astype(np.float64)
+        p = np.exp(logits - logits.max())
+        p /= p.sum()
+        order = sorted(range(n_expert), key=lambda e: (-p[e], e))[:n_used]
+        assert list(ids[t]) == order, t
+        wt = p[order]
+        if norm_w:
+            wt = wt / max(wt.sum(), 1e-30)  # the clamp only matters for a vanishing sum
+        assert np.allclose(w[t], wt, rtol=2e-5, atol=0), t
+        acc = np.zeros(n_embd)
+        for e, we in zip(order, wt):
+            g, u = dense["gate"][e] @ x[t], dense["up"][e] @ x[t]
+            acc += we * (dense["down"][e] @ (g / (1.0 + np.exp(-g)) * u))
+        scale = max(1.0, float(np.abs(acc).max()))
+        assert np.abs(out[t] - acc).max() <= 2e-4 * scale, (t, float(np.abs(out[t] - acc).max()), scale)
+
+
+def test_dense_walk_in_float64_numpy_agrees_with_the_oracle(orc):
+    """Llama::forward_layers (decode.rs:2737-3097) once more in float64 numpy from the reference's text: RMSNorm with unit
+    weights, rotary embedding over adjacent pairs at angle pos * base^(-2i / head_dim) (rope, :11578), grouped-query
+    attention with scores scaled by 1/sqrt(head_dim) over the positions up to the token's own, SwiGLU, residual adds,
+    the last row's logits.  The oracle's walk is what every session test compares with; its pairing, scaling and head
+    mapping must not be a private reading."""
+    import llama_walk as lw
+    from helpers import Q4_K
+    cfg = dict(n_layer=2, n_embd=256, n_head=4, n_head_kv=2, head_dim=64, n_ff=256, n_vocab=40)
+    rng = np.random.default_rng(23)
+    tl = lw.tensor_list(cfg)
+    kinds = [Q4_K] * len(tl)
+    weights = [lw.center_q4k(random_packed(rng, Q4_K, r, c)) for _, _, r, c in tl]
+    embd = lw.center_q4k(random_packed(rng, Q4_K, cfg["n_vocab"], cfg["n_embd"]))
+    prompt = np.array([3, 17, 5, 39, 0, 8, 21], np.int32)
+    want = lw.run_cpu(cfg, 16, weights, embd, prompt, 0, want_logits=True, kinds=kinds)[2].astype(np.float64)
+
+    E, H, HKV, HD = cfg["n_embd"], cfg["n_head"], cfg["n_head_kv"], cfg["head_dim"]
+    W = [orc.dequant_matrix(Q4_K, r, c, w).astype(np.float64) for (_, _, r, c), w in zip(tl, weights)]
+    x = orc.dequant_matrix(Q4_K, cfg["n_vocab"], E, embd).astype(np.float64)[prompt]
+    n = len(prompt)
+
+    def rms(v):
+        return v / np.sqrt((v * v).mean(axis=-1, keepdims=True) + 1e-5)
+
+    def rope(v, heads):  # v [n, heads * HD]
+        v = v.reshape(n, heads, HD // 2, 2)
+        ang = np.arange(n)[:, None] * (10000.0 ** (-2.0 * np.arange(HD // 2) / HD))[None, :]
+        c, s = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+        return np.stack([v[..., 0] * c - v[..., 1] * s, v[..., 0] * s + v[..., 1] * c], axis=-1).reshape(n, heads * HD)
+
+    for li in range(cfg["n_layer"]):
+        wq, wk, wv, wo, wg, wu, wd = W[7 * li:7 * li + 7]
+        xn = rms(x)
+        q, k, v = rope(xn @ wq.T, H).reshape(n, H, HD), rope(xn @ wk.T, HKV).reshape(n, HKV, HD), (xn @ wv.T).reshape(n, HKV, HD)
+        att = np.zeros((n, H, HD))
+        for h in range(H):
+            kv = h // (H // HKV)
+            sc = q[:, h] @ k[:, kv].T / np.sqrt(HD)
+            sc = np.where(np.tril(np.ones((n, n), bool)), sc, -np.inf)
+            p = np.exp(sc - sc.max(axis=1, keepdims=True))
+            att[:, h] = (p / p.sum(axis=1, keepdims=True)) @ v[:, kv]
+        x = x + att.reshape(n, H * HD) @ wo.T
+        xn = rms(x)
+        g = xn @ wg.T
+        x = x + (g / (1.0 + np.exp(-g)) * (xn @ wu.T)) @ wd.T
+    got = rms(x[-1]) @ W[-1].T
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= 1e-4 * scale, (float(np.abs(got - want).max()), float(scale))
+    assert int(np.argmax(got)) == int(np.argmax(want))
