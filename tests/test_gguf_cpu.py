@@ -225,6 +225,28 @@ def test_a_tensor_name_with_nul_bytes_crosses_the_boundary_whole():
     assert isinstance(GgufFile(image), GgufFile)
 
 
+def test_stable_keys_are_the_blob_ranges_of_rows_and_parts():
+    """quant_mat / quant_mat_rows (decode.rs:9612-9713): rows [first, first + n) of part p of a tensor start at
+    start + (p * rows + first) * row_bytes; the key of that slice is (open file, that byte offset).  Host arithmetic
+    only: no executor is involved."""
+    from llama_rust_b200 import NativeCudaError
+    image, _ = _sample_file()
+    g = _agree(image)
+    w, e, nrm = g.tensor("w_q4k"), g.tensor("exps"), g.tensor("norm")
+    file_id = g.key("w_q4k")[0]
+    assert g.key("w_q4k") == (file_id, w.start) and g.key("w_q4k", 0, 1, 1) == (file_id, w.start + 144)
+    assert g.key("exps", 2) == (file_id, e.start + 2 * 4 * 210) and g.key("exps", 1, 3, 1) == (file_id, e.start + (4 + 3) * 210)
+    assert g.key("exps", 0, 0, 4) == g.key("exps") and g.key("norm") == (file_id, nrm.start)
+    assert e.start + 3 * 4 * 210 == e.end
+    for bad in (("exps", 3), ("exps", 0, 4, 1), ("exps", 0, 2, 3), ("exps", 0, 1, 0), ("w_q4k", 1), ("absent",), ("x_q8k",)):
+        with pytest.raises(NativeCudaError):
+            g.key(*bad)
+    other = _agree(image)
+    assert other.key("w_q4k")[0] != file_id  # another open file, another key space
+    other.close()
+    g.close()
+
+
 def test_open_from_a_path_maps_the_file(tmp_path):
     from llama_rust_b200.gguf import GgufError, GgufFile
     image, payload = _sample_file()
