@@ -192,3 +192,25 @@ def test_dense_walk_in_float64_numpy_agrees_with_the_oracle(orc):
     scale = np.abs(want).max()
     assert np.abs(got - want).max() <= 1e-4 * scale, (float(np.abs(got - want).max()), float(scale))
     assert int(np.argmax(got)) == int(np.argmax(want))
+
+
+@pytest.mark.parametrize("name", ["Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q4_K", "Q5_K", "Q6_K"])
+def test_row_products_against_the_vectorized_decoder_in_float64(orc, name):
+    """y = W x with W from the numpy decoder above, accumulated in float64: the oracle's float64 product agrees to
+    float64 rounding, and its f32 row kernels (scalar order and AVX2 order) stay within the forward error bound
+    gamma(n) * sum |w_i x_i| of an n-term f32 sum."""
+    kind = ALL[name]
+    rng = np.random.default_rng(0xD07 + kind)
+    rows, cols, tokens = 7, 2048, 3
+    w = random_packed(rng, kind, rows, cols)
+    x = rng.standard_normal((tokens, cols)).astype(np.float32)
+    dense = dequant(name, w).reshape(rows, cols).astype(np.float64)
+    want = x.astype(np.float64) @ dense.T                      # [tokens, rows]
+    mass = np.abs(x).astype(np.float64) @ np.abs(dense).T
+    f64 = orc.gemm_f64(kind, cols, tokens, w, x.ravel(), rows).reshape(tokens, rows)
+    assert np.abs(f64 - want).max() <= 1e-12 * mass.max()
+    u = 2.0 ** -24
+    bound = (cols + 3) * u / (1 - (cols + 3) * u) * mass
+    for simd in (False, True):
+        y = orc.gemm(kind, cols, tokens, w, x.ravel(), rows, simd=simd).reshape(tokens, rows).astype(np.float64)
+        assert np.all(np.abs(y - want) <= bound), (name, simd, float((np.abs(y - want) / bound).max()))
